@@ -1,0 +1,461 @@
+"""Bounded-cache differential attention on B200.
+
+``CoDAGQALandmarkPerf2`` keeps the constructor, parameter names and the methods
+``init_state / prefill_chunked / step / attend_step / cache_bytes / reset_metrics`` of upstream
+``src/coda_gqa_l/attention.py:72-760``; the state object keeps the upstream field names.  The
+projections are PyTorch GEMMs; everything between them (RoPE, noise-query rotation, gate and
+lambda sigmoids, the two-stream attention with its subtraction/RMSNorm epilogue, candidate
+selection, bank routing, ring maintenance) runs in the sm_100a kernels of libcoda_b200.so, reached
+through the C ABI of include/coda_b200.h.  There is no other compute path: tensors must be CUDA
+tensors in float32 or bfloat16, and the module must be in eval mode.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib
+from ._lib import LayerCfg, RingPos, StatePtrs, check, lib
+from .primitives import HeadwiseRMSNorm, RotaryEmbedding
+from .state import CoDAGQALandmarkStatePerf2, allocate_state
+
+__all__ = ["CoDAGQALandmarkPerf2", "CoDAGQALandmarkStatePerf2"]
+
+_DT = {torch.float32: _lib.CODA_F32, torch.bfloat16: _lib.CODA_BF16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class CoDAGQALandmarkPerf2(nn.Module):
+    """Differential attention (signal minus lambda-gated, theta-rotated noise stream) over a
+    bounded per-layer state: a W-slot ring of recent tokens, an Me-slot exact landmark bank with
+    LRU replacement and an Ms-slot summary bank of EMA prototypes."""
+
+    def __init__(
+        self,
+        *,
+        embed_dim: int,
+        num_heads: int,
+        num_kv_heads: int,
+        window: int,
+        num_landmarks_exact: int,
+        num_landmarks_summary: int,
+        rope_base: float = 10_000.0,
+        lambda_init_bias: float = -6.0,
+        theta_init: float = math.pi / 2,
+        write_policy: str = "gated",
+        write_gate_init_bias: float = -2.0,
+        write_gate_threshold_exact: float = 0.10,
+        write_gate_threshold_summary: float = 0.05,
+        exact_match_threshold: float = 0.90,
+        exact_novelty_threshold: float = 0.70,
+        exact_refresh_on_hit: bool = False,
+        exact_candidates_per_block: int = 8,
+        summary_eta_init_logit: float = -3.0,
+        summary_candidates_per_block: int = 64,
+        summary_overwrite_on_insert: bool = True,
+        min_landmarks_exact: Optional[int] = None,
+        max_landmarks_exact: Optional[int] = None,
+        min_landmarks_summary: Optional[int] = None,
+        max_landmarks_summary: Optional[int] = None,
+        expansion_t_max: int = 1_000_000,
+        mem_init: str = "random_normal",
+        mask_unused_memory: bool = True,
+        detach_evicted: bool = True,
+        eps: float = 1e-6,
+        collect_metrics: bool = False,
+        head_norm_mode: str = "full",
+        rope_interleaved: bool = True,
+    ):
+        super().__init__()
+        # validation messages as upstream attention.py:143-157,176-181,233
+        if embed_dim % num_heads != 0:
+            raise ValueError("embed_dim must be divisible by num_heads")
+        if num_heads % num_kv_heads != 0:
+            raise ValueError("num_heads must be divisible by num_kv_heads")
+        if window <= 0:
+            raise ValueError("window must be positive")
+        if num_landmarks_exact < 0 or num_landmarks_summary < 0:
+            raise ValueError("num_landmarks_* must be non-negative")
+        self.embed_dim = int(embed_dim)
+        self.num_heads = int(num_heads)
+        self.num_kv_heads = int(num_kv_heads)
+        self.head_dim = self.embed_dim // self.num_heads
+        if self.head_dim % 2 != 0:
+            raise ValueError("head_dim must be even (RoPE requirement)")
+        self.lf_start = self.head_dim // 2
+        self.lf_dim = self.head_dim - self.lf_start
+        self.energy_scale = math.sqrt(self.head_dim / self.lf_dim)
+        self.window = int(window)
+
+        me, ms = int(num_landmarks_exact), int(num_landmarks_summary)
+        self.Me_min = int(min_landmarks_exact) if min_landmarks_exact is not None else me
+        self.Me_max = int(max_landmarks_exact) if max_landmarks_exact is not None else me
+        self.Ms_min = int(min_landmarks_summary) if min_landmarks_summary is not None else ms
+        self.Ms_max = int(max_landmarks_summary) if max_landmarks_summary is not None else ms
+        self.expansion_t_max = int(expansion_t_max)
+        if self.Me_min > self.Me_max:
+            raise ValueError(f"min_landmarks_exact ({self.Me_min}) > max ({self.Me_max})")
+        if self.Ms_min > self.Ms_max:
+            raise ValueError(f"min_landmarks_summary ({self.Ms_min}) > max ({self.Ms_max})")
+        if self.Me_min < 0 or self.Ms_min < 0:
+            raise ValueError("min_landmarks_* must be non-negative")
+        self.Me, self.Ms = self.Me_max, self.Ms_max
+        self.Lbuf = self.window + self.Me + self.Ms
+
+        # Parameters are created in upstream's order (attention.py:189-234) so that the same
+        # torch.manual_seed gives the same default weights.
+        H, Hkv, Dh = self.num_heads, self.num_kv_heads, self.head_dim
+        self.q_proj = nn.Linear(self.embed_dim, H * Dh, bias=False)
+        self.k_proj = nn.Linear(self.embed_dim, Hkv * Dh, bias=False)
+        self.v_proj = nn.Linear(self.embed_dim, Hkv * Dh, bias=False)
+        self.theta = nn.Parameter(torch.full((H, Dh // 2), float(theta_init)))
+        self.lambda_proj = nn.Linear(self.embed_dim, H, bias=True)
+        nn.init.constant_(self.lambda_proj.bias, float(lambda_init_bias))
+        self.write_policy = write_policy
+        self.write_proj = nn.Linear(self.embed_dim, 1, bias=True)
+        nn.init.zeros_(self.write_proj.weight)
+        nn.init.constant_(self.write_proj.bias, float(write_gate_init_bias))
+        self.write_gate_threshold_exact = float(write_gate_threshold_exact)
+        self.write_gate_threshold_summary = float(write_gate_threshold_summary)
+        self.exact_match_threshold = float(exact_match_threshold)
+        self.exact_novelty_threshold = float(exact_novelty_threshold)
+        self.exact_refresh_on_hit = bool(exact_refresh_on_hit)
+        self.exact_candidates_per_block = int(max(0, exact_candidates_per_block))
+        self.summary_eta_logit = nn.Parameter(torch.full((Hkv,), float(summary_eta_init_logit)))
+        self.summary_candidates_per_block = int(max(0, summary_candidates_per_block))
+        self.summary_overwrite_on_insert = bool(summary_overwrite_on_insert)
+        self.mem_init = mem_init
+        self.mask_unused_memory = bool(mask_unused_memory)
+        self.detach_evicted = bool(detach_evicted)
+        self.collect_metrics = bool(collect_metrics)
+        self.rope_interleaved = bool(rope_interleaved)
+        self.rope_base = float(rope_base)
+        self.rope = RotaryEmbedding(Dh, base=float(rope_base))
+        self.head_norm_mode = head_norm_mode
+        if head_norm_mode == "full":
+            self.head_norm = HeadwiseRMSNorm(Dh, eps=eps)
+        elif head_norm_mode == "identity":
+            self.head_norm = nn.Identity()
+        else:
+            raise ValueError(f"head_norm_mode must be 'full' or 'identity', got {head_norm_mode!r}")
+        self.eps = float(eps)
+        self.o_proj = nn.Linear(H * Dh, self.embed_dim, bias=False)
+
+        self._cfg_cache: Dict[tuple, LayerCfg] = {}
+        self._const_cache: Dict[tuple, tuple] = {}
+        self._scratch: Dict[tuple, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ state
+    def init_state(self, *, batch_size: int, device, dtype: torch.dtype,
+                   mem_init: Optional[str] = None) -> CoDAGQALandmarkStatePerf2:
+        """Fresh state in one arena allocation (upstream attention.py:247-338).
+
+        The bank slots are filled with N(0, 0.02^2) in upstream's order (exact K, exact V, summary
+        K low-frequency band, summary V) from the generator of ``device``; a CPU device may be
+        given to stage a state (e.g. to reproduce a CPU-seeded initial state) and moved with
+        :func:`state_to`, but the compute methods only accept CUDA states."""
+        if self.Me_min != self.Me_max or self.Ms_min != self.Ms_max:
+            raise NotImplementedError("dynamic bank expansion (min_landmarks_* != max_landmarks_*) is not supported")
+        if self.collect_metrics:
+            raise NotImplementedError("collect_metrics=True is not supported by the CUDA path")
+        if dtype not in _DT:
+            raise RuntimeError(f"unsupported dtype {dtype}: the CUDA kernels handle float32 and bfloat16")
+        B, W, Me, Ms = int(batch_size), self.window, self.Me, self.Ms
+        st = allocate_state(B, self.num_kv_heads, self.head_dim, W, Me, Ms, torch.device(device), dtype)
+        mode = self.mem_init if mem_init is None else mem_init
+        if mode == "random_normal":
+            if Me > 0:
+                st.k_buf[:, :, W:W + Me, :].normal_(mean=0.0, std=0.02)
+                st.v_buf[:, :, W:W + Me, :].normal_(mean=0.0, std=0.02)
+            if Ms > 0:
+                st.k_buf[:, :, W + Me:, self.lf_start:].normal_(mean=0.0, std=0.02)
+                st.v_buf[:, :, W + Me:, :].normal_(mean=0.0, std=0.02)
+        elif mode != "zeros":
+            raise ValueError("mem_init must be 'zeros' or 'random_normal'")
+        st.active_exact = self.Me_min if Me > 0 else 0
+        st.active_summary = self.Ms_min if Ms > 0 else 0
+        if Me > 0:
+            st._exact_v_norm.copy_(F.normalize(st.v_buf[:, :, W:W + Me, :], dim=-1, eps=1e-6))
+        if Ms > 0:
+            st._sum_lf_k_norm.copy_(F.normalize(st.k_buf[:, :, W + Me:, self.lf_start:], dim=-1, eps=1e-6))
+        return st
+
+    # ------------------------------------------------------------------ plumbing
+    def _require_ready(self, x: torch.Tensor, st: CoDAGQALandmarkStatePerf2) -> None:
+        if self.training:
+            raise RuntimeError("CoDAGQALandmarkPerf2 (B200) is inference-only: call .eval() first")
+        if not self.detach_evicted:
+            raise NotImplementedError("detach_evicted=False (autograd through bank updates) is not supported")
+        if not x.is_cuda:
+            raise RuntimeError("input must be a CUDA tensor: this implementation has no CPU path")
+        if x.dtype not in _DT:
+            raise RuntimeError(f"unsupported dtype {x.dtype}")
+        if st.k_buf.device != x.device or st.k_buf.dtype != x.dtype:
+            raise RuntimeError("state and input must share device and dtype")
+        if st.k_buf.shape != (x.shape[0], self.num_kv_heads, self.Lbuf, self.head_dim):
+            raise RuntimeError(f"state k_buf shape {tuple(st.k_buf.shape)} does not match this layer / batch")
+        for name in ("k_buf", "v_buf", "allowed", "g_recent", "mem_last_exact"):
+            t = getattr(st, name)
+            if not t.is_contiguous():
+                setattr(st, name, t.contiguous())
+        # routing caches may have been widened to fp32 by a serialisation helper: bring them back
+        if st._exact_v_norm is not None and (st._exact_v_norm.dtype != x.dtype or not st._exact_v_norm.is_contiguous()):
+            st._exact_v_norm = st._exact_v_norm.to(x.dtype).contiguous()
+        if st._sum_lf_k_norm is not None and (st._sum_lf_k_norm.dtype != x.dtype or not st._sum_lf_k_norm.is_contiguous()):
+            st._sum_lf_k_norm = st._sum_lf_k_norm.to(x.dtype).contiguous()
+        if st.g_recent.dtype != torch.float32:
+            st.g_recent = st.g_recent.float()
+
+    def _cfg(self, B: int, dtype: torch.dtype, st: CoDAGQALandmarkStatePerf2) -> LayerCfg:
+        adt = self.rope.inv_freq.dtype
+        key = (B, dtype, adt, st.active_exact, st.active_summary)
+        c = self._cfg_cache.get(key)
+        if c is None:
+            c = LayerCfg(
+                B=B, H=self.num_heads, Hkv=self.num_kv_heads, Dh=self.head_dim, W=self.window, Me=self.Me, Ms=self.Ms,
+                dtype=_DT[dtype], angle_dtype=_DT.get(adt, _lib.CODA_F32) if dtype != torch.float32 else _lib.CODA_F32,
+                rope_interleaved=int(self.rope_interleaved), head_norm_full=int(self.head_norm_mode == "full"),
+                mask_unused=int(self.mask_unused_memory), gated=int(self.write_policy != "none"),
+                refresh_on_hit=int(self.exact_refresh_on_hit), overwrite_on_insert=int(self.summary_overwrite_on_insert),
+                Te=self.exact_candidates_per_block, Ts=self.summary_candidates_per_block,
+                active_exact=int(st.active_exact), active_summary=int(st.active_summary),
+                tau_gate_exact=self.write_gate_threshold_exact, tau_gate_summary=self.write_gate_threshold_summary,
+                tau_match=self.exact_match_threshold, tau_novel=self.exact_novelty_threshold,
+                eps=self.eps, energy_scale=self.energy_scale)
+            self._cfg_cache[key] = c
+        return c
+
+    @staticmethod
+    def _ptrs(st: CoDAGQALandmarkStatePerf2) -> StatePtrs:
+        return StatePtrs(st.k_buf.data_ptr(), st.v_buf.data_ptr(), st.allowed.data_ptr(), st.g_recent.data_ptr(),
+                         st.mem_last_exact.data_ptr() if st.mem_last_exact.numel() else None,
+                         _p(st._exact_v_norm), _p(st._sum_lf_k_norm))
+
+    def _consts(self, device, dtype):
+        """(inv_freq fp32, cos(theta), sin(theta) in dtype, eta logits fp32, head-norm weight) cached per parameter version."""
+        nw = self.head_norm.weight if self.head_norm_mode == "full" else None
+        key = (device, dtype, self.theta.data_ptr(), self.theta._version, self.summary_eta_logit.data_ptr(),
+               self.summary_eta_logit._version, self.rope.inv_freq.data_ptr(), _p(nw), 0 if nw is None else nw._version)
+        hit = self._const_cache.get("k")
+        if hit is not None and hit[0] == key:
+            return hit[1]
+        th = self.theta.detach()
+        vals = (self.rope.inv_freq.detach().to(device=device, dtype=torch.float32).contiguous(),
+                torch.cos(th).to(device=device, dtype=dtype).contiguous(),
+                torch.sin(th).to(device=device, dtype=dtype).contiguous(),
+                self.summary_eta_logit.detach().to(device=device, dtype=torch.float32).contiguous(),
+                None if nw is None else nw.detach().to(device=device, dtype=dtype).contiguous())
+        self._const_cache["k"] = (key, vals)
+        return vals
+
+    def _project(self, x: torch.Tensor, need_kv: bool):
+        """q, k, v, lambda logits, gate logits as (B, L, features) tensors (upstream attention.py:396-410,508)."""
+        q = self.q_proj(x)
+        k = self.k_proj(x) if need_kv else None
+        v = self.v_proj(x) if need_kv else None
+        lam = self.lambda_proj(x)
+        gate = self.write_proj(x) if (need_kv and self.write_policy != "none") else None
+        return q, k, v, lam, gate
+
+    def _prep(self, cfg, L, pos, q, k, lam_logit, gate_logit, want_gate: bool, step_dev=None):
+        B = q.shape[0]
+        dev, dt = q.device, q.dtype
+        inv_freq, cos_t, sin_t, _, _ = self._consts(dev, dt)
+        qn = torch.empty((B, L, self.num_heads * self.head_dim), device=dev, dtype=dt)
+        lam = torch.empty((B, L, self.num_heads), device=dev, dtype=torch.float32)
+        g = torch.empty((B, L), device=dev, dtype=torch.float32) if want_gate else None
+        rp = RingPos(int(pos), 0, 0, step_dev)
+        check(lib.coda_b200_prep(
+            C.byref(cfg), L, rp,
+            q.data_ptr(), q.stride(0), q.stride(1),
+            _p(k), 0 if k is None else k.stride(0), 0 if k is None else k.stride(1),
+            qn.data_ptr(),
+            lam_logit.data_ptr(), lam_logit.stride(0), lam_logit.stride(1), lam.data_ptr(),
+            _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0),
+            0 if gate_logit is None else gate_logit.stride(1), _p(g),
+            inv_freq.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), _stream()), "coda_b200_prep")
+        return qn, lam, g
+
+    def _attend(self, cfg, st, Lq, q, qn, lam, k_blk, v_blk, out):
+        _, _, _, _, nw = self._consts(q.device, q.dtype)
+        ptrs = self._ptrs(st)
+        check(lib.coda_b200_attend(
+            C.byref(cfg), C.byref(ptrs), Lq,
+            q.data_ptr(), q.stride(0), q.stride(1), qn.data_ptr(), qn.stride(0), qn.stride(1),
+            lam.data_ptr(), lam.stride(0), lam.stride(1),
+            _p(k_blk), 0 if k_blk is None else k_blk.stride(0), 0 if k_blk is None else k_blk.stride(1),
+            _p(v_blk), 0 if v_blk is None else v_blk.stride(0), 0 if v_blk is None else v_blk.stride(1),
+            _p(nw), out.data_ptr(), out.stride(0), out.stride(1), _stream()), "coda_b200_attend")
+
+    def _write_one(self, cfg, st, k, v, g):
+        """Ring write of one token per state plus routing of the evicted one (upstream memory_banks.py:183-224)."""
+        _, _, _, eta, _ = self._consts(k.device, k.dtype)
+        ptrs = self._ptrs(st)
+        rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
+        check(lib.coda_b200_step_write(C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0),
+                                       v.data_ptr(), v.stride(0), g.data_ptr(), eta.data_ptr(), _stream()),
+              "coda_b200_step_write")
+        W = self.window
+        if st.recent_filled < W:
+            st.recent_filled += 1
+        else:
+            st.recent_idx = (st.recent_idx + 1) % W
+        st.pos += 1
+
+    def _nothing_visible(self, st) -> bool:
+        # Only an empty ring can leave every slot masked; the check costs a sync, so it is made
+        # only then (upstream attention.py:485-488 returns zeros in that case).
+        return self.mask_unused_memory and st.recent_filled == 0 and not bool(st.allowed.any())
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def attend_step(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, *,
+                    query_pos: Optional[int] = None) -> torch.Tensor:
+        """Attention of one new token per state over the current slots (upstream attention.py:476-514)."""
+        B, L, _ = x.shape
+        assert L == 1
+        self._require_ready(x, state)
+        if self._nothing_visible(state):
+            return torch.zeros_like(x)
+        cfg = self._cfg(B, x.dtype, state)
+        q, _, _, lam_logit, _ = self._project(x, need_kv=False)
+        qp = state.pos if query_pos is None else int(query_pos)
+        qn, lam, _ = self._prep(cfg, 1, qp, q, None, lam_logit, None, False)
+        out = torch.empty_like(q)
+        self._attend(cfg, state, 1, q, qn, lam, None, None, out)
+        return self.o_proj(out)
+
+    @torch.no_grad()
+    def step(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, *, attend: bool = True,
+             write_cache: bool = True, include_current_in_attention: bool = True
+             ) -> Tuple[torch.Tensor, CoDAGQALandmarkStatePerf2]:
+        """One decode token per state (upstream attention.py:516-547): by default the token is written
+        to the cache first and then attends over all slots, itself included."""
+        B, L, _ = x.shape
+        assert L == 1
+        self._require_ready(x, state)
+        cfg = self._cfg(B, x.dtype, state)
+        qp = int(state.pos)
+        q, k, v, lam_logit, gate_logit = self._project(x, need_kv=write_cache)
+        qn, lam, g = self._prep(cfg, 1, qp, q, k, lam_logit, gate_logit, write_cache)
+        write_first = attend and include_current_in_attention and write_cache
+        if write_first:
+            self._write_one(cfg, state, k, v, g)
+        if attend and not self._nothing_visible(state):
+            out = torch.empty_like(q)
+            self._attend(cfg, state, 1, q, qn, lam, None, None, out)
+            y = self.o_proj(out)
+        else:
+            y = torch.zeros_like(x)
+        if write_cache and not write_first:
+            self._write_one(cfg, state, k, v, g)
+        return y, state
+
+    # ------------------------------------------------------------------ prefill
+    def _linearize_ring(self, st) -> None:
+        """Rotate the ring so that slot 0 holds its oldest token; contents in time order are unchanged."""
+        r, W = int(st.recent_idx), self.window
+        if r == 0:
+            return
+        st.k_buf[:, :, :W, :] = torch.roll(st.k_buf[:, :, :W, :], -r, dims=2)
+        st.v_buf[:, :, :W, :] = torch.roll(st.v_buf[:, :, :W, :], -r, dims=2)
+        st.g_recent.copy_(torch.roll(st.g_recent, -r, dims=1))
+        st.recent_idx = 0
+
+    def _route_scratch(self, cfg, device) -> torch.Tensor:
+        n = int(lib.coda_b200_route_scratch_bytes(C.byref(cfg)))
+        key = (device, n)
+        t = self._scratch.get(key)
+        if t is None:
+            t = torch.empty(n, dtype=torch.uint8, device=device)
+            self._scratch[key] = t
+        return t
+
+    @torch.no_grad()
+    def prefill_chunked(self, x_seq: torch.Tensor, state: CoDAGQALandmarkStatePerf2, *, block_size: int = 256,
+                        write_cache: bool = True, return_outputs: bool = True
+                        ) -> Tuple[Optional[torch.Tensor], CoDAGQALandmarkStatePerf2]:
+        """Blockwise prefill (upstream attention.py:567-728): block j attends over
+        [state after block j-1 | block j, causal], then the block is pushed through the ring and the
+        tokens it evicts are routed into the banks."""
+        B, L, _ = x_seq.shape
+        if L == 0:
+            return (x_seq[:, :0, :].clone() if return_outputs else None), state
+        if block_size <= 0:
+            raise ValueError("block_size must be positive")
+        self._require_ready(x_seq, state)
+        cfg = self._cfg(B, x_seq.dtype, state)
+        dev, dt = x_seq.device, x_seq.dtype
+        H, Hkv, Dh, W = self.num_heads, self.num_kv_heads, self.head_dim, self.window
+        pos0 = int(state.pos)
+        q, k, v, lam_logit, gate_logit = self._project(x_seq, need_kv=True)
+        qn, lam, g = self._prep(cfg, L, pos0, q, k, lam_logit, gate_logit, True)
+
+        block = int(block_size)
+        nblk = (L + block - 1) // block
+        if write_cache:
+            self._linearize_ring(state)
+            fill0 = int(state.recent_filled)
+            gates = torch.cat([state.g_recent[:, :fill0], g], dim=1).contiguous()
+            te = self.exact_candidates_per_block if self.Me > 0 else 0
+            ts = self.summary_candidates_per_block if self.Ms > 0 else 0
+            tmax = max(1, min(max(te, ts), block))
+            cand = torch.empty((B, nblk, tmax), device=dev, dtype=torch.int32)
+            if max(te, ts) > 0:
+                check(lib.coda_b200_select_candidates(C.byref(cfg), gates.data_ptr(), gates.stride(0), fill0, L, block,
+                                                      cand.data_ptr(), tmax, _stream()), "coda_b200_select_candidates")
+            scratch = self._route_scratch(cfg, dev)
+            _, _, _, eta, _ = self._consts(dev, dt)
+            ptrs = self._ptrs(state)
+        y_heads = torch.empty((B, L, H * Dh), device=dev, dtype=dt) if return_outputs else None
+
+        for j in range(nblk):
+            t0 = j * block
+            blk = min(block, L - t0)
+            kb, vb = k[:, t0:t0 + blk], v[:, t0:t0 + blk]
+            if return_outputs:
+                self._attend(cfg, state, blk, q[:, t0:t0 + blk], qn[:, t0:t0 + blk], lam[:, t0:t0 + blk],
+                             kb, vb, y_heads[:, t0:t0 + blk])
+            if write_cache:
+                fill = int(state.recent_filled)
+                seen = fill0 + t0
+                check(lib.coda_b200_route_block(
+                    C.byref(cfg), C.byref(ptrs), fill, blk, pos0 + t0,
+                    kb.data_ptr(), k.stride(0), k.stride(1), vb.data_ptr(), v.stride(0), v.stride(1),
+                    gates.data_ptr(), gates.stride(0), seen - fill,
+                    cand[:, j].data_ptr(), cand.stride(0), eta.data_ptr(), scratch.data_ptr(), _stream()),
+                    "coda_b200_route_block")
+                state.recent_filled = min(W, fill + blk)
+                state.recent_idx = 0
+                state.pos = pos0 + t0 + blk
+        if not return_outputs:
+            return None, state
+        return self.o_proj(y_heads), state
+
+    # ------------------------------------------------------------------ utility
+    def cache_bytes(self, *, batch_size: int, dtype: torch.dtype) -> int:
+        """State size in bytes, same accounting as upstream attention.py:734-751."""
+        B, Hkv, Dh = int(batch_size), self.num_kv_heads, self.head_dim
+        e = torch.tensor([], dtype=dtype).element_size()
+        kv = 2 * B * Hkv * self.Lbuf * Dh * e
+        exact_norm = B * Hkv * self.Me * Dh * e if self.Me > 0 else 0
+        sum_norm = B * Hkv * self.Ms * self.lf_dim * e if self.Ms > 0 else 0
+        return int(kv + exact_norm + sum_norm + B * self.window * 4 + B * self.Lbuf + B * self.Me * 8)
+
+    def reset_metrics(self, state: CoDAGQALandmarkStatePerf2) -> None:
+        """Zero the metrics counters of a state that carries them (upstream attention.py:753-760)."""
+        if state.metrics is not None:
+            for key in state.metrics:
+                state.metrics[key] = 0 if isinstance(state.metrics[key], int) else 0.0

@@ -1,0 +1,72 @@
+// C-ABI glue: error channel, dispatch of coda_b200_attend, the step counter and the host-side
+// selection-order helpers.
+#include "coda_common.cuh"
+#include "topk_order.h"
+#include <stdarg.h>
+#include <vector>
+
+static thread_local char g_err[512] = "";
+
+void coda_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* coda_b200_last_error(void) { return g_err; }
+extern "C" int coda_b200_version(void) { return 1; }
+
+int coda_attend_generic(const coda_layer_cfg* cfg, const coda_state_ptrs* st, int32_t Lq,
+                        const void* q, int64_t q_bs, int64_t q_rs,
+                        const void* q_noise, int64_t qn_bs, int64_t qn_rs,
+                        const float* lam, int64_t lam_bs, int64_t lam_rs,
+                        const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                        const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                        const void* norm_w, void* out, int64_t out_bs, int64_t out_rs, cudaStream_t s);
+
+extern "C" int coda_b200_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, int32_t Lq,
+                                const void* q, int64_t q_bs, int64_t q_rs,
+                                const void* q_noise, int64_t qn_bs, int64_t qn_rs,
+                                const float* lam, int64_t lam_bs, int64_t lam_rs,
+                                const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                                const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                                const void* norm_w,
+                                void* out, int64_t out_bs, int64_t out_rs,
+                                coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "attend: invalid layer configuration");
+  CODA_REQUIRE(Lq > 0, CODA_ERR_ARG, "attend: Lq must be positive");
+  CODA_REQUIRE(q && q_noise && lam && out && st->k_buf && st->v_buf && st->allowed, CODA_ERR_ARG, "attend: null pointer");
+  CODA_REQUIRE((k_blk == nullptr) == (v_blk == nullptr), CODA_ERR_ARG, "attend: k_blk and v_blk must be given together");
+  CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "attend: head-norm weight missing");
+  return coda_attend_generic(cfg, st, Lq, q, q_bs, q_rs, q_noise, qn_bs, qn_rs, lam, lam_bs, lam_rs,
+                             k_blk, kb_bs, kb_rs, v_blk, vb_bs, vb_rs, norm_w, out, out_bs, out_rs,
+                             (cudaStream_t)stream);
+}
+
+__global__ void advance_steps_kernel(long long* ctr, long long n) { *ctr += n; }
+
+extern "C" int coda_b200_advance_steps(int64_t* step_dev, int64_t n, coda_stream_t stream) {
+  CODA_REQUIRE(step_dev, CODA_ERR_ARG, "advance_steps: null counter");
+  advance_steps_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((long long*)step_dev, (long long)n);
+  CODA_CHECK_LAUNCH("advance_steps");
+  return CODA_OK;
+}
+
+template <typename V>
+static int host_topk(const V* v, int n, int k, int largest, int sorted, int32_t* out) {
+  if (!v || !out || n < 0 || k < 0 || k > n) { coda_set_error("host_topk: bad arguments"); return CODA_ERR_ARG; }
+  std::vector<topk_order::Item<V>> q((size_t)(n > 0 ? n : 1));
+  for (int j = 0; j < n; ++j) { q[j].v = v[j]; q[j].i = j; }
+  if (largest) topk_order::topk_queue<V, true>(q.data(), n, k, sorted != 0);
+  else topk_order::topk_queue<V, false>(q.data(), n, k, sorted != 0);
+  for (int j = 0; j < k; ++j) out[j] = q[j].i;
+  return CODA_OK;
+}
+
+extern "C" int coda_b200_host_topk_f32(const float* v, int32_t n, int32_t k, int32_t largest, int32_t sorted, int32_t* out) {
+  return host_topk<float>(v, n, k, largest, sorted, out);
+}
+extern "C" int coda_b200_host_topk_i64(const int64_t* v, int32_t n, int32_t k, int32_t largest, int32_t sorted, int32_t* out) {
+  return host_topk<long long>((const long long*)v, n, k, largest, sorted, out);
+}

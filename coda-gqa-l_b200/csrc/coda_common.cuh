@@ -1,0 +1,80 @@
+// Shared device helpers: element-type traits with "round like a tensor op" arithmetic,
+// warp reductions, ring-scalar arithmetic and the host-side error channel.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "coda_b200.h"
+
+typedef __nv_bfloat16 bf16;
+
+// ---- element traits -------------------------------------------------------------------------
+// The reference path runs as a chain of separate tensor ops; each op rounds its result to the
+// tensor dtype.  rnd() applies that rounding to an fp32 intermediate (identity for fp32), and
+// the rn intrinsics keep the compiler from contracting a*b+c into one fused rounding.
+template <typename T> struct El;
+template <> struct El<float> {
+  static __device__ __forceinline__ float ld(const float* p) { return *p; }
+  static __device__ __forceinline__ void st(float* p, float x) { *p = x; }
+  static __device__ __forceinline__ float rnd(float x) { return x; }
+};
+template <> struct El<bf16> {
+  static __device__ __forceinline__ float ld(const bf16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void st(bf16* p, float x) { *p = __float2bfloat16_rn(x); }
+  static __device__ __forceinline__ float rnd(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+};
+
+template <typename T> __device__ __forceinline__ float t_mul(float a, float b) { return El<T>::rnd(__fmul_rn(a, b)); }
+template <typename T> __device__ __forceinline__ float t_add(float a, float b) { return El<T>::rnd(__fadd_rn(a, b)); }
+template <typename T> __device__ __forceinline__ float t_sub(float a, float b) { return El<T>::rnd(__fsub_rn(a, b)); }
+template <typename T> __device__ __forceinline__ float t_div(float a, float b) { return El<T>::rnd(__fdiv_rn(a, b)); }
+
+// sigmoid of a value held in dtype T, result rounded to T
+template <typename T> __device__ __forceinline__ float t_sigmoid(float z) {
+  return El<T>::rnd(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z))));
+}
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ---- warp helpers ---------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- ring scalars ---------------------------------------------------------------------------
+struct RingNow { long long pos; int idx; int filled; };
+
+// Scalars after `n` more single-token writes (memory_banks.py:195-224): the ring fills slot by
+// slot, then the eviction pointer walks round it.
+__device__ __forceinline__ RingNow ring_now(const coda_ring_pos& rp, int W) {
+  RingNow r; r.pos = rp.pos; r.idx = rp.recent_idx; r.filled = rp.recent_filled;
+  if (rp.step_dev != nullptr) {
+    long long n = *rp.step_dev;
+    long long to_fill = (long long)W - r.filled;
+    if (to_fill < 0) to_fill = 0;
+    long long nf = n < to_fill ? n : to_fill;
+    r.filled += (int)nf;
+    r.idx = (int)(((long long)r.idx + (n - nf)) % W);
+    r.pos += n;
+  }
+  return r;
+}
+
+// ---- host error channel ---------------------------------------------------------------------
+void coda_set_error(const char* fmt, ...);
+#define CODA_REQUIRE(cond, code, ...) do { if (!(cond)) { coda_set_error(__VA_ARGS__); return (code); } } while (0)
+#define CODA_CHECK_LAUNCH(what) do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) { \
+  coda_set_error("%s: %s", what, cudaGetErrorString(e__)); return CODA_ERR_LAUNCH; } } while (0)
+
+static inline bool coda_cfg_ok(const coda_layer_cfg* c) {
+  return c && c->B > 0 && c->H > 0 && c->Hkv > 0 && c->H % c->Hkv == 0 && c->Dh > 0 && (c->Dh % 2) == 0 &&
+         c->W > 0 && c->Me >= 0 && c->Ms >= 0 && (c->dtype == CODA_F32 || c->dtype == CODA_BF16);
+}

@@ -1,0 +1,128 @@
+// Projection post-processing: RoPE on q/k, the theta-rotated noise query, lambda / gate sigmoids.
+// One CTA per token; HBM-bound elementwise work (reads q,k once, writes q,k,q_noise once).
+#include "coda_common.cuh"
+
+struct PrepParams {
+  int B, L, H, Hkv, Dh, interleaved, gated;
+  coda_ring_pos rp; int W;
+  void* q; long long q_bs, q_rs;
+  void* k; long long k_bs, k_rs;
+  void* qn;
+  const void* lam_logit; long long lam_bs, lam_rs; float* lam;
+  const void* gate_logit; long long gate_bs, gate_rs; float* gate;
+  const float* inv_freq; const void* cos_t; const void* sin_t;
+};
+
+// T: activation dtype, A: dtype the angles are evaluated in.
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) prep_kernel(PrepParams p) {
+  extern __shared__ float sm[];
+  const int half = p.Dh >> 1;
+  float* cs = sm;                 // [half] cos, rounded to T
+  float* sn = sm + half;          // [half] sin
+  float* qrow = sm + 2 * half;    // [H*Dh] rotated query row (noise rotation pairs cross RoPE pairs)
+  const int tid = threadIdx.x, NT = blockDim.x;
+  const long long ntok = (long long)p.B * p.L;
+  // In a decode graph the position comes from the step counter; prefill passes step_dev == NULL.
+  const long long pos_base = ring_now(p.rp, p.W).pos;
+  for (long long tok = blockIdx.x; tok < ntok; tok += gridDim.x) {
+    const int b = (int)(tok / p.L), t = (int)(tok % p.L);
+    const long long pos = pos_base + t;
+    for (int i = tid; i < half; i += NT) {
+      // upstream primitives.py:51-54: t = arange(dtype=inv_freq.dtype); freqs = t (x) inv_freq; cos().to(dtype)
+      float ta = El<A>::rnd((float)pos);
+      float inv = El<A>::rnd(p.inv_freq[i]);
+      float ang = El<A>::rnd(__fmul_rn(ta, inv));
+      cs[i] = El<T>::rnd(El<A>::rnd(cosf(ang)));
+      sn[i] = El<T>::rnd(El<A>::rnd(sinf(ang)));
+    }
+    __syncthreads();
+    T* qt = (T*)p.q + (long long)b * p.q_bs + (long long)t * p.q_rs;
+    T* kt = p.k ? (T*)p.k + (long long)b * p.k_bs + (long long)t * p.k_rs : nullptr;
+    const int nq = p.H * half, nk = p.k ? p.Hkv * half : 0;
+    for (int w = tid; w < nq + nk; w += NT) {
+      const bool isq = w < nq;
+      const int ww = isq ? w : w - nq;
+      const int h = ww / half, i = ww % half;
+      T* row = (isq ? qt : kt) + h * p.Dh;
+      const float c = cs[i], s = sn[i];
+      int ia, ib;
+      float oa, ob;
+      if (p.interleaved) {                  // primitives.py:99-106
+        ia = 2 * i; ib = 2 * i + 1;
+        const float xe = El<T>::ld(row + ia), xo = El<T>::ld(row + ib);
+        oa = t_sub<T>(t_mul<T>(xe, c), t_mul<T>(xo, s));
+        ob = t_add<T>(t_mul<T>(xe, s), t_mul<T>(xo, c));
+      } else {                              // primitives.py:108-113: x*cos_full + rotate_half(x)*sin_full
+        ia = i; ib = i + half;
+        const float x1 = El<T>::ld(row + ia), x2 = El<T>::ld(row + ib);
+        oa = t_add<T>(t_mul<T>(x1, c), t_mul<T>(-x2, s));
+        ob = t_add<T>(t_mul<T>(x2, c), t_mul<T>(x1, s));
+      }
+      El<T>::st(row + ia, oa);
+      El<T>::st(row + ib, ob);
+      if (isq) { qrow[h * p.Dh + ia] = oa; qrow[h * p.Dh + ib] = ob; }
+    }
+    __syncthreads();
+    T* qnt = (T*)p.qn + tok * (long long)(p.H * p.Dh);
+    for (int w = tid; w < nq; w += NT) {    // primitives.py:58-80, always (even, odd) pairs
+      const int h = w / half, i = w % half;
+      const float qe = qrow[h * p.Dh + 2 * i], qo = qrow[h * p.Dh + 2 * i + 1];
+      const float ct = El<T>::ld((const T*)p.cos_t + h * half + i);
+      const float st = El<T>::ld((const T*)p.sin_t + h * half + i);
+      El<T>::st(qnt + h * p.Dh + 2 * i, t_sub<T>(t_mul<T>(qe, ct), t_mul<T>(qo, st)));
+      El<T>::st(qnt + h * p.Dh + 2 * i + 1, t_add<T>(t_mul<T>(qe, st), t_mul<T>(qo, ct)));
+    }
+    for (int h = tid; h < p.H; h += NT) {
+      const float z = El<T>::ld((const T*)p.lam_logit + (long long)b * p.lam_bs + (long long)t * p.lam_rs + h);
+      p.lam[tok * p.H + h] = t_sigmoid<T>(z);
+    }
+    if (tid == 0 && p.gate != nullptr) {
+      float g = 1.0f;                       // write_policy "none": attention.py:407-408
+      if (p.gated) g = t_sigmoid<T>(El<T>::ld((const T*)p.gate_logit + (long long)b * p.gate_bs + (long long)t * p.gate_rs));
+      p.gate[tok] = g;
+    }
+    __syncthreads();
+  }
+}
+
+extern "C" int coda_b200_prep(const coda_layer_cfg* cfg, int32_t L, coda_ring_pos rp,
+                              void* q, int64_t q_bs, int64_t q_rs,
+                              void* k, int64_t k_bs, int64_t k_rs,
+                              void* q_noise,
+                              const void* lam_logit, int64_t lam_bs, int64_t lam_rs, float* lam,
+                              const void* gate_logit, int64_t gate_bs, int64_t gate_rs, float* gate,
+                              const float* inv_freq, const void* cos_theta, const void* sin_theta,
+                              coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg), CODA_ERR_ARG, "prep: invalid layer configuration");
+  CODA_REQUIRE(L >= 0, CODA_ERR_ARG, "prep: negative L");
+  if (L == 0) return CODA_OK;
+  CODA_REQUIRE(q && q_noise && lam_logit && lam && inv_freq && cos_theta && sin_theta, CODA_ERR_ARG, "prep: null pointer");
+  CODA_REQUIRE(!(cfg->gated && gate && !gate_logit), CODA_ERR_ARG, "prep: gated write policy needs gate logits");
+  PrepParams p;
+  p.B = cfg->B; p.L = L; p.H = cfg->H; p.Hkv = cfg->Hkv; p.Dh = cfg->Dh;
+  p.interleaved = cfg->rope_interleaved; p.gated = cfg->gated; p.rp = rp; p.W = cfg->W;
+  p.q = q; p.q_bs = q_bs; p.q_rs = q_rs; p.k = k; p.k_bs = k_bs; p.k_rs = k_rs; p.qn = q_noise;
+  p.lam_logit = lam_logit; p.lam_bs = lam_bs; p.lam_rs = lam_rs; p.lam = lam;
+  p.gate_logit = gate_logit; p.gate_bs = gate_bs; p.gate_rs = gate_rs; p.gate = gate;
+  p.inv_freq = inv_freq; p.cos_t = cos_theta; p.sin_t = sin_theta;
+  const long long ntok = (long long)cfg->B * L;
+  const int grid = (int)(ntok < 148LL * 16 ? ntok : 148LL * 16);
+  const size_t smem = sizeof(float) * (size_t)(cfg->Dh + cfg->H * cfg->Dh);
+  CODA_REQUIRE(smem <= 200 * 1024, CODA_ERR_LIMIT, "prep: H*Dh = %d exceeds the shared-memory row limit", cfg->H * cfg->Dh);
+  cudaStream_t s = (cudaStream_t)stream;
+#define LAUNCH(T, A) do { \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(prep_kernel<T, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    prep_kernel<T, A><<<grid, 256, smem, s>>>(p); } while (0)
+  if (cfg->dtype == CODA_F32) {
+    CODA_REQUIRE(cfg->angle_dtype == CODA_F32, CODA_ERR_ARG, "prep: fp32 activations need fp32 angles");
+    LAUNCH(float, float);
+  } else if (cfg->angle_dtype == CODA_BF16) {
+    LAUNCH(bf16, bf16);
+  } else {
+    LAUNCH(bf16, float);
+  }
+#undef LAUNCH
+  CODA_CHECK_LAUNCH("prep");
+  return CODA_OK;
+}

@@ -1,0 +1,229 @@
+// Decode-step cache write: ring FIFO + routing of the evicted token into the exact and summary banks.
+// One CTA per state.  Reads the two unit-norm routing caches once, rewrites at most one slot per bank.
+#include "coda_common.cuh"
+
+struct StepParams {
+  coda_layer_cfg c;
+  coda_state_ptrs st;
+  coda_ring_pos rp;
+  const void* k_new; long long k_bs;
+  const void* v_new; long long v_bs;
+  const float* gate; const float* eta_logit;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
+  extern __shared__ float sm[];
+  const coda_layer_cfg& c = p.c;
+  const int b = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, NW = NT >> 5;
+  const int W = c.W, Me = c.Me, Ms = c.Ms, Hkv = c.Hkv, Dh = c.Dh;
+  const int Lbuf = W + Me + Ms, HD = Hkv * Dh, lf = Dh / 2, lfd = Dh - lf;
+  const RingNow r = ring_now(p.rp, W);
+
+  T* kb = (T*)p.st.k_buf + (long long)b * Hkv * Lbuf * Dh;
+  T* vb = (T*)p.st.v_buf + (long long)b * Hkv * Lbuf * Dh;
+  uint8_t* al = p.st.allowed + (long long)b * Lbuf;
+  float* gr = p.st.g_recent + (long long)b * W;
+  const T* kn = (const T*)p.k_new + (long long)b * p.k_bs;
+  const T* vn = (const T*)p.v_new + (long long)b * p.v_bs;
+  const float g_new = p.gate[b];
+
+  if (r.filled < W) {                                   // memory_banks.py:195-201
+    const int slot = r.filled;
+    for (int e = tid; e < HD; e += NT) {
+      const int h = e / Dh, d = e % Dh;
+      kb[((long long)h * Lbuf + slot) * Dh + d] = kn[e];
+      vb[((long long)h * Lbuf + slot) * Dh + d] = vn[e];
+    }
+    if (tid == 0) { gr[slot] = g_new; al[slot] = 1; }
+    return;
+  }
+
+  // ---- ring full: evict slot ev (memory_banks.py:203-222) ----
+  const int ev = r.idx;
+  const long long pos_e = r.pos - W;
+  float* ke = sm;                 // [HD] evicted key
+  float* ve = ke + HD;            // [HD] evicted value
+  float* vhat = ve + HD;          // [HD] unit-norm value   (later: new V row for re-normalising)
+  float* khat = vhat + HD;        // [Hkv*lfd] unit-norm LF key (later: new LF key row)
+  float* sc = khat + Hkv * lfd;   // [max(Me,Ms)] scores
+  __shared__ int s_idx, s_flag;
+  __shared__ float s_eta_keep;
+
+  for (int e = tid; e < HD; e += NT) {
+    const int h = e / Dh, d = e % Dh;
+    ke[e] = El<T>::ld(kb + ((long long)h * Lbuf + ev) * Dh + d);
+    ve[e] = El<T>::ld(vb + ((long long)h * Lbuf + ev) * Dh + d);
+  }
+  const float g_e = gr[ev];
+  __syncthreads();
+  // unit vectors: x / max(||x||, 1e-6) per head (F.normalize, memory_banks.py:258,372)
+  for (int h = warp; h < Hkv; h += NW) {
+    float ssv = 0.f, ssk = 0.f;
+    for (int d = lane; d < Dh; d += 32) {
+      const float v = ve[h * Dh + d]; ssv += v * v;
+      if (d >= lf) { const float k = ke[h * Dh + d]; ssk += k * k; }
+    }
+    ssv = warp_sum(ssv); ssk = warp_sum(ssk);
+    const float dv = fmaxf(El<T>::rnd(sqrtf(ssv)), 1e-6f), dk = fmaxf(El<T>::rnd(sqrtf(ssk)), 1e-6f);
+    for (int d = lane; d < Dh; d += 32) {
+      vhat[h * Dh + d] = t_div<T>(ve[h * Dh + d], dv);
+      if (d >= lf) khat[h * lfd + d - lf] = t_div<T>(ke[h * Dh + d], dk);
+    }
+  }
+  __syncthreads();
+
+  // ================= exact bank (memory_banks.py:230-337) =================
+  if (Me > 0) {
+    const int Ae = c.active_exact;
+    const T* vnorm = (const T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh;
+    for (int m = warp; m < Me; m += NW) {
+      float tot = 0.f;
+      for (int h = 0; h < Hkv; ++h) {
+        const T* row = vnorm + ((long long)h * Me + m) * Dh;
+        float part = 0.f;
+        for (int d = lane; d < Dh; d += 32) part += vhat[h * Dh + d] * El<T>::ld(row + d);
+        tot += El<T>::rnd(warp_sum(part));
+      }
+      if (lane == 0) sc[m] = (m >= Ae || !al[W + m]) ? -1e9f : El<T>::rnd(tot / (float)Hkv);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      long long* last = (long long*)p.st.mem_last_exact + (long long)b * Me;
+      float best = sc[0]; int bi = 0;
+      for (int m = 1; m < Me; ++m) if (sc[m] > best) { best = sc[m]; bi = m; }
+      bool any_used = false; int free_i = -1; int lru_i = 0; long long lru_v = 0x7fffffffffffffffLL;
+      for (int m = 0; m < Me; ++m) {
+        const bool used = al[W + m] != 0, act = m < Ae;
+        if (act && used) any_used = true;
+        if (act && !used && free_i < 0) free_i = m;
+        const long long key = (used && act) ? last[m] : (1LL << 62);
+        if (key < lru_v) { lru_v = key; lru_i = m; }
+      }
+      const bool novel = !any_used || best < El<T>::rnd(c.tau_novel);
+      const bool hit = any_used && best >= El<T>::rnd(c.tau_match);
+      const bool keep = c.gated ? (g_e >= c.tau_gate_exact) : true;
+      const int idx = novel ? (free_i >= 0 ? free_i : lru_i) : bi;
+      const bool ow = (novel || (c.refresh_on_hit && hit)) && keep;
+      if (keep) last[idx] = pos_e;                       // memory_banks.py:325-331
+      s_idx = idx; s_flag = ow ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_flag) {
+      const int slot = W + s_idx;
+      for (int e = tid; e < HD; e += NT) {
+        const int h = e / Dh, d = e % Dh;
+        T* pk = kb + ((long long)h * Lbuf + slot) * Dh + d;
+        T* pv = vb + ((long long)h * Lbuf + slot) * Dh + d;
+        const float ok = El<T>::ld(pk), ov = El<T>::ld(pv);
+        El<T>::st(pk, t_add<T>(ok, t_sub<T>(ke[e], ok)));  // mem + 1*(x - mem), memory_banks.py:301-302
+        const float nv = t_add<T>(ov, t_sub<T>(ve[e], ov));
+        El<T>::st(pv, nv);
+        vhat[e] = nv;
+      }
+      if (tid == 0) al[slot] = 1;
+      __syncthreads();
+      T* vnorm_w = (T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh;
+      for (int h = warp; h < Hkv; h += NW) {              // re-normalise the written slot only
+        float ss = 0.f;
+        for (int d = lane; d < Dh; d += 32) { const float v = vhat[h * Dh + d]; ss += v * v; }
+        const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
+        for (int d = lane; d < Dh; d += 32)
+          El<T>::st(vnorm_w + ((long long)h * Me + s_idx) * Dh + d, t_div<T>(vhat[h * Dh + d], den));
+      }
+    }
+    __syncthreads();
+  }
+
+  // ================= summary bank (memory_banks.py:343-432) =================
+  if (Ms > 0) {
+    const int As = c.active_summary;
+    const T* knorm = (const T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
+    for (int m = warp; m < Ms; m += NW) {
+      float tot = 0.f;
+      for (int h = 0; h < Hkv; ++h) {
+        const T* row = knorm + ((long long)h * Ms + m) * lfd;
+        float part = 0.f;
+        for (int d = lane; d < lfd; d += 32) part += khat[h * lfd + d] * El<T>::ld(row + d);
+        tot += El<T>::rnd(warp_sum(part));
+      }
+      if (lane == 0) sc[m] = (m >= As) ? -1e9f : El<T>::rnd(tot / (float)Hkv);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float best = sc[0]; int bi = 0;
+      for (int m = 1; m < Ms; ++m) if (sc[m] > best) { best = sc[m]; bi = m; }
+      const bool is_new = al[W + Me + bi] == 0;
+      const bool keep = c.gated ? (g_e >= c.tau_gate_summary) : true;
+      s_idx = bi; s_flag = (c.overwrite_on_insert && is_new) ? 1 : 0;
+      s_eta_keep = keep ? 1.f : 0.f;
+      if (keep) al[W + Me + bi] = 1;
+    }
+    __syncthreads();
+    const int slot = W + Me + s_idx;
+    const float gT = El<T>::rnd(g_e);
+    for (int e = tid; e < HD; e += NT) {
+      const int h = e / Dh, d = e % Dh;
+      float eta = t_sigmoid<T>(p.eta_logit[h]);
+      if (c.gated) eta = t_mul<T>(eta, gT);
+      if (s_flag) eta = 1.f;
+      eta = t_mul<T>(eta, s_eta_keep);
+      T* pk = kb + ((long long)h * Lbuf + slot) * Dh + d;
+      T* pv = vb + ((long long)h * Lbuf + slot) * Dh + d;
+      const float ok = El<T>::ld(pk), ov = El<T>::ld(pv);
+      if (d >= lf) {                                     // phase-safe EMA: LF band only
+        const float inc = El<T>::rnd(__fmul_rn(ke[e], c.energy_scale));
+        const float nk = t_add<T>(ok, t_mul<T>(eta, t_sub<T>(inc, ok)));
+        El<T>::st(pk, nk);
+        khat[h * lfd + d - lf] = nk;
+      }
+      El<T>::st(pv, t_add<T>(ov, t_mul<T>(eta, t_sub<T>(ve[e], ov))));
+    }
+    __syncthreads();
+    T* knorm_w = (T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
+    for (int h = warp; h < Hkv; h += NW) {
+      float ss = 0.f;
+      for (int d = lane; d < lfd; d += 32) { const float k = khat[h * lfd + d]; ss += k * k; }
+      const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
+      for (int d = lane; d < lfd; d += 32)
+        El<T>::st(knorm_w + ((long long)h * Ms + s_idx) * lfd + d, t_div<T>(khat[h * lfd + d], den));
+    }
+  }
+
+  // ---- the new token takes the evicted slot (memory_banks.py:219-222) ----
+  for (int e = tid; e < HD; e += NT) {
+    const int h = e / Dh, d = e % Dh;
+    kb[((long long)h * Lbuf + ev) * Dh + d] = kn[e];
+    vb[((long long)h * Lbuf + ev) * Dh + d] = vn[e];
+  }
+  if (tid == 0) gr[ev] = g_new;
+}
+
+extern "C" int coda_b200_step_write(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                    const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                    const float* gate, const float* eta_logit, coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "step_write: invalid layer configuration");
+  CODA_REQUIRE(st->k_buf && st->v_buf && st->allowed && st->g_recent && k_new && v_new && gate, CODA_ERR_ARG,
+               "step_write: null pointer");
+  CODA_REQUIRE(cfg->Me == 0 || (st->mem_last_exact && st->exact_v_norm), CODA_ERR_ARG, "step_write: exact bank pointers missing");
+  CODA_REQUIRE(cfg->Ms == 0 || (st->sum_lf_k_norm && eta_logit), CODA_ERR_ARG, "step_write: summary bank pointers missing");
+  CODA_REQUIRE(rp.recent_idx >= 0 && rp.recent_idx < cfg->W && rp.recent_filled >= 0 && rp.recent_filled <= cfg->W,
+               CODA_ERR_ARG, "step_write: ring scalars out of range");
+  StepParams p; p.c = *cfg; p.st = *st; p.rp = rp;
+  p.k_new = k_new; p.k_bs = k_bs; p.v_new = v_new; p.v_bs = v_bs; p.gate = gate; p.eta_logit = eta_logit;
+  const int HD = cfg->Hkv * cfg->Dh, lfd = cfg->Dh - cfg->Dh / 2;
+  const int mx = cfg->Me > cfg->Ms ? cfg->Me : cfg->Ms;
+  const size_t smem = sizeof(float) * (size_t)(3 * HD + cfg->Hkv * lfd + mx + 1);
+  CODA_REQUIRE(smem <= 200 * 1024, CODA_ERR_LIMIT, "step_write: Hkv*Dh = %d too large for one CTA", HD);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cfg->dtype == CODA_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(step_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    step_write_kernel<float><<<cfg->B, 256, smem, s>>>(p);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(step_write_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    step_write_kernel<bf16><<<cfg->B, 256, smem, s>>>(p);
+  }
+  CODA_CHECK_LAUNCH("step_write");
+  return CODA_OK;
+}

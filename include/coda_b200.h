@@ -1,0 +1,176 @@
+/*
+ * coda_b200.h -- C ABI of the B200 (sm_100a) kernels for bounded-cache differential attention.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream, allocates nothing and never synchronises.  It returns 0 on
+ * success and a negative code when an argument is rejected; coda_b200_last_error() then
+ * gives the reason.  The library has no CPU fallback: all pointers must be device pointers.
+ *
+ * Upstream paths below are relative to the CoDA-GQA-L project root.  The binding pattern
+ * (raw pointers + cudaStream_t behind extern "C") follows upstream's own native layer,
+ * kernels/coda_diff_epilogue/kernel_src/diff_epilogue.cu:465-568.
+ *
+ * Tensor layouts (row-major, innermost dimension last):
+ *   k_buf, v_buf      [B][Hkv][Lbuf][Dh]   Lbuf = W + Me + Ms, slot order [ring | exact | summary]
+ *   allowed           [B][Lbuf]            1 byte per slot, non-zero = slot holds valid data
+ *   g_recent          [B][W]               fp32 write gate of each ring slot
+ *   mem_last_exact    [B][Me]              int64 LRU stamp (position of the last touch)
+ *   exact_v_norm      [B][Hkv][Me][Dh]     unit-norm copy of the exact bank's V rows
+ *   sum_lf_k_norm     [B][Hkv][Ms][Dh/2]   unit-norm copy of the summary bank's low-frequency K band
+ * Activations q/k/v are [B][L][heads][Dh] with Dh contiguous, heads Dh apart, and explicit
+ * token (row) and batch strides in elements, so a slice of a fused projection can be passed.
+ */
+#ifndef CODA_B200_H
+#define CODA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* coda_stream_t; /* == cudaStream_t */
+
+enum { CODA_F32 = 0, CODA_BF16 = 1 };
+
+enum {
+  CODA_OK = 0,
+  CODA_ERR_ARG = -1,      /* bad size / null pointer / unsupported combination */
+  CODA_ERR_LAUNCH = -2,   /* the CUDA runtime refused the launch */
+  CODA_ERR_LIMIT = -3     /* a documented size limit was exceeded */
+};
+
+/* Hyper-parameters of one layer; mirrors the constructor arguments of upstream
+ * CoDAGQALandmarkPerf2 (src/coda_gqa_l/attention.py:89-141) that the kernels need. */
+typedef struct coda_layer_cfg {
+  int32_t B, H, Hkv, Dh;
+  int32_t W, Me, Ms;
+  int32_t dtype;               /* CODA_F32 / CODA_BF16: k_buf, v_buf, norm caches, q, k, v, out */
+  int32_t angle_dtype;         /* dtype RoPE angles are evaluated in (dtype of upstream's inv_freq buffer) */
+  int32_t rope_interleaved;    /* 1: pairs (2i,2i+1); 0: pairs (i, i+Dh/2) */
+  int32_t head_norm_full;      /* 1: RMSNorm over Dh in the epilogue; 0: plain subtraction */
+  int32_t mask_unused;         /* 1: slots with allowed==0 are invisible to attention */
+  int32_t gated;               /* 1: write_policy "gated"; 0: "none" (gate == 1, no thresholds) */
+  int32_t refresh_on_hit;
+  int32_t overwrite_on_insert;
+  int32_t Te, Ts;              /* exact / summary candidates per block */
+  int32_t active_exact, active_summary;
+  float tau_gate_exact, tau_gate_summary, tau_match, tau_novel;
+  float eps;                   /* head-norm epsilon */
+  float energy_scale;          /* sqrt(Dh / (Dh - Dh/2)) */
+} coda_layer_cfg;
+
+/* Device pointers of one layer's state; the fields of upstream's state dataclass
+ * (src/coda_gqa_l/state.py:23-54). Pointers of absent banks (Me==0 / Ms==0) may be NULL. */
+typedef struct coda_state_ptrs {
+  void* k_buf;
+  void* v_buf;
+  uint8_t* allowed;
+  float* g_recent;
+  int64_t* mem_last_exact;
+  void* exact_v_norm;
+  void* sum_lf_k_norm;
+} coda_state_ptrs;
+
+/* Ring scalars (state.py:28-36).  They are deterministic functions of the number of tokens
+ * written, so the host keeps them as integers.  When step_dev is non-NULL the kernels add the
+ * int64 it points to (a count of decode steps taken since the scalars were read) before use,
+ * which lets a captured CUDA graph be replayed without re-baking the scalars. */
+typedef struct coda_ring_pos {
+  int64_t pos;
+  int32_t recent_idx;
+  int32_t recent_filled;
+  const int64_t* step_dev;
+} coda_ring_pos;
+
+const char* coda_b200_last_error(void);
+int coda_b200_version(void);
+
+/* Projection post-processing for L tokens per state: RoPE on q and k in place, the
+ * theta-rotated noise query, sigmoid of the lambda and write-gate logits.
+ * Replaces RotaryEmbedding.forward + apply_rope + _apply_pairwise_rotation
+ * (src/coda_gqa_l/primitives.py:43-113) and the sigmoids of attention.py:406-410,508,603.
+ * q [B][L][H][Dh], k [B][L][Hkv][Dh] strided; q_noise [B][L][H][Dh] contiguous;
+ * lam_logit [B][L][H] strided (dtype) -> lam [B][L][H] fp32; gate_logit [B][L] strided
+ * (dtype, NULL when !gated) -> gate [B][L] fp32.  inv_freq fp32[Dh/2]; cos_theta/sin_theta
+ * [H][Dh/2] in dtype.  Positions are rp.pos .. rp.pos+L-1.  k may be NULL (query only). */
+int coda_b200_prep(const coda_layer_cfg* cfg, int32_t L, coda_ring_pos rp,
+                   void* q, int64_t q_bs, int64_t q_rs,
+                   void* k, int64_t k_bs, int64_t k_rs,
+                   void* q_noise,
+                   const void* lam_logit, int64_t lam_bs, int64_t lam_rs, float* lam,
+                   const void* gate_logit, int64_t gate_bs, int64_t gate_rs, float* gate,
+                   const float* inv_freq, const void* cos_theta, const void* sin_theta,
+                   coda_stream_t stream);
+
+/* One decode token per state: ring FIFO write, and when the ring is full the evicted token is
+ * routed to the exact bank (value-space cosine novelty, first-free-else-LRU slot) and the
+ * summary bank (low-frequency-key cosine argmax, phase-safe EMA).
+ * Replaces _write_one / _exact_update_one / _summary_update_one
+ * (src/coda_gqa_l/memory_banks.py:183-224, 230-337, 343-432).
+ * k_new (already rotated), v_new: [B][Hkv][Dh] with batch stride; gate fp32[B];
+ * eta_logit fp32[Hkv] (summary_eta_logit).  rp holds the scalars BEFORE the write. */
+int coda_b200_step_write(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                         const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
+                         const float* gate, const float* eta_logit, coda_stream_t stream);
+
+/* Differential attention of Lq query rows per state over [all Lbuf slots | optional block].
+ * out = head_norm( softmax(q K^T) V - lam * softmax(q_noise K^T) V ), GQA by head index.
+ * Slots are masked by `allowed` (when mask_unused); block key j is visible to row i iff j <= i.
+ * Replaces _sdpa_stacked_two_stream + HeadwiseRMSNorm + the mask construction of
+ * attend_step / prefill_chunked (src/coda_gqa_l/attention.py:416-465, 476-514, 553-565,
+ * 612-701) and upstream's triton_diff_flash / coda_diff_epilogue accelerators.
+ * q, q_noise [B][Lq][H][Dh] strided; lam fp32 [B][Lq][H] with strides; k_blk, v_blk
+ * [B][Lq][Hkv][Dh] strided or NULL (decode); norm_w [Dh] in dtype or NULL;
+ * out [B][Lq][H*Dh] with strides. */
+int coda_b200_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, int32_t Lq,
+                     const void* q, int64_t q_bs, int64_t q_rs,
+                     const void* q_noise, int64_t qn_bs, int64_t qn_rs,
+                     const float* lam, int64_t lam_bs, int64_t lam_rs,
+                     const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                     const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                     const void* norm_w,
+                     void* out, int64_t out_bs, int64_t out_rs,
+                     coda_stream_t stream);
+
+/* Candidate selection for every block of one prefill call: for block j the tokens that leave
+ * the ring are a contiguous run of the token stream; their fp32 gates are ranked exactly like
+ * the host top-k upstream uses (memory_banks.py:486-552, torch.topk largest, unsorted), tie
+ * order included, and the first T_max indices are written.
+ * gates [B][ring_fill0 + L] (gates of the ring's tokens in chronological order, then the new
+ * tokens); cand int32 [B][nblk][cand_stride]; nblk = ceil(L / block).  T_max per block is
+ * max(Te', Ts') with Te' = min(Te, evict_len) (0 if that bank is off). */
+int coda_b200_select_candidates(const coda_layer_cfg* cfg, const float* gates, int64_t gates_bs,
+                                int32_t ring_fill0, int32_t L, int32_t block,
+                                int32_t* cand, int32_t cand_stride, coda_stream_t stream);
+
+/* Bank + ring update with one prefill block.  Requires recent_idx == 0 (ring stored in
+ * chronological order; rotate it first if a decode phase moved the pointer).
+ * Replaces _write_block_fast / _exact_update_block_vectorized / _summary_update_block_hard /
+ * _set_recent_from_sequence (src/coda_gqa_l/memory_banks.py:438-564, 570-774, 780-950,
+ * 152-177; PyTorch branches, not the Triton ones).
+ * k_blk, v_blk [B][blk][Hkv][Dh] strided (k rotated); gates as for select_candidates with
+ * gate_ev0 = index in `gates` rows of the first evicted token; cand int32 [B][*] with batch
+ * stride cand_bs (this block's list); ring_fill = tokens in the ring before the block;
+ * pos0 = position of the block's first token; scratch: coda_b200_route_scratch_bytes() bytes. */
+int64_t coda_b200_route_scratch_bytes(const coda_layer_cfg* cfg);
+int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                          int32_t ring_fill, int32_t blk, int64_t pos0,
+                          const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                          const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                          const float* gates, int64_t gates_bs, int64_t gate_ev0,
+                          const int32_t* cand, int64_t cand_bs,
+                          const float* eta_logit, void* scratch, coda_stream_t stream);
+
+/* Adds `n` to the int64 step counter that coda_ring_pos.step_dev points to (one thread). */
+int coda_b200_advance_steps(int64_t* step_dev, int64_t n, coda_stream_t stream);
+
+/* Host-only helpers (no GPU needed): the selection order used by select_candidates and by
+ * the LRU victim ranking, exposed so that CPU tests can compare it with torch.topk. */
+int coda_b200_host_topk_f32(const float* v, int32_t n, int32_t k, int32_t largest, int32_t sorted, int32_t* out);
+int coda_b200_host_topk_i64(const int64_t* v, int32_t n, int32_t k, int32_t largest, int32_t sorted, int32_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CODA_B200_H */

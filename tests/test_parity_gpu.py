@@ -1,0 +1,180 @@
+"""GPU: the CUDA path (through the C ABI) against the CPU oracle run live on the same seeded inputs,
+and against the fixtures generated from the upstream implementation.
+
+Bar: ring scalars, `allowed` and the LRU stamps bit-exact in fp32; layer outputs within 1e-4 relative
+(fp32) / 2e-2 relative (bf16) of the reference."""
+import pytest
+import torch
+
+from tests.helpers import (SCENARIOS, TOL_BF16, TOL_F32, build_inputs, build_module, load_golden, oracle_state_from,
+                           orc, rel_err, weights_of)
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(name, check_golden=True):
+    from coda_gqa_l_b200 import state_from_fields
+    sc = SCENARIOS[name]
+    dtype = getattr(torch, sc.get("dtype", "float32"))
+    f32 = dtype == torch.float32
+    tol = TOL_F32 if f32 else TOL_BF16
+    mod = build_module(sc, dtype)
+    wts = weights_of(mod)
+    cfg = orc.OracleConfig.from_module(mod)
+    torch.manual_seed(sc["state_seed"])
+    st_cpu = mod.init_state(batch_size=sc["B"], device="cpu", dtype=dtype)
+    ost = oracle_state_from(st_cpu)
+    mod = mod.to("cuda")
+    st = state_from_fields(st_cpu, "cuda")
+    x_pre, x_dec = build_inputs(sc, dtype)
+    gold = load_golden(name) if check_golden else None
+    for i, phase in enumerate(sc["phases"]):
+        if phase[0] == "prefill":
+            lo, hi, blk = phase[1:]
+            y_o = orc.prefill_chunked(cfg, wts, x_pre[:, lo:hi], ost, block_size=blk)
+            y, st = mod.prefill_chunked(x_pre[:, lo:hi].cuda(), st, block_size=blk)
+        else:
+            lo, hi = phase[1:]
+            xs = x_dec.cuda()
+            ys, yo = [], []
+            for t in range(lo, hi):
+                yy, st = mod.step(xs[:, t:t + 1], st)
+                ys.append(yy)
+                yo.append(orc.step(cfg, wts, x_dec[:, t:t + 1], ost))
+            y, y_o = torch.cat(ys, 1), torch.cat(yo, 1)
+        torch.cuda.synchronize()
+        tag = f"{name} phase {i} {phase}"
+        assert (st.recent_idx, st.recent_filled, st.pos) == (ost.recent_idx, ost.recent_filled, ost.pos), tag
+        if f32:
+            assert torch.equal(st.allowed.cpu(), ost.allowed), f"{tag}: slot occupancy differs"
+            assert torch.equal(st.mem_last_exact.cpu(), ost.mem_last_exact), f"{tag}: LRU stamps differ"
+            assert torch.equal(st.g_recent.cpu(), ost.g_recent) or rel_err(st.g_recent, ost.g_recent) < 1e-6, tag
+        e = rel_err(y, y_o)
+        assert e < tol, f"{tag}: output rel err {e:.3e} vs oracle"
+        if f32:
+            assert rel_err(st.k_buf, ost.k_buf) < tol and rel_err(st.v_buf, ost.v_buf) < tol, f"{tag}: K/V"
+            if ost._exact_v_norm is not None:
+                assert rel_err(st._exact_v_norm, ost._exact_v_norm) < tol, tag
+            if ost._sum_lf_k_norm is not None:
+                assert rel_err(st._sum_lf_k_norm, ost._sum_lf_k_norm) < tol, tag
+        if gold is not None:
+            snap = gold["snapshots"][i]
+            eg = rel_err(y[:, ::gold["y_stride"]], gold["y"][i])
+            assert eg < tol, f"{tag}: output rel err {eg:.3e} vs upstream fixture"
+            assert (st.recent_idx, st.recent_filled, st.pos) == (snap["recent_idx"], snap["recent_filled"], snap["pos"])
+            if f32:
+                assert torch.equal(st.allowed.cpu(), snap["allowed"]), f"{tag}: occupancy vs fixture"
+                assert torch.equal(st.mem_last_exact.cpu(), snap["mem_last_exact"]), f"{tag}: stamps vs fixture"
+    return mod, st, ost
+
+
+@pytest.mark.parametrize("name", [n for n in SCENARIOS if n != "c1"])
+def test_scenario_matches_oracle_and_fixture(name):
+    _run(name)
+
+
+def test_config1_cpu_reference_run():
+    """BASELINE config 1 exactly: fp32, B=1, 2048-token prefill in blocks of 256, then 1000 decode steps."""
+    _run("c1")
+
+
+def test_flag_combinations_of_step():
+    """attend=False writes only; write_cache=False leaves the state untouched;
+    include_current_in_attention=False attends before writing (upstream attention.py:529-547)."""
+    from coda_gqa_l_b200 import state_from_fields
+    sc = SCENARIOS["small_b2"]
+    mod = build_module(sc, torch.float32)
+    wts, cfg = weights_of(mod), None
+    cfg = orc.OracleConfig.from_module(mod)
+    torch.manual_seed(1)
+    st_cpu = mod.init_state(batch_size=2, device="cpu", dtype=torch.float32)
+    ost = oracle_state_from(st_cpu)
+    mod = mod.cuda()
+    st = state_from_fields(st_cpu, "cuda")
+    x = torch.randn(2, 90, 128, generator=torch.Generator().manual_seed(4))
+    for t in range(90):
+        kw = [dict(), dict(attend=False), dict(write_cache=False), dict(include_current_in_attention=False)][t % 4]
+        y, st = mod.step(x[:, t:t + 1].cuda(), st, **kw)
+        y_o = orc.step(cfg, wts, x[:, t:t + 1], ost, **kw)
+        assert (st.pos, st.recent_idx, st.recent_filled) == (ost.pos, ost.recent_idx, ost.recent_filled)
+        if float(y_o.abs().sum()) == 0.0:
+            assert float(y.abs().sum()) == 0.0
+        else:
+            assert rel_err(y, y_o) < TOL_F32, (t, kw)
+    assert torch.equal(st.allowed.cpu(), ost.allowed)
+    assert torch.equal(st.mem_last_exact.cpu(), ost.mem_last_exact)
+
+
+def test_prefill_without_write_and_streaming_equivalence():
+    """write_cache=False leaves pos and buffers untouched; prefilling in two calls equals one call."""
+    from coda_gqa_l_b200 import _deep_copy_state, state_from_fields
+    sc = SCENARIOS["small_b2"]
+    mod = build_module(sc, torch.float32)
+    torch.manual_seed(1)
+    st_cpu = mod.init_state(batch_size=2, device="cpu", dtype=torch.float32)
+    mod = mod.cuda()
+    x, _ = build_inputs(sc, torch.float32)
+    x = x.cuda()
+    a = state_from_fields(st_cpu, "cuda")
+    k0 = a.k_buf.clone()
+    y0, a = mod.prefill_chunked(x[:, :64], a, block_size=32, write_cache=False)
+    assert a.pos == 0 and torch.equal(a.k_buf, k0) and y0.shape == (2, 64, 128)
+    y1, a = mod.prefill_chunked(x, a, block_size=32)
+    b = state_from_fields(st_cpu, "cuda")
+    y2a, b = mod.prefill_chunked(x[:, :96], b, block_size=32)
+    y2b, b = mod.prefill_chunked(x[:, 96:], b, block_size=32)
+    assert torch.equal(torch.cat([y2a, y2b], 1), y1)
+    assert torch.equal(a.k_buf, b.k_buf) and torch.equal(a.mem_last_exact, b.mem_last_exact) and a.pos == b.pos
+    c = _deep_copy_state(a)
+    none, c = mod.prefill_chunked(x[:, :40], c, block_size=16, return_outputs=False)
+    assert none is None and c.pos == a.pos + 40
+    empty, c = mod.prefill_chunked(x[:, :0], c)
+    assert empty.shape == (2, 0, 128)
+    with pytest.raises(ValueError):
+        mod.prefill_chunked(x, c, block_size=0)
+
+
+def test_bounded_equals_unbounded_when_window_covers_sequence():
+    """Independent of the bank code: with W >= L nothing is evicted, so prefill and token-by-token decode must
+    equal plain full causal differential attention with the same weights (upstream README.md:263-269)."""
+    from coda_gqa_l_b200 import CoDAGQA, CoDAGQALandmarkPerf2
+    torch.manual_seed(0)
+    kw = dict(embed_dim=256, num_heads=4, num_kv_heads=2)
+    bounded = CoDAGQALandmarkPerf2(window=320, num_landmarks_exact=8, num_landmarks_summary=8, **kw).eval()
+    plain = CoDAGQA(**kw).eval()
+    plain.load_state_dict({k: v for k, v in bounded.state_dict().items() if k in plain.state_dict()})
+    x = torch.randn(2, 300, 256, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        y_ref, _ = plain(x)
+    bounded = bounded.cuda()
+    st = bounded.init_state(batch_size=2, device="cuda", dtype=torch.float32)
+    y, st = bounded.prefill_chunked(x[:, :236].cuda(), st, block_size=100)
+    assert rel_err(y, y_ref[:, :236]) < TOL_F32
+    ys = []
+    for t in range(236, 300):
+        yy, st = bounded.step(x[:, t:t + 1].cuda(), st)
+        ys.append(yy)
+    assert rel_err(torch.cat(ys, 1), y_ref[:, 236:]) < TOL_F32
+
+
+def test_run_to_run_determinism():
+    """Same inputs twice give bit-identical outputs and state: the kernels use no atomics."""
+    outs = []
+    for _ in range(2):
+        mod, st, _ = _run("small_randn", check_golden=False)
+        outs.append((st.k_buf.clone(), st.v_buf.clone(), st.mem_last_exact.clone()))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+def test_rejects_cpu_tensors_and_training_mode():
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    mod = CoDAGQALandmarkPerf2(embed_dim=64, num_heads=2, num_kv_heads=1, window=8, num_landmarks_exact=4,
+                               num_landmarks_summary=4).eval()
+    st = mod.init_state(batch_size=1, device="cpu", dtype=torch.float32)
+    with pytest.raises(RuntimeError):
+        mod.step(torch.randn(1, 1, 64), st)
+    mod = mod.cuda().train()
+    st = mod.init_state(batch_size=1, device="cuda", dtype=torch.float32)
+    with pytest.raises(RuntimeError):
+        mod.step(torch.randn(1, 1, 64, device="cuda"), st)
