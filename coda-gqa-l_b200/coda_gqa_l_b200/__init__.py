@@ -7,11 +7,12 @@ from .adapters import EveCoDAAdapter, LlamaCoDAAdapter
 from .attention import CoDAGQALandmarkPerf2
 from .baseline import CoDAGQA
 from .primitives import HeadwiseRMSNorm, RotaryEmbedding
+from .stack import CoDAStack
 from .state import CoDAGQALandmarkStatePerf2
 from .state_io import _deep_copy_state, _state_to_cpu, _state_to_device, state_from_fields
 
 __all__ = [
-    "CoDAGQALandmarkPerf2", "CoDAGQALandmarkStatePerf2", "CoDAGQA", "LlamaCoDAAdapter", "EveCoDAAdapter",
+    "CoDAGQALandmarkPerf2", "CoDAGQALandmarkStatePerf2", "CoDAGQA", "CoDAStack", "LlamaCoDAAdapter", "EveCoDAAdapter",
     "HeadwiseRMSNorm", "RotaryEmbedding", "state_from_fields", "_state_to_cpu", "_state_to_device",
     "_deep_copy_state",
 ]

@@ -156,6 +156,9 @@ class CoDAGQALandmarkPerf2(nn.Module):
         self._cfg_cache: Dict[tuple, LayerCfg] = {}
         self._const_cache: Dict[tuple, tuple] = {}
         self._scratch: Dict[tuple, torch.Tensor] = {}
+        self._fused = None
+        # When set to a list, every attention launch appends (Lq, start_event, end_event) to it.
+        self.kernel_timers = None
 
     # ------------------------------------------------------------------ state
     def init_state(self, *, batch_size: int, device, dtype: torch.dtype,
@@ -260,8 +263,54 @@ class CoDAGQALandmarkPerf2(nn.Module):
         self._const_cache["k"] = (key, vals)
         return vals
 
+    def _fused_weight(self):
+        """One [q | k | v | lambda | gate | pad] weight so that the five input projections are a single GEMM.
+
+        The individual ``nn.Linear`` parameters are re-pointed at row ranges of the fused matrix (no second
+        copy of the weights; ``state_dict`` / ``load_state_dict`` keep working).  Rebuilt whenever a
+        parameter no longer aliases it (after ``.to()``, or when a projection was replaced)."""
+        lins = (self.q_proj, self.k_proj, self.v_proj, self.lambda_proj, self.write_proj)
+        if not all(type(l) is nn.Linear for l in lins):
+            return None
+        f = self._fused
+        w0 = self.q_proj.weight
+        if f is not None and f[0].device == w0.device and f[0].dtype == w0.dtype:
+            off, ok = 0, True
+            for l in lins:
+                if l.weight.data_ptr() != f[0][off:off + l.out_features].data_ptr():
+                    ok = False
+                    break
+                if l.bias is not None and l.bias.data_ptr() != f[1][off:off + l.out_features].data_ptr():
+                    ok = False
+                    break
+                off += l.out_features
+            if ok:
+                return f
+        n = sum(l.out_features for l in lins)
+        npad = (n + 15) // 16 * 16
+        W = torch.zeros((npad, self.embed_dim), device=w0.device, dtype=w0.dtype)
+        b = torch.zeros((npad,), device=w0.device, dtype=w0.dtype)
+        off = 0
+        for l in lins:
+            W[off:off + l.out_features].copy_(l.weight.data)
+            l.weight.data = W[off:off + l.out_features]
+            if l.bias is not None:
+                b[off:off + l.out_features].copy_(l.bias.data)
+                l.bias.data = b[off:off + l.out_features]
+            off += l.out_features
+        self._fused = (W, b)
+        return self._fused
+
     def _project(self, x: torch.Tensor, need_kv: bool):
         """q, k, v, lambda logits, gate logits as (B, L, features) tensors (upstream attention.py:396-410,508)."""
+        f = self._fused_weight() if need_kv else None
+        if f is not None:
+            H, Hkv, Dh = self.num_heads, self.num_kv_heads, self.head_dim
+            y = F.linear(x, f[0], f[1])
+            nq, nkv = H * Dh, Hkv * Dh
+            gate = y[..., nq + 2 * nkv + H:nq + 2 * nkv + H + 1] if self.write_policy != "none" else None
+            return (y[..., :nq], y[..., nq:nq + nkv], y[..., nq + nkv:nq + 2 * nkv],
+                    y[..., nq + 2 * nkv:nq + 2 * nkv + H], gate)
         q = self.q_proj(x)
         k = self.k_proj(x) if need_kv else None
         v = self.v_proj(x) if need_kv else None
@@ -291,6 +340,10 @@ class CoDAGQALandmarkPerf2(nn.Module):
     def _attend(self, cfg, st, Lq, q, qn, lam, k_blk, v_blk, out):
         _, _, _, _, nw = self._consts(q.device, q.dtype)
         ptrs = self._ptrs(st)
+        timers = self.kernel_timers
+        if timers is not None:                  # benchmark hook: CUDA events around the attention launch
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         check(lib.coda_b200_attend(
             C.byref(cfg), C.byref(ptrs), Lq,
             q.data_ptr(), q.stride(0), q.stride(1), qn.data_ptr(), qn.stride(0), qn.stride(1),
@@ -298,21 +351,46 @@ class CoDAGQALandmarkPerf2(nn.Module):
             _p(k_blk), 0 if k_blk is None else k_blk.stride(0), 0 if k_blk is None else k_blk.stride(1),
             _p(v_blk), 0 if v_blk is None else v_blk.stride(0), 0 if v_blk is None else v_blk.stride(1),
             _p(nw), out.data_ptr(), out.stride(0), out.stride(1), _stream()), "coda_b200_attend")
+        if timers is not None:
+            ev1.record()
+            timers.append((Lq, ev0, ev1))
 
-    def _write_one(self, cfg, st, k, v, g):
-        """Ring write of one token per state plus routing of the evicted one (upstream memory_banks.py:183-224)."""
+    def _write_one(self, cfg, st, k, v, g, rp: Optional[RingPos] = None):
+        """Ring write of one token per state plus routing of the evicted one (upstream memory_banks.py:183-224).
+
+        With ``rp`` given (CUDA-graph replay: scalars baked at capture time plus a device step counter) the
+        host mirrors are left alone; the caller advances them with :meth:`advance_host_scalars`."""
         _, _, _, eta, _ = self._consts(k.device, k.dtype)
         ptrs = self._ptrs(st)
-        rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
+        host = rp is None
+        if host:
+            rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
         check(lib.coda_b200_step_write(C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0),
                                        v.data_ptr(), v.stride(0), g.data_ptr(), eta.data_ptr(), _stream()),
               "coda_b200_step_write")
+        if host:
+            self.advance_host_scalars(st)
+
+    def advance_host_scalars(self, st: CoDAGQALandmarkStatePerf2, n: int = 1) -> None:
+        """Host mirror of ``n`` single-token writes: the ring fills, then the eviction pointer walks round it."""
         W = self.window
-        if st.recent_filled < W:
-            st.recent_filled += 1
-        else:
-            st.recent_idx = (st.recent_idx + 1) % W
-        st.pos += 1
+        fill = min(n, W - st.recent_filled)
+        st.recent_filled += fill
+        st.recent_idx = (st.recent_idx + (n - fill)) % W
+        st.pos += n
+
+    def step_graphable(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos) -> torch.Tensor:
+        """The default ``step`` (write, then attend) with no host-side branching on the state, so that it
+        can be captured in a CUDA graph: ring scalars come from ``rp`` (values at capture time plus the device
+        step counter ``rp.step_dev``).  Does not touch the Python-side scalars."""
+        B = x.shape[0]
+        cfg = self._cfg(B, x.dtype, state)
+        q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)
+        qn, lam, g = self._prep(cfg, 1, rp.pos, q, k, lam_logit, gate_logit, True, step_dev=rp.step_dev)
+        self._write_one(cfg, state, k, v, g, rp=rp)
+        out = torch.empty((B, 1, self.num_heads * self.head_dim), device=x.device, dtype=x.dtype)
+        self._attend(cfg, state, 1, q, qn, lam, None, None, out)
+        return self.o_proj(out)
 
     def _nothing_visible(self, st) -> bool:
         # Only an empty ring can leave every slot masked; the check costs a sync, so it is made
