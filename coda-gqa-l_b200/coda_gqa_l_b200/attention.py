@@ -159,6 +159,9 @@ class CoDAGQALandmarkPerf2(nn.Module):
         self._fused = None
         # When set to a list, every attention launch appends (Lq, start_event, end_event) to it.
         self.kernel_timers = None
+        # False forces the shape-generic kernels even where a tuned one exists (used by tests).
+        self.use_tuned_kernels = True
+        self._status = None
 
     # ------------------------------------------------------------------ state
     def init_state(self, *, batch_size: int, device, dtype: torch.dtype,
@@ -379,12 +382,60 @@ class CoDAGQALandmarkPerf2(nn.Module):
         st.recent_idx = (st.recent_idx + (n - fill)) % W
         st.pos += n
 
+    def _tuned_decode(self, cfg) -> bool:
+        ok = getattr(cfg, "_tuned_decode", None)
+        if ok is None:
+            ok = bool(lib.coda_b200_decode_attend_supported(C.byref(cfg)))
+            cfg._tuned_decode = ok
+        return ok and self.use_tuned_kernels
+
+    def _status_word(self, device) -> torch.Tensor:
+        if self._status is None or self._status.device != device:
+            self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._status
+
+    def device_status(self) -> int:
+        """0, or the code of a bounded device-side wait that expired in one of the tuned kernels
+        (1 = producer waiting for a free tile, 2 = consumer waiting for a tile).  Synchronises."""
+        return 0 if self._status is None else int(self._status.item())
+
+    def _step_fused(self, cfg, x, state, rp: RingPos, host_update: bool) -> torch.Tensor:
+        """Write-then-attend decode step on the tuned kernels: two launches between the two GEMMs
+        (cache write with in-kernel RoPE / gate sigmoid, then the fused attention)."""
+        B = x.shape[0]
+        dev, dt = x.device, x.dtype
+        q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)
+        inv_freq, cos_t, sin_t, eta, nw = self._consts(dev, dt)
+        ptrs = self._ptrs(state)
+        s = _stream()
+        check(lib.coda_b200_step_write_raw(
+            C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+            _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(), eta.data_ptr(), s),
+            "coda_b200_step_write_raw")
+        out = torch.empty((B, 1, self.num_heads * self.head_dim), device=dev, dtype=dt)
+        timers = self.kernel_timers
+        if timers is not None:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        check(lib.coda_b200_decode_attend(
+            C.byref(cfg), C.byref(ptrs), rp, 0, q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0),
+            inv_freq.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), _p(nw), out.data_ptr(), out.stride(0),
+            self._status_word(dev).data_ptr(), s), "coda_b200_decode_attend")
+        if timers is not None:
+            ev1.record()
+            timers.append((1, ev0, ev1))
+        if host_update:
+            self.advance_host_scalars(state)
+        return self.o_proj(out)
+
     def step_graphable(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos) -> torch.Tensor:
         """The default ``step`` (write, then attend) with no host-side branching on the state, so that it
         can be captured in a CUDA graph: ring scalars come from ``rp`` (values at capture time plus the device
         step counter ``rp.step_dev``).  Does not touch the Python-side scalars."""
         B = x.shape[0]
         cfg = self._cfg(B, x.dtype, state)
+        if self._tuned_decode(cfg):
+            return self._step_fused(cfg, x, state, rp, host_update=False)
         q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)
         qn, lam, g = self._prep(cfg, 1, rp.pos, q, k, lam_logit, gate_logit, True, step_dev=rp.step_dev)
         self._write_one(cfg, state, k, v, g, rp=rp)
@@ -426,6 +477,9 @@ class CoDAGQALandmarkPerf2(nn.Module):
         self._require_ready(x, state)
         cfg = self._cfg(B, x.dtype, state)
         qp = int(state.pos)
+        if attend and write_cache and include_current_in_attention and self._tuned_decode(cfg):
+            rp = RingPos(qp, int(state.recent_idx), int(state.recent_filled), None)
+            return self._step_fused(cfg, x, state, rp, host_update=True), state
         q, k, v, lam_logit, gate_logit = self._project(x, need_kv=write_cache)
         qn, lam, g = self._prep(cfg, 1, qp, q, k, lam_logit, gate_logit, write_cache)
         write_first = attend and include_current_in_attention and write_cache

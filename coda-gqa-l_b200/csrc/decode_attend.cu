@@ -1,0 +1,444 @@
+// Fused decode attention for bf16 states (head_dim 64 or 128, up to 8 query heads per KV head).
+//
+// One CTA per (state, KV head).  The K and V planes of that head -- all W+Me+Ms slots -- are read
+// from HBM exactly once, by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a 3-stage ring of
+// 64-slot tiles in shared memory; a producer warp keeps the ring full while four consumer warps
+// each own 16 slots of every tile.  All query heads of the GQA group and both streams (signal and
+// theta-rotated noise) share the staged tiles: they form the 16 rows of the m16n8k16 tensor-core
+// tiles used for Q.K^T and P.V.  The prologue applies RoPE and the learned per-head rotation to
+// the raw query projection and evaluates the lambda sigmoid while the first tiles are in flight;
+// softmax is an online, per-warp one (quad shuffles), merged across the four warps at the end;
+// the epilogue subtracts lambda * noise and applies the head RMSNorm.
+//
+// HBM traffic per CTA = the two planes (2 * Lbuf * Dh * 2 bytes) + a few hundred bytes of q,
+// lambda, mask and output: the kernel is bandwidth-bound by construction.  Every mbarrier wait is
+// bounded; on expiry a status word is set and the kernel finishes (with undefined output) instead
+// of hanging.
+#include "coda_common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <map>
+#include <tuple>
+
+namespace {
+
+constexpr int DA_TILE = 64;          // slots per stage
+constexpr int DA_STAGES = 3;
+constexpr int DA_CWARPS = 4;         // consumer warps
+constexpr int DA_THREADS = (DA_CWARPS + 1) * 32;
+constexpr int DA_WAIT_LIMIT = 1 << 22;
+
+struct DecodeParams {
+  int B, H, Hkv, G, Lbuf, mask_unused, norm_full, interleaved, angle_bf16;
+  float eps, scale_log2;
+  coda_ring_pos rp; int W; int pos_minus_one;     // query position = ring position (- 1 when the token was written first)
+  const bf16* q; long long q_bs;                  // raw query projection [B][H*Dh]
+  const bf16* lam_logit; long long lam_bs;        // [B][H]
+  const float* inv_freq; const bf16* cos_t; const bf16* sin_t;
+  const uint8_t* allowed;
+  const bf16* norm_w;
+  bf16* out; long long out_bs;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after DA_WAIT_LIMIT polls, records where, and lets the kernel run to its end.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (int it = 0; it < DA_WAIT_LIMIT; ++it) if (mbar_try(bar, parity)) return;
+  if (status) atomicExch(status, code);
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(DA_CWARPS * 32) : "memory"); }
+
+// Byte offset of 16-byte chunk `c` of row `s` inside a [64 x DH] bf16 tile written by TMA as DH/64
+// boxes of 64 rows x 128 bytes with the 128-byte swizzle (chunk index XOR row mod 8).
+template <int DH>
+__device__ __forceinline__ uint32_t tile_off(int s, int c) {
+  return (uint32_t)((c >> 3) * (DA_TILE * 128) + s * 128 + (((c & 7) ^ (s & 7)) << 4));
+}
+
+template <int DH>
+__global__ void __launch_bounds__(DA_THREADS, 2)
+decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
+  constexpr int HALF = DH / 2;
+  constexpr int KSTEPS = DH / 16;            // k-steps of Q.K^T
+  constexpr int NT_O = DH / 8;               // n-tiles of the output
+  constexpr int TILE_BYTES = DA_TILE * DH * 2;
+  constexpr int QSTR = DH + 8;               // padded row stride of the staged queries (elements)
+
+  extern __shared__ unsigned char smem_raw[];
+  // the swizzled TMA tiles need a 1024-byte aligned base; the launch reserves the slack
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* stage0 = smem;                                            // DA_STAGES * 2 * TILE_BYTES
+  bf16* sQ = reinterpret_cast<bf16*>(smem + DA_STAGES * 2 * TILE_BYTES);   // [16][QSTR]
+  float* sML = reinterpret_cast<float*>(sQ + 16 * QSTR);                   // [2][DA_CWARPS][16]  (m, l)
+  float* sLam = sML + 2 * DA_CWARPS * 16;                                  // [8]
+  float* sCS = sLam + 8;                                                   // [HALF] cos, [HALF] sin
+  uint64_t* full = reinterpret_cast<uint64_t*>(sCS + 2 * HALF);            // [DA_STAGES]
+  uint64_t* empty = full + DA_STAGES;                                      // [DA_STAGES]
+  uint8_t* sAl = reinterpret_cast<uint8_t*>(empty + DA_STAGES);            // [Lbuf rounded up to a tile]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int hk = blockIdx.x, b = blockIdx.y, G = p.G;
+  const int nst = (p.Lbuf + DA_TILE - 1) / DA_TILE;
+  const int plane = b * p.Hkv + hk;
+
+  if (tid == 0) {
+    for (int i = 0; i < DA_STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], DA_CWARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == DA_CWARPS) {
+    // ---------------- producer: keep the ring of K/V tiles full ----------------
+    if (lane == 0) {
+      for (int s = 0; s < nst; ++s) {
+        const int bi = s % DA_STAGES;
+        if (s >= DA_STAGES) mbar_wait(&empty[bi], ((s / DA_STAGES) - 1) & 1, p.status, 1);
+        mbar_expect_tx(&full[bi], 2 * TILE_BYTES);
+        unsigned char* kd = stage0 + bi * 2 * TILE_BYTES;
+        unsigned char* vd = kd + TILE_BYTES;
+#pragma unroll
+        for (int hf = 0; hf < DH / 64; ++hf) {
+          tma_load_3d(kd + hf * (DA_TILE * 128), &kmap, &full[bi], hf * 64, s * DA_TILE, plane);
+          tma_load_3d(vd + hf * (DA_TILE * 128), &vmap, &full[bi], hf * 64, s * DA_TILE, plane);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers: prologue (queries) while the first tiles are in flight ----------------
+  const int CT = DA_CWARPS * 32;
+  const long long qpos = ring_now(p.rp, p.W).pos - p.pos_minus_one;
+  for (int i = tid; i < HALF; i += CT) {
+    float ta = (float)qpos, inv = p.inv_freq[i];
+    if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
+    float ang = __fmul_rn(ta, inv);
+    if (p.angle_bf16) ang = bf16_round(ang);
+    float c = cosf(ang), s = sinf(ang);
+    if (p.angle_bf16) { c = bf16_round(c); s = bf16_round(s); }
+    sCS[i] = bf16_round(c);
+    sCS[HALF + i] = bf16_round(s);
+  }
+  for (int i = tid; i < 16 * QSTR; i += CT) sQ[i] = __float2bfloat16_rn(0.f);
+  for (int i = tid; i < nst * DA_TILE; i += CT) sAl[i] = (i < p.Lbuf) ? p.allowed[(long long)b * p.Lbuf + i] : 0;
+  if (tid < G) {
+    const float z = __bfloat162float(p.lam_logit[(long long)b * p.lam_bs + hk * G + tid]);
+    sLam[tid] = t_sigmoid<bf16>(z);
+  }
+  bar_consumers();
+  const bf16* qrow = p.q + (long long)b * p.q_bs + (long long)hk * G * DH;
+  for (int w = tid; w < G * HALF; w += CT) {           // RoPE -> rows 0..G-1 (signal)
+    const int g = w / HALF, i = w % HALF;
+    const float c = sCS[i], s = sCS[HALF + i];
+    int ia, ib; float oa, ob;
+    if (p.interleaved) {
+      ia = 2 * i; ib = 2 * i + 1;
+      const float xe = __bfloat162float(qrow[g * DH + ia]), xo = __bfloat162float(qrow[g * DH + ib]);
+      oa = t_sub<bf16>(t_mul<bf16>(xe, c), t_mul<bf16>(xo, s));
+      ob = t_add<bf16>(t_mul<bf16>(xe, s), t_mul<bf16>(xo, c));
+    } else {
+      ia = i; ib = i + HALF;
+      const float x1 = __bfloat162float(qrow[g * DH + ia]), x2 = __bfloat162float(qrow[g * DH + ib]);
+      oa = t_add<bf16>(t_mul<bf16>(x1, c), t_mul<bf16>(-x2, s));
+      ob = t_add<bf16>(t_mul<bf16>(x2, c), t_mul<bf16>(x1, s));
+    }
+    sQ[g * QSTR + ia] = __float2bfloat16_rn(oa);
+    sQ[g * QSTR + ib] = __float2bfloat16_rn(ob);
+  }
+  bar_consumers();
+  for (int w = tid; w < G * HALF; w += CT) {           // learned rotation of (even, odd) pairs -> rows G..2G-1 (noise)
+    const int g = w / HALF, i = w % HALF;
+    const int hq = hk * G + g;
+    const float qe = __bfloat162float(sQ[g * QSTR + 2 * i]), qo = __bfloat162float(sQ[g * QSTR + 2 * i + 1]);
+    const float ct = __bfloat162float(p.cos_t[hq * HALF + i]), st = __bfloat162float(p.sin_t[hq * HALF + i]);
+    sQ[(G + g) * QSTR + 2 * i] = __float2bfloat16_rn(t_sub<bf16>(t_mul<bf16>(qe, ct), t_mul<bf16>(qo, st)));
+    sQ[(G + g) * QSTR + 2 * i + 1] = __float2bfloat16_rn(t_add<bf16>(t_mul<bf16>(qe, st), t_mul<bf16>(qo, ct)));
+  }
+  bar_consumers();
+
+  uint32_t qf[KSTEPS][4];
+  {
+    const uint32_t qbase = smem_u32(sQ) + (uint32_t)(((lane & 15) * QSTR + (lane >> 4) * 8) * 2);
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) ldsm_x4(qf[kk], qbase + kk * 32);
+  }
+
+  float oacc[NT_O][4];
+#pragma unroll
+  for (int j = 0; j < NT_O; ++j) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows lane/4 and lane/4 + 8
+  const int li = lane >> 3, lr = lane & 7;
+
+  for (int s = 0; s < nst; ++s) {
+    const int bi = s % DA_STAGES;
+    mbar_wait(&full[bi], (s / DA_STAGES) & 1, p.status, 2);
+    const uint32_t kb = smem_u32(stage0 + bi * 2 * TILE_BYTES);
+    const uint32_t vb = kb + TILE_BYTES;
+    // ---- S = Q K^T over this warp's 16 slots ----
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const int krow = warp * 16 + (li >> 1) * 8 + lr;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      uint32_t kf[4];
+      ldsm_x4(kf, kb + tile_off<DH>(krow, kk * 2 + (li & 1)));
+      mma_bf16(sc[0], qf[kk], kf[0], kf[1]);
+      mma_bf16(sc[1], qf[kk], kf[2], kf[3]);
+    }
+    // ---- mask + online softmax (rows r0 = lane/4, r1 = r0 + 8) ----
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int slot = s * DA_TILE + warp * 16 + nt * 8 + 2 * (lane & 3) + e;
+        const bool vis = slot < p.Lbuf && (!p.mask_unused || sAl[slot] != 0);
+        sc[nt][e] = vis ? sc[nt][e] * p.scale_log2 : -INFINITY;
+        sc[nt][2 + e] = vis ? sc[nt][2 + e] * p.scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, sc[nt][e]);
+        mx1 = fmaxf(mx1, sc[nt][2 + e]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
+    const float ref0 = nm0 == -INFINITY ? 0.f : nm0, ref1 = nm1 == -INFINITY ? 0.f : nm1;
+    const float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);
+    m0 = nm0; m1 = nm1;
+    uint32_t pf[4];
+    {
+      const float p00 = exp2f(sc[0][0] - ref0), p01 = exp2f(sc[0][1] - ref0), p02 = exp2f(sc[0][2] - ref1), p03 = exp2f(sc[0][3] - ref1);
+      const float p10 = exp2f(sc[1][0] - ref0), p11 = exp2f(sc[1][1] - ref0), p12 = exp2f(sc[1][2] - ref1), p13 = exp2f(sc[1][3] - ref1);
+      l0 = l0 * a0 + (p00 + p01 + p10 + p11);
+      l1 = l1 * a1 + (p02 + p03 + p12 + p13);
+      pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03); pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
+    }
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) { oacc[j][0] *= a0; oacc[j][1] *= a0; oacc[j][2] *= a1; oacc[j][3] *= a1; }
+    // ---- O += P V ----
+    const int vrow = warp * 16 + (li & 1) * 8 + lr;
+#pragma unroll
+    for (int j = 0; j < NT_O; j += 2) {
+      uint32_t vf[4];
+      ldsm_x4_t(vf, vb + tile_off<DH>(vrow, j + (li >> 1)));
+      mma_bf16(oacc[j], pf, vf[0], vf[1]);
+      mma_bf16(oacc[j + 1], pf, vf[2], vf[3]);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[bi]);
+  }
+
+  // ---- merge the four warps' partial softmaxes ----
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if ((lane & 3) == 0) {
+    const int r = lane >> 2;
+    sML[warp * 16 + r] = m0; sML[warp * 16 + r + 8] = m1;
+    sML[DA_CWARPS * 16 + warp * 16 + r] = l0; sML[DA_CWARPS * 16 + warp * 16 + r + 8] = l1;
+  }
+  bar_consumers();                       // every warp is done with the tiles: their memory can be reused
+  float* comb = reinterpret_cast<float*>(stage0);            // [DA_CWARPS][16][DH]
+  {
+    const int r = lane >> 2, cb = 2 * (lane & 3);
+#pragma unroll
+    for (int j = 0; j < NT_O; ++j) {
+      float* d0 = comb + ((warp * 16 + r) * DH + j * 8 + cb);
+      float* d1 = comb + ((warp * 16 + r + 8) * DH + j * 8 + cb);
+      d0[0] = oacc[j][0]; d0[1] = oacc[j][1]; d1[0] = oacc[j][2]; d1[1] = oacc[j][3];
+    }
+  }
+  bar_consumers();
+
+  // ---- epilogue: one warp per query head: sig - lam*noise, optional RMSNorm, bf16 store ----
+  for (int g = warp; g < G; g += DA_CWARPS) {
+    float os[DH / 32], on[DH / 32];
+#pragma unroll
+    for (int st = 0; st < 2; ++st) {
+      const int row = st * G + g;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < DA_CWARPS; ++w) M = fmaxf(M, sML[w * 16 + row]);
+      float f[DA_CWARPS], L = 0.f;
+#pragma unroll
+      for (int w = 0; w < DA_CWARPS; ++w) {
+        const float mw = sML[w * 16 + row];
+        f[w] = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        L += f[w] * sML[DA_CWARPS * 16 + w * 16 + row];
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+      for (int i = 0; i < DH / 32; ++i) {
+        const int d = lane + 32 * i;
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < DA_CWARPS; ++w) acc += f[w] * comb[(w * 16 + row) * DH + d];
+        const float v = bf16_round(acc * inv);
+        if (st == 0) os[i] = v; else on[i] = v;
+      }
+    }
+    const float lam = sLam[g];
+    float diff[DH / 32], sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < DH / 32; ++i) {
+      diff[i] = t_sub<bf16>(os[i], t_mul<bf16>(lam, on[i]));
+      sq += bf16_round(diff[i] * diff[i]);
+    }
+    bf16* op = p.out + (long long)b * p.out_bs + (long long)(hk * G + g) * DH;
+    if (p.norm_full) {
+      const float var = bf16_round(warp_sum(sq) / (float)DH);
+      const float rs = bf16_round(rsqrtf(bf16_round(var + p.eps)));
+#pragma unroll
+      for (int i = 0; i < DH / 32; ++i) {
+        const int d = lane + 32 * i;
+        op[d] = __float2bfloat16_rn(t_mul<bf16>(t_mul<bf16>(diff[i], rs), __bfloat162float(p.norm_w[d])));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < DH / 32; ++i) op[lane + 32 * i] = __float2bfloat16_rn(diff[i]);
+    }
+  }
+}
+
+// ---- host side: tensor maps for the K and V planes ---------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// Tensor map over a [planes][Lbuf][Dh] bf16 buffer: box = 64 elements x 64 rows x 1 plane, 128-byte swizzle.
+// Rows past Lbuf inside a box are filled with zeros and never bleed into the next plane.
+bool plane_map(CUtensorMap* out, const void* base, int planes, int Lbuf, int Dh) {
+  static std::mutex mu;
+  static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_tuple(base, planes, Lbuf, Dh);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return true; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)Dh, (cuuint64_t)Lbuf, (cuuint64_t)planes};
+  cuuint64_t strides[2] = {(cuuint64_t)Dh * 2, (cuuint64_t)Lbuf * Dh * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)DA_TILE, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *out = m;
+  return true;
+}
+
+template <int DH>
+size_t decode_smem(int Lbuf) {
+  const int nst = (Lbuf + DA_TILE - 1) / DA_TILE;
+  return (size_t)DA_STAGES * 2 * DA_TILE * DH * 2 + 16 * (DH + 8) * 2 + (2 * DA_CWARPS * 16 + 8 + DH) * 4 +
+         2 * DA_STAGES * 8 + (size_t)nst * DA_TILE + 16 + 1024;
+}
+
+template <int DH>
+int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, const DecodeParams& p, cudaStream_t s) {
+  const size_t smem = decode_smem<DH>(p.Lbuf);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(decode_attend_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    configured = true;
+  }
+  CODA_REQUIRE(smem <= 110 * 1024, CODA_ERR_LIMIT, "decode_attend: %d slots need %zu bytes of shared memory", p.Lbuf, smem);
+  decode_attend_kernel<DH><<<dim3(p.Hkv, p.B), DA_THREADS, smem, s>>>(km, vm, p);
+  CODA_CHECK_LAUNCH("decode_attend");
+  return CODA_OK;
+}
+
+}  // namespace
+
+// True when the tuned kernel covers this configuration; otherwise callers use the generic kernels.
+extern "C" int coda_b200_decode_attend_supported(const coda_layer_cfg* cfg) {
+  if (!coda_cfg_ok(cfg)) return 0;
+  const int G = cfg->H / cfg->Hkv;
+  return cfg->dtype == CODA_BF16 && (cfg->Dh == 64 || cfg->Dh == 128) && G <= 8 &&
+         (size_t)(cfg->W + cfg->Me + cfg->Ms) <= 4096 && encode_fn() != nullptr;
+}
+
+extern "C" int coda_b200_decode_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                       int32_t token_already_written,
+                                       const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                       const float* inv_freq, const void* cos_theta, const void* sin_theta,
+                                       const void* norm_w, void* out, int64_t out_bs, int32_t* status,
+                                       coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "decode_attend: invalid layer configuration");
+  CODA_REQUIRE(coda_b200_decode_attend_supported(cfg), CODA_ERR_ARG,
+               "decode_attend: needs bf16, head_dim 64 or 128 and at most 8 query heads per KV head");
+  CODA_REQUIRE(q_raw && lam_logit && inv_freq && cos_theta && sin_theta && out && st->k_buf && st->v_buf && st->allowed,
+               CODA_ERR_ARG, "decode_attend: null pointer");
+  CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "decode_attend: head-norm weight missing");
+  CODA_REQUIRE(((uintptr_t)st->k_buf % 16 == 0) && ((uintptr_t)st->v_buf % 16 == 0), CODA_ERR_ARG,
+               "decode_attend: k_buf / v_buf must be 16-byte aligned");
+  const int Lbuf = cfg->W + cfg->Me + cfg->Ms;
+  CUtensorMap km, vm;
+  CODA_REQUIRE(plane_map(&km, st->k_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh) &&
+               plane_map(&vm, st->v_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh), CODA_ERR_LAUNCH,
+               "decode_attend: cuTensorMapEncodeTiled failed");
+  DecodeParams p;
+  p.B = cfg->B; p.H = cfg->H; p.Hkv = cfg->Hkv; p.G = cfg->H / cfg->Hkv; p.Lbuf = Lbuf;
+  p.mask_unused = cfg->mask_unused; p.norm_full = cfg->head_norm_full; p.interleaved = cfg->rope_interleaved;
+  p.angle_bf16 = cfg->angle_dtype == CODA_BF16; p.eps = cfg->eps;
+  p.scale_log2 = 1.4426950408889634f / sqrtf((float)cfg->Dh);
+  p.rp = rp; p.W = cfg->W; p.pos_minus_one = token_already_written ? 1 : 0;
+  p.q = (const bf16*)q_raw; p.q_bs = q_bs; p.lam_logit = (const bf16*)lam_logit; p.lam_bs = lam_bs;
+  p.inv_freq = inv_freq; p.cos_t = (const bf16*)cos_theta; p.sin_t = (const bf16*)sin_theta;
+  p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w; p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
+  cudaStream_t s = (cudaStream_t)stream;
+  return cfg->Dh == 128 ? launch_decode<128>(km, vm, p, s) : launch_decode<64>(km, vm, p, s);
+}

@@ -9,7 +9,24 @@ struct StepParams {
   const void* k_new; long long k_bs;
   const void* v_new; long long v_bs;
   const float* gate; const float* eta_logit;
+  // raw mode: k_new is the un-rotated key projection and the gate comes as a logit; RoPE and the
+  // sigmoid are applied here (saves the separate post-processing launch on the decode path)
+  int raw; const float* inv_freq; const void* gate_logit; long long gate_bs;
 };
+
+// RoPE'd element d of head-row `row` (Dh values, un-rotated) given cos/sin tables of Dh/2 entries.
+template <typename T>
+__device__ __forceinline__ float rope_elem(const T* row, int d, int Dh, int interleaved, const float* cs, const float* sn) {
+  const int half = Dh >> 1;
+  if (interleaved) {                                   // primitives.py:99-106
+    const int i = d >> 1;
+    const float xe = El<T>::ld(row + 2 * i), xo = El<T>::ld(row + 2 * i + 1);
+    return (d & 1) ? t_add<T>(t_mul<T>(xe, sn[i]), t_mul<T>(xo, cs[i])) : t_sub<T>(t_mul<T>(xe, cs[i]), t_mul<T>(xo, sn[i]));
+  }
+  const int i = d < half ? d : d - half;               // primitives.py:108-113
+  const float x1 = El<T>::ld(row + i), x2 = El<T>::ld(row + i + half);
+  return d < half ? t_add<T>(t_mul<T>(x1, cs[i]), t_mul<T>(-x2, sn[i])) : t_add<T>(t_mul<T>(x2, cs[i]), t_mul<T>(x1, sn[i]));
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
@@ -27,13 +44,38 @@ __global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
   float* gr = p.st.g_recent + (long long)b * W;
   const T* kn = (const T*)p.k_new + (long long)b * p.k_bs;
   const T* vn = (const T*)p.v_new + (long long)b * p.v_bs;
-  const float g_new = p.gate[b];
+  float g_new;
+  float* cs = sm + 3 * HD + Hkv * lfd + (Me > Ms ? Me : Ms) + 1;   // [Dh/2] cos, then [Dh/2] sin (raw mode)
+  float* sn = cs + Dh / 2;
+  if (p.raw) {
+    g_new = 1.0f;
+    if (c.gated) g_new = t_sigmoid<T>(El<T>::ld((const T*)p.gate_logit + (long long)b * p.gate_bs));
+    const bool abf = c.angle_dtype == CODA_BF16;
+    for (int i = tid; i < Dh / 2; i += NT) {
+      float ta = (float)r.pos, inv = p.inv_freq[i];
+      if (abf) { ta = bf16_round(ta); inv = bf16_round(inv); }
+      float ang = __fmul_rn(ta, inv);
+      if (abf) ang = bf16_round(ang);
+      float cc = cosf(ang), ss = sinf(ang);
+      if (abf) { cc = bf16_round(cc); ss = bf16_round(ss); }
+      cs[i] = El<T>::rnd(cc); sn[i] = El<T>::rnd(ss);
+    }
+    __syncthreads();
+  } else {
+    g_new = p.gate[b];
+  }
+  // element e = h*Dh + d of the new (rotated) key
+  auto new_k = [&](int e) -> float {
+    if (!p.raw) return El<T>::ld(kn + e);
+    const int h = e / Dh, d = e % Dh;
+    return rope_elem<T>(kn + h * Dh, d, Dh, c.rope_interleaved, cs, sn);
+  };
 
   if (r.filled < W) {                                   // memory_banks.py:195-201
     const int slot = r.filled;
     for (int e = tid; e < HD; e += NT) {
       const int h = e / Dh, d = e % Dh;
-      kb[((long long)h * Lbuf + slot) * Dh + d] = kn[e];
+      El<T>::st(kb + ((long long)h * Lbuf + slot) * Dh + d, new_k(e));
       vb[((long long)h * Lbuf + slot) * Dh + d] = vn[e];
     }
     if (tid == 0) { gr[slot] = g_new; al[slot] = 1; }
@@ -194,27 +236,31 @@ __global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
   // ---- the new token takes the evicted slot (memory_banks.py:219-222) ----
   for (int e = tid; e < HD; e += NT) {
     const int h = e / Dh, d = e % Dh;
-    kb[((long long)h * Lbuf + ev) * Dh + d] = kn[e];
+    El<T>::st(kb + ((long long)h * Lbuf + ev) * Dh + d, new_k(e));
     vb[((long long)h * Lbuf + ev) * Dh + d] = vn[e];
   }
   if (tid == 0) gr[ev] = g_new;
 }
 
-extern "C" int coda_b200_step_write(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
-                                    const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
-                                    const float* gate, const float* eta_logit, coda_stream_t stream) {
+static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                           const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
+                           const float* gate, const float* eta_logit, int raw, const float* inv_freq,
+                           const void* gate_logit, int64_t gate_bs, coda_stream_t stream) {
   CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "step_write: invalid layer configuration");
-  CODA_REQUIRE(st->k_buf && st->v_buf && st->allowed && st->g_recent && k_new && v_new && gate, CODA_ERR_ARG,
+  CODA_REQUIRE(st->k_buf && st->v_buf && st->allowed && st->g_recent && k_new && v_new, CODA_ERR_ARG,
                "step_write: null pointer");
+  CODA_REQUIRE(raw ? (inv_freq && (!cfg->gated || gate_logit)) : (gate != nullptr), CODA_ERR_ARG,
+               "step_write: gate / frequency inputs missing");
   CODA_REQUIRE(cfg->Me == 0 || (st->mem_last_exact && st->exact_v_norm), CODA_ERR_ARG, "step_write: exact bank pointers missing");
   CODA_REQUIRE(cfg->Ms == 0 || (st->sum_lf_k_norm && eta_logit), CODA_ERR_ARG, "step_write: summary bank pointers missing");
   CODA_REQUIRE(rp.recent_idx >= 0 && rp.recent_idx < cfg->W && rp.recent_filled >= 0 && rp.recent_filled <= cfg->W,
                CODA_ERR_ARG, "step_write: ring scalars out of range");
   StepParams p; p.c = *cfg; p.st = *st; p.rp = rp;
   p.k_new = k_new; p.k_bs = k_bs; p.v_new = v_new; p.v_bs = v_bs; p.gate = gate; p.eta_logit = eta_logit;
+  p.raw = raw; p.inv_freq = inv_freq; p.gate_logit = gate_logit; p.gate_bs = gate_bs;
   const int HD = cfg->Hkv * cfg->Dh, lfd = cfg->Dh - cfg->Dh / 2;
   const int mx = cfg->Me > cfg->Ms ? cfg->Me : cfg->Ms;
-  const size_t smem = sizeof(float) * (size_t)(3 * HD + cfg->Hkv * lfd + mx + 1);
+  const size_t smem = sizeof(float) * (size_t)(3 * HD + cfg->Hkv * lfd + mx + 1 + cfg->Dh);
   CODA_REQUIRE(smem <= 200 * 1024, CODA_ERR_LIMIT, "step_write: Hkv*Dh = %d too large for one CTA", HD);
   cudaStream_t s = (cudaStream_t)stream;
   if (cfg->dtype == CODA_F32) {
@@ -226,4 +272,17 @@ extern "C" int coda_b200_step_write(const coda_layer_cfg* cfg, const coda_state_
   }
   CODA_CHECK_LAUNCH("step_write");
   return CODA_OK;
+}
+
+extern "C" int coda_b200_step_write(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                    const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                    const float* gate, const float* eta_logit, coda_stream_t stream) {
+  return step_write_impl(cfg, st, rp, k_new, k_bs, v_new, v_bs, gate, eta_logit, 0, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int coda_b200_step_write_raw(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                        const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                        const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                        const float* eta_logit, coda_stream_t stream) {
+  return step_write_impl(cfg, st, rp, k_raw, k_bs, v_new, v_bs, nullptr, eta_logit, 1, inv_freq, gate_logit, gate_bs, stream);
 }
