@@ -15,6 +15,7 @@
 // bounded; on expiry a status word is set and the kernel finishes (with undefined output) instead
 // of hanging.
 #include "coda_common.cuh"
+#include "tma_utils.cuh"
 #include <cuda.h>
 #include <mutex>
 #include <map>
@@ -26,7 +27,6 @@ constexpr int DA_TILE = 64;          // slots per stage
 constexpr int DA_STAGES = 3;
 constexpr int DA_CWARPS = 4;         // consumer warps
 constexpr int DA_THREADS = (DA_CWARPS + 1) * 32;
-constexpr int DA_WAIT_LIMIT = 1 << 22;
 
 struct DecodeParams {
   int B, H, Hkv, G, Lbuf, mask_unused, norm_full, interleaved, angle_bf16;
@@ -41,28 +41,8 @@ struct DecodeParams {
   int* status;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up after DA_WAIT_LIMIT polls, records where, and lets the kernel run to its end.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (int it = 0; it < DA_WAIT_LIMIT; ++it) if (mbar_try(bar, parity)) return;
-  if (status) atomicExch(status, code);
-}
+using tma::smem_u32; using tma::mbar_init; using tma::mbar_expect_tx; using tma::mbar_arrive; using tma::mbar_try;
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) { tma::mbar_wait(bar, parity, status, code); }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");

@@ -1,6 +1,7 @@
 // Decode-step cache write: ring FIFO + routing of the evicted token into the exact and summary banks.
 // One CTA per state.  Reads the two unit-norm routing caches once, rewrites at most one slot per bank.
 #include "coda_common.cuh"
+#include "tma_utils.cuh"
 
 struct StepParams {
   coda_layer_cfg c;
@@ -12,7 +13,73 @@ struct StepParams {
   // raw mode: k_new is the un-rotated key projection and the gate comes as a logit; RoPE and the
   // sigmoid are applied here (saves the separate post-processing launch on the decode path)
   int raw; const float* inv_freq; const void* gate_logit; long long gate_bs;
+  // stage != 0: both routing caches of the state (contiguous per state) are brought into shared memory by
+  // two bulk copies issued at kernel entry, so that scoring does not wait on one global round trip per row
+  int stage; int stage_off;       // byte offset of the staged caches inside dynamic shared memory
+  int* status;
 };
+
+// Lane-partial dot product of a shared-memory fp32 vector with a row of n elements (no reduction):
+// each lane takes one contiguous chunk, so a row is one vector load per lane.
+template <typename T>
+__device__ __forceinline__ float lane_dot(const float* __restrict__ a, const T* __restrict__ row, int n, int lane) {
+  float part = 0.f;
+  if (sizeof(T) == 2 && n == 128) {
+    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(row) + lane * 2;
+    const float4 av = *reinterpret_cast<const float4*>(a + lane * 4);
+    const __nv_bfloat162 p0 = r2[0], p1 = r2[1];
+    part = av.x * __low2float(p0) + av.y * __high2float(p0) + av.z * __low2float(p1) + av.w * __high2float(p1);
+  } else if (sizeof(T) == 2 && n == 64) {
+    const __nv_bfloat162 p0 = reinterpret_cast<const __nv_bfloat162*>(row)[lane];
+    const float2 av = *reinterpret_cast<const float2*>(a + lane * 2);
+    part = av.x * __low2float(p0) + av.y * __high2float(p0);
+  } else {
+    for (int d = lane; d < n; d += 32) part += a[d] * El<T>::ld(row + d);
+  }
+  return part;
+}
+
+// Score of bank slot m: sum over KV heads of the (dtype-rounded) dot products of the Hkv unit vectors in
+// `hat` ([Hkv][n], shared) with rows (h, m) of `cache` ([Hkv][M][n]).  Heads are processed eight at a time:
+// the eight lane-partial sums are reduced together by a butterfly that halves the number of live values at
+// every exchange (12 shuffles per group instead of 40).  All lanes return the same value.
+template <typename T>
+__device__ __forceinline__ float slot_score(const float* __restrict__ hat, const T* __restrict__ cache,
+                                            int m, int M, int n, int Hkv, int lane) {
+  float tot = 0.f;
+  for (int h0 = 0; h0 < Hkv; h0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int h = h0 + i;
+      v[i] = h < Hkv ? lane_dot<T>(hat + h * n, cache + ((long long)h * M + m) * n, n, lane) : 0.f;
+    }
+    const bool u16 = lane & 16, u8 = lane & 8, u4 = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float keep = u16 ? v[i + 4] : v[i], send = u16 ? v[i] : v[i + 4];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float keep = u8 ? v[i + 2] : v[i], send = u8 ? v[i] : v[i + 2];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    {
+      const float keep = u4 ? v[1] : v[0], send = u4 ? v[0] : v[1];
+      v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+    // lanes with the same bits 4,3,2 now hold the full dot product of head h0 + 4*b4 + 2*b3 + b2
+    float s = El<T>::rnd(v[0]);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    s += __shfl_xor_sync(0xffffffffu, s, 8);
+    s += __shfl_xor_sync(0xffffffffu, s, 16);
+    tot += s;
+  }
+  return tot;
+}
 
 // RoPE'd element d of head-row `row` (Dh values, un-rotated) given cos/sin tables of Dh/2 entries.
 template <typename T>
@@ -29,7 +96,7 @@ __device__ __forceinline__ float rope_elem(const T* row, int d, int Dh, int inte
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
+__global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
   extern __shared__ float sm[];
   const coda_layer_cfg& c = p.c;
   const int b = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
@@ -90,8 +157,29 @@ __global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
   float* vhat = ve + HD;          // [HD] unit-norm value   (later: new V row for re-normalising)
   float* khat = vhat + HD;        // [Hkv*lfd] unit-norm LF key (later: new LF key row)
   float* sc = khat + Hkv * lfd;   // [max(Me,Ms)] scores
+  long long* s_last = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(sn + Dh / 2) + 7) & ~(uintptr_t)7);  // [Me] LRU stamps
+  unsigned char* s_used = reinterpret_cast<unsigned char*>(s_last + Me);             // [Me + Ms] slot-in-use flags
   __shared__ int s_idx, s_flag;
   __shared__ float s_eta_keep;
+  const size_t vbytes = (size_t)Hkv * Me * Dh * sizeof(T), kbytes = (size_t)Hkv * Ms * lfd * sizeof(T);
+  T* cacheV = reinterpret_cast<T*>(reinterpret_cast<unsigned char*>(sm) + p.stage_off);
+  T* cacheK = reinterpret_cast<T*>(reinterpret_cast<unsigned char*>(cacheV) + vbytes);
+  __shared__ __align__(8) uint64_t s_bar;
+  if (p.stage) {
+    if (tid == 0) { tma::mbar_init(&s_bar, 1); tma::fence_barrier_init(); }
+    __syncthreads();
+    if (tid == 0) {
+      tma::mbar_expect_tx(&s_bar, (uint32_t)(vbytes + kbytes));
+      const unsigned char* gv = reinterpret_cast<const unsigned char*>(p.st.exact_v_norm) + (size_t)b * vbytes;
+      const unsigned char* gk = reinterpret_cast<const unsigned char*>(p.st.sum_lf_k_norm) + (size_t)b * kbytes;
+      for (size_t o = 0; o < vbytes; o += 32768)
+        tma::bulk_load(reinterpret_cast<unsigned char*>(cacheV) + o, gv + o, (uint32_t)(vbytes - o < 32768 ? vbytes - o : 32768), &s_bar);
+      for (size_t o = 0; o < kbytes; o += 32768)
+        tma::bulk_load(reinterpret_cast<unsigned char*>(cacheK) + o, gk + o, (uint32_t)(kbytes - o < 32768 ? kbytes - o : 32768), &s_bar);
+    }
+  }
+  for (int m = tid; m < Me + Ms; m += NT) s_used[m] = al[W + m];
+  for (int m = tid; m < Me; m += NT) s_last[m] = ((const long long*)p.st.mem_last_exact)[(long long)b * Me + m];
 
   for (int e = tid; e < HD; e += NT) {
     const int h = e / Dh, d = e % Dh;
@@ -116,19 +204,15 @@ __global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
   }
   __syncthreads();
 
+  if (p.stage) tma::mbar_wait(&s_bar, 0, p.status, 3);
+
   // ================= exact bank (memory_banks.py:230-337) =================
   if (Me > 0) {
     const int Ae = c.active_exact;
-    const T* vnorm = (const T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh;
+    const T* vnorm = p.stage ? cacheV : (const T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh;
     for (int m = warp; m < Me; m += NW) {
-      float tot = 0.f;
-      for (int h = 0; h < Hkv; ++h) {
-        const T* row = vnorm + ((long long)h * Me + m) * Dh;
-        float part = 0.f;
-        for (int d = lane; d < Dh; d += 32) part += vhat[h * Dh + d] * El<T>::ld(row + d);
-        tot += El<T>::rnd(warp_sum(part));
-      }
-      if (lane == 0) sc[m] = (m >= Ae || !al[W + m]) ? -1e9f : El<T>::rnd(tot / (float)Hkv);
+      const float tot = slot_score<T>(vhat, vnorm, m, Me, Dh, Hkv, lane);
+      if (lane == 0) sc[m] = (m >= Ae || !s_used[m]) ? -1e9f : El<T>::rnd(tot / (float)Hkv);
     }
     __syncthreads();
     if (tid == 0) {
@@ -137,10 +221,10 @@ __global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
       for (int m = 1; m < Me; ++m) if (sc[m] > best) { best = sc[m]; bi = m; }
       bool any_used = false; int free_i = -1; int lru_i = 0; long long lru_v = 0x7fffffffffffffffLL;
       for (int m = 0; m < Me; ++m) {
-        const bool used = al[W + m] != 0, act = m < Ae;
+        const bool used = s_used[m] != 0, act = m < Ae;
         if (act && used) any_used = true;
         if (act && !used && free_i < 0) free_i = m;
-        const long long key = (used && act) ? last[m] : (1LL << 62);
+        const long long key = (used && act) ? s_last[m] : (1LL << 62);
         if (key < lru_v) { lru_v = key; lru_i = m; }
       }
       const bool novel = !any_used || best < El<T>::rnd(c.tau_novel);
@@ -181,22 +265,16 @@ __global__ void __launch_bounds__(256) step_write_kernel(StepParams p) {
   // ================= summary bank (memory_banks.py:343-432) =================
   if (Ms > 0) {
     const int As = c.active_summary;
-    const T* knorm = (const T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
+    const T* knorm = p.stage ? cacheK : (const T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
     for (int m = warp; m < Ms; m += NW) {
-      float tot = 0.f;
-      for (int h = 0; h < Hkv; ++h) {
-        const T* row = knorm + ((long long)h * Ms + m) * lfd;
-        float part = 0.f;
-        for (int d = lane; d < lfd; d += 32) part += khat[h * lfd + d] * El<T>::ld(row + d);
-        tot += El<T>::rnd(warp_sum(part));
-      }
+      const float tot = slot_score<T>(khat, knorm, m, Ms, lfd, Hkv, lane);
       if (lane == 0) sc[m] = (m >= As) ? -1e9f : El<T>::rnd(tot / (float)Hkv);
     }
     __syncthreads();
     if (tid == 0) {
       float best = sc[0]; int bi = 0;
       for (int m = 1; m < Ms; ++m) if (sc[m] > best) { best = sc[m]; bi = m; }
-      const bool is_new = al[W + Me + bi] == 0;
+      const bool is_new = s_used[Me + bi] == 0;
       const bool keep = c.gated ? (g_e >= c.tau_gate_summary) : true;
       s_idx = bi; s_flag = (c.overwrite_on_insert && is_new) ? 1 : 0;
       s_eta_keep = keep ? 1.f : 0.f;
@@ -260,15 +338,26 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
   p.raw = raw; p.inv_freq = inv_freq; p.gate_logit = gate_logit; p.gate_bs = gate_bs;
   const int HD = cfg->Hkv * cfg->Dh, lfd = cfg->Dh - cfg->Dh / 2;
   const int mx = cfg->Me > cfg->Ms ? cfg->Me : cfg->Ms;
-  const size_t smem = sizeof(float) * (size_t)(3 * HD + cfg->Hkv * lfd + mx + 1 + cfg->Dh);
-  CODA_REQUIRE(smem <= 200 * 1024, CODA_ERR_LIMIT, "step_write: Hkv*Dh = %d too large for one CTA", HD);
+  size_t smem = sizeof(float) * (size_t)(3 * HD + cfg->Hkv * lfd + mx + 1 + cfg->Dh + 2) +
+                8 * (size_t)cfg->Me + (size_t)(cfg->Me + cfg->Ms) + 16;
+  const size_t es = cfg->dtype == CODA_F32 ? 4 : 2;
+  const size_t vbytes = (size_t)cfg->Hkv * cfg->Me * cfg->Dh * es, kbytes = (size_t)cfg->Hkv * cfg->Ms * lfd * es;
+  p.stage = 0; p.stage_off = 0; p.status = nullptr;
+  if (vbytes % 16 == 0 && kbytes % 16 == 0 && vbytes + kbytes > 0 && vbytes + kbytes < (1u << 20) &&
+      (cfg->Me == 0 || (uintptr_t)st->exact_v_norm % 16 == 0) && (cfg->Ms == 0 || (uintptr_t)st->sum_lf_k_norm % 16 == 0) &&
+      ((smem + 127) / 128 * 128) + vbytes + kbytes <= 226 * 1024) {
+    p.stage = 1;
+    p.stage_off = (int)((smem + 127) / 128 * 128);
+    smem = (size_t)p.stage_off + vbytes + kbytes;
+  }
+  CODA_REQUIRE(smem <= 226 * 1024, CODA_ERR_LIMIT, "step_write: Hkv*Dh = %d too large for one CTA", HD);
   cudaStream_t s = (cudaStream_t)stream;
   if (cfg->dtype == CODA_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(step_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    step_write_kernel<float><<<cfg->B, 256, smem, s>>>(p);
+    step_write_kernel<float><<<cfg->B, 512, smem, s>>>(p);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(step_write_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    step_write_kernel<bf16><<<cfg->B, 256, smem, s>>>(p);
+    step_write_kernel<bf16><<<cfg->B, 512, smem, s>>>(p);
   }
   CODA_CHECK_LAUNCH("step_write");
   return CODA_OK;

@@ -237,7 +237,10 @@ def test_graph_replay_equals_eager_steps():
     for t in range(16, 56):
         outs_a.append(stack.step_graph(x[:, t:t + 1], sa).clone())
         outs_b.append(stack.step(x[:, t:t + 1], sb))
+    # Library GEMMs may pick another algorithm under capture, so floats are compared with the bf16 tolerance
+    # and only the integer state exactly.
     for a, b in zip(sa, sb):
         assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
-        assert torch.equal(a.k_buf, b.k_buf) and torch.equal(a.allowed, b.allowed) and torch.equal(a.mem_last_exact, b.mem_last_exact)
-    assert torch.equal(torch.cat(outs_a, 1), torch.cat(outs_b, 1))
+        assert torch.equal(a.allowed, b.allowed) and torch.equal(a.mem_last_exact, b.mem_last_exact)
+        assert rel_err(a.k_buf, b.k_buf) < TOL_BF16 and rel_err(a.v_buf, b.v_buf) < TOL_BF16
+    assert rel_err(torch.cat(outs_a, 1), torch.cat(outs_b, 1)) < TOL_BF16
