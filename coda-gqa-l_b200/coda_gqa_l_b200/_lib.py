@@ -51,6 +51,9 @@ def _load() -> C.CDLL:
     lib.coda_b200_step_write_raw.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp, fp, vp]
     lib.coda_b200_decode_attend_supported.argtypes = [cfgp]
     lib.coda_b200_decode_attend.argtypes = [cfgp, stp, RingPos, i32, vp, i64, vp, i64, fp, vp, vp, vp, vp, i64, vp, vp]
+    lib.coda_b200_prefill_attend_supported.argtypes = [cfgp]
+    lib.coda_b200_prefill_attend.argtypes = [cfgp, stp, i32, i32, i32, vp, i64, i64, vp, i64, i64, fp, i64, i64,
+                                             vp, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp, vp]
     lib.coda_b200_attend.argtypes = [cfgp, stp, i32, vp, i64, i64, vp, i64, i64, fp, i64, i64,
                                      vp, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp]
     lib.coda_b200_select_candidates.argtypes = [cfgp, fp, i64, i32, i32, i32, vp, i32, vp]
@@ -71,6 +74,7 @@ def _load() -> C.CDLL:
 EXPORTS = (
     "coda_b200_last_error", "coda_b200_version", "coda_b200_prep", "coda_b200_step_write",
     "coda_b200_step_write_raw", "coda_b200_decode_attend_supported", "coda_b200_decode_attend",
+    "coda_b200_prefill_attend_supported", "coda_b200_prefill_attend",
     "coda_b200_attend", "coda_b200_select_candidates", "coda_b200_route_scratch_bytes",
     "coda_b200_route_block", "coda_b200_advance_steps", "coda_b200_host_topk_f32",
     "coda_b200_host_topk_i64",

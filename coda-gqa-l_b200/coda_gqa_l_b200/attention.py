@@ -382,6 +382,32 @@ class CoDAGQALandmarkPerf2(nn.Module):
         st.recent_idx = (st.recent_idx + (n - fill)) % W
         st.pos += n
 
+    def _tuned_prefill(self, cfg) -> bool:
+        ok = getattr(cfg, "_tuned_prefill", None)
+        if ok is None:
+            ok = bool(lib.coda_b200_prefill_attend_supported(C.byref(cfg)))
+            cfg._tuned_prefill = ok
+        return ok and self.use_tuned_kernels
+
+    def _attend_block_tc(self, cfg, st, L, t0, blk, q, qn, lam, k, v, out):
+        """Tensor-core prefill attention of rows t0..t0+blk of the chunk (whole-chunk tensors are passed)."""
+        _, _, _, _, nw = self._consts(q.device, q.dtype)
+        ptrs = self._ptrs(st)
+        timers = self.kernel_timers
+        if timers is not None:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        check(lib.coda_b200_prefill_attend(
+            C.byref(cfg), C.byref(ptrs), L, t0, blk,
+            q.data_ptr(), q.stride(0), q.stride(1), qn.data_ptr(), qn.stride(0), qn.stride(1),
+            lam.data_ptr(), lam.stride(0), lam.stride(1),
+            k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0), v.stride(1),
+            _p(nw), out.data_ptr(), out.stride(0), out.stride(1),
+            self._status_word(q.device).data_ptr(), _stream()), "coda_b200_prefill_attend")
+        if timers is not None:
+            ev1.record()
+            timers.append((blk, ev0, ev1))
+
     def _tuned_decode(self, cfg) -> bool:
         ok = getattr(cfg, "_tuned_decode", None)
         if ok is None:
@@ -552,12 +578,16 @@ class CoDAGQALandmarkPerf2(nn.Module):
             _, _, _, eta, _ = self._consts(dev, dt)
             ptrs = self._ptrs(state)
         y_heads = torch.empty((B, L, H * Dh), device=dev, dtype=dt) if return_outputs else None
+        tc_ok = (return_outputs and self._tuned_prefill(cfg) and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
+                 and v.data_ptr() % 16 == 0 and all(t.stride(i) % 8 == 0 for t in (q, k, v) for i in (0, 1)))
 
         for j in range(nblk):
             t0 = j * block
             blk = min(block, L - t0)
             kb, vb = k[:, t0:t0 + blk], v[:, t0:t0 + blk]
-            if return_outputs:
+            if return_outputs and tc_ok:
+                self._attend_block_tc(cfg, state, L, t0, blk, q, qn, lam, k, v, y_heads)
+            elif return_outputs:
                 self._attend(cfg, state, blk, q[:, t0:t0 + blk], qn[:, t0:t0 + blk], lam[:, t0:t0 + blk],
                              kb, vb, y_heads[:, t0:t0 + blk])
             if write_cache:

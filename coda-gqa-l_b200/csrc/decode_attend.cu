@@ -16,10 +16,7 @@
 // of hanging.
 #include "coda_common.cuh"
 #include "tma_utils.cuh"
-#include <cuda.h>
-#include <mutex>
-#include <map>
-#include <tuple>
+#include "tensor_maps.h"
 
 namespace {
 
@@ -316,50 +313,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   }
 }
 
-// ---- host side: tensor maps for the K and V planes ---------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
-  return fn;
-}
-
-// Tensor map over a [planes][Lbuf][Dh] bf16 buffer: box = 64 elements x 64 rows x 1 plane, 128-byte swizzle.
-// Rows past Lbuf inside a box are filled with zeros and never bleed into the next plane.
-bool plane_map(CUtensorMap* out, const void* base, int planes, int Lbuf, int Dh) {
-  static std::mutex mu;
-  static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
-  std::lock_guard<std::mutex> lock(mu);
-  auto key = std::make_tuple(base, planes, Lbuf, Dh);
-  auto it = cache.find(key);
-  if (it != cache.end()) { *out = it->second; return true; }
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)Dh, (cuuint64_t)Lbuf, (cuuint64_t)planes};
-  cuuint64_t strides[2] = {(cuuint64_t)Dh * 2, (cuuint64_t)Lbuf * Dh * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)DA_TILE, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUtensorMap m;
-  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return false;
-  if (cache.size() > 4096) cache.clear();
-  cache[key] = m;
-  *out = m;
-  return true;
-}
-
 template <int DH>
 size_t decode_smem(int Lbuf) {
   const int nst = (Lbuf + DA_TILE - 1) / DA_TILE;
@@ -388,7 +341,7 @@ extern "C" int coda_b200_decode_attend_supported(const coda_layer_cfg* cfg) {
   if (!coda_cfg_ok(cfg)) return 0;
   const int G = cfg->H / cfg->Hkv;
   return cfg->dtype == CODA_BF16 && (cfg->Dh == 64 || cfg->Dh == 128) && G <= 8 &&
-         (size_t)(cfg->W + cfg->Me + cfg->Ms) <= 4096 && encode_fn() != nullptr;
+         (size_t)(cfg->W + cfg->Me + cfg->Ms) <= 4096 && tmaps::available();
 }
 
 extern "C" int coda_b200_decode_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
@@ -407,8 +360,8 @@ extern "C" int coda_b200_decode_attend(const coda_layer_cfg* cfg, const coda_sta
                "decode_attend: k_buf / v_buf must be 16-byte aligned");
   const int Lbuf = cfg->W + cfg->Me + cfg->Ms;
   CUtensorMap km, vm;
-  CODA_REQUIRE(plane_map(&km, st->k_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh) &&
-               plane_map(&vm, st->v_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh), CODA_ERR_LAUNCH,
+  CODA_REQUIRE(tmaps::plane_map(&km, st->k_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh) &&
+               tmaps::plane_map(&vm, st->v_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh), CODA_ERR_LAUNCH,
                "decode_attend: cuTensorMapEncodeTiled failed");
   DecodeParams p;
   p.B = cfg->B; p.H = cfg->H; p.Hkv = cfg->Hkv; p.G = cfg->H / cfg->Hkv; p.Lbuf = Lbuf;

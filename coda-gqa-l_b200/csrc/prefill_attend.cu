@@ -1,0 +1,458 @@
+// Chunked-prefill differential attention on the 5th-generation tensor cores (tcgen05 + TMEM), bf16.
+//
+// One CTA = one (state, query head, 128-row query tile) and BOTH streams: signal Q and theta-rotated noise Q
+// share every K/V tile.  Keys are the layer's Lbuf slots (masked by `allowed`) followed by the block's own
+// tokens (causal).  Per 64-key tile:
+//     S_sig, S_noise = Q . K^T      tcgen05.mma  M=128 N=64  K=Dh     accumulators in TMEM (double-buffered)
+//     P = exp2(S - m)               softmax warps: tcgen05.ld, lazy-rescaled online softmax, bf16 P -> shared
+//     O_sig, O_noise += P . V       tcgen05.mma  M=128 N=Dh  K=64     accumulators in TMEM
+// Warp roles: warp 0 = TMA producer (cp.async.bulk.tensor, 128-byte swizzle, 2-stage K/V ring), warp 1 = MMA
+// issuer and TMEM owner, warps 2-5 = softmax / correction / epilogue (one thread per query row, both streams).
+// The MMA issuer runs one tile ahead (Q.K^T of tile j+1 is in flight while tile j is in softmax).  TMEM map
+// (512 columns): S_sig[2] 0..127, S_noise[2] 128..255, O_sig 256.., O_noise 384.. (Dh columns each).
+// Epilogue: O/l per stream, sig - lambda*noise, optional RMSNorm over Dh, bf16 rows written in the (B, L, H*Dh)
+// layout the output projection reads.  All mbarrier waits are bounded (status word, no hang, TMEM is freed).
+#include "coda_common.cuh"
+#include "tma_utils.cuh"
+#include "tensor_maps.h"
+
+namespace {
+
+constexpr int PF_BM = 128;       // query rows per CTA
+constexpr int PF_BN = 64;        // keys per tile
+constexpr int PF_THREADS = 192;  // 6 warps
+constexpr float PF_RESCALE_GAP = 8.0f;   // log2 units the running max may lag before O is rescaled
+
+struct PrefillParams {
+  int B, H, Hkv, Lbuf, blk, t0, mask_unused, norm_full;
+  float eps, scale_log2;
+  const float* lam; long long lam_bs, lam_rs;
+  const uint8_t* allowed;
+  const bf16* norm_w;
+  bf16* out; long long out_bs, out_rs;
+  int* status;
+};
+
+using tma::smem_u32;
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// ---- tcgen05 wrappers ----
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+               : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (Blackwell).  K-major operands (rows of 64
+// bf16 = 128 bytes, 8-row groups 1024 bytes apart): lbo unused (1), sbo = 1024.  MN-major operands (rows are
+// the K index, 64 MN elements per 128-byte row): lbo = distance between 64-element MN groups, sbo = 1024.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulate, bf16 x bf16, M = 128, N = n, A K-major, B K-major or MN-major.
+__device__ __forceinline__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(PF_BM >> 4) << 24);
+}
+__device__ __forceinline__ void bar_softmax() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int DH>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap qnmap,
+                      const __grid_constant__ CUtensorMap kpmap, const __grid_constant__ CUtensorMap vpmap,
+                      const __grid_constant__ CUtensorMap kbmap, const __grid_constant__ CUtensorMap vbmap,
+                      PrefillParams p) {
+  constexpr int HALVES = DH / 64;                 // 64-element (128-byte) column groups per row
+  constexpr int Q_HALF = PF_BM * 128;             // bytes of one Q half tile
+  constexpr int Q_BYTES = HALVES * Q_HALF;
+  constexpr int KV_HALF = PF_BN * 128;
+  constexpr int KV_BYTES = HALVES * KV_HALF;      // one K (or V) tile
+  constexpr int P_BYTES = PF_BM * 128;            // [128 rows][64 keys] bf16
+  constexpr int KSTEPS_QK = DH / 16;
+  constexpr int KSTEPS_PV = PF_BN / 16;
+  constexpr uint32_t TM_SN = 128, TM_OS = 256, TM_ON = 256 + DH;   // TMEM column offsets (S_sig at 0)
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sQs = smem;
+  unsigned char* sQn = sQs + Q_BYTES;
+  unsigned char* sPs = sQn + Q_BYTES;
+  unsigned char* sPn = sPs + P_BYTES;
+  unsigned char* sK = sPn + P_BYTES;               // [2 stages][KV_BYTES]
+  unsigned char* sV = sK + 2 * KV_BYTES;           // [2 stages][KV_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * KV_BYTES);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* kv_full = bars + 1;       // 2
+  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* s_full = bars + 5;        // 2
+  uint64_t* s_free = bars + 7;        // 2
+  uint64_t* p_full = bars + 9;        // 1
+  uint64_t* pv_done = bars + 10;      // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint32_t* sMask = tmem_slot + 2;    // visibility bits of the prefix slots, 32 per word
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r0 = blockIdx.x * PF_BM, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int NP = (p.Lbuf + PF_BN - 1) / PF_BN;                                   // prefix tiles
+  const int last_row = min(r0 + PF_BM, p.blk) - 1;
+  const int NB = last_row / PF_BN + 1;                                            // block tiles (causal limit)
+  const int NT = NP + NB;
+
+  if (tid == 0) {
+    tma::mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      tma::mbar_init(&kv_full[i], 1); tma::mbar_init(&kv_empty[i], 1);
+      tma::mbar_init(&s_full[i], 1); tma::mbar_init(&s_free[i], 4);
+    }
+    tma::mbar_init(p_full, 4);
+    tma::mbar_init(pv_done, 1);
+    tma::fence_barrier_init();
+  }
+  if (warp == 1) {                                   // TMEM: all 512 columns, owned by warp 1
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      tma::mbar_expect_tx(q_full, 2 * Q_BYTES);
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf) {
+        tma_load_4d(sQs + hf * Q_HALF, &qmap, q_full, hf * 64, h, p.t0 + r0, b);
+        tma_load_4d(sQn + hf * Q_HALF, &qnmap, q_full, hf * 64, h, p.t0 + r0, b);
+      }
+      for (int j = 0; j < NT; ++j) {
+        const int st = j & 1;
+        if (j >= 2) tma::mbar_wait(&kv_empty[st], ((j >> 1) - 1) & 1, p.status, 11);
+        tma::mbar_expect_tx(&kv_full[st], 2 * KV_BYTES);
+        unsigned char* kd = sK + st * KV_BYTES;
+        unsigned char* vd = sV + st * KV_BYTES;
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) {
+          if (j < NP) {
+            tma_load_3d(kd + hf * KV_HALF, &kpmap, &kv_full[st], hf * 64, j * PF_BN, b * p.Hkv + hk);
+            tma_load_3d(vd + hf * KV_HALF, &vpmap, &kv_full[st], hf * 64, j * PF_BN, b * p.Hkv + hk);
+          } else {
+            tma_load_4d(kd + hf * KV_HALF, &kbmap, &kv_full[st], hf * 64, hk, p.t0 + (j - NP) * PF_BN, b);
+            tma_load_4d(vd + hf * KV_HALF, &vbmap, &kv_full[st], hf * 64, hk, p.t0 + (j - NP) * PF_BN, b);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = instr_desc(PF_BN, false);
+      constexpr uint32_t IDESC_PV = instr_desc(DH, true);
+      auto issue_pv = [&](int i) {
+        const int st = i & 1;
+        tma::mbar_wait(p_full, i & 1, p.status, 12);
+        tc_fence_after();
+        const uint32_t vbase = smem_u32(sV + st * KV_BYTES);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          const uint32_t pbase = smem_u32(s ? sPn : sPs);
+          const uint32_t dcol = tmem + (s ? TM_ON : TM_OS);
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS_PV; ++kk) {
+            const uint64_t ad = smem_desc(pbase + kk * 32, 16, 1024);
+            const uint64_t bd = smem_desc(vbase + kk * 2048, KV_HALF, 1024);
+            tc_mma(dcol, ad, bd, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        tc_commit(pv_done);
+        tc_commit(&kv_empty[st]);
+      };
+      tma::mbar_wait(q_full, 0, p.status, 13);
+      for (int j = 0; j < NT; ++j) {
+        const int sb = j & 1;
+        tma::mbar_wait(&kv_full[sb], (j >> 1) & 1, p.status, 14);
+        if (j >= 2) tma::mbar_wait(&s_free[sb], ((j >> 1) - 1) & 1, p.status, 15);
+        tc_fence_after();
+        const uint32_t kbase = smem_u32(sK + sb * KV_BYTES);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          const uint32_t qbase = smem_u32(s ? sQn : sQs);
+          const uint32_t dcol = tmem + (s ? TM_SN : 0u) + sb * PF_BN;
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS_QK; ++kk) {
+            const uint64_t ad = smem_desc(qbase + (kk >> 2) * Q_HALF + (kk & 3) * 32, 16, 1024);
+            const uint64_t bd = smem_desc(kbase + (kk >> 2) * KV_HALF + (kk & 3) * 32, 16, 1024);
+            tc_mma(dcol, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+          }
+        }
+        tc_commit(&s_full[sb]);
+        if (j >= 1) issue_pv(j - 1);
+      }
+      issue_pv(NT - 1);
+    }
+  } else {
+    // =========================== softmax / correction / epilogue ===========================
+    const int sw = warp - 2;                              // 0..3
+    const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;                  // row of the query tile
+    const int grow = r0 + row;                            // row inside the block
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    // visibility bits of the prefix slots
+    for (int w32 = sw; w32 < NP * 2; w32 += 4) {
+      const int c = w32 * 32 + lane;
+      const bool vis = c < p.Lbuf && (!p.mask_unused || p.allowed[(long long)b * p.Lbuf + c] != 0);
+      const unsigned bits = __ballot_sync(0xffffffffu, vis);
+      if (lane == 0) sMask[w32] = bits;
+    }
+    bar_softmax();
+
+    float mb[2] = {-INFINITY, -INFINITY};                 // exponent base per stream (lags the true max by < GAP)
+    float l[2] = {0.f, 0.f};
+    for (int j = 0; j < NT; ++j) {
+      const int sb = j & 1;
+      tma::mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, 16);
+      tc_fence_after();
+      uint32_t vis_lo, vis_hi;
+      if (j < NP) { vis_lo = sMask[2 * j]; vis_hi = sMask[2 * j + 1]; }
+      else {
+        const int c0 = (j - NP) * PF_BN;                  // key c0+i visible iff c0+i <= grow
+        const int nvis = grow - c0 + 1;
+        vis_lo = nvis >= 32 ? 0xffffffffu : (nvis <= 0 ? 0u : ((1u << nvis) - 1u));
+        vis_hi = nvis >= 64 ? 0xffffffffu : (nvis <= 32 ? 0u : ((1u << (nvis - 32)) - 1u));
+      }
+      float alpha[2] = {1.f, 1.f};
+      uint32_t pk[2][32];                                 // packed bf16 probabilities, both streams
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        uint32_t v0[32], v1[32];
+        const uint32_t scol = lane_addr + (s ? TM_SN : 0u) + sb * PF_BN;
+        tc_ld32(scol, v0);
+        tc_ld32(scol + 32, v1);
+        tc_wait_ld();
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float a = ((vis_lo >> i) & 1u) ? __uint_as_float(v0[i]) * p.scale_log2 : -INFINITY;
+          const float c = ((vis_hi >> i) & 1u) ? __uint_as_float(v1[i]) * p.scale_log2 : -INFINITY;
+          v0[i] = __float_as_uint(a); v1[i] = __float_as_uint(c);
+          mx = fmaxf(mx, fmaxf(a, c));
+        }
+        if (mx > mb[s] + PF_RESCALE_GAP || (mb[s] == -INFINITY && mx > -INFINITY)) {
+          alpha[s] = (mb[s] == -INFINITY) ? 0.f : exp2f(mb[s] - mx);
+          mb[s] = mx;
+          l[s] *= alpha[s];
+        }
+        const float ref = mb[s] == -INFINITY ? 0.f : mb[s];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float a0 = exp2f(__uint_as_float(v0[2 * i]) - ref), a1 = exp2f(__uint_as_float(v0[2 * i + 1]) - ref);
+          const float c0 = exp2f(__uint_as_float(v1[2 * i]) - ref), c1 = exp2f(__uint_as_float(v1[2 * i + 1]) - ref);
+          sum += (a0 + a1) + (c0 + c1);
+          pk[s][i] = pack2(a0, a1);
+          pk[s][16 + i] = pack2(c0, c1);
+        }
+        l[s] += sum;
+      }
+      // S has been read: the MMA warp may overwrite this S buffer (tile j+2)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tma::mbar_arrive(&s_free[sb]);
+      // P buffer and O are quiescent once P.V of the previous tile has completed
+      if (j >= 1) { tma::mbar_wait(pv_done, (j - 1) & 1, p.status, 17); tc_fence_after(); }
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        // rescale O when some row of this warp moved its exponent base (skipped for the first tile: O is
+        // overwritten, not accumulated, by the first P.V)
+        const bool need = (alpha[s] != 1.f) && j > 0;
+        if (__any_sync(0xffffffffu, need)) {
+          const uint32_t ocol = lane_addr + (s ? TM_ON : TM_OS);
+#pragma unroll
+          for (int c = 0; c < DH / 32; ++c) {
+            uint32_t o[32];
+            tc_ld32(ocol + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha[s]);
+            tc_st32(ocol + c * 32, o);
+          }
+          tc_wait_st();
+        }
+        // P row -> shared, K-major 128-byte-swizzled tile ([row][64 keys])
+        unsigned char* prow = (s ? sPn : sPs) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 val = make_uint4(pk[s][4 * c], pk[s][4 * c + 1], pk[s][4 * c + 2], pk[s][4 * c + 3]);
+          *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = val;
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tma::mbar_arrive(p_full);
+    }
+
+    // ---- epilogue ----
+    tma::mbar_wait(pv_done, (NT - 1) & 1, p.status, 18);
+    tc_fence_after();
+    const bool valid = grow < p.blk;
+    const float inv_s = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_n = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    float lam = 0.f;
+    if (valid) lam = bf16_round(p.lam[(long long)b * p.lam_bs + (long long)(p.t0 + grow) * p.lam_rs + h]);
+    uint32_t dpk[DH / 2];                                  // packed bf16 differences of the row
+    float sq = 0.f;
+#pragma unroll
+    for (int c = 0; c < DH / 32; ++c) {
+      uint32_t os[32], on[32];
+      tc_ld32(lane_addr + TM_OS + c * 32, os);
+      tc_ld32(lane_addr + TM_ON + c * 32, on);
+      tc_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float d[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float vs = bf16_round(__uint_as_float(os[2 * i + e]) * inv_s);
+          const float vn = bf16_round(__uint_as_float(on[2 * i + e]) * inv_n);
+          d[e] = t_sub<bf16>(vs, t_mul<bf16>(lam, vn));
+          sq += bf16_round(d[e] * d[e]);
+        }
+        dpk[c * 16 + i] = pack2(d[0], d[1]);
+      }
+    }
+    if (valid) {
+      bf16* op = p.out + (long long)b * p.out_bs + (long long)(p.t0 + grow) * p.out_rs + (long long)h * DH;
+      if (p.norm_full) {
+        const float var = bf16_round(sq / (float)DH);
+        const float rs = bf16_round(rsqrtf(bf16_round(var + p.eps)));
+#pragma unroll
+        for (int i = 0; i < DH / 2; ++i) {
+          const __nv_bfloat162 dv = *reinterpret_cast<__nv_bfloat162*>(&dpk[i]);
+          const __nv_bfloat162 wv = reinterpret_cast<const __nv_bfloat162*>(p.norm_w)[i];
+          const float y0 = t_mul<bf16>(t_mul<bf16>(__low2float(dv), rs), __low2float(wv));
+          const float y1 = t_mul<bf16>(t_mul<bf16>(__high2float(dv), rs), __high2float(wv));
+          dpk[i] = pack2(y0, y1);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < DH / 8; ++i)
+        reinterpret_cast<uint4*>(op)[i] = make_uint4(dpk[4 * i], dpk[4 * i + 1], dpk[4 * i + 2], dpk[4 * i + 3]);
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  }
+}
+
+template <int DH>
+size_t prefill_smem(int Lbuf) {
+  const int NP = (Lbuf + PF_BN - 1) / PF_BN;
+  return (size_t)2 * (DH / 64) * PF_BM * 128 + 2 * PF_BM * 128 + 4 * (size_t)(DH / 64) * PF_BN * 128 + 11 * 8 + 8 +
+         (size_t)NP * 2 * 4 + 1024 + 64;
+}
+
+template <int DH>
+int launch_prefill(const CUtensorMap* maps, const PrefillParams& p, cudaStream_t s) {
+  const size_t smem = prefill_smem<DH>(p.Lbuf);
+  CODA_REQUIRE(smem <= 226 * 1024, CODA_ERR_LIMIT, "prefill_attend: %d slots need %zu bytes of shared memory", p.Lbuf, smem);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(prefill_attend_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    configured = true;
+  }
+  dim3 grid((p.blk + PF_BM - 1) / PF_BM, p.H, p.B);
+  prefill_attend_kernel<DH><<<grid, PF_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  CODA_CHECK_LAUNCH("prefill_attend");
+  return CODA_OK;
+}
+
+}  // namespace
+
+extern "C" int coda_b200_prefill_attend_supported(const coda_layer_cfg* cfg) {
+  if (!coda_cfg_ok(cfg)) return 0;
+  return cfg->dtype == CODA_BF16 && (cfg->Dh == 64 || cfg->Dh == 128) && tmaps::available();
+}
+
+extern "C" int coda_b200_prefill_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                                        int32_t L, int32_t t0, int32_t blk,
+                                        const void* q, int64_t q_bs, int64_t q_rs,
+                                        const void* q_noise, int64_t qn_bs, int64_t qn_rs,
+                                        const float* lam, int64_t lam_bs, int64_t lam_rs,
+                                        const void* k_seq, int64_t k_bs, int64_t k_rs,
+                                        const void* v_seq, int64_t v_bs, int64_t v_rs,
+                                        const void* norm_w, void* out, int64_t out_bs, int64_t out_rs,
+                                        int32_t* status, coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "prefill_attend: invalid layer configuration");
+  CODA_REQUIRE(coda_b200_prefill_attend_supported(cfg), CODA_ERR_ARG, "prefill_attend: needs bf16 and head_dim 64 or 128");
+  CODA_REQUIRE(L > 0 && blk > 0 && t0 >= 0 && t0 + blk <= L, CODA_ERR_ARG, "prefill_attend: block [%d, %d) outside the %d tokens", t0, t0 + blk, L);
+  CODA_REQUIRE(q && q_noise && lam && k_seq && v_seq && out && st->k_buf && st->v_buf && st->allowed, CODA_ERR_ARG,
+               "prefill_attend: null pointer");
+  CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "prefill_attend: head-norm weight missing");
+  const uintptr_t al = (uintptr_t)q | (uintptr_t)q_noise | (uintptr_t)k_seq | (uintptr_t)v_seq | (uintptr_t)out |
+                       (uintptr_t)st->k_buf | (uintptr_t)st->v_buf;
+  CODA_REQUIRE(al % 16 == 0 && (q_bs | q_rs | qn_bs | qn_rs | k_bs | k_rs | v_bs | v_rs | out_bs | out_rs) % 8 == 0, CODA_ERR_ARG,
+               "prefill_attend: pointers must be 16-byte aligned and strides multiples of 8 elements");
+  const int Lbuf = cfg->W + cfg->Me + cfg->Ms, Dh = cfg->Dh;
+  CUtensorMap maps[6];
+  const bool ok = tmaps::token_map(&maps[0], q, cfg->B, L, cfg->H, Dh, q_bs, q_rs, PF_BM) &&
+                  tmaps::token_map(&maps[1], q_noise, cfg->B, L, cfg->H, Dh, qn_bs, qn_rs, PF_BM) &&
+                  tmaps::plane_map(&maps[2], st->k_buf, cfg->B * cfg->Hkv, Lbuf, Dh, PF_BN) &&
+                  tmaps::plane_map(&maps[3], st->v_buf, cfg->B * cfg->Hkv, Lbuf, Dh, PF_BN) &&
+                  tmaps::token_map(&maps[4], k_seq, cfg->B, L, cfg->Hkv, Dh, k_bs, k_rs, PF_BN) &&
+                  tmaps::token_map(&maps[5], v_seq, cfg->B, L, cfg->Hkv, Dh, v_bs, v_rs, PF_BN);
+  CODA_REQUIRE(ok, CODA_ERR_LAUNCH, "prefill_attend: cuTensorMapEncodeTiled failed");
+  PrefillParams p;
+  p.B = cfg->B; p.H = cfg->H; p.Hkv = cfg->Hkv; p.Lbuf = Lbuf; p.blk = blk; p.t0 = t0;
+  p.mask_unused = cfg->mask_unused; p.norm_full = cfg->head_norm_full; p.eps = cfg->eps;
+  p.scale_log2 = 1.4426950408889634f / sqrtf((float)Dh);
+  p.lam = lam; p.lam_bs = lam_bs; p.lam_rs = lam_rs; p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w;
+  p.out = (bf16*)out; p.out_bs = out_bs; p.out_rs = out_rs; p.status = status;
+  cudaStream_t s = (cudaStream_t)stream;
+  return Dh == 128 ? launch_prefill<128>(maps, p, s) : launch_prefill<64>(maps, p, s);
+}

@@ -157,6 +157,24 @@ int coda_b200_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, int32
                      void* out, int64_t out_bs, int64_t out_rs,
                      coda_stream_t stream);
 
+/* Tensor-core prefill attention (bf16, head_dim 64/128): same result as coda_b200_attend for one block of `blk`
+ * query rows starting at token t0 of an L-token chunk, computed with tcgen05.mma (accumulators in TMEM) on
+ * TMA-staged tiles; both streams of a query head share every K/V tile.  Replaces the prefix+block attention of
+ * prefill_chunked (src/coda_gqa_l/attention.py:612-701, _sdpa_stacked_two_stream :416-465, mask :553-565) and
+ * upstream's triton_diff_flash kernel.  q, q_noise [B][L][H][Dh], k_seq, v_seq [B][L][Hkv][Dh] are the WHOLE
+ * chunk's tensors (bf16, 16-byte aligned, strides multiples of 8 elements); lam fp32 [B][L][H]; out [B][L][H*Dh]
+ * (rows t0 .. t0+blk-1 are written).  status: optional device int set when a bounded wait expires. */
+int coda_b200_prefill_attend_supported(const coda_layer_cfg* cfg);
+int coda_b200_prefill_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                             int32_t L, int32_t t0, int32_t blk,
+                             const void* q, int64_t q_bs, int64_t q_rs,
+                             const void* q_noise, int64_t qn_bs, int64_t qn_rs,
+                             const float* lam, int64_t lam_bs, int64_t lam_rs,
+                             const void* k_seq, int64_t k_bs, int64_t k_rs,
+                             const void* v_seq, int64_t v_bs, int64_t v_rs,
+                             const void* norm_w, void* out, int64_t out_bs, int64_t out_rs,
+                             int32_t* status, coda_stream_t stream);
+
 /* Candidate selection for every block of one prefill call: for block j the tokens that leave
  * the ring are a contiguous run of the token stream; their fp32 gates are ranked exactly like
  * the host top-k upstream uses (memory_banks.py:486-552, torch.topk largest, unsorted), tie

@@ -244,3 +244,38 @@ def test_graph_replay_equals_eager_steps():
         assert torch.equal(a.allowed, b.allowed) and torch.equal(a.mem_last_exact, b.mem_last_exact)
         assert rel_err(a.k_buf, b.k_buf) < TOL_BF16 and rel_err(a.v_buf, b.v_buf) < TOL_BF16
     assert rel_err(torch.cat(outs_a, 1), torch.cat(outs_b, 1)) < TOL_BF16
+
+
+@pytest.mark.parametrize("shape,block,L", [
+    (dict(embed_dim=512, num_heads=4, num_kv_heads=1, window=100, num_landmarks_exact=20, num_landmarks_summary=12), 128, 384),
+    (dict(embed_dim=512, num_heads=8, num_kv_heads=2, window=256, num_landmarks_exact=64, num_landmarks_summary=64), 256, 768),
+    (dict(embed_dim=384, num_heads=3, num_kv_heads=3, window=40, num_landmarks_exact=8, num_landmarks_summary=8,
+          head_norm_mode="identity", rope_interleaved=False, rope_base=1e6), 100, 250),
+    (dict(embed_dim=576, num_heads=9, num_kv_heads=3, window=128, num_landmarks_exact=32, num_landmarks_summary=32,
+          head_norm_mode="identity", rope_interleaved=False), 128, 300),
+    (dict(embed_dim=256, num_heads=2, num_kv_heads=1, window=64, num_landmarks_exact=16, num_landmarks_summary=16), 48, 200),
+])
+def test_tensor_core_prefill_matches_generic_kernel(shape, block, L):
+    """The tcgen05 prefill attention against the shape-generic kernel on identical inputs and states (bf16):
+    ragged last blocks, several query tiles per block, slot counts that are not multiples of the key tile,
+    partly masked banks."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, _deep_copy_state
+    from tests.scenarios import randomize_weights
+    torch.manual_seed(3)
+    mod = CoDAGQALandmarkPerf2(**shape).eval()
+    randomize_weights(mod, 3)
+    mod = mod.to(torch.bfloat16).cuda()
+    D, B = shape["embed_dim"], 2
+    x = orc.mixture_inputs(B, L, D, centroids=16, sigma=0.3, seed=5, dtype=torch.bfloat16).cuda()
+    torch.manual_seed(4)
+    sa = mod.init_state(batch_size=B, device="cuda", dtype=torch.bfloat16)
+    sb = _deep_copy_state(sa)
+    mod.use_tuned_kernels = True
+    ya, sa = mod.prefill_chunked(x, sa, block_size=block)
+    assert mod.device_status() == 0
+    mod.use_tuned_kernels = False
+    yb, sb = mod.prefill_chunked(x, sb, block_size=block)
+    assert torch.equal(sa.k_buf, sb.k_buf) and torch.equal(sa.allowed, sb.allowed)
+    assert torch.isfinite(ya).all()
+    e = rel_err(ya, yb)
+    assert e < 8e-3, f"tensor-core vs generic prefill attention: rel err {e:.3e}"
