@@ -37,6 +37,48 @@ template <typename T> __device__ __forceinline__ float t_sigmoid(float z) {
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// ---- batched loads ---------------------------------------------------------------------------
+// CNT consecutive elements starting at p, converted to fp32.  All loads are issued before any use (one
+// memory round trip instead of CNT dependent ones); 16-byte vectors when the run is aligned.
+template <typename T, int CNT>
+__device__ __forceinline__ void load_run(const T* __restrict__ p, float (&out)[CNT]) {
+  constexpr int BYTES = CNT * (int)sizeof(T);
+  if constexpr (BYTES % 16 == 0) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+      uint4 v[BYTES / 16];
+#pragma unroll
+      for (int i = 0; i < BYTES / 16; ++i) v[i] = reinterpret_cast<const uint4*>(p)[i];
+#pragma unroll
+      for (int i = 0; i < BYTES / 16; ++i) {
+        const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+        if (sizeof(T) == 2) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            out[i * 8 + 2 * j] = __uint_as_float(w[j] << 16);
+            out[i * 8 + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) out[i * 4 + j] = __uint_as_float(w[j]);
+        }
+      }
+      return;
+    }
+  } else if constexpr (BYTES == 8 && sizeof(T) == 2) {
+    if ((reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+      const uint2 v = *reinterpret_cast<const uint2*>(p);
+      out[0] = __uint_as_float(v.x << 16); out[1] = __uint_as_float(v.x & 0xffff0000u);
+      out[2] = __uint_as_float(v.y << 16); out[3] = __uint_as_float(v.y & 0xffff0000u);
+      return;
+    }
+  }
+  T raw[CNT];
+#pragma unroll
+  for (int i = 0; i < CNT; ++i) raw[i] = p[i];
+#pragma unroll
+  for (int i = 0; i < CNT; ++i) out[i] = El<T>::ld(&raw[i]);
+}
+
 // ---- warp helpers ---------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -7,8 +7,10 @@
 //     P = exp2(S - m)               softmax warps: tcgen05.ld, lazy-rescaled online softmax, bf16 P -> shared
 //     O_sig, O_noise += P . V       tcgen05.mma  M=128 N=Dh  K=64     accumulators in TMEM
 // Warp roles: warp 0 = TMA producer (cp.async.bulk.tensor, 128-byte swizzle, 2-stage K/V ring), warp 1 = MMA
-// issuer and TMEM owner, warps 2-5 = softmax / correction / epilogue (one thread per query row, both streams).
-// The MMA issuer runs one tile ahead (Q.K^T of tile j+1 is in flight while tile j is in softmax).  TMEM map
+// issuer and TMEM owner, warps 2-5 = softmax / correction / epilogue of the signal stream, warps 6-9 = the same
+// for the noise stream (one thread per query row).  The two streams are independent pipelines through the tensor
+// core (own S buffers, P tile and barriers), so one stream's softmax overlaps the other's MMAs, and the MMA
+// issuer runs one tile ahead (Q.K^T of tile j+1 is in flight while tile j is in softmax).  TMEM map
 // (512 columns): S_sig[2] 0..127, S_noise[2] 128..255, O_sig 256.., O_noise 384.. (Dh columns each).
 // Epilogue: O/l per stream, sig - lambda*noise, optional RMSNorm over Dh, bf16 rows written in the (B, L, H*Dh)
 // layout the output projection reads.  All mbarrier waits are bounded (status word, no hang, TMEM is freed).
@@ -20,7 +22,7 @@ namespace {
 
 constexpr int PF_BM = 128;       // query rows per CTA
 constexpr int PF_BN = 64;        // keys per tile
-constexpr int PF_THREADS = 192;  // 6 warps
+constexpr int PF_THREADS = 320;  // 10 warps
 constexpr float PF_RESCALE_GAP = 8.0f;   // log2 units the running max may lag before O is rescaled
 
 struct PrefillParams {
@@ -90,7 +92,7 @@ __device__ __forceinline__ constexpr uint32_t instr_desc(int n, bool b_mn_major)
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(PF_BM >> 4) << 24);
 }
-__device__ __forceinline__ void bar_softmax() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void bar_softmax_all() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -124,11 +126,11 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   uint64_t* q_full = bars;            // 1
   uint64_t* kv_full = bars + 1;       // 2
   uint64_t* kv_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;        // 2
-  uint64_t* s_free = bars + 7;        // 2
-  uint64_t* p_full = bars + 9;        // 1
-  uint64_t* pv_done = bars + 10;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* s_full = bars + 5;        // [stream][buffer] 4
+  uint64_t* s_free = bars + 9;        // [stream][buffer] 4
+  uint64_t* p_full = bars + 13;       // [stream] 2
+  uint64_t* pv_done = bars + 15;      // [stream] 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   uint32_t* sMask = tmem_slot + 2;    // visibility bits of the prefix slots, 32 per word
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -141,12 +143,9 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
 
   if (tid == 0) {
     tma::mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      tma::mbar_init(&kv_full[i], 1); tma::mbar_init(&kv_empty[i], 1);
-      tma::mbar_init(&s_full[i], 1); tma::mbar_init(&s_free[i], 4);
-    }
-    tma::mbar_init(p_full, 4);
-    tma::mbar_init(pv_done, 1);
+    for (int i = 0; i < 2; ++i) { tma::mbar_init(&kv_full[i], 1); tma::mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 4; ++i) { tma::mbar_init(&s_full[i], 1); tma::mbar_init(&s_free[i], 4); }
+    for (int i = 0; i < 2; ++i) { tma::mbar_init(&p_full[i], 4); tma::mbar_init(&pv_done[i], 1); }
     tma::fence_barrier_init();
   }
   if (warp == 1) {                                   // TMEM: all 512 columns, owned by warp 1
@@ -192,11 +191,11 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       constexpr uint32_t IDESC_PV = instr_desc(DH, true);
       auto issue_pv = [&](int i) {
         const int st = i & 1;
-        tma::mbar_wait(p_full, i & 1, p.status, 12);
-        tc_fence_after();
         const uint32_t vbase = smem_u32(sV + st * KV_BYTES);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
+          tma::mbar_wait(&p_full[s], i & 1, p.status, 12);
+          tc_fence_after();
           const uint32_t pbase = smem_u32(s ? sPn : sPs);
           const uint32_t dcol = tmem + (s ? TM_ON : TM_OS);
 #pragma unroll
@@ -205,19 +204,19 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const uint64_t bd = smem_desc(vbase + kk * 2048, KV_HALF, 1024);
             tc_mma(dcol, ad, bd, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
           }
+          tc_commit(&pv_done[s]);
         }
-        tc_commit(pv_done);
         tc_commit(&kv_empty[st]);
       };
       tma::mbar_wait(q_full, 0, p.status, 13);
       for (int j = 0; j < NT; ++j) {
         const int sb = j & 1;
         tma::mbar_wait(&kv_full[sb], (j >> 1) & 1, p.status, 14);
-        if (j >= 2) tma::mbar_wait(&s_free[sb], ((j >> 1) - 1) & 1, p.status, 15);
-        tc_fence_after();
         const uint32_t kbase = smem_u32(sK + sb * KV_BYTES);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
+          if (j >= 2) tma::mbar_wait(&s_free[s * 2 + sb], ((j >> 1) - 1) & 1, p.status, 15);
+          tc_fence_after();
           const uint32_t qbase = smem_u32(s ? sQn : sQs);
           const uint32_t dcol = tmem + (s ? TM_SN : 0u) + sb * PF_BN;
 #pragma unroll
@@ -226,33 +225,38 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
             const uint64_t bd = smem_desc(kbase + (kk >> 2) * KV_HALF + (kk & 3) * 32, 16, 1024);
             tc_mma(dcol, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
           }
+          tc_commit(&s_full[s * 2 + sb]);
         }
-        tc_commit(&s_full[sb]);
         if (j >= 1) issue_pv(j - 1);
       }
       issue_pv(NT - 1);
     }
   } else {
-    // =========================== softmax / correction / epilogue ===========================
-    const int sw = warp - 2;                              // 0..3
+    // =========================== softmax / correction / epilogue (one stream per warp group) ===========================
+    const int s = warp >= 6 ? 1 : 0;                      // 0 = signal, 1 = noise
+    const int sw = (warp - 2) & 3;                        // warp index inside its group
     const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;                  // row of the query tile
     const int grow = r0 + row;                            // row inside the block
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    // visibility bits of the prefix slots
-    for (int w32 = sw; w32 < NP * 2; w32 += 4) {
-      const int c = w32 * 32 + lane;
-      const bool vis = c < p.Lbuf && (!p.mask_unused || p.allowed[(long long)b * p.Lbuf + c] != 0);
-      const unsigned bits = __ballot_sync(0xffffffffu, vis);
-      if (lane == 0) sMask[w32] = bits;
+    const uint32_t s_col = lane_addr + (s ? TM_SN : 0u);
+    const uint32_t o_col = lane_addr + (s ? TM_ON : TM_OS);
+    unsigned char* prow = (s ? sPn : sPs) + row * 128;
+    if (s == 0) {                                         // visibility bits of the prefix slots
+      for (int w32 = sw; w32 < NP * 2; w32 += 4) {
+        const int c = w32 * 32 + lane;
+        const bool vis = c < p.Lbuf && (!p.mask_unused || p.allowed[(long long)b * p.Lbuf + c] != 0);
+        const unsigned bits = __ballot_sync(0xffffffffu, vis);
+        if (lane == 0) sMask[w32] = bits;
+      }
     }
-    bar_softmax();
+    bar_softmax_all();
 
-    float mb[2] = {-INFINITY, -INFINITY};                 // exponent base per stream (lags the true max by < GAP)
-    float l[2] = {0.f, 0.f};
+    float mb = -INFINITY;                                 // exponent base (lags the true max by < GAP)
+    float l = 0.f;
     for (int j = 0; j < NT; ++j) {
       const int sb = j & 1;
-      tma::mbar_wait(&s_full[sb], (j >> 1) & 1, p.status, 16);
+      tma::mbar_wait(&s_full[s * 2 + sb], (j >> 1) & 1, p.status, 16);
       tc_fence_after();
       uint32_t vis_lo, vis_hi;
       if (j < NP) { vis_lo = sMask[2 * j]; vis_hi = sMask[2 * j + 1]; }
@@ -262,125 +266,146 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         vis_lo = nvis >= 32 ? 0xffffffffu : (nvis <= 0 ? 0u : ((1u << nvis) - 1u));
         vis_hi = nvis >= 64 ? 0xffffffffu : (nvis <= 32 ? 0u : ((1u << (nvis - 32)) - 1u));
       }
-      float alpha[2] = {1.f, 1.f};
-      uint32_t pk[2][32];                                 // packed bf16 probabilities, both streams
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        uint32_t v0[32], v1[32];
-        const uint32_t scol = lane_addr + (s ? TM_SN : 0u) + sb * PF_BN;
-        tc_ld32(scol, v0);
-        tc_ld32(scol + 32, v1);
-        tc_wait_ld();
-        float mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float a = ((vis_lo >> i) & 1u) ? __uint_as_float(v0[i]) * p.scale_log2 : -INFINITY;
-          const float c = ((vis_hi >> i) & 1u) ? __uint_as_float(v1[i]) * p.scale_log2 : -INFINITY;
-          v0[i] = __float_as_uint(a); v1[i] = __float_as_uint(c);
-          mx = fmaxf(mx, fmaxf(a, c));
-        }
-        if (mx > mb[s] + PF_RESCALE_GAP || (mb[s] == -INFINITY && mx > -INFINITY)) {
-          alpha[s] = (mb[s] == -INFINITY) ? 0.f : exp2f(mb[s] - mx);
-          mb[s] = mx;
-          l[s] *= alpha[s];
-        }
-        const float ref = mb[s] == -INFINITY ? 0.f : mb[s];
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float a0 = exp2f(__uint_as_float(v0[2 * i]) - ref), a1 = exp2f(__uint_as_float(v0[2 * i + 1]) - ref);
-          const float c0 = exp2f(__uint_as_float(v1[2 * i]) - ref), c1 = exp2f(__uint_as_float(v1[2 * i + 1]) - ref);
-          sum += (a0 + a1) + (c0 + c1);
-          pk[s][i] = pack2(a0, a1);
-          pk[s][16 + i] = pack2(c0, c1);
-        }
-        l[s] += sum;
-      }
+      uint32_t v0[32], v1[32];
+      tc_ld32(s_col + sb * PF_BN, v0);
+      tc_ld32(s_col + sb * PF_BN + 32, v1);
+      tc_wait_ld();
       // S has been read: the MMA warp may overwrite this S buffer (tile j+2)
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) tma::mbar_arrive(&s_free[sb]);
-      // P buffer and O are quiescent once P.V of the previous tile has completed
-      if (j >= 1) { tma::mbar_wait(pv_done, (j - 1) & 1, p.status, 17); tc_fence_after(); }
+      if (lane == 0) tma::mbar_arrive(&s_free[s * 2 + sb]);
+      float mx = -INFINITY;
+      if ((vis_lo & vis_hi) == 0xffffffffu) {
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        // rescale O when some row of this warp moved its exponent base (skipped for the first tile: O is
-        // overwritten, not accumulated, by the first P.V)
-        const bool need = (alpha[s] != 1.f) && j > 0;
-        if (__any_sync(0xffffffffu, need)) {
-          const uint32_t ocol = lane_addr + (s ? TM_ON : TM_OS);
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+      } else {
 #pragma unroll
-          for (int c = 0; c < DH / 32; ++c) {
-            uint32_t o[32];
-            tc_ld32(ocol + c * 32, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha[s]);
-            tc_st32(ocol + c * 32, o);
-          }
-          tc_wait_st();
-        }
-        // P row -> shared, K-major 128-byte-swizzled tile ([row][64 keys])
-        unsigned char* prow = (s ? sPn : sPs) + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4 val = make_uint4(pk[s][4 * c], pk[s][4 * c + 1], pk[s][4 * c + 2], pk[s][4 * c + 3]);
-          *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = val;
+        for (int i = 0; i < 32; ++i) {
+          if (!((vis_lo >> i) & 1u)) v0[i] = 0xff800000u;   // -inf
+          if (!((vis_hi >> i) & 1u)) v1[i] = 0xff800000u;
+          mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
         }
       }
+      mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
+      float alpha = 1.f;
+      if (mx > mb + PF_RESCALE_GAP || (mb == -INFINITY && mx > -INFINITY)) {
+        alpha = (mb == -INFINITY) ? 0.f : exp2f(mb - mx);
+        mb = mx;
+        l *= alpha;
+      }
+      const float nref = mb == -INFINITY ? 0.f : -mb;
+      float sum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a0 = exp2f(fmaf(__uint_as_float(v0[2 * i]), p.scale_log2, nref));
+        const float a1 = exp2f(fmaf(__uint_as_float(v0[2 * i + 1]), p.scale_log2, nref));
+        const float c0 = exp2f(fmaf(__uint_as_float(v1[2 * i]), p.scale_log2, nref));
+        const float c1 = exp2f(fmaf(__uint_as_float(v1[2 * i + 1]), p.scale_log2, nref));
+        sum += (a0 + a1) + (c0 + c1);
+        pk[i] = pack2(a0, a1);
+        pk[16 + i] = pack2(c0, c1);
+      }
+      l += sum;
+      // this stream's P tile and O accumulator are quiescent once its previous P.V has completed
+      if (j >= 1) { tma::mbar_wait(&pv_done[s], (j - 1) & 1, p.status, 17); tc_fence_after(); }
+      // rescale O when some row of this warp moved its exponent base (not for the first tile: the first
+      // P.V overwrites O instead of accumulating)
+      if (__any_sync(0xffffffffu, (alpha != 1.f) && j > 0)) {
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t o[32];
+          tc_ld32(o_col + c * 32, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc_st32(o_col + c * 32, o);
+        }
+        tc_wait_st();
+      }
+      // P row -> shared, K-major 128-byte-swizzled tile ([row][64 keys])
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) tma::mbar_arrive(p_full);
+      if (lane == 0) tma::mbar_arrive(&p_full[s]);
     }
 
-    // ---- epilogue ----
-    tma::mbar_wait(pv_done, (NT - 1) & 1, p.status, 18);
+    // ---- epilogue: normalise, exchange the noise rows through shared memory, subtract, norm, store ----
+    tma::mbar_wait(&pv_done[s], (NT - 1) & 1, p.status, 18);
     tc_fence_after();
     const bool valid = grow < p.blk;
-    const float inv_s = l[0] > 0.f ? 1.f / l[0] : 0.f, inv_n = l[1] > 0.f ? 1.f / l[1] : 0.f;
-    float lam = 0.f;
-    if (valid) lam = bf16_round(p.lam[(long long)b * p.lam_bs + (long long)(p.t0 + grow) * p.lam_rs + h]);
-    uint32_t dpk[DH / 2];                                  // packed bf16 differences of the row
-    float sq = 0.f;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    constexpr int CHUNKS = DH / 8;                         // 16-byte chunks per exchanged row
+    unsigned char* xrow = sQn + row * (DH * 2);            // the query tiles are dead once every Q.K^T has completed
+    if (s == 1) {
+      // all MMAs of both streams are complete when the noise stream's last P.V is (it is issued last)
 #pragma unroll
-    for (int c = 0; c < DH / 32; ++c) {
-      uint32_t os[32], on[32];
-      tc_ld32(lane_addr + TM_OS + c * 32, os);
-      tc_ld32(lane_addr + TM_ON + c * 32, on);
-      tc_wait_ld();
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t o[32];
+        tc_ld32(o_col + c * 32, o);
+        tc_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float d[2];
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w[4];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float vs = bf16_round(__uint_as_float(os[2 * i + e]) * inv_s);
-          const float vn = bf16_round(__uint_as_float(on[2 * i + e]) * inv_n);
-          d[e] = t_sub<bf16>(vs, t_mul<bf16>(lam, vn));
-          sq += bf16_round(d[e] * d[e]);
-        }
-        dpk[c * 16 + i] = pack2(d[0], d[1]);
-      }
-    }
-    if (valid) {
-      bf16* op = p.out + (long long)b * p.out_bs + (long long)(p.t0 + grow) * p.out_rs + (long long)h * DH;
-      if (p.norm_full) {
-        const float var = bf16_round(sq / (float)DH);
-        const float rs = bf16_round(rsqrtf(bf16_round(var + p.eps)));
-#pragma unroll
-        for (int i = 0; i < DH / 2; ++i) {
-          const __nv_bfloat162 dv = *reinterpret_cast<__nv_bfloat162*>(&dpk[i]);
-          const __nv_bfloat162 wv = reinterpret_cast<const __nv_bfloat162*>(p.norm_w)[i];
-          const float y0 = t_mul<bf16>(t_mul<bf16>(__low2float(dv), rs), __low2float(wv));
-          const float y1 = t_mul<bf16>(t_mul<bf16>(__high2float(dv), rs), __high2float(wv));
-          dpk[i] = pack2(y0, y1);
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack2(__uint_as_float(o[q4 * 8 + 2 * e]) * inv, __uint_as_float(o[q4 * 8 + 2 * e + 1]) * inv);
+          const int ch = c * 4 + q4;
+          *reinterpret_cast<uint4*>(xrow + ((ch ^ (row & (CHUNKS - 1))) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
+      tc_fence_before();
+      bar_softmax_all();
+    } else {
+      float lam = 0.f;
+      if (valid) lam = bf16_round(p.lam[(long long)b * p.lam_bs + (long long)(p.t0 + grow) * p.lam_rs + h]);
+      bar_softmax_all();                                   // noise rows are in shared memory
+      uint32_t dpk[DH / 2];                                // packed bf16 differences of the row
+      float sq = 0.f;
 #pragma unroll
-      for (int i = 0; i < DH / 8; ++i)
-        reinterpret_cast<uint4*>(op)[i] = make_uint4(dpk[4 * i], dpk[4 * i + 1], dpk[4 * i + 2], dpk[4 * i + 3]);
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t o[32];
+        tc_ld32(o_col + c * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int ch = c * 4 + q4;
+          const uint4 nz = *reinterpret_cast<const uint4*>(xrow + ((ch ^ (row & (CHUNKS - 1))) << 4));
+          const uint32_t nw[4] = {nz.x, nz.y, nz.z, nz.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 nv = *reinterpret_cast<const __nv_bfloat162*>(&nw[e]);
+            const float vs0 = bf16_round(__uint_as_float(o[q4 * 8 + 2 * e]) * inv);
+            const float vs1 = bf16_round(__uint_as_float(o[q4 * 8 + 2 * e + 1]) * inv);
+            const float d0 = t_sub<bf16>(vs0, t_mul<bf16>(lam, __low2float(nv)));
+            const float d1 = t_sub<bf16>(vs1, t_mul<bf16>(lam, __high2float(nv)));
+            sq += bf16_round(d0 * d0) + bf16_round(d1 * d1);
+            dpk[c * 16 + q4 * 4 + e] = pack2(d0, d1);
+          }
+        }
+      }
+      if (valid) {
+        bf16* op = p.out + (long long)b * p.out_bs + (long long)(p.t0 + grow) * p.out_rs + (long long)h * DH;
+        if (p.norm_full) {
+          const float var = bf16_round(sq / (float)DH);
+          const float rs = bf16_round(rsqrtf(bf16_round(var + p.eps)));
+#pragma unroll
+          for (int i = 0; i < DH / 2; ++i) {
+            const __nv_bfloat162 dv = *reinterpret_cast<__nv_bfloat162*>(&dpk[i]);
+            const __nv_bfloat162 wv = reinterpret_cast<const __nv_bfloat162*>(p.norm_w)[i];
+            dpk[i] = pack2(t_mul<bf16>(t_mul<bf16>(__low2float(dv), rs), __low2float(wv)),
+                           t_mul<bf16>(t_mul<bf16>(__high2float(dv), rs), __high2float(wv)));
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i)
+          reinterpret_cast<uint4*>(op)[i] = make_uint4(dpk[4 * i], dpk[4 * i + 1], dpk[4 * i + 2], dpk[4 * i + 3]);
+      }
+      tc_fence_before();
     }
-    tc_fence_before();
   }
 
   __syncthreads();
@@ -393,7 +418,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
 template <int DH>
 size_t prefill_smem(int Lbuf) {
   const int NP = (Lbuf + PF_BN - 1) / PF_BN;
-  return (size_t)2 * (DH / 64) * PF_BM * 128 + 2 * PF_BM * 128 + 4 * (size_t)(DH / 64) * PF_BN * 128 + 11 * 8 + 8 +
+  return (size_t)2 * (DH / 64) * PF_BM * 128 + 2 * PF_BM * 128 + 4 * (size_t)(DH / 64) * PF_BN * 128 + 17 * 8 + 8 +
          (size_t)NP * 2 * 4 + 1024 + 64;
 }
 

@@ -1,13 +1,16 @@
-// Bank + ring update with one prefill block, as three launches:
-//   route_score   grid (candidate groups, B): cosine scores of each candidate against the
-//                 routing caches as they were before the block; per candidate the best exact
-//                 slot/score and the summary argmax go to a small global scratch.
-//   route_commit  grid (B): the order-dependent decisions (LRU victim ranking, novel-rank
-//                 assignment, stamps) on one thread, then the slot writes and cache re-normalisation.
-//   ring_rewrite  grid (Hkv, B): kept ring rows shift to the front, the block's tail is appended.
+// Bank + ring update with one prefill block, as four launches:
+//   route_score   grid (2, B): cosine scores of every candidate against the routing caches as they were
+//                 before the block (a register-tiled fp32 mini-GEMM per bank); per candidate the best
+//                 exact slot/score and the summary argmax go to a small global scratch.
+//   route_decide  grid (B): the order-dependent decisions (LRU victim ranking, novel-rank assignment,
+//                 stamps, per-slot candidate lists) -> a small per-state plan in global scratch.
+//   route_apply   grid (written slots, B): one CTA per written bank slot: values + cache re-normalisation.
+//   ring_rewrite  grid (2*Hkv, B): kept ring rows shift to the front, the block's tail is appended.
 // Semantics: upstream memory_banks.py:438-564 (block write), 633-742 (exact), 853-932 (summary).
 #include "coda_common.cuh"
 #include "topk_order.h"
+#include "tma_utils.cuh"
+#include "bank_score.cuh"
 
 struct RouteParams {
   coda_layer_cfg c;
@@ -20,6 +23,7 @@ struct RouteParams {
   const int* cand; long long cand_bs;
   const float* eta_logit;
   float* ex_best; int* ex_bi; int* su_idx;   // scratch: [B][Te], [B][Te], [B][Ts]
+  int* plan;                                 // scratch: per-state plan (see Plan)
 };
 
 // Row of evicted token e (ring slot e when e < fill, else row e-fill of the block), head h.
@@ -31,115 +35,223 @@ __device__ __forceinline__ const T* src_row(const RouteParams& p, const void* bu
   return (const T*)blkp + (long long)b * bbs + (long long)(e - p.fill) * brs + (long long)h * Dh;
 }
 
-constexpr int RS_WARPS = 8;
+// ---- scores: a register-tiled fp32 mini-GEMM per state and bank ----
+// S[candidate][slot] = mean over heads of the dtype-rounded per-head dot products of the unit-norm candidate
+// with the bank's unit-norm cache row; the kernel keeps only the row-wise first-index argmax (and, for the
+// exact bank, the best score).  Grid (2, B): x = 0 exact bank (V rows, n = Dh), x = 1 summary bank (LF half of
+// the K rows, n = Dh/2).  Tiles: RS_ROWS candidates x 64 slots x 64-element K chunks of one head, staged
+// transposed ([k][row]) in shared memory as fp32; 256 threads, each TM x 4 outputs.
+constexpr int RS_KC = 64;
+constexpr int RS_COLS = 64;
 
-template <typename T>
-__global__ void __launch_bounds__(RS_WARPS * 32) route_score_kernel(RouteParams p) {
-  extern __shared__ float sm[];
+template <typename T, int TM>
+__device__ __forceinline__ void route_score_bank(const RouteParams& p, int b, bool exact, float* sm) {
+  constexpr int ROWS = 16 * TM;
   const coda_layer_cfg& c = p.c;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int b = blockIdx.y;
-  const int Hkv = c.Hkv, Dh = c.Dh, lf = Dh / 2, lfd = Dh - lf, Me = c.Me, Ms = c.Ms, W = c.W;
-  const int ge = (p.te + RS_WARPS - 1) / RS_WARPS;          // groups of exact candidates
-  const bool exact = (int)blockIdx.x < ge;
-  const int t = (exact ? blockIdx.x : blockIdx.x - ge) * RS_WARPS + warp;
-  if (t >= (exact ? p.te : p.ts)) return;
-  float* hat = sm + (size_t)warp * Hkv * Dh;                // this warp's unit-norm candidate
-  const int e = p.cand[(long long)b * p.cand_bs + t];
+  const int tid = threadIdx.x;
+  const int Hkv = c.Hkv, Dh = c.Dh, lf = Dh / 2, W = c.W, Me = c.Me, Ms = c.Ms;
+  const int n = exact ? Dh : Dh - lf, M = exact ? Me : Ms, Tn = exact ? p.te : p.ts;
+  const int active = exact ? c.active_exact : c.active_summary;
+  const T* cache = exact ? (const T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh
+                         : (const T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * n;
   const uint8_t* al = p.st.allowed + (long long)b * (W + Me + Ms);
-  if (exact) {
-    for (int h = 0; h < Hkv; ++h) {                         // v_hat = v / max(||v||, 1e-6)  (:498)
-      const T* row = src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, e, h);
+  float* As = sm;                                  // [RS_KC][ROWS]
+  float* Bs = As + RS_KC * ROWS;                   // [RS_KC][RS_COLS]
+  float* Ss = Bs + RS_KC * RS_COLS;                // [ROWS][RS_COLS + 1]
+  float* den = Ss + ROWS * (RS_COLS + 1);          // [ROWS][Hkv]
+  int* cidx = reinterpret_cast<int*>(den + ROWS * Hkv);   // [ROWS]
+  const int ty = tid >> 4, tx = tid & 15;          // 16 x 16 thread grid
+
+  for (int r0 = 0; r0 < Tn; r0 += ROWS) {
+    const int nrows = min(ROWS, Tn - r0);
+    __syncthreads();
+    for (int r = tid; r < ROWS; r += 256) cidx[r] = r < nrows ? p.cand[(long long)b * p.cand_bs + r0 + r] : -1;
+    __syncthreads();
+    // ||x|| of every (candidate, head) of the tile: one thread per pair, batched loads  (memory_banks.py:498-500)
+    for (int it = tid; it < ROWS * Hkv; it += 256) {
+      const int r = it / Hkv, h = it % Hkv;
       float ss = 0.f;
-      for (int d = lane; d < Dh; d += 32) { const float v = El<T>::ld(row + d); hat[h * Dh + d] = v; ss += v * v; }
-      const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
-      for (int d = lane; d < Dh; d += 32) hat[h * Dh + d] = t_div<T>(hat[h * Dh + d], den);
-    }
-    __syncwarp();
-    const T* vnorm = (const T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh;
-    float best = 0.f; int bi = 0;
-    for (int m = 0; m < Me; ++m) {
-      float tot = 0.f;
-      for (int h = 0; h < Hkv; ++h) {
-        const T* row = vnorm + ((long long)h * Me + m) * Dh;
-        float part = 0.f;
-        for (int d = lane; d < Dh; d += 32) part += hat[h * Dh + d] * El<T>::ld(row + d);
-        tot += El<T>::rnd(warp_sum(part));
+      if (cidx[r] >= 0) {
+        const T* row = exact ? src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, cidx[r], h)
+                             : src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, cidx[r], h) + lf;
+        int d = 0;
+        for (; d + 16 <= n; d += 16) {
+          float x[16];
+          load_run<T, 16>(row + d, x);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ss = fmaf(x[i], x[i], ss);
+        }
+        for (; d < n; ++d) { const float v = El<T>::ld(row + d); ss = fmaf(v, v, ss); }
       }
-      float s = El<T>::rnd(tot / (float)Hkv);
-      if (m >= c.active_exact || !al[W + m]) s = -1e9f;      // (:646-650)
-      if (m == 0 || s > best) { best = s; bi = m; }
+      den[it] = fmaxf(El<T>::rnd(sqrtf(ss)), 1e-6f);
     }
-    if (lane == 0) { p.ex_best[(long long)b * c.Te + t] = best; p.ex_bi[(long long)b * c.Te + t] = bi; }
-  } else {
-    for (int h = 0; h < Hkv; ++h) {                         // k_hat over the LF band (:500)
-      const T* row = src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, e, h) + lf;
-      float ss = 0.f;
-      for (int d = lane; d < lfd; d += 32) { const float v = El<T>::ld(row + d); hat[h * lfd + d] = v; ss += v * v; }
-      const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
-      for (int d = lane; d < lfd; d += 32) hat[h * lfd + d] = t_div<T>(hat[h * lfd + d], den);
-    }
-    __syncwarp();
-    const T* knorm = (const T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
-    float best = 0.f; int bi = 0;
-    for (int m = 0; m < Ms; ++m) {
-      float tot = 0.f;
+    float best = 0.f; int bi = 0;                  // running first-index argmax of row `tid` (tid < ROWS)
+    for (int c0 = 0; c0 < M; c0 += RS_COLS) {
+      float tot[TM][4];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) { tot[i][0] = tot[i][1] = tot[i][2] = tot[i][3] = 0.f; }
       for (int h = 0; h < Hkv; ++h) {
-        const T* row = knorm + ((long long)h * Ms + m) * lfd;
-        float part = 0.f;
-        for (int d = lane; d < lfd; d += 32) part += hat[h * lfd + d] * El<T>::ld(row + d);
-        tot += El<T>::rnd(warp_sum(part));
+        float acc[TM][4];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        for (int k0 = 0; k0 < n; k0 += RS_KC) {
+          __syncthreads();
+          // stage: candidates (normalised, dtype-rounded) and cache rows, both transposed to [k][row];
+          // every thread owns a run of KRUN consecutive k of one row and loads it in one batch
+          {
+            constexpr int KRUN_A = RS_KC * ROWS / 256;          // 16 (64-row tile) or 4 (16-row tile)
+            const int r = tid % ROWS, kq0 = (tid / ROWS) * KRUN_A;
+            float x[KRUN_A];
+#pragma unroll
+            for (int i = 0; i < KRUN_A; ++i) x[i] = 0.f;
+            if (cidx[r] >= 0) {
+              const T* row = exact ? src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, cidx[r], h)
+                                   : src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, cidx[r], h) + lf;
+              if (k0 + kq0 + KRUN_A <= n) load_run<T, KRUN_A>(row + k0 + kq0, x);
+              else
+                for (int i = 0; i < KRUN_A; ++i) if (k0 + kq0 + i < n) x[i] = El<T>::ld(row + k0 + kq0 + i);
+              const float dn = den[r * Hkv + h];
+#pragma unroll
+              for (int i = 0; i < KRUN_A; ++i) x[i] = t_div<T>(x[i], dn);
+            }
+#pragma unroll
+            for (int i = 0; i < KRUN_A; ++i) As[(kq0 + i) * ROWS + r] = x[i];
+          }
+          {
+            constexpr int KRUN_B = RS_KC * RS_COLS / 256;       // 16
+            const int col = tid % RS_COLS, kq0 = (tid / RS_COLS) * KRUN_B, m = c0 + col;
+            float x[KRUN_B];
+#pragma unroll
+            for (int i = 0; i < KRUN_B; ++i) x[i] = 0.f;
+            if (m < M) {
+              const T* row = cache + ((long long)h * M + m) * n;
+              if (k0 + kq0 + KRUN_B <= n) load_run<T, KRUN_B>(row + k0 + kq0, x);
+              else
+                for (int i = 0; i < KRUN_B; ++i) if (k0 + kq0 + i < n) x[i] = El<T>::ld(row + k0 + kq0 + i);
+            }
+#pragma unroll
+            for (int i = 0; i < KRUN_B; ++i) Bs[(kq0 + i) * RS_COLS + col] = x[i];
+          }
+          __syncthreads();
+#pragma unroll 8
+          for (int kq = 0; kq < RS_KC; ++kq) {
+            float a[TM];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kq * ROWS + ty * TM + i];
+            const float4 bv = *reinterpret_cast<const float4*>(Bs + kq * RS_COLS + tx * 4);
+#pragma unroll
+            for (int i = 0; i < TM; ++i) {
+              acc[i][0] = fmaf(a[i], bv.x, acc[i][0]); acc[i][1] = fmaf(a[i], bv.y, acc[i][1]);
+              acc[i][2] = fmaf(a[i], bv.z, acc[i][2]); acc[i][3] = fmaf(a[i], bv.w, acc[i][3]);
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) tot[i][jj] += El<T>::rnd(acc[i][jj]);
       }
-      float s = El<T>::rnd(tot / (float)Hkv);
-      if (m >= c.active_summary) s = -1e9f;                  // (:875-877)
-      if (m == 0 || s > best) { best = s; bi = m; }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int m = c0 + tx * 4 + jj;
+          float s = El<T>::rnd(tot[i][jj] / (float)Hkv);
+          if (m >= M) s = -INFINITY;                                   // padding column: never wins
+          else if (m >= active || (exact && !al[W + m])) s = -1e9f;    // (:646-650, :875-877)
+          Ss[(ty * TM + i) * (RS_COLS + 1) + tx * 4 + jj] = s;
+        }
+      __syncthreads();
+      if (tid < nrows) {
+        for (int col = 0; col < RS_COLS && c0 + col < M; ++col) {
+          const float s = Ss[tid * (RS_COLS + 1) + col];
+          if ((c0 == 0 && col == 0) || s > best) { best = s; bi = c0 + col; }
+        }
+      }
     }
-    if (lane == 0) p.su_idx[(long long)b * c.Ts + t] = bi;
+    if (tid < nrows) {
+      if (exact) { p.ex_best[(long long)b * c.Te + r0 + tid] = best; p.ex_bi[(long long)b * c.Te + r0 + tid] = bi; }
+      else p.su_idx[(long long)b * c.Ts + r0 + tid] = bi;
+    }
   }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) route_commit_kernel(RouteParams p) {
+__global__ void __launch_bounds__(256) route_score_kernel(RouteParams p) {
+  extern __shared__ float sm[];
+  const bool exact = blockIdx.x == 0;
+  if (exact) { if (p.te > 0 && p.c.Me > 0) route_score_bank<T, 1>(p, blockIdx.y, true, sm); }
+  else if (p.ts > 0 && p.c.Ms > 0) route_score_bank<T, 4>(p, blockIdx.y, false, sm);
+}
+
+// Per-state plan written by route_decide and consumed by route_apply (all int32 / fp32, in global scratch).
+struct Plan {
+  int* e_tgt; int* e_flag;            // [Te]  target slot; bit0 overwrite, bit1 touch, bit2 first overwriter of its slot
+  float* s_w; int* s_ord;             // [Ts]  summary weights; candidates grouped by slot
+  int* s_start; float* s_cnt; int* s_was;   // [Ms+1], [Ms], [Ms]
+};
+__device__ __forceinline__ Plan plan_of(const RouteParams& p, int b) {
+  const int Te = p.c.Te > 0 ? p.c.Te : 0, Ts = p.c.Ts > 0 ? p.c.Ts : 0, Ms = p.c.Ms;
+  const size_t per = (size_t)(2 * Te + 2 * Ts + 3 * Ms + 1);
+  int* base = p.plan + (size_t)b * per;
+  Plan pl;
+  pl.e_tgt = base; pl.e_flag = base + Te;
+  pl.s_w = reinterpret_cast<float*>(base + 2 * Te); pl.s_ord = base + 2 * Te + Ts;
+  pl.s_start = base + 2 * Te + 2 * Ts; pl.s_cnt = reinterpret_cast<float*>(pl.s_start + Ms + 1);
+  pl.s_was = pl.s_start + Ms + 1 + Ms;
+  return pl;
+}
+
+// ---- decisions: the order-dependent part, one small CTA per state ----
+// Inputs are staged into shared memory by all threads, the two serial sections (exact bank on thread 0,
+// summary bank on thread 32) work on shared memory only, and the plan is copied out cooperatively.
+template <typename T>
+__global__ void __launch_bounds__(64) route_decide_kernel(RouteParams p) {
   extern __shared__ unsigned char smraw[];
   const coda_layer_cfg& c = p.c;
-  const int b = blockIdx.x, tid = threadIdx.x, NT = blockDim.x, lane = tid & 31, warp = tid >> 5, NW = NT >> 5;
-  const int Hkv = c.Hkv, Dh = c.Dh, HD = Hkv * Dh, lf = Dh / 2, lfd = Dh - lf;
+  const int b = blockIdx.x, tid = threadIdx.x, NT = blockDim.x;
   const int Me = c.Me, Ms = c.Ms, W = c.W, Lbuf = W + Me + Ms;
-  const int te = p.te, ts = p.ts, tmax = te > ts ? te : ts;
-  // shared layout
+  const int te = (Me > 0) ? p.te : 0, ts = (Ms > 0) ? p.ts : 0, tmax = te > ts ? te : ts;
   typedef topk_order::Item<long long> It64;
   It64* lruq = reinterpret_cast<It64*>(smraw);                       // [Me]
-  float* stash = reinterpret_cast<float*>(lruq + (Me > 0 ? Me : 1)); // [HD] new row for re-normalising
-  float* c_g = stash + HD;                                           // [tmax] gates
-  float* s_w = c_g + tmax;                                           // [ts] summary weights
-  float* s_cnt = s_w + (ts > 0 ? ts : 1);                            // [Ms] per-slot weight sum
-  int* c_e = reinterpret_cast<int*>(s_cnt + (Ms > 0 ? Ms : 1));      // [tmax] evicted index
-  int* e_tgt = c_e + tmax;                                           // [te] exact target slot
-  int* e_ow = e_tgt + (te > 0 ? te : 1);                             // [te] overwrite flag
-  int* s_ord = e_ow + (te > 0 ? te : 1);                             // [ts] candidates grouped by slot
-  int* s_start = s_ord + (ts > 0 ? ts : 1);                          // [Ms+1]
-  int* s_was = s_start + Ms + 1;                                     // [Ms] slot was used before the block
-
-  uint8_t* al = p.st.allowed + (long long)b * Lbuf;
-  T* kb = (T*)p.st.k_buf + (long long)b * Hkv * Lbuf * Dh;
-  T* vb = (T*)p.st.v_buf + (long long)b * Hkv * Lbuf * Dh;
-
+  long long* s_last = reinterpret_cast<long long*>(lruq + (Me > 0 ? Me : 1));   // [Me]
+  long long* n_last = s_last + (Me > 0 ? Me : 1);                    // [Me] new stamps
+  float* c_g = reinterpret_cast<float*>(n_last + (Me > 0 ? Me : 1)); // [tmax] gates
+  float* x_best = c_g + (tmax > 0 ? tmax : 1);                       // [te]
+  float* w_s = x_best + (te > 0 ? te : 1);                           // [ts] summary weights
+  float* cnt_s = w_s + (ts > 0 ? ts : 1);                            // [Ms]
+  int* c_e = reinterpret_cast<int*>(cnt_s + (Ms > 0 ? Ms : 1));      // [tmax] evicted index
+  int* x_bi = c_e + (tmax > 0 ? tmax : 1);                           // [te]
+  int* tgt_s = x_bi + (te > 0 ? te : 1);                             // [te]
+  int* flag_s = tgt_s + (te > 0 ? te : 1);                           // [te]
+  int* s_idx = flag_s + (te > 0 ? te : 1);                           // [ts]
+  int* ord_s = s_idx + (ts > 0 ? ts : 1);                            // [ts]
+  int* start_s = ord_s + (ts > 0 ? ts : 1);                          // [Ms+1]
+  int* s_cur = start_s + Ms + 1;                                     // [Ms]
+  unsigned char* s_used = reinterpret_cast<unsigned char*>(s_cur + (Ms > 0 ? Ms : 1));   // [Me + Ms]
+  const uint8_t* al = p.st.allowed + (long long)b * Lbuf;
+  long long* last = (long long*)p.st.mem_last_exact + (long long)b * Me;
+  Plan pl = plan_of(p, b);
   for (int t = tid; t < tmax; t += NT) {
     const int e = p.cand[(long long)b * p.cand_bs + t];
     c_e[t] = e;
     c_g[t] = p.gates[(long long)b * p.gates_bs + p.gate_ev0 + e];
   }
+  for (int t = tid; t < te; t += NT) { x_best[t] = p.ex_best[(long long)b * c.Te + t]; x_bi[t] = p.ex_bi[(long long)b * c.Te + t]; }
+  for (int t = tid; t < ts; t += NT) s_idx[t] = p.su_idx[(long long)b * c.Ts + t];
+  for (int m = tid; m < Me + Ms; m += NT) s_used[m] = al[W + m];
+  for (int m = tid; m < Me; m += NT) { s_last[m] = last[m]; n_last[m] = last[m]; }
   __syncthreads();
 
-  if (tid == 0 && te > 0 && Me > 0) {
-    // ---- exact bank decisions (memory_banks.py:635-697) ----
-    long long* last = (long long*)p.st.mem_last_exact + (long long)b * Me;
+  if (tid == 0 && te > 0) {
+    // ---- exact bank (memory_banks.py:635-697) ----
     const int Ae = c.active_exact;
     bool any_used = false;
     for (int m = 0; m < Me; ++m) {
-      const bool used = al[W + m] != 0;
+      const bool used = s_used[m] != 0;
       any_used |= used;
-      lruq[m].v = (used && m < Ae) ? last[m] : -(1LL << 62);
+      lruq[m].v = (used && m < Ae) ? s_last[m] : -(1LL << 62);
       lruq[m].i = m;
     }
     const int n_lru = te < Ae ? te : Ae;
@@ -147,8 +259,7 @@ __global__ void __launch_bounds__(256) route_commit_kernel(RouteParams p) {
     const float tn = El<T>::rnd(c.tau_novel), tm = El<T>::rnd(c.tau_match);
     int rank = -1;
     for (int t = 0; t < te; ++t) {
-      const float best = p.ex_best[(long long)b * c.Te + t];
-      const int bi = p.ex_bi[(long long)b * c.Te + t];
+      const float best = x_best[t];
       const bool keep = c.gated ? (c_g[t] >= c.tau_gate_exact) : true;
       const bool novel = !any_used || best < tn;
       const bool hit = any_used && best >= tm;
@@ -157,168 +268,222 @@ __global__ void __launch_bounds__(256) route_commit_kernel(RouteParams p) {
       const bool capped = nk && rank < Ae;
       int r = rank < 0 ? 0 : rank;
       if (r > n_lru - 1) r = n_lru - 1 > 0 ? n_lru - 1 : 0;
-      const int tgt = capped ? lruq[r].i : bi;
+      const int tgt = capped ? lruq[r].i : x_bi[t];
       const bool touch = keep && (!novel || capped);
-      e_tgt[t] = tgt;
-      e_ow[t] = (c.refresh_on_hit ? (keep && (capped || hit)) : capped) ? 1 : 0;
-      // bit 1 of e_ow marks "touch" for the stamp pass below
-      if (touch) e_ow[t] |= 2;
+      const bool ow = c.refresh_on_hit ? (keep && (capped || hit)) : capped;
+      int flag = (ow ? 1 : 0) | (touch ? 2 : 0);
+      if (ow) {
+        bool first = true;
+        for (int u = 0; u < t; ++u) if ((flag_s[u] & 1) && tgt_s[u] == tgt) { first = false; break; }
+        if (first) flag |= 4;
+      }
+      tgt_s[t] = tgt;
+      flag_s[t] = flag;
     }
-    // stamps: per slot the largest position among touching candidates replaces the old stamp
+    // stamps: per slot the largest position among touching candidates replaces the old stamp (:682-697)
     for (int t = 0; t < te; ++t) {
-      if (!(e_ow[t] & 2)) continue;
+      if (!(flag_s[t] & 2)) continue;
+      const int tgt = tgt_s[t];
       bool first = true;
-      for (int u = 0; u < t; ++u) if ((e_ow[u] & 2) && e_tgt[u] == e_tgt[t]) { first = false; break; }
+      for (int u = 0; u < t; ++u) if ((flag_s[u] & 2) && tgt_s[u] == tgt) { first = false; break; }
       if (!first) continue;
       long long mx = p.pos_first + c_e[t];
       for (int u = t + 1; u < te; ++u)
-        if ((e_ow[u] & 2) && e_tgt[u] == e_tgt[t]) { const long long pu = p.pos_first + c_e[u]; if (pu > mx) mx = pu; }
-      last[e_tgt[t]] = mx;
+        if ((flag_s[u] & 2) && tgt_s[u] == tgt) { const long long pu = p.pos_first + c_e[u]; if (pu > mx) mx = pu; }
+      n_last[tgt] = mx;
     }
   }
-  if (tid == 32 % NT && ts > 0 && Ms > 0) {
-    // ---- summary bank bookkeeping (memory_banks.py:880-885, 906): weights, per-slot lists ----
-    for (int m = 0; m < Ms; ++m) { s_cnt[m] = 0.f; s_start[m] = 0; s_was[m] = al[W + Me + m] != 0; }
-    s_start[Ms] = 0;
+  if (tid == 32 && ts > 0) {
+    // ---- summary bank bookkeeping (memory_banks.py:880-885, 906): weights, per-slot candidate lists ----
+    for (int m = 0; m < Ms; ++m) { cnt_s[m] = 0.f; start_s[m] = 0; }
+    start_s[Ms] = 0;
     for (int t = 0; t < ts; ++t) {
       float w = El<T>::rnd(c_g[t]);
       if (c.gated && !(c_g[t] >= c.tau_gate_summary)) w = 0.f;           // (:518-523)
-      s_w[t] = w;
-      const int m = p.su_idx[(long long)b * c.Ts + t];
-      s_cnt[m] = t_add<T>(s_cnt[m], w);
-      s_start[m + 1] += 1;
+      w_s[t] = w;
+      const int m = s_idx[t];
+      cnt_s[m] = t_add<T>(cnt_s[m], w);
+      start_s[m + 1] += 1;
     }
-    for (int m = 0; m < Ms; ++m) s_start[m + 1] += s_start[m];
-    // stable grouping by slot (fill positions from a running cursor kept in s_ord's tail-free pass)
-    for (int m = 0; m < Ms; ++m) {
-      int w_ = s_start[m];
-      for (int t = 0; t < ts; ++t) if (p.su_idx[(long long)b * c.Ts + t] == m) s_ord[w_++] = t;
-    }
+    for (int m = 0; m < Ms; ++m) start_s[m + 1] += start_s[m];
+    for (int m = 0; m < Ms; ++m) s_cur[m] = start_s[m];
+    for (int t = 0; t < ts; ++t) ord_s[s_cur[s_idx[t]]++] = t;            // stable grouping by slot
   }
   __syncthreads();
-
-  // ---- exact bank writes (memory_banks.py:707-742) ----
-  if (te > 0 && Me > 0) {
-    T* vnorm = (T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh;
-    for (int t = 0; t < te; ++t) {
-      if (!(e_ow[t] & 1)) continue;
-      const int slot = e_tgt[t];
-      bool leader = true;
-      for (int u = 0; u < t; ++u) if ((e_ow[u] & 1) && e_tgt[u] == slot) { leader = false; break; }
-      if (!leader) continue;                                             // CTA-uniform
-      for (int e = tid; e < HD; e += NT) {
-        const int h = e / Dh, d = e % Dh;
-        T* pk = kb + ((long long)h * Lbuf + W + slot) * Dh + d;
-        T* pv = vb + ((long long)h * Lbuf + W + slot) * Dh + d;
-        const float ok = El<T>::ld(pk), ov = El<T>::ld(pv);
-        float ck = 0.f, cv = 0.f;                                        // scatter_add of deltas, candidate order
-        for (int u = t; u < te; ++u) {
-          if (!(e_ow[u] & 1) || e_tgt[u] != slot) continue;
-          const float xk = El<T>::ld(src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, c_e[u], h) + d);
-          const float xv = El<T>::ld(src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, c_e[u], h) + d);
-          ck = t_add<T>(ck, t_sub<T>(xk, ok));
-          cv = t_add<T>(cv, t_sub<T>(xv, ov));
-        }
-        El<T>::st(pk, t_add<T>(ok, ck));
-        const float nv = t_add<T>(ov, cv);
-        El<T>::st(pv, nv);
-        stash[e] = nv;
-      }
-      if (tid == 0) al[W + slot] = 1;
-      __syncthreads();
-      for (int h = warp; h < Hkv; h += NW) {
-        float ss = 0.f;
-        for (int d = lane; d < Dh; d += 32) { const float v = stash[h * Dh + d]; ss += v * v; }
-        const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
-        for (int d = lane; d < Dh; d += 32)
-          El<T>::st(vnorm + ((long long)h * Me + slot) * Dh + d, t_div<T>(stash[h * Dh + d], den));
-      }
-      __syncthreads();
-    }
-  }
-
-  // ---- summary bank EMA (memory_banks.py:887-932) ----
-  if (ts > 0 && Ms > 0) {
-    T* knorm = (T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
-    const float cmin = El<T>::rnd(1e-6f);
-    for (int m = 0; m < Ms; ++m) {
-      const float cnt = s_cnt[m];
-      if (!(cnt > 0.f)) continue;                                        // CTA-uniform
-      const int a0 = s_start[m], a1 = s_start[m + 1];
-      const float cden = fmaxf(cnt, cmin);
-      const bool fresh = c.overwrite_on_insert && !s_was[m];
-      for (int e = tid; e < HD; e += NT) {
-        const int h = e / Dh, d = e % Dh;
-        float sk = 0.f, sv = 0.f;
-        for (int a = a0; a < a1; ++a) {
-          const int t = s_ord[a];
-          const float w = s_w[t];
-          const float xk = El<T>::ld(src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, c_e[t], h) + d);
-          const float xv = El<T>::ld(src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, c_e[t], h) + d);
-          sk = t_add<T>(sk, t_mul<T>(xk, w));
-          sv = t_add<T>(sv, t_mul<T>(xv, w));
-        }
-        const float eta = fresh ? 1.f : t_sigmoid<T>(p.eta_logit[h]);
-        T* pk = kb + ((long long)h * Lbuf + W + Me + m) * Dh + d;
-        T* pv = vb + ((long long)h * Lbuf + W + Me + m) * Dh + d;
-        const float ov = El<T>::ld(pv);
-        El<T>::st(pv, t_add<T>(ov, t_mul<T>(eta, t_sub<T>(t_div<T>(sv, cden), ov))));
-        if (d >= lf) {
-          const float ok = El<T>::ld(pk);
-          const float inc = El<T>::rnd(__fmul_rn(t_div<T>(sk, cden), c.energy_scale));
-          const float nk = t_add<T>(ok, t_mul<T>(eta, t_sub<T>(inc, ok)));
-          El<T>::st(pk, nk);
-          stash[h * lfd + d - lf] = nk;
-        }
-      }
-      if (tid == 0) al[W + Me + m] = 1;
-      __syncthreads();
-      for (int h = warp; h < Hkv; h += NW) {
-        float ss = 0.f;
-        for (int d = lane; d < lfd; d += 32) { const float v = stash[h * lfd + d]; ss += v * v; }
-        const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
-        for (int d = lane; d < lfd; d += 32)
-          El<T>::st(knorm + ((long long)h * Ms + m) * lfd + d, t_div<T>(stash[h * lfd + d], den));
-      }
-      __syncthreads();
-    }
+  for (int t = tid; t < te; t += NT) { pl.e_tgt[t] = tgt_s[t]; pl.e_flag[t] = flag_s[t]; }
+  for (int m = tid; m < Me; m += NT) if (te > 0 && n_last[m] != s_last[m]) last[m] = n_last[m];
+  for (int t = tid; t < ts; t += NT) { pl.s_w[t] = w_s[t]; pl.s_ord[t] = ord_s[t]; }
+  if (ts > 0) {
+    for (int m = tid; m <= Ms; m += NT) pl.s_start[m] = start_s[m];
+    for (int m = tid; m < Ms; m += NT) { pl.s_cnt[m] = cnt_s[m]; pl.s_was[m] = s_used[Me + m] != 0; }
   }
 }
 
-// Ring rewrite (memory_banks.py:152-177, 554-563): with the ring in chronological order the kept
-// rows [drop, fill) move down to [0, fill-drop) and block rows [bstart, blk) follow them.
-constexpr int RR_PER = 8;
+// ---- slot writes: one CTA per written slot (exact: per overwriting candidate group; summary: per slot) ----
+// Each thread owns runs of 8 consecutive elements of the slot's [Hkv*Dh] row pair and loads old values and
+// candidate rows in batches.
 template <typename T>
-__global__ void __launch_bounds__(256) ring_rewrite_kernel(RouteParams p) {
+__global__ void __launch_bounds__(128) route_apply_kernel(RouteParams p) {
+  extern __shared__ float stash[];                                   // [Hkv*Dh] new row for re-normalising
   const coda_layer_cfg& c = p.c;
-  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, NT = blockDim.x;
+  const int b = blockIdx.y, tid = threadIdx.x, NT = blockDim.x, lane = tid & 31, warp = tid >> 5, NW = NT >> 5;
+  const int Hkv = c.Hkv, Dh = c.Dh, HD = Hkv * Dh, lf = Dh / 2, lfd = Dh - lf;
+  const int Me = c.Me, Ms = c.Ms, W = c.W, Lbuf = W + Me + Ms;
+  const int te = (Me > 0) ? p.te : 0;
+  uint8_t* al = p.st.allowed + (long long)b * Lbuf;
+  T* kb = (T*)p.st.k_buf + (long long)b * Hkv * Lbuf * Dh;
+  T* vb = (T*)p.st.v_buf + (long long)b * Hkv * Lbuf * Dh;
+  const Plan pl = plan_of(p, b);
+  __shared__ int s_n, s_cand[128];
+  __shared__ float s_wt[128];
+  const bool exact = (int)blockIdx.x < te;
+  int slot;                                                          // slot index inside its bank
+  float cden = 1.f; bool fresh = false;
+  if (exact) {
+    // ---- exact bank write (memory_banks.py:707-742): candidates that overwrite this slot, in list order ----
+    const int t = blockIdx.x;
+    if ((pl.e_flag[t] & 5) != 5) return;                               // not the first overwriter of its slot
+    slot = pl.e_tgt[t];
+    if (tid == 0) {
+      int nn = 0;
+      for (int u = t; u < te && nn < 128; ++u)
+        if ((pl.e_flag[u] & 1) && pl.e_tgt[u] == slot) { s_cand[nn] = p.cand[(long long)b * p.cand_bs + u]; s_wt[nn] = 1.f; ++nn; }
+      s_n = nn;
+    }
+  } else {
+    // ---- summary bank EMA of one slot (memory_banks.py:887-932) ----
+    slot = blockIdx.x - te;
+    if (slot >= Ms || p.ts <= 0) return;
+    const float cnt = pl.s_cnt[slot];
+    if (!(cnt > 0.f)) return;
+    cden = fmaxf(cnt, El<T>::rnd(1e-6f));
+    fresh = c.overwrite_on_insert && !pl.s_was[slot];
+    if (tid == 0) {
+      const int a0 = pl.s_start[slot], a1 = pl.s_start[slot + 1];
+      int nn = 0;
+      for (int a = a0; a < a1 && nn < 128; ++a) {
+        const int t = pl.s_ord[a];
+        s_cand[nn] = p.cand[(long long)b * p.cand_bs + t]; s_wt[nn] = pl.s_w[t]; ++nn;
+      }
+      s_n = nn;
+    }
+  }
+  __syncthreads();
+  const int nn = s_n;
+  const int gslot = W + (exact ? 0 : Me) + slot;
+  constexpr int R = 8;
+  const bool runs = (Dh % R) == 0;
+  for (int e0 = tid * R; e0 < HD; e0 += NT * R) {
+    const int h = e0 / Dh, d0 = e0 % Dh;
+    T* pk = kb + ((long long)h * Lbuf + gslot) * Dh + d0;
+    T* pv = vb + ((long long)h * Lbuf + gslot) * Dh + d0;
+    float ok[R], ov[R], ak[R], av[R];
+    if (runs) { load_run<T, R>(pk, ok); load_run<T, R>(pv, ov); }
+    else for (int i = 0; i < R; ++i) { ok[i] = (e0 + i < HD) ? El<T>::ld(kb + ((long long)((e0 + i) / Dh) * Lbuf + gslot) * Dh + (e0 + i) % Dh) : 0.f;
+                                       ov[i] = (e0 + i < HD) ? El<T>::ld(vb + ((long long)((e0 + i) / Dh) * Lbuf + gslot) * Dh + (e0 + i) % Dh) : 0.f; }
+#pragma unroll
+    for (int i = 0; i < R; ++i) { ak[i] = 0.f; av[i] = 0.f; }
+    for (int q = 0; q < nn; ++q) {
+      const int ce = s_cand[q];
+      const float w = s_wt[q];
+      float xk[R], xv[R];
+      if (runs) {
+        load_run<T, R>(src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, ce, h) + d0, xk);
+        load_run<T, R>(src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, ce, h) + d0, xv);
+      } else {
+        for (int i = 0; i < R; ++i) {
+          const int hh = (e0 + i) / Dh, dd = (e0 + i) % Dh;
+          xk[i] = (e0 + i < HD) ? El<T>::ld(src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, ce, hh) + dd) : 0.f;
+          xv[i] = (e0 + i < HD) ? El<T>::ld(src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, ce, hh) + dd) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        if (exact) { ak[i] = t_add<T>(ak[i], t_sub<T>(xk[i], ok[i])); av[i] = t_add<T>(av[i], t_sub<T>(xv[i], ov[i])); }
+        else { ak[i] = t_add<T>(ak[i], t_mul<T>(xk[i], w)); av[i] = t_add<T>(av[i], t_mul<T>(xv[i], w)); }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int e = e0 + i;
+      if (e >= HD) break;
+      const int hh = runs ? h : e / Dh, dd = runs ? d0 + i : e % Dh;
+      T* qk = runs ? pk + i : kb + ((long long)hh * Lbuf + gslot) * Dh + dd;
+      T* qv = runs ? pv + i : vb + ((long long)hh * Lbuf + gslot) * Dh + dd;
+      if (exact) {                                                     // mem + sum of deltas
+        El<T>::st(qk, t_add<T>(ok[i], ak[i]));
+        const float nv = t_add<T>(ov[i], av[i]);
+        El<T>::st(qv, nv);
+        stash[e] = nv;
+      } else {                                                         // phase-safe EMA
+        const float eta = fresh ? 1.f : t_sigmoid<T>(p.eta_logit[hh]);
+        El<T>::st(qv, t_add<T>(ov[i], t_mul<T>(eta, t_sub<T>(t_div<T>(av[i], cden), ov[i]))));
+        if (dd >= lf) {
+          const float inc = El<T>::rnd(__fmul_rn(t_div<T>(ak[i], cden), c.energy_scale));
+          const float nk = t_add<T>(ok[i], t_mul<T>(eta, t_sub<T>(inc, ok[i])));
+          El<T>::st(qk, nk);
+          stash[hh * lfd + dd - lf] = nk;
+        }
+      }
+    }
+  }
+  if (tid == 0) al[gslot] = 1;
+  __syncthreads();
+  const int nn_norm = exact ? Dh : lfd;
+  T* cachep = exact ? (T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh : (T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
+  const int Mb = exact ? Me : Ms;
+  for (int h = warp; h < Hkv; h += NW) {
+    float ss = 0.f;
+    for (int d = lane; d < nn_norm; d += 32) { const float v = stash[h * nn_norm + d]; ss += v * v; }
+    const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
+    for (int d = lane; d < nn_norm; d += 32)
+      El<T>::st(cachep + ((long long)h * Mb + slot) * nn_norm + d, t_div<T>(stash[h * nn_norm + d], den));
+  }
+}
+
+// Ring rewrite (memory_banks.py:152-177, 554-563): with the ring in chronological order the kept rows
+// [drop, fill) move down to [0, fill-drop) and block rows [bstart, blk) follow them.  One CTA per
+// (plane, K|V); 16-byte vectors when rows allow it; the in-place shift goes chunk by chunk in ascending order.
+template <typename T, typename V>
+__device__ __forceinline__ void ring_plane(T* ring, const T* src, long long src_rs, int Dh, int drop, int kept,
+                                           int bstart, int nnew, int tid, int NT) {
+  constexpr int PER = 4;
+  constexpr int EV = sizeof(V) / sizeof(T);
+  const int rowv = Dh / EV;                                            // vectors per row
+  V* rv = reinterpret_cast<V*>(ring);
+  if (drop > 0 && kept > 0) {
+    const long long n = (long long)kept * rowv, off = (long long)drop * rowv;
+    for (long long c0 = 0; c0 < n; c0 += (long long)NT * PER) {
+      V tmp[PER];
+#pragma unroll
+      for (int i = 0; i < PER; ++i) { const long long x = c0 + (long long)i * NT + tid; if (x < n) tmp[i] = rv[off + x]; }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < PER; ++i) { const long long x = c0 + (long long)i * NT + tid; if (x < n) rv[x] = tmp[i]; }
+      __syncthreads();
+    }
+  }
+  for (long long x = tid; x < (long long)nnew * rowv; x += NT) {
+    const int r = (int)(x / rowv), dv = (int)(x % rowv);
+    rv[(long long)(kept + r) * rowv + dv] = *reinterpret_cast<const V*>(src + (long long)(bstart + r) * src_rs + (long long)dv * EV);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) ring_rewrite_kernel(RouteParams p, int vec16) {
+  const coda_layer_cfg& c = p.c;
+  const int h = blockIdx.x >> 1, pass = blockIdx.x & 1, b = blockIdx.y, tid = threadIdx.x, NT = blockDim.x;
   const int W = c.W, Dh = c.Dh, Lbuf = W + c.Me + c.Ms;
   const int drop = p.n_ev < p.fill ? p.n_ev : p.fill;
   const int kept = p.fill - drop;
   const int bstart = p.n_ev > p.fill ? p.n_ev - p.fill : 0;
   const int nnew = p.blk - bstart;
-  for (int pass = 0; pass < 2; ++pass) {
-    T* ring = (T*)(pass ? p.st.v_buf : p.st.k_buf) + ((long long)b * c.Hkv + h) * Lbuf * Dh;
-    if (drop > 0 && kept > 0) {
-      const long long n = (long long)kept * Dh, off = (long long)drop * Dh;
-      for (long long c0 = 0; c0 < n; c0 += (long long)NT * RR_PER) {
-        T tmp[RR_PER];
-#pragma unroll
-        for (int i = 0; i < RR_PER; ++i) { const long long x = c0 + (long long)i * NT + tid; if (x < n) tmp[i] = ring[off + x]; }
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < RR_PER; ++i) { const long long x = c0 + (long long)i * NT + tid; if (x < n) ring[x] = tmp[i]; }
-        __syncthreads();
-      }
-    }
-    const T* src = (const T*)(pass ? p.vblk : p.kblk) + (long long)b * (pass ? p.vb_bs : p.kb_bs) + (long long)h * Dh;
-    const long long rs = pass ? p.vb_rs : p.kb_rs;
-    for (long long x = tid; x < (long long)nnew * Dh; x += NT) {
-      const int r = (int)(x / Dh), d = (int)(x % Dh);
-      ring[(long long)(kept + r) * Dh + d] = src[(long long)(bstart + r) * rs + d];
-    }
-  }
-  if (h == 0) {
+  T* ring = (T*)(pass ? p.st.v_buf : p.st.k_buf) + ((long long)b * c.Hkv + h) * Lbuf * Dh;
+  const T* src = (const T*)(pass ? p.vblk : p.kblk) + (long long)b * (pass ? p.vb_bs : p.kb_bs) + (long long)h * Dh;
+  const long long rs = pass ? p.vb_rs : p.kb_rs;
+  if (vec16) ring_plane<T, uint4>(ring, src, rs, Dh, drop, kept, bstart, nnew, tid, NT);
+  else ring_plane<T, T>(ring, src, rs, Dh, drop, kept, bstart, nnew, tid, NT);
+  if (blockIdx.x == 0) {
     float* gr = p.st.g_recent + (long long)b * W;
     uint8_t* al = p.st.allowed + (long long)b * Lbuf;
     if (drop > 0 && kept > 0) {
@@ -338,8 +503,8 @@ __global__ void __launch_bounds__(256) ring_rewrite_kernel(RouteParams p) {
 }
 
 static size_t route_scratch_bytes(const coda_layer_cfg* c) {
-  const size_t te = c->Te > 0 ? c->Te : 0, ts = c->Ts > 0 ? c->Ts : 0;
-  return (size_t)c->B * (te * 8 + ts * 4) + 64;
+  const size_t te = c->Te > 0 ? c->Te : 0, ts = c->Ts > 0 ? c->Ts : 0, ms = c->Ms;
+  return (size_t)c->B * 4 * (2 * te + ts + (2 * te + 2 * ts + 3 * ms + 1)) + 64;
 }
 
 extern "C" int64_t coda_b200_route_scratch_bytes(const coda_layer_cfg* cfg) {
@@ -352,21 +517,31 @@ static int launch_route(RouteParams& p, cudaStream_t s) {
   const coda_layer_cfg& c = p.c;
   const int HD = c.Hkv * c.Dh;
   if (p.te > 0 || p.ts > 0) {
-    const int groups = (p.te + RS_WARPS - 1) / RS_WARPS + (p.ts + RS_WARPS - 1) / RS_WARPS;
-    const size_t smem1 = sizeof(float) * (size_t)RS_WARPS * HD;
-    CODA_REQUIRE(smem1 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: Hkv*Dh = %d too large", HD);
+    const size_t smem1 = sizeof(float) * (size_t)(RS_KC * 64 + RS_KC * RS_COLS + 64 * (RS_COLS + 1) + 64 * c.Hkv + 64);
+    CODA_REQUIRE(smem1 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: %d KV heads too many for the scoring tile", c.Hkv);
     if (smem1 > 48 * 1024) cudaFuncSetAttribute(route_score_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
-    route_score_kernel<T><<<dim3(groups, c.B), RS_WARPS * 32, smem1, s>>>(p);
+    route_score_kernel<T><<<dim3(2, c.B), 256, smem1, s>>>(p);
     CODA_CHECK_LAUNCH("route_block (score)");
     const int tmax = p.te > p.ts ? p.te : p.ts;
-    const size_t smem2 = 16 * (size_t)(c.Me > 0 ? c.Me : 1) + 4 * ((size_t)HD + tmax + (p.ts > 0 ? p.ts : 1) + (c.Ms > 0 ? c.Ms : 1) +
-                         tmax + 2 * (size_t)(p.te > 0 ? p.te : 1) + (p.ts > 0 ? p.ts : 1) + c.Ms + 1 + c.Ms) + 64;
-    CODA_REQUIRE(smem2 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: commit stage needs %zu bytes of shared memory", smem2);
-    if (smem2 > 48 * 1024) cudaFuncSetAttribute(route_commit_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-    route_commit_kernel<T><<<c.B, 256, smem2, s>>>(p);
-    CODA_CHECK_LAUNCH("route_block (commit)");
+    const size_t smem2 = 32 * (size_t)(c.Me > 0 ? c.Me : 1) + 4 * ((size_t)2 * (tmax + 1) + 4 * (size_t)(p.te + 1) + 4 * (size_t)(p.ts + 1) +
+                         3 * (size_t)(c.Ms + 1) + 2) + c.Me + c.Ms + 64;
+    CODA_REQUIRE(smem2 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: decision stage needs %zu bytes of shared memory", smem2);
+    if (smem2 > 48 * 1024) cudaFuncSetAttribute(route_decide_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    route_decide_kernel<T><<<c.B, 64, smem2, s>>>(p);
+    CODA_CHECK_LAUNCH("route_block (decide)");
+    const size_t smem3 = sizeof(float) * (size_t)HD;
+    CODA_REQUIRE(smem3 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: Hkv*Dh = %d too large", HD);
+    if (smem3 > 48 * 1024) cudaFuncSetAttribute(route_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+    const int nslots = (c.Me > 0 ? p.te : 0) + (p.ts > 0 ? c.Ms : 0);
+    if (nslots > 0) {
+      route_apply_kernel<T><<<dim3(nslots, c.B), 128, smem3, s>>>(p);
+      CODA_CHECK_LAUNCH("route_block (apply)");
+    }
   }
-  ring_rewrite_kernel<T><<<dim3(c.Hkv, c.B), 256, 0, s>>>(p);
+  const int vec16 = (c.Dh * sizeof(T)) % 16 == 0 && ((uintptr_t)p.st.k_buf % 16 == 0) && ((uintptr_t)p.st.v_buf % 16 == 0) &&
+                    ((uintptr_t)p.kblk % 16 == 0) && ((uintptr_t)p.vblk % 16 == 0) && (p.kb_rs * sizeof(T)) % 16 == 0 &&
+                    (p.vb_rs * sizeof(T)) % 16 == 0 && (p.kb_bs * sizeof(T)) % 16 == 0 && (p.vb_bs * sizeof(T)) % 16 == 0;
+  ring_rewrite_kernel<T><<<dim3(2 * c.Hkv, c.B), 256, 0, s>>>(p, vec16);
   CODA_CHECK_LAUNCH("route_block (ring)");
   return CODA_OK;
 }
@@ -402,9 +577,10 @@ extern "C" int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state
     char* sp = (char*)scratch;
     p.ex_best = (float*)sp; sp += (size_t)cfg->B * te_all * 4;
     p.ex_bi = (int*)sp; sp += (size_t)cfg->B * te_all * 4;
-    p.su_idx = (int*)sp;
+    p.su_idx = (int*)sp; sp += (size_t)cfg->B * (cfg->Ts > 0 ? cfg->Ts : 0) * 4;
+    p.plan = (int*)sp;
   } else {
-    p.ex_best = nullptr; p.ex_bi = nullptr; p.su_idx = nullptr;
+    p.ex_best = nullptr; p.ex_bi = nullptr; p.su_idx = nullptr; p.plan = nullptr;
   }
   cudaStream_t s = (cudaStream_t)stream;
   return cfg->dtype == CODA_F32 ? launch_route<float>(p, s) : launch_route<bf16>(p, s);

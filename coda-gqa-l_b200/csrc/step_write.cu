@@ -2,6 +2,7 @@
 // One CTA per state.  Reads the two unit-norm routing caches once, rewrites at most one slot per bank.
 #include "coda_common.cuh"
 #include "tma_utils.cuh"
+#include "bank_score.cuh"
 
 struct StepParams {
   coda_layer_cfg c;
@@ -18,68 +19,6 @@ struct StepParams {
   int stage; int stage_off;       // byte offset of the staged caches inside dynamic shared memory
   int* status;
 };
-
-// Lane-partial dot product of a shared-memory fp32 vector with a row of n elements (no reduction):
-// each lane takes one contiguous chunk, so a row is one vector load per lane.
-template <typename T>
-__device__ __forceinline__ float lane_dot(const float* __restrict__ a, const T* __restrict__ row, int n, int lane) {
-  float part = 0.f;
-  if (sizeof(T) == 2 && n == 128) {
-    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(row) + lane * 2;
-    const float4 av = *reinterpret_cast<const float4*>(a + lane * 4);
-    const __nv_bfloat162 p0 = r2[0], p1 = r2[1];
-    part = av.x * __low2float(p0) + av.y * __high2float(p0) + av.z * __low2float(p1) + av.w * __high2float(p1);
-  } else if (sizeof(T) == 2 && n == 64) {
-    const __nv_bfloat162 p0 = reinterpret_cast<const __nv_bfloat162*>(row)[lane];
-    const float2 av = *reinterpret_cast<const float2*>(a + lane * 2);
-    part = av.x * __low2float(p0) + av.y * __high2float(p0);
-  } else {
-    for (int d = lane; d < n; d += 32) part += a[d] * El<T>::ld(row + d);
-  }
-  return part;
-}
-
-// Score of bank slot m: sum over KV heads of the (dtype-rounded) dot products of the Hkv unit vectors in
-// `hat` ([Hkv][n], shared) with rows (h, m) of `cache` ([Hkv][M][n]).  Heads are processed eight at a time:
-// the eight lane-partial sums are reduced together by a butterfly that halves the number of live values at
-// every exchange (12 shuffles per group instead of 40).  All lanes return the same value.
-template <typename T>
-__device__ __forceinline__ float slot_score(const float* __restrict__ hat, const T* __restrict__ cache,
-                                            int m, int M, int n, int Hkv, int lane) {
-  float tot = 0.f;
-  for (int h0 = 0; h0 < Hkv; h0 += 8) {
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int h = h0 + i;
-      v[i] = h < Hkv ? lane_dot<T>(hat + h * n, cache + ((long long)h * M + m) * n, n, lane) : 0.f;
-    }
-    const bool u16 = lane & 16, u8 = lane & 8, u4 = lane & 4;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float keep = u16 ? v[i + 4] : v[i], send = u16 ? v[i] : v[i + 4];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float keep = u8 ? v[i + 2] : v[i], send = u8 ? v[i] : v[i + 2];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-    }
-    {
-      const float keep = u4 ? v[1] : v[0], send = u4 ? v[0] : v[1];
-      v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
-    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
-    // lanes with the same bits 4,3,2 now hold the full dot product of head h0 + 4*b4 + 2*b3 + b2
-    float s = El<T>::rnd(v[0]);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    s += __shfl_xor_sync(0xffffffffu, s, 8);
-    s += __shfl_xor_sync(0xffffffffu, s, 16);
-    tot += s;
-  }
-  return tot;
-}
 
 // RoPE'd element d of head-row `row` (Dh values, un-rotated) given cos/sin tables of Dh/2 entries.
 template <typename T>
@@ -159,6 +98,7 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
   float* sc = khat + Hkv * lfd;   // [max(Me,Ms)] scores
   long long* s_last = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(sn + Dh / 2) + 7) & ~(uintptr_t)7);  // [Me] LRU stamps
   unsigned char* s_used = reinterpret_cast<unsigned char*>(s_last + Me);             // [Me + Ms] slot-in-use flags
+  float* dots = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(s_used + Me + Ms) + 15) & ~(uintptr_t)15);  // [max(Me,Ms)*Hkv]
   __shared__ int s_idx, s_flag;
   __shared__ float s_eta_keep;
   const size_t vbytes = (size_t)Hkv * Me * Dh * sizeof(T), kbytes = (size_t)Hkv * Ms * lfd * sizeof(T);
@@ -210,10 +150,8 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
   if (Me > 0) {
     const int Ae = c.active_exact;
     const T* vnorm = p.stage ? cacheV : (const T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh;
-    for (int m = warp; m < Me; m += NW) {
-      const float tot = slot_score<T>(vhat, vnorm, m, Me, Dh, Hkv, lane);
-      if (lane == 0) sc[m] = (m >= Ae || !s_used[m]) ? -1e9f : El<T>::rnd(tot / (float)Hkv);
-    }
+    bank_scores_one<T>(vhat, vnorm, Me, Dh, Hkv, dots, sc, tid, NT);
+    for (int m = tid; m < Me; m += NT) sc[m] = (m >= Ae || !s_used[m]) ? -1e9f : El<T>::rnd(sc[m] / (float)Hkv);
     __syncthreads();
     if (tid == 0) {
       long long* last = (long long*)p.st.mem_last_exact + (long long)b * Me;
@@ -266,10 +204,8 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
   if (Ms > 0) {
     const int As = c.active_summary;
     const T* knorm = p.stage ? cacheK : (const T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * lfd;
-    for (int m = warp; m < Ms; m += NW) {
-      const float tot = slot_score<T>(khat, knorm, m, Ms, lfd, Hkv, lane);
-      if (lane == 0) sc[m] = (m >= As) ? -1e9f : El<T>::rnd(tot / (float)Hkv);
-    }
+    bank_scores_one<T>(khat, knorm, Ms, lfd, Hkv, dots, sc, tid, NT);
+    for (int m = tid; m < Ms; m += NT) sc[m] = (m >= As) ? -1e9f : El<T>::rnd(sc[m] / (float)Hkv);
     __syncthreads();
     if (tid == 0) {
       float best = sc[0]; int bi = 0;
@@ -339,7 +275,7 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
   const int HD = cfg->Hkv * cfg->Dh, lfd = cfg->Dh - cfg->Dh / 2;
   const int mx = cfg->Me > cfg->Ms ? cfg->Me : cfg->Ms;
   size_t smem = sizeof(float) * (size_t)(3 * HD + cfg->Hkv * lfd + mx + 1 + cfg->Dh + 2) +
-                8 * (size_t)cfg->Me + (size_t)(cfg->Me + cfg->Ms) + 16;
+                8 * (size_t)cfg->Me + (size_t)(cfg->Me + cfg->Ms) + 32 + sizeof(float) * (size_t)mx * cfg->Hkv;
   const size_t es = cfg->dtype == CODA_F32 ? 4 : 2;
   const size_t vbytes = (size_t)cfg->Hkv * cfg->Me * cfg->Dh * es, kbytes = (size_t)cfg->Hkv * cfg->Ms * lfd * es;
   p.stage = 0; p.stage_off = 0; p.status = nullptr;
