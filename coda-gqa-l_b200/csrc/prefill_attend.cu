@@ -2,16 +2,16 @@
 //
 // One CTA = one (state, query head, 128-row query tile) and BOTH streams: signal Q and theta-rotated noise Q
 // share every K/V tile.  Keys are the layer's Lbuf slots (masked by `allowed`) followed by the block's own
-// tokens (causal).  Per 64-key tile:
-//     S_sig, S_noise = Q . K^T      tcgen05.mma  M=128 N=64  K=Dh     accumulators in TMEM (double-buffered)
-//     P = exp2(S - m)               softmax warps: tcgen05.ld, lazy-rescaled online softmax, bf16 P -> shared
-//     O_sig, O_noise += P . V       tcgen05.mma  M=128 N=Dh  K=64     accumulators in TMEM
-// Warp roles: warp 0 = TMA producer (cp.async.bulk.tensor, 128-byte swizzle, 2-stage K/V ring), warp 1 = MMA
-// issuer and TMEM owner, warps 2-5 = softmax / correction / epilogue of the signal stream, warps 6-9 = the same
-// for the noise stream (one thread per query row).  The two streams are independent pipelines through the tensor
-// core (own S buffers, P tile and barriers), so one stream's softmax overlaps the other's MMAs, and the MMA
-// issuer runs one tile ahead (Q.K^T of tile j+1 is in flight while tile j is in softmax).  TMEM map
-// (512 columns): S_sig[2] 0..127, S_noise[2] 128..255, O_sig 256.., O_noise 384.. (Dh columns each).
+// tokens (causal).  Per 128-key tile and stream:
+//     S = Q . K^T          tcgen05.mma  M=128 N=128 K=Dh   A, B from shared memory, S in TMEM
+//     P = exp2(S - m)      softmax warps: tcgen05.ld, lazy-rescaled online softmax, bf16 P written back over S
+//     O += P . V           tcgen05.mma  M=128 N=Dh  K=128  A = P straight from TMEM, B = V from shared memory
+// Warp roles: warp 0 = TMA producer (cp.async.bulk.tensor, 128-byte swizzle, 2-stage ring of 128-key K/V
+// tiles), warp 1 = MMA issuer and TMEM owner, warps 2-5 = softmax / correction / epilogue of the signal stream,
+// warps 6-9 = the same for the noise stream (one thread per query row).  The two streams ping-pong on the
+// tensor core: while one stream is in softmax the other's P.V and next Q.K^T run.  Keeping P in TMEM halves
+// the shared-memory operand traffic of P.V and N=128 tiles keep Q.K^T at the operand-bandwidth limit.
+// TMEM map (512 columns): S_sig 0..127 (P_sig aliases 0..63), S_noise 128..255, O_sig 256.., O_noise 256+Dh..
 // Epilogue: O/l per stream, sig - lambda*noise, optional RMSNorm over Dh, bf16 rows written in the (B, L, H*Dh)
 // layout the output projection reads.  All mbarrier waits are bounded (status word, no hang, TMEM is freed).
 #include "coda_common.cuh"
@@ -21,8 +21,9 @@
 namespace {
 
 constexpr int PF_BM = 128;       // query rows per CTA
-constexpr int PF_BN = 64;        // keys per tile
+constexpr int PF_BN = 128;       // keys per tile
 constexpr int PF_THREADS = 320;  // 10 warps
+constexpr int PF_STAGES = 2;     // K/V tiles in flight
 constexpr float PF_RESCALE_GAP = 8.0f;   // log2 units the running max may lag before O is rescaled
 
 struct PrefillParams {
@@ -59,6 +60,13 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
                "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -92,6 +100,26 @@ __device__ __forceinline__ constexpr uint32_t instr_desc(int n, bool b_mn_major)
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(PF_BM >> 4) << 24);
 }
+// 2^x for x <= 0 on the special-function unit (one MUFU op).
+__device__ __forceinline__ float ex2_mufu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x for x <= 0 on the FMA / integer pipes: x = n + f with n = floor(x) (round-down add of 1.5*2^23 leaves n
+// in the low mantissa bits), 2^f by a cubic (relative error < 1e-4, far below the bf16 rounding of P), and n
+// added straight into the exponent field.  Spreads the exponentials over two pipes: the softmax is bound by
+// the 16 MUFU results per clock an SM can produce, not by issue slots.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -127.0f);
+  float t;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.0f));
+  const float f = x - (t - 12582912.0f);
+  float r = fmaf(f, 0.077119089663028717f, 0.227564394474029541f);
+  r = fmaf(r, f, 0.695146143436431885f);
+  r = fmaf(r, f, 1.0f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ void bar_softmax_all() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -109,7 +137,6 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   constexpr int Q_BYTES = HALVES * Q_HALF;
   constexpr int KV_HALF = PF_BN * 128;
   constexpr int KV_BYTES = HALVES * KV_HALF;      // one K (or V) tile
-  constexpr int P_BYTES = PF_BM * 128;            // [128 rows][64 keys] bf16
   constexpr int KSTEPS_QK = DH / 16;
   constexpr int KSTEPS_PV = PF_BN / 16;
   constexpr uint32_t TM_SN = 128, TM_OS = 256, TM_ON = 256 + DH;   // TMEM column offsets (S_sig at 0)
@@ -118,20 +145,17 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sQs = smem;
   unsigned char* sQn = sQs + Q_BYTES;
-  unsigned char* sPs = sQn + Q_BYTES;
-  unsigned char* sPn = sPs + P_BYTES;
-  unsigned char* sK = sPn + P_BYTES;               // [2 stages][KV_BYTES]
-  unsigned char* sV = sK + 2 * KV_BYTES;           // [2 stages][KV_BYTES]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * KV_BYTES);
-  uint64_t* q_full = bars;            // 1
-  uint64_t* kv_full = bars + 1;       // 2
-  uint64_t* kv_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;        // [stream][buffer] 4
-  uint64_t* s_free = bars + 9;        // [stream][buffer] 4
-  uint64_t* p_full = bars + 13;       // [stream] 2
-  uint64_t* pv_done = bars + 15;      // [stream] 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
-  uint32_t* sMask = tmem_slot + 2;    // visibility bits of the prefix slots, 32 per word
+  unsigned char* sK = sQn + Q_BYTES;               // [PF_STAGES][KV_BYTES]
+  unsigned char* sV = sK + PF_STAGES * KV_BYTES;   // [PF_STAGES][KV_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + PF_STAGES * KV_BYTES);
+  uint64_t* q_full = bars;                          // 1
+  uint64_t* kv_full = bars + 1;                     // PF_STAGES
+  uint64_t* kv_empty = kv_full + PF_STAGES;         // PF_STAGES
+  uint64_t* s_full = kv_empty + PF_STAGES;          // [stream]
+  uint64_t* p_full = s_full + 2;                    // [stream]
+  uint64_t* pv_done = p_full + 2;                   // [stream]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint32_t* sMask = tmem_slot + 2;                  // visibility bits of the prefix slots, 32 per word
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r0 = blockIdx.x * PF_BM, h = blockIdx.y, b = blockIdx.z;
@@ -143,9 +167,8 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
 
   if (tid == 0) {
     tma::mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { tma::mbar_init(&kv_full[i], 1); tma::mbar_init(&kv_empty[i], 1); }
-    for (int i = 0; i < 4; ++i) { tma::mbar_init(&s_full[i], 1); tma::mbar_init(&s_free[i], 4); }
-    for (int i = 0; i < 2; ++i) { tma::mbar_init(&p_full[i], 4); tma::mbar_init(&pv_done[i], 1); }
+    for (int i = 0; i < PF_STAGES; ++i) { tma::mbar_init(&kv_full[i], 1); tma::mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { tma::mbar_init(&s_full[i], 1); tma::mbar_init(&p_full[i], 4); tma::mbar_init(&pv_done[i], 1); }
     tma::fence_barrier_init();
   }
   if (warp == 1) {                                   // TMEM: all 512 columns, owned by warp 1
@@ -167,8 +190,8 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         tma_load_4d(sQn + hf * Q_HALF, &qnmap, q_full, hf * 64, h, p.t0 + r0, b);
       }
       for (int j = 0; j < NT; ++j) {
-        const int st = j & 1;
-        if (j >= 2) tma::mbar_wait(&kv_empty[st], ((j >> 1) - 1) & 1, p.status, 11);
+        const int st = j % PF_STAGES;
+        if (j >= PF_STAGES) tma::mbar_wait(&kv_empty[st], ((j / PF_STAGES) - 1) & 1, p.status, 11);
         tma::mbar_expect_tx(&kv_full[st], 2 * KV_BYTES);
         unsigned char* kd = sK + st * KV_BYTES;
         unsigned char* vd = sV + st * KV_BYTES;
@@ -189,47 +212,45 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = instr_desc(PF_BN, false);
       constexpr uint32_t IDESC_PV = instr_desc(DH, true);
-      auto issue_pv = [&](int i) {
-        const int st = i & 1;
+      // S_s = Q_s . K_j^T  (the stream's S columns are free: its previous P.V, which read P from them, was
+      // issued earlier by this same thread and the tensor pipe executes in order)
+      auto issue_qk = [&](int j, int s) {
+        const uint32_t kbase = smem_u32(sK + (j % PF_STAGES) * KV_BYTES);
+        const uint32_t qbase = smem_u32(s ? sQn : sQs);
+        const uint32_t dcol = tmem + (s ? TM_SN : 0u);
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS_QK; ++kk) {
+          const uint64_t ad = smem_desc(qbase + (kk >> 2) * Q_HALF + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = smem_desc(kbase + (kk >> 2) * KV_HALF + (kk & 3) * 32, 16, 1024);
+          tc_mma(dcol, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[s]);
+      };
+      tma::mbar_wait(q_full, 0, p.status, 13);
+      tma::mbar_wait(&kv_full[0], 0, p.status, 14);
+      tc_fence_after();
+      issue_qk(0, 0);
+      issue_qk(0, 1);
+      for (int j = 0; j < NT; ++j) {
+        const int st = j % PF_STAGES;
         const uint32_t vbase = smem_u32(sV + st * KV_BYTES);
+        if (j + 1 < NT) tma::mbar_wait(&kv_full[(j + 1) % PF_STAGES], ((j + 1) / PF_STAGES) & 1, p.status, 14);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          tma::mbar_wait(&p_full[s], i & 1, p.status, 12);
+          tma::mbar_wait(&p_full[s], j & 1, p.status, 12);
           tc_fence_after();
-          const uint32_t pbase = smem_u32(s ? sPn : sPs);
+          const uint32_t pcol = tmem + (s ? TM_SN : 0u);          // P (bf16 pairs) sits in the first 64 S columns
           const uint32_t dcol = tmem + (s ? TM_ON : TM_OS);
 #pragma unroll
           for (int kk = 0; kk < KSTEPS_PV; ++kk) {
-            const uint64_t ad = smem_desc(pbase + kk * 32, 16, 1024);
             const uint64_t bd = smem_desc(vbase + kk * 2048, KV_HALF, 1024);
-            tc_mma(dcol, ad, bd, IDESC_PV, (i > 0 || kk > 0) ? 1u : 0u);
+            tc_mma_ts(dcol, pcol + kk * 8, bd, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(&pv_done[s]);
+          if (s == 1) tc_commit(&kv_empty[st]);
+          if (j + 1 < NT) issue_qk(j + 1, s);
         }
-        tc_commit(&kv_empty[st]);
-      };
-      tma::mbar_wait(q_full, 0, p.status, 13);
-      for (int j = 0; j < NT; ++j) {
-        const int sb = j & 1;
-        tma::mbar_wait(&kv_full[sb], (j >> 1) & 1, p.status, 14);
-        const uint32_t kbase = smem_u32(sK + sb * KV_BYTES);
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          if (j >= 2) tma::mbar_wait(&s_free[s * 2 + sb], ((j >> 1) - 1) & 1, p.status, 15);
-          tc_fence_after();
-          const uint32_t qbase = smem_u32(s ? sQn : sQs);
-          const uint32_t dcol = tmem + (s ? TM_SN : 0u) + sb * PF_BN;
-#pragma unroll
-          for (int kk = 0; kk < KSTEPS_QK; ++kk) {
-            const uint64_t ad = smem_desc(qbase + (kk >> 2) * Q_HALF + (kk & 3) * 32, 16, 1024);
-            const uint64_t bd = smem_desc(kbase + (kk >> 2) * KV_HALF + (kk & 3) * 32, 16, 1024);
-            tc_mma(dcol, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
-          }
-          tc_commit(&s_full[s * 2 + sb]);
-        }
-        if (j >= 1) issue_pv(j - 1);
       }
-      issue_pv(NT - 1);
     }
   } else {
     // =========================== softmax / correction / epilogue (one stream per warp group) ===========================
@@ -241,9 +262,8 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_col = lane_addr + (s ? TM_SN : 0u);
     const uint32_t o_col = lane_addr + (s ? TM_ON : TM_OS);
-    unsigned char* prow = (s ? sPn : sPs) + row * 128;
     if (s == 0) {                                         // visibility bits of the prefix slots
-      for (int w32 = sw; w32 < NP * 2; w32 += 4) {
+      for (int w32 = sw; w32 < NP * 4; w32 += 4) {
         const int c = w32 * 32 + lane;
         const bool vis = c < p.Lbuf && (!p.mask_unused || p.allowed[(long long)b * p.Lbuf + c] != 0);
         const unsigned bits = __ballot_sync(0xffffffffu, vis);
@@ -255,36 +275,44 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     float mb = -INFINITY;                                 // exponent base (lags the true max by < GAP)
     float l = 0.f;
     for (int j = 0; j < NT; ++j) {
-      const int sb = j & 1;
-      tma::mbar_wait(&s_full[s * 2 + sb], (j >> 1) & 1, p.status, 16);
+      tma::mbar_wait(&s_full[s], j & 1, p.status, 16);
       tc_fence_after();
-      uint32_t vis_lo, vis_hi;
-      if (j < NP) { vis_lo = sMask[2 * j]; vis_hi = sMask[2 * j + 1]; }
-      else {
-        const int c0 = (j - NP) * PF_BN;                  // key c0+i visible iff c0+i <= grow
-        const int nvis = grow - c0 + 1;
-        vis_lo = nvis >= 32 ? 0xffffffffu : (nvis <= 0 ? 0u : ((1u << nvis) - 1u));
-        vis_hi = nvis >= 64 ? 0xffffffffu : (nvis <= 32 ? 0u : ((1u << (nvis - 32)) - 1u));
-      }
-      uint32_t v0[32], v1[32];
-      tc_ld32(s_col + sb * PF_BN, v0);
-      tc_ld32(s_col + sb * PF_BN + 32, v1);
-      tc_wait_ld();
-      // S has been read: the MMA warp may overwrite this S buffer (tile j+2)
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) tma::mbar_arrive(&s_free[s * 2 + sb]);
-      float mx = -INFINITY;
-      if ((vis_lo & vis_hi) == 0xffffffffu) {
+      uint32_t vis[4];
+      if (j < NP) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+        for (int q4 = 0; q4 < 4; ++q4) vis[q4] = sMask[4 * j + q4];
       } else {
+        const int nvis = grow - (j - NP) * PF_BN + 1;     // key c0+i visible iff c0+i <= grow
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (!((vis_lo >> i) & 1u)) v0[i] = 0xff800000u;   // -inf
-          if (!((vis_hi >> i) & 1u)) v1[i] = 0xff800000u;
-          mx = fmaxf(mx, fmaxf(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int nq = nvis - 32 * q4;
+          vis[q4] = nq >= 32 ? 0xffffffffu : (nq <= 0 ? 0u : ((1u << nq) - 1u));
         }
+      }
+      const bool all_vis = (vis[0] & vis[1] & vis[2] & vis[3]) == 0xffffffffu;
+      // pass 1: row maximum over the 128 keys (two TMEM loads in flight at a time)
+      float mx = -INFINITY;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t v0[32], v1[32];
+        tc_ld32(s_col + hf * 64, v0);
+        tc_ld32(s_col + hf * 64 + 32, v1);
+        tc_wait_ld();
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+        if (all_vis) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            m0 = fmaxf(m0, __uint_as_float(v0[i])); m1 = fmaxf(m1, __uint_as_float(v0[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(v1[i])); m3 = fmaxf(m3, __uint_as_float(v1[i + 1]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if ((vis[2 * hf] >> i) & 1u) m0 = fmaxf(m0, __uint_as_float(v0[i]));
+            if ((vis[2 * hf + 1] >> i) & 1u) m2 = fmaxf(m2, __uint_as_float(v1[i]));
+          }
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
       }
       mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
       float alpha = 1.f;
@@ -293,25 +321,11 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         mb = mx;
         l *= alpha;
       }
-      const float nref = mb == -INFINITY ? 0.f : -mb;
-      float sum = 0.f;
-      uint32_t pk[32];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float a0 = exp2f(fmaf(__uint_as_float(v0[2 * i]), p.scale_log2, nref));
-        const float a1 = exp2f(fmaf(__uint_as_float(v0[2 * i + 1]), p.scale_log2, nref));
-        const float c0 = exp2f(fmaf(__uint_as_float(v1[2 * i]), p.scale_log2, nref));
-        const float c1 = exp2f(fmaf(__uint_as_float(v1[2 * i + 1]), p.scale_log2, nref));
-        sum += (a0 + a1) + (c0 + c1);
-        pk[i] = pack2(a0, a1);
-        pk[16 + i] = pack2(c0, c1);
-      }
-      l += sum;
-      // this stream's P tile and O accumulator are quiescent once its previous P.V has completed
-      if (j >= 1) { tma::mbar_wait(&pv_done[s], (j - 1) & 1, p.status, 17); tc_fence_after(); }
       // rescale O when some row of this warp moved its exponent base (not for the first tile: the first
-      // P.V overwrites O instead of accumulating)
+      // P.V overwrites O instead of accumulating); O must be quiescent: wait for the previous P.V
       if (__any_sync(0xffffffffu, (alpha != 1.f) && j > 0)) {
+        tma::mbar_wait(&pv_done[s], (j - 1) & 1, p.status, 19);
+        tc_fence_after();
 #pragma unroll
         for (int c = 0; c < DH / 32; ++c) {
           uint32_t o[32];
@@ -321,13 +335,45 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
           tc_st32(o_col + c * 32, o);
         }
-        tc_wait_st();
       }
-      // P row -> shared, K-major 128-byte-swizzled tile ([row][64 keys])
+      // pass 2: probabilities, written back over S as packed bf16 (key 2i, 2i+1 -> column i)
+      const float nref = mb == -INFINITY ? 0.f : -mb;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t v0[32], v1[32], pk[32];
+        tc_ld32(s_col + hf * 64, v0);
+        tc_ld32(s_col + hf * 64 + 32, v1);
+        tc_wait_ld();
+        if (!all_vis) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (!((vis[2 * hf] >> i) & 1u)) v0[i] = 0xff800000u;     // -inf
+            if (!((vis[2 * hf + 1] >> i) & 1u)) v1[i] = 0xff800000u;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {            // half of the exponentials on MUFU, half on the FMA pipe
+          const float a0 = ex2_mufu(fmaf(__uint_as_float(v0[2 * i]), p.scale_log2, nref));
+          const float a1 = ex2_poly(fmaf(__uint_as_float(v0[2 * i + 1]), p.scale_log2, nref));
+          const float c0 = ex2_mufu(fmaf(__uint_as_float(v1[2 * i]), p.scale_log2, nref));
+          const float c1 = ex2_poly(fmaf(__uint_as_float(v1[2 * i + 1]), p.scale_log2, nref));
+          if (i & 1) { sum1 += a0 + a1; sum3 += c0 + c1; } else { sum0 += a0 + a1; sum2 += c0 + c1; }
+          pk[i] = pack2(a0, a1);
+          pk[16 + i] = pack2(c0, c1);
+        }
+        // the second half's S columns (64..127) are read before the first half's P (columns 0..31) is
+        // written only when hf == 0 has been fully loaded: keep the order load(hf) -> store(hf)
+        if (hf == 0) {
+          // columns 0..31 hold keys 0..63 of P; S columns 0..63 were read above, 64..127 are read next and
+          // are not touched by this store
+          tc_st32(s_col, pk);
+        } else {
+          tc_st32(s_col + 32, pk);
+        }
+      }
+      l += (sum0 + sum1) + (sum2 + sum3);
+      tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) tma::mbar_arrive(&p_full[s]);
@@ -338,8 +384,11 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     tc_fence_after();
     const bool valid = grow < p.blk;
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    constexpr int CHUNKS = DH / 8;                         // 16-byte chunks per exchanged row
-    unsigned char* xrow = sQn + row * (DH * 2);            // the query tiles are dead once every Q.K^T has completed
+    // The query tiles are dead once every Q.K^T has completed: their 2*Q_BYTES of shared memory carry the
+    // noise rows (fp32, 16-byte chunks XOR-swizzled by row) over to the signal threads.  The arithmetic is
+    // fp32 end to end with a single rounding of the result (conversions run at a quarter of the FMA rate).
+    constexpr int CHUNKS = DH / 4;                         // 16-byte chunks per exchanged fp32 row
+    unsigned char* xrow = sQs + row * (DH * 4);
     if (s == 1) {
       // all MMAs of both streams are complete when the noise stream's last P.V is (it is issued last)
 #pragma unroll
@@ -348,13 +397,11 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         tc_ld32(o_col + c * 32, o);
         tc_wait_ld();
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            w[e] = pack2(__uint_as_float(o[q4 * 8 + 2 * e]) * inv, __uint_as_float(o[q4 * 8 + 2 * e + 1]) * inv);
-          const int ch = c * 4 + q4;
-          *reinterpret_cast<uint4*>(xrow + ((ch ^ (row & (CHUNKS - 1))) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int q8 = 0; q8 < 8; ++q8) {
+          const int ch = c * 8 + q8;
+          *reinterpret_cast<float4*>(xrow + ((ch ^ (row & (CHUNKS - 1))) << 4)) =
+              make_float4(__uint_as_float(o[q8 * 4]) * inv, __uint_as_float(o[q8 * 4 + 1]) * inv,
+                          __uint_as_float(o[q8 * 4 + 2]) * inv, __uint_as_float(o[q8 * 4 + 3]) * inv);
         }
       }
       tc_fence_before();
@@ -363,7 +410,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       float lam = 0.f;
       if (valid) lam = bf16_round(p.lam[(long long)b * p.lam_bs + (long long)(p.t0 + grow) * p.lam_rs + h]);
       bar_softmax_all();                                   // noise rows are in shared memory
-      uint32_t dpk[DH / 2];                                // packed bf16 differences of the row
+      float dv[DH];                                        // sig - lam * noise of the row
       float sq = 0.f;
 #pragma unroll
       for (int c = 0; c < DH / 32; ++c) {
@@ -371,38 +418,35 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         tc_ld32(o_col + c * 32, o);
         tc_wait_ld();
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int ch = c * 4 + q4;
-          const uint4 nz = *reinterpret_cast<const uint4*>(xrow + ((ch ^ (row & (CHUNKS - 1))) << 4));
-          const uint32_t nw[4] = {nz.x, nz.y, nz.z, nz.w};
+        for (int q8 = 0; q8 < 8; ++q8) {
+          const int ch = c * 8 + q8;
+          const float4 nz = *reinterpret_cast<const float4*>(xrow + ((ch ^ (row & (CHUNKS - 1))) << 4));
+          const float nn[4] = {nz.x, nz.y, nz.z, nz.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const __nv_bfloat162 nv = *reinterpret_cast<const __nv_bfloat162*>(&nw[e]);
-            const float vs0 = bf16_round(__uint_as_float(o[q4 * 8 + 2 * e]) * inv);
-            const float vs1 = bf16_round(__uint_as_float(o[q4 * 8 + 2 * e + 1]) * inv);
-            const float d0 = t_sub<bf16>(vs0, t_mul<bf16>(lam, __low2float(nv)));
-            const float d1 = t_sub<bf16>(vs1, t_mul<bf16>(lam, __high2float(nv)));
-            sq += bf16_round(d0 * d0) + bf16_round(d1 * d1);
-            dpk[c * 16 + q4 * 4 + e] = pack2(d0, d1);
+            const float d = fmaf(-lam, nn[e], __uint_as_float(o[q8 * 4 + e]) * inv);
+            sq = fmaf(d, d, sq);
+            dv[c * 32 + q8 * 4 + e] = d;
           }
         }
       }
       if (valid) {
         bf16* op = p.out + (long long)b * p.out_bs + (long long)(p.t0 + grow) * p.out_rs + (long long)h * DH;
-        if (p.norm_full) {
-          const float var = bf16_round(sq / (float)DH);
-          const float rs = bf16_round(rsqrtf(bf16_round(var + p.eps)));
+        const float rs = p.norm_full ? rsqrtf(sq / (float)DH + p.eps) : 1.f;
 #pragma unroll
-          for (int i = 0; i < DH / 2; ++i) {
-            const __nv_bfloat162 dv = *reinterpret_cast<__nv_bfloat162*>(&dpk[i]);
-            const __nv_bfloat162 wv = reinterpret_cast<const __nv_bfloat162*>(p.norm_w)[i];
-            dpk[i] = pack2(t_mul<bf16>(t_mul<bf16>(__low2float(dv), rs), __low2float(wv)),
-                           t_mul<bf16>(t_mul<bf16>(__high2float(dv), rs), __high2float(wv)));
+        for (int i = 0; i < DH / 8; ++i) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float y0 = dv[8 * i + 2 * e] * rs, y1 = dv[8 * i + 2 * e + 1] * rs;
+            if (p.norm_full) {
+              const __nv_bfloat162 wv = reinterpret_cast<const __nv_bfloat162*>(p.norm_w)[4 * i + e];
+              y0 *= __low2float(wv); y1 *= __high2float(wv);
+            }
+            w[e] = pack2(y0, y1);
           }
+          reinterpret_cast<uint4*>(op)[i] = make_uint4(w[0], w[1], w[2], w[3]);
         }
-#pragma unroll
-        for (int i = 0; i < DH / 8; ++i)
-          reinterpret_cast<uint4*>(op)[i] = make_uint4(dpk[4 * i], dpk[4 * i + 1], dpk[4 * i + 2], dpk[4 * i + 3]);
       }
       tc_fence_before();
     }
@@ -418,8 +462,8 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
 template <int DH>
 size_t prefill_smem(int Lbuf) {
   const int NP = (Lbuf + PF_BN - 1) / PF_BN;
-  return (size_t)2 * (DH / 64) * PF_BM * 128 + 2 * PF_BM * 128 + 4 * (size_t)(DH / 64) * PF_BN * 128 + 17 * 8 + 8 +
-         (size_t)NP * 2 * 4 + 1024 + 64;
+  return (size_t)2 * (DH / 64) * PF_BM * 128 + 2 * PF_STAGES * (size_t)(DH / 64) * PF_BN * 128 +
+         (7 + 2 * PF_STAGES) * 8 + 8 + (size_t)NP * 4 * 4 + 1024 + 64;
 }
 
 template <int DH>
