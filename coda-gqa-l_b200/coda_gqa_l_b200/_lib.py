@@ -61,12 +61,16 @@ def _load() -> C.CDLL:
     lib.coda_b200_route_scratch_bytes.restype = i64
     lib.coda_b200_route_block.argtypes = [cfgp, stp, i32, i32, i64, vp, i64, i64, vp, i64, i64,
                                           fp, i64, i64, vp, i64, fp, vp, vp]
+    lib.coda_b200_route_static_scratch_bytes.argtypes = []
+    lib.coda_b200_route_static_scratch_bytes.restype = i64
+    lib.coda_b200_route_block_noalloc.argtypes = [cfgp, stp, i32, i32, i64, vp, i64, i64, vp, i64, i64,
+                                                  fp, i64, i64, vp, i64, fp, vp]
     lib.coda_b200_advance_steps.argtypes = [vp, i64, vp]
     lib.coda_b200_host_topk_f32.argtypes = [vp, i32, i32, i32, i32, vp]
     lib.coda_b200_host_topk_i64.argtypes = [vp, i32, i32, i32, i32, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name not in ("coda_b200_last_error", "coda_b200_route_scratch_bytes"):
+        if name not in ("coda_b200_last_error", "coda_b200_route_scratch_bytes", "coda_b200_route_static_scratch_bytes"):
             fn.restype = C.c_int
     return lib
 
@@ -76,7 +80,8 @@ EXPORTS = (
     "coda_b200_step_write_raw", "coda_b200_decode_attend_supported", "coda_b200_decode_attend",
     "coda_b200_prefill_attend_supported", "coda_b200_prefill_attend",
     "coda_b200_attend", "coda_b200_select_candidates", "coda_b200_route_scratch_bytes",
-    "coda_b200_route_block", "coda_b200_advance_steps", "coda_b200_host_topk_f32",
+    "coda_b200_route_block", "coda_b200_route_static_scratch_bytes", "coda_b200_route_block_noalloc",
+    "coda_b200_advance_steps", "coda_b200_host_topk_f32",
     "coda_b200_host_topk_i64",
 )
 

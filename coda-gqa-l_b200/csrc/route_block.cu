@@ -11,6 +11,7 @@
 #include "topk_order.h"
 #include "tma_utils.cuh"
 #include "bank_score.cuh"
+#include <mutex>
 
 struct RouteParams {
   coda_layer_cfg c;
@@ -544,6 +545,58 @@ static int launch_route(RouteParams& p, cudaStream_t s) {
   ring_rewrite_kernel<T><<<dim3(2 * c.Hkv, c.B), 256, 0, s>>>(p, vec16);
   CODA_CHECK_LAUNCH("route_block (ring)");
   return CODA_OK;
+}
+
+// ---- allocation-free variant -------------------------------------------------------------------------------
+// Scratch for callers that are not allowed to allocate device memory: a fixed array in the library's own
+// device image.  Every GPU that loads the library carries these bytes until the process exits.
+constexpr size_t CODA_STATIC_SCRATCH_BYTES = 1u << 20;
+static __device__ __align__(256) unsigned char g_route_scratch[CODA_STATIC_SCRATCH_BYTES];
+
+extern "C" int64_t coda_b200_route_static_scratch_bytes(void) { return (int64_t)CODA_STATIC_SCRATCH_BYTES; }
+
+// In host code `g_route_scratch` is only a handle for the symbol, not a device address; the address is looked
+// up once per device (with that device current) and remembered.
+static void* static_scratch_for_current_device() {
+  constexpr int MAX_DEV = 64;
+  static void* ptrs[MAX_DEV] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_route_scratch) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    ptrs[dev] = ptr;
+  }
+  return ptrs[dev];
+}
+
+extern "C" int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                                     int32_t ring_fill, int32_t blk, int64_t pos0,
+                                     const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                                     const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                                     const float* gates, int64_t gates_bs, int64_t gate_ev0,
+                                     const int32_t* cand, int64_t cand_bs,
+                                     const float* eta_logit, void* scratch, coda_stream_t stream);
+
+extern "C" int coda_b200_route_block_noalloc(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                                             int32_t ring_fill, int32_t blk, int64_t pos0,
+                                             const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                                             const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                                             const float* gates, int64_t gates_bs, int64_t gate_ev0,
+                                             const int32_t* cand, int64_t cand_bs,
+                                             const float* eta_logit, coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg), CODA_ERR_ARG, "route_block_noalloc: invalid layer configuration");
+  const size_t need = route_scratch_bytes(cfg);
+  CODA_REQUIRE(need <= CODA_STATIC_SCRATCH_BYTES, CODA_ERR_LIMIT,
+               "route_block_noalloc: this configuration needs %zu bytes of scratch, the built-in buffer holds %zu "
+               "(fewer states per call, or use coda_b200_route_block with caller-provided scratch)",
+               need, CODA_STATIC_SCRATCH_BYTES);
+  void* scratch = static_scratch_for_current_device();
+  CODA_REQUIRE(scratch != nullptr, CODA_ERR_LAUNCH, "route_block_noalloc: cudaGetSymbolAddress failed for the built-in scratch");
+  return coda_b200_route_block(cfg, st, ring_fill, blk, pos0, k_blk, kb_bs, kb_rs, v_blk, vb_bs, vb_rs,
+                               gates, gates_bs, gate_ev0, cand, cand_bs, eta_logit, scratch, stream);
 }
 
 extern "C" int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state_ptrs* st,

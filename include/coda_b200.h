@@ -204,6 +204,27 @@ int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
                           const int32_t* cand, int64_t cand_bs,
                           const float* eta_logit, void* scratch, coda_stream_t stream);
 
+/* coda_b200_route_block for callers that may not allocate device memory -- code running where cudaMalloc is
+ * forbidden or unavailable: inside a serving engine whose memory pool is frozen after start-up, under a
+ * framework that owns all allocations, or in a latency-critical loop where an allocation could stall.  It has no
+ * counterpart in the reference (which allocates freely through PyTorch).  The per-state plan and score scratch
+ * lives in a fixed array inside the library's device image; coda_b200_route_static_scratch_bytes() (1 MiB)
+ * is its size, and a configuration whose coda_b200_route_scratch_bytes() exceeds it is rejected with
+ * CODA_ERR_LIMIT (at the 7B shape that is reached beyond ~600 states per call).  Every GPU that loads the
+ * library carries the array until the process exits.  The first call on a device looks up the array's address
+ * (cudaGetSymbolAddress, with that device current): make that first call outside any stream capture.  All
+ * calls on a device share the one array: the kernels overwrite every word they later read, so nothing has to be
+ * cleared between calls, but two calls that overlap on the GPU (different streams) race on it.  Inputs and
+ * outputs are the caller's, exactly as for coda_b200_route_block; no allocation happens on any path. */
+int64_t coda_b200_route_static_scratch_bytes(void);
+int coda_b200_route_block_noalloc(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                                  int32_t ring_fill, int32_t blk, int64_t pos0,
+                                  const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                                  const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                                  const float* gates, int64_t gates_bs, int64_t gate_ev0,
+                                  const int32_t* cand, int64_t cand_bs,
+                                  const float* eta_logit, coda_stream_t stream);
+
 /* Adds `n` to the int64 step counter that coda_ring_pos.step_dev points to (one thread). */
 int coda_b200_advance_steps(int64_t* step_dev, int64_t n, coda_stream_t stream);
 
