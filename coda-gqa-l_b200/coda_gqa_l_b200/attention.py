@@ -439,20 +439,21 @@ class CoDAGQALandmarkPerf2(nn.Module):
             _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(), eta.data_ptr(), s),
             "coda_b200_step_write_raw")
         out = torch.empty((B, 1, self.num_heads * self.head_dim), device=dev, dtype=dt)
-        timers = self.kernel_timers
-        if timers is not None:
-            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            ev0.record()
-        check(lib.coda_b200_decode_attend(
-            C.byref(cfg), C.byref(ptrs), rp, 0, q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0),
-            inv_freq.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), _p(nw), out.data_ptr(), out.stride(0),
-            self._status_word(dev).data_ptr(), s), "coda_b200_decode_attend")
-        if timers is not None:
-            ev1.record()
-            timers.append((1, ev0, ev1))
+        self.decode_attend_launch(cfg, state, rp, 0, q, lam_logit, out)
         if host_update:
             self.advance_host_scalars(state)
         return self.o_proj(out)
+
+    def decode_attend_launch(self, cfg, state, rp: RingPos, token_already_written: int, q, lam_logit, out) -> None:
+        """One launch of the fused decode attention kernel: raw query projection ``q`` [B, H*Dh] and lambda
+        logits [B, H] in, head-normalised differential attention [B, 1, H*Dh] out.  No other work."""
+        inv_freq, cos_t, sin_t, _, nw = self._consts(q.device, q.dtype)
+        ptrs = self._ptrs(state)
+        check(lib.coda_b200_decode_attend(
+            C.byref(cfg), C.byref(ptrs), rp, token_already_written, q.data_ptr(), q.stride(0),
+            lam_logit.data_ptr(), lam_logit.stride(0), inv_freq.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
+            _p(nw), out.data_ptr(), out.stride(0), self._status_word(q.device).data_ptr(), _stream()),
+            "coda_b200_decode_attend")
 
     def step_graphable(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos) -> torch.Tensor:
         """The default ``step`` (write, then attend) with no host-side branching on the state, so that it

@@ -2,15 +2,18 @@
 //
 // Persistent kernel: one CTA per SM, each walking over (state, KV head) planes plane = blockIdx.x, + gridDim.x, ...
 // The K and V planes of a head -- all W+Me+Ms slots -- are read from HBM exactly once, by TMA
-// (cp.async.bulk.tensor, 128-byte swizzle) into a 4-stage ring of 64-slot tiles in shared memory.  The producer
-// warp streams tiles continuously ACROSS plane boundaries, so the ring never drains between work items and
-// HBM stays busy while the consumers merge / write one plane and prepare the queries of the next (whose
-// inputs are prefetched into registers one plane ahead).  Two groups of four consumer warps take alternate
-// tiles; inside a group each warp owns 16 slots of the tile.  All query heads of the GQA group and both streams (signal and
-// theta-rotated noise) share the staged tiles: they form the 16 rows of the m16n8k16 tensor-core tiles used
-// for Q.K^T and P.V.  Per plane the prologue applies RoPE and the learned per-head rotation to the raw query
-// projection and evaluates the lambda sigmoid; softmax is an online, per-warp one (quad shuffles), merged
-// across the eight warps at the end; the epilogue subtracts lambda * noise and applies the head RMSNorm.
+// (cp.async.bulk.tensor, 128-byte swizzle) into a ring of 64-slot tiles in shared memory.  Three roles:
+//   * one producer warp streams tiles continuously ACROSS plane boundaries, so the ring never drains between
+//     work items;
+//   * eight consumer warps (two groups of four taking alternate tiles; inside a group each warp owns 16 slots
+//     of the tile) do nothing but tensor-core work: all query heads of the GQA group and both streams (signal
+//     and theta-rotated noise) share the staged tiles as the 16 rows of the m16n8k16 tiles used for Q.K^T and
+//     P.V, with an online per-warp softmax (quad shuffles);
+//   * four auxiliary warps prepare the queries of the NEXT plane (RoPE, learned per-head rotation, lambda
+//     sigmoid, visibility mask; double-buffered) and finish the PREVIOUS one (merge of the eight partial
+//     softmaxes, signal - lambda * noise, head RMSNorm, store) while the consumers are already on the next
+//     plane's tiles.
+// The roles meet only through mbarriers in shared memory.
 //
 // HBM traffic per plane = the two planes (2 * Lbuf * Dh * 2 bytes) + a few hundred bytes of q, lambda, mask
 // and output: the kernel is bandwidth-bound by construction.  Every mbarrier wait is bounded; on expiry a
@@ -22,12 +25,13 @@
 namespace {
 
 constexpr int DA_TILE = 64;          // slots per stage
-constexpr int DA_STAGES = 4;
+constexpr int DA_MAX_STAGES = 8;
 constexpr int DA_CWARPS = 8;         // consumer warps (two groups of four)
-constexpr int DA_THREADS = (DA_CWARPS + 1) * 32;
+constexpr int DA_AWARPS = 4;         // auxiliary warps (query preparation, merge + epilogue)
+constexpr int DA_THREADS = (DA_CWARPS + DA_AWARPS + 4) * 32;   // the producer's warpgroup has one working warp
 
 struct DecodeParams {
-  int B, H, Hkv, G, Lbuf, mask_unused, norm_full, interleaved, angle_bf16;
+  int B, H, Hkv, G, Lbuf, mask_unused, norm_full, interleaved, angle_bf16, stages;
   float eps, scale_log2;
   coda_ring_pos rp; int W; int pos_minus_one;     // query position = ring position (- 1 when the token was written first)
   const bf16* q; long long q_bs;                  // raw query projection [B][H*Dh]
@@ -58,11 +62,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(DA_CWARPS * 32) : "memory"); }
+__device__ __forceinline__ void bar_aux() { asm volatile("bar.sync 2, %0;" ::"n"(DA_AWARPS * 32) : "memory"); }
 
 // Byte offset of 16-byte chunk `c` of row `s` inside a [64 x DH] bf16 tile written by TMA as DH/64
 // boxes of 64 rows x 128 bytes with the 128-byte swizzle (chunk index XOR row mod 8).
@@ -71,48 +80,142 @@ __device__ __forceinline__ uint32_t tile_off(int s, int c) {
   return (uint32_t)((c >> 3) * (DA_TILE * 128) + s * 128 + (((c & 7) ^ (s & 7)) << 4));
 }
 
+// Shared-memory carve-up, the same on host and device.  RL = live query rows (2 * G).
 template <int DH>
+struct DecodeSmem {
+  static constexpr int TILE_BYTES = DA_TILE * DH * 2;
+  static constexpr int QSTR = DH + 8;               // padded row stride of the staged queries (elements)
+  int comb, sq, sml, slam, scs, bars, sal, total;
+  __host__ __device__ DecodeSmem(int stages, int G, int nst) {
+    int o = stages * 2 * TILE_BYTES;
+    comb = o; o += DA_CWARPS * 2 * G * DH * 4;      // [DA_CWARPS][2G][DH] partial outputs
+    sq = o;   o += 2 * 16 * QSTR * 2;               // [2][16][QSTR] staged queries (double-buffered)
+    sml = o;  o += 2 * DA_CWARPS * 16 * 4;          // [2][DA_CWARPS][16]  (m, l)
+    slam = o; o += 2 * 8 * 4;                       // [2][8] lambda
+    scs = o;  o += DH * 4;                          // [DH/2] cos, [DH/2] sin
+    bars = o; o += (2 * DA_MAX_STAGES + 4) * 8;     // full[], empty[], q_ready[2], comb_full, comb_free
+    sal = o;  o += 2 * nst * DA_TILE;               // [2][nst * DA_TILE] visibility mask
+    total = o;
+  }
+};
+
+template <int DH, int NQ>
 __global__ void __launch_bounds__(DA_THREADS, 1)
 decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
   constexpr int HALF = DH / 2;
   constexpr int KSTEPS = DH / 16;            // k-steps of Q.K^T
-  constexpr int NT_O = DH / 8;               // n-tiles of the output
+  constexpr int MT_O = DH / 16;              // m-tiles of the (transposed) output
   constexpr int TILE_BYTES = DA_TILE * DH * 2;
-  constexpr int QSTR = DH + 8;               // padded row stride of the staged queries (elements)
-  constexpr int CT = DA_CWARPS * 32;         // consumer threads
+  constexpr int QSTR = DH + 8;
+  constexpr int AT = DA_AWARPS * 32;         // auxiliary threads
 
   extern __shared__ unsigned char smem_raw[];
   // the swizzled TMA tiles need a 1024-byte aligned base; the launch reserves the slack
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* stage0 = smem;                                            // DA_STAGES * 2 * TILE_BYTES
-  float* comb = reinterpret_cast<float*>(smem + DA_STAGES * 2 * TILE_BYTES);   // [DA_CWARPS][16][DH] partial outputs
-  bf16* sQ = reinterpret_cast<bf16*>(comb + DA_CWARPS * 16 * DH);          // [16][QSTR]
-  float* sML = reinterpret_cast<float*>(sQ + 16 * QSTR);                   // [2][DA_CWARPS][16]  (m, l)
-  float* sLam = sML + 2 * DA_CWARPS * 16;                                  // [8]
-  float* sCS = sLam + 8;                                                   // [HALF] cos, [HALF] sin
-  uint64_t* full = reinterpret_cast<uint64_t*>(sCS + 2 * HALF);            // [DA_STAGES]
-  uint64_t* empty = full + DA_STAGES;                                      // [DA_STAGES]
-  uint8_t* sAl = reinterpret_cast<uint8_t*>(empty + DA_STAGES);            // [Lbuf rounded up to a tile]
-
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int G = p.G;
+  const int G = p.G, RL = 2 * G, S = p.stages;
   const int nst = (p.Lbuf + DA_TILE - 1) / DA_TILE;
   const int nplanes = p.B * p.Hkv;
+  const DecodeSmem<DH> L(S, G, nst);
+  unsigned char* stage0 = smem;
+  float* comb = reinterpret_cast<float*>(smem + L.comb);
+  bf16* sQ = reinterpret_cast<bf16*>(smem + L.sq);
+  float* sML = reinterpret_cast<float*>(smem + L.sml);
+  float* sLam = reinterpret_cast<float*>(smem + L.slam);
+  float* sCS = reinterpret_cast<float*>(smem + L.scs);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* empty = full + DA_MAX_STAGES;
+  uint64_t* q_ready = empty + DA_MAX_STAGES;       // [2]
+  uint64_t* comb_full = q_ready + 2;
+  uint64_t* comb_free = comb_full + 1;
+  uint8_t* sAl = smem + L.sal;
+  const int al_stride = nst * DA_TILE;
+
+  // ---- auxiliary warps: first requests, issued before the producer starts to fill the ring ----
+  const bool is_aux = warp >= DA_CWARPS && warp < DA_CWARPS + DA_AWARPS;
+  const int at = tid - DA_CWARPS * 32, aw = warp - DA_CWARPS;
+  // Global loads of these warps queue behind the tile traffic of the whole chip (a few thousand cycles when
+  // the ring is being filled), so every input of a plane is requested in ONE batch into registers
+  // (fetch), long before it is consumed (stage).  Item (g, i): RoPE'd elements 2i and 2i+1 of head g
+  // (signal row g) and their learned (even, odd) rotation by theta (noise row G + g).
+  constexpr int ITEMS = (8 * HALF + AT - 1) / AT;        // G <= 8
+  constexpr int ALW = (4096 / 4 + AT - 1) / AT;          // mask words per thread (Lbuf <= 4096)
+  struct Inputs { uint32_t q0[ITEMS], q1[ITEMS], al[ALW]; bf16 ct[ITEMS], st[ITEMS]; float lam; };
+  // Two sets: set (k % 2) holds the inputs of this CTA's k-th plane.  A request stands behind everything the
+  // producer has in flight for this SM (a full ring: several microseconds at this SM's share of the HBM
+  // bandwidth), so it is made two planes ahead.
+  Inputs inA, inB;
+  auto fetch = [&](int plane, Inputs& in) {
+    const int b = plane / p.Hkv, hk = plane % p.Hkv;
+    const bf16* qrow = p.q + (long long)b * p.q_bs + (long long)hk * G * DH;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int w = at + it * AT;
+      in.q0[it] = in.q1[it] = 0u;
+      in.ct[it] = in.st[it] = __float2bfloat16_rn(0.f);
+      if (w < G * HALF) {
+        const int g = w / HALF, i = w % HALF;
+        const bf16* qh = qrow + g * DH;
+        if (p.interleaved) {
+          in.q0[it] = *reinterpret_cast<const uint32_t*>(qh + 2 * i);
+        } else {
+          const int pi = 2 * i < HALF ? 2 * i : 2 * i - HALF;        // pair index of element 2i (2i+1: the next)
+          in.q0[it] = *reinterpret_cast<const uint32_t*>(qh + pi);
+          in.q1[it] = *reinterpret_cast<const uint32_t*>(qh + pi + HALF);
+        }
+        in.ct[it] = p.cos_t[(hk * G + g) * HALF + i];
+        in.st[it] = p.sin_t[(hk * G + g) * HALF + i];
+      }
+    }
+    in.lam = 0.f;
+    if (at < G) in.lam = __bfloat162float(p.lam_logit[(long long)b * p.lam_bs + hk * G + at]);
+    const uint8_t* alb = p.allowed + (long long)b * p.Lbuf;
+    const bool al4 = (reinterpret_cast<uintptr_t>(alb) & 3) == 0;
+#pragma unroll
+    for (int a = 0; a < ALW; ++a) {
+      const int i0 = (at + a * AT) * 4;
+      uint32_t wv = 0;
+      if (i0 < p.Lbuf) {
+        if (al4 && i0 + 3 < p.Lbuf) wv = *reinterpret_cast<const uint32_t*>(alb + i0);
+        else for (int e = 0; e < 4; ++e) if (i0 + e < p.Lbuf) wv |= (uint32_t)alb[i0 + e] << (8 * e);
+      }
+      in.al[a] = wv;
+    }
+  };
+  constexpr int DV = 4;                                  // output dims per lane in the epilogue: 4*lane .. 4*lane+3
+  const bool dact = 4 * lane < DH;                       // (head_dim 64: the upper half-warp idles there)
+  float nw[DV], inv_pre = 0.f;
+  long long steps_pre = 0;
+  if (is_aux) {
+    if ((int)blockIdx.x < nplanes) fetch(blockIdx.x, inA);
+    if ((int)(blockIdx.x + gridDim.x) < nplanes) fetch(blockIdx.x + gridDim.x, inB);
+    if (at < HALF) inv_pre = p.inv_freq[at];
+    if (p.rp.step_dev != nullptr) steps_pre = *p.rp.step_dev;
+#pragma unroll
+    for (int k = 0; k < DV; ++k) nw[k] = (p.norm_full && dact) ? __bfloat162float(p.norm_w[4 * lane + k]) : 1.f;
+  }
 
   if (tid == 0) {
-    for (int i = 0; i < DA_STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
+    for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
+    mbar_init(&q_ready[0], DA_AWARPS); mbar_init(&q_ready[1], DA_AWARPS);
+    mbar_init(comb_full, DA_CWARPS); mbar_init(comb_free, DA_AWARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // The producer starts only here, after the auxiliary warps have made their first requests: whatever is
+  // requested later (instruction and constant fetches included) stands behind a ring's worth of tile traffic.
   __syncthreads();
 
-  if (warp == DA_CWARPS) {
+  // Registers follow the roles (per warpgroup): the consumers hold the output accumulators and the query
+  // fragments, the other warps need little.
+  if (warp >= DA_CWARPS + DA_AWARPS) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp > DA_CWARPS + DA_AWARPS) return;
     // ---------------- producer: keep the ring of K/V tiles full, across plane boundaries ----------------
     if (lane == 0) {
-      int t = 0;                                           // tiles issued by this CTA so far (all planes)
+      int bi = 0, round = 0;                               // ring slot and how often the ring has wrapped
       for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x) {
-        for (int s = 0; s < nst; ++s, ++t) {
-          const int bi = t % DA_STAGES;
-          if (t >= DA_STAGES) mbar_wait(&empty[bi], ((t / DA_STAGES) - 1) & 1, p.status, 1);
+        for (int s = 0; s < nst; ++s) {
+          if (round > 0) mbar_wait(&empty[bi], (round - 1) & 1, p.status, 1);
           mbar_expect_tx(&full[bi], 2 * TILE_BYTES);
           unsigned char* kd = stage0 + bi * 2 * TILE_BYTES;
           unsigned char* vd = kd + TILE_BYTES;
@@ -121,281 +224,305 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
             tma_load_3d(kd + hf * (DA_TILE * 128), &kmap, &full[bi], hf * 64, s * DA_TILE, plane);
             tma_load_3d(vd + hf * (DA_TILE * 128), &vmap, &full[bi], hf * 64, s * DA_TILE, plane);
           }
+          if (++bi == S) { bi = 0; ++round; }
         }
       }
     }
     return;
   }
 
-  // ---------------- consumers: two groups of four warps, each taking every other tile ----------------
-  const int grp = warp >> 2, gw = warp & 3;            // group, warp inside the group (owns slots gw*16..+15 of a tile)
-  // RoPE cos/sin of the query position: the same for every plane
-  const long long qpos = ring_now(p.rp, p.W).pos - p.pos_minus_one;
-  for (int i = tid; i < HALF; i += CT) {
-    float ta = (float)qpos, inv = p.inv_freq[i];
-    if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
-    float ang = __fmul_rn(ta, inv);
-    if (p.angle_bf16) ang = bf16_round(ang);
-    float c = cosf(ang), s = sinf(ang);
-    if (p.angle_bf16) { c = bf16_round(c); s = bf16_round(s); }
-    sCS[i] = bf16_round(c);
-    sCS[HALF + i] = bf16_round(s);
-  }
-  for (int i = tid; i < 16 * QSTR; i += CT) sQ[i] = __float2bfloat16_rn(0.f);   // rows >= 2G stay zero
-
-  // Per-plane inputs are fetched one plane ahead into registers, so that only the first plane's prologue
-  // waits on global memory.  Work split of the G*HALF (head, pair) items: item w = tid, tid + CT, ...
-  constexpr int ITEMS = (8 * HALF + CT - 1) / CT;      // G <= 8
-  constexpr int ALW = (4096 / CT + 3) / 4;             // allowed mask words per thread (Lbuf <= 4096)
-  float pre_qa[ITEMS], pre_qb[ITEMS], pre_ct[ITEMS], pre_st[ITEMS], pre_lam = 0.f;
-  uint32_t pre_al[ALW];
-  auto prefetch = [&](int plane) {
-    const int b = plane / p.Hkv, hk = plane % p.Hkv;
-    const bf16* qrow = p.q + (long long)b * p.q_bs + (long long)hk * G * DH;
+  if (warp >= DA_CWARPS) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    // ---------------- auxiliary warps: queries of the next plane, merge + epilogue of the previous ----------------
+    auto stage = [&](int buf, const Inputs& in) {
+      bf16* q_s = sQ + buf * 16 * QSTR;
 #pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-      const int w = tid + it * CT;
-      pre_qa[it] = pre_qb[it] = pre_ct[it] = pre_st[it] = 0.f;
-      if (w < G * HALF) {
-        const int g = w / HALF, i = w % HALF;
-        const int ia = p.interleaved ? 2 * i : i, ib = p.interleaved ? 2 * i + 1 : i + HALF;
-        pre_qa[it] = __bfloat162float(qrow[g * DH + ia]);
-        pre_qb[it] = __bfloat162float(qrow[g * DH + ib]);
-        pre_ct[it] = __bfloat162float(p.cos_t[(hk * G + g) * HALF + i]);
-        pre_st[it] = __bfloat162float(p.sin_t[(hk * G + g) * HALF + i]);
-      }
-    }
-    if (tid < G) pre_lam = __bfloat162float(p.lam_logit[(long long)b * p.lam_bs + hk * G + tid]);
-#pragma unroll
-    for (int a = 0; a < ALW; ++a) {
-      const int i0 = (tid + a * CT) * 4;
-      uint32_t wv = 0;
-      if (i0 + 3 < p.Lbuf && ((reinterpret_cast<uintptr_t>(p.allowed + (long long)b * p.Lbuf + i0) & 3) == 0)) {
-        wv = *reinterpret_cast<const uint32_t*>(p.allowed + (long long)b * p.Lbuf + i0);
-      } else {
-        for (int e = 0; e < 4; ++e) if (i0 + e < p.Lbuf) wv |= (uint32_t)p.allowed[(long long)b * p.Lbuf + i0 + e] << (8 * e);
-      }
-      pre_al[a] = wv;
-    }
-  };
-  if ((int)blockIdx.x < nplanes) prefetch(blockIdx.x);
-  bar_consumers();
-
-  int tbase = 0;                                           // tiles consumed before the current plane
-  for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, tbase += nst) {
-    const int b = plane / p.Hkv, hk = plane % p.Hkv;
-    // ---- prologue: RoPE -> signal rows, learned (even, odd) rotation -> noise rows, lambda, mask ----
-#pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-      const int w = tid + it * CT;
-      if (w < G * HALF) {
-        const int g = w / HALF, i = w % HALF;
-        const float c = sCS[i], s = sCS[HALF + i];
-        float oa, ob; int ia, ib;
-        if (p.interleaved) {
-          ia = 2 * i; ib = 2 * i + 1;
-          oa = t_sub<bf16>(t_mul<bf16>(pre_qa[it], c), t_mul<bf16>(pre_qb[it], s));
-          ob = t_add<bf16>(t_mul<bf16>(pre_qa[it], s), t_mul<bf16>(pre_qb[it], c));
-        } else {
-          ia = i; ib = i + HALF;
-          oa = t_add<bf16>(t_mul<bf16>(pre_qa[it], c), t_mul<bf16>(-pre_qb[it], s));
-          ob = t_add<bf16>(t_mul<bf16>(pre_qb[it], c), t_mul<bf16>(pre_qa[it], s));
+      for (int it = 0; it < ITEMS; ++it) {
+        const int w = at + it * AT;
+        if (w < G * HALF) {
+          const int g = w / HALF, i = w % HALF;
+          const float a0 = __uint_as_float(in.q0[it] << 16), a1 = __uint_as_float(in.q0[it] & 0xffff0000u);
+          const float b0 = __uint_as_float(in.q1[it] << 16), b1 = __uint_as_float(in.q1[it] & 0xffff0000u);
+          float e0, e1;                                    // RoPE'd elements 2i, 2i+1 (primitives.py:99-113)
+          if (p.interleaved) {
+            const float c = sCS[i], s = sCS[HALF + i];
+            e0 = t_sub<bf16>(t_mul<bf16>(a0, c), t_mul<bf16>(a1, s));
+            e1 = t_add<bf16>(t_mul<bf16>(a0, s), t_mul<bf16>(a1, c));
+          } else {
+            const bool lo = 2 * i < HALF;
+            const int pi = lo ? 2 * i : 2 * i - HALF;
+            const float c0 = sCS[pi], s0 = sCS[HALF + pi], c1 = sCS[pi + 1], s1 = sCS[HALF + pi + 1];
+            e0 = lo ? t_add<bf16>(t_mul<bf16>(a0, c0), t_mul<bf16>(-b0, s0)) : t_add<bf16>(t_mul<bf16>(b0, c0), t_mul<bf16>(a0, s0));
+            e1 = lo ? t_add<bf16>(t_mul<bf16>(a1, c1), t_mul<bf16>(-b1, s1)) : t_add<bf16>(t_mul<bf16>(b1, c1), t_mul<bf16>(a1, s1));
+          }
+          const float ct = __bfloat162float(in.ct[it]), st = __bfloat162float(in.st[it]);
+          const float n0 = t_sub<bf16>(t_mul<bf16>(e0, ct), t_mul<bf16>(e1, st));
+          const float n1 = t_add<bf16>(t_mul<bf16>(e0, st), t_mul<bf16>(e1, ct));
+          *reinterpret_cast<uint32_t*>(q_s + g * QSTR + 2 * i) = pack_bf16(e0, e1);
+          *reinterpret_cast<uint32_t*>(q_s + (G + g) * QSTR + 2 * i) = pack_bf16(n0, n1);
         }
-        sQ[g * QSTR + ia] = __float2bfloat16_rn(oa);
-        sQ[g * QSTR + ib] = __float2bfloat16_rn(ob);
       }
-    }
-    if (tid < G) sLam[tid] = t_sigmoid<bf16>(pre_lam);
+      if (at < G) sLam[buf * 8 + at] = t_sigmoid<bf16>(in.lam);
+      uint8_t* al_s = sAl + buf * al_stride;
 #pragma unroll
-    for (int a = 0; a < ALW; ++a) {
-      const int i0 = (tid + a * CT) * 4;
-      if (i0 < nst * DA_TILE) *reinterpret_cast<uint32_t*>(sAl + i0) = pre_al[a];
-    }
-    bar_consumers();
-#pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-      const int w = tid + it * CT;
-      if (w < G * HALF) {
-        const int g = w / HALF, i = w % HALF;
-        const float qe = __bfloat162float(sQ[g * QSTR + 2 * i]), qo = __bfloat162float(sQ[g * QSTR + 2 * i + 1]);
-        sQ[(G + g) * QSTR + 2 * i] = __float2bfloat16_rn(t_sub<bf16>(t_mul<bf16>(qe, pre_ct[it]), t_mul<bf16>(qo, pre_st[it])));
-        sQ[(G + g) * QSTR + 2 * i + 1] = __float2bfloat16_rn(t_add<bf16>(t_mul<bf16>(qe, pre_st[it]), t_mul<bf16>(qo, pre_ct[it])));
+      for (int a = 0; a < ALW; ++a) {
+        const int i0 = (at + a * AT) * 4;
+        if (i0 < al_stride) *reinterpret_cast<uint32_t*>(al_s + i0) = in.al[a];
       }
-    }
-    bar_consumers();
-    // inputs of the next plane: in flight while this plane's tiles are processed
-    if (plane + (int)gridDim.x < nplanes) prefetch(plane + gridDim.x);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_ready[buf]);
+    };
 
-    uint32_t qf[KSTEPS][4];
     {
-      const uint32_t qbase = smem_u32(sQ) + (uint32_t)(((lane & 15) * QSTR + (lane >> 4) * 8) * 2);
-#pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) ldsm_x4(qf[kk], qbase + kk * 32);
+      // RoPE cos/sin of the query position (ring position + device step counter): the same for every plane
+      const long long qpos = p.rp.pos + steps_pre - p.pos_minus_one;
+      if (at < HALF) {
+        float ta = (float)qpos, inv = inv_pre;
+        if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
+        float ang = __fmul_rn(ta, inv);
+        if (p.angle_bf16) ang = bf16_round(ang);
+        float c = cosf(ang), s = sinf(ang);
+        if (p.angle_bf16) { c = bf16_round(c); s = bf16_round(s); }
+        sCS[at] = bf16_round(c);
+        sCS[HALF + at] = bf16_round(s);
+      }
+      for (int i = at; i < 2 * 16 * QSTR; i += AT) sQ[i] = __float2bfloat16_rn(0.f);   // rows >= 2G stay zero
+      bar_aux();
     }
-    float oacc[NT_O][4];
+    const int gstep = (int)gridDim.x;
+    if ((int)blockIdx.x < nplanes) stage(0, inA);
+    if ((int)blockIdx.x + 2 * gstep < nplanes) fetch(blockIdx.x + 2 * gstep, inA);
+
+    // One plane of this CTA (its i-th); `nxt` is the input set of the following one.
+    auto aux_plane = [&](int i, int plane, Inputs& nxt) {
+      // queries of the next plane (requested two planes ago) first, then the request for the plane that will
+      // use the same set: both are off the consumers' critical path, which is inside the current plane's tiles
+      if (plane + gstep < nplanes) stage((i + 1) & 1, nxt);
+      if (plane + 3 * gstep < nplanes) fetch(plane + 3 * gstep, nxt);
+      // ---- merge of the eight partial softmaxes; one warp per query head: sig - lam*noise, RMSNorm, store ----
+      mbar_wait(comb_full, i & 1, p.status, 5);
+      const int b = plane / p.Hkv, hk = plane % p.Hkv;
+      for (int g = aw; g < G; g += DA_AWARPS) {
+        // lanes 0-7: partial w = lane of the signal row g; lanes 8-15: of the noise row G + g (16-31 mirror them)
+        const int mrow = ((lane >> 3) & 1) * G + g, mw = lane & 7;
+        const float m_w = sML[mw * 16 + mrow], l_w = sML[DA_CWARPS * 16 + mw * 16 + mrow];
+        float M = m_w;
 #pragma unroll
-    for (int j = 0; j < NT_O; ++j) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f; }
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows lane/4 and lane/4 + 8
-    const int li = lane >> 3, lr = lane & 7;
+        for (int o = 1; o < 8; o <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float f_w = (m_w == -INFINITY) ? 0.f : exp2f(m_w - M);
+        float Lsum = f_w * l_w;
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) Lsum += __shfl_xor_sync(0xffffffffu, Lsum, o);
+        const float inv_w = Lsum > 0.f ? 1.f / Lsum : 0.f;
+        float v[2][DV];                                    // [stream][dims 4*lane .. 4*lane+3 (+128 ...)]
+#pragma unroll
+        for (int st = 0; st < 2; ++st) {
+          const int row = st * G + g;
+          const int sw = ((row >> 1) & 3) << 3;            // column swizzle of the partials (see the consumer)
+          const float inv = __shfl_sync(0xffffffffu, inv_w, st * 8);
+          float acc[DV];
+#pragma unroll
+          for (int k = 0; k < DV; ++k) acc[k] = 0.f;
+#pragma unroll
+          for (int w = 0; w < DA_CWARPS; ++w) {
+            const float f = __shfl_sync(0xffffffffu, f_w, st * 8 + w);
+            const float4 c4 = *reinterpret_cast<const float4*>(comb + (w * RL + row) * DH + (dact ? ((4 * lane) ^ sw) : 0));
+            acc[0] += f * c4.x; acc[1] += f * c4.y; acc[2] += f * c4.z; acc[3] += f * c4.w;
+          }
+#pragma unroll
+          for (int k = 0; k < DV; ++k) v[st][k] = bf16_round(acc[k] * inv);
+        }
+        const float lam = sLam[(i & 1) * 8 + g];
+        float diff[DV], sq = 0.f;
+#pragma unroll
+        for (int k = 0; k < DV; ++k) {
+          diff[k] = t_sub<bf16>(v[0][k], t_mul<bf16>(lam, v[1][k]));
+          if (dact) sq += bf16_round(diff[k] * diff[k]);
+        }
+        bf16* op = p.out + (long long)b * p.out_bs + (long long)(hk * G + g) * DH;
+        if (p.norm_full) {
+          const float var = bf16_round(warp_sum(sq) / (float)DH);
+          const float rs = bf16_round(rsqrtf(bf16_round(var + p.eps)));
+#pragma unroll
+          for (int k = 0; k < DV; ++k) diff[k] = t_mul<bf16>(t_mul<bf16>(diff[k], rs), nw[k]);
+        }
+        if (dact) {
+          uint2 o2;
+          o2.x = pack_bf16(diff[0], diff[1]); o2.y = pack_bf16(diff[2], diff[3]);
+          *reinterpret_cast<uint2*>(op + 4 * lane) = o2;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(comb_free);
+    };
+    for (int i = 0, plane = blockIdx.x; plane < nplanes; i += 2, plane += 2 * gstep) {
+      aux_plane(i, plane, inB);
+      if (plane + gstep < nplanes) aux_plane(i + 1, plane + gstep, inA);
+    }
+    return;
+  }
+
+  // ---------------- consumers: two groups of four warps, each taking every other tile ----------------
+  // Tensor-core tiles are laid out with the SLOTS as the m dimension and the queries as n = 8:
+  //   S^T[16 slots x 8 q] = K[16 x Dh] . Q^T,   O^T[Dh x 8 q] += V^T[16 dh x 16 slots] . P^T
+  // so that the 2G <= 8 live query rows fill an n-tile exactly (NQ = 2 n-tiles for 8 < 2G <= 16); with the
+  // queries as m = 16 half of every tile would be padding, and the legacy tensor path is what bounds a tile.
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+  const int grp = warp >> 2, gw = warp & 3;            // group, warp inside the group (owns slots gw*16..+15 of a tile)
+  const int li = lane >> 3, lr = lane & 7;
+  const int qa = 2 * (lane & 3);                        // this thread's query columns: nq*8 + qa + {0, 1}
+  int i = 0;
+  for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
+    const int buf = i & 1;
+    mbar_wait(&q_ready[buf], (i >> 1) & 1, p.status, 3);
+    const uint8_t* al_s = sAl + buf * al_stride;
+    // B fragments of Q^T: one ldmatrix.x4 covers two k-steps of one n-tile (matrices: dh chunks 4j .. 4j+3)
+    uint32_t qf[NQ][KSTEPS / 2][4];
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq) {
+      const uint32_t qbase = smem_u32(sQ + buf * 16 * QSTR) + (uint32_t)(((nq * 8 + lr) * QSTR + li * 8) * 2);
+#pragma unroll
+      for (int j = 0; j < KSTEPS / 2; ++j) ldsm_x4(qf[nq][j], qbase + j * 64);
+    }
+    float oacc[NQ][MT_O][4];
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+      for (int j = 0; j < MT_O; ++j) { oacc[nq][j][0] = oacc[nq][j][1] = oacc[nq][j][2] = oacc[nq][j][3] = 0.f; }
+    float mrun[NQ][2], lrun[NQ][2];                       // running max / (per-thread partial) sum of columns qa, qa+1
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq) { mrun[nq][0] = mrun[nq][1] = -INFINITY; lrun[nq][0] = lrun[nq][1] = 0.f; }
+    // tile s of this CTA's i-th plane is the (i * nst + s)-th tile through the ring
+    int bi = (i * nst + grp) % S, round = (i * nst + grp) / S;
 
     for (int s = grp; s < nst; s += 2) {
-      const int t = tbase + s;
-      const int bi = t % DA_STAGES;
-      mbar_wait(&full[bi], (t / DA_STAGES) & 1, p.status, 2);
+      mbar_wait(&full[bi], round & 1, p.status, 2);
       const uint32_t kb = smem_u32(stage0 + bi * 2 * TILE_BYTES);
       const uint32_t vb = kb + TILE_BYTES;
-      // ---- S = Q K^T over this warp's 16 slots (two accumulation chains per n-tile) ----
-      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      float sd[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      const int krow = gw * 16 + (li >> 1) * 8 + lr;
+      // ---- S^T = K Q^T over this warp's 16 slots (two accumulation chains per n-tile) ----
+      float sc[NQ][4], sd[NQ][4];
+#pragma unroll
+      for (int nq = 0; nq < NQ; ++nq) { sc[nq][0] = sc[nq][1] = sc[nq][2] = sc[nq][3] = 0.f; sd[nq][0] = sd[nq][1] = sd[nq][2] = sd[nq][3] = 0.f; }
+      const int krow = gw * 16 + (li & 1) * 8 + lr;
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; kk += 2) {
         uint32_t kf[4], kg[4];
-        ldsm_x4(kf, kb + tile_off<DH>(krow, kk * 2 + (li & 1)));
-        ldsm_x4(kg, kb + tile_off<DH>(krow, (kk + 1) * 2 + (li & 1)));
-        mma_bf16(sc[0], qf[kk], kf[0], kf[1]);
-        mma_bf16(sc[1], qf[kk], kf[2], kf[3]);
-        mma_bf16(sd[0], qf[kk + 1], kg[0], kg[1]);
-        mma_bf16(sd[1], qf[kk + 1], kg[2], kg[3]);
-      }
-      // ---- mask + online softmax (rows r0 = lane/4, r1 = r0 + 8) ----
-      float mx0 = -INFINITY, mx1 = -INFINITY;
+        ldsm_x4(kf, kb + tile_off<DH>(krow, kk * 2 + (li >> 1)));
+        ldsm_x4(kg, kb + tile_off<DH>(krow, (kk + 1) * 2 + (li >> 1)));
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int slot = s * DA_TILE + gw * 16 + nt * 8 + 2 * (lane & 3) + e;
-          const bool vis = slot < p.Lbuf && (!p.mask_unused || sAl[slot] != 0);
-          sc[nt][e] = vis ? (sc[nt][e] + sd[nt][e]) * p.scale_log2 : -INFINITY;
-          sc[nt][2 + e] = vis ? (sc[nt][2 + e] + sd[nt][2 + e]) * p.scale_log2 : -INFINITY;
-          mx0 = fmaxf(mx0, sc[nt][e]);
-          mx1 = fmaxf(mx1, sc[nt][2 + e]);
+        for (int nq = 0; nq < NQ; ++nq) {
+          mma_bf16(sc[nq], kf, qf[nq][kk / 2][0], qf[nq][kk / 2][1]);
+          mma_bf16(sd[nq], kg, qf[nq][kk / 2][2], qf[nq][kk / 2][3]);
         }
       }
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-      const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
-      const float ref0 = nm0 == -INFINITY ? 0.f : nm0, ref1 = nm1 == -INFINITY ? 0.f : nm1;
-      const float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);
-      m0 = nm0; m1 = nm1;
-      uint32_t pf[4];
-      {
-        const float p00 = exp2f(sc[0][0] - ref0), p01 = exp2f(sc[0][1] - ref0), p02 = exp2f(sc[0][2] - ref1), p03 = exp2f(sc[0][3] - ref1);
-        const float p10 = exp2f(sc[1][0] - ref0), p11 = exp2f(sc[1][1] - ref0), p12 = exp2f(sc[1][2] - ref1), p13 = exp2f(sc[1][3] - ref1);
-        l0 = l0 * a0 + (p00 + p01 + p10 + p11);
-        l1 = l1 * a1 + (p02 + p03 + p12 + p13);
-        pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03); pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
-      }
-      if (a0 != 1.f || a1 != 1.f) {
+      // ---- mask + online softmax; this thread: slots r0 = lane/4 and r0 + 8, columns qa, qa + 1 ----
+      const int slot0 = s * DA_TILE + gw * 16 + (lane >> 2);
+      const bool vis0 = slot0 < p.Lbuf && (!p.mask_unused || al_s[slot0] != 0);
+      const bool vis1 = slot0 + 8 < p.Lbuf && (!p.mask_unused || al_s[slot0 + 8] != 0);
+      uint32_t pb[NQ][2];                                  // B fragments of P^T
 #pragma unroll
-        for (int j = 0; j < NT_O; ++j) { oacc[j][0] *= a0; oacc[j][1] *= a0; oacc[j][2] *= a1; oacc[j][3] *= a1; }
-      }
-      // ---- O += P V ----
-      const int vrow = gw * 16 + (li & 1) * 8 + lr;
+      for (int nq = 0; nq < NQ; ++nq) {
+        float x[4];
+        x[0] = vis0 ? (sc[nq][0] + sd[nq][0]) * p.scale_log2 : -INFINITY;
+        x[1] = vis0 ? (sc[nq][1] + sd[nq][1]) * p.scale_log2 : -INFINITY;
+        x[2] = vis1 ? (sc[nq][2] + sd[nq][2]) * p.scale_log2 : -INFINITY;
+        x[3] = vis1 ? (sc[nq][3] + sd[nq][3]) * p.scale_log2 : -INFINITY;
+        float mx0 = fmaxf(x[0], x[2]), mx1 = fmaxf(x[1], x[3]);
 #pragma unroll
-      for (int j = 0; j < NT_O; j += 2) {
+        for (int o = 4; o < 32; o <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+        }
+        const float nm0 = fmaxf(mrun[nq][0], mx0), nm1 = fmaxf(mrun[nq][1], mx1);
+        const float ref0 = nm0 == -INFINITY ? 0.f : nm0, ref1 = nm1 == -INFINITY ? 0.f : nm1;
+        const float a0 = exp2f(mrun[nq][0] - ref0), a1 = exp2f(mrun[nq][1] - ref1);
+        mrun[nq][0] = nm0; mrun[nq][1] = nm1;
+        const float p0 = exp2f(x[0] - ref0), p1 = exp2f(x[1] - ref1), p2 = exp2f(x[2] - ref0), p3 = exp2f(x[3] - ref1);
+        lrun[nq][0] = lrun[nq][0] * a0 + (p0 + p2);
+        lrun[nq][1] = lrun[nq][1] * a1 + (p1 + p3);
+        // [slot][q] fragments -> [q][slot] (the B operand of P^T): 8x8 transposes across the warp
+        pb[nq][0] = movmatrix_t(pack_bf16(p0, p1));
+        pb[nq][1] = movmatrix_t(pack_bf16(p2, p3));
+        if (a0 != 1.f || a1 != 1.f) {
+#pragma unroll
+          for (int j = 0; j < MT_O; ++j) { oacc[nq][j][0] *= a0; oacc[nq][j][1] *= a1; oacc[nq][j][2] *= a0; oacc[nq][j][3] *= a1; }
+        }
+      }
+      // ---- O^T += V^T P^T ----
+      const int vrow = gw * 16 + (li >> 1) * 8 + lr;
+#pragma unroll
+      for (int j = 0; j < MT_O; ++j) {
         uint32_t vf[4];
-        ldsm_x4_t(vf, vb + tile_off<DH>(vrow, j + (li >> 1)));
-        mma_bf16(oacc[j], pf, vf[0], vf[1]);
-        mma_bf16(oacc[j + 1], pf, vf[2], vf[3]);
+        ldsm_x4_t(vf, vb + tile_off<DH>(vrow, 2 * j + (li & 1)));
+#pragma unroll
+        for (int nq = 0; nq < NQ; ++nq) mma_bf16(oacc[nq][j], vf, pb[nq][0], pb[nq][1]);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[bi]);
+      bi += 2;
+      if (bi >= S) { bi -= S; ++round; }
     }
 
-    // ---- merge the eight warps' partial softmaxes ----
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    if ((lane & 3) == 0) {
-      const int r = lane >> 2;
-      sML[warp * 16 + r] = m0; sML[warp * 16 + r + 8] = m1;
-      sML[DA_CWARPS * 16 + warp * 16 + r] = l0; sML[DA_CWARPS * 16 + warp * 16 + r + 8] = l1;
+    // ---- hand the partial softmax of this warp to the auxiliary warps ----
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        lrun[nq][0] += __shfl_xor_sync(0xffffffffu, lrun[nq][0], o);
+        lrun[nq][1] += __shfl_xor_sync(0xffffffffu, lrun[nq][1], o);
+      }
+    if (i >= 1) mbar_wait(comb_free, (i - 1) & 1, p.status, 4);
+    if (lane < 4) {
+#pragma unroll
+      for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int q = nq * 8 + qa + e;
+          sML[warp * 16 + q] = mrun[nq][e];
+          sML[DA_CWARPS * 16 + warp * 16 + q] = lrun[nq][e];
+        }
     }
     {
-      // only the 2G live rows are exchanged (row r and r + 8 of the accumulator tile)
-      const int r = lane >> 2, cb = 2 * (lane & 3);
+      // comb[warp][q][dh]; the dh index is XOR-swizzled with (q / 2) % 4 = lane % 4, so that the four query
+      // pairs a warp stores at once fall into different banks.  Only the 2G live rows are exchanged.
+      const int sw = (lane & 3) << 3;
 #pragma unroll
-      for (int j = 0; j < NT_O; ++j) {
-        if (r < 2 * G) {
-          float* d0 = comb + ((warp * 16 + r) * DH + j * 8 + cb);
-          d0[0] = oacc[j][0]; d0[1] = oacc[j][1];
+      for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+        for (int j = 0; j < MT_O; ++j) {
+          const int d0 = (j * 16 + (lane >> 2)) ^ sw, d1 = (j * 16 + 8 + (lane >> 2)) ^ sw;
+          const int q = nq * 8 + qa;
+          if (q < RL) {
+            comb[(warp * RL + q) * DH + d0] = oacc[nq][j][0];
+            comb[(warp * RL + q) * DH + d1] = oacc[nq][j][2];
+          }
+          if (q + 1 < RL) {
+            comb[(warp * RL + q + 1) * DH + d0] = oacc[nq][j][1];
+            comb[(warp * RL + q + 1) * DH + d1] = oacc[nq][j][3];
+          }
         }
-        if (r + 8 < 2 * G) {
-          float* d1 = comb + ((warp * 16 + r + 8) * DH + j * 8 + cb);
-          d1[0] = oacc[j][2]; d1[1] = oacc[j][3];
-        }
-      }
     }
-    bar_consumers();
-
-    // ---- epilogue: one warp per query head: sig - lam*noise, optional RMSNorm, bf16 store ----
-    for (int g = warp; g < G; g += DA_CWARPS) {
-      float os[DH / 32], on[DH / 32];
-#pragma unroll
-      for (int st = 0; st < 2; ++st) {
-        const int row = st * G + g;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < DA_CWARPS; ++w) M = fmaxf(M, sML[w * 16 + row]);
-        float f[DA_CWARPS], L = 0.f;
-#pragma unroll
-        for (int w = 0; w < DA_CWARPS; ++w) {
-          const float mw = sML[w * 16 + row];
-          f[w] = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-          L += f[w] * sML[DA_CWARPS * 16 + w * 16 + row];
-        }
-        const float inv = L > 0.f ? 1.f / L : 0.f;
-#pragma unroll
-        for (int i = 0; i < DH / 32; ++i) {
-          const int d = lane + 32 * i;
-          float acc = 0.f;
-#pragma unroll
-          for (int w = 0; w < DA_CWARPS; ++w) acc += f[w] * comb[(w * 16 + row) * DH + d];
-          const float v = bf16_round(acc * inv);
-          if (st == 0) os[i] = v; else on[i] = v;
-        }
-      }
-      const float lam = sLam[g];
-      float diff[DH / 32], sq = 0.f;
-#pragma unroll
-      for (int i = 0; i < DH / 32; ++i) {
-        diff[i] = t_sub<bf16>(os[i], t_mul<bf16>(lam, on[i]));
-        sq += bf16_round(diff[i] * diff[i]);
-      }
-      bf16* op = p.out + (long long)b * p.out_bs + (long long)(hk * G + g) * DH;
-      if (p.norm_full) {
-        const float var = bf16_round(warp_sum(sq) / (float)DH);
-        const float rs = bf16_round(rsqrtf(bf16_round(var + p.eps)));
-#pragma unroll
-        for (int i = 0; i < DH / 32; ++i) {
-          const int d = lane + 32 * i;
-          op[d] = __float2bfloat16_rn(t_mul<bf16>(t_mul<bf16>(diff[i], rs), __bfloat162float(p.norm_w[d])));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < DH / 32; ++i) op[lane + 32 * i] = __float2bfloat16_rn(diff[i]);
-      }
-    }
-    bar_consumers();                       // sQ / sML / comb / sAl are rewritten by the next plane's prologue
+    __syncwarp();
+    if (lane == 0) mbar_arrive(comb_full);
   }  // plane loop
 }
 
-template <int DH>
-size_t decode_smem(int Lbuf) {
-  const int nst = (Lbuf + DA_TILE - 1) / DA_TILE;
-  return (size_t)DA_STAGES * 2 * DA_TILE * DH * 2 + (size_t)DA_CWARPS * 16 * DH * 4 + 16 * (DH + 8) * 2 + (2 * DA_CWARPS * 16 + 8 + DH) * 4 +
-         2 * DA_STAGES * 8 + (size_t)nst * DA_TILE + 16 + 1024;
-}
-
-template <int DH>
-int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, const DecodeParams& p, cudaStream_t s) {
-  const size_t smem = decode_smem<DH>(p.Lbuf);
+template <int DH, int NQ>
+int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, cudaStream_t s) {
+  constexpr int BUDGET = 226 * 1024;
+  const int nst = (p.Lbuf + DA_TILE - 1) / DA_TILE;
+  // as many ring stages as fit beside the fixed buffers (at least 2, at most DA_MAX_STAGES)
+  const int fixed = DecodeSmem<DH>(0, p.G, nst).total + 1024;
+  int stages = (BUDGET - fixed) / (2 * DecodeSmem<DH>::TILE_BYTES);
+  if (stages > DA_MAX_STAGES) stages = DA_MAX_STAGES;
+  CODA_REQUIRE(stages >= 2, CODA_ERR_LIMIT, "decode_attend: %d slots leave no room for the tile ring in shared memory", p.Lbuf);
+  p.stages = stages;
+  const size_t smem = (size_t)DecodeSmem<DH>(stages, p.G, nst).total + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(decode_attend_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    cudaFuncSetAttribute(decode_attend_kernel<DH, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BUDGET);
     configured = true;
   }
-  CODA_REQUIRE(smem <= 226 * 1024, CODA_ERR_LIMIT, "decode_attend: %d slots need %zu bytes of shared memory", p.Lbuf, smem);
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -403,7 +530,7 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, const DecodePara
     if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
   }
   const int nplanes = p.B * p.Hkv;
-  decode_attend_kernel<DH><<<nplanes < num_sms ? nplanes : num_sms, DA_THREADS, smem, s>>>(km, vm, p);
+  decode_attend_kernel<DH, NQ><<<nplanes < num_sms ? nplanes : num_sms, DA_THREADS, smem, s>>>(km, vm, p);
   CODA_CHECK_LAUNCH("decode_attend");
   return CODA_OK;
 }
@@ -447,5 +574,6 @@ extern "C" int coda_b200_decode_attend(const coda_layer_cfg* cfg, const coda_sta
   p.inv_freq = inv_freq; p.cos_t = (const bf16*)cos_theta; p.sin_t = (const bf16*)sin_theta;
   p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w; p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
   cudaStream_t s = (cudaStream_t)stream;
-  return cfg->Dh == 128 ? launch_decode<128>(km, vm, p, s) : launch_decode<64>(km, vm, p, s);
+  if (p.G <= 4) return cfg->Dh == 128 ? launch_decode<128, 1>(km, vm, p, s) : launch_decode<64, 1>(km, vm, p, s);
+  return cfg->Dh == 128 ? launch_decode<128, 2>(km, vm, p, s) : launch_decode<64, 2>(km, vm, p, s);
 }

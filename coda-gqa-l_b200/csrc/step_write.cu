@@ -256,6 +256,311 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
   if (tid == 0) gr[ev] = g_new;
 }
 
+
+// ------------------------------------------------------------------------------------------------------------
+// Cluster variant: one CTA per (state, KV head), the Hkv CTAs of a state forming one thread-block cluster.
+// The work of a decode write is a chain of short dependent steps (evicted row -> unit vectors -> scores ->
+// decision -> slot update); one CTA per state leaves it on 1/5 of the SMs with every global round trip on
+// the critical path.  Here each CTA touches one head only: its slice of both routing caches is requested
+// into registers at kernel entry (two threads per bank row), the exact- and summary-bank scores are
+// computed together, the per-head dot products are exchanged through distributed shared memory (every CTA
+// stores its values into all CTAs of the cluster, one cluster barrier), and each CTA then takes both routing
+// decisions redundantly, warp-parallel, before rewriting its own head's rows.
+template <typename T, int DH>
+__global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
+  constexpr int NT = 256, LF = DH / 2, LFD = DH - LF;
+  constexpr int EV = (DH / 2) * (int)sizeof(T) / 16;      // 16-byte vectors per thread of an exact-bank half row
+  constexpr int SV = (LFD / 2) * (int)sizeof(T) / 16;     // ... of a summary-bank half row
+  constexpr int EPV = 16 / (int)sizeof(T);                // elements per vector
+  extern __shared__ float sm[];
+  const coda_layer_cfg& c = p.c;
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int W = c.W, Me = c.Me, Ms = c.Ms, Hkv = c.Hkv;
+  const int Lbuf = W + Me + Ms, MM = Me + Ms;
+
+  __shared__ float ke[DH], ve[DH], vhat[DH], khat[LFD], cs[DH / 2], sn[DH / 2], s_den[2];
+  __shared__ int s_eidx, s_eflag, s_sidx, s_sflag;
+  __shared__ float s_keep;
+  float* xdots = sm;                                      // [Hkv][MM] per-head dots of every CTA of the cluster
+  float* sc = xdots + Hkv * MM;                           // [MM] reduced scores
+  long long* s_last = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(sc + MM) + 7) & ~(uintptr_t)7);  // [Me]
+  unsigned char* s_used = reinterpret_cast<unsigned char*>(s_last + Me);                                         // [MM]
+
+  T* kb = (T*)p.st.k_buf + ((long long)b * Hkv + h) * Lbuf * DH;       // this head's planes
+  T* vb = (T*)p.st.v_buf + ((long long)b * Hkv + h) * Lbuf * DH;
+  uint8_t* al = p.st.allowed + (long long)b * Lbuf;
+  float* gr = p.st.g_recent + (long long)b * W;
+  const T* kn = (const T*)p.k_new + (long long)b * p.k_bs + h * DH;
+  const T* vn = (const T*)p.v_new + (long long)b * p.v_bs + h * DH;
+
+  // ---- requests that depend on nothing but (b, h): issued first, consumed later ----
+  // bank rows: item it -> (row it/2, half it%2); exact rows first, then summary rows
+  const T* vnorm = (const T*)p.st.exact_v_norm + ((long long)b * Hkv + h) * Me * DH;
+  const T* knorm = (const T*)p.st.sum_lf_k_norm + ((long long)b * Hkv + h) * Ms * LFD;
+  uint4 seg[EV];
+  auto load_seg = [&](int it) {
+    if (it < 2 * Me) {
+      const uint4* src = reinterpret_cast<const uint4*>(vnorm + (long long)(it >> 1) * DH + (it & 1) * (DH / 2));
+#pragma unroll
+      for (int j = 0; j < EV; ++j) seg[j] = src[j];
+    } else if (it < 2 * MM) {
+      const int m = (it - 2 * Me) >> 1;
+      const uint4* src = reinterpret_cast<const uint4*>(knorm + (long long)m * LFD + (it & 1) * (LFD / 2));
+#pragma unroll
+      for (int j = 0; j < SV; ++j) seg[j] = src[j];
+    }
+  };
+  load_seg(tid);
+  for (int m = tid; m < MM; m += NT) s_used[m] = al[W + m];
+  for (int m = tid; m < Me; m += NT) s_last[m] = ((const long long*)p.st.mem_last_exact)[(long long)b * Me + m];
+  // the new token's row (element tid < DH: key, DH <= tid < 2*DH: value)
+  float nk_a = 0.f, nk_b = 0.f, nv_x = 0.f, eta_raw = 0.f, glog = 0.f;
+  const bool is_k = tid < DH, is_v = tid >= DH && tid < 2 * DH;
+  const int d = is_k ? tid : tid - DH;
+  int ri = 0;                                             // RoPE pair index of key element d
+  if (is_k) {
+    if (p.raw) {
+      int ia, ib;
+      if (c.rope_interleaved) { ri = d >> 1; ia = 2 * ri; ib = ia + 1; }
+      else { ri = d < LF ? d : d - LF; ia = ri; ib = ri + LF; }
+      nk_a = El<T>::ld(kn + ia); nk_b = El<T>::ld(kn + ib);
+    } else {
+      nk_a = El<T>::ld(kn + d);
+    }
+  }
+  T nv_raw = T();
+  if (is_v) nv_raw = vn[d];
+  (void)nv_x;
+  if (Ms > 0) eta_raw = p.eta_logit[h];
+  if (p.raw) { if (c.gated) glog = El<T>::ld((const T*)p.gate_logit + (long long)b * p.gate_bs); }
+  else glog = p.gate[b];
+
+  const RingNow r = ring_now(p.rp, W);
+  float g_new;
+  if (p.raw) {
+    g_new = c.gated ? t_sigmoid<T>(glog) : 1.0f;
+    const bool abf = c.angle_dtype == CODA_BF16;
+    if (tid < DH / 2) {
+      float ta = (float)r.pos, inv = p.inv_freq[tid];
+      if (abf) { ta = bf16_round(ta); inv = bf16_round(inv); }
+      float ang = __fmul_rn(ta, inv);
+      if (abf) ang = bf16_round(ang);
+      float cc = cosf(ang), ss = sinf(ang);
+      if (abf) { cc = bf16_round(cc); ss = bf16_round(ss); }
+      cs[tid] = El<T>::rnd(cc); sn[tid] = El<T>::rnd(ss);
+    }
+  } else {
+    g_new = glog;
+  }
+  const bool full = r.filled >= W;
+  const int ev = full ? r.idx : r.filled;                 // the ring slot the new token takes
+  float g_e = 0.f;
+  if (full) {                                             // evicted row of this head
+    if (is_k) ke[d] = El<T>::ld(kb + (long long)ev * DH + d);
+    if (is_v) ve[d] = El<T>::ld(vb + (long long)ev * DH + d);
+    g_e = gr[ev];
+  }
+  __syncthreads();
+  // rotated key element d (primitives.py:99-113)
+  float new_k = nk_a;
+  if (is_k && p.raw) {
+    const float cc = cs[ri], ss = sn[ri];
+    if (c.rope_interleaved) new_k = (d & 1) ? t_add<T>(t_mul<T>(nk_a, ss), t_mul<T>(nk_b, cc)) : t_sub<T>(t_mul<T>(nk_a, cc), t_mul<T>(nk_b, ss));
+    else new_k = d < LF ? t_add<T>(t_mul<T>(nk_a, cc), t_mul<T>(-nk_b, ss)) : t_add<T>(t_mul<T>(nk_b, cc), t_mul<T>(nk_a, ss));
+  }
+
+  if (!full) {                                            // memory_banks.py:195-201 (uniform over the grid)
+    if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
+    if (is_v) vb[(long long)ev * DH + d] = nv_raw;
+    if (h == 0 && tid == 0) { gr[ev] = g_new; al[ev] = 1; }
+    return;
+  }
+
+  // ---- ring full: the evicted token is routed (memory_banks.py:203-222) ----
+  const long long pos_e = r.pos - W;
+  // unit vectors x / max(||x||, 1e-6) (F.normalize, memory_banks.py:258,372): warp 0 value, warp 1 LF key
+  if (warp < 2) {
+    float ss = 0.f;
+    if (warp == 0) { for (int i = lane; i < DH; i += 32) ss += ve[i] * ve[i]; }
+    else { for (int i = LF + lane; i < DH; i += 32) ss += ke[i] * ke[i]; }
+    ss = warp_sum(ss);
+    if (lane == 0) s_den[warp] = fmaxf(El<T>::rnd(sqrtf(ss)), 1e-6f);
+  }
+  __syncthreads();
+  if (is_v) vhat[d] = t_div<T>(ve[d], s_den[0]);
+  if (is_k && d >= LF) khat[d - LF] = t_div<T>(ke[d], s_den[1]);
+  __syncthreads();
+
+  // ---- per-head dot products of both banks, sent to every CTA of the cluster ----
+  for (int base = 0; base < 2 * MM; base += NT) {
+    const int it = base + tid;
+    float acc0 = 0.f, acc1 = 0.f;
+    if (it < 2 * MM) {
+      const bool ex = it < 2 * Me;
+      const float* a = ex ? vhat + (it & 1) * (DH / 2) : khat + (it & 1) * (LFD / 2);
+      const int nv = ex ? EV : SV;
+#pragma unroll
+      for (int j = 0; j < EV; ++j) {
+        if (j < nv) {
+          float f[EPV];
+          const uint32_t w[4] = {seg[j].x, seg[j].y, seg[j].z, seg[j].w};
+          if (sizeof(T) == 2) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { f[2 * q] = __uint_as_float(w[q] << 16); f[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u); }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) f[q] = __uint_as_float(w[q]);
+          }
+#pragma unroll
+          for (int q = 0; q < EPV; q += 2) {
+            acc0 = fmaf(a[j * EPV + q], f[q], acc0);
+            acc1 = fmaf(a[j * EPV + q + 1], f[q + 1], acc1);
+          }
+        }
+      }
+    }
+    float acc = acc0 + acc1;
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    if (it < 2 * MM && (it & 1) == 0) {
+      const float v = El<T>::rnd(acc);
+      const uint32_t local = tma::smem_u32(xdots + h * MM + (it >> 1));
+      for (int rk = 0; rk < Hkv; ++rk) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rk));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+      }
+    }
+    if (base + NT < 2 * MM) load_seg(base + NT + tid);
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+
+  // ---- scores: sum over heads of the rounded per-head dots, mean, masks ----
+  const int Ae = c.active_exact, As = c.active_summary;
+  for (int m = tid; m < MM; m += NT) {
+    float tot = 0.f;
+    for (int hh = 0; hh < Hkv; ++hh) tot += xdots[hh * MM + m];
+    const float mean = El<T>::rnd(tot / (float)Hkv);
+    sc[m] = m < Me ? ((m >= Ae || !s_used[m]) ? -1e9f : mean) : ((m - Me >= As) ? -1e9f : mean);
+  }
+  __syncthreads();
+  // ---- decisions, taken redundantly by every CTA: warp 0 exact bank, warp 1 summary bank ----
+  auto arg_best = [&](const float* v, int n, float& best, int& bi) {     // first index of the maximum
+    best = -INFINITY; bi = 0x7fffffff;
+    for (int m = lane; m < n; m += 32) if (v[m] > best || bi == 0x7fffffff) { best = v[m]; bi = m; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+    }
+  };
+  if (warp == 0 && Me > 0) {                              // memory_banks.py:230-337
+    float best; int bi;
+    arg_best(sc, Me, best, bi);
+    int free_i = 0x7fffffff, lru_i = 0x7fffffff; long long lru_v = 0x7fffffffffffffffLL; bool any_used = false;
+    for (int m = lane; m < Me; m += 32) {
+      const bool used = s_used[m] != 0, act = m < Ae;
+      if (act && used) any_used = true;
+      if (act && !used && m < free_i) free_i = m;
+      const long long key = (used && act) ? s_last[m] : (1LL << 62);
+      if (key < lru_v) { lru_v = key; lru_i = m; }
+    }
+    any_used = __any_sync(0xffffffffu, any_used);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      free_i = min(free_i, __shfl_xor_sync(0xffffffffu, free_i, o));
+      const long long ov = __shfl_xor_sync(0xffffffffu, lru_v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, lru_i, o);
+      if (ov < lru_v || (ov == lru_v && oi < lru_i)) { lru_v = ov; lru_i = oi; }
+    }
+    if (lane == 0) {
+      const bool novel = !any_used || best < El<T>::rnd(c.tau_novel);
+      const bool hit = any_used && best >= El<T>::rnd(c.tau_match);
+      const bool keep = c.gated ? (g_e >= c.tau_gate_exact) : true;
+      const int idx = novel ? (free_i != 0x7fffffff ? free_i : lru_i) : bi;
+      const bool ow = (novel || (c.refresh_on_hit && hit)) && keep;
+      if (keep && h == 0) ((long long*)p.st.mem_last_exact)[(long long)b * Me + idx] = pos_e;   // memory_banks.py:325-331
+      if (ow && h == 0) al[W + idx] = 1;
+      s_eidx = idx; s_eflag = ow ? 1 : 0;
+    }
+  }
+  if (warp == 1 && Ms > 0) {                              // memory_banks.py:343-432
+    float best; int bi;
+    arg_best(sc + Me, Ms, best, bi);
+    if (lane == 0) {
+      const bool is_new = s_used[Me + bi] == 0;
+      const bool keep = c.gated ? (g_e >= c.tau_gate_summary) : true;
+      s_sidx = bi; s_sflag = (c.overwrite_on_insert && is_new) ? 1 : 0;
+      s_keep = keep ? 1.f : 0.f;
+      if (keep && h == 0) al[W + Me + bi] = 1;
+    }
+  }
+  __syncthreads();
+
+  // ---- slot updates of this head: the old rows of both banks are requested together ----
+  const bool do_e = Me > 0 && s_eflag != 0, do_s = Ms > 0;
+  const long long eoff = (long long)(W + s_eidx) * DH + d, soff = (long long)(W + Me + s_sidx) * DH + d;
+  float eo = 0.f, so = 0.f;
+  if (do_e && (is_k || is_v)) eo = El<T>::ld((is_k ? kb : vb) + eoff);
+  if (do_s && (is_v || (is_k && d >= LF))) so = El<T>::ld((is_k ? kb : vb) + soff);
+  if (do_e) {
+    if (is_k) El<T>::st(kb + eoff, t_add<T>(eo, t_sub<T>(ke[d], eo)));       // mem + 1*(x - mem), memory_banks.py:301-302
+    if (is_v) { const float nv = t_add<T>(eo, t_sub<T>(ve[d], eo)); El<T>::st(vb + eoff, nv); vhat[d] = nv; }
+  }
+  if (do_s) {
+    float eta = t_sigmoid<T>(eta_raw);
+    if (c.gated) eta = t_mul<T>(eta, El<T>::rnd(g_e));
+    if (s_sflag) eta = 1.f;
+    eta = t_mul<T>(eta, s_keep);
+    if (is_k && d >= LF) {                                // phase-safe EMA: LF band only
+      const float inc = El<T>::rnd(__fmul_rn(ke[d], c.energy_scale));
+      const float nk = t_add<T>(so, t_mul<T>(eta, t_sub<T>(inc, so)));
+      El<T>::st(kb + soff, nk);
+      khat[d - LF] = nk;
+    }
+    if (is_v) El<T>::st(vb + soff, t_add<T>(so, t_mul<T>(eta, t_sub<T>(ve[d], so))));
+  }
+  __syncthreads();
+  // re-normalise the two rewritten rows of the routing caches
+  if (warp == 0 && do_e) {
+    float ss = 0.f;
+    for (int i = lane; i < DH; i += 32) ss += vhat[i] * vhat[i];
+    const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
+    T* dst = (T*)p.st.exact_v_norm + (((long long)b * Hkv + h) * Me + s_eidx) * DH;
+    for (int i = lane; i < DH; i += 32) El<T>::st(dst + i, t_div<T>(vhat[i], den));
+  }
+  if (warp == 1 && do_s) {
+    float ss = 0.f;
+    for (int i = lane; i < LFD; i += 32) ss += khat[i] * khat[i];
+    const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
+    T* dst = (T*)p.st.sum_lf_k_norm + (((long long)b * Hkv + h) * Ms + s_sidx) * LFD;
+    for (int i = lane; i < LFD; i += 32) El<T>::st(dst + i, t_div<T>(khat[i], den));
+  }
+  // ---- the new token takes the evicted slot (memory_banks.py:219-222) ----
+  if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
+  if (is_v) vb[(long long)ev * DH + d] = nv_raw;
+  if (h == 0 && tid == 0) gr[ev] = g_new;
+}
+
+template <typename T, int DH>
+static int launch_step_cluster(const StepParams& p, cudaStream_t s) {
+  const coda_layer_cfg& c = p.c;
+  const int MM = c.Me + c.Ms;
+  const size_t smem = sizeof(float) * ((size_t)c.Hkv * MM + MM) + 8 + 8 * (size_t)c.Me + MM + 16;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(c.Hkv, c.B, 1);
+  lc.blockDim = dim3(256, 1, 1);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = c.Hkv; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  lc.attrs = at; lc.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&lc, step_write_cluster_kernel<T, DH>, p);
+  if (e != cudaSuccess) { coda_set_error("step_write (cluster): %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
+  return CODA_OK;
+}
+
 static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
                            const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
                            const float* gate, const float* eta_logit, int raw, const float* inv_freq,
@@ -272,6 +577,21 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
   StepParams p; p.c = *cfg; p.st = *st; p.rp = rp;
   p.k_new = k_new; p.k_bs = k_bs; p.v_new = v_new; p.v_bs = v_bs; p.gate = gate; p.eta_logit = eta_logit;
   p.raw = raw; p.inv_freq = inv_freq; p.gate_logit = gate_logit; p.gate_bs = gate_bs;
+  cudaStream_t s = (cudaStream_t)stream;
+  {
+    // cluster variant: one CTA per (state, head); needs a portable cluster size and vector-aligned cache rows
+    const size_t es0 = cfg->dtype == CODA_F32 ? 4 : 2;
+    const int MM = cfg->Me + cfg->Ms;
+    const size_t csm = sizeof(float) * ((size_t)cfg->Hkv * MM + MM) + 8 + 8 * (size_t)cfg->Me + MM + 16;
+    const bool ok = cfg->Hkv <= 8 && (cfg->Dh == 64 || cfg->Dh == 128) && csm <= 40 * 1024 && cfg->B <= 65535 &&
+                    (cfg->Me == 0 || (uintptr_t)st->exact_v_norm % 16 == 0) && (cfg->Ms == 0 || (uintptr_t)st->sum_lf_k_norm % 16 == 0) &&
+                    ((size_t)cfg->Dh / 4 * es0) % 16 == 0;
+    if (ok) {
+      p.stage = 0; p.stage_off = 0; p.status = nullptr;
+      if (cfg->dtype == CODA_F32) return cfg->Dh == 128 ? launch_step_cluster<float, 128>(p, s) : launch_step_cluster<float, 64>(p, s);
+      return cfg->Dh == 128 ? launch_step_cluster<bf16, 128>(p, s) : launch_step_cluster<bf16, 64>(p, s);
+    }
+  }
   const int HD = cfg->Hkv * cfg->Dh, lfd = cfg->Dh - cfg->Dh / 2;
   const int mx = cfg->Me > cfg->Ms ? cfg->Me : cfg->Ms;
   size_t smem = sizeof(float) * (size_t)(3 * HD + cfg->Hkv * lfd + mx + 1 + cfg->Dh + 2) +
@@ -287,7 +607,6 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
     smem = (size_t)p.stage_off + vbytes + kbytes;
   }
   CODA_REQUIRE(smem <= 226 * 1024, CODA_ERR_LIMIT, "step_write: Hkv*Dh = %d too large for one CTA", HD);
-  cudaStream_t s = (cudaStream_t)stream;
   if (cfg->dtype == CODA_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(step_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     step_write_kernel<float><<<cfg->B, 512, smem, s>>>(p);

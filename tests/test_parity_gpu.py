@@ -187,6 +187,7 @@ def test_rejects_cpu_tensors_and_training_mode():
          head_norm_mode="identity", rope_interleaved=False, rope_base=1e6),                                          # Dh 128, MHA
     dict(embed_dim=576, num_heads=9, num_kv_heads=3, window=128, num_landmarks_exact=32, num_landmarks_summary=32,
          head_norm_mode="identity", rope_interleaved=False),                                                         # config-2 shape
+    dict(embed_dim=1024, num_heads=8, num_kv_heads=1, window=70, num_landmarks_exact=16, num_landmarks_summary=10),   # Dh 128, G 8 (two query n-tiles)
 ])
 def test_tuned_decode_kernel_matches_generic_kernels(shape):
     """The TMA / tensor-core decode kernel against the shape-generic kernels on identical states (bf16),
