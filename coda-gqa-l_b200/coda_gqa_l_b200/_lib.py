@@ -50,7 +50,13 @@ def _load() -> C.CDLL:
     lib.coda_b200_step_write.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, fp, fp, vp]
     lib.coda_b200_step_write_raw.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp, fp, vp]
     lib.coda_b200_decode_attend_supported.argtypes = [cfgp]
-    lib.coda_b200_decode_attend.argtypes = [cfgp, stp, RingPos, i32, vp, i64, vp, i64, fp, vp, vp, vp, vp, i64, vp, vp]
+    lib.coda_b200_decode_attend.argtypes = [cfgp, stp, RingPos, i32, vp, i64, vp, i64, fp, vp, vp, vp, vp, vp, i64, vp, vp]
+    lib.coda_b200_decode_attend_prepared.argtypes = [cfgp, stp, vp, vp, vp, i64, vp, vp]
+    lib.coda_b200_decode_record_bytes.argtypes = [cfgp]
+    lib.coda_b200_decode_record_bytes.restype = C.c_int64
+    lib.coda_b200_step_write_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp, fp,
+                                               vp, i64, vp, i64, vp, vp, vp, vp]
+    lib.coda_b200_step_write_fused_supported.argtypes = [cfgp]
     lib.coda_b200_prefill_attend_supported.argtypes = [cfgp]
     lib.coda_b200_prefill_attend.argtypes = [cfgp, stp, i32, i32, i32, vp, i64, i64, vp, i64, i64, fp, i64, i64,
                                              vp, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp, vp]
@@ -70,14 +76,17 @@ def _load() -> C.CDLL:
     lib.coda_b200_host_topk_i64.argtypes = [vp, i32, i32, i32, i32, vp]
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name not in ("coda_b200_last_error", "coda_b200_route_scratch_bytes", "coda_b200_route_static_scratch_bytes"):
+        if name not in ("coda_b200_last_error", "coda_b200_route_scratch_bytes", "coda_b200_route_static_scratch_bytes",
+                        "coda_b200_decode_record_bytes"):
             fn.restype = C.c_int
     return lib
 
 
 EXPORTS = (
     "coda_b200_last_error", "coda_b200_version", "coda_b200_prep", "coda_b200_step_write",
-    "coda_b200_step_write_raw", "coda_b200_decode_attend_supported", "coda_b200_decode_attend",
+    "coda_b200_step_write_raw", "coda_b200_step_write_fused", "coda_b200_step_write_fused_supported",
+    "coda_b200_decode_attend_supported", "coda_b200_decode_attend", "coda_b200_decode_attend_prepared",
+    "coda_b200_decode_record_bytes",
     "coda_b200_prefill_attend_supported", "coda_b200_prefill_attend",
     "coda_b200_attend", "coda_b200_select_candidates", "coda_b200_route_scratch_bytes",
     "coda_b200_route_block", "coda_b200_route_static_scratch_bytes", "coda_b200_route_block_noalloc",

@@ -159,6 +159,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
         self._fused = None
         # When set to a list, every attention launch appends (Lq, start_event, end_event) to it.
         self.kernel_timers = None
+        self._qrec = None
         # False forces the shape-generic kernels even where a tuned one exists (used by tests).
         self.use_tuned_kernels = True
         self._status = None
@@ -425,35 +426,69 @@ class CoDAGQALandmarkPerf2(nn.Module):
         (1 = producer waiting for a free tile, 2 = consumer waiting for a tile).  Synchronises."""
         return 0 if self._status is None else int(self._status.item())
 
+    def _decode_records(self, cfg, device) -> torch.Tensor:
+        """Device buffer for the per-plane decode records (prepared queries, lambda, visibility mask)."""
+        n = int(lib.coda_b200_decode_record_bytes(C.byref(cfg)))
+        buf = self._qrec
+        if buf is None or buf.numel() < n or buf.device != device:
+            buf = torch.empty(n, dtype=torch.uint8, device=device)
+            self._qrec = buf
+        return buf
+
     def _step_fused(self, cfg, x, state, rp: RingPos, host_update: bool) -> torch.Tensor:
-        """Write-then-attend decode step on the tuned kernels: two launches between the two GEMMs
-        (cache write with in-kernel RoPE / gate sigmoid, then the fused attention)."""
+        """Write-then-attend decode step on the tuned kernels: two launches between the two GEMMs.  The cache
+        write applies RoPE / the gate sigmoid and, where it can, also prepares the attention's queries
+        (decode records); the fused attention then only streams the state."""
         B = x.shape[0]
         dev, dt = x.device, x.dtype
         q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)
         inv_freq, cos_t, sin_t, eta, nw = self._consts(dev, dt)
         ptrs = self._ptrs(state)
         s = _stream()
-        check(lib.coda_b200_step_write_raw(
-            C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
-            _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(), eta.data_ptr(), s),
-            "coda_b200_step_write_raw")
         out = torch.empty((B, 1, self.num_heads * self.head_dim), device=dev, dtype=dt)
-        self.decode_attend_launch(cfg, state, rp, 0, q, lam_logit, out)
+        fused_ok = getattr(cfg, "_fused_write", None)
+        if fused_ok is None:
+            fused_ok = bool(lib.coda_b200_step_write_fused_supported(C.byref(cfg))) and q.data_ptr() % 4 == 0
+            cfg._fused_write = fused_ok
+        if fused_ok:
+            qrec = self._decode_records(cfg, dev)
+            check(lib.coda_b200_step_write_fused(
+                C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(), eta.data_ptr(),
+                q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0), cos_t.data_ptr(), sin_t.data_ptr(),
+                qrec.data_ptr(), s), "coda_b200_step_write_fused")
+            check(lib.coda_b200_decode_attend_prepared(
+                C.byref(cfg), C.byref(ptrs), qrec.data_ptr(), _p(nw), out.data_ptr(), out.stride(0),
+                self._status_word(dev).data_ptr(), s), "coda_b200_decode_attend_prepared")
+        else:
+            check(lib.coda_b200_step_write_raw(
+                C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(), eta.data_ptr(), s),
+                "coda_b200_step_write_raw")
+            self.decode_attend_launch(cfg, state, rp, 0, q, lam_logit, out)
         if host_update:
             self.advance_host_scalars(state)
         return self.o_proj(out)
 
     def decode_attend_launch(self, cfg, state, rp: RingPos, token_already_written: int, q, lam_logit, out) -> None:
-        """One launch of the fused decode attention kernel: raw query projection ``q`` [B, H*Dh] and lambda
-        logits [B, H] in, head-normalised differential attention [B, 1, H*Dh] out.  No other work."""
+        """The fused decode attention alone: raw query projection ``q`` [B, H*Dh] and lambda logits [B, H] in,
+        head-normalised differential attention [B, 1, H*Dh] out (a small preparation launch, then the kernel)."""
         inv_freq, cos_t, sin_t, _, nw = self._consts(q.device, q.dtype)
         ptrs = self._ptrs(state)
+        qrec = self._decode_records(cfg, q.device)
         check(lib.coda_b200_decode_attend(
             C.byref(cfg), C.byref(ptrs), rp, token_already_written, q.data_ptr(), q.stride(0),
             lam_logit.data_ptr(), lam_logit.stride(0), inv_freq.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
-            _p(nw), out.data_ptr(), out.stride(0), self._status_word(q.device).data_ptr(), _stream()),
+            _p(nw), qrec.data_ptr(), out.data_ptr(), out.stride(0), self._status_word(q.device).data_ptr(), _stream()),
             "coda_b200_decode_attend")
+
+    def decode_attend_prepared_launch(self, cfg, state, out) -> None:
+        """One launch of the decode attention kernel on the records the last fused cache write left behind."""
+        _, _, _, _, nw = self._consts(out.device, out.dtype)
+        ptrs = self._ptrs(state)
+        check(lib.coda_b200_decode_attend_prepared(
+            C.byref(cfg), C.byref(ptrs), self._decode_records(cfg, out.device).data_ptr(), _p(nw), out.data_ptr(),
+            out.stride(0), self._status_word(out.device).data_ptr(), _stream()), "coda_b200_decode_attend_prepared")
 
     def step_graphable(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos) -> torch.Tensor:
         """The default ``step`` (write, then attend) with no host-side branching on the state, so that it

@@ -21,6 +21,9 @@
 #include "coda_common.cuh"
 #include "tma_utils.cuh"
 #include "tensor_maps.h"
+#include "decode_record.h"
+
+extern "C" int coda_b200_decode_attend_supported(const coda_layer_cfg* cfg);
 
 namespace {
 
@@ -33,11 +36,9 @@ constexpr int DA_THREADS = (DA_CWARPS + DA_AWARPS + 4) * 32;   // the producer's
 struct DecodeParams {
   int B, H, Hkv, G, Lbuf, mask_unused, norm_full, interleaved, angle_bf16, stages;
   float eps, scale_log2;
-  coda_ring_pos rp; int W; int pos_minus_one;     // query position = ring position (- 1 when the token was written first)
-  const bf16* q; long long q_bs;                  // raw query projection [B][H*Dh]
-  const bf16* lam_logit; long long lam_bs;        // [B][H]
-  const float* inv_freq; const bf16* cos_t; const bf16* sin_t;
-  const uint8_t* allowed;
+  coda_ring_pos rp; int W;                        // (preparation kernel only)
+  unsigned char* qrec;                            // decode records, one per (state, KV head) plane
+  const uint8_t* allowed;                         // (preparation kernel only)
   const bf16* norm_w;
   bf16* out; long long out_bs;
   int* status;
@@ -84,30 +85,85 @@ __device__ __forceinline__ uint32_t tile_off(int s, int c) {
 template <int DH>
 struct DecodeSmem {
   static constexpr int TILE_BYTES = DA_TILE * DH * 2;
-  static constexpr int QSTR = DH + 8;               // padded row stride of the staged queries (elements)
-  int comb, sq, sml, slam, scs, bars, sal, total;
-  __host__ __device__ DecodeSmem(int stages, int G, int nst) {
+  int comb, rec, rec_stride, sml, bars, total;
+  __host__ __device__ DecodeSmem(int stages, int G, int Lbuf) {
     int o = stages * 2 * TILE_BYTES;
     comb = o; o += DA_CWARPS * 2 * G * DH * 4;      // [DA_CWARPS][2G][DH] partial outputs
-    sq = o;   o += 2 * 16 * QSTR * 2;               // [2][16][QSTR] staged queries (double-buffered)
+    rec_stride = (DecodeRecord::bytes(G, DH, Lbuf) + 127) / 128 * 128;
+    rec = o;  o += 2 * rec_stride;                  // [2] decode records (double-buffered)
     sml = o;  o += 2 * DA_CWARPS * 16 * 4;          // [2][DA_CWARPS][16]  (m, l)
-    slam = o; o += 2 * 8 * 4;                       // [2][8] lambda
-    scs = o;  o += DH * 4;                          // [DH/2] cos, [DH/2] sin
-    bars = o; o += (2 * DA_MAX_STAGES + 4) * 8;     // full[], empty[], q_ready[2], comb_full, comb_free
-    sal = o;  o += 2 * nst * DA_TILE;               // [2][nst * DA_TILE] visibility mask
+    bars = o; o += (2 * DA_MAX_STAGES + 6) * 8;     // full[], empty[], q_ready[2], q_free[2], comb_full, comb_free
     total = o;
   }
 };
 
+// Decode record of one plane from the raw query projection (used when the cache write has not prepared it).
+template <int DH>
+__global__ void __launch_bounds__(128) decode_prep_kernel(DecodeParams p, const bf16* q, long long q_bs, const bf16* lam_logit,
+                                                          long long lam_bs, const float* inv_freq, const bf16* cos_t,
+                                                          const bf16* sin_t, int pos_minus_one) {
+  constexpr int HALF = DH / 2, QSTR = DH + 8;
+  __shared__ float sCS[DH];
+  const int plane = blockIdx.x, b = plane / p.Hkv, hk = plane % p.Hkv, tid = threadIdx.x, G = p.G;
+  unsigned char* rec = p.qrec + (long long)plane * DecodeRecord::bytes(G, DH, p.Lbuf);
+  bf16* q_s = reinterpret_cast<bf16*>(rec);
+  const long long qpos = ring_now(p.rp, p.W).pos - pos_minus_one;
+  for (int i = tid; i < HALF; i += blockDim.x) {
+    float ta = (float)qpos, inv = inv_freq[i];
+    if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
+    float ang = __fmul_rn(ta, inv);
+    if (p.angle_bf16) ang = bf16_round(ang);
+    float c = cosf(ang), s = sinf(ang);
+    if (p.angle_bf16) { c = bf16_round(c); s = bf16_round(s); }
+    sCS[i] = bf16_round(c);
+    sCS[HALF + i] = bf16_round(s);
+  }
+  __syncthreads();
+  const bf16* qrow = q + (long long)b * q_bs + (long long)hk * G * DH;
+  const int rows = DecodeRecord::qrows(G);
+  // item (g, i): RoPE'd elements 2i, 2i+1 of head g (primitives.py:99-113) and their rotation by theta
+  for (int w = tid; w < rows * HALF; w += blockDim.x) {
+    const int g = w / HALF, i = w % HALF;
+    if (g >= G) {
+      if (g >= 2 * G) *reinterpret_cast<uint32_t*>(q_s + g * QSTR + 2 * i) = 0u;
+      continue;
+    }
+    const bf16* qh = qrow + g * DH;
+    float e0, e1;
+    if (p.interleaved) {
+      const float a0 = __bfloat162float(qh[2 * i]), a1 = __bfloat162float(qh[2 * i + 1]);
+      const float c = sCS[i], s = sCS[HALF + i];
+      e0 = t_sub<bf16>(t_mul<bf16>(a0, c), t_mul<bf16>(a1, s));
+      e1 = t_add<bf16>(t_mul<bf16>(a0, s), t_mul<bf16>(a1, c));
+    } else {
+      const bool lo = 2 * i < HALF;
+      const int pi = lo ? 2 * i : 2 * i - HALF;
+      const float a0 = __bfloat162float(qh[pi]), a1 = __bfloat162float(qh[pi + 1]);
+      const float b0 = __bfloat162float(qh[pi + HALF]), b1 = __bfloat162float(qh[pi + HALF + 1]);
+      const float c0 = sCS[pi], s0 = sCS[HALF + pi], c1 = sCS[pi + 1], s1 = sCS[HALF + pi + 1];
+      e0 = lo ? t_add<bf16>(t_mul<bf16>(a0, c0), t_mul<bf16>(-b0, s0)) : t_add<bf16>(t_mul<bf16>(b0, c0), t_mul<bf16>(a0, s0));
+      e1 = lo ? t_add<bf16>(t_mul<bf16>(a1, c1), t_mul<bf16>(-b1, s1)) : t_add<bf16>(t_mul<bf16>(b1, c1), t_mul<bf16>(a1, s1));
+    }
+    const float ct = __bfloat162float(cos_t[(hk * G + g) * HALF + i]), st = __bfloat162float(sin_t[(hk * G + g) * HALF + i]);
+    const float n0 = t_sub<bf16>(t_mul<bf16>(e0, ct), t_mul<bf16>(e1, st));
+    const float n1 = t_add<bf16>(t_mul<bf16>(e0, st), t_mul<bf16>(e1, ct));
+    *reinterpret_cast<uint32_t*>(q_s + g * QSTR + 2 * i) = pack_bf16(e0, e1);
+    *reinterpret_cast<uint32_t*>(q_s + (G + g) * QSTR + 2 * i) = pack_bf16(n0, n1);
+  }
+  float* lam = reinterpret_cast<float*>(rec + DecodeRecord::lam_off(G, DH));
+  if (tid < 8) lam[tid] = tid < G ? t_sigmoid<bf16>(__bfloat162float(lam_logit[(long long)b * lam_bs + hk * G + tid])) : 0.f;
+  uint8_t* mk = rec + DecodeRecord::mask_off(G, DH);
+  const uint8_t* alb = p.allowed + (long long)b * p.Lbuf;
+  for (int i = tid; i < DecodeRecord::mask_bytes(p.Lbuf); i += blockDim.x) mk[i] = i < p.Lbuf ? alb[i] : 0;
+}
+
 template <int DH, int NQ>
 __global__ void __launch_bounds__(DA_THREADS, 1)
 decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
-  constexpr int HALF = DH / 2;
   constexpr int KSTEPS = DH / 16;            // k-steps of Q.K^T
   constexpr int MT_O = DH / 16;              // m-tiles of the (transposed) output
   constexpr int TILE_BYTES = DA_TILE * DH * 2;
   constexpr int QSTR = DH + 8;
-  constexpr int AT = DA_AWARPS * 32;         // auxiliary threads
 
   extern __shared__ unsigned char smem_raw[];
   // the swizzled TMA tiles need a 1024-byte aligned base; the launch reserves the slack
@@ -116,93 +172,27 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   const int G = p.G, RL = 2 * G, S = p.stages;
   const int nst = (p.Lbuf + DA_TILE - 1) / DA_TILE;
   const int nplanes = p.B * p.Hkv;
-  const DecodeSmem<DH> L(S, G, nst);
+  const DecodeSmem<DH> L(S, G, p.Lbuf);
+  const int rec_bytes = DecodeRecord::bytes(G, DH, p.Lbuf);
+  const int lam_off = DecodeRecord::lam_off(G, DH), mask_off = DecodeRecord::mask_off(G, DH);
   unsigned char* stage0 = smem;
   float* comb = reinterpret_cast<float*>(smem + L.comb);
-  bf16* sQ = reinterpret_cast<bf16*>(smem + L.sq);
+  unsigned char* rec0 = smem + L.rec;
   float* sML = reinterpret_cast<float*>(smem + L.sml);
-  float* sLam = reinterpret_cast<float*>(smem + L.slam);
-  float* sCS = reinterpret_cast<float*>(smem + L.scs);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
   uint64_t* empty = full + DA_MAX_STAGES;
-  uint64_t* q_ready = empty + DA_MAX_STAGES;       // [2]
-  uint64_t* comb_full = q_ready + 2;
+  uint64_t* q_ready = empty + DA_MAX_STAGES;       // [2] record of the plane has landed
+  uint64_t* q_free = q_ready + 2;                  // [2] record buffer may be overwritten
+  uint64_t* comb_full = q_free + 2;
   uint64_t* comb_free = comb_full + 1;
-  uint8_t* sAl = smem + L.sal;
-  const int al_stride = nst * DA_TILE;
-
-  // ---- auxiliary warps: first requests, issued before the producer starts to fill the ring ----
-  const bool is_aux = warp >= DA_CWARPS && warp < DA_CWARPS + DA_AWARPS;
-  const int at = tid - DA_CWARPS * 32, aw = warp - DA_CWARPS;
-  // Global loads of these warps queue behind the tile traffic of the whole chip (a few thousand cycles when
-  // the ring is being filled), so every input of a plane is requested in ONE batch into registers
-  // (fetch), long before it is consumed (stage).  Item (g, i): RoPE'd elements 2i and 2i+1 of head g
-  // (signal row g) and their learned (even, odd) rotation by theta (noise row G + g).
-  constexpr int ITEMS = (8 * HALF + AT - 1) / AT;        // G <= 8
-  constexpr int ALW = (4096 / 4 + AT - 1) / AT;          // mask words per thread (Lbuf <= 4096)
-  struct Inputs { uint32_t q0[ITEMS], q1[ITEMS], al[ALW]; bf16 ct[ITEMS], st[ITEMS]; float lam; };
-  // Two sets: set (k % 2) holds the inputs of this CTA's k-th plane.  A request stands behind everything the
-  // producer has in flight for this SM (a full ring: several microseconds at this SM's share of the HBM
-  // bandwidth), so it is made two planes ahead.
-  Inputs inA, inB;
-  auto fetch = [&](int plane, Inputs& in) {
-    const int b = plane / p.Hkv, hk = plane % p.Hkv;
-    const bf16* qrow = p.q + (long long)b * p.q_bs + (long long)hk * G * DH;
-#pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-      const int w = at + it * AT;
-      in.q0[it] = in.q1[it] = 0u;
-      in.ct[it] = in.st[it] = __float2bfloat16_rn(0.f);
-      if (w < G * HALF) {
-        const int g = w / HALF, i = w % HALF;
-        const bf16* qh = qrow + g * DH;
-        if (p.interleaved) {
-          in.q0[it] = *reinterpret_cast<const uint32_t*>(qh + 2 * i);
-        } else {
-          const int pi = 2 * i < HALF ? 2 * i : 2 * i - HALF;        // pair index of element 2i (2i+1: the next)
-          in.q0[it] = *reinterpret_cast<const uint32_t*>(qh + pi);
-          in.q1[it] = *reinterpret_cast<const uint32_t*>(qh + pi + HALF);
-        }
-        in.ct[it] = p.cos_t[(hk * G + g) * HALF + i];
-        in.st[it] = p.sin_t[(hk * G + g) * HALF + i];
-      }
-    }
-    in.lam = 0.f;
-    if (at < G) in.lam = __bfloat162float(p.lam_logit[(long long)b * p.lam_bs + hk * G + at]);
-    const uint8_t* alb = p.allowed + (long long)b * p.Lbuf;
-    const bool al4 = (reinterpret_cast<uintptr_t>(alb) & 3) == 0;
-#pragma unroll
-    for (int a = 0; a < ALW; ++a) {
-      const int i0 = (at + a * AT) * 4;
-      uint32_t wv = 0;
-      if (i0 < p.Lbuf) {
-        if (al4 && i0 + 3 < p.Lbuf) wv = *reinterpret_cast<const uint32_t*>(alb + i0);
-        else for (int e = 0; e < 4; ++e) if (i0 + e < p.Lbuf) wv |= (uint32_t)alb[i0 + e] << (8 * e);
-      }
-      in.al[a] = wv;
-    }
-  };
-  constexpr int DV = 4;                                  // output dims per lane in the epilogue: 4*lane .. 4*lane+3
-  const bool dact = 4 * lane < DH;                       // (head_dim 64: the upper half-warp idles there)
-  float nw[DV], inv_pre = 0.f;
-  long long steps_pre = 0;
-  if (is_aux) {
-    if ((int)blockIdx.x < nplanes) fetch(blockIdx.x, inA);
-    if ((int)(blockIdx.x + gridDim.x) < nplanes) fetch(blockIdx.x + gridDim.x, inB);
-    if (at < HALF) inv_pre = p.inv_freq[at];
-    if (p.rp.step_dev != nullptr) steps_pre = *p.rp.step_dev;
-#pragma unroll
-    for (int k = 0; k < DV; ++k) nw[k] = (p.norm_full && dact) ? __bfloat162float(p.norm_w[4 * lane + k]) : 1.f;
-  }
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
-    mbar_init(&q_ready[0], DA_AWARPS); mbar_init(&q_ready[1], DA_AWARPS);
+    mbar_init(&q_ready[0], 1); mbar_init(&q_ready[1], 1);
+    mbar_init(&q_free[0], DA_CWARPS + DA_AWARPS); mbar_init(&q_free[1], DA_CWARPS + DA_AWARPS);
     mbar_init(comb_full, DA_CWARPS); mbar_init(comb_free, DA_AWARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // The producer starts only here, after the auxiliary warps have made their first requests: whatever is
-  // requested later (instruction and constant fetches included) stands behind a ring's worth of tile traffic.
   __syncthreads();
 
   // Registers follow the roles (per warpgroup): the consumers hold the output accumulators and the query
@@ -210,11 +200,23 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   if (warp >= DA_CWARPS + DA_AWARPS) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp > DA_CWARPS + DA_AWARPS) return;
-    // ---------------- producer: keep the ring of K/V tiles full, across plane boundaries ----------------
+    // ---------------- producer: records first, then the ring of K/V tiles, across plane boundaries ----------------
     if (lane == 0) {
-      int bi = 0, round = 0;                               // ring slot and how often the ring has wrapped
-      for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x) {
+      int bi = 0, round = 0, i = 0;                        // ring slot, how often the ring has wrapped, plane count
+      // k-th plane of this CTA -> record buffer k % 2; the buffer was last used by plane k - 2
+      auto record_free = [&](int k) { return k < 2 || mbar_try(&q_free[k & 1], ((k >> 1) - 1) & 1); };
+      auto load_record = [&](int plane, int k) {
+        const int buf = k & 1;
+        mbar_expect_tx(&q_ready[buf], rec_bytes);
+        tma::bulk_load(rec0 + buf * L.rec_stride, p.qrec + (long long)plane * rec_bytes, rec_bytes, &q_ready[buf]);
+      };
+      if ((int)blockIdx.x < nplanes) load_record(blockIdx.x, 0);
+      for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
+        // The next plane's record is requested as soon as its buffer is free -- normally before this plane's
+        // first tile, so that it never stands behind a ring's worth of tile traffic -- without holding up the tiles.
+        bool pending = plane + (int)gridDim.x < nplanes;
         for (int s = 0; s < nst; ++s) {
+          if (pending && record_free(i + 1)) { load_record(plane + gridDim.x, i + 1); pending = false; }
           if (round > 0) mbar_wait(&empty[bi], (round - 1) & 1, p.status, 1);
           mbar_expect_tx(&full[bi], 2 * TILE_BYTES);
           unsigned char* kd = stage0 + bi * 2 * TILE_BYTES;
@@ -226,6 +228,10 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
           }
           if (++bi == S) { bi = 0; ++round; }
         }
+        if (pending) {
+          mbar_wait(&q_free[(i + 1) & 1], (((i + 1) >> 1) - 1) & 1, p.status, 6);
+          load_record(plane + gridDim.x, i + 1);
+        }
       }
     }
     return;
@@ -233,75 +239,21 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
 
   if (warp >= DA_CWARPS) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
-    // ---------------- auxiliary warps: queries of the next plane, merge + epilogue of the previous ----------------
-    auto stage = [&](int buf, const Inputs& in) {
-      bf16* q_s = sQ + buf * 16 * QSTR;
+    // ---------------- auxiliary warps: merge of the eight partial softmaxes + epilogue, one warp per query head ----------------
+    const int aw = warp - DA_CWARPS;
+    constexpr int DV = 4;                                  // output dims per lane: 4*lane .. 4*lane+3
+    const bool dact = 4 * lane < DH;                       // (head_dim 64: the upper half-warp idles)
+    float nw[DV];
 #pragma unroll
-      for (int it = 0; it < ITEMS; ++it) {
-        const int w = at + it * AT;
-        if (w < G * HALF) {
-          const int g = w / HALF, i = w % HALF;
-          const float a0 = __uint_as_float(in.q0[it] << 16), a1 = __uint_as_float(in.q0[it] & 0xffff0000u);
-          const float b0 = __uint_as_float(in.q1[it] << 16), b1 = __uint_as_float(in.q1[it] & 0xffff0000u);
-          float e0, e1;                                    // RoPE'd elements 2i, 2i+1 (primitives.py:99-113)
-          if (p.interleaved) {
-            const float c = sCS[i], s = sCS[HALF + i];
-            e0 = t_sub<bf16>(t_mul<bf16>(a0, c), t_mul<bf16>(a1, s));
-            e1 = t_add<bf16>(t_mul<bf16>(a0, s), t_mul<bf16>(a1, c));
-          } else {
-            const bool lo = 2 * i < HALF;
-            const int pi = lo ? 2 * i : 2 * i - HALF;
-            const float c0 = sCS[pi], s0 = sCS[HALF + pi], c1 = sCS[pi + 1], s1 = sCS[HALF + pi + 1];
-            e0 = lo ? t_add<bf16>(t_mul<bf16>(a0, c0), t_mul<bf16>(-b0, s0)) : t_add<bf16>(t_mul<bf16>(b0, c0), t_mul<bf16>(a0, s0));
-            e1 = lo ? t_add<bf16>(t_mul<bf16>(a1, c1), t_mul<bf16>(-b1, s1)) : t_add<bf16>(t_mul<bf16>(b1, c1), t_mul<bf16>(a1, s1));
-          }
-          const float ct = __bfloat162float(in.ct[it]), st = __bfloat162float(in.st[it]);
-          const float n0 = t_sub<bf16>(t_mul<bf16>(e0, ct), t_mul<bf16>(e1, st));
-          const float n1 = t_add<bf16>(t_mul<bf16>(e0, st), t_mul<bf16>(e1, ct));
-          *reinterpret_cast<uint32_t*>(q_s + g * QSTR + 2 * i) = pack_bf16(e0, e1);
-          *reinterpret_cast<uint32_t*>(q_s + (G + g) * QSTR + 2 * i) = pack_bf16(n0, n1);
-        }
-      }
-      if (at < G) sLam[buf * 8 + at] = t_sigmoid<bf16>(in.lam);
-      uint8_t* al_s = sAl + buf * al_stride;
-#pragma unroll
-      for (int a = 0; a < ALW; ++a) {
-        const int i0 = (at + a * AT) * 4;
-        if (i0 < al_stride) *reinterpret_cast<uint32_t*>(al_s + i0) = in.al[a];
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&q_ready[buf]);
-    };
-
-    {
-      // RoPE cos/sin of the query position (ring position + device step counter): the same for every plane
-      const long long qpos = p.rp.pos + steps_pre - p.pos_minus_one;
-      if (at < HALF) {
-        float ta = (float)qpos, inv = inv_pre;
-        if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
-        float ang = __fmul_rn(ta, inv);
-        if (p.angle_bf16) ang = bf16_round(ang);
-        float c = cosf(ang), s = sinf(ang);
-        if (p.angle_bf16) { c = bf16_round(c); s = bf16_round(s); }
-        sCS[at] = bf16_round(c);
-        sCS[HALF + at] = bf16_round(s);
-      }
-      for (int i = at; i < 2 * 16 * QSTR; i += AT) sQ[i] = __float2bfloat16_rn(0.f);   // rows >= 2G stay zero
-      bar_aux();
-    }
-    const int gstep = (int)gridDim.x;
-    if ((int)blockIdx.x < nplanes) stage(0, inA);
-    if ((int)blockIdx.x + 2 * gstep < nplanes) fetch(blockIdx.x + 2 * gstep, inA);
-
-    // One plane of this CTA (its i-th); `nxt` is the input set of the following one.
-    auto aux_plane = [&](int i, int plane, Inputs& nxt) {
-      // queries of the next plane (requested two planes ago) first, then the request for the plane that will
-      // use the same set: both are off the consumers' critical path, which is inside the current plane's tiles
-      if (plane + gstep < nplanes) stage((i + 1) & 1, nxt);
-      if (plane + 3 * gstep < nplanes) fetch(plane + 3 * gstep, nxt);
-      // ---- merge of the eight partial softmaxes; one warp per query head: sig - lam*noise, RMSNorm, store ----
+    for (int k = 0; k < DV; ++k) nw[k] = (p.norm_full && dact) ? __bfloat162float(p.norm_w[4 * lane + k]) : 1.f;
+    int i = 0;
+    for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
       mbar_wait(comb_full, i & 1, p.status, 5);
       const int b = plane / p.Hkv, hk = plane % p.Hkv;
+      const float* sLam = reinterpret_cast<const float*>(rec0 + (i & 1) * L.rec_stride + lam_off);
+      const float lam_a = sLam[aw], lam_b = sLam[(aw + DA_AWARPS) & 7];   // heads aw and aw + 4 of the group (G <= 8)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_free[i & 1]);          // the record buffer is no longer needed by this warp
       for (int g = aw; g < G; g += DA_AWARPS) {
         // lanes 0-7: partial w = lane of the signal row g; lanes 8-15: of the noise row G + g (16-31 mirror them)
         const int mrow = ((lane >> 3) & 1) * G + g, mw = lane & 7;
@@ -332,7 +284,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
 #pragma unroll
           for (int k = 0; k < DV; ++k) v[st][k] = bf16_round(acc[k] * inv);
         }
-        const float lam = sLam[(i & 1) * 8 + g];
+        const float lam = g == aw ? lam_a : lam_b;
         float diff[DV], sq = 0.f;
 #pragma unroll
         for (int k = 0; k < DV; ++k) {
@@ -354,10 +306,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(comb_free);
-    };
-    for (int i = 0, plane = blockIdx.x; plane < nplanes; i += 2, plane += 2 * gstep) {
-      aux_plane(i, plane, inB);
-      if (plane + gstep < nplanes) aux_plane(i + 1, plane + gstep, inA);
     }
     return;
   }
@@ -375,12 +323,13 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
     const int buf = i & 1;
     mbar_wait(&q_ready[buf], (i >> 1) & 1, p.status, 3);
-    const uint8_t* al_s = sAl + buf * al_stride;
+    const unsigned char* rec = rec0 + buf * L.rec_stride;
+    const uint8_t* al_s = rec + mask_off;
     // B fragments of Q^T: one ldmatrix.x4 covers two k-steps of one n-tile (matrices: dh chunks 4j .. 4j+3)
     uint32_t qf[NQ][KSTEPS / 2][4];
 #pragma unroll
     for (int nq = 0; nq < NQ; ++nq) {
-      const uint32_t qbase = smem_u32(sQ + buf * 16 * QSTR) + (uint32_t)(((nq * 8 + lr) * QSTR + li * 8) * 2);
+      const uint32_t qbase = smem_u32(rec) + (uint32_t)(((nq * 8 + lr) * QSTR + li * 8) * 2);
 #pragma unroll
       for (int j = 0; j < KSTEPS / 2; ++j) ldsm_x4(qf[nq][j], qbase + j * 64);
     }
@@ -463,6 +412,8 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       if (bi >= S) { bi -= S; ++round; }
     }
 
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_free[buf]);              // queries are in registers, the mask is no longer read
     // ---- hand the partial softmax of this warp to the auxiliary warps ----
 #pragma unroll
     for (int nq = 0; nq < NQ; ++nq)
@@ -510,14 +461,13 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
 template <int DH, int NQ>
 int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, cudaStream_t s) {
   constexpr int BUDGET = 226 * 1024;
-  const int nst = (p.Lbuf + DA_TILE - 1) / DA_TILE;
   // as many ring stages as fit beside the fixed buffers (at least 2, at most DA_MAX_STAGES)
-  const int fixed = DecodeSmem<DH>(0, p.G, nst).total + 1024;
+  const int fixed = DecodeSmem<DH>(0, p.G, p.Lbuf).total + 1024;
   int stages = (BUDGET - fixed) / (2 * DecodeSmem<DH>::TILE_BYTES);
   if (stages > DA_MAX_STAGES) stages = DA_MAX_STAGES;
   CODA_REQUIRE(stages >= 2, CODA_ERR_LIMIT, "decode_attend: %d slots leave no room for the tile ring in shared memory", p.Lbuf);
   p.stages = stages;
-  const size_t smem = (size_t)DecodeSmem<DH>(stages, p.G, nst).total + 1024;
+  const size_t smem = (size_t)DecodeSmem<DH>(stages, p.G, p.Lbuf).total + 1024;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(decode_attend_kernel<DH, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BUDGET);
@@ -535,6 +485,39 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
   return CODA_OK;
 }
 
+int check_common(const coda_layer_cfg* cfg, const coda_state_ptrs* st, const void* qrec, const void* norm_w, const void* out) {
+  CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "decode_attend: invalid layer configuration");
+  CODA_REQUIRE(coda_b200_decode_attend_supported(cfg), CODA_ERR_ARG,
+               "decode_attend: needs bf16, head_dim 64 or 128 and at most 8 query heads per KV head");
+  CODA_REQUIRE(qrec && out && st->k_buf && st->v_buf && st->allowed, CODA_ERR_ARG, "decode_attend: null pointer");
+  CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "decode_attend: head-norm weight missing");
+  CODA_REQUIRE(((uintptr_t)st->k_buf % 16 == 0) && ((uintptr_t)st->v_buf % 16 == 0) && ((uintptr_t)qrec % 16 == 0), CODA_ERR_ARG,
+               "decode_attend: k_buf / v_buf / record buffer must be 16-byte aligned");
+  return CODA_OK;
+}
+
+DecodeParams make_params(const coda_layer_cfg* cfg, const coda_state_ptrs* st, void* qrec, const void* norm_w, void* out,
+                         int64_t out_bs, int32_t* status) {
+  DecodeParams p;
+  p.B = cfg->B; p.H = cfg->H; p.Hkv = cfg->Hkv; p.G = cfg->H / cfg->Hkv; p.Lbuf = cfg->W + cfg->Me + cfg->Ms;
+  p.mask_unused = cfg->mask_unused; p.norm_full = cfg->head_norm_full; p.interleaved = cfg->rope_interleaved;
+  p.angle_bf16 = cfg->angle_dtype == CODA_BF16; p.stages = 0; p.eps = cfg->eps;
+  p.scale_log2 = 1.4426950408889634f / sqrtf((float)cfg->Dh);
+  p.rp = coda_ring_pos{0, 0, 0, nullptr}; p.W = cfg->W;
+  p.qrec = (unsigned char*)qrec; p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w;
+  p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
+  return p;
+}
+
+int launch_main(const coda_layer_cfg* cfg, const coda_state_ptrs* st, const DecodeParams& p, cudaStream_t s) {
+  CUtensorMap km, vm;
+  CODA_REQUIRE(tmaps::plane_map(&km, st->k_buf, cfg->B * cfg->Hkv, p.Lbuf, cfg->Dh) &&
+               tmaps::plane_map(&vm, st->v_buf, cfg->B * cfg->Hkv, p.Lbuf, cfg->Dh), CODA_ERR_LAUNCH,
+               "decode_attend: cuTensorMapEncodeTiled failed");
+  if (p.G <= 4) return cfg->Dh == 128 ? launch_decode<128, 1>(km, vm, p, s) : launch_decode<64, 1>(km, vm, p, s);
+  return cfg->Dh == 128 ? launch_decode<128, 2>(km, vm, p, s) : launch_decode<64, 2>(km, vm, p, s);
+}
+
 }  // namespace
 
 // True when the tuned kernel covers this configuration; otherwise callers use the generic kernels.
@@ -545,35 +528,40 @@ extern "C" int coda_b200_decode_attend_supported(const coda_layer_cfg* cfg) {
          (size_t)(cfg->W + cfg->Me + cfg->Ms) <= 4096 && tmaps::available();
 }
 
+// Bytes of the decode-record buffer (one record per state and KV head) for this configuration.
+extern "C" int64_t coda_b200_decode_record_bytes(const coda_layer_cfg* cfg) {
+  if (!coda_cfg_ok(cfg)) return 0;
+  return (int64_t)cfg->B * cfg->Hkv * DecodeRecord::bytes(cfg->H / cfg->Hkv, cfg->Dh, cfg->W + cfg->Me + cfg->Ms);
+}
+
 extern "C" int coda_b200_decode_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
                                        int32_t token_already_written,
                                        const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
                                        const float* inv_freq, const void* cos_theta, const void* sin_theta,
-                                       const void* norm_w, void* out, int64_t out_bs, int32_t* status,
+                                       const void* norm_w, void* qrec, void* out, int64_t out_bs, int32_t* status,
                                        coda_stream_t stream) {
-  CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "decode_attend: invalid layer configuration");
-  CODA_REQUIRE(coda_b200_decode_attend_supported(cfg), CODA_ERR_ARG,
-               "decode_attend: needs bf16, head_dim 64 or 128 and at most 8 query heads per KV head");
-  CODA_REQUIRE(q_raw && lam_logit && inv_freq && cos_theta && sin_theta && out && st->k_buf && st->v_buf && st->allowed,
-               CODA_ERR_ARG, "decode_attend: null pointer");
-  CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "decode_attend: head-norm weight missing");
-  CODA_REQUIRE(((uintptr_t)st->k_buf % 16 == 0) && ((uintptr_t)st->v_buf % 16 == 0), CODA_ERR_ARG,
-               "decode_attend: k_buf / v_buf must be 16-byte aligned");
-  const int Lbuf = cfg->W + cfg->Me + cfg->Ms;
-  CUtensorMap km, vm;
-  CODA_REQUIRE(tmaps::plane_map(&km, st->k_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh) &&
-               tmaps::plane_map(&vm, st->v_buf, cfg->B * cfg->Hkv, Lbuf, cfg->Dh), CODA_ERR_LAUNCH,
-               "decode_attend: cuTensorMapEncodeTiled failed");
-  DecodeParams p;
-  p.B = cfg->B; p.H = cfg->H; p.Hkv = cfg->Hkv; p.G = cfg->H / cfg->Hkv; p.Lbuf = Lbuf;
-  p.mask_unused = cfg->mask_unused; p.norm_full = cfg->head_norm_full; p.interleaved = cfg->rope_interleaved;
-  p.angle_bf16 = cfg->angle_dtype == CODA_BF16; p.eps = cfg->eps;
-  p.scale_log2 = 1.4426950408889634f / sqrtf((float)cfg->Dh);
-  p.rp = rp; p.W = cfg->W; p.pos_minus_one = token_already_written ? 1 : 0;
-  p.q = (const bf16*)q_raw; p.q_bs = q_bs; p.lam_logit = (const bf16*)lam_logit; p.lam_bs = lam_bs;
-  p.inv_freq = inv_freq; p.cos_t = (const bf16*)cos_theta; p.sin_t = (const bf16*)sin_theta;
-  p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w; p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
+  int rc = check_common(cfg, st, qrec, norm_w, out);
+  if (rc != CODA_OK) return rc;
+  CODA_REQUIRE(q_raw && lam_logit && inv_freq && cos_theta && sin_theta, CODA_ERR_ARG, "decode_attend: null pointer");
+  DecodeParams p = make_params(cfg, st, qrec, norm_w, out, out_bs, status);
+  p.rp = rp;
   cudaStream_t s = (cudaStream_t)stream;
-  if (p.G <= 4) return cfg->Dh == 128 ? launch_decode<128, 1>(km, vm, p, s) : launch_decode<64, 1>(km, vm, p, s);
-  return cfg->Dh == 128 ? launch_decode<128, 2>(km, vm, p, s) : launch_decode<64, 2>(km, vm, p, s);
+  const int nplanes = cfg->B * cfg->Hkv;
+  if (cfg->Dh == 128)
+    decode_prep_kernel<128><<<nplanes, 128, 0, s>>>(p, (const bf16*)q_raw, q_bs, (const bf16*)lam_logit, lam_bs, inv_freq,
+                                                    (const bf16*)cos_theta, (const bf16*)sin_theta, token_already_written ? 1 : 0);
+  else
+    decode_prep_kernel<64><<<nplanes, 128, 0, s>>>(p, (const bf16*)q_raw, q_bs, (const bf16*)lam_logit, lam_bs, inv_freq,
+                                                   (const bf16*)cos_theta, (const bf16*)sin_theta, token_already_written ? 1 : 0);
+  CODA_CHECK_LAUNCH("decode_prep");
+  return launch_main(cfg, st, p, s);
+}
+
+extern "C" int coda_b200_decode_attend_prepared(const coda_layer_cfg* cfg, const coda_state_ptrs* st, const void* qrec,
+                                                const void* norm_w, void* out, int64_t out_bs, int32_t* status,
+                                                coda_stream_t stream) {
+  int rc = check_common(cfg, st, qrec, norm_w, out);
+  if (rc != CODA_OK) return rc;
+  const DecodeParams p = make_params(cfg, st, const_cast<void*>(qrec), norm_w, out, out_bs, status);
+  return launch_main(cfg, st, p, (cudaStream_t)stream);
 }

@@ -3,6 +3,7 @@
 #include "coda_common.cuh"
 #include "tma_utils.cuh"
 #include "bank_score.cuh"
+#include "decode_record.h"
 
 struct StepParams {
   coda_layer_cfg c;
@@ -18,6 +19,9 @@ struct StepParams {
   // two bulk copies issued at kernel entry, so that scoring does not wait on one global round trip per row
   int stage; int stage_off;       // byte offset of the staged caches inside dynamic shared memory
   int* status;
+  // fused mode (cluster kernel, bf16): the decode record of each plane is written as well
+  const void* q_raw; long long q_bs; const void* lam_logit; long long lam_bs;
+  const void* cos_t; const void* sin_t; unsigned char* qrec;
 };
 
 // RoPE'd element d of head-row `row` (Dh values, un-rotated) given cos/sin tables of Dh/2 entries.
@@ -284,7 +288,8 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   float* xdots = sm;                                      // [Hkv][MM] per-head dots of every CTA of the cluster
   float* sc = xdots + Hkv * MM;                           // [MM] reduced scores
   long long* s_last = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(sc + MM) + 7) & ~(uintptr_t)7);  // [Me]
-  unsigned char* s_used = reinterpret_cast<unsigned char*>(s_last + Me);                                         // [MM]
+  unsigned char* s_al = reinterpret_cast<unsigned char*>(s_last + Me);                                           // [Lbuf] slot flags before the write
+  unsigned char* s_used = s_al + W;                                                                              // [MM] the banks' part
 
   T* kb = (T*)p.st.k_buf + ((long long)b * Hkv + h) * Lbuf * DH;       // this head's planes
   T* vb = (T*)p.st.v_buf + ((long long)b * Hkv + h) * Lbuf * DH;
@@ -292,6 +297,10 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   float* gr = p.st.g_recent + (long long)b * W;
   const T* kn = (const T*)p.k_new + (long long)b * p.k_bs + h * DH;
   const T* vn = (const T*)p.v_new + (long long)b * p.v_bs + h * DH;
+
+  // Distributed shared memory of a CTA may be written only once that CTA runs: every CTA announces itself
+  // here and waits for the others just before its first remote store (or before it leaves).
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
   // ---- requests that depend on nothing but (b, h): issued first, consumed later ----
   // bank rows: item it -> (row it/2, half it%2); exact rows first, then summary rows
@@ -311,7 +320,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     }
   };
   load_seg(tid);
-  for (int m = tid; m < MM; m += NT) s_used[m] = al[W + m];
+  for (int m = tid; m < Lbuf; m += NT) s_al[m] = al[m];
   for (int m = tid; m < Me; m += NT) s_last[m] = ((const long long*)p.st.mem_last_exact)[(long long)b * Me + m];
   // the new token's row (element tid < DH: key, DH <= tid < 2*DH: value)
   float nk_a = 0.f, nk_b = 0.f, nv_x = 0.f, eta_raw = 0.f, glog = 0.f;
@@ -334,6 +343,35 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   if (Ms > 0) eta_raw = p.eta_logit[h];
   if (p.raw) { if (c.gated) glog = El<T>::ld((const T*)p.gate_logit + (long long)b * p.gate_bs); }
   else glog = p.gate[b];
+
+  // fused mode: raw query pairs, theta tables and lambda logit (requested now, used last)
+  constexpr int QI = (8 * (DH / 2) + NT - 1) / NT;        // (head, pair) items per thread, G <= 8
+  const bool fused = p.qrec != nullptr;
+  const int G = c.H / Hkv;
+  uint32_t fq0[QI], fq1[QI]; bf16 fct[QI], fst[QI];
+  float flam = 0.f;
+  if (fused) {
+    const bf16* qrow = (const bf16*)p.q_raw + (long long)b * p.q_bs + (long long)h * G * DH;
+#pragma unroll
+    for (int it = 0; it < QI; ++it) {
+      const int w = tid + it * NT;
+      fq0[it] = fq1[it] = 0u; fct[it] = fst[it] = __float2bfloat16_rn(0.f);
+      if (w < G * (DH / 2)) {
+        const int g = w / (DH / 2), i = w % (DH / 2);
+        const bf16* qh = qrow + g * DH;
+        if (c.rope_interleaved) {
+          fq0[it] = *reinterpret_cast<const uint32_t*>(qh + 2 * i);
+        } else {
+          const int pi = 2 * i < DH / 2 ? 2 * i : 2 * i - DH / 2;
+          fq0[it] = *reinterpret_cast<const uint32_t*>(qh + pi);
+          fq1[it] = *reinterpret_cast<const uint32_t*>(qh + pi + DH / 2);
+        }
+        fct[it] = ((const bf16*)p.cos_t)[(h * G + g) * (DH / 2) + i];
+        fst[it] = ((const bf16*)p.sin_t)[(h * G + g) * (DH / 2) + i];
+      }
+    }
+    if (tid < G) flam = __bfloat162float(((const bf16*)p.lam_logit)[(long long)b * p.lam_bs + h * G + tid]);
+  }
 
   const RingNow r = ring_now(p.rp, W);
   float g_new;
@@ -369,7 +407,55 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     else new_k = d < LF ? t_add<T>(t_mul<T>(nk_a, cc), t_mul<T>(-nk_b, ss)) : t_add<T>(t_mul<T>(nk_b, cc), t_mul<T>(nk_a, ss));
   }
 
+  // Decode record of this plane (queries of the token being written, lambda, visibility mask after the write).
+  // `e_on`/`s_on`: bank slots switched on by this write (-1: none).
+  auto write_record = [&](int e_on, int s_on) {
+    if constexpr (sizeof(T) == 2) {
+      constexpr int HALF = DH / 2, QSTR = DH + 8;
+      unsigned char* rec = p.qrec + ((long long)b * Hkv + h) * DecodeRecord::bytes(G, DH, Lbuf);
+      bf16* q_s = reinterpret_cast<bf16*>(rec);
+#pragma unroll
+      for (int it = 0; it < QI; ++it) {
+        const int w = tid + it * NT;
+        if (w < G * HALF) {
+          const int g = w / HALF, i = w % HALF;
+          const float a0 = __uint_as_float(fq0[it] << 16), a1 = __uint_as_float(fq0[it] & 0xffff0000u);
+          const float b0 = __uint_as_float(fq1[it] << 16), b1 = __uint_as_float(fq1[it] & 0xffff0000u);
+          float e0, e1;                                    // RoPE'd elements 2i, 2i+1 (primitives.py:99-113)
+          if (c.rope_interleaved) {
+            e0 = t_sub<T>(t_mul<T>(a0, cs[i]), t_mul<T>(a1, sn[i]));
+            e1 = t_add<T>(t_mul<T>(a0, sn[i]), t_mul<T>(a1, cs[i]));
+          } else {
+            const bool lo = 2 * i < HALF;
+            const int pi = lo ? 2 * i : 2 * i - HALF;
+            e0 = lo ? t_add<T>(t_mul<T>(a0, cs[pi]), t_mul<T>(-b0, sn[pi])) : t_add<T>(t_mul<T>(b0, cs[pi]), t_mul<T>(a0, sn[pi]));
+            e1 = lo ? t_add<T>(t_mul<T>(a1, cs[pi + 1]), t_mul<T>(-b1, sn[pi + 1])) : t_add<T>(t_mul<T>(b1, cs[pi + 1]), t_mul<T>(a1, sn[pi + 1]));
+          }
+          const float ct = __bfloat162float(fct[it]), st = __bfloat162float(fst[it]);
+          const float n0 = t_sub<T>(t_mul<T>(e0, ct), t_mul<T>(e1, st));
+          const float n1 = t_add<T>(t_mul<T>(e0, st), t_mul<T>(e1, ct));
+          __nv_bfloat162 sv = __floats2bfloat162_rn(e0, e1), nv2 = __floats2bfloat162_rn(n0, n1);
+          *reinterpret_cast<__nv_bfloat162*>(q_s + g * QSTR + 2 * i) = sv;
+          *reinterpret_cast<__nv_bfloat162*>(q_s + (G + g) * QSTR + 2 * i) = nv2;
+        }
+      }
+      const int rows = DecodeRecord::qrows(G);
+      for (int w = tid; w < (rows - 2 * G) * HALF; w += NT)   // unused rows of the query tile: zero
+        *reinterpret_cast<uint32_t*>(q_s + (2 * G + w / HALF) * QSTR + 2 * (w % HALF)) = 0u;
+      float* lam = reinterpret_cast<float*>(rec + DecodeRecord::lam_off(G, DH));
+      if (tid < 8) lam[tid] = tid < G ? t_sigmoid<T>(flam) : 0.f;
+      uint8_t* mk = rec + DecodeRecord::mask_off(G, DH);
+      for (int i = tid; i < DecodeRecord::mask_bytes(Lbuf); i += NT) {
+        uint8_t v = 0;
+        if (i < Lbuf) v = (i == ev || (e_on >= 0 && i == W + e_on) || (s_on >= 0 && i == W + Me + s_on)) ? 1 : s_al[i];
+        mk[i] = v;
+      }
+    }
+  };
+
   if (!full) {                                            // memory_banks.py:195-201 (uniform over the grid)
+    if (fused) write_record(-1, -1);
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
     if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
     if (is_v) vb[(long long)ev * DH + d] = nv_raw;
     if (h == 0 && tid == 0) { gr[ev] = g_new; al[ev] = 1; }
@@ -391,6 +477,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   if (is_k && d >= LF) khat[d - LF] = t_div<T>(ke[d], s_den[1]);
   __syncthreads();
 
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");       // all CTAs of the cluster are running
   // ---- per-head dot products of both banks, sent to every CTA of the cluster ----
   for (int base = 0; base < 2 * MM; base += NT) {
     const int it = base + tid;
@@ -499,6 +586,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
 
   // ---- slot updates of this head: the old rows of both banks are requested together ----
   const bool do_e = Me > 0 && s_eflag != 0, do_s = Ms > 0;
+  if (fused) write_record(do_e ? s_eidx : -1, (do_s && s_keep != 0.f) ? s_sidx : -1);
   const long long eoff = (long long)(W + s_eidx) * DH + d, soff = (long long)(W + Me + s_sidx) * DH + d;
   float eo = 0.f, so = 0.f;
   if (do_e && (is_k || is_v)) eo = El<T>::ld((is_k ? kb : vb) + eoff);
@@ -546,7 +634,7 @@ template <typename T, int DH>
 static int launch_step_cluster(const StepParams& p, cudaStream_t s) {
   const coda_layer_cfg& c = p.c;
   const int MM = c.Me + c.Ms;
-  const size_t smem = sizeof(float) * ((size_t)c.Hkv * MM + MM) + 8 + 8 * (size_t)c.Me + MM + 16;
+  const size_t smem = sizeof(float) * ((size_t)c.Hkv * MM + MM) + 8 + 8 * (size_t)c.Me + (size_t)(c.W + MM) + 16;
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(c.Hkv, c.B, 1);
   lc.blockDim = dim3(256, 1, 1);
@@ -564,7 +652,8 @@ static int launch_step_cluster(const StepParams& p, cudaStream_t s) {
 static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
                            const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
                            const float* gate, const float* eta_logit, int raw, const float* inv_freq,
-                           const void* gate_logit, int64_t gate_bs, coda_stream_t stream) {
+                           const void* gate_logit, int64_t gate_bs, coda_stream_t stream,
+                           const StepParams* fused = nullptr) {
   CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "step_write: invalid layer configuration");
   CODA_REQUIRE(st->k_buf && st->v_buf && st->allowed && st->g_recent && k_new && v_new, CODA_ERR_ARG,
                "step_write: null pointer");
@@ -577,12 +666,17 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
   StepParams p; p.c = *cfg; p.st = *st; p.rp = rp;
   p.k_new = k_new; p.k_bs = k_bs; p.v_new = v_new; p.v_bs = v_bs; p.gate = gate; p.eta_logit = eta_logit;
   p.raw = raw; p.inv_freq = inv_freq; p.gate_logit = gate_logit; p.gate_bs = gate_bs;
+  p.q_raw = nullptr; p.q_bs = 0; p.lam_logit = nullptr; p.lam_bs = 0; p.cos_t = nullptr; p.sin_t = nullptr; p.qrec = nullptr;
+  if (fused) {
+    p.q_raw = fused->q_raw; p.q_bs = fused->q_bs; p.lam_logit = fused->lam_logit; p.lam_bs = fused->lam_bs;
+    p.cos_t = fused->cos_t; p.sin_t = fused->sin_t; p.qrec = fused->qrec;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   {
     // cluster variant: one CTA per (state, head); needs a portable cluster size and vector-aligned cache rows
     const size_t es0 = cfg->dtype == CODA_F32 ? 4 : 2;
     const int MM = cfg->Me + cfg->Ms;
-    const size_t csm = sizeof(float) * ((size_t)cfg->Hkv * MM + MM) + 8 + 8 * (size_t)cfg->Me + MM + 16;
+    const size_t csm = sizeof(float) * ((size_t)cfg->Hkv * MM + MM) + 8 + 8 * (size_t)cfg->Me + (size_t)(cfg->W + MM) + 16;
     const bool ok = cfg->Hkv <= 8 && (cfg->Dh == 64 || cfg->Dh == 128) && csm <= 40 * 1024 && cfg->B <= 65535 &&
                     (cfg->Me == 0 || (uintptr_t)st->exact_v_norm % 16 == 0) && (cfg->Ms == 0 || (uintptr_t)st->sum_lf_k_norm % 16 == 0) &&
                     ((size_t)cfg->Dh / 4 * es0) % 16 == 0;
@@ -591,6 +685,7 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
       if (cfg->dtype == CODA_F32) return cfg->Dh == 128 ? launch_step_cluster<float, 128>(p, s) : launch_step_cluster<float, 64>(p, s);
       return cfg->Dh == 128 ? launch_step_cluster<bf16, 128>(p, s) : launch_step_cluster<bf16, 64>(p, s);
     }
+    CODA_REQUIRE(!fused, CODA_ERR_ARG, "step_write_fused: configuration not covered by the cluster kernel");
   }
   const int HD = cfg->Hkv * cfg->Dh, lfd = cfg->Dh - cfg->Dh / 2;
   const int mx = cfg->Me > cfg->Ms ? cfg->Me : cfg->Ms;
@@ -629,4 +724,32 @@ extern "C" int coda_b200_step_write_raw(const coda_layer_cfg* cfg, const coda_st
                                         const void* gate_logit, int64_t gate_bs, const float* inv_freq,
                                         const float* eta_logit, coda_stream_t stream) {
   return step_write_impl(cfg, st, rp, k_raw, k_bs, v_new, v_bs, nullptr, eta_logit, 1, inv_freq, gate_logit, gate_bs, stream);
+}
+
+// The fused write + query preparation runs on the cluster kernel only (bf16, Hkv <= 8, head_dim 64 / 128).
+extern "C" int coda_b200_step_write_fused_supported(const coda_layer_cfg* cfg) {
+  if (!coda_cfg_ok(cfg)) return 0;
+  const int MM = cfg->Me + cfg->Ms, G = cfg->H / cfg->Hkv;
+  const size_t csm = sizeof(float) * ((size_t)cfg->Hkv * MM + MM) + 8 + 8 * (size_t)cfg->Me + (size_t)(cfg->W + MM) + 16;
+  return cfg->dtype == CODA_BF16 && cfg->Hkv <= 8 && G <= 8 && (cfg->Dh == 64 || cfg->Dh == 128) && csm <= 40 * 1024 &&
+         cfg->B <= 65535;
+}
+
+extern "C" int coda_b200_step_write_fused(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                          const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                          const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                          const float* eta_logit,
+                                          const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                          const void* cos_theta, const void* sin_theta, void* qrec,
+                                          coda_stream_t stream) {
+  CODA_REQUIRE(coda_b200_step_write_fused_supported(cfg), CODA_ERR_ARG,
+               "step_write_fused: needs bf16, at most 8 KV heads and 8 query heads per KV head, head_dim 64 or 128");
+  CODA_REQUIRE(q_raw && lam_logit && cos_theta && sin_theta && qrec && ((uintptr_t)qrec % 16 == 0) && ((uintptr_t)q_raw % 4 == 0) &&
+               (q_bs % 2 == 0), CODA_ERR_ARG, "step_write_fused: query-side pointers missing or misaligned");
+  CODA_REQUIRE(st && (cfg->Me == 0 || (uintptr_t)st->exact_v_norm % 16 == 0) && (cfg->Ms == 0 || (uintptr_t)st->sum_lf_k_norm % 16 == 0),
+               CODA_ERR_ARG, "step_write_fused: routing caches must be 16-byte aligned");
+  StepParams f;
+  f.q_raw = q_raw; f.q_bs = q_bs; f.lam_logit = lam_logit; f.lam_bs = lam_bs; f.cos_t = cos_theta; f.sin_t = sin_theta;
+  f.qrec = (unsigned char*)qrec;
+  return step_write_impl(cfg, st, rp, k_raw, k_bs, v_new, v_bs, nullptr, eta_logit, 1, inv_freq, gate_logit, gate_bs, stream, &f);
 }

@@ -122,21 +122,44 @@ int coda_b200_step_write_raw(const coda_layer_cfg* cfg, const coda_state_ptrs* s
                              const void* gate_logit, int64_t gate_bs, const float* inv_freq,
                              const float* eta_logit, coda_stream_t stream);
 
+/* Same as coda_b200_step_write_raw and, in the same launch, prepares the decode attention of the token being
+ * written (the query side of attend_step, src/coda_gqa_l/attention.py:476-514): RoPE of the raw query
+ * projection at position rp.pos, the learned theta rotation, the lambda sigmoid and the slot visibility mask
+ * AFTER this write go into `qrec`, one record per (state, KV head), for coda_b200_decode_attend_prepared.
+ * bf16 only; q_raw [B][H*Dh], lam_logit [B][H] with batch strides; cos_theta/sin_theta [H][Dh/2];
+ * qrec: device buffer of coda_b200_decode_record_bytes(cfg) bytes, 16-byte aligned.  Needs a configuration
+ * for which coda_b200_decode_attend_supported() is true and Hkv <= 8. */
+int coda_b200_step_write_fused(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                               const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                               const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                               const float* eta_logit,
+                               const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                               const void* cos_theta, const void* sin_theta, void* qrec,
+                               coda_stream_t stream);
+int coda_b200_step_write_fused_supported(const coda_layer_cfg* cfg);
+
 /* Fused decode attention (bf16, head_dim 64/128, <= 8 query heads per KV head): for every state and KV
  * head the K and V planes are read once (TMA into shared memory) and serve all query heads of the group
  * and both streams; RoPE at position rp.pos (- 1 if token_already_written), the theta rotation, the lambda
  * sigmoid, the lambda-gated subtraction and the head RMSNorm are fused.  Same result as
  * coda_b200_prep + coda_b200_attend with Lq = 1; replaces attend_step (src/coda_gqa_l/attention.py:476-514)
  * with _sdpa_stacked_two_stream (:416-465).  q_raw [B][H*Dh] and lam_logit [B][H] are bf16 with batch
- * strides; out [B][H*Dh] bf16.  status: optional device int, set non-zero if a bounded wait expired.
- * coda_b200_decode_attend_supported() tells whether this configuration is covered. */
+ * strides; out [B][H*Dh] bf16.  qrec: device scratch of coda_b200_decode_record_bytes(cfg) bytes (16-byte
+ * aligned) that receives the prepared queries.  status: optional device int, set non-zero if a bounded wait
+ * expired.  coda_b200_decode_attend_supported() tells whether this configuration is covered.
+ * coda_b200_decode_attend_prepared is the second half alone, on records already written by
+ * coda_b200_step_write_fused. */
 int coda_b200_decode_attend_supported(const coda_layer_cfg* cfg);
+int64_t coda_b200_decode_record_bytes(const coda_layer_cfg* cfg);
 int coda_b200_decode_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
                             int32_t token_already_written,
                             const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
                             const float* inv_freq, const void* cos_theta, const void* sin_theta,
-                            const void* norm_w, void* out, int64_t out_bs, int32_t* status,
+                            const void* norm_w, void* qrec, void* out, int64_t out_bs, int32_t* status,
                             coda_stream_t stream);
+int coda_b200_decode_attend_prepared(const coda_layer_cfg* cfg, const coda_state_ptrs* st, const void* qrec,
+                                     const void* norm_w, void* out, int64_t out_bs, int32_t* status,
+                                     coda_stream_t stream);
 
 /* Differential attention of Lq query rows per state over [all Lbuf slots | optional block].
  * out = head_norm( softmax(q K^T) V - lam * softmax(q_noise K^T) V ), GQA by head index.

@@ -280,3 +280,48 @@ def test_tensor_core_prefill_matches_generic_kernel(shape, block, L):
     assert torch.isfinite(ya).all()
     e = rel_err(ya, yb)
     assert e < 8e-3, f"tensor-core vs generic prefill attention: rel err {e:.3e}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [
+    dict(embed_dim=512, num_heads=4, num_kv_heads=1, window=100, num_landmarks_exact=20, num_landmarks_summary=12),   # Dh 128, G 4
+    dict(embed_dim=576, num_heads=9, num_kv_heads=3, window=24, num_landmarks_exact=6, num_landmarks_summary=5,
+         head_norm_mode="identity", rope_interleaved=False),                                                         # Dh 64, G 3, 35 slots
+])
+def test_decode_records_of_fused_write_match_preparation_kernel(shape):
+    """The decode records (prepared queries, lambda, visibility mask after the write) that the fused cache
+    write leaves behind are bit-identical to what the stand-alone preparation computes from the state after
+    the write -- while the ring fills and after it wraps."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    from coda_gqa_l_b200._lib import RingPos
+    from tests.scenarios import randomize_weights
+    torch.manual_seed(3)
+    mod = CoDAGQALandmarkPerf2(**shape).eval()
+    randomize_weights(mod, 3)
+    mod = mod.to(torch.bfloat16).cuda()
+    D, B = shape["embed_dim"], 3
+    H, Hkv = shape["num_heads"], shape["num_kv_heads"]
+    G, Dh = H // Hkv, D // H
+    Lbuf = shape["window"] + shape["num_landmarks_exact"] + shape["num_landmarks_summary"]
+    rows, qstr = (8 if 2 * G <= 8 else 16), Dh + 8
+    rec_bytes = rows * qstr * 2 + 32 + (Lbuf + 63) // 64 * 64
+    x = orc.mixture_inputs(B, 80, D, centroids=16, sigma=0.3, seed=5, dtype=torch.bfloat16).cuda()
+    st = mod.init_state(batch_size=B, device="cuda", dtype=torch.bfloat16)
+    _, st = mod.prefill_chunked(x[:, :8], st, block_size=8)        # ring not yet full
+    out = torch.empty(B, 1, D, device="cuda", dtype=torch.bfloat16)
+    for t in range(8, 80):
+        xt = x[:, t:t + 1]
+        cfg = mod._cfg(B, xt.dtype, st)
+        q, _, _, lam_logit, _ = mod._project(xt, need_kv=True)
+        y, st = mod.step(xt, st)
+        fused = mod._qrec[:B * Hkv * rec_bytes].clone()
+        assert fused.numel() == B * Hkv * rec_bytes
+        rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
+        mod.decode_attend_launch(cfg, st, rp, 1, q, lam_logit, out)
+        prep = mod._qrec[:B * Hkv * rec_bytes].clone()
+        f, p = fused.view(B * Hkv, rec_bytes), prep.view(B * Hkv, rec_bytes)
+        qf = f[:, :rows * qstr * 2].contiguous().view(torch.bfloat16).view(-1, rows, qstr)[:, :, :Dh]
+        qp = p[:, :rows * qstr * 2].contiguous().view(torch.bfloat16).view(-1, rows, qstr)[:, :, :Dh]
+        assert torch.equal(qf, qp), f"step {t}: prepared queries differ"
+        assert torch.equal(f[:, rows * qstr * 2:], p[:, rows * qstr * 2:]), f"step {t}: lambda / mask differ"
+    assert mod.device_status() == 0
