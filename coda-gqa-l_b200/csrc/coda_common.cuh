@@ -28,12 +28,17 @@ template <> struct El<bf16> {
 template <typename T> __device__ __forceinline__ float t_mul(float a, float b) { return El<T>::rnd(__fmul_rn(a, b)); }
 template <typename T> __device__ __forceinline__ float t_add(float a, float b) { return El<T>::rnd(__fadd_rn(a, b)); }
 template <typename T> __device__ __forceinline__ float t_sub(float a, float b) { return El<T>::rnd(__fsub_rn(a, b)); }
-template <typename T> __device__ __forceinline__ float t_div(float a, float b) { return El<T>::rnd(__fdiv_rn(a, b)); }
+// The correctly rounded division, exp and sin/cos expand to long instruction sequences (slow paths included).
+// Kernels that run every instruction once pay for their code size in instruction fetches, so these live in
+// one out-of-line copy per kernel.
+static __device__ __noinline__ float div_rn_call(float a, float b) { return __fdiv_rn(a, b); }
+static __device__ __noinline__ float sigmoid_call(float z) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z))); }
+static __device__ __noinline__ void sincos_call(float x, float* s, float* c) { *s = sinf(x); *c = cosf(x); }
+
+template <typename T> __device__ __forceinline__ float t_div(float a, float b) { return El<T>::rnd(div_rn_call(a, b)); }
 
 // sigmoid of a value held in dtype T, result rounded to T
-template <typename T> __device__ __forceinline__ float t_sigmoid(float z) {
-  return El<T>::rnd(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z))));
-}
+template <typename T> __device__ __forceinline__ float t_sigmoid(float z) { return El<T>::rnd(sigmoid_call(z)); }
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 

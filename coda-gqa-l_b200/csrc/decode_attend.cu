@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(128) decode_prep_kernel(DecodeParams p, const 
     if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
     float ang = __fmul_rn(ta, inv);
     if (p.angle_bf16) ang = bf16_round(ang);
-    float c = cosf(ang), s = sinf(ang);
+    float c, s; sincos_call(ang, &s, &c);
     if (p.angle_bf16) { c = bf16_round(c); s = bf16_round(s); }
     sCS[i] = bf16_round(c);
     sCS[HALF + i] = bf16_round(s);

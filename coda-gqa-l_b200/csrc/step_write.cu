@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
       if (abf) { ta = bf16_round(ta); inv = bf16_round(inv); }
       float ang = __fmul_rn(ta, inv);
       if (abf) ang = bf16_round(ang);
-      float cc = cosf(ang), ss = sinf(ang);
+      float cc, ss; sincos_call(ang, &ss, &cc);
       if (abf) { cc = bf16_round(cc); ss = bf16_round(ss); }
       cs[i] = El<T>::rnd(cc); sn[i] = El<T>::rnd(ss);
     }
@@ -320,8 +320,12 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     }
   };
   load_seg(tid);
-  for (int m = tid; m < Lbuf; m += NT) s_al[m] = al[m];
-  for (int m = tid; m < Me; m += NT) s_last[m] = ((const long long*)p.st.mem_last_exact)[(long long)b * Me + m];
+  // slot flags and LRU stamps: requested into registers now, parked in shared memory once every other request
+  // is out (a load -> shared-store loop would cost one memory round trip per loop); Lbuf <= 4 * NT, Me <= NT
+  uint8_t alr[4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) { const int m = tid + a * NT; alr[a] = m < Lbuf ? al[m] : (uint8_t)0; }
+  const long long lastr = tid < Me ? ((const long long*)p.st.mem_last_exact)[(long long)b * Me + tid] : 0;
   // the new token's row (element tid < DH: key, DH <= tid < 2*DH: value)
   float nk_a = 0.f, nk_b = 0.f, nv_x = 0.f, eta_raw = 0.f, glog = 0.f;
   const bool is_k = tid < DH, is_v = tid >= DH && tid < 2 * DH;
@@ -383,7 +387,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
       if (abf) { ta = bf16_round(ta); inv = bf16_round(inv); }
       float ang = __fmul_rn(ta, inv);
       if (abf) ang = bf16_round(ang);
-      float cc = cosf(ang), ss = sinf(ang);
+      float cc, ss; sincos_call(ang, &ss, &cc);
       if (abf) { cc = bf16_round(cc); ss = bf16_round(ss); }
       cs[tid] = El<T>::rnd(cc); sn[tid] = El<T>::rnd(ss);
     }
@@ -398,6 +402,9 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     if (is_v) ve[d] = El<T>::ld(vb + (long long)ev * DH + d);
     g_e = gr[ev];
   }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) { const int m = tid + a * NT; if (m < Lbuf) s_al[m] = alr[a]; }
+  if (tid < Me) s_last[tid] = lastr;
   __syncthreads();
   // rotated key element d (primitives.py:99-113)
   float new_k = nk_a;
@@ -440,11 +447,13 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
         }
       }
       const int rows = DecodeRecord::qrows(G);
+      #pragma unroll 1
       for (int w = tid; w < (rows - 2 * G) * HALF; w += NT)   // unused rows of the query tile: zero
         *reinterpret_cast<uint32_t*>(q_s + (2 * G + w / HALF) * QSTR + 2 * (w % HALF)) = 0u;
       float* lam = reinterpret_cast<float*>(rec + DecodeRecord::lam_off(G, DH));
       if (tid < 8) lam[tid] = tid < G ? t_sigmoid<T>(flam) : 0.f;
       uint8_t* mk = rec + DecodeRecord::mask_off(G, DH);
+      #pragma unroll 1
       for (int i = tid; i < DecodeRecord::mask_bytes(Lbuf); i += NT) {
         uint8_t v = 0;
         if (i < Lbuf) v = (i == ev || (e_on >= 0 && i == W + e_on) || (s_on >= 0 && i == W + Me + s_on)) ? 1 : s_al[i];
@@ -479,6 +488,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
 
   asm volatile("barrier.cluster.wait.aligned;" ::: "memory");       // all CTAs of the cluster are running
   // ---- per-head dot products of both banks, sent to every CTA of the cluster ----
+  #pragma unroll 1
   for (int base = 0; base < 2 * MM; base += NT) {
     const int it = base + tid;
     float acc0 = 0.f, acc1 = 0.f;
@@ -511,6 +521,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     if (it < 2 * MM && (it & 1) == 0) {
       const float v = El<T>::rnd(acc);
       const uint32_t local = tma::smem_u32(xdots + h * MM + (it >> 1));
+      #pragma unroll 1
       for (int rk = 0; rk < Hkv; ++rk) {
         uint32_t remote;
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rk));
@@ -523,8 +534,10 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
 
   // ---- scores: sum over heads of the rounded per-head dots, mean, masks ----
   const int Ae = c.active_exact, As = c.active_summary;
+  #pragma unroll 1
   for (int m = tid; m < MM; m += NT) {
     float tot = 0.f;
+    #pragma unroll 1
     for (int hh = 0; hh < Hkv; ++hh) tot += xdots[hh * MM + m];
     const float mean = El<T>::rnd(tot / (float)Hkv);
     sc[m] = m < Me ? ((m >= Ae || !s_used[m]) ? -1e9f : mean) : ((m - Me >= As) ? -1e9f : mean);
@@ -533,6 +546,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   // ---- decisions, taken redundantly by every CTA: warp 0 exact bank, warp 1 summary bank ----
   auto arg_best = [&](const float* v, int n, float& best, int& bi) {     // first index of the maximum
     best = -INFINITY; bi = 0x7fffffff;
+    #pragma unroll 1
     for (int m = lane; m < n; m += 32) if (v[m] > best || bi == 0x7fffffff) { best = v[m]; bi = m; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -545,6 +559,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     float best; int bi;
     arg_best(sc, Me, best, bi);
     int free_i = 0x7fffffff, lru_i = 0x7fffffff; long long lru_v = 0x7fffffffffffffffLL; bool any_used = false;
+    #pragma unroll 1
     for (int m = lane; m < Me; m += 32) {
       const bool used = s_used[m] != 0, act = m < Ae;
       if (act && used) any_used = true;
@@ -612,16 +627,20 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   // re-normalise the two rewritten rows of the routing caches
   if (warp == 0 && do_e) {
     float ss = 0.f;
+    #pragma unroll 1
     for (int i = lane; i < DH; i += 32) ss += vhat[i] * vhat[i];
     const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
     T* dst = (T*)p.st.exact_v_norm + (((long long)b * Hkv + h) * Me + s_eidx) * DH;
+    #pragma unroll 1
     for (int i = lane; i < DH; i += 32) El<T>::st(dst + i, t_div<T>(vhat[i], den));
   }
   if (warp == 1 && do_s) {
     float ss = 0.f;
+    #pragma unroll 1
     for (int i = lane; i < LFD; i += 32) ss += khat[i] * khat[i];
     const float den = fmaxf(El<T>::rnd(sqrtf(warp_sum(ss))), 1e-6f);
     T* dst = (T*)p.st.sum_lf_k_norm + (((long long)b * Hkv + h) * Ms + s_sidx) * LFD;
+    #pragma unroll 1
     for (int i = lane; i < LFD; i += 32) El<T>::st(dst + i, t_div<T>(khat[i], den));
   }
   // ---- the new token takes the evicted slot (memory_banks.py:219-222) ----
@@ -678,6 +697,7 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
     const int MM = cfg->Me + cfg->Ms;
     const size_t csm = sizeof(float) * ((size_t)cfg->Hkv * MM + MM) + 8 + 8 * (size_t)cfg->Me + (size_t)(cfg->W + MM) + 16;
     const bool ok = cfg->Hkv <= 8 && (cfg->Dh == 64 || cfg->Dh == 128) && csm <= 40 * 1024 && cfg->B <= 65535 &&
+                    cfg->W + MM <= 1024 && cfg->Me <= 256 &&
                     (cfg->Me == 0 || (uintptr_t)st->exact_v_norm % 16 == 0) && (cfg->Ms == 0 || (uintptr_t)st->sum_lf_k_norm % 16 == 0) &&
                     ((size_t)cfg->Dh / 4 * es0) % 16 == 0;
     if (ok) {
@@ -732,7 +752,7 @@ extern "C" int coda_b200_step_write_fused_supported(const coda_layer_cfg* cfg) {
   const int MM = cfg->Me + cfg->Ms, G = cfg->H / cfg->Hkv;
   const size_t csm = sizeof(float) * ((size_t)cfg->Hkv * MM + MM) + 8 + 8 * (size_t)cfg->Me + (size_t)(cfg->W + MM) + 16;
   return cfg->dtype == CODA_BF16 && cfg->Hkv <= 8 && G <= 8 && (cfg->Dh == 64 || cfg->Dh == 128) && csm <= 40 * 1024 &&
-         cfg->B <= 65535;
+         cfg->B <= 65535 && cfg->W + MM <= 1024 && cfg->Me <= 256;
 }
 
 extern "C" int coda_b200_step_write_fused(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
