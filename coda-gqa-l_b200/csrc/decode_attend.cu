@@ -31,6 +31,11 @@ constexpr int DA_TILE = 64;          // slots per stage
 constexpr int DA_MAX_STAGES = 8;
 constexpr int DA_CWARPS = 8;         // consumer warps (two groups of four)
 constexpr int DA_AWARPS = 4;         // auxiliary warps (query preparation, merge + epilogue)
+// Register split after launch (setmaxnreg), per warpgroup.  A warpgroup asking for more than the CTA's pool
+// (threads x registers at launch) can give would wait forever: the launcher checks the sum against the kernel's
+// compiled register count and refuses to launch otherwise.
+constexpr int DA_REGS_CONSUMER = 152, DA_REGS_AUX = 104, DA_REGS_PRODUCER = 40;
+constexpr int DA_REGS_TOTAL = DA_CWARPS * 32 * DA_REGS_CONSUMER + DA_AWARPS * 32 * DA_REGS_AUX + 128 * DA_REGS_PRODUCER;
 constexpr int DA_THREADS = (DA_CWARPS + DA_AWARPS + 4) * 32;   // the producer's warpgroup has one working warp
 
 struct DecodeParams {
@@ -72,7 +77,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ void bar_aux() { asm volatile("bar.sync 2, %0;" ::"n"(DA_AWARPS * 32) : "memory"); }
 
 // Byte offset of 16-byte chunk `c` of row `s` inside a [64 x DH] bf16 tile written by TMA as DH/64
 // boxes of 64 rows x 128 bytes with the 128-byte swizzle (chunk index XOR row mod 8).
@@ -157,8 +161,10 @@ __global__ void __launch_bounds__(128) decode_prep_kernel(DecodeParams p, const 
   for (int i = tid; i < DecodeRecord::mask_bytes(p.Lbuf); i += blockDim.x) mk[i] = i < p.Lbuf ? alb[i] : 0;
 }
 
+// 120 registers per thread at launch (512 threads: 60 K of the SM's 64 K registers, so that a tool which
+// needs a few registers of its own can still launch the kernel); the roles re-split them below.
 template <int DH, int NQ>
-__global__ void __launch_bounds__(DA_THREADS, 1)
+__global__ void __maxnreg__(120)
 decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
   constexpr int KSTEPS = DH / 16;            // k-steps of Q.K^T
   constexpr int MT_O = DH / 16;              // m-tiles of the (transposed) output
@@ -198,7 +204,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   // Registers follow the roles (per warpgroup): the consumers hold the output accumulators and the query
   // fragments, the other warps need little.
   if (warp >= DA_CWARPS + DA_AWARPS) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DA_REGS_PRODUCER));
     if (warp > DA_CWARPS + DA_AWARPS) return;
     // ---------------- producer: records first, then the ring of K/V tiles, across plane boundaries ----------------
     if (lane == 0) {
@@ -238,7 +244,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   }
 
   if (warp >= DA_CWARPS) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DA_REGS_AUX));
     // ---------------- auxiliary warps: merge of the eight partial softmaxes + epilogue, one warp per query head ----------------
     const int aw = warp - DA_CWARPS;
     constexpr int DV = 4;                                  // output dims per lane: 4*lane .. 4*lane+3
@@ -315,7 +321,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   //   S^T[16 slots x 8 q] = K[16 x Dh] . Q^T,   O^T[Dh x 8 q] += V^T[16 dh x 16 slots] . P^T
   // so that the 2G <= 8 live query rows fill an n-tile exactly (NQ = 2 n-tiles for 8 < 2G <= 16); with the
   // queries as m = 16 half of every tile would be padding, and the legacy tensor path is what bounds a tile.
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DA_REGS_CONSUMER));
   const int grp = warp >> 2, gw = warp & 3;            // group, warp inside the group (owns slots gw*16..+15 of a tile)
   const int li = lane >> 3, lr = lane & 7;
   const int qa = 2 * (lane & 3);                        // this thread's query columns: nq*8 + qa + {0, 1}
@@ -478,6 +484,15 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
     int dev = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
+  }
+  {
+    static int pool = 0;
+    if (pool == 0) {
+      cudaFuncAttributes fa;
+      CODA_REQUIRE(cudaFuncGetAttributes(&fa, decode_attend_kernel<DH, NQ>) == cudaSuccess, CODA_ERR_LAUNCH, "decode_attend: cudaFuncGetAttributes failed");
+      pool = fa.numRegs * DA_THREADS;
+    }
+    CODA_REQUIRE(pool >= DA_REGS_TOTAL, CODA_ERR_LAUNCH, "decode_attend: register pool %d below the %d the roles ask for", pool, DA_REGS_TOTAL);
   }
   const int nplanes = p.B * p.Hkv;
   decode_attend_kernel<DH, NQ><<<nplanes < num_sms ? nplanes : num_sms, DA_THREADS, smem, s>>>(km, vm, p);

@@ -6,9 +6,10 @@
 //     S = Q . K^T          tcgen05.mma  M=128 N=128 K=Dh   A, B from shared memory, S in TMEM
 //     P = exp2(S - m)      softmax warps: tcgen05.ld, lazy-rescaled online softmax, bf16 P written back over S
 //     O += P . V           tcgen05.mma  M=128 N=Dh  K=128  A = P straight from TMEM, B = V from shared memory
-// Warp roles: warp 0 = TMA producer (cp.async.bulk.tensor, 128-byte swizzle, 2-stage ring of 128-key K/V
-// tiles), warp 1 = MMA issuer and TMEM owner, warps 2-5 = softmax / correction / epilogue of the signal stream,
-// warps 6-9 = the same for the noise stream (one thread per query row).  The two streams ping-pong on the
+// Warp roles: warps 0-3 = softmax / correction / epilogue of the signal stream, warps 4-7 = the same for the
+// noise stream (one thread per query row, the whole row of S in registers: setmaxnreg gives these two
+// warpgroups 208 registers), warp 8 = TMA producer (cp.async.bulk.tensor, 128-byte swizzle, 2-stage ring of
+// 128-key K/V tiles), warp 9 = MMA issuer and TMEM owner.  The two streams ping-pong on the
 // tensor core: while one stream is in softmax the other's P.V and next Q.K^T run.  Keeping P in TMEM halves
 // the shared-memory operand traffic of P.V and N=128 tiles keep Q.K^T at the operand-bandwidth limit.
 // TMEM map (512 columns): S_sig 0..127 (P_sig aliases 0..63), S_noise 128..255, O_sig 256.., O_noise 256+Dh..
@@ -22,7 +23,12 @@ namespace {
 
 constexpr int PF_BM = 128;       // query rows per CTA
 constexpr int PF_BN = 128;       // keys per tile
-constexpr int PF_THREADS = 320;  // 10 warps
+// Register split after launch (setmaxnreg): the two softmax warpgroups grow, the third warpgroup shrinks.  A
+// warpgroup that asks for more than the CTA's pool (threads x registers at launch) can give waits forever, so the
+// launcher checks the sum against the kernel's compiled register count and refuses to launch otherwise.
+constexpr int PF_REGS_SOFTMAX = 208, PF_REGS_AUX = 72;
+constexpr int PF_REGS_TOTAL = 256 * PF_REGS_SOFTMAX + 128 * PF_REGS_AUX;
+constexpr int PF_THREADS = 384;  // warps 0-3 / 4-7: softmax of the signal / noise stream, 8: TMA, 9: MMA issuer, 10-11 idle
 constexpr int PF_STAGES = 2;     // K/V tiles in flight
 constexpr float PF_RESCALE_GAP = 8.0f;   // log2 units the running max may lag before O is rescaled
 
@@ -85,6 +91,18 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
                  "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
                : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+               : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -106,19 +124,52 @@ __device__ __forceinline__ float ex2_mufu(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x for x <= 0 on the FMA / integer pipes: x = n + f with n = floor(x) (round-down add of 1.5*2^23 leaves n
-// in the low mantissa bits), 2^f by a cubic (relative error < 1e-4, far below the bf16 rounding of P), and n
-// added straight into the exponent field.  Spreads the exponentials over two pipes: the softmax is bound by
-// the 16 MUFU results per clock an SM can produce, not by issue slots.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -127.0f);
-  float t;
-  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(t) : "f"(x), "f"(12582912.0f));
-  const float f = x - (t - 12582912.0f);
-  float r = fmaf(f, 0.077119089663028717f, 0.227564394474029541f);
-  r = fmaf(r, f, 0.695146143436431885f);
-  r = fmaf(r, f, 1.0f);
-  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+// Packed fp32 pairs (one instruction for two lanes of a register pair) and the three-input maximum.
+__device__ __forceinline__ uint64_t pk64(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpk64(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2_rm(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// 2^x for a pair of arguments on the FMA / integer pipes (x = n + f, n = floor(x) left in the low mantissa bits
+// by a round-down add of 1.5 * 2^23; 2^f by a cubic, relative error < 1e-4, far below the bf16 rounding of P;
+// n added into the exponent field).  The special-function unit delivers one warp of exponentials per 8 cycles
+// per scheduler; a third of the exponentials go this way so that neither pipe bounds the softmax.
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& y0, float& y1) {
+  const uint64_t x = pk64(fmaxf(x0, -127.0f), fmaxf(x1, -127.0f));
+  const uint64_t magic = pk64(12582912.0f, 12582912.0f), nmagic = pk64(-12582912.0f, -12582912.0f);
+  const uint64_t t = add2_rm(x, magic);
+  const uint64_t fl = add2(t, nmagic);                           // floor(x), exact
+  const uint64_t mone = pk64(-1.0f, -1.0f);
+  const uint64_t f = fma2(fl, mone, x);                          // x - floor(x), exact
+  uint64_t r = fma2(f, pk64(0.077119089663028717f, 0.077119089663028717f), pk64(0.227564394474029541f, 0.227564394474029541f));
+  r = fma2(r, f, pk64(0.695146143436431885f, 0.695146143436431885f));
+  r = fma2(r, f, pk64(1.0f, 1.0f));
+  float r0, r1, t0, t1;
+  unpk64(r, r0, r1);
+  unpk64(t, t0, t1);
+  y0 = __int_as_float(__float_as_int(r0) + (__float_as_int(t0) << 23));
+  y1 = __int_as_float(__float_as_int(r1) + (__float_as_int(t1) << 23));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 __device__ __forceinline__ void bar_softmax_all() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -171,7 +222,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     for (int i = 0; i < 2; ++i) { tma::mbar_init(&s_full[i], 1); tma::mbar_init(&p_full[i], 4); tma::mbar_init(&pv_done[i], 1); }
     tma::fence_barrier_init();
   }
-  if (warp == 1) {                                   // TMEM: all 512 columns, owned by warp 1
+  if (warp == 9) {                                   // TMEM: all 512 columns, owned by the MMA warp
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     tc_fence_before();
@@ -180,7 +231,10 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 0) {
+  // Registers follow the roles, per warpgroup: a softmax thread keeps a whole row of S (128 values) in registers.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PF_REGS_AUX));
+  if (warp == 8) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
       tma::mbar_expect_tx(q_full, 2 * Q_BYTES);
@@ -207,7 +261,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 9) {
     // =========================== MMA issuer ===========================
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = instr_desc(PF_BN, false);
@@ -252,10 +306,19 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         }
       }
     }
-  } else {
+  }
+    __syncthreads();                                   // every role meets here once all tensor work is done
+    if (warp == 9) {
+      tc_fence_after();
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+    return;
+  }
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PF_REGS_SOFTMAX));
+  {
     // =========================== softmax / correction / epilogue (one stream per warp group) ===========================
-    const int s = warp >= 6 ? 1 : 0;                      // 0 = signal, 1 = noise
-    const int sw = (warp - 2) & 3;                        // warp index inside its group
+    const int s = warp >> 2;                              // 0 = signal, 1 = noise
+    const int sw = warp & 3;                              // warp index inside its group
     const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;                  // row of the query tile
     const int grow = r0 + row;                            // row inside the block
@@ -277,42 +340,51 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     for (int j = 0; j < NT; ++j) {
       tma::mbar_wait(&s_full[s], j & 1, p.status, 16);
       tc_fence_after();
-      uint32_t vis[4];
+      // Visibility per group of 32 keys.  cls: 2 = all visible, 0 = none, 1 = mixed; the class is the same for
+      // every lane of a warp: prefix slots carry one mask per state, and in a block tile the 32 rows of a warp
+      // meet the causal diagonal inside one group only.
+      uint32_t vis[4]; int cls[4];
       if (j < NP) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) vis[q4] = sMask[4 * j + q4];
+        for (int q4 = 0; q4 < 4; ++q4) {
+          vis[q4] = sMask[4 * j + q4];
+          cls[q4] = vis[q4] == 0xffffffffu ? 2 : (vis[q4] == 0u ? 0 : 1);
+        }
       } else {
         const int nvis = grow - (j - NP) * PF_BN + 1;     // key c0+i visible iff c0+i <= grow
+        const int qd = (r0 + quarter * 32 - (j - NP) * PF_BN) >> 5;    // group holding this warp's diagonal
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int nq = nvis - 32 * q4;
           vis[q4] = nq >= 32 ? 0xffffffffu : (nq <= 0 ? 0u : ((1u << nq) - 1u));
+          cls[q4] = q4 < qd ? 2 : (q4 == qd ? 1 : 0);
         }
       }
-      const bool all_vis = (vis[0] & vis[1] & vis[2] & vis[3]) == 0xffffffffu;
-      // pass 1: row maximum over the 128 keys (two TMEM loads in flight at a time)
+      // S is read from TMEM once, all 128 keys of the row into registers (TMEM -> register bandwidth, not
+      // arithmetic, bounds a two-pass softmax here); groups without a visible key are not read at all.
+      uint32_t v[4][32];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) if (cls[g] != 0) tc_ld32(s_col + g * 32, v[g]);
+      tc_wait_ld();
+      // row maximum over the visible keys
       float mx = -INFINITY;
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t v0[32], v1[32];
-        tc_ld32(s_col + hf * 64, v0);
-        tc_ld32(s_col + hf * 64 + 32, v1);
-        tc_wait_ld();
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-        if (all_vis) {
+      for (int g = 0; g < 4; ++g) {
+        float m0 = -INFINITY, m1 = -INFINITY;
+        if (cls[g] == 2) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            m0 = fmaxf(m0, __uint_as_float(v0[i])); m1 = fmaxf(m1, __uint_as_float(v0[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(v1[i])); m3 = fmaxf(m3, __uint_as_float(v1[i + 1]));
+          for (int i = 0; i < 32; i += 4) {
+            m0 = max3(m0, __uint_as_float(v[g][i]), __uint_as_float(v[g][i + 1]));
+            m1 = max3(m1, __uint_as_float(v[g][i + 2]), __uint_as_float(v[g][i + 3]));
           }
-        } else {
+        } else if (cls[g] == 1) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if ((vis[2 * hf] >> i) & 1u) m0 = fmaxf(m0, __uint_as_float(v0[i]));
-            if ((vis[2 * hf + 1] >> i) & 1u) m2 = fmaxf(m2, __uint_as_float(v1[i]));
+            if (!((vis[g] >> i) & 1u)) v[g][i] = 0xff800000u;       // -inf: exp gives 0 below
+            m0 = fmaxf(m0, __uint_as_float(v[g][i]));
           }
         }
-        mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+        mx = max3(mx, m0, m1);
       }
       mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
       float alpha = 1.f;
@@ -326,53 +398,48 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       if (__any_sync(0xffffffffu, (alpha != 1.f) && j > 0)) {
         tma::mbar_wait(&pv_done[s], (j - 1) & 1, p.status, 19);
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
-          uint32_t o[32];
-          tc_ld32(o_col + c * 32, o);
+#pragma unroll 1
+        for (int c = 0; c < DH / 16; ++c) {
+          uint32_t o[16];
+          tc_ld16(o_col + c * 16, o);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tc_st32(o_col + c * 32, o);
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc_st16(o_col + c * 16, o);
         }
       }
-      // pass 2: probabilities, written back over S as packed bf16 (key 2i, 2i+1 -> column i)
+      // probabilities, written back over S as packed bf16 (key 2i, 2i+1 -> column i); every S column has been
+      // read by now
       const float nref = mb == -INFINITY ? 0.f : -mb;
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      const uint64_t scale2 = pk64(p.scale_log2, p.scale_log2), nref2 = pk64(nref, nref);
+      uint64_t sum0 = 0ull, sum1 = 0ull, sum2 = 0ull, sum3 = 0ull;     // four independent chains of packed pairs
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t v0[32], v1[32], pk[32];
-        tc_ld32(s_col + hf * 64, v0);
-        tc_ld32(s_col + hf * 64 + 32, v1);
-        tc_wait_ld();
-        if (!all_vis) {
+      for (int g = 0; g < 4; ++g) {
+        uint32_t pk[16];
+        if (cls[g] == 0) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (!((vis[2 * hf] >> i) & 1u)) v0[i] = 0xff800000u;     // -inf
-            if (!((vis[2 * hf + 1] >> i) & 1u)) v1[i] = 0xff800000u;
+          for (int i = 0; i < 16; ++i) pk[i] = 0u;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // exponent arguments of two keys per instruction; two pairs in three on the special-function
+            // unit, the third on the FMA pipe
+            float x0, x1, a0, a1;
+            unpk64(fma2(pk64(__uint_as_float(v[g][2 * i]), __uint_as_float(v[g][2 * i + 1])), scale2, nref2), x0, x1);
+            if (i % 3 == 2) { ex2_poly2(x0, x1, a0, a1); } else { a0 = ex2_mufu(x0); a1 = ex2_mufu(x1); }
+            const uint64_t pr = pk64(a0, a1);
+            if ((i & 3) == 0) sum0 = add2(sum0, pr); else if ((i & 3) == 1) sum1 = add2(sum1, pr);
+            else if ((i & 3) == 2) sum2 = add2(sum2, pr); else sum3 = add2(sum3, pr);
+            pk[i] = pack2(a0, a1);
           }
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {            // half of the exponentials on MUFU, half on the FMA pipe
-          const float a0 = ex2_mufu(fmaf(__uint_as_float(v0[2 * i]), p.scale_log2, nref));
-          const float a1 = ex2_poly(fmaf(__uint_as_float(v0[2 * i + 1]), p.scale_log2, nref));
-          const float c0 = ex2_mufu(fmaf(__uint_as_float(v1[2 * i]), p.scale_log2, nref));
-          const float c1 = ex2_poly(fmaf(__uint_as_float(v1[2 * i + 1]), p.scale_log2, nref));
-          if (i & 1) { sum1 += a0 + a1; sum3 += c0 + c1; } else { sum0 += a0 + a1; sum2 += c0 + c1; }
-          pk[i] = pack2(a0, a1);
-          pk[16 + i] = pack2(c0, c1);
-        }
-        // the second half's S columns (64..127) are read before the first half's P (columns 0..31) is
-        // written only when hf == 0 has been fully loaded: keep the order load(hf) -> store(hf)
-        if (hf == 0) {
-          // columns 0..31 hold keys 0..63 of P; S columns 0..63 were read above, 64..127 are read next and
-          // are not touched by this store
-          tc_st32(s_col, pk);
-        } else {
-          tc_st32(s_col + 32, pk);
-        }
+        tc_st16(s_col + g * 16, pk);
       }
-      l += (sum0 + sum1) + (sum2 + sum3);
+      {
+        float t0, t1;
+        unpk64(add2(add2(sum0, sum1), add2(sum2, sum3)), t0, t1);
+        l += t0 + t1;
+      }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -453,10 +520,6 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   }
 
   __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
-  }
 }
 
 template <int DH>
@@ -476,6 +539,15 @@ int launch_prefill(const CUtensorMap* maps, const PrefillParams& p, cudaStream_t
     configured = true;
   }
   dim3 grid((p.blk + PF_BM - 1) / PF_BM, p.H, p.B);
+  {
+    static int pool = 0;
+    if (pool == 0) {
+      cudaFuncAttributes fa;
+      CODA_REQUIRE(cudaFuncGetAttributes(&fa, prefill_attend_kernel<DH>) == cudaSuccess, CODA_ERR_LAUNCH, "prefill_attend: cudaFuncGetAttributes failed");
+      pool = fa.numRegs * PF_THREADS;
+    }
+    CODA_REQUIRE(pool >= PF_REGS_TOTAL, CODA_ERR_LAUNCH, "prefill_attend: register pool %d below the %d the roles ask for", pool, PF_REGS_TOTAL);
+  }
   prefill_attend_kernel<DH><<<grid, PF_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
   CODA_CHECK_LAUNCH("prefill_attend");
   return CODA_OK;
