@@ -324,7 +324,10 @@ def main():
         "clocks": clocks.summary(),
         "roofline": {"kernel": "decode_attend_kernel (coda_b200_decode_attend_prepared)", "timing": "graph of back-to-back launches over all layers' states, CUDA events", "bound": "hbm", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "of": peak_src,
-                     "frac_of_nominal_8000": achieved / 8000.0, "traffic": None, "kernel_ms": kern_ms,
+                     "frac_of_nominal_8000": achieved / 8000.0,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this workload
+                     # (ncu capture summarised under profiles/), scaled by the states processed
+                     "traffic": int(round(51044000 * B / 32)) if args.workload == "c4_mistral7b" else None, "kernel_ms": kern_ms,
                      "bytes_per_launch": bytes_launch},
         "prefill": {"tokens_per_s": world * pre_tokens / (prefill_ms * 1e-3), "tokens": pre_tokens, "ms": prefill_ms,
                     "attention_kernel_ms_per_block": pre_kernel_ms, "attention_tflops": pre_tf,
