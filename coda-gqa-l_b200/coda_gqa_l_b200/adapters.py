@@ -177,6 +177,64 @@ class LlamaCoDAAdapter(_AdapterBase):
                 f"head_dim={self.head_dim}, mode={'bounded' if self.bounded else 'unbounded'}")
 
 
+class Qwen3CoDAAdapter(LlamaCoDAAdapter):
+    """Replacement for a HuggingFace Qwen3 ``self_attn`` module (upstream qwen3_adapter.py:25-219).
+
+    Qwen3 attention has the Llama layout (separate q/k/v/o projections, GQA, half-split RoPE pairs), so this is
+    the Llama adapter with Qwen3's ``rope_theta`` of 1e6 as the default; weights map one to one."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, bounded: bool = False,
+                 rope_theta: float = 1_000_000.0, lambda_init_bias: float = -6.0, theta_init: float = math.pi / 2,
+                 eps: float = 1e-6, head_norm_mode: str = "identity", rope_interleaved: bool = False,
+                 window: int = 256, num_landmarks_exact: int = 64, num_landmarks_summary: int = 64,
+                 block_size: int = 1024, **coda_kwargs):
+        super().__init__(hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                         bounded=bounded, rope_theta=rope_theta, lambda_init_bias=lambda_init_bias,
+                         theta_init=theta_init, eps=eps, head_norm_mode=head_norm_mode,
+                         rope_interleaved=rope_interleaved, window=window, num_landmarks_exact=num_landmarks_exact,
+                         num_landmarks_summary=num_landmarks_summary, block_size=block_size, **coda_kwargs)
+
+    @classmethod
+    def from_qwen3_attention(cls, qwen3_attn: nn.Module, bounded: bool = False, head_norm_mode: str = "identity",
+                             rope_interleaved: bool = False, **coda_kwargs) -> "Qwen3CoDAAdapter":
+        """Build an adapter with the q/k/v/o weights (and biases, if any) of ``qwen3_attn``; head counts come
+        from the module's attributes or, failing that, from the projection shapes; ``rope_theta`` from its
+        ``config`` when present, else 1e6 (upstream qwen3_adapter.py:79-180)."""
+        hidden = qwen3_attn.q_proj.in_features
+        n_q = getattr(qwen3_attn, "num_heads", None)
+        n_kv = getattr(qwen3_attn, "num_key_value_heads", None)
+        hd = getattr(qwen3_attn, "head_dim", None)
+        if hd is None:
+            q_out = qwen3_attn.q_proj.out_features
+            hd = q_out // n_q if n_q is not None else next((c for c in (128, 64, 96, 256) if q_out % c == 0), None)
+            if hd is None:
+                raise ValueError(f"Cannot infer head_dim from q_proj shape {q_out}")
+        if n_q is None:
+            n_q = qwen3_attn.q_proj.out_features // hd
+        if n_kv is None:
+            n_kv = qwen3_attn.k_proj.out_features // hd
+        config = getattr(qwen3_attn, "config", None)
+        rope_theta = getattr(config, "rope_theta", 1_000_000.0) if config is not None else 1_000_000.0
+        ad = cls(hidden_size=hidden, num_heads=n_q, num_kv_heads=n_kv, head_dim=hd, bounded=bounded,
+                 rope_theta=rope_theta, head_norm_mode=head_norm_mode, rope_interleaved=rope_interleaved, **coda_kwargs)
+        for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            src = getattr(qwen3_attn, name)
+            _copy_linear(ad.coda, name, src.weight.data, None if src.bias is None else src.bias.data)
+        return ad
+
+    @classmethod
+    def swap_qwen3_layers(cls, model: nn.Module, bounded: bool = False, head_norm_mode: str = "identity",
+                          rope_interleaved: bool = False, **coda_kwargs) -> List["Qwen3CoDAAdapter"]:
+        """Replace ``self_attn`` of every block in ``model.model.layers`` (upstream qwen3_adapter.py:182-219)."""
+        made = []
+        for block in model.model.layers:
+            ad = cls.from_qwen3_attention(block.self_attn, bounded=bounded, head_norm_mode=head_norm_mode,
+                                          rope_interleaved=rope_interleaved, **coda_kwargs)
+            block.self_attn = ad
+            made.append(ad)
+        return made
+
+
 class EveCoDAAdapter(_AdapterBase):
     """Replacement for Eve-2's ``CausalSelfAttention`` (multi-head, fused QKV projection with biases);
     ``forward(x, freqs_cis=None)`` returns the output tensor only (upstream eve_adapter.py:308-328)."""

@@ -4,7 +4,7 @@ import io
 import pytest
 import torch
 
-from coda_gqa_l_b200 import (CoDAGQALandmarkPerf2, CoDAGQALandmarkStatePerf2, EveCoDAAdapter, LlamaCoDAAdapter,
+from coda_gqa_l_b200 import (CoDAGQALandmarkPerf2, CoDAGQALandmarkStatePerf2, EveCoDAAdapter, LlamaCoDAAdapter, Qwen3CoDAAdapter,
                              _deep_copy_state, _state_to_cpu, _state_to_device, state_from_fields)
 from coda_gqa_l_b200.state import arena_layout
 
@@ -128,3 +128,62 @@ def test_eve_adapter_splits_fused_qkv():
     assert torch.equal(ad.coda.k_proj.weight, w[64:128]) and torch.equal(ad.coda.v_proj.bias, b[128:])
     assert ad.coda.num_kv_heads == 4 and ad.coda.head_norm_mode == "full" and ad.coda.rope_interleaved
     assert "block_size=1024" in ad.extra_repr()
+
+
+def test_qwen3_adapter_defaults_and_weight_copy():
+    """Qwen3 adapter = Llama adapter with rope_theta 1e6 by default (upstream qwen3_adapter.py:25-219)."""
+    ad = Qwen3CoDAAdapter(hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16, bounded=True, window=8,
+                          num_landmarks_exact=4, num_landmarks_summary=4)
+    assert ad.coda.rope_base == 1e6 and ad.coda.head_norm_mode == "identity" and not ad.coda.rope_interleaved
+    src = _FakeLlamaAttn()
+    del src.config                                                     # no config: the Qwen3 default applies
+    src.num_heads = None                                               # head count inferred from the projection shape
+    ad = Qwen3CoDAAdapter.from_qwen3_attention(src, bounded=True, window=8, num_landmarks_exact=4,
+                                               num_landmarks_summary=4)
+    assert isinstance(ad, LlamaCoDAAdapter) and ad.num_heads == 4 and ad.num_kv_heads == 2 and ad.head_dim == 16
+    assert ad.coda.rope_base == 1e6
+    for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+        assert torch.equal(getattr(ad.coda, name).weight, getattr(src, name).weight)
+    assert torch.equal(ad.coda.q_proj.bias, src.q_proj.bias) and ad.coda.k_proj.bias is None
+    model = type("M", (torch.nn.Module,), {})()
+    model.model = type("Inner", (torch.nn.Module,), {})()
+    blocks = [type("Blk", (torch.nn.Module,), {})() for _ in range(3)]
+    for b in blocks:
+        b.self_attn = _FakeLlamaAttn()
+    model.model.layers = torch.nn.ModuleList(blocks)
+    ads = Qwen3CoDAAdapter.swap_qwen3_layers(model, bounded=False)
+    assert len(ads) == 3 and all(model.model.layers[i].self_attn is ads[i] for i in range(3))
+    y, _ = ads[1](torch.randn(2, 3, 64))
+    assert y.shape == (2, 3, 64)
+
+
+def test_state_wire_format_round_trip_and_validation():
+    """One blob per layer state: header + arena bytes; round trip restores every field; bad blobs are refused."""
+    from coda_gqa_l_b200 import state_from_bytes, state_to_bytes
+    from coda_gqa_l_b200.state import allocate_state
+    from coda_gqa_l_b200.state_io import WIRE_HEADER_BYTES
+    for dtype in (torch.float32, torch.bfloat16):
+        st = allocate_state(2, 3, 16, 10, 4, 5, "cpu", dtype)
+        g = torch.Generator().manual_seed(1)
+        st.k_buf.copy_(torch.randn(st.k_buf.shape, generator=g).to(dtype))
+        st.v_buf.copy_(torch.randn(st.v_buf.shape, generator=g).to(dtype))
+        st._exact_v_norm.copy_(torch.randn(st._exact_v_norm.shape, generator=g).to(dtype))
+        st._sum_lf_k_norm.copy_(torch.randn(st._sum_lf_k_norm.shape, generator=g).to(dtype))
+        st.g_recent.copy_(torch.rand(st.g_recent.shape, generator=g))
+        st.mem_last_exact.copy_(torch.randint(-1, 1000, st.mem_last_exact.shape, generator=g))
+        st.allowed.copy_(torch.rand(st.allowed.shape, generator=g) > 0.5)
+        st.pos, st.recent_idx, st.recent_filled, st.active_exact, st.active_summary = 12345678901, 7, 10, 4, 5
+        blob = state_to_bytes(st)
+        assert len(blob) == WIRE_HEADER_BYTES + st._arena.numel() and blob[:7] == b"CODAB2S"
+        back = state_from_bytes(blob, "cpu")
+        for name in ("k_buf", "v_buf", "allowed", "g_recent", "mem_last_exact", "_exact_v_norm", "_sum_lf_k_norm"):
+            a, b = getattr(st, name), getattr(back, name)
+            assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b), name
+        assert (back.pos, back.recent_idx, back.recent_filled, back.active_exact, back.active_summary) == \
+               (12345678901, 7, 10, 4, 5)
+        with pytest.raises(ValueError):
+            state_from_bytes(b"XXXXXXXX" + blob[8:], "cpu")
+        with pytest.raises(ValueError):
+            state_from_bytes(blob[:-1], "cpu")
+        with pytest.raises(ValueError):
+            state_from_bytes(blob[:8] + (99).to_bytes(4, "little") + blob[12:], "cpu")

@@ -325,3 +325,27 @@ def test_decode_records_of_fused_write_match_preparation_kernel(shape):
         assert torch.equal(qf, qp), f"step {t}: prepared queries differ"
         assert torch.equal(f[:, rows * qstr * 2:], p[:, rows * qstr * 2:]), f"step {t}: lambda / mask differ"
     assert mod.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_wire_format_restores_a_live_state():
+    """A state shipped as one blob and restored continues bit-identically to the original."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, state_from_bytes, state_to_bytes
+    from tests.scenarios import randomize_weights
+    torch.manual_seed(0)
+    mod = CoDAGQALandmarkPerf2(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=8,
+                               num_landmarks_summary=8).eval()
+    randomize_weights(mod, 1)
+    mod = mod.to(torch.bfloat16).cuda()
+    x = orc.mixture_inputs(2, 90, 256, centroids=8, sigma=0.3, seed=2, dtype=torch.bfloat16).cuda()
+    st = mod.init_state(batch_size=2, device="cuda", dtype=torch.bfloat16)
+    _, st = mod.prefill_chunked(x[:, :40], st, block_size=16)
+    for t in range(40, 60):
+        _, st = mod.step(x[:, t:t + 1], st)
+    twin = state_from_bytes(state_to_bytes(st), "cuda")
+    assert (twin.pos, twin.recent_idx, twin.recent_filled) == (st.pos, st.recent_idx, st.recent_filled)
+    for t in range(60, 90):
+        ya, st = mod.step(x[:, t:t + 1], st)
+        yb, twin = mod.step(x[:, t:t + 1], twin)
+        assert torch.equal(ya, yb)
+    assert torch.equal(st._arena, twin._arena)
