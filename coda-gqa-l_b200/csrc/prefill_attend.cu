@@ -26,7 +26,7 @@ constexpr int PF_BN = 128;       // keys per tile
 // Register split after launch (setmaxnreg): the two softmax warpgroups grow, the third warpgroup shrinks.  A
 // warpgroup that asks for more than the CTA's pool (threads x registers at launch) can give waits forever, so the
 // launcher checks the sum against the kernel's compiled register count and refuses to launch otherwise.
-constexpr int PF_REGS_SOFTMAX = 216, PF_REGS_AUX = 72;
+constexpr int PF_REGS_SOFTMAX = 208, PF_REGS_AUX = 72;
 constexpr int PF_REGS_TOTAL = 256 * PF_REGS_SOFTMAX + 128 * PF_REGS_AUX;
 constexpr int PF_THREADS = 384;  // warps 0-3 / 4-7: softmax of the signal / noise stream, 8: TMA, 9: MMA issuer, 10-11 idle
 constexpr int PF_STAGES = 2;     // K/V tiles in flight
@@ -205,35 +205,21 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   uint64_t* s_full = kv_empty + PF_STAGES;          // [stream]
   uint64_t* p_full = s_full + 2;                    // [stream]
   uint64_t* pv_done = p_full + 2;                   // [stream]
-  uint64_t* q_empty = pv_done + 2;                  // every Q.K^T of the work item has completed: Q may be replaced
-  uint64_t* o_free = q_empty + 1;                   // the epilogue has read O of the work item: it may be overwritten
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 1);
-  float* xch = reinterpret_cast<float*>(tmem_slot + 2);   // [4][PF_BM] row sums exchanged between the two warp groups
-  uint32_t* sMask = reinterpret_cast<uint32_t*>(xch + 4 * PF_BM);   // visibility bits of the prefix slots, 32 per word
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint32_t* sMask = tmem_slot + 2;                  // visibility bits of the prefix slots, 32 per word
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  // Persistent CTA: work item w = (query tile x, head h, state b), w = blockIdx.x, + gridDim.x, ...  The
-  // producer and the MMA issuer run ahead into the next item while the softmax warps finish the current one,
-  // so that the start-up of an item (Q and first K/V tile in flight, first Q.K^T) hides under the epilogue of
-  // the one before; TMEM is allocated once.  Barrier parities follow running counters (tiles, items).
-  const int GX = (p.blk + PF_BM - 1) / PF_BM;
-  const int items = GX * p.H * p.B;
+  const int r0 = blockIdx.x * PF_BM, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
   const int NP = (p.Lbuf + PF_BN - 1) / PF_BN;                                   // prefix tiles
-  struct Item { int r0, h, b, hk, NT; };
-  auto decode = [&](int w) {
-    Item it;
-    it.r0 = (w % GX) * PF_BM; it.h = (w / GX) % p.H; it.b = w / (GX * p.H);
-    it.hk = it.h / (p.H / p.Hkv);
-    const int last_row = min(it.r0 + PF_BM, p.blk) - 1;
-    it.NT = NP + last_row / PF_BN + 1;                                            // prefix + block tiles (causal limit)
-    return it;
-  };
+  const int last_row = min(r0 + PF_BM, p.blk) - 1;
+  const int NB = last_row / PF_BN + 1;                                            // block tiles (causal limit)
+  const int NT = NP + NB;
 
   if (tid == 0) {
     tma::mbar_init(q_full, 1);
     for (int i = 0; i < PF_STAGES; ++i) { tma::mbar_init(&kv_full[i], 1); tma::mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { tma::mbar_init(&s_full[i], 1); tma::mbar_init(&p_full[i], 4); tma::mbar_init(&pv_done[i], 1); }
-    tma::mbar_init(q_empty, 1); tma::mbar_init(o_free, 8);
     tma::fence_barrier_init();
   }
   if (warp == 9) {                                   // TMEM: all 512 columns, owned by the MMA warp
@@ -251,32 +237,26 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   if (warp == 8) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
-      int g = 0;                                           // K/V tiles issued so far (ring position)
-      int n = 0;
-      for (int w = blockIdx.x; w < items; w += gridDim.x, ++n) {
-        const Item it = decode(w);
-        if (n > 0) tma::mbar_wait(q_empty, (n - 1) & 1, p.status, 10);
-        tma::mbar_expect_tx(q_full, 2 * Q_BYTES);
+      tma::mbar_expect_tx(q_full, 2 * Q_BYTES);
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf) {
+        tma_load_4d(sQs + hf * Q_HALF, &qmap, q_full, hf * 64, h, p.t0 + r0, b);
+        tma_load_4d(sQn + hf * Q_HALF, &qnmap, q_full, hf * 64, h, p.t0 + r0, b);
+      }
+      for (int j = 0; j < NT; ++j) {
+        const int st = j % PF_STAGES;
+        if (j >= PF_STAGES) tma::mbar_wait(&kv_empty[st], ((j / PF_STAGES) - 1) & 1, p.status, 11);
+        tma::mbar_expect_tx(&kv_full[st], 2 * KV_BYTES);
+        unsigned char* kd = sK + st * KV_BYTES;
+        unsigned char* vd = sV + st * KV_BYTES;
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf) {
-          tma_load_4d(sQs + hf * Q_HALF, &qmap, q_full, hf * 64, it.h, p.t0 + it.r0, it.b);
-          tma_load_4d(sQn + hf * Q_HALF, &qnmap, q_full, hf * 64, it.h, p.t0 + it.r0, it.b);
-        }
-        for (int j = 0; j < it.NT; ++j, ++g) {
-          const int st = g % PF_STAGES;
-          if (g >= PF_STAGES) tma::mbar_wait(&kv_empty[st], ((g / PF_STAGES) - 1) & 1, p.status, 11);
-          tma::mbar_expect_tx(&kv_full[st], 2 * KV_BYTES);
-          unsigned char* kd = sK + st * KV_BYTES;
-          unsigned char* vd = sV + st * KV_BYTES;
-#pragma unroll
-          for (int hf = 0; hf < HALVES; ++hf) {
-            if (j < NP) {
-              tma_load_3d(kd + hf * KV_HALF, &kpmap, &kv_full[st], hf * 64, j * PF_BN, it.b * p.Hkv + it.hk);
-              tma_load_3d(vd + hf * KV_HALF, &vpmap, &kv_full[st], hf * 64, j * PF_BN, it.b * p.Hkv + it.hk);
-            } else {
-              tma_load_4d(kd + hf * KV_HALF, &kbmap, &kv_full[st], hf * 64, it.hk, p.t0 + (j - NP) * PF_BN, it.b);
-              tma_load_4d(vd + hf * KV_HALF, &vbmap, &kv_full[st], hf * 64, it.hk, p.t0 + (j - NP) * PF_BN, it.b);
-            }
+          if (j < NP) {
+            tma_load_3d(kd + hf * KV_HALF, &kpmap, &kv_full[st], hf * 64, j * PF_BN, b * p.Hkv + hk);
+            tma_load_3d(vd + hf * KV_HALF, &vpmap, &kv_full[st], hf * 64, j * PF_BN, b * p.Hkv + hk);
+          } else {
+            tma_load_4d(kd + hf * KV_HALF, &kbmap, &kv_full[st], hf * 64, hk, p.t0 + (j - NP) * PF_BN, b);
+            tma_load_4d(vd + hf * KV_HALF, &vbmap, &kv_full[st], hf * 64, hk, p.t0 + (j - NP) * PF_BN, b);
           }
         }
       }
@@ -288,9 +268,8 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       constexpr uint32_t IDESC_PV = instr_desc(DH, true);
       // S_s = Q_s . K_j^T  (the stream's S columns are free: its previous P.V, which read P from them, was
       // issued earlier by this same thread and the tensor pipe executes in order)
-      // g: running tile count of this CTA (ring stage g % PF_STAGES, barrier parities g & 1)
-      auto issue_qk = [&](int g, int s) {
-        const uint32_t kbase = smem_u32(sK + (g % PF_STAGES) * KV_BYTES);
+      auto issue_qk = [&](int j, int s) {
+        const uint32_t kbase = smem_u32(sK + (j % PF_STAGES) * KV_BYTES);
         const uint32_t qbase = smem_u32(s ? sQn : sQs);
         const uint32_t dcol = tmem + (s ? TM_SN : 0u);
 #pragma unroll
@@ -301,44 +280,30 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         }
         tc_commit(&s_full[s]);
       };
-      int g0 = 0, n = 0;
-      for (int w = blockIdx.x; w < items; w += gridDim.x, ++n) {
-        const int NT = decode(w).NT;
-        tma::mbar_wait(q_full, n & 1, p.status, 13);
-        tma::mbar_wait(&kv_full[g0 % PF_STAGES], (g0 / PF_STAGES) & 1, p.status, 14);
-        tc_fence_after();
-        // S columns are free: the previous item's last P.V of each stream was issued earlier by this thread
-        // and the tensor pipe executes in order
-        issue_qk(g0, 0);
-        issue_qk(g0, 1);
-        if (NT == 1) tc_commit(q_empty);
-        for (int j = 0; j < NT; ++j) {
-          const int g = g0 + j;
-          const int st = g % PF_STAGES;
-          const uint32_t vbase = smem_u32(sV + st * KV_BYTES);
-          if (j + 1 < NT) tma::mbar_wait(&kv_full[(g + 1) % PF_STAGES], ((g + 1) / PF_STAGES) & 1, p.status, 14);
+      tma::mbar_wait(q_full, 0, p.status, 13);
+      tma::mbar_wait(&kv_full[0], 0, p.status, 14);
+      tc_fence_after();
+      issue_qk(0, 0);
+      issue_qk(0, 1);
+      for (int j = 0; j < NT; ++j) {
+        const int st = j % PF_STAGES;
+        const uint32_t vbase = smem_u32(sV + st * KV_BYTES);
+        if (j + 1 < NT) tma::mbar_wait(&kv_full[(j + 1) % PF_STAGES], ((j + 1) / PF_STAGES) & 1, p.status, 14);
 #pragma unroll
-          for (int s = 0; s < 2; ++s) {
-            tma::mbar_wait(&p_full[s], g & 1, p.status, 12);
-            // the first P.V of an item overwrites O: the previous item's epilogue must have read it
-            if (j == 0 && s == 0 && n > 0) tma::mbar_wait(o_free, (n - 1) & 1, p.status, 15);
-            tc_fence_after();
-            const uint32_t pcol = tmem + (s ? TM_SN : 0u);          // P (bf16 pairs) sits in the first 64 S columns
-            const uint32_t dcol = tmem + (s ? TM_ON : TM_OS);
+        for (int s = 0; s < 2; ++s) {
+          tma::mbar_wait(&p_full[s], j & 1, p.status, 12);
+          tc_fence_after();
+          const uint32_t pcol = tmem + (s ? TM_SN : 0u);          // P (bf16 pairs) sits in the first 64 S columns
+          const uint32_t dcol = tmem + (s ? TM_ON : TM_OS);
 #pragma unroll
-            for (int kk = 0; kk < KSTEPS_PV; ++kk) {
-              const uint64_t bd = smem_desc(vbase + kk * 2048, KV_HALF, 1024);
-              tc_mma_ts(dcol, pcol + kk * 8, bd, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-            }
-            tc_commit(&pv_done[s]);
-            if (s == 1) tc_commit(&kv_empty[st]);
-            if (j + 1 < NT) {
-              issue_qk(g + 1, s);
-              if (j + 2 == NT && s == 1) tc_commit(q_empty);       // that was the item's last Q.K^T
-            }
+          for (int kk = 0; kk < KSTEPS_PV; ++kk) {
+            const uint64_t bd = smem_desc(vbase + kk * 2048, KV_HALF, 1024);
+            tc_mma_ts(dcol, pcol + kk * 8, bd, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
           }
+          tc_commit(&pv_done[s]);
+          if (s == 1) tc_commit(&kv_empty[st]);
+          if (j + 1 < NT) issue_qk(j + 1, s);
         }
-        g0 += NT;
       }
     }
   }
@@ -356,42 +321,24 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     const int sw = warp & 3;                              // warp index inside its group
     const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;                  // row of the query tile
+    const int grow = r0 + row;                            // row inside the block
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_col = lane_addr + (s ? TM_SN : 0u);
     const uint32_t o_col = lane_addr + (s ? TM_ON : TM_OS);
-    constexpr int HC = DH / 2;                             // epilogue columns per thread
-    // visibility bytes of the prefix slots this lane turns into mask bits (signal warps; word w32 = sw + 4k):
-    // the next item's are requested before the epilogue and turned into sMask after it
-    constexpr int MW = 8;                                  // up to 32 mask words = 1024 prefix slots per 4 warps
-    uint8_t mvis[MW];
-    auto fetch_mask = [&](int bb) {
-#pragma unroll
-      for (int k = 0; k < MW; ++k) {
-        const int c = (sw + 4 * k) * 32 + lane;
-        mvis[k] = (sw + 4 * k < NP * 4 && c < p.Lbuf) ? (p.mask_unused ? p.allowed[(long long)bb * p.Lbuf + c] : (uint8_t)1) : (uint8_t)0;
+    if (s == 0) {                                         // visibility bits of the prefix slots
+      for (int w32 = sw; w32 < NP * 4; w32 += 4) {
+        const int c = w32 * 32 + lane;
+        const bool vis = c < p.Lbuf && (!p.mask_unused || p.allowed[(long long)b * p.Lbuf + c] != 0);
+        const unsigned bits = __ballot_sync(0xffffffffu, vis);
+        if (lane == 0) sMask[w32] = bits;
       }
-    };
-    auto publish_mask = [&]() {
-#pragma unroll
-      for (int k = 0; k < MW; ++k) {
-        const unsigned bits = __ballot_sync(0xffffffffu, mvis[k] != 0);
-        if (lane == 0 && sw + 4 * k < NP * 4) sMask[sw + 4 * k] = bits;
-      }
-    };
-    if (s == 0 && (int)blockIdx.x < items) { fetch_mask(decode(blockIdx.x).b); publish_mask(); }
-
-    int g0 = 0, n = 0;                                     // running tile / item counts (barrier parities)
-    for (int w = blockIdx.x; w < items; w += gridDim.x, ++n) {
-    const int r0 = (w % GX) * PF_BM;
-    const int NT = NP + (min(r0 + PF_BM, p.blk) - 1) / PF_BN + 1;
-    const int grow = r0 + row;                            // row inside the block
-    bar_softmax_all();                                    // sMask of this item is in place
+    }
+    bar_softmax_all();
 
     float mb = -INFINITY;                                 // exponent base (lags the true max by < GAP)
     float l = 0.f;
     for (int j = 0; j < NT; ++j) {
-      const int g = g0 + j;
-      tma::mbar_wait(&s_full[s], g & 1, p.status, 16);
+      tma::mbar_wait(&s_full[s], j & 1, p.status, 16);
       tc_fence_after();
       // Visibility per group of 32 keys.  cls: 2 = all visible, 0 = none, 1 = mixed; the class is the same for
       // every lane of a warp: prefix slots carry one mask per state, and in a block tile the 32 rows of a warp
@@ -449,7 +396,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       // rescale O when some row of this warp moved its exponent base (not for the first tile: the first
       // P.V overwrites O instead of accumulating); O must be quiescent: wait for the previous P.V
       if (__any_sync(0xffffffffu, (alpha != 1.f) && j > 0)) {
-        tma::mbar_wait(&pv_done[s], (g - 1) & 1, p.status, 19);
+        tma::mbar_wait(&pv_done[s], (j - 1) & 1, p.status, 19);
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < DH / 16; ++c) {
@@ -502,17 +449,24 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     // ---- epilogue: signal / l_s - lambda * noise / l_n, head RMSNorm, store ----
     // Both accumulators of a row sit in the same TMEM lane, so a thread reads both streams directly; the two
     // warp groups split the head dimension (group s takes columns s*Dh/2 ..) and exchange only the row sums
-    // (1/l of each stream, partial sums of squares) through a small shared-memory area.  fp32 end to end with a
-    // single rounding of the result.
-    const bool more = w + (int)gridDim.x < items;
-    if (s == 0 && more) fetch_mask(decode(w + gridDim.x).b);
-    const int h = (w / GX) % p.H, b = w / (GX * p.H);      // (recomputed here: few values live across the tile loop)
+    // (1/l of each stream, partial sums of squares) through the shared memory of the query tiles, which are
+    // dead once every Q.K^T has completed.  fp32 end to end with a single rounding of the result.
     const bool valid = grow < p.blk;
     float lam = 0.f;
     if (valid) lam = bf16_round(p.lam[(long long)b * p.lam_bs + (long long)(p.t0 + grow) * p.lam_rs + h]);
-    tma::mbar_wait(&pv_done[0], (g0 + NT - 1) & 1, p.status, 18);
-    tma::mbar_wait(&pv_done[1], (g0 + NT - 1) & 1, p.status, 18);
+    constexpr int HC = DH / 2;                             // columns per thread
+    float nwv[HC];
+    if (p.norm_full) {
+#pragma unroll
+      for (int i = 0; i < HC / 2; ++i) {
+        const __nv_bfloat162 wv = reinterpret_cast<const __nv_bfloat162*>(p.norm_w)[(s * HC) / 2 + i];
+        nwv[2 * i] = __low2float(wv); nwv[2 * i + 1] = __high2float(wv);
+      }
+    }
+    tma::mbar_wait(&pv_done[0], (NT - 1) & 1, p.status, 18);
+    tma::mbar_wait(&pv_done[1], (NT - 1) & 1, p.status, 18);
     tc_fence_after();
+    float* xch = reinterpret_cast<float*>(sQs);            // [2][128] 1/l, then [2][128] partial sums of squares
     xch[s * PF_BM + row] = l > 0.f ? 1.f / l : 0.f;
     bar_softmax_all();
     const float inv_s = xch[row], inv_n = xch[PF_BM + row];
@@ -531,10 +485,6 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         dv[c * 32 + i] = d;
       }
     }
-    // O of this item is in registers: the MMA issuer may start the next item's P.V
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) tma::mbar_arrive(o_free);
     xch[2 * PF_BM + s * PF_BM + row] = sq;
     bar_softmax_all();
     if (valid) {
@@ -547,19 +497,12 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float y0 = dv[8 * i + 2 * e] * rs, y1 = dv[8 * i + 2 * e + 1] * rs;
-          if (p.norm_full) {
-            const __nv_bfloat162 wv = reinterpret_cast<const __nv_bfloat162*>(p.norm_w)[(s * HC) / 2 + 4 * i + e];
-            y0 *= __low2float(wv); y1 *= __high2float(wv);
-          }
+          if (p.norm_full) { y0 *= nwv[8 * i + 2 * e]; y1 *= nwv[8 * i + 2 * e + 1]; }
           w[e] = pack2(y0, y1);
         }
         reinterpret_cast<uint4*>(op)[i] = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    // every warp has left its tile loop (the two barriers above): the mask words may change
-    if (s == 0 && more) publish_mask();
-    g0 += NT;
-    }  // work items
     tc_fence_before();
   }
 
@@ -570,7 +513,7 @@ template <int DH>
 size_t prefill_smem(int Lbuf) {
   const int NP = (Lbuf + PF_BN - 1) / PF_BN;
   return (size_t)2 * (DH / 64) * PF_BM * 128 + 2 * PF_STAGES * (size_t)(DH / 64) * PF_BN * 128 +
-         (9 + 2 * PF_STAGES) * 8 + 8 + 4 * PF_BM * 4 + (size_t)NP * 4 * 4 + 1024 + 64;
+         (7 + 2 * PF_STAGES) * 8 + 8 + (size_t)NP * 4 * 4 + 1024 + 64;
 }
 
 template <int DH>
@@ -582,15 +525,7 @@ int launch_prefill(const CUtensorMap* maps, const PrefillParams& p, cudaStream_t
     cudaFuncSetAttribute(prefill_attend_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
     configured = true;
   }
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
-  }
-  const long long items = (long long)((p.blk + PF_BM - 1) / PF_BM) * p.H * p.B;
-  CODA_REQUIRE(items < (1ll << 31), CODA_ERR_LIMIT, "prefill_attend: too many work items");
-  dim3 grid((unsigned)(items < num_sms ? items : num_sms), 1, 1);
+  dim3 grid((p.blk + PF_BM - 1) / PF_BM, p.H, p.B);
   {
     static int pool = 0;
     if (pool == 0) {
