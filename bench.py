@@ -345,9 +345,13 @@ def main():
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_decode_baseline(w, budget_s=15.0, threads=cores)
+    # Every rank finishes its own (unsynchronised) roofline section before any rank tears the process group down:
+    # a communicator destroyed while a peer still runs kernels took that peer's kernels down with it.
+    barrier()
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        barrier()
         dist.destroy_process_group()
 
 

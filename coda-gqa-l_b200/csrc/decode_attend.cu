@@ -31,12 +31,7 @@ constexpr int DA_TILE = 64;          // slots per stage
 constexpr int DA_MAX_STAGES = 8;
 constexpr int DA_CWARPS = 8;         // consumer warps (two groups of four)
 constexpr int DA_AWARPS = 4;         // auxiliary warps (query preparation, merge + epilogue)
-// Register split after launch (setmaxnreg), per warpgroup.  A warpgroup asking for more than the CTA's pool
-// (threads x registers at launch) can give would wait forever: the launcher checks the sum against the kernel's
-// compiled register count and refuses to launch otherwise.
-constexpr int DA_REGS_CONSUMER = 152, DA_REGS_AUX = 104, DA_REGS_PRODUCER = 40;
-constexpr int DA_REGS_TOTAL = DA_CWARPS * 32 * DA_REGS_CONSUMER + DA_AWARPS * 32 * DA_REGS_AUX + 128 * DA_REGS_PRODUCER;
-constexpr int DA_THREADS = (DA_CWARPS + DA_AWARPS + 4) * 32;   // the producer's warpgroup has one working warp
+constexpr int DA_THREADS = (DA_CWARPS + DA_AWARPS + 1) * 32;   // 8 consumer, 4 auxiliary, 1 producer warp
 
 struct DecodeParams {
   int B, H, Hkv, G, Lbuf, mask_unused, norm_full, interleaved, angle_bf16, stages;
@@ -161,10 +156,8 @@ __global__ void __launch_bounds__(128) decode_prep_kernel(DecodeParams p, const 
   for (int i = tid; i < DecodeRecord::mask_bytes(p.Lbuf); i += blockDim.x) mk[i] = i < p.Lbuf ? alb[i] : 0;
 }
 
-// 120 registers per thread at launch (512 threads: 60 K of the SM's 64 K registers, so that a tool which
-// needs a few registers of its own can still launch the kernel); the roles re-split them below.
 template <int DH, int NQ>
-__global__ void __maxnreg__(120)
+__global__ void __launch_bounds__(DA_THREADS, 1)
 decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
   constexpr int KSTEPS = DH / 16;            // k-steps of Q.K^T
   constexpr int MT_O = DH / 16;              // m-tiles of the (transposed) output
@@ -201,11 +194,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   }
   __syncthreads();
 
-  // Registers follow the roles (per warpgroup): the consumers hold the output accumulators and the query
-  // fragments, the other warps need little.
   if (warp >= DA_CWARPS + DA_AWARPS) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DA_REGS_PRODUCER));
-    if (warp > DA_CWARPS + DA_AWARPS) return;
     // ---------------- producer: records first, then the ring of K/V tiles, across plane boundaries ----------------
     if (lane == 0) {
       int bi = 0, round = 0, i = 0;                        // ring slot, how often the ring has wrapped, plane count
@@ -244,7 +233,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   }
 
   if (warp >= DA_CWARPS) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DA_REGS_AUX));
     // ---------------- auxiliary warps: merge of the eight partial softmaxes + epilogue, one warp per query head ----------------
     const int aw = warp - DA_CWARPS;
     constexpr int DV = 4;                                  // output dims per lane: 4*lane .. 4*lane+3
@@ -254,6 +242,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     for (int k = 0; k < DV; ++k) nw[k] = (p.norm_full && dact) ? __bfloat162float(p.norm_w[4 * lane + k]) : 1.f;
     int i = 0;
     for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
+      mbar_wait(&q_ready[i & 1], (i >> 1) & 1, p.status, 7);   // lambda comes from the plane's record (a bulk copy: observed through its own barrier)
       mbar_wait(comb_full, i & 1, p.status, 5);
       const int b = plane / p.Hkv, hk = plane % p.Hkv;
       const float* sLam = reinterpret_cast<const float*>(rec0 + (i & 1) * L.rec_stride + lam_off);
@@ -321,7 +310,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   //   S^T[16 slots x 8 q] = K[16 x Dh] . Q^T,   O^T[Dh x 8 q] += V^T[16 dh x 16 slots] . P^T
   // so that the 2G <= 8 live query rows fill an n-tile exactly (NQ = 2 n-tiles for 8 < 2G <= 16); with the
   // queries as m = 16 half of every tile would be padding, and the legacy tensor path is what bounds a tile.
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DA_REGS_CONSUMER));
   const int grp = warp >> 2, gw = warp & 3;            // group, warp inside the group (owns slots gw*16..+15 of a tile)
   const int li = lane >> 3, lr = lane & 7;
   const int qa = 2 * (lane & 3);                        // this thread's query columns: nq*8 + qa + {0, 1}
@@ -347,10 +335,15 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     float mrun[NQ][2], lrun[NQ][2];                       // running max / (per-thread partial) sum of columns qa, qa+1
 #pragma unroll
     for (int nq = 0; nq < NQ; ++nq) { mrun[nq][0] = mrun[nq][1] = -INFINITY; lrun[nq][0] = lrun[nq][1] = 0.f; }
-    // tile s of this CTA's i-th plane is the (i * nst + s)-th tile through the ring
-    int bi = (i * nst + grp) % S, round = (i * nst + grp) / S;
+    // Tile s of this CTA's i-th plane is the t = (i * nst + s)-th tile through the ring (stage t % S).  A group
+    // takes the tiles of ITS parity of t, and S is even, so a ring stage is only ever consumed by one group:
+    // a parity wait tells "this phase or the one before" apart, nothing more, and a group that met a stage
+    // whose previous use belonged to the other group could run past a phase it never observed (TMA tiles
+    // need not land in issue order).
+    const int s0 = (grp ^ (i * nst)) & 1;
+    int bi = (i * nst + s0) % S, round = (i * nst + s0) / S;
 
-    for (int s = grp; s < nst; s += 2) {
+    for (int s = s0; s < nst; s += 2) {
       mbar_wait(&full[bi], round & 1, p.status, 2);
       const uint32_t kb = smem_u32(stage0 + bi * 2 * TILE_BYTES);
       const uint32_t vb = kb + TILE_BYTES;
@@ -471,6 +464,7 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
   const int fixed = DecodeSmem<DH>(0, p.G, p.Lbuf).total + 1024;
   int stages = (BUDGET - fixed) / (2 * DecodeSmem<DH>::TILE_BYTES);
   if (stages > DA_MAX_STAGES) stages = DA_MAX_STAGES;
+  stages &= ~1;                                      // even: each ring stage belongs to one consumer group (see the kernel)
   CODA_REQUIRE(stages >= 2, CODA_ERR_LIMIT, "decode_attend: %d slots leave no room for the tile ring in shared memory", p.Lbuf);
   p.stages = stages;
   const size_t smem = (size_t)DecodeSmem<DH>(stages, p.G, p.Lbuf).total + 1024;
@@ -484,15 +478,6 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
     int dev = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
-  }
-  {
-    static int pool = 0;
-    if (pool == 0) {
-      cudaFuncAttributes fa;
-      CODA_REQUIRE(cudaFuncGetAttributes(&fa, decode_attend_kernel<DH, NQ>) == cudaSuccess, CODA_ERR_LAUNCH, "decode_attend: cudaFuncGetAttributes failed");
-      pool = fa.numRegs * DA_THREADS;
-    }
-    CODA_REQUIRE(pool >= DA_REGS_TOTAL, CODA_ERR_LAUNCH, "decode_attend: register pool %d below the %d the roles ask for", pool, DA_REGS_TOTAL);
   }
   const int nplanes = p.B * p.Hkv;
   decode_attend_kernel<DH, NQ><<<nplanes < num_sms ? nplanes : num_sms, DA_THREADS, smem, s>>>(km, vm, p);

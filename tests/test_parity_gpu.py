@@ -349,3 +349,43 @@ def test_wire_format_restores_a_live_state():
         yb, twin = mod.step(x[:, t:t + 1], twin)
         assert torch.equal(ya, yb)
     assert torch.equal(st._arena, twin._arena)
+
+
+@pytest.mark.gpu
+def test_decode_attention_back_to_back_replays_are_stable():
+    """Thousands of back-to-back launches of the decode attention kernel (a CUDA graph, CTAs with two planes
+    each, tiles landing in any order) give the same bits every time.  Guards the ring's stage ownership: each
+    stage is consumed by one consumer group only, so a parity wait can never run past an unobserved phase."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    from coda_gqa_l_b200._lib import RingPos
+    torch.manual_seed(0)
+    B, H, Hkv, Dh = 32, 8, 8, 128                       # 256 planes on 148 SMs, 6 tiles of 64 slots per plane
+    mod = CoDAGQALandmarkPerf2(embed_dim=H * Dh, num_heads=H, num_kv_heads=Hkv, window=256, num_landmarks_exact=64,
+                               num_landmarks_summary=64, head_norm_mode="identity", rope_interleaved=False)
+    mod = mod.eval().to(torch.bfloat16).cuda()
+    st = mod.init_state(batch_size=B, device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(B, 384, H * Dh, device="cuda") * 0.5).to(torch.bfloat16)
+    mod.prefill_chunked(x, st, block_size=128, return_outputs=False)
+    cfg = mod._cfg(B, torch.bfloat16, st)
+    q = torch.randn(B, H * Dh, device="cuda", dtype=torch.bfloat16)
+    lam = torch.randn(B, H, device="cuda", dtype=torch.bfloat16)
+    outs = [torch.empty(B, 1, H * Dh, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        mod.decode_attend_launch(cfg, st, rp, 1, q, lam, outs[0])         # writes the decode records
+        torch.cuda.synchronize()
+        ref = outs[0].clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for o in outs:
+                mod.decode_attend_prepared_launch(cfg, st, o)
+        for rep in range(1500):
+            g.replay()
+            if rep % 500 == 499:
+                torch.cuda.synchronize()
+                for o in outs:
+                    assert torch.equal(o, ref), f"replay {rep}: output changed"
+    torch.cuda.synchronize()
+    assert mod.device_status() == 0
