@@ -463,12 +463,16 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         nwv[2 * i] = __low2float(wv); nwv[2 * i + 1] = __high2float(wv);
       }
     }
-    tma::mbar_wait(&pv_done[0], (NT - 1) & 1, p.status, 18);
-    tma::mbar_wait(&pv_done[1], (NT - 1) & 1, p.status, 18);
+    // Each group waits for ITS stream's last P.V only -- a barrier whose phases it has followed in order; a
+    // parity wait on the other stream's barrier could pass on a phase two tiles back.  The block barrier below
+    // then carries "both streams are complete" across the groups.
+    tma::mbar_wait(&pv_done[s], (NT - 1) & 1, p.status, 18);
     tc_fence_after();
     float* xch = reinterpret_cast<float*>(sQs);            // [2][128] 1/l, then [2][128] partial sums of squares
     xch[s * PF_BM + row] = l > 0.f ? 1.f / l : 0.f;
+    tc_fence_before();
     bar_softmax_all();
+    tc_fence_after();
     const float inv_s = xch[row], inv_n = xch[PF_BM + row];
     float dv[HC];                                          // sig - lam * noise of this thread's columns
     float sq = 0.f;

@@ -389,3 +389,26 @@ def test_decode_attention_back_to_back_replays_are_stable():
                     assert torch.equal(o, ref), f"replay {rep}: output changed"
     torch.cuda.synchronize()
     assert mod.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_prefill_attention_repeated_launches_are_stable():
+    """The tcgen05 prefill kernel on the same state and inputs, launched back to back many times (no cache
+    write), returns the same bits every time: its barriers are only ever waited on by threads that follow
+    their phases in order."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    torch.manual_seed(1)
+    mod = CoDAGQALandmarkPerf2(embed_dim=1024, num_heads=8, num_kv_heads=2, window=256, num_landmarks_exact=64,
+                               num_landmarks_summary=64, head_norm_mode="identity", rope_interleaved=False)
+    mod = mod.eval().to(torch.bfloat16).cuda()
+    B = 24                                               # 24 x 8 heads = 192 CTAs: more than one wave
+    st = mod.init_state(batch_size=B, device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(B, 512, 1024, device="cuda") * 0.5).to(torch.bfloat16)
+    mod.prefill_chunked(x[:, :384], st, block_size=128, return_outputs=False)
+    ref, _ = mod.prefill_chunked(x[:, 384:], st, block_size=128, write_cache=False)
+    ref = ref.clone()
+    for rep in range(300):
+        y, _ = mod.prefill_chunked(x[:, 384:], st, block_size=128, write_cache=False)
+        if rep % 50 == 49:
+            assert torch.equal(y, ref), f"repeat {rep}: output changed"
+    assert mod.device_status() == 0
