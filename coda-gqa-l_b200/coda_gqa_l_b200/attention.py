@@ -523,6 +523,12 @@ class CoDAGQALandmarkPerf2(nn.Module):
         cfg = self._cfg(B, x.dtype, state)
         q, _, _, lam_logit, _ = self._project(x, need_kv=False)
         qp = state.pos if query_pos is None else int(query_pos)
+        if self._tuned_decode(cfg):
+            # fused kernel: raw query projection in, RoPE at qp / theta rotation / lambda sigmoid inside
+            out = torch.empty((B, 1, self.num_heads * self.head_dim), device=x.device, dtype=x.dtype)
+            rp = RingPos(int(qp), int(state.recent_idx), int(state.recent_filled), None)
+            self.decode_attend_launch(cfg, state, rp, 0, q, lam_logit, out)
+            return self.o_proj(out)
         qn, lam, _ = self._prep(cfg, 1, qp, q, None, lam_logit, None, False)
         out = torch.empty_like(q)
         self._attend(cfg, state, 1, q, qn, lam, None, None, out)

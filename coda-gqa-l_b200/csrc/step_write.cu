@@ -283,6 +283,9 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   const int Lbuf = W + Me + Ms, MM = Me + Ms;
 
   __shared__ float ke[DH], ve[DH], vhat[DH], khat[LFD], cs[DH / 2], sn[DH / 2], s_den[2];
+  // unit vectors for the scoring loop: the second half of each starts 4 words further, so that the two halves
+  // (read by alternate lanes) fall into different banks
+  __shared__ float hv[DH + 4], hk[LFD + 4];
   __shared__ int s_eidx, s_eflag, s_sidx, s_sflag;
   __shared__ float s_keep;
   float* xdots = sm;                                      // [Hkv][MM] per-head dots of every CTA of the cluster
@@ -482,8 +485,8 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     if (lane == 0) s_den[warp] = fmaxf(El<T>::rnd(sqrtf(ss)), 1e-6f);
   }
   __syncthreads();
-  if (is_v) vhat[d] = t_div<T>(ve[d], s_den[0]);
-  if (is_k && d >= LF) khat[d - LF] = t_div<T>(ke[d], s_den[1]);
+  if (is_v) hv[d + (d >= DH / 2 ? 4 : 0)] = t_div<T>(ve[d], s_den[0]);
+  if (is_k && d >= LF) hk[(d - LF) + ((d - LF) >= LFD / 2 ? 4 : 0)] = t_div<T>(ke[d], s_den[1]);
   __syncthreads();
 
   asm volatile("barrier.cluster.wait.aligned;" ::: "memory");       // all CTAs of the cluster are running
@@ -494,7 +497,7 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     float acc0 = 0.f, acc1 = 0.f;
     if (it < 2 * MM) {
       const bool ex = it < 2 * Me;
-      const float* a = ex ? vhat + (it & 1) * (DH / 2) : khat + (it & 1) * (LFD / 2);
+      const float* a = ex ? hv + (it & 1) * (DH / 2 + 4) : hk + (it & 1) * (LFD / 2 + 4);
       const int nv = ex ? EV : SV;
 #pragma unroll
       for (int j = 0; j < EV; ++j) {

@@ -412,3 +412,27 @@ def test_prefill_attention_repeated_launches_are_stable():
         if rep % 50 == 49:
             assert torch.equal(y, ref), f"repeat {rep}: output changed"
     assert mod.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_attend_step_tuned_matches_generic():
+    """attend_step (attention only, no cache write) on the fused decode kernel against the generic kernels,
+    at the state's own position and at an explicit query position."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    from tests.scenarios import randomize_weights
+    torch.manual_seed(2)
+    mod = CoDAGQALandmarkPerf2(embed_dim=512, num_heads=4, num_kv_heads=2, window=48, num_landmarks_exact=16,
+                               num_landmarks_summary=8).eval()
+    randomize_weights(mod, 5)
+    mod = mod.to(torch.bfloat16).cuda()
+    x = orc.mixture_inputs(3, 120, 512, centroids=8, sigma=0.3, seed=3, dtype=torch.bfloat16).cuda()
+    st = mod.init_state(batch_size=3, device="cuda", dtype=torch.bfloat16)
+    _, st = mod.prefill_chunked(x[:, :100], st, block_size=32)
+    for qpos in (None, 7, 250):
+        mod.use_tuned_kernels = True
+        ya = mod.attend_step(x[:, 100:101], st, query_pos=qpos)
+        mod.use_tuned_kernels = False
+        yb = mod.attend_step(x[:, 100:101], st, query_pos=qpos)
+        assert rel_err(ya, yb) < 5e-3, f"query_pos={qpos}"
+    mod.use_tuned_kernels = True
+    assert mod.device_status() == 0
