@@ -12,6 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libcoda_b200.so")
 
 CODA_F32, CODA_BF16 = 0, 1
+CODA_EVENT_WORDS = 16   # int32 words per state in the routing-event record (coda_b200.h)
 
 
 class LayerCfg(C.Structure):
@@ -26,7 +27,7 @@ class LayerCfg(C.Structure):
 class StatePtrs(C.Structure):
     """struct coda_state_ptrs"""
     _fields_ = [(n, C.c_void_p) for n in (
-        "k_buf", "v_buf", "allowed", "g_recent", "mem_last_exact", "exact_v_norm", "sum_lf_k_norm")]
+        "k_buf", "v_buf", "allowed", "g_recent", "mem_last_exact", "exact_v_norm", "sum_lf_k_norm", "events")]
 
 
 class RingPos(C.Structure):

@@ -29,6 +29,20 @@ __all__ = ["CoDAGQALandmarkPerf2", "CoDAGQALandmarkStatePerf2"]
 _DT = {torch.float32: _lib.CODA_F32, torch.bfloat16: _lib.CODA_BF16}
 
 
+METRIC_KEYS = ("exact_hits", "exact_inserts", "exact_overwrites", "exact_fill_ratio", "summary_updates",
+               "summary_inserts", "summary_fill_ratio", "tokens_gated_out", "total_evictions", "exact_frustrated",
+               "summary_frustrated", "active_exact", "active_summary", "expansions_exact", "expansions_summary")
+
+
+def new_metrics(active_exact: int, active_summary: int) -> Dict[str, object]:
+    """The counters a state carries when ``collect_metrics`` is on (upstream attention.py:319-336)."""
+    m: Dict[str, object] = {k: 0 for k in METRIC_KEYS}
+    m["exact_fill_ratio"] = 0.0
+    m["summary_fill_ratio"] = 0.0
+    m["active_exact"], m["active_summary"] = int(active_exact), int(active_summary)
+    return m
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -173,10 +187,6 @@ class CoDAGQALandmarkPerf2(nn.Module):
         K low-frequency band, summary V) from the generator of ``device``; a CPU device may be
         given to stage a state (e.g. to reproduce a CPU-seeded initial state) and moved with
         :func:`state_to`, but the compute methods only accept CUDA states."""
-        if self.Me_min != self.Me_max or self.Ms_min != self.Ms_max:
-            raise NotImplementedError("dynamic bank expansion (min_landmarks_* != max_landmarks_*) is not supported")
-        if self.collect_metrics:
-            raise NotImplementedError("collect_metrics=True is not supported by the CUDA path")
         if dtype not in _DT:
             raise RuntimeError(f"unsupported dtype {dtype}: the CUDA kernels handle float32 and bfloat16")
         B, W, Me, Ms = int(batch_size), self.window, self.Me, self.Ms
@@ -197,6 +207,8 @@ class CoDAGQALandmarkPerf2(nn.Module):
             st._exact_v_norm.copy_(F.normalize(st.v_buf[:, :, W:W + Me, :], dim=-1, eps=1e-6))
         if Ms > 0:
             st._sum_lf_k_norm.copy_(F.normalize(st.k_buf[:, :, W + Me:, self.lf_start:], dim=-1, eps=1e-6))
+        if self.collect_metrics:
+            st.metrics = new_metrics(st.active_exact, st.active_summary)
         return st
 
     # ------------------------------------------------------------------ plumbing
@@ -225,6 +237,106 @@ class CoDAGQALandmarkPerf2(nn.Module):
         if st.g_recent.dtype != torch.float32:
             st.g_recent = st.g_recent.float()
 
+    # ------------------------------------------------------------------ metrics / bank expansion
+    @property
+    def expandable(self) -> bool:
+        """True when the banks start below their full size and grow under pressure."""
+        return self.Me_min != self.Me_max or self.Ms_min != self.Ms_max
+
+    def _tracked(self, st: CoDAGQALandmarkStatePerf2) -> bool:
+        """Does a cache write on ``st`` have to report its routing events to the host?  (Counters and the
+        growth decision are host scalars, so such a write ends with one small device-to-host read.)"""
+        return self.expandable or st.metrics is not None
+
+    def _arm_events(self, st: CoDAGQALandmarkStatePerf2) -> None:
+        """Give ``st`` the int32 [B, 16] event record the cache-write kernels fill (or take it away)."""
+        if not self._tracked(st):
+            st._events = None
+        elif st._events is None or st._events.device != st.k_buf.device or st._events.shape[0] != st.k_buf.shape[0]:
+            st._events = torch.zeros((st.k_buf.shape[0], _lib.CODA_EVENT_WORDS), device=st.k_buf.device,
+                                     dtype=torch.int32)
+
+    def _log_ceiling(self, tokens_seen: int) -> Tuple[int, int]:
+        """Largest active bank sizes allowed after ``tokens_seen`` tokens (upstream attention.py:344-356)."""
+        if self.expansion_t_max <= 0:
+            return self.Me_max, self.Ms_max
+        ratio = min(math.log(1 + tokens_seen) / math.log(1 + self.expansion_t_max), 1.0)
+        return (self.Me_min + int((self.Me_max - self.Me_min) * ratio),
+                self.Ms_min + int((self.Ms_max - self.Ms_min) * ratio))
+
+    def _try_expand(self, st: CoDAGQALandmarkStatePerf2, frustrated_exact: int, frustrated_summary: int) -> None:
+        """Grow the active capacities under pressure, up to the logarithmic ceiling (upstream
+        attention.py:358-390).  ``st.pos`` must still be the position before the write."""
+        if not self.expandable or (frustrated_exact <= 0 and frustrated_summary <= 0):
+            return
+        ceil_e, ceil_s = self._log_ceiling(int(st.pos))
+        grow_e = grow_s = 0
+        if frustrated_exact > 0 and st.active_exact < ceil_e:
+            grow_e = min(int(frustrated_exact), ceil_e - st.active_exact)
+            st.active_exact += grow_e
+        if frustrated_summary > 0 and st.active_summary < ceil_s:
+            grow_s = min(int(frustrated_summary), ceil_s - st.active_summary)
+            st.active_summary += grow_s
+        if st.metrics is not None:
+            st.metrics["active_exact"], st.metrics["active_summary"] = st.active_exact, st.active_summary
+            st.metrics["expansions_exact"] += grow_e
+            st.metrics["expansions_summary"] += grow_s
+
+    def _account(self, st: CoDAGQALandmarkStatePerf2, n_evicted: int, block: bool) -> None:
+        """Host side of a cache write that evicted ``n_evicted`` ring tokens per state: read the event record
+        the kernel left, update the counters and grow the banks, in upstream's order (single token:
+        memory_banks.py:315-337 and :416-432; block: :758-774 and :934-950).  Call before ``st.pos`` advances.
+
+        Event words per state: [0] exact candidates gated out, [1] hits, [2] inserts, [3] overwrites,
+        [4] frustrated (single token: 0/1), [5] summary updates, [6] first fills, [7] every active summary slot
+        in use afterwards, [8] a summary candidate came in."""
+        if n_evicted <= 0 or not self._tracked(st):
+            return
+        W, Me, Ms = self.window, self.Me, self.Ms
+        do_e = Me > 0 and (not block or self.exact_candidates_per_block > 0)
+        do_s = Ms > 0 and (not block or self.summary_candidates_per_block > 0)
+        m = st.metrics
+        if m is not None:
+            m["total_evictions"] += int(n_evicted)
+        if not (do_e or do_s):
+            return
+        # everything the host needs in one small tensor, hence one synchronising read
+        evf = st._events.to(torch.float64)
+        zero = evf.new_zeros(1)
+        fill_e = st.allowed[:, W:W + Me].any(dim=0).float().mean().double().view(1) if do_e else zero
+        fill_s = st.allowed[:, W + Me:].any(dim=0).float().mean().double().view(1) if do_s else zero
+        host = torch.cat([evf.sum(dim=0), evf[:, 7].min().view(1), fill_e, fill_s]).tolist()
+        ev = [int(t) for t in host[:_lib.CODA_EVENT_WORDS]]
+        every, fill_e, fill_s = int(host[-3]) == 1, host[-2], host[-1]
+        if do_e:
+            if m is not None:
+                if block:
+                    m["exact_overwrites"] += ev[3]
+                    m["exact_frustrated"] += ev[4]
+                    m["exact_fill_ratio"] = fill_e
+                    m["exact_inserts"] += ev[2]
+                    m["exact_hits"] += ev[1]
+                    if self.write_policy != "none":
+                        m["tokens_gated_out"] += ev[0]
+                else:
+                    if self.write_policy != "none":
+                        m["tokens_gated_out"] += ev[0]
+                    m["exact_hits"] += ev[1]
+                    m["exact_inserts"] += ev[2]
+                    m["exact_overwrites"] += ev[3]
+                    m["exact_fill_ratio"] = fill_e
+            # single token: one step of growth per call however many rows are under pressure
+            self._try_expand(st, ev[4] if block else int(ev[4] > 0), 0)
+        if do_s:
+            frustrated = int(every and ev[8] > 0)
+            self._try_expand(st, 0, frustrated)
+            if m is not None:
+                m["summary_updates"] += ev[5]
+                m["summary_frustrated"] += frustrated
+                if self.summary_overwrite_on_insert:
+                    m["summary_inserts"] += ev[6]
+                m["summary_fill_ratio"] = fill_s
+
     def _cfg(self, B: int, dtype: torch.dtype, st: CoDAGQALandmarkStatePerf2) -> LayerCfg:
         adt = self.rope.inv_freq.dtype
         key = (B, dtype, adt, st.active_exact, st.active_summary)
@@ -248,7 +360,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
     def _ptrs(st: CoDAGQALandmarkStatePerf2) -> StatePtrs:
         return StatePtrs(st.k_buf.data_ptr(), st.v_buf.data_ptr(), st.allowed.data_ptr(), st.g_recent.data_ptr(),
                          st.mem_last_exact.data_ptr() if st.mem_last_exact.numel() else None,
-                         _p(st._exact_v_norm), _p(st._sum_lf_k_norm))
+                         _p(st._exact_v_norm), _p(st._sum_lf_k_norm), _p(getattr(st, "_events", None)))
 
     def _consts(self, device, dtype):
         """(inv_freq fp32, cos(theta), sin(theta) in dtype, eta logits fp32, head-norm weight) cached per parameter version."""
@@ -365,14 +477,16 @@ class CoDAGQALandmarkPerf2(nn.Module):
         With ``rp`` given (CUDA-graph replay: scalars baked at capture time plus a device step counter) the
         host mirrors are left alone; the caller advances them with :meth:`advance_host_scalars`."""
         _, _, _, eta, _ = self._consts(k.device, k.dtype)
-        ptrs = self._ptrs(st)
         host = rp is None
         if host:
+            self._arm_events(st)
             rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
+        ptrs = self._ptrs(st)
         check(lib.coda_b200_step_write(C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0),
                                        v.data_ptr(), v.stride(0), g.data_ptr(), eta.data_ptr(), _stream()),
               "coda_b200_step_write")
         if host:
+            self._account(st, int(st.recent_filled >= self.window), block=False)
             self.advance_host_scalars(st)
 
     def advance_host_scalars(self, st: CoDAGQALandmarkStatePerf2, n: int = 1) -> None:
@@ -443,6 +557,8 @@ class CoDAGQALandmarkPerf2(nn.Module):
         dev, dt = x.device, x.dtype
         q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)
         inv_freq, cos_t, sin_t, eta, nw = self._consts(dev, dt)
+        if host_update:
+            self._arm_events(state)
         ptrs = self._ptrs(state)
         s = _stream()
         out = torch.empty((B, 1, self.num_heads * self.head_dim), device=dev, dtype=dt)
@@ -467,6 +583,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
                 "coda_b200_step_write_raw")
             self.decode_attend_launch(cfg, state, rp, 0, q, lam_logit, out)
         if host_update:
+            self._account(state, int(state.recent_filled >= self.window), block=False)
             self.advance_host_scalars(state)
         return self.o_proj(out)
 
@@ -494,6 +611,9 @@ class CoDAGQALandmarkPerf2(nn.Module):
         """The default ``step`` (write, then attend) with no host-side branching on the state, so that it
         can be captured in a CUDA graph: ring scalars come from ``rp`` (values at capture time plus the device
         step counter ``rp.step_dev``).  Does not touch the Python-side scalars."""
+        if self._tracked(state):
+            raise RuntimeError("a state with metrics or expandable banks needs a host read after every cache write "
+                               "and cannot be replayed from a CUDA graph: use step()")
         B = x.shape[0]
         cfg = self._cfg(B, x.dtype, state)
         if self._tuned_decode(cfg):
@@ -618,6 +738,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
                                                       cand.data_ptr(), tmax, _stream()), "coda_b200_select_candidates")
             scratch = self._route_scratch(cfg, dev)
             _, _, _, eta, _ = self._consts(dev, dt)
+            self._arm_events(state)
             ptrs = self._ptrs(state)
         y_heads = torch.empty((B, L, H * Dh), device=dev, dtype=dt) if return_outputs else None
         tc_ok = (return_outputs and self._tuned_prefill(cfg) and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
@@ -641,6 +762,9 @@ class CoDAGQALandmarkPerf2(nn.Module):
                     gates.data_ptr(), gates.stride(0), seen - fill,
                     cand[:, j].data_ptr(), cand.stride(0), eta.data_ptr(), scratch.data_ptr(), _stream()),
                     "coda_b200_route_block")
+                if state._events is not None:
+                    self._account(state, fill + blk - min(W, fill + blk), block=True)
+                    cfg = self._cfg(B, dt, state)          # the banks may have grown
                 state.recent_filled = min(W, fill + blk)
                 state.recent_idx = 0
                 state.pos = pos0 + t0 + blk

@@ -40,12 +40,15 @@ class CoDAGQALandmarkStatePerf2:
 
     # The single allocation the tensors above are carved from (None for states built field by field).
     _arena: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
+    # int32 (B, 16) routing-event record the cache-write kernels fill when metrics or bank expansion are on
+    _events: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
 
     def __getstate__(self):
         """Pickle / ``torch.save`` support: the arena's planes have different dtypes over one storage,
         which the serialiser refuses, so every tensor is saved as its own copy and the arena is dropped."""
         d = dict(self.__dict__)
         d["_arena"] = None
+        d["_events"] = None
         for k, v in d.items():
             if torch.is_tensor(v):
                 d[k] = v.detach().clone()

@@ -245,9 +245,14 @@ __global__ void __launch_bounds__(64) route_decide_kernel(RouteParams p) {
   for (int m = tid; m < Me; m += NT) { s_last[m] = last[m]; n_last[m] = last[m]; }
   __syncthreads();
 
+  // routing-event record of this call (optional): cleared here, filled by the two deciding threads below
+  int32_t* evw = p.st.events != nullptr ? p.st.events + (long long)b * CODA_EVENT_WORDS : nullptr;
+  if (evw != nullptr && tid < CODA_EVENT_WORDS) evw[tid] = 0;
+  __syncthreads();
   if (tid == 0 && te > 0) {
     // ---- exact bank (memory_banks.py:635-697) ----
     const int Ae = c.active_exact;
+    int n_gated = 0, n_hit = 0, n_ins = 0, n_ow = 0, n_frus = 0;
     bool any_used = false;
     for (int m = 0; m < Me; ++m) {
       const bool used = s_used[m] != 0;
@@ -280,7 +285,10 @@ __global__ void __launch_bounds__(64) route_decide_kernel(RouteParams p) {
       }
       tgt_s[t] = tgt;
       flag_s[t] = flag;
+      n_gated += (c.gated && !keep) ? 1 : 0; n_hit += (hit && keep) ? 1 : 0; n_ins += capped ? 1 : 0;
+      n_ow += ow ? 1 : 0; n_frus += (nk && !capped) ? 1 : 0;
     }
+    if (evw != nullptr) { evw[0] = n_gated; evw[1] = n_hit; evw[2] = n_ins; evw[3] = n_ow; evw[4] = n_frus; }
     // stamps: per slot the largest position among touching candidates replaces the old stamp (:682-697)
     for (int t = 0; t < te; ++t) {
       if (!(flag_s[t] & 2)) continue;
@@ -309,6 +317,16 @@ __global__ void __launch_bounds__(64) route_decide_kernel(RouteParams p) {
     for (int m = 0; m < Ms; ++m) start_s[m + 1] += start_s[m];
     for (int m = 0; m < Ms; ++m) s_cur[m] = start_s[m];
     for (int t = 0; t < ts; ++t) ord_s[s_cur[s_idx[t]]++] = t;            // stable grouping by slot
+    if (evw != nullptr) {
+      const int As = c.active_summary;
+      int n_upd = 0, n_new = 0; bool all_used = true, incoming = false;
+      for (int m = 0; m < Ms; ++m) {
+        const bool got = cnt_s[m] > 0.f, was = s_used[Me + m] != 0;
+        n_upd += got ? 1 : 0; n_new += (got && !was) ? 1 : 0;
+        if (m < As) { all_used = all_used && (was || got); incoming = incoming || got; }
+      }
+      evw[5] = n_upd; evw[6] = n_new; evw[7] = all_used ? 1 : 0; evw[8] = incoming ? 1 : 0;
+    }
   }
   __syncthreads();
   for (int t = tid; t < te; t += NT) { pl.e_tgt[t] = tgt_s[t]; pl.e_flag[t] = flag_s[t]; }

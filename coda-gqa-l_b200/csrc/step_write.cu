@@ -81,6 +81,9 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
     return rope_elem<T>(kn + h * Dh, d, Dh, c.rope_interleaved, cs, sn);
   };
 
+  // routing-event record of this call (optional): cleared here, filled by the deciding thread
+  int32_t* evw = p.st.events != nullptr ? p.st.events + (long long)b * CODA_EVENT_WORDS : nullptr;
+  if (evw != nullptr && tid < CODA_EVENT_WORDS) evw[tid] = 0;
   if (r.filled < W) {                                   // memory_banks.py:195-201
     const int slot = r.filled;
     for (int e = tid; e < HD; e += NT) {
@@ -176,6 +179,13 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
       const bool ow = (novel || (c.refresh_on_hit && hit)) && keep;
       if (keep) last[idx] = pos_e;                       // memory_banks.py:325-331
       s_idx = idx; s_flag = ow ? 1 : 0;
+      if (evw != nullptr) {
+        evw[0] = (c.gated && !keep) ? 1 : 0;
+        evw[1] = hit ? 1 : 0;
+        evw[2] = (novel && keep) ? 1 : 0;
+        evw[3] = ow ? 1 : 0;
+        evw[4] = (novel && keep && free_i < 0) ? 1 : 0;
+      }
     }
     __syncthreads();
     if (s_flag) {
@@ -219,6 +229,14 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
       s_idx = bi; s_flag = (c.overwrite_on_insert && is_new) ? 1 : 0;
       s_eta_keep = keep ? 1.f : 0.f;
       if (keep) al[W + Me + bi] = 1;
+      if (evw != nullptr) {
+        bool all_used = true;                              // every active slot in use after this write?
+        for (int m = 0; m < As; ++m) all_used = all_used && (s_used[Me + m] != 0 || (m == bi && keep));
+        evw[5] = keep ? 1 : 0;
+        evw[6] = (is_new && keep) ? 1 : 0;
+        evw[7] = all_used ? 1 : 0;
+        evw[8] = keep ? 1 : 0;
+      }
     }
     __syncthreads();
     const int slot = W + Me + s_idx;
@@ -304,6 +322,10 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   // Distributed shared memory of a CTA may be written only once that CTA runs: every CTA announces itself
   // here and waits for the others just before its first remote store (or before it leaves).
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+
+  // routing-event record of this call (optional): cleared here, filled by the deciding lanes of head 0
+  int32_t* evw = (p.st.events != nullptr && h == 0) ? p.st.events + (long long)b * CODA_EVENT_WORDS : nullptr;
+  if (evw != nullptr && tid < CODA_EVENT_WORDS) evw[tid] = 0;
 
   // ---- requests that depend on nothing but (b, h): issued first, consumed later ----
   // bank rows: item it -> (row it/2, half it%2); exact rows first, then summary rows
@@ -587,17 +609,35 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
       if (keep && h == 0) ((long long*)p.st.mem_last_exact)[(long long)b * Me + idx] = pos_e;   // memory_banks.py:325-331
       if (ow && h == 0) al[W + idx] = 1;
       s_eidx = idx; s_eflag = ow ? 1 : 0;
+      if (evw != nullptr) {
+        evw[0] = (c.gated && !keep) ? 1 : 0;
+        evw[1] = hit ? 1 : 0;
+        evw[2] = (novel && keep) ? 1 : 0;
+        evw[3] = ow ? 1 : 0;
+        evw[4] = (novel && keep && free_i == 0x7fffffff) ? 1 : 0;
+      }
     }
   }
   if (warp == 1 && Ms > 0) {                              // memory_banks.py:343-432
     float best; int bi;
     arg_best(sc + Me, Ms, best, bi);
+    const bool keep_s = c.gated ? (g_e >= c.tau_gate_summary) : true;
+    bool all_used = true;                                  // every active slot in use after this write?
+    #pragma unroll 1
+    for (int m = lane; m < As; m += 32) all_used = all_used && (s_used[Me + m] != 0 || (m == bi && keep_s));
+    all_used = __all_sync(0xffffffffu, all_used);
     if (lane == 0) {
       const bool is_new = s_used[Me + bi] == 0;
-      const bool keep = c.gated ? (g_e >= c.tau_gate_summary) : true;
+      const bool keep = keep_s;
       s_sidx = bi; s_sflag = (c.overwrite_on_insert && is_new) ? 1 : 0;
       s_keep = keep ? 1.f : 0.f;
       if (keep && h == 0) al[W + Me + bi] = 1;
+      if (evw != nullptr) {
+        evw[5] = keep ? 1 : 0;
+        evw[6] = (is_new && keep) ? 1 : 0;
+        evw[7] = all_used ? 1 : 0;
+        evw[8] = keep ? 1 : 0;
+      }
     }
   }
   __syncthreads();

@@ -70,7 +70,18 @@ typedef struct coda_state_ptrs {
   int64_t* mem_last_exact;
   void* exact_v_norm;
   void* sum_lf_k_norm;
+  /* Optional routing-event record, int32 [B][CODA_EVENT_WORDS], or NULL.  Each cache write (step_write*,
+   * route_block*) overwrites the words it owns with what happened to the state IN THAT CALL; the host turns
+   * them into upstream's metrics counters (src/coda_gqa_l/attention.py:319-336) and into the pressure signals
+   * of dynamic bank expansion (attention.py:358-390, memory_banks.py:333-337,416-420,744-760,934-940):
+   *   [0] exact: candidates below the write gate        [1] exact: hits (decode: hit; block: hit and kept)
+   *   [2] exact: inserts (novel, kept, within capacity) [3] exact: overwrites
+   *   [4] exact: novel kept candidates that found no free active slot (decode) / beyond the capacity (block)
+   *   [5] summary: updates (decode: kept; block: slots that received weight)   [6] summary: first fills
+   *   [7] summary: every active slot in use after the call (0/1)              [8] summary: something came in */
+  int32_t* events;
 } coda_state_ptrs;
+#define CODA_EVENT_WORDS 16
 
 /* Ring scalars (state.py:28-36).  They are deterministic functions of the number of tokens
  * written, so the host keeps them as integers.  When step_dev is non-NULL the kernels add the

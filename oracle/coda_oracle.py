@@ -68,6 +68,20 @@ class OracleConfig:
     # ``arange(..., dtype=inv_freq.dtype)`` and their product are then rounded to bf16
     # (primitives.py:51-52).  None = same as the activations.
     angle_dtype: Optional[torch.dtype] = None
+    # dynamic bank expansion (attention.py:116-122,344-390): banks start at min_* active slots and grow towards
+    # num_landmarks_* under pressure; None = fixed size.  collect_metrics: attention.py:319-336.
+    min_landmarks_exact: Optional[int] = None
+    min_landmarks_summary: Optional[int] = None
+    expansion_t_max: int = 1_000_000
+    collect_metrics: bool = False
+
+    @property
+    def Me_min(self) -> int:
+        return self.num_landmarks_exact if self.min_landmarks_exact is None else int(self.min_landmarks_exact)
+
+    @property
+    def Ms_min(self) -> int:
+        return self.num_landmarks_summary if self.min_landmarks_summary is None else int(self.min_landmarks_summary)
 
     @property
     def head_dim(self) -> int:
@@ -106,6 +120,9 @@ class OracleConfig:
             eps=float(getattr(getattr(m, "head_norm", None), "eps", 1e-6)),
             head_norm_mode=m.head_norm_mode, rope_interleaved=m.rope_interleaved,
             angle_dtype=m.rope.inv_freq.dtype,
+            min_landmarks_exact=getattr(m, "Me_min", None), min_landmarks_summary=getattr(m, "Ms_min", None),
+            expansion_t_max=int(getattr(m, "expansion_t_max", 1_000_000)),
+            collect_metrics=bool(getattr(m, "collect_metrics", False)),
         )
 
 
@@ -128,6 +145,49 @@ class OracleState:
     metrics: Optional[dict] = field(default=None, repr=False)
     # Trace of routing decisions, appended by the bank updates (oracle-only).
     trace: Optional[list] = field(default=None, repr=False)
+
+
+METRIC_KEYS = ("exact_hits", "exact_inserts", "exact_overwrites", "exact_fill_ratio", "summary_updates",
+               "summary_inserts", "summary_fill_ratio", "tokens_gated_out", "total_evictions", "exact_frustrated",
+               "summary_frustrated", "active_exact", "active_summary", "expansions_exact", "expansions_summary")
+
+
+def new_metrics(active_exact: int, active_summary: int) -> dict:
+    """The counters dict of attention.py:319-336."""
+    m = {k: 0 for k in METRIC_KEYS}
+    m["exact_fill_ratio"] = 0.0
+    m["summary_fill_ratio"] = 0.0
+    m["active_exact"], m["active_summary"] = active_exact, active_summary
+    return m
+
+
+def log_ceiling(cfg, tokens_seen: int):
+    """Largest active bank sizes allowed after ``tokens_seen`` tokens (attention.py:344-356)."""
+    Me, Ms = cfg.num_landmarks_exact, cfg.num_landmarks_summary
+    if cfg.expansion_t_max <= 0:
+        return Me, Ms
+    ratio = min(math.log(1 + tokens_seen) / math.log(1 + cfg.expansion_t_max), 1.0)
+    return cfg.Me_min + int((Me - cfg.Me_min) * ratio), cfg.Ms_min + int((Ms - cfg.Ms_min) * ratio)
+
+
+def try_expand(cfg, st, frustrated_exact: int, frustrated_summary: int) -> None:
+    """Grow the active capacities under pressure, up to the logarithmic ceiling (attention.py:358-390)."""
+    if cfg.Me_min == cfg.num_landmarks_exact and cfg.Ms_min == cfg.num_landmarks_summary:
+        return
+    if frustrated_exact <= 0 and frustrated_summary <= 0:
+        return
+    ceil_e, ceil_s = log_ceiling(cfg, st.pos)
+    grow_e = grow_s = 0
+    if frustrated_exact > 0 and st.active_exact < ceil_e:
+        grow_e = min(frustrated_exact, ceil_e - st.active_exact)
+        st.active_exact += grow_e
+    if frustrated_summary > 0 and st.active_summary < ceil_s:
+        grow_s = min(frustrated_summary, ceil_s - st.active_summary)
+        st.active_summary += grow_s
+    if st.metrics is not None:
+        st.metrics["active_exact"], st.metrics["active_summary"] = st.active_exact, st.active_summary
+        st.metrics["expansions_exact"] += grow_e
+        st.metrics["expansions_summary"] += grow_s
 
 
 def _unit(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
@@ -161,8 +221,10 @@ def init_state(cfg: OracleConfig, batch_size: int, dtype: torch.dtype,
         g_recent=torch.zeros(B, W, dtype=torch.float32),
         recent_idx=0, recent_filled=0,
         mem_last_exact=torch.zeros(B, Me, dtype=torch.int64),
-        pos=0, active_exact=Me, active_summary=Ms,
+        pos=0, active_exact=cfg.Me_min if Me > 0 else 0, active_summary=cfg.Ms_min if Ms > 0 else 0,
     )
+    if cfg.collect_metrics:
+        st.metrics = new_metrics(st.active_exact, st.active_summary)
     if Me > 0:
         st._exact_v_norm = _unit(v[:, :, W:W + Me, :]).clone()
     if Ms > 0:
@@ -314,6 +376,17 @@ def _exact_one(cfg, st: OracleState, k_e, v_e, pos_e: int, gate):
     cur = st.mem_last_exact.gather(1, target.view(B, 1)).squeeze(1)
     st.mem_last_exact.scatter_(1, target.view(B, 1),
                                torch.where(keep, torch.full_like(cur, pos_e), cur).view(B, 1))
+    if st.metrics is not None:                               # memory_banks.py:315-323
+        m = st.metrics
+        if cfg.write_policy != "none":
+            m["tokens_gated_out"] += int((~keep).sum())
+        m["exact_hits"] += int(hit.sum())
+        m["exact_inserts"] += int((novel & keep).sum())
+        m["exact_overwrites"] += int(ow.sum())
+        m["exact_fill_ratio"] = float(st.allowed[:, sl].any(dim=0).float().mean())
+    # pressure: a novel, kept token that had to evict because no active slot was free (:333-337);
+    # one step of growth per call whatever the number of rows under pressure
+    try_expand(cfg, st, int(bool((novel & keep & ~free.any(dim=-1)).any())), 0)
     if st.trace is not None:
         st.trace.append(("exact_one", pos_e, target.clone(), ow.clone()))
 
@@ -352,8 +425,19 @@ def _summary_one(cfg, wts, st: OracleState, k_e, v_e, gate):
     mv = mv + eta * w4 * (v_e.unsqueeze(2) - mv)
     st.k_buf[:, :, sl, :] = mk
     st.v_buf[:, :, sl, :] = mv
-    st.allowed[:, sl] = used | (keep.view(B, 1) & w.to(torch.bool))
+    used_after = used | (keep.view(B, 1) & w.to(torch.bool))
+    st.allowed[:, sl] = used_after
     st._sum_lf_k_norm = _unit(mk[..., lf:])
+    # pressure: every active slot of every row is in use and something came in (:416-420)
+    frustrated = int(bool(used_after[:, :As].all()) and bool(keep.any()))
+    try_expand(cfg, st, 0, frustrated)
+    if st.metrics is not None:                               # memory_banks.py:423-432
+        m = st.metrics
+        m["summary_updates"] += int(keep.sum())
+        m["summary_frustrated"] += frustrated
+        if cfg.summary_overwrite_on_insert:
+            m["summary_inserts"] += int((fresh & keep).sum())
+        m["summary_fill_ratio"] = float(used_after.any(dim=0).float().mean())
     if st.trace is not None:
         st.trace.append(("summary_one", target.clone(), keep.clone()))
 
@@ -373,6 +457,8 @@ def write_one(cfg, wts, st: OracleState, k_new, v_new, g_new):
         k_e = st.k_buf[:, :, ev, :].clone()
         v_e = st.v_buf[:, :, ev, :].clone()
         g_e = st.g_recent[:, ev].clone()
+        if st.metrics is not None:
+            st.metrics["total_evictions"] += 1
         _exact_one(cfg, st, k_e, v_e, st.pos - W, g_e)
         _summary_one(cfg, wts, st, k_e, v_e, g_e)
         st.k_buf[:, :, ev, :] = k_new[:, :, 0, :]
@@ -464,6 +550,18 @@ def _exact_block(cfg, st: OracleState, k_c, v_c, pos_c, g_c, vhat):
     st.allowed[:, sl] = used | wrote
     cols = wrote.any(dim=0).nonzero(as_tuple=True)[0]
     st._exact_v_norm[:, :, cols, :] = _unit(mv[:, :, cols, :])
+    # pressure: novel, kept candidates beyond the active capacity (memory_banks.py:758-760)
+    frustrated = int((novel_keep & ~capped).sum())
+    try_expand(cfg, st, frustrated, 0)
+    if st.metrics is not None:                               # memory_banks.py:763-774 (PyTorch branch)
+        m = st.metrics
+        m["exact_overwrites"] += int(ow.sum())
+        m["exact_frustrated"] += frustrated
+        m["exact_fill_ratio"] = float(st.allowed[:, sl].any(dim=0).float().mean())
+        m["exact_inserts"] += int(capped.sum())
+        m["exact_hits"] += int((hit & keep).sum())
+        if cfg.write_policy != "none":
+            m["tokens_gated_out"] += int((~keep).sum())
     if st.trace is not None:
         st.trace.append(("exact_block", pos_c.clone(), target.clone(), ow.clone(), touch.clone()))
 
@@ -503,10 +601,22 @@ def _summary_block(cfg, wts, st: OracleState, k_c, v_c, w_c, khat):
     mv = torch.where(got, mv + eta_eff * (av - mv), mv)
     st.k_buf[:, :, sl, :] = mk
     st.v_buf[:, :, sl, :] = mv
-    st.allowed[:, sl] = used | (cnt > 0)
+    used_after = used | (cnt > 0)
+    n_fresh = int(((~used) & (cnt > 0)).sum())              # before `used` (a view of allowed) is overwritten
+    st.allowed[:, sl] = used_after
     cols = (cnt > 0).any(dim=0).nonzero(as_tuple=True)[0]
     if cols.numel() > 0:
         st._sum_lf_k_norm[:, :, cols, :] = _unit(mk[:, :, cols, lf:])
+    # pressure: all active slots of all rows in use and candidates arriving (memory_banks.py:934-940)
+    frustrated = int(bool(used_after[:, :As].all()) and bool((cnt[:, :As] > 0).any()))
+    try_expand(cfg, st, 0, frustrated)
+    if st.metrics is not None:                               # memory_banks.py:943-950
+        m = st.metrics
+        m["summary_updates"] += int((cnt > 0).sum())
+        m["summary_frustrated"] += frustrated
+        if cfg.summary_overwrite_on_insert:
+            m["summary_inserts"] += n_fresh
+        m["summary_fill_ratio"] = float(used_after.any(dim=0).float().mean())
     if st.trace is not None:
         st.trace.append(("summary_block", target.clone(), w.clone()))
 
@@ -533,6 +643,8 @@ def write_block(cfg, wts, st: OracleState, k_blk, v_blk, g_blk, pos0: int):
     n_ev, n_keep = eviction_plan(W, n, blk)
     first_pos = pos0 - n
     if n_ev > 0:
+        if st.metrics is not None:
+            st.metrics["total_evictions"] += n_ev               # memory_banks.py:468-469
         g_e = g_cat[:, :n_ev]
         do_e = Me > 0 and cfg.exact_candidates_per_block > 0
         do_s = Ms > 0 and cfg.summary_candidates_per_block > 0

@@ -58,6 +58,7 @@ def _to_oracle_state(ref_state) -> orc.OracleState:
         active_exact=ref_state.active_exact, active_summary=ref_state.active_summary,
         _exact_v_norm=None if ref_state._exact_v_norm is None else ref_state._exact_v_norm.clone(),
         _sum_lf_k_norm=None if ref_state._sum_lf_k_norm is None else ref_state._sum_lf_k_norm.clone(),
+        metrics=None if getattr(ref_state, "metrics", None) is None else dict(ref_state.metrics),
         trace=[],
     )
 
@@ -74,6 +75,8 @@ def _snapshot(st):
         "recent_filled": int(st.recent_filled), "pos": int(st.pos),
         "k_abs_sum": float(st.k_buf.double().abs().sum()), "v_abs_sum": float(st.v_buf.double().abs().sum()),
         "k_bank": st.k_buf[:, :, -8:, :].clone(), "v_bank": st.v_buf[:, :, -8:, :].clone(),
+        "active_exact": int(st.active_exact), "active_summary": int(st.active_summary),
+        "metrics": None if getattr(st, "metrics", None) is None else dict(st.metrics),
     }
 
 
@@ -124,6 +127,13 @@ def run_scenario(name, sc, RefCls, out_dir):
                 assert torch.equal(ost.allowed, rst.allowed), f"{name}: allowed differs after {phase}"
                 assert torch.equal(ost.mem_last_exact, rst.mem_last_exact), f"{name}: LRU stamps differ after {phase}"
             assert (ost.recent_idx, ost.recent_filled, ost.pos) == (rst.recent_idx, rst.recent_filled, rst.pos)
+            assert (ost.active_exact, ost.active_summary) == (rst.active_exact, rst.active_summary), \
+                f"{name}: active bank sizes differ after {phase}"
+            if rst.metrics is not None:
+                for key, val in rst.metrics.items():
+                    ov = ost.metrics[key]
+                    assert (abs(ov - val) < 1e-6) if isinstance(val, float) else (ov == val), \
+                        f"{name}: metric {key} differs after {phase}: oracle {ov} upstream {val}"
             assert _rel(ost.k_buf, rst.k_buf) < tol and _rel(ost.v_buf, rst.v_buf) < tol, f"{name}: K/V differ"
             ys_ref.append(y_r)
             ys_orc.append(y_o)

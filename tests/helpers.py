@@ -45,7 +45,8 @@ def oracle_state_from(st) -> orc.OracleState:
         k_buf=c(st.k_buf), v_buf=c(st.v_buf), allowed=c(st.allowed), g_recent=c(st.g_recent),
         recent_idx=int(st.recent_idx), recent_filled=int(st.recent_filled), mem_last_exact=c(st.mem_last_exact),
         pos=int(st.pos), active_exact=int(st.active_exact), active_summary=int(st.active_summary),
-        _exact_v_norm=c(st._exact_v_norm), _sum_lf_k_norm=c(st._sum_lf_k_norm), trace=[])
+        _exact_v_norm=c(st._exact_v_norm), _sum_lf_k_norm=c(st._sum_lf_k_norm),
+        metrics=None if getattr(st, "metrics", None) is None else dict(st.metrics), trace=[])
 
 
 def load_golden(name):

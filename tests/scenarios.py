@@ -52,6 +52,31 @@ SCENARIOS = {
         inputs=dict(kind="mixture", centroids=32, sigma=0.5, seed=21, L=256, Ldec=70),
         phases=[("prefill", 0, 256, 64), ("decode", 0, 70)],
     ),
+    # dynamic bank expansion + metrics: banks start at 4 active slots and grow under pressure (white noise:
+    # every evicted token is novel); counters collected
+    "expand_metrics": dict(
+        model=dict(_SMALL, min_landmarks_exact=4, min_landmarks_summary=4, expansion_t_max=2000,
+                   collect_metrics=True),
+        model_seed=42, state_seed=99, B=2,
+        inputs=dict(kind="randn", seed=7, L=160, Ldec=100),
+        phases=[("prefill", 0, 160, 32), ("decode", 0, 100)],
+    ),
+    # metrics on fixed-size banks, clustered inputs (hits, gated-out tokens, summary inserts)
+    "metrics_only": dict(
+        model=dict(_SMALL, collect_metrics=True), model_seed=5, state_seed=11, B=2, random_gate=True,
+        inputs=dict(kind="mixture", centroids=24, sigma=0.3, seed=3, L=200, Ldec=60),
+        phases=[("prefill", 0, 200, 48), ("decode", 0, 60)],
+    ),
+    # the same on a Dh=64 layer (the per-head cluster cache-write kernel) with a trained-like gate: some evicted
+    # tokens are gated out, banks start at 2 / 3 active slots, three states
+    "expand_dh64": dict(
+        model=dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=12,
+                   num_landmarks_summary=10, min_landmarks_exact=2, min_landmarks_summary=3, expansion_t_max=400,
+                   collect_metrics=True),
+        model_seed=6, state_seed=12, B=3, random_gate=True,
+        inputs=dict(kind="mixture", centroids=48, sigma=0.6, seed=13, L=96, Ldec=120),
+        phases=[("prefill", 0, 96, 40), ("decode", 0, 120)],
+    ),
     # block larger than the window (adapter default block 1024): evicted tokens come from the block itself
     "big_block": dict(
         model=dict(_SMALL), model_seed=42, state_seed=99, B=2,

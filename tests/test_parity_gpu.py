@@ -12,6 +12,19 @@ from tests.helpers import (SCENARIOS, TOL_BF16, TOL_F32, build_inputs, build_mod
 pytestmark = pytest.mark.gpu
 
 
+def _same_metrics(got, want, tag):
+    """Counters are integers and must agree exactly; the two fill ratios are fp32 means."""
+    assert (got is None) == (want is None), f"{tag}: one side carries no metrics"
+    if want is None:
+        return
+    assert set(got) == set(want), tag
+    for key, val in want.items():
+        if isinstance(val, float):
+            assert abs(got[key] - val) < 1e-6, f"{tag}: {key} {got[key]} != {val}"
+        else:
+            assert got[key] == val, f"{tag}: {key} {got[key]} != {val}"
+
+
 def _run(name, check_golden=True):
     from coda_gqa_l_b200 import state_from_fields
     sc = SCENARIOS[name]
@@ -49,6 +62,9 @@ def _run(name, check_golden=True):
             assert torch.equal(st.allowed.cpu(), ost.allowed), f"{tag}: slot occupancy differs"
             assert torch.equal(st.mem_last_exact.cpu(), ost.mem_last_exact), f"{tag}: LRU stamps differ"
             assert torch.equal(st.g_recent.cpu(), ost.g_recent) or rel_err(st.g_recent, ost.g_recent) < 1e-6, tag
+        assert (st.active_exact, st.active_summary) == (ost.active_exact, ost.active_summary), f"{tag}: bank growth"
+        if f32:
+            _same_metrics(st.metrics, ost.metrics, f"{tag} vs oracle")
         e = rel_err(y, y_o)
         assert e < tol, f"{tag}: output rel err {e:.3e} vs oracle"
         if f32:
@@ -65,6 +81,9 @@ def _run(name, check_golden=True):
             if f32:
                 assert torch.equal(st.allowed.cpu(), snap["allowed"]), f"{tag}: occupancy vs fixture"
                 assert torch.equal(st.mem_last_exact.cpu(), snap["mem_last_exact"]), f"{tag}: stamps vs fixture"
+                if "active_exact" in snap:
+                    assert (st.active_exact, st.active_summary) == (snap["active_exact"], snap["active_summary"]), tag
+                    _same_metrics(st.metrics, snap["metrics"], f"{tag} vs fixture")
     return mod, st, ost
 
 
@@ -188,6 +207,8 @@ def test_rejects_cpu_tensors_and_training_mode():
     dict(embed_dim=576, num_heads=9, num_kv_heads=3, window=128, num_landmarks_exact=32, num_landmarks_summary=32,
          head_norm_mode="identity", rope_interleaved=False),                                                         # config-2 shape
     dict(embed_dim=1024, num_heads=8, num_kv_heads=1, window=70, num_landmarks_exact=16, num_landmarks_summary=10),   # Dh 128, G 8 (two query n-tiles)
+    dict(embed_dim=512, num_heads=8, num_kv_heads=2, window=40, num_landmarks_exact=24, num_landmarks_summary=16,
+         min_landmarks_exact=3, min_landmarks_summary=2, expansion_t_max=300, collect_metrics=True),                  # growing banks, counters
 ])
 def test_tuned_decode_kernel_matches_generic_kernels(shape):
     """The TMA / tensor-core decode kernel against the shape-generic kernels on identical states (bf16),
@@ -216,6 +237,9 @@ def test_tuned_decode_kernel_matches_generic_kernels(shape):
     # the cache-write kernel is the same code in both modes (raw vs pre-rotated input): state must agree exactly
     assert torch.equal(sa.allowed, sb.allowed) and torch.equal(sa.mem_last_exact, sb.mem_last_exact)
     assert torch.equal(sa.k_buf, sb.k_buf) and torch.equal(sa.v_buf, sb.v_buf)
+    assert (sa.active_exact, sa.active_summary) == (sb.active_exact, sb.active_summary) and sa.metrics == sb.metrics
+    if shape.get("collect_metrics"):
+        assert sa.metrics["total_evictions"] > 0 and sa.active_exact > shape["min_landmarks_exact"]
     e = rel_err(torch.cat(ya, 1), torch.cat(yb, 1))
     assert e < 5e-3, f"tuned vs generic decode attention: rel err {e:.3e}"
 
