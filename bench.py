@@ -162,6 +162,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=512)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replay")
+    ap.add_argument("--no-split-routing", action="store_true",
+                    help="route the evicted tokens inside each layer's chain instead of on a second graph branch")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.layers:
@@ -210,6 +212,7 @@ def main():
         with torch.device(dev):
             layers.append(CoDAGQALandmarkPerf2(**layer_kwargs(w)).eval().to(dtype))
     stack = CoDAStack(layers)
+    stack.split_routing = not args.no_split_routing
     B, D = w["B"], w["D"]
     torch.manual_seed(7 + rank)
     states = stack.init_states(batch_size=B, device=dev, dtype=dtype)
@@ -330,7 +333,7 @@ def main():
                 "ms_per_step": ms_e2e / K},
         # this repository's kernels inside the timed region: per layer the fused cache write and the decode
         # attention, plus the step-counter kernel of the captured graph (the two GEMMs per layer are library calls)
-        "gpu_launches": K * (2 * w["layers"] + (0 if args.eager else 1)),
+        "gpu_launches": K * ((2 if args.eager or args.no_split_routing else 3) * w["layers"] + (0 if args.eager else 1)),
         "clocks": clocks.summary(),
         "roofline": {"kernel": "decode_attend_kernel (coda_b200_decode_attend_prepared)", "timing": "graph of back-to-back launches over all layers' states, CUDA events", "bound": "hbm", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "of": peak_src,

@@ -58,6 +58,9 @@ def _load() -> C.CDLL:
     lib.coda_b200_step_write_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp, fp,
                                                vp, i64, vp, i64, vp, vp, vp, vp]
     lib.coda_b200_step_write_fused_supported.argtypes = [cfgp]
+    lib.coda_b200_step_route.argtypes = [cfgp, stp, RingPos, fp, vp]
+    lib.coda_b200_step_append_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp,
+                                                vp, i64, vp, i64, vp, vp, vp, vp]
     lib.coda_b200_prefill_attend_supported.argtypes = [cfgp]
     lib.coda_b200_prefill_attend.argtypes = [cfgp, stp, i32, i32, i32, vp, i64, i64, vp, i64, i64, fp, i64, i64,
                                              vp, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp, vp]
@@ -86,6 +89,7 @@ def _load() -> C.CDLL:
 EXPORTS = (
     "coda_b200_last_error", "coda_b200_version", "coda_b200_prep", "coda_b200_step_write",
     "coda_b200_step_write_raw", "coda_b200_step_write_fused", "coda_b200_step_write_fused_supported",
+    "coda_b200_step_route", "coda_b200_step_append_fused",
     "coda_b200_decode_attend_supported", "coda_b200_decode_attend", "coda_b200_decode_attend_prepared",
     "coda_b200_decode_record_bytes",
     "coda_b200_prefill_attend_supported", "coda_b200_prefill_attend",

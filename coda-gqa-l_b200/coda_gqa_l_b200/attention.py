@@ -549,10 +549,31 @@ class CoDAGQALandmarkPerf2(nn.Module):
             self._qrec = buf
         return buf
 
-    def _step_fused(self, cfg, x, state, rp: RingPos, host_update: bool) -> torch.Tensor:
+    def _fused_write_ok(self, cfg, q: Optional[torch.Tensor] = None) -> bool:
+        ok = getattr(cfg, "_fused_write", None)
+        if ok is None:
+            ok = bool(lib.coda_b200_step_write_fused_supported(C.byref(cfg)))
+            cfg._fused_write = ok
+        return ok and (q is None or q.data_ptr() % 4 == 0)
+
+    def route_launch(self, x_dtype: torch.dtype, state: CoDAGQALandmarkStatePerf2, rp: RingPos, stream: int) -> bool:
+        """First half of a decode step, on ``stream``: the token the ring is about to evict is routed into the
+        banks.  It depends on the state alone, so it may run beside the projection GEMM of the same step; the
+        second half is ``step_graphable(..., routed=True)`` with the same ``rp``, ordered after it.  Returns
+        False (nothing launched) where the step runs as one launch."""
+        cfg = self._cfg(state.k_buf.shape[0], x_dtype, state)
+        if not (self._tuned_decode(cfg) and self._fused_write_ok(cfg)) or self._tracked(state):
+            return False
+        _, _, _, eta, _ = self._consts(state.k_buf.device, x_dtype)
+        check(lib.coda_b200_step_route(C.byref(cfg), C.byref(self._ptrs(state)), rp, eta.data_ptr(), stream),
+              "coda_b200_step_route")
+        return True
+
+    def _step_fused(self, cfg, x, state, rp: RingPos, host_update: bool, routed: bool = False) -> torch.Tensor:
         """Write-then-attend decode step on the tuned kernels: two launches between the two GEMMs.  The cache
         write applies RoPE / the gate sigmoid and, where it can, also prepares the attention's queries
-        (decode records); the fused attention then only streams the state."""
+        (decode records); the fused attention then only streams the state.  ``routed``: the evicted token
+        has been routed already (:meth:`route_launch`), only the new token is left to write."""
         B = x.shape[0]
         dev, dt = x.device, x.dtype
         q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)
@@ -562,11 +583,20 @@ class CoDAGQALandmarkPerf2(nn.Module):
         ptrs = self._ptrs(state)
         s = _stream()
         out = torch.empty((B, 1, self.num_heads * self.head_dim), device=dev, dtype=dt)
-        fused_ok = getattr(cfg, "_fused_write", None)
-        if fused_ok is None:
-            fused_ok = bool(lib.coda_b200_step_write_fused_supported(C.byref(cfg))) and q.data_ptr() % 4 == 0
-            cfg._fused_write = fused_ok
-        if fused_ok:
+        fused_ok = self._fused_write_ok(cfg, q)
+        if routed:
+            if not fused_ok:
+                raise RuntimeError("routed=True needs the fused cache-write kernel")
+            qrec = self._decode_records(cfg, dev)
+            check(lib.coda_b200_step_append_fused(
+                C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(),
+                q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0), cos_t.data_ptr(), sin_t.data_ptr(),
+                qrec.data_ptr(), s), "coda_b200_step_append_fused")
+            check(lib.coda_b200_decode_attend_prepared(
+                C.byref(cfg), C.byref(ptrs), qrec.data_ptr(), _p(nw), out.data_ptr(), out.stride(0),
+                self._status_word(dev).data_ptr(), s), "coda_b200_decode_attend_prepared")
+        elif fused_ok:
             qrec = self._decode_records(cfg, dev)
             check(lib.coda_b200_step_write_fused(
                 C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
@@ -607,7 +637,8 @@ class CoDAGQALandmarkPerf2(nn.Module):
             C.byref(cfg), C.byref(ptrs), self._decode_records(cfg, out.device).data_ptr(), _p(nw), out.data_ptr(),
             out.stride(0), self._status_word(out.device).data_ptr(), _stream()), "coda_b200_decode_attend_prepared")
 
-    def step_graphable(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos) -> torch.Tensor:
+    def step_graphable(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos,
+                       routed: bool = False) -> torch.Tensor:
         """The default ``step`` (write, then attend) with no host-side branching on the state, so that it
         can be captured in a CUDA graph: ring scalars come from ``rp`` (values at capture time plus the device
         step counter ``rp.step_dev``).  Does not touch the Python-side scalars."""
@@ -617,7 +648,9 @@ class CoDAGQALandmarkPerf2(nn.Module):
         B = x.shape[0]
         cfg = self._cfg(B, x.dtype, state)
         if self._tuned_decode(cfg):
-            return self._step_fused(cfg, x, state, rp, host_update=False)
+            return self._step_fused(cfg, x, state, rp, host_update=False, routed=routed)
+        if routed:
+            raise RuntimeError("routed=True needs the tuned decode kernels")
         q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)
         qn, lam, g = self._prep(cfg, 1, rp.pos, q, k, lam_logit, gate_logit, True, step_dev=rp.step_dev)
         self._write_one(cfg, state, k, v, g, rp=rp)

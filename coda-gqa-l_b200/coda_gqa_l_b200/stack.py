@@ -24,6 +24,9 @@ class CoDAStack(nn.Module):
         super().__init__()
         self.layers = nn.ModuleList(layers)
         self._graph = None
+        # Captured decode step: route every layer's evicted token on a second branch of the graph, beside the
+        # projection GEMMs, instead of inside the layer's own chain (set before the first step_graph).
+        self.split_routing = True
 
     def init_states(self, *, batch_size: int, device, dtype) -> List[CoDAGQALandmarkStatePerf2]:
         return [l.init_state(batch_size=batch_size, device=device, dtype=dtype) for l in self.layers]
@@ -70,10 +73,30 @@ class CoDAStack(nn.Module):
         x_static = example_x.clone()
         rps = [RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), ctr.data_ptr()) for st in states]
         g = torch.cuda.CUDAGraph()
+        branch = torch.cuda.Stream(device=dev)
         with torch.cuda.graph(g):
+            main = torch.cuda.current_stream(dev)
+            # Routing of the tokens this step evicts needs the states only: every layer's goes to a second branch
+            # of the graph at once, and each layer's new token waits for its own layer's routing.
+            routed = []
+            if self.split_routing:
+                branch.wait_stream(main)
+                with torch.cuda.stream(branch):
+                    for layer, st, rp in zip(self.layers, states, rps):
+                        done = None
+                        if layer.route_launch(x_static.dtype, st, rp, branch.cuda_stream):
+                            done = torch.cuda.Event()
+                            done.record(branch)
+                        routed.append(done)
+            else:
+                routed = [None] * len(self.layers)
             h = x_static
-            for layer, st, rp in zip(self.layers, states, rps):
-                h = h + layer.step_graphable(h, st, rp)
+            for layer, st, rp, done in zip(self.layers, states, rps, routed):
+                if done is not None:
+                    main.wait_event(done)
+                h = h + layer.step_graphable(h, st, rp, routed=done is not None)
+            if self.split_routing:
+                main.wait_stream(branch)
             check(lib.coda_b200_advance_steps(ctr.data_ptr(), 1, torch.cuda.current_stream(dev).cuda_stream),
                   "coda_b200_advance_steps")
             out_static = h

@@ -101,10 +101,9 @@ struct RingNow { long long pos; int idx; int filled; };
 
 // Scalars after `n` more single-token writes (memory_banks.py:195-224): the ring fills slot by
 // slot, then the eviction pointer walks round it.
-__device__ __forceinline__ RingNow ring_now(const coda_ring_pos& rp, int W) {
+__device__ __forceinline__ RingNow ring_after(const coda_ring_pos& rp, int W, long long n) {
   RingNow r; r.pos = rp.pos; r.idx = rp.recent_idx; r.filled = rp.recent_filled;
-  if (rp.step_dev != nullptr) {
-    long long n = *rp.step_dev;
+  if (n != 0) {
     long long to_fill = (long long)W - r.filled;
     if (to_fill < 0) to_fill = 0;
     long long nf = n < to_fill ? n : to_fill;
@@ -114,6 +113,10 @@ __device__ __forceinline__ RingNow ring_now(const coda_ring_pos& rp, int W) {
   }
   return r;
 }
+// The device step counter (0 without one): a kernel on a latency chain requests it first of all ...
+__device__ __forceinline__ long long ring_steps(const coda_ring_pos& rp) { return rp.step_dev != nullptr ? *rp.step_dev : 0; }
+// ... and uses it once its other requests are out.
+__device__ __forceinline__ RingNow ring_now(const coda_ring_pos& rp, int W) { return ring_after(rp, W, ring_steps(rp)); }
 
 // ---- host error channel ---------------------------------------------------------------------
 void coda_set_error(const char* fmt, ...);

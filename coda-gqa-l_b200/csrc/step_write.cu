@@ -5,6 +5,10 @@
 #include "bank_score.cuh"
 #include "decode_record.h"
 
+#ifndef CODA_STEP_PREFETCH
+#define CODA_STEP_PREFETCH 1   // fused decode write: ask the head's K/V planes into L2 for the attention that follows
+#endif
+
 struct StepParams {
   coda_layer_cfg c;
   coda_state_ptrs st;
@@ -288,8 +292,15 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
 // computed together, the per-head dot products are exchanged through distributed shared memory (every CTA
 // stores its values into all CTAs of the cluster, one cluster barrier), and each CTA then takes both routing
 // decisions redundantly, warp-parallel, before rewriting its own head's rows.
-template <typename T, int DH>
+//
+// MODE splits the step in two launches: the routing of the evicted token depends on the state alone and can
+// run beside the projection GEMM that produces the new token, off the critical path.
+//   0: everything (route the evicted token, then the new token takes its ring slot; fused mode: + record)
+//   1: routing only: banks, routing caches, LRU stamps, slot flags, event record; the ring is left alone
+//   2: the new token only, after a MODE 1 launch on the same ring position: ring slot, gate, record
+template <typename T, int DH, int MODE>
 __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
+  constexpr bool ROUTE = MODE != 2, APPEND = MODE != 1;
   constexpr int NT = 256, LF = DH / 2, LFD = DH - LF;
   constexpr int EV = (DH / 2) * (int)sizeof(T) / 16;      // 16-byte vectors per thread of an exact-bank half row
   constexpr int SV = (LFD / 2) * (int)sizeof(T) / 16;     // ... of a summary-bank half row
@@ -322,9 +333,13 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   // Distributed shared memory of a CTA may be written only once that CTA runs: every CTA announces itself
   // here and waits for the others just before its first remote store (or before it leaves).
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  // Everything below is a chain of memory round trips, so requests go out as early as their addresses are known
+  // and nothing is converted or otherwise touched before the next batch of requests is out (a warp issues in
+  // order: the first use of a pending load holds up every request behind it).
+  const long long nsteps = ring_steps(p.rp);             // the ring position hangs on it: asked for first
 
   // routing-event record of this call (optional): cleared here, filled by the deciding lanes of head 0
-  int32_t* evw = (p.st.events != nullptr && h == 0) ? p.st.events + (long long)b * CODA_EVENT_WORDS : nullptr;
+  int32_t* evw = (ROUTE && p.st.events != nullptr && h == 0) ? p.st.events + (long long)b * CODA_EVENT_WORDS : nullptr;
   if (evw != nullptr && tid < CODA_EVENT_WORDS) evw[tid] = 0;
 
   // ---- requests that depend on nothing but (b, h): issued first, consumed later ----
@@ -344,41 +359,46 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
       for (int j = 0; j < SV; ++j) seg[j] = src[j];
     }
   };
-  load_seg(tid);
+  if (ROUTE) load_seg(tid);
   // slot flags and LRU stamps: requested into registers now, parked in shared memory once every other request
   // is out (a load -> shared-store loop would cost one memory round trip per loop); Lbuf <= 4 * NT, Me <= NT
   uint8_t alr[4];
 #pragma unroll
   for (int a = 0; a < 4; ++a) { const int m = tid + a * NT; alr[a] = m < Lbuf ? al[m] : (uint8_t)0; }
-  const long long lastr = tid < Me ? ((const long long*)p.st.mem_last_exact)[(long long)b * Me + tid] : 0;
+  const long long lastr = (ROUTE && tid < Me) ? ((const long long*)p.st.mem_last_exact)[(long long)b * Me + tid] : 0;
   // the new token's row (element tid < DH: key, DH <= tid < 2*DH: value)
-  float nk_a = 0.f, nk_b = 0.f, nv_x = 0.f, eta_raw = 0.f, glog = 0.f;
+  T nk_a_raw = T(), nk_b_raw = T(), glog_raw = T();
+  float nv_x = 0.f, eta_raw = 0.f, glog = 0.f;
   const bool is_k = tid < DH, is_v = tid >= DH && tid < 2 * DH;
   const int d = is_k ? tid : tid - DH;
   int ri = 0;                                             // RoPE pair index of key element d
-  if (is_k) {
+  if (APPEND && is_k) {
     if (p.raw) {
       int ia, ib;
       if (c.rope_interleaved) { ri = d >> 1; ia = 2 * ri; ib = ia + 1; }
       else { ri = d < LF ? d : d - LF; ia = ri; ib = ri + LF; }
-      nk_a = El<T>::ld(kn + ia); nk_b = El<T>::ld(kn + ib);
+      nk_a_raw = kn[ia]; nk_b_raw = kn[ib];
     } else {
-      nk_a = El<T>::ld(kn + d);
+      nk_a_raw = kn[d];
     }
   }
   T nv_raw = T();
-  if (is_v) nv_raw = vn[d];
+  if (APPEND && is_v) nv_raw = vn[d];
   (void)nv_x;
-  if (Ms > 0) eta_raw = p.eta_logit[h];
-  if (p.raw) { if (c.gated) glog = El<T>::ld((const T*)p.gate_logit + (long long)b * p.gate_bs); }
-  else glog = p.gate[b];
+  if (ROUTE && Ms > 0) eta_raw = p.eta_logit[h];
+  const float inv_f = (APPEND && p.raw && tid < DH / 2) ? p.inv_freq[tid] : 0.f;
+  if (APPEND) {
+    if (p.raw) { if (c.gated) glog_raw = ((const T*)p.gate_logit)[(long long)b * p.gate_bs]; }
+    else glog = p.gate[b];
+  }
 
   // fused mode: raw query pairs, theta tables and lambda logit (requested now, used last)
   constexpr int QI = (8 * (DH / 2) + NT - 1) / NT;        // (head, pair) items per thread, G <= 8
-  const bool fused = p.qrec != nullptr;
+  const bool fused = APPEND && p.qrec != nullptr;
   const int G = c.H / Hkv;
   uint32_t fq0[QI], fq1[QI]; bf16 fct[QI], fst[QI];
   float flam = 0.f;
+  bf16 flam_raw = __float2bfloat16_rn(0.f);
   if (fused) {
     const bf16* qrow = (const bf16*)p.q_raw + (long long)b * p.q_bs + (long long)h * G * DH;
 #pragma unroll
@@ -399,16 +419,47 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
         fst[it] = ((const bf16*)p.sin_t)[(h * G + g) * (DH / 2) + i];
       }
     }
-    if (tid < G) flam = __bfloat162float(((const bf16*)p.lam_logit)[(long long)b * p.lam_bs + h * G + tid]);
+    if (tid < G) flam_raw = ((const bf16*)p.lam_logit)[(long long)b * p.lam_bs + h * G + tid];
   }
 
-  const RingNow r = ring_now(p.rp, W);
-  float g_new;
-  if (p.raw) {
+  const RingNow r = ring_after(p.rp, W, nsteps);
+  const bool full = r.filled >= W;
+  const int ev = full ? r.idx : r.filled;                 // the ring slot the new token takes
+  T ke_raw = T(), ve_raw = T();
+  float g_e = 0.f;
+  if (ROUTE && full) {                                    // evicted row of this head
+    if (is_k) ke_raw = kb[(long long)ev * DH + d];
+    if (is_v) ve_raw = vb[(long long)ev * DH + d];
+    g_e = gr[ev];
+  }
+#if CODA_STEP_PREFETCH
+  // Fused mode is followed at once by the decode attention, which reads this head's whole K and V planes: the
+  // routing below is a chain of memory round trips that leaves HBM idle, so the planes are asked into L2
+  // meanwhile (a hint: no completion, nothing depends on it).  Issued after this CTA's own latency-critical
+  // requests; the bank slots -- whose rows the routing is about to read -- go first.
+  if (fused) {
+    constexpr unsigned CH = 16384;
+    const unsigned plane_bytes = (unsigned)Lbuf * DH * (unsigned)sizeof(T);      // a multiple of 128
+    const unsigned nch = (plane_bytes + CH - 1) / CH;
+    for (unsigned i = tid; i < 2 * nch; i += NT) {
+      const unsigned cidx = nch - 1 - (i >> 1);                                   // from the end of the plane (banks) backwards
+      const unsigned off = cidx * CH, sz = plane_bytes - off < CH ? plane_bytes - off : CH;
+      const char* base = reinterpret_cast<const char*>((i & 1) ? vb : kb) + off;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(sz) : "memory");
+    }
+  }
+#endif
+  // ---- the first batch of requests is out: from here on values may be used ----
+  const float nk_a = El<T>::ld(&nk_a_raw), nk_b = El<T>::ld(&nk_b_raw);
+  if (p.raw && c.gated) glog = El<T>::ld(&glog_raw);
+  flam = __bfloat162float(flam_raw);
+  float g_new = 0.f;
+  if (!APPEND) {
+  } else if (p.raw) {
     g_new = c.gated ? t_sigmoid<T>(glog) : 1.0f;
     const bool abf = c.angle_dtype == CODA_BF16;
     if (tid < DH / 2) {
-      float ta = (float)r.pos, inv = p.inv_freq[tid];
+      float ta = (float)r.pos, inv = inv_f;
       if (abf) { ta = bf16_round(ta); inv = bf16_round(inv); }
       float ang = __fmul_rn(ta, inv);
       if (abf) ang = bf16_round(ang);
@@ -419,13 +470,9 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
   } else {
     g_new = glog;
   }
-  const bool full = r.filled >= W;
-  const int ev = full ? r.idx : r.filled;                 // the ring slot the new token takes
-  float g_e = 0.f;
-  if (full) {                                             // evicted row of this head
-    if (is_k) ke[d] = El<T>::ld(kb + (long long)ev * DH + d);
-    if (is_v) ve[d] = El<T>::ld(vb + (long long)ev * DH + d);
-    g_e = gr[ev];
+  if (ROUTE && full) {
+    if (is_k) ke[d] = El<T>::ld(&ke_raw);
+    if (is_v) ve[d] = El<T>::ld(&ve_raw);
   }
 #pragma unroll
   for (int a = 0; a < 4; ++a) { const int m = tid + a * NT; if (m < Lbuf) s_al[m] = alr[a]; }
@@ -487,12 +534,14 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     }
   };
 
-  if (!full) {                                            // memory_banks.py:195-201 (uniform over the grid)
+  if (!full || !ROUTE) {                                  // ring still filling (memory_banks.py:195-201; uniform over the grid), or routing done by an earlier launch
     if (fused) write_record(-1, -1);
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
-    if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
-    if (is_v) vb[(long long)ev * DH + d] = nv_raw;
-    if (h == 0 && tid == 0) { gr[ev] = g_new; al[ev] = 1; }
+    if (APPEND) {
+      if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
+      if (is_v) vb[(long long)ev * DH + d] = nv_raw;
+      if (h == 0 && tid == 0) { gr[ev] = g_new; if (!full) al[ev] = 1; }
+    }
     return;
   }
 
@@ -644,11 +693,13 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
 
   // ---- slot updates of this head: the old rows of both banks are requested together ----
   const bool do_e = Me > 0 && s_eflag != 0, do_s = Ms > 0;
-  if (fused) write_record(do_e ? s_eidx : -1, (do_s && s_keep != 0.f) ? s_sidx : -1);
   const long long eoff = (long long)(W + s_eidx) * DH + d, soff = (long long)(W + Me + s_sidx) * DH + d;
-  float eo = 0.f, so = 0.f;
-  if (do_e && (is_k || is_v)) eo = El<T>::ld((is_k ? kb : vb) + eoff);
-  if (do_s && (is_v || (is_k && d >= LF))) so = El<T>::ld((is_k ? kb : vb) + soff);
+  T eo_raw = T(), so_raw = T();
+  if (do_e && (is_k || is_v)) eo_raw = ((is_k ? kb : vb))[eoff];
+  if (do_s && (is_v || (is_k && d >= LF))) so_raw = ((is_k ? kb : vb))[soff];
+  // the record is written while the old rows travel
+  if (fused) write_record(do_e ? s_eidx : -1, (do_s && s_keep != 0.f) ? s_sidx : -1);
+  const float eo = El<T>::ld(&eo_raw), so = El<T>::ld(&so_raw);
   if (do_e) {
     if (is_k) El<T>::st(kb + eoff, t_add<T>(eo, t_sub<T>(ke[d], eo)));       // mem + 1*(x - mem), memory_banks.py:301-302
     if (is_v) { const float nv = t_add<T>(eo, t_sub<T>(ve[d], eo)); El<T>::st(vb + eoff, nv); vhat[d] = nv; }
@@ -687,12 +738,14 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
     for (int i = lane; i < LFD; i += 32) El<T>::st(dst + i, t_div<T>(khat[i], den));
   }
   // ---- the new token takes the evicted slot (memory_banks.py:219-222) ----
-  if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
-  if (is_v) vb[(long long)ev * DH + d] = nv_raw;
-  if (h == 0 && tid == 0) gr[ev] = g_new;
+  if (APPEND) {
+    if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
+    if (is_v) vb[(long long)ev * DH + d] = nv_raw;
+    if (h == 0 && tid == 0) gr[ev] = g_new;
+  }
 }
 
-template <typename T, int DH>
+template <typename T, int DH, int MODE>
 static int launch_step_cluster(const StepParams& p, cudaStream_t s) {
   const coda_layer_cfg& c = p.c;
   const int MM = c.Me + c.Ms;
@@ -706,7 +759,7 @@ static int launch_step_cluster(const StepParams& p, cudaStream_t s) {
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = c.Hkv; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   lc.attrs = at; lc.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&lc, step_write_cluster_kernel<T, DH>, p);
+  cudaError_t e = cudaLaunchKernelEx(&lc, step_write_cluster_kernel<T, DH, MODE>, p);
   if (e != cudaSuccess) { coda_set_error("step_write (cluster): %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
   return CODA_OK;
 }
@@ -715,14 +768,14 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
                            const void* k_new, int64_t k_bs, const void* v_new, int64_t v_bs,
                            const float* gate, const float* eta_logit, int raw, const float* inv_freq,
                            const void* gate_logit, int64_t gate_bs, coda_stream_t stream,
-                           const StepParams* fused = nullptr) {
+                           const StepParams* fused = nullptr, int mode = 0) {
   CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "step_write: invalid layer configuration");
-  CODA_REQUIRE(st->k_buf && st->v_buf && st->allowed && st->g_recent && k_new && v_new, CODA_ERR_ARG,
+  CODA_REQUIRE(st->k_buf && st->v_buf && st->allowed && st->g_recent && (mode == 1 || (k_new && v_new)), CODA_ERR_ARG,
                "step_write: null pointer");
-  CODA_REQUIRE(raw ? (inv_freq && (!cfg->gated || gate_logit)) : (gate != nullptr), CODA_ERR_ARG,
+  CODA_REQUIRE(mode == 1 || (raw ? (inv_freq && (!cfg->gated || gate_logit)) : (gate != nullptr)), CODA_ERR_ARG,
                "step_write: gate / frequency inputs missing");
   CODA_REQUIRE(cfg->Me == 0 || (st->mem_last_exact && st->exact_v_norm), CODA_ERR_ARG, "step_write: exact bank pointers missing");
-  CODA_REQUIRE(cfg->Ms == 0 || (st->sum_lf_k_norm && eta_logit), CODA_ERR_ARG, "step_write: summary bank pointers missing");
+  CODA_REQUIRE(cfg->Ms == 0 || (st->sum_lf_k_norm && (mode == 2 || eta_logit)), CODA_ERR_ARG, "step_write: summary bank pointers missing");
   CODA_REQUIRE(rp.recent_idx >= 0 && rp.recent_idx < cfg->W && rp.recent_filled >= 0 && rp.recent_filled <= cfg->W,
                CODA_ERR_ARG, "step_write: ring scalars out of range");
   StepParams p; p.c = *cfg; p.st = *st; p.rp = rp;
@@ -745,10 +798,12 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
                     ((size_t)cfg->Dh / 4 * es0) % 16 == 0;
     if (ok) {
       p.stage = 0; p.stage_off = 0; p.status = nullptr;
-      if (cfg->dtype == CODA_F32) return cfg->Dh == 128 ? launch_step_cluster<float, 128>(p, s) : launch_step_cluster<float, 64>(p, s);
-      return cfg->Dh == 128 ? launch_step_cluster<bf16, 128>(p, s) : launch_step_cluster<bf16, 64>(p, s);
+      if (mode == 1) return cfg->Dh == 128 ? launch_step_cluster<bf16, 128, 1>(p, s) : launch_step_cluster<bf16, 64, 1>(p, s);
+      if (mode == 2) return cfg->Dh == 128 ? launch_step_cluster<bf16, 128, 2>(p, s) : launch_step_cluster<bf16, 64, 2>(p, s);
+      if (cfg->dtype == CODA_F32) return cfg->Dh == 128 ? launch_step_cluster<float, 128, 0>(p, s) : launch_step_cluster<float, 64, 0>(p, s);
+      return cfg->Dh == 128 ? launch_step_cluster<bf16, 128, 0>(p, s) : launch_step_cluster<bf16, 64, 0>(p, s);
     }
-    CODA_REQUIRE(!fused, CODA_ERR_ARG, "step_write_fused: configuration not covered by the cluster kernel");
+    CODA_REQUIRE(!fused && mode == 0, CODA_ERR_ARG, "step_write_fused: configuration not covered by the cluster kernel");
   }
   const int HD = cfg->Hkv * cfg->Dh, lfd = cfg->Dh - cfg->Dh / 2;
   const int mx = cfg->Me > cfg->Ms ? cfg->Me : cfg->Ms;
@@ -815,4 +870,34 @@ extern "C" int coda_b200_step_write_fused(const coda_layer_cfg* cfg, const coda_
   f.q_raw = q_raw; f.q_bs = q_bs; f.lam_logit = lam_logit; f.lam_bs = lam_bs; f.cos_t = cos_theta; f.sin_t = sin_theta;
   f.qrec = (unsigned char*)qrec;
   return step_write_impl(cfg, st, rp, k_raw, k_bs, v_new, v_bs, nullptr, eta_logit, 1, inv_freq, gate_logit, gate_bs, stream, &f);
+}
+
+// The same step in two launches (configurations of coda_b200_step_write_fused_supported): the routing of the
+// token the ring is about to evict needs nothing of the new token ...
+extern "C" int coda_b200_step_route(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                    const float* eta_logit, coda_stream_t stream) {
+  CODA_REQUIRE(coda_b200_step_write_fused_supported(cfg), CODA_ERR_ARG,
+               "step_route: needs bf16, at most 8 KV heads and 8 query heads per KV head, head_dim 64 or 128");
+  CODA_REQUIRE(st && (cfg->Me == 0 || (uintptr_t)st->exact_v_norm % 16 == 0) && (cfg->Ms == 0 || (uintptr_t)st->sum_lf_k_norm % 16 == 0),
+               CODA_ERR_ARG, "step_route: routing caches must be 16-byte aligned");
+  return step_write_impl(cfg, st, rp, nullptr, 0, nullptr, 0, nullptr, eta_logit, 1, nullptr, nullptr, 0, stream, nullptr, 1);
+}
+
+// ... and the new token then takes the ring slot (and leaves its decode record), with the same `rp`.
+extern "C" int coda_b200_step_append_fused(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                           const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                           const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                           const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                           const void* cos_theta, const void* sin_theta, void* qrec,
+                                           coda_stream_t stream) {
+  CODA_REQUIRE(coda_b200_step_write_fused_supported(cfg), CODA_ERR_ARG,
+               "step_append_fused: needs bf16, at most 8 KV heads and 8 query heads per KV head, head_dim 64 or 128");
+  CODA_REQUIRE(q_raw && lam_logit && cos_theta && sin_theta && qrec && ((uintptr_t)qrec % 16 == 0) && ((uintptr_t)q_raw % 4 == 0) &&
+               (q_bs % 2 == 0), CODA_ERR_ARG, "step_append_fused: query-side pointers missing or misaligned");
+  CODA_REQUIRE(st && (cfg->Me == 0 || (uintptr_t)st->exact_v_norm % 16 == 0) && (cfg->Ms == 0 || (uintptr_t)st->sum_lf_k_norm % 16 == 0),
+               CODA_ERR_ARG, "step_append_fused: routing caches must be 16-byte aligned");
+  StepParams f;
+  f.q_raw = q_raw; f.q_bs = q_bs; f.lam_logit = lam_logit; f.lam_bs = lam_bs; f.cos_t = cos_theta; f.sin_t = sin_theta;
+  f.qrec = (unsigned char*)qrec;
+  return step_write_impl(cfg, st, rp, k_raw, k_bs, v_new, v_bs, nullptr, nullptr, 1, inv_freq, gate_logit, gate_bs, stream, &f, 2);
 }

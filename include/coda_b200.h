@@ -149,6 +149,21 @@ int coda_b200_step_write_fused(const coda_layer_cfg* cfg, const coda_state_ptrs*
                                coda_stream_t stream);
 int coda_b200_step_write_fused_supported(const coda_layer_cfg* cfg);
 
+/* coda_b200_step_write_fused in two launches, for callers that want the routing off their critical path: the
+ * token the ring is about to evict is routed into the banks from the state alone (coda_b200_step_route: may run
+ * beside the projection GEMM that produces the new token, e.g. on another stream), then the new token takes the
+ * ring slot and leaves its decode record (coda_b200_step_append_fused; same rp; must follow the route launch of
+ * the same step).  The pair leaves the state exactly as the single launch does.  Same configurations as
+ * coda_b200_step_write_fused_supported. */
+int coda_b200_step_route(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                         const float* eta_logit, coda_stream_t stream);
+int coda_b200_step_append_fused(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                const void* cos_theta, const void* sin_theta, void* qrec,
+                                coda_stream_t stream);
+
 /* Fused decode attention (bf16, head_dim 64/128, <= 8 query heads per KV head): for every state and KV
  * head the K and V planes are read once (TMA into shared memory) and serve all query heads of the group
  * and both streams; RoPE at position rp.pos (- 1 if token_already_written), the theta rotation, the lambda
