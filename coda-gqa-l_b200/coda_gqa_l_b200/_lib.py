@@ -59,6 +59,11 @@ def _load() -> C.CDLL:
                                                vp, i64, vp, i64, vp, vp, vp, vp]
     lib.coda_b200_step_write_fused_supported.argtypes = [cfgp]
     lib.coda_b200_step_route.argtypes = [cfgp, stp, RingPos, fp, vp]
+    lib.coda_b200_step_route_plan_bytes.argtypes = [i32]
+    lib.coda_b200_step_route_plan_bytes.restype = C.c_int64
+    lib.coda_b200_step_route_plan.argtypes = [cfgp, C.POINTER(StatePtrs), C.POINTER(RingPos), C.POINTER(C.c_void_p),
+                                              i32, vp, vp]
+    lib.coda_b200_step_route_batched.argtypes = [cfgp, vp, i32, vp]
     lib.coda_b200_step_append_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp,
                                                 vp, i64, vp, i64, vp, vp, vp, vp]
     lib.coda_b200_prefill_attend_supported.argtypes = [cfgp]
@@ -89,7 +94,8 @@ def _load() -> C.CDLL:
 EXPORTS = (
     "coda_b200_last_error", "coda_b200_version", "coda_b200_prep", "coda_b200_step_write",
     "coda_b200_step_write_raw", "coda_b200_step_write_fused", "coda_b200_step_write_fused_supported",
-    "coda_b200_step_route", "coda_b200_step_append_fused",
+    "coda_b200_step_route", "coda_b200_step_append_fused", "coda_b200_step_route_plan_bytes",
+    "coda_b200_step_route_plan", "coda_b200_step_route_batched",
     "coda_b200_decode_attend_supported", "coda_b200_decode_attend", "coda_b200_decode_attend_prepared",
     "coda_b200_decode_record_bytes",
     "coda_b200_prefill_attend_supported", "coda_b200_prefill_attend",

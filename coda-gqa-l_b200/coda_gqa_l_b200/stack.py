@@ -14,7 +14,7 @@ from typing import List, Optional
 import torch
 import torch.nn as nn
 
-from ._lib import RingPos, check, lib
+from ._lib import RingPos, StatePtrs, check, lib
 from .attention import CoDAGQALandmarkPerf2
 from .state import CoDAGQALandmarkStatePerf2
 
@@ -24,8 +24,8 @@ class CoDAStack(nn.Module):
         super().__init__()
         self.layers = nn.ModuleList(layers)
         self._graph = None
-        # Captured decode step: route every layer's evicted token on a second branch of the graph, beside the
-        # projection GEMMs, instead of inside the layer's own chain (set before the first step_graph).
+        # Captured decode step: route every layer's evicted token in one launch at the start of the step instead of
+        # inside each layer's own chain (set before the first step_graph).
         self.split_routing = True
 
     def init_states(self, *, batch_size: int, device, dtype) -> List[CoDAGQALandmarkStatePerf2]:
@@ -72,35 +72,47 @@ class CoDAStack(nn.Module):
         ctr = torch.zeros(1, dtype=torch.int64, device=dev)
         x_static = example_x.clone()
         rps = [RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), ctr.data_ptr()) for st in states]
+        plan = self._route_plan(states, rps, x_static.dtype) if self.split_routing else None
         g = torch.cuda.CUDAGraph()
-        branch = torch.cuda.Stream(device=dev)
         with torch.cuda.graph(g):
-            main = torch.cuda.current_stream(dev)
-            # Routing of the tokens this step evicts needs the states only: every layer's goes to a second branch
-            # of the graph at once, and each layer's new token waits for its own layer's routing.
-            routed = []
-            if self.split_routing:
-                branch.wait_stream(main)
-                with torch.cuda.stream(branch):
-                    for layer, st, rp in zip(self.layers, states, rps):
-                        done = None
-                        if layer.route_launch(x_static.dtype, st, rp, branch.cuda_stream):
-                            done = torch.cuda.Event()
-                            done.record(branch)
-                        routed.append(done)
-            else:
-                routed = [None] * len(self.layers)
+            # Routing of the tokens this step evicts needs the states only: all layers' in one launch up front
+            # (one layer's routing is a chain of memory round trips; side by side they are bandwidth-bound), so
+            # that a layer's own chain is projection -> new token's write -> attention -> output projection.
+            if plan is not None:
+                check(lib.coda_b200_step_route_batched(C.byref(plan[0]), plan[1].data_ptr(), len(self.layers),
+                                                       torch.cuda.current_stream(dev).cuda_stream),
+                      "coda_b200_step_route_batched")
             h = x_static
-            for layer, st, rp, done in zip(self.layers, states, rps, routed):
-                if done is not None:
-                    main.wait_event(done)
-                h = h + layer.step_graphable(h, st, rp, routed=done is not None)
-            if self.split_routing:
-                main.wait_stream(branch)
+            for layer, st, rp in zip(self.layers, states, rps):
+                h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h)
             check(lib.coda_b200_advance_steps(ctr.data_ptr(), 1, torch.cuda.current_stream(dev).cuda_stream),
                   "coda_b200_advance_steps")
             out_static = h
-        self._graph = (g, x_static, out_static, ctr, [id(s) for s in states])
+        self._graph = (g, x_static, out_static, ctr, [id(s) for s in states], plan)   # the plan lives as long as the graph
+
+    def _route_plan(self, states, rps, dtype):
+        """Device plan for the batched routing launch, or None where the layers do not share one configuration
+        the fused cache-write kernel covers (then every layer routes inside its own step)."""
+        l0 = self.layers[0]
+        cfg = l0._cfg(states[0].k_buf.shape[0], dtype, states[0])
+        keys = ("B", "H", "Hkv", "Dh", "W", "Me", "Ms", "dtype", "rope_interleaved", "gated", "refresh_on_hit",
+                "overwrite_on_insert", "active_exact", "active_summary", "tau_gate_exact", "tau_gate_summary",
+                "tau_match", "tau_novel", "energy_scale")
+        for layer, st in zip(self.layers, states):
+            c = layer._cfg(st.k_buf.shape[0], dtype, st)
+            if any(getattr(c, k) != getattr(cfg, k) for k in keys) or layer._tracked(st):
+                return None
+            if not (layer._tuned_decode(c) and layer._fused_write_ok(c)):
+                return None
+        n = len(self.layers)
+        dev = states[0].k_buf.device
+        sts = (StatePtrs * n)(*[layer._ptrs(st) for layer, st in zip(self.layers, states)])
+        rpa = (RingPos * n)(*rps)
+        etas = (C.c_void_p * n)(*[layer._consts(dev, dtype)[3].data_ptr() for layer in self.layers])
+        buf = torch.zeros(int(lib.coda_b200_step_route_plan_bytes(n)), dtype=torch.uint8, device=dev)
+        check(lib.coda_b200_step_route_plan(C.byref(cfg), sts, rpa, etas, n, buf.data_ptr(),
+                                            torch.cuda.current_stream(dev).cuda_stream), "coda_b200_step_route_plan")
+        return cfg, buf
 
     @torch.no_grad()
     def step_graph(self, x: torch.Tensor, states) -> torch.Tensor:
@@ -108,7 +120,7 @@ class CoDAStack(nn.Module):
         buffer, which the next replay overwrites."""
         if self._graph is None or self._graph[4] != [id(s) for s in states]:
             self.capture_step(states, x)
-        g, x_static, out_static, _, _ = self._graph
+        g, x_static, out_static = self._graph[:3]
         x_static.copy_(x, non_blocking=True)
         g.replay()
         for layer, st in zip(self.layers, states):

@@ -1,5 +1,7 @@
 // Decode-step cache write: ring FIFO + routing of the evicted token into the exact and summary banks.
 // One CTA per state.  Reads the two unit-norm routing caches once, rewrites at most one slot per bank.
+#include <cstring>
+#include <vector>
 #include "coda_common.cuh"
 #include "tma_utils.cuh"
 #include "bank_score.cuh"
@@ -299,7 +301,7 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
 //   1: routing only: banks, routing caches, LRU stamps, slot flags, event record; the ring is left alone
 //   2: the new token only, after a MODE 1 launch on the same ring position: ring slot, gate, record
 template <typename T, int DH, int MODE>
-__global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
+__device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   constexpr bool ROUTE = MODE != 2, APPEND = MODE != 1;
   constexpr int NT = 256, LF = DH / 2, LFD = DH - LF;
   constexpr int EV = (DH / 2) * (int)sizeof(T) / 16;      // 16-byte vectors per thread of an exact-bank half row
@@ -746,6 +748,22 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
 }
 
 template <typename T, int DH, int MODE>
+__global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) { step_cluster_body<T, DH, MODE>(p); }
+
+// Routing (MODE 1) of MANY layers' states in one launch: blockIdx.z picks the layer's parameter block from a
+// device array.  The routing of one layer is a latency chain that keeps an SM's resources while it waits; all
+// layers' chains side by side fill the machine and are bounded by memory bandwidth instead.
+template <typename T, int DH>
+__global__ void __launch_bounds__(256, 4) step_route_batched_kernel(const StepParams* __restrict__ layers) {
+  __shared__ StepParams sp;
+  static_assert(sizeof(StepParams) % 4 == 0, "StepParams is copied word by word");
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(layers + blockIdx.z);
+  for (int i = threadIdx.x; i < (int)(sizeof(StepParams) / 4); i += 256) reinterpret_cast<uint32_t*>(&sp)[i] = src[i];
+  __syncthreads();
+  step_cluster_body<T, DH, 1>(sp);
+}
+
+template <typename T, int DH, int MODE>
 static int launch_step_cluster(const StepParams& p, cudaStream_t s) {
   const coda_layer_cfg& c = p.c;
   const int MM = c.Me + c.Ms;
@@ -900,4 +918,64 @@ extern "C" int coda_b200_step_append_fused(const coda_layer_cfg* cfg, const coda
   f.q_raw = q_raw; f.q_bs = q_bs; f.lam_logit = lam_logit; f.lam_bs = lam_bs; f.cos_t = cos_theta; f.sin_t = sin_theta;
   f.qrec = (unsigned char*)qrec;
   return step_write_impl(cfg, st, rp, k_raw, k_bs, v_new, v_bs, nullptr, nullptr, 1, inv_freq, gate_logit, gate_bs, stream, &f, 2);
+}
+
+// ---- routing of several layers' states in one launch -------------------------------------------------------
+// A plan is the device array of per-layer parameter blocks the batched kernel indexes with blockIdx.z.  It is
+// written once (pointers and ring scalars at that moment plus the device step counter, as for a captured
+// step) and then serves every launch / graph replay.
+extern "C" int64_t coda_b200_step_route_plan_bytes(int32_t n_layers) {
+  return n_layers > 0 ? (int64_t)n_layers * (int64_t)sizeof(StepParams) : 0;
+}
+
+extern "C" int coda_b200_step_route_plan(const coda_layer_cfg* cfg, const coda_state_ptrs* sts, const coda_ring_pos* rps,
+                                         const float* const* eta_logits, int32_t n_layers, void* plan_dev,
+                                         coda_stream_t stream) {
+  CODA_REQUIRE(coda_b200_step_write_fused_supported(cfg), CODA_ERR_ARG,
+               "step_route_plan: needs bf16, at most 8 KV heads and 8 query heads per KV head, head_dim 64 or 128");
+  CODA_REQUIRE(sts && rps && eta_logits && plan_dev && n_layers > 0 && n_layers <= 65535, CODA_ERR_ARG,
+               "step_route_plan: null pointer or layer count out of range");
+  std::vector<StepParams> host((size_t)n_layers);
+  for (int i = 0; i < n_layers; ++i) {
+    const coda_state_ptrs& st = sts[i];
+    CODA_REQUIRE(st.k_buf && st.v_buf && st.allowed && st.g_recent, CODA_ERR_ARG, "step_route_plan: null state pointer (layer %d)", i);
+    CODA_REQUIRE(cfg->Me == 0 || (st.mem_last_exact && st.exact_v_norm && (uintptr_t)st.exact_v_norm % 16 == 0), CODA_ERR_ARG,
+                 "step_route_plan: exact bank pointers missing or misaligned (layer %d)", i);
+    CODA_REQUIRE(cfg->Ms == 0 || (st.sum_lf_k_norm && eta_logits[i] && (uintptr_t)st.sum_lf_k_norm % 16 == 0), CODA_ERR_ARG,
+                 "step_route_plan: summary bank pointers missing or misaligned (layer %d)", i);
+    CODA_REQUIRE(rps[i].recent_idx >= 0 && rps[i].recent_idx < cfg->W && rps[i].recent_filled >= 0 && rps[i].recent_filled <= cfg->W,
+                 CODA_ERR_ARG, "step_route_plan: ring scalars out of range (layer %d)", i);
+    StepParams p;
+    memset(&p, 0, sizeof(p));
+    p.c = *cfg; p.st = st; p.rp = rps[i]; p.eta_logit = eta_logits[i]; p.raw = 1;
+    host[(size_t)i] = p;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(plan_dev, host.data(), host.size() * sizeof(StepParams), cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);       // `host` goes away with this call
+  if (e != cudaSuccess) { coda_set_error("step_route_plan: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
+  return CODA_OK;
+}
+
+extern "C" int coda_b200_step_route_batched(const coda_layer_cfg* cfg, const void* plan_dev, int32_t n_layers,
+                                            coda_stream_t stream) {
+  CODA_REQUIRE(coda_b200_step_write_fused_supported(cfg), CODA_ERR_ARG,
+               "step_route_batched: needs bf16, at most 8 KV heads and 8 query heads per KV head, head_dim 64 or 128");
+  CODA_REQUIRE(plan_dev && n_layers > 0 && n_layers <= 65535 && (uintptr_t)plan_dev % 8 == 0, CODA_ERR_ARG,
+               "step_route_batched: plan missing or layer count out of range");
+  const int MM = cfg->Me + cfg->Ms;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(cfg->Hkv, cfg->B, n_layers);
+  lc.blockDim = dim3(256, 1, 1);
+  lc.dynamicSmemBytes = sizeof(float) * ((size_t)cfg->Hkv * MM + MM) + 8 + 8 * (size_t)cfg->Me + (size_t)(cfg->W + MM) + 16;
+  lc.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = cfg->Hkv; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  lc.attrs = at; lc.numAttrs = 1;
+  const StepParams* plan = (const StepParams*)plan_dev;
+  cudaError_t e = cfg->Dh == 128 ? cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 128>, plan)
+                                 : cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 64>, plan);
+  if (e != cudaSuccess) { coda_set_error("step_route_batched: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
+  return CODA_OK;
 }

@@ -157,6 +157,19 @@ int coda_b200_step_write_fused_supported(const coda_layer_cfg* cfg);
  * coda_b200_step_write_fused_supported. */
 int coda_b200_step_route(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
                          const float* eta_logit, coda_stream_t stream);
+/* coda_b200_step_route for n_layers states of the same configuration in ONE launch (a decoder stack routes all
+ * its layers' evicted tokens at the start of a step: one layer's routing is a chain of memory round trips, many
+ * side by side are bound by bandwidth).  sts / rps / eta_logits are HOST arrays of n_layers entries;
+ * coda_b200_step_route_plan copies what the kernel needs to `plan_dev` (device,
+ * coda_b200_step_route_plan_bytes(n_layers) bytes, 8-byte aligned) and returns when the copy is done -- call it
+ * outside stream capture; coda_b200_step_route_batched launches on a plan and may be captured and replayed
+ * (with rp.step_dev set, as for any captured step). */
+int64_t coda_b200_step_route_plan_bytes(int32_t n_layers);
+int coda_b200_step_route_plan(const coda_layer_cfg* cfg, const coda_state_ptrs* sts, const coda_ring_pos* rps,
+                              const float* const* eta_logits, int32_t n_layers, void* plan_dev,
+                              coda_stream_t stream);
+int coda_b200_step_route_batched(const coda_layer_cfg* cfg, const void* plan_dev, int32_t n_layers,
+                                 coda_stream_t stream);
 int coda_b200_step_append_fused(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
                                 const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
                                 const void* gate_logit, int64_t gate_bs, const float* inv_freq,
