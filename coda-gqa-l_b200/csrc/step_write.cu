@@ -747,6 +747,149 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The new token's half of a split decode step (bf16, raw inputs, after the routing of the same ring position):
+// RoPE of the key, ring slot, gate, decode record.  What step_cluster_body<MODE 2> does, without the routing
+// code around it and without a cluster: eight warps work, a ninth does nothing but hand the L2 prefetch of the
+// head's planes to the copy engine (~2 K cycles of issue that would otherwise sit on the kernel's only chain).
+template <int DH>
+__global__ void __launch_bounds__(288) step_append_kernel(StepParams p) {
+  using T = bf16;
+  constexpr int NT = 256, LF = DH / 2, HALF = DH / 2, QSTR = DH + 8;
+  constexpr int QI = (8 * (DH / 2) + NT - 1) / NT;        // (head, pair) items per thread, G <= 8
+  const coda_layer_cfg& c = p.c;
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int W = c.W, Me = c.Me, Ms = c.Ms, Hkv = c.Hkv, Lbuf = W + Me + Ms, G = c.H / Hkv;
+  __shared__ float cs[DH / 2], sn[DH / 2];
+  __shared__ unsigned char s_al[1024];                    // Lbuf <= 1024 (fused-mode limit)
+  T* kb = (T*)p.st.k_buf + ((long long)b * Hkv + h) * Lbuf * DH;
+  T* vb = (T*)p.st.v_buf + ((long long)b * Hkv + h) * Lbuf * DH;
+  const long long nsteps = ring_steps(p.rp);             // the ring position hangs on it: asked for first
+  if (warp == NT / 32) {
+    constexpr unsigned CH = 16384;
+    const unsigned plane_bytes = (unsigned)Lbuf * DH * (unsigned)sizeof(T);      // a multiple of 128
+    const unsigned nch = (plane_bytes + CH - 1) / CH;
+    for (unsigned i = lane; i < 2 * nch; i += 32) {
+      const unsigned cidx = i >> 1, off = cidx * CH, sz = plane_bytes - off < CH ? plane_bytes - off : CH;
+      const char* base = reinterpret_cast<const char*>((i & 1) ? vb : kb) + off;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base), "r"(sz) : "memory");
+    }
+    return;
+  }
+  uint8_t* al = p.st.allowed + (long long)b * Lbuf;
+  float* gr = p.st.g_recent + (long long)b * W;
+  const T* kn = (const T*)p.k_new + (long long)b * p.k_bs + h * DH;
+  const T* vn = (const T*)p.v_new + (long long)b * p.v_bs + h * DH;
+  // ---- every request first (a warp issues in order: the first use of a pending load holds up those behind it) ----
+  uint8_t alr[4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) { const int m = tid + a * NT; alr[a] = m < Lbuf ? al[m] : (uint8_t)0; }
+  const bool is_k = tid < DH, is_v = tid >= DH && tid < 2 * DH;
+  const int d = is_k ? tid : tid - DH;
+  int ri = 0;
+  T nk_a_raw = T(), nk_b_raw = T(), nv_raw = T(), glog_raw = T();
+  if (is_k) {
+    int ia, ib;
+    if (c.rope_interleaved) { ri = d >> 1; ia = 2 * ri; ib = ia + 1; }
+    else { ri = d < LF ? d : d - LF; ia = ri; ib = ri + LF; }
+    nk_a_raw = kn[ia]; nk_b_raw = kn[ib];
+  }
+  if (is_v) nv_raw = vn[d];
+  const float inv_f = tid < DH / 2 ? p.inv_freq[tid] : 0.f;
+  if (c.gated) glog_raw = ((const T*)p.gate_logit)[(long long)b * p.gate_bs];
+  uint32_t fq0[QI], fq1[QI]; bf16 fct[QI], fst[QI];
+  bf16 flam_raw = __float2bfloat16_rn(0.f);
+  {
+    const bf16* qrow = (const bf16*)p.q_raw + (long long)b * p.q_bs + (long long)h * G * DH;
+#pragma unroll
+    for (int it = 0; it < QI; ++it) {
+      const int w = tid + it * NT;
+      fq0[it] = fq1[it] = 0u; fct[it] = fst[it] = __float2bfloat16_rn(0.f);
+      if (w < G * HALF) {
+        const int g = w / HALF, i = w % HALF;
+        const bf16* qh = qrow + g * DH;
+        if (c.rope_interleaved) {
+          fq0[it] = *reinterpret_cast<const uint32_t*>(qh + 2 * i);
+        } else {
+          const int pi = 2 * i < HALF ? 2 * i : 2 * i - HALF;
+          fq0[it] = *reinterpret_cast<const uint32_t*>(qh + pi);
+          fq1[it] = *reinterpret_cast<const uint32_t*>(qh + pi + HALF);
+        }
+        fct[it] = ((const bf16*)p.cos_t)[(h * G + g) * HALF + i];
+        fst[it] = ((const bf16*)p.sin_t)[(h * G + g) * HALF + i];
+      }
+    }
+    if (tid < G) flam_raw = ((const bf16*)p.lam_logit)[(long long)b * p.lam_bs + h * G + tid];
+  }
+  const RingNow r = ring_after(p.rp, W, nsteps);
+  const bool full = r.filled >= W;
+  const int ev = full ? r.idx : r.filled;                 // the ring slot the new token takes
+  // ---- cos / sin of the position, gate ----
+  const bool abf = c.angle_dtype == CODA_BF16;
+  if (tid < DH / 2) {
+    float ta = (float)r.pos, inv = inv_f;
+    if (abf) { ta = bf16_round(ta); inv = bf16_round(inv); }
+    float ang = __fmul_rn(ta, inv);
+    if (abf) ang = bf16_round(ang);
+    float cc, ss; sincos_call(ang, &ss, &cc);
+    if (abf) { cc = bf16_round(cc); ss = bf16_round(ss); }
+    cs[tid] = El<T>::rnd(cc); sn[tid] = El<T>::rnd(ss);
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) { const int m = tid + a * NT; if (m < Lbuf) s_al[m] = alr[a]; }
+  asm volatile("bar.sync 1, 256;" ::: "memory");         // the eight working warps only
+  // ---- key: RoPE (primitives.py:99-113), ring slot ----
+  if (is_k) {
+    const float nk_a = __bfloat162float(nk_a_raw), nk_b = __bfloat162float(nk_b_raw);
+    const float cc = cs[ri], ss = sn[ri];
+    float new_k;
+    if (c.rope_interleaved) new_k = (d & 1) ? t_add<T>(t_mul<T>(nk_a, ss), t_mul<T>(nk_b, cc)) : t_sub<T>(t_mul<T>(nk_a, cc), t_mul<T>(nk_b, ss));
+    else new_k = d < LF ? t_add<T>(t_mul<T>(nk_a, cc), t_mul<T>(-nk_b, ss)) : t_add<T>(t_mul<T>(nk_b, cc), t_mul<T>(nk_a, ss));
+    El<T>::st(kb + (long long)ev * DH + d, new_k);
+  }
+  if (is_v) vb[(long long)ev * DH + d] = nv_raw;
+  if (h == 0 && tid == 0) {
+    gr[ev] = c.gated ? t_sigmoid<T>(__bfloat162float(glog_raw)) : 1.0f;
+    if (!full) al[ev] = 1;
+  }
+  // ---- decode record of this plane: queries, lambda, visibility mask after the write ----
+  unsigned char* rec = p.qrec + ((long long)b * Hkv + h) * DecodeRecord::bytes(G, DH, Lbuf);
+  bf16* q_s = reinterpret_cast<bf16*>(rec);
+#pragma unroll
+  for (int it = 0; it < QI; ++it) {
+    const int w = tid + it * NT;
+    if (w < G * HALF) {
+      const int g = w / HALF, i = w % HALF;
+      const float a0 = __uint_as_float(fq0[it] << 16), a1 = __uint_as_float(fq0[it] & 0xffff0000u);
+      const float b0 = __uint_as_float(fq1[it] << 16), b1 = __uint_as_float(fq1[it] & 0xffff0000u);
+      float e0, e1;
+      if (c.rope_interleaved) {
+        e0 = t_sub<T>(t_mul<T>(a0, cs[i]), t_mul<T>(a1, sn[i]));
+        e1 = t_add<T>(t_mul<T>(a0, sn[i]), t_mul<T>(a1, cs[i]));
+      } else {
+        const bool lo = 2 * i < HALF;
+        const int pi = lo ? 2 * i : 2 * i - HALF;
+        e0 = lo ? t_add<T>(t_mul<T>(a0, cs[pi]), t_mul<T>(-b0, sn[pi])) : t_add<T>(t_mul<T>(b0, cs[pi]), t_mul<T>(a0, sn[pi]));
+        e1 = lo ? t_add<T>(t_mul<T>(a1, cs[pi + 1]), t_mul<T>(-b1, sn[pi + 1])) : t_add<T>(t_mul<T>(b1, cs[pi + 1]), t_mul<T>(a1, sn[pi + 1]));
+      }
+      const float ct = __bfloat162float(fct[it]), st = __bfloat162float(fst[it]);
+      const float n0 = t_sub<T>(t_mul<T>(e0, ct), t_mul<T>(e1, st));
+      const float n1 = t_add<T>(t_mul<T>(e0, st), t_mul<T>(e1, ct));
+      *reinterpret_cast<__nv_bfloat162*>(q_s + g * QSTR + 2 * i) = __floats2bfloat162_rn(e0, e1);
+      *reinterpret_cast<__nv_bfloat162*>(q_s + (G + g) * QSTR + 2 * i) = __floats2bfloat162_rn(n0, n1);
+    }
+  }
+  const int rows = DecodeRecord::qrows(G);
+  #pragma unroll 1
+  for (int w = tid; w < (rows - 2 * G) * HALF; w += NT)   // unused rows of the query tile: zero
+    *reinterpret_cast<uint32_t*>(q_s + (2 * G + w / HALF) * QSTR + 2 * (w % HALF)) = 0u;
+  float* lam = reinterpret_cast<float*>(rec + DecodeRecord::lam_off(G, DH));
+  if (tid < 8) lam[tid] = tid < G ? t_sigmoid<T>(__bfloat162float(flam_raw)) : 0.f;
+  uint8_t* mk = rec + DecodeRecord::mask_off(G, DH);
+  #pragma unroll 1
+  for (int i = tid; i < DecodeRecord::mask_bytes(Lbuf); i += NT) mk[i] = i < Lbuf ? (i == ev ? (uint8_t)1 : s_al[i]) : (uint8_t)0;
+}
+
 template <typename T, int DH, int MODE>
 __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) { step_cluster_body<T, DH, MODE>(p); }
 
@@ -817,7 +960,12 @@ static int step_write_impl(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
     if (ok) {
       p.stage = 0; p.stage_off = 0; p.status = nullptr;
       if (mode == 1) return cfg->Dh == 128 ? launch_step_cluster<bf16, 128, 1>(p, s) : launch_step_cluster<bf16, 64, 1>(p, s);
-      if (mode == 2) return cfg->Dh == 128 ? launch_step_cluster<bf16, 128, 2>(p, s) : launch_step_cluster<bf16, 64, 2>(p, s);
+      if (mode == 2) {
+        if (cfg->Dh == 128) step_append_kernel<128><<<dim3(cfg->Hkv, cfg->B), 288, 0, s>>>(p);
+        else step_append_kernel<64><<<dim3(cfg->Hkv, cfg->B), 288, 0, s>>>(p);
+        CODA_CHECK_LAUNCH("step_append");
+        return CODA_OK;
+      }
       if (cfg->dtype == CODA_F32) return cfg->Dh == 128 ? launch_step_cluster<float, 128, 0>(p, s) : launch_step_cluster<float, 64, 0>(p, s);
       return cfg->Dh == 128 ? launch_step_cluster<bf16, 128, 0>(p, s) : launch_step_cluster<bf16, 64, 0>(p, s);
     }
