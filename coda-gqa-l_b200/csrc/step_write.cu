@@ -304,9 +304,9 @@ template <typename T, int DH, int MODE>
 __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   constexpr bool ROUTE = MODE != 2, APPEND = MODE != 1;
   constexpr int NT = 256, LF = DH / 2, LFD = DH - LF;
-  constexpr int EV = (DH / 2) * (int)sizeof(T) / 16;      // 16-byte vectors per thread of an exact-bank half row
-  constexpr int SV = (LFD / 2) * (int)sizeof(T) / 16;     // ... of a summary-bank half row
-  constexpr int EPV = 16 / (int)sizeof(T);                // elements per vector
+  constexpr int EPV = 16 / (int)sizeof(T);                // elements per 16-byte chunk
+  constexpr int CE = DH / EPV, CS = LFD / EPV;            // chunks per exact / summary routing-cache row (powers of two <= 32)
+  constexpr int PE = 4, PS = 2;                           // chunks per thread requested at kernel entry
   extern __shared__ float sm[];
   const coda_layer_cfg& c = p.c;
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -316,7 +316,7 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   __shared__ float ke[DH], ve[DH], vhat[DH], khat[LFD], cs[DH / 2], sn[DH / 2], s_den[2];
   // unit vectors for the scoring loop: the second half of each starts 4 words further, so that the two halves
   // (read by alternate lanes) fall into different banks
-  __shared__ float hv[DH + 4], hk[LFD + 4];
+  __shared__ __align__(16) float hv[DH + DH / 8], hk[LFD + LFD / 8];   // element e sits at e + 4 * (e / 32)
   __shared__ int s_eidx, s_eflag, s_sidx, s_sflag;
   __shared__ float s_keep;
   float* xdots = sm;                                      // [Hkv][MM] per-head dots of every CTA of the cluster
@@ -345,23 +345,19 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   if (evw != nullptr && tid < CODA_EVENT_WORDS) evw[tid] = 0;
 
   // ---- requests that depend on nothing but (b, h): issued first, consumed later ----
-  // bank rows: item it -> (row it/2, half it%2); exact rows first, then summary rows
+  // Both routing caches of this head are contiguous: thread t takes the 16-byte chunks t, t + NT, ... of each
+  // (coalesced; CE / CS chunks make a row, held by CE / CS neighbouring lanes).  The first PE / PS passes --
+  // 64 rows of each bank at bf16, Dh 128 -- are requested here; larger banks load the rest in the scoring loop.
   const T* vnorm = (const T*)p.st.exact_v_norm + ((long long)b * Hkv + h) * Me * DH;
   const T* knorm = (const T*)p.st.sum_lf_k_norm + ((long long)b * Hkv + h) * Ms * LFD;
-  uint4 seg[EV];
-  auto load_seg = [&](int it) {
-    if (it < 2 * Me) {
-      const uint4* src = reinterpret_cast<const uint4*>(vnorm + (long long)(it >> 1) * DH + (it & 1) * (DH / 2));
+  const uint4* vn4 = reinterpret_cast<const uint4*>(vnorm);
+  const uint4* kn4 = reinterpret_cast<const uint4*>(knorm);
+  const int nce = Me * CE, ncs = Ms * CS;
+  uint4 pe[PE], ps[PS];
 #pragma unroll
-      for (int j = 0; j < EV; ++j) seg[j] = src[j];
-    } else if (it < 2 * MM) {
-      const int m = (it - 2 * Me) >> 1;
-      const uint4* src = reinterpret_cast<const uint4*>(knorm + (long long)m * LFD + (it & 1) * (LFD / 2));
+  for (int j = 0; j < PE; ++j) pe[j] = (ROUTE && tid + j * NT < nce) ? vn4[tid + j * NT] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int j = 0; j < SV; ++j) seg[j] = src[j];
-    }
-  };
-  if (ROUTE) load_seg(tid);
+  for (int j = 0; j < PS; ++j) ps[j] = (ROUTE && tid + j * NT < ncs) ? kn4[tid + j * NT] : make_uint4(0u, 0u, 0u, 0u);
   // slot flags and LRU stamps: requested into registers now, parked in shared memory once every other request
   // is out (a load -> shared-store loop would cost one memory round trip per loop); Lbuf <= 4 * NT, Me <= NT
   uint8_t alr[4];
@@ -558,53 +554,76 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
     if (lane == 0) s_den[warp] = fmaxf(El<T>::rnd(sqrtf(ss)), 1e-6f);
   }
   __syncthreads();
-  if (is_v) hv[d + (d >= DH / 2 ? 4 : 0)] = t_div<T>(ve[d], s_den[0]);
-  if (is_k && d >= LF) hk[(d - LF) + ((d - LF) >= LFD / 2 ? 4 : 0)] = t_div<T>(ke[d], s_den[1]);
+  if (is_v) hv[d + 4 * (d >> 5)] = t_div<T>(ve[d], s_den[0]);
+  if (is_k && d >= LF) hk[(d - LF) + 4 * ((d - LF) >> 5)] = t_div<T>(ke[d], s_den[1]);
   __syncthreads();
 
   asm volatile("barrier.cluster.wait.aligned;" ::: "memory");       // all CTAs of the cluster are running
   // ---- per-head dot products of both banks, sent to every CTA of the cluster ----
-  #pragma unroll 1
-  for (int base = 0; base < 2 * MM; base += NT) {
-    const int it = base + tid;
+  // dot of one chunk with the matching EPV elements of a unit vector (two accumulation chains)
+  auto chunk_dot = [&](const uint4& v, const float* a) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float f[EPV];
+    if (sizeof(T) == 2) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { f[2 * q] = __uint_as_float(w[q] << 16); f[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u); }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) f[q] = __uint_as_float(w[q]);
+    }
     float acc0 = 0.f, acc1 = 0.f;
-    if (it < 2 * MM) {
-      const bool ex = it < 2 * Me;
-      const float* a = ex ? hv + (it & 1) * (DH / 2 + 4) : hk + (it & 1) * (LFD / 2 + 4);
-      const int nv = ex ? EV : SV;
 #pragma unroll
-      for (int j = 0; j < EV; ++j) {
-        if (j < nv) {
-          float f[EPV];
-          const uint32_t w[4] = {seg[j].x, seg[j].y, seg[j].z, seg[j].w};
-          if (sizeof(T) == 2) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) { f[2 * q] = __uint_as_float(w[q] << 16); f[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u); }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) f[q] = __uint_as_float(w[q]);
-          }
-#pragma unroll
-          for (int q = 0; q < EPV; q += 2) {
-            acc0 = fmaf(a[j * EPV + q], f[q], acc0);
-            acc1 = fmaf(a[j * EPV + q + 1], f[q + 1], acc1);
-          }
-        }
-      }
+    for (int q4 = 0; q4 < EPV; q4 += 4) {
+      const float4 av = *reinterpret_cast<const float4*>(a + q4);
+      acc0 = fmaf(av.x, f[q4], acc0); acc1 = fmaf(av.y, f[q4 + 1], acc1);
+      acc0 = fmaf(av.z, f[q4 + 2], acc0); acc1 = fmaf(av.w, f[q4 + 3], acc1);
     }
-    float acc = acc0 + acc1;
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    if (it < 2 * MM && (it & 1) == 0) {
-      const float v = El<T>::rnd(acc);
-      const uint32_t local = tma::smem_u32(xdots + h * MM + (it >> 1));
-      #pragma unroll 1
-      for (int rk = 0; rk < Hkv; ++rk) {
-        uint32_t remote;
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rk));
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-      }
+    return acc0 + acc1;
+  };
+  // the rounded per-head dot of bank slot m goes to every CTA of the cluster
+  auto send = [&](int m, float acc) {
+    const float v = El<T>::rnd(acc);
+    const uint32_t local = tma::smem_u32(xdots + h * MM + m);
+    #pragma unroll 1
+    for (int rk = 0; rk < Hkv; ++rk) {
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rk));
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
     }
-    if (base + NT < 2 * MM) load_seg(base + NT + tid);
+  };
+  {
+    // this thread's chunk position inside a row is the same in every pass (NT is a multiple of CE and CS)
+    const int ce = tid % CE, cs_ = tid % CS;
+    const float* ae = hv + ce * EPV + 4 * ((ce * EPV) >> 5);
+    const float* as = hk + cs_ * EPV + 4 * ((cs_ * EPV) >> 5);
+    auto exact_pass = [&](const uint4& v, int j) {
+      const int ch = tid + j * NT;
+      float acc = ch < nce ? chunk_dot(v, ae) : 0.f;
+#pragma unroll
+      for (int o = CE / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (ch < nce && ce == 0) send(ch / CE, acc);
+    };
+    auto summary_pass = [&](const uint4& v, int j) {
+      const int ch = tid + j * NT;
+      float acc = ch < ncs ? chunk_dot(v, as) : 0.f;
+#pragma unroll
+      for (int o = CS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (ch < ncs && cs_ == 0) send(Me + ch / CS, acc);
+    };
+#pragma unroll
+    for (int j = 0; j < PE; ++j) if (j * NT < nce) exact_pass(pe[j], j);
+    #pragma unroll 1
+    for (int j = PE; j * NT < nce; ++j) {
+      const int ch = tid + j * NT;
+      exact_pass(ch < nce ? vn4[ch] : make_uint4(0u, 0u, 0u, 0u), j);
+    }
+#pragma unroll
+    for (int j = 0; j < PS; ++j) if (j * NT < ncs) summary_pass(ps[j], j);
+    #pragma unroll 1
+    for (int j = PS; j * NT < ncs; ++j) {
+      const int ch = tid + j * NT;
+      summary_pass(ch < ncs ? kn4[ch] : make_uint4(0u, 0u, 0u, 0u), j);
+    }
   }
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 
