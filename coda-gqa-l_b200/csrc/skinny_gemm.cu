@@ -1,0 +1,232 @@
+// Y[M x N] = X[M x K] . W[N x K]^T (+ R), bf16 in / fp32 accumulate / bf16 out, for M <= 32 rows: the decode
+// step's output projection (upstream attention.py:514, `self.o_proj(...)`, with the decoder's residual added
+// in the same pass).  With so few rows the GEMM is a stream of the weight matrix: 2*N*K bytes from HBM once.
+//
+// One thread-block cluster of two CTAs per 64 weight rows; the pair splits K.  Each CTA keeps ITS half of X in
+// shared memory for the whole kernel (TMA, 128-byte swizzle: 32 rows x 64 elements per box) and streams its half
+// of the 64 weight rows through a ring of 64 x 64 boxes.  Tensor-core tiles take the WEIGHT rows as m = 16 and the
+// X rows as n = 8 (Y^T = W . X^T), so that M = 32 fills four n-tiles with no padding.  Eight consumer warps: warp w
+// owns weight rows (w % 4) * 16 .. + 15 and k-steps 2 * (w / 4), + 1 of every box.  At the end the two k-step halves
+// meet in shared memory, the second CTA's sum crosses to the first through distributed shared memory, and the
+// first adds the residual and writes the 32 x 64 output tile with 16-byte stores.
+// Every mbarrier wait is bounded (status word); the cluster barriers are hardware barriers among co-scheduled CTAs.
+#include "coda_common.cuh"
+#include "tma_utils.cuh"
+#include "tensor_maps.h"
+
+namespace {
+
+constexpr int SG_BN = 64;            // weight rows per cluster
+constexpr int SG_BK = 64;            // elements per box row (128 bytes)
+constexpr int SG_MAXM = 32;          // rows of X
+constexpr int SG_STAGES = 11;        // ring of weight boxes (8 KB each)
+constexpr int SG_CWARPS = 8;
+constexpr int SG_THREADS = (SG_CWARPS + 1) * 32;
+constexpr int SG_XGROUP = 4;         // X boxes per arrival barrier
+constexpr int SG_MAXXG = 8;          // (K / 2 / 64) / SG_XGROUP at K = 4096
+constexpr int SG_WBOX = SG_BN * 128; // bytes of a weight box
+constexpr int SG_XBOX = SG_MAXM * 128;
+
+struct SkinnyParams {
+  int M, N, K;
+  const bf16* res; long long res_rs;   // optional residual [M][N]
+  bf16* y; long long y_rs;
+  int* status;
+};
+
+using tma::smem_u32;
+
+__device__ __forceinline__ void sg_tma_load(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(0) : "memory");
+}
+__device__ __forceinline__ void sg_ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sg_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t bf16_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// byte offset of 16-byte chunk c (0..7) of row r inside a box of 128-byte rows written with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sg_off(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+// shared-memory carve-up (after 1024-byte alignment): X half | weight ring | exchange tile | barriers
+struct SkinnySmem {
+  int x, ring, xchg, bars, total;
+  __host__ __device__ explicit SkinnySmem(int khalf) {
+    x = 0;
+    ring = x + (khalf / SG_BK) * SG_XBOX;
+    xchg = ring + SG_STAGES * SG_WBOX;                 // [32][64] fp32 from the other CTA of the pair
+    bars = xchg + SG_MAXM * SG_BN * 4;
+    total = bars + (2 * SG_STAGES + SG_MAXXG) * 8;
+  }
+};
+
+__global__ void __launch_bounds__(SG_THREADS, 1)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, SkinnyParams p) {
+  extern __shared__ unsigned char sg_raw[];
+  unsigned char* smem = sg_raw + ((1024u - (smem_u32(sg_raw) & 1023u)) & 1023u);   // swizzled boxes need 1024-byte alignment
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rank = blockIdx.x;                           // position in the pair = cluster rank (cluster dims (2,1,1))
+  const int n0 = blockIdx.y * SG_BN;
+  const int khalf = p.K / 2, kbase = rank * khalf, nbox = khalf / SG_BK;
+  const SkinnySmem L(khalf);
+  unsigned char* xs = smem + L.x;
+  unsigned char* ring = smem + L.ring;
+  float* xchg = reinterpret_cast<float*>(smem + L.xchg);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* empty = full + SG_STAGES;
+  uint64_t* xbar = empty + SG_STAGES;
+
+  // The other CTA's shared memory may be written only once that CTA runs: announce here, wait before the exchange.
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  if (tid == 0) {
+    for (int i = 0; i < SG_STAGES; ++i) { tma::mbar_init(&full[i], 1); tma::mbar_init(&empty[i], SG_CWARPS); }
+    for (int i = 0; i < SG_MAXXG; ++i) tma::mbar_init(&xbar[i], 1);
+    tma::fence_barrier_init();
+  }
+  __syncthreads();
+
+  float acc[4][4];
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+  const int rb = warp & 3, kp = (warp >> 2) & 1;         // consumer warp: weight rows rb*16.., k-steps 2*kp, 2*kp+1 of a box
+  const int li = lane >> 3, lr = lane & 7;
+
+  if (warp == SG_CWARPS) {
+    // ---------------- producer: this CTA's half of X, then the ring of weight boxes ----------------
+    if (lane == 0) {
+      for (int i = 0; i < nbox; ++i) {
+        // X travels in groups of SG_XGROUP boxes, each just ahead of the weight boxes that need it, so that the
+        // first tiles do not wait for all of X
+        if (i % SG_XGROUP == 0) {
+          const int g = i / SG_XGROUP, nb = min(SG_XGROUP, nbox - i);
+          tma::mbar_expect_tx(&xbar[g], (uint32_t)nb * SG_XBOX);
+          for (int j = 0; j < nb; ++j) sg_tma_load(xs + (i + j) * SG_XBOX, &xmap, &xbar[g], kbase + (i + j) * SG_BK, 0);
+        }
+        const int s = i % SG_STAGES, round = i / SG_STAGES;
+        if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, p.status, 21);
+        tma::mbar_expect_tx(&full[s], SG_WBOX);
+        sg_tma_load(ring + s * SG_WBOX, &wmap, &full[s], kbase + i * SG_BK, n0);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- consumers ----------------
+    const uint32_t xs_u = smem_u32(xs), ring_u = smem_u32(ring);
+    for (int i = 0; i < nbox; ++i) {
+      if (i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 22);   // each X barrier completes once
+      const int s = i % SG_STAGES, round = i / SG_STAGES;
+      tma::mbar_wait(&full[s], round & 1, p.status, 23);
+      const uint32_t wb = ring_u + s * SG_WBOX, xb = xs_u + i * SG_XBOX;
+      uint32_t a0[4], a1[4];                               // weight fragments of the two k-steps
+      const int wrow = rb * 16 + (li & 1) * 8 + lr;
+      sg_ldsm_x4(a0, wb + sg_off(wrow, (2 * kp) * 2 + (li >> 1)));
+      sg_ldsm_x4(a1, wb + sg_off(wrow, (2 * kp + 1) * 2 + (li >> 1)));
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t bx[4];                                    // X^T fragments: {k 0-7, k 8-15} of both k-steps
+        sg_ldsm_x4(bx, xb + sg_off(mt * 8 + lr, 4 * kp + li));
+        sg_mma(acc[mt], a0, bx[0], bx[1]);
+        sg_mma(acc[mt], a1, bx[2], bx[3]);
+      }
+      __syncwarp();
+      if (lane == 0) tma::mbar_arrive(&empty[s]);
+    }
+    // ---- the two k-step halves meet in shared memory (the ring is free: every box has been consumed) ----
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    float* red = reinterpret_cast<float*>(ring);           // [2][32][64]
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      const int n = rb * 16 + (lane >> 2), m = mt * 8 + 2 * (lane & 3);
+      float* r0 = red + (kp * SG_MAXM + m) * SG_BN + n;
+      r0[0] = acc[mt][0]; r0[SG_BN] = acc[mt][1]; r0[8] = acc[mt][2]; r0[SG_BN + 8] = acc[mt][3];
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+  }
+
+  // ---- pair exchange: the second CTA's sums cross to the first, which finishes the tile ----
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");          // (pairs with the arrive at entry)
+  const int m = tid >> 3, n8 = (tid & 7) * 8;                          // this thread's 8 outputs (consumer threads only)
+  float sum[8];
+  if (warp < SG_CWARPS) {
+    const float* red = reinterpret_cast<const float*>(ring);
+    const float4 u0 = *reinterpret_cast<const float4*>(red + m * SG_BN + n8), u1 = *reinterpret_cast<const float4*>(red + m * SG_BN + n8 + 4);
+    const float4 v0 = *reinterpret_cast<const float4*>(red + (SG_MAXM + m) * SG_BN + n8), v1 = *reinterpret_cast<const float4*>(red + (SG_MAXM + m) * SG_BN + n8 + 4);
+    sum[0] = u0.x + v0.x; sum[1] = u0.y + v0.y; sum[2] = u0.z + v0.z; sum[3] = u0.w + v0.w;
+    sum[4] = u1.x + v1.x; sum[5] = u1.y + v1.y; sum[6] = u1.z + v1.z; sum[7] = u1.w + v1.w;
+    if (rank == 1) {
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(xchg + m * SG_BN + n8)), "r"(0));
+      asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(sum[0]), "f"(sum[1]), "f"(sum[2]), "f"(sum[3]) : "memory");
+      asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + 16), "f"(sum[4]), "f"(sum[5]), "f"(sum[6]), "f"(sum[7]) : "memory");
+    }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (rank == 0 && warp < SG_CWARPS && m < p.M) {
+    const float4 o0 = *reinterpret_cast<const float4*>(xchg + m * SG_BN + n8), o1 = *reinterpret_cast<const float4*>(xchg + m * SG_BN + n8 + 4);
+    float t[8] = {sum[0] + o0.x, sum[1] + o0.y, sum[2] + o0.z, sum[3] + o0.w, sum[4] + o1.x, sum[5] + o1.y, sum[6] + o1.z, sum[7] + o1.w};
+    if (p.res != nullptr) {
+      const uint4 rv = *reinterpret_cast<const uint4*>(p.res + (long long)m * p.res_rs + n0 + n8);
+      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        // the product is rounded to bf16 first, as a GEMM followed by a separate add would
+        t[2 * q] = bf16_round(t[2 * q]) + __uint_as_float(rw[q] << 16);
+        t[2 * q + 1] = bf16_round(t[2 * q + 1]) + __uint_as_float(rw[q] & 0xffff0000u);
+      }
+    }
+    uint4 ov;
+    ov.x = bf16_pack(t[0], t[1]); ov.y = bf16_pack(t[2], t[3]); ov.z = bf16_pack(t[4], t[5]); ov.w = bf16_pack(t[6], t[7]);
+    *reinterpret_cast<uint4*>(p.y + (long long)m * p.y_rs + n0 + n8) = ov;
+  }
+}
+
+}  // namespace
+
+// Shapes the kernel covers: up to 32 rows, K a multiple of 128 and at most 4096 (each CTA of a pair keeps K/2
+// columns of X in shared memory), N a multiple of 64.
+extern "C" int coda_b200_skinny_gemm_supported(int32_t M, int32_t K, int32_t N) {
+  return M >= 1 && M <= SG_MAXM && K >= 128 && K % 128 == 0 && K <= 4096 && N >= SG_BN && N % SG_BN == 0 && N / SG_BN <= 65535 &&
+         tmaps::available();
+}
+
+extern "C" int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, int32_t N,
+                                     const void* residual, int64_t res_rs, void* y, int64_t y_rs,
+                                     int32_t* status, coda_stream_t stream) {
+  CODA_REQUIRE(coda_b200_skinny_gemm_supported(M, K, N), CODA_ERR_ARG,
+               "skinny_gemm: needs 1..32 rows, K a multiple of 128 up to 4096, N a multiple of 64 (got %d x %d -> %d)", M, K, N);
+  CODA_REQUIRE(x && w && y && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)y % 16 == 0 && y_rs % 8 == 0 && y_rs >= N,
+               CODA_ERR_ARG, "skinny_gemm: null or misaligned pointer / output stride");
+  CODA_REQUIRE(!residual || ((uintptr_t)residual % 16 == 0 && res_rs % 8 == 0 && res_rs >= N), CODA_ERR_ARG,
+               "skinny_gemm: misaligned residual");
+  CUtensorMap xm, wm;
+  CODA_REQUIRE(tmaps::plane_map(&xm, x, 1, M, K, SG_MAXM) && tmaps::plane_map(&wm, w, 1, N, K, SG_BN), CODA_ERR_LAUNCH,
+               "skinny_gemm: cuTensorMapEncodeTiled failed");
+  SkinnyParams p;
+  p.M = M; p.N = N; p.K = K; p.res = (const bf16*)residual; p.res_rs = res_rs; p.y = (bf16*)y; p.y_rs = y_rs; p.status = status;
+  const size_t smem = (size_t)SkinnySmem(K / 2).total + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    configured = true;
+  }
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(2, N / SG_BN, 1);
+  lc.blockDim = dim3(SG_THREADS, 1, 1);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  lc.attrs = at; lc.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&lc, skinny_gemm_kernel, xm, wm, p);
+  if (e != cudaSuccess) { coda_set_error("skinny_gemm: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
+  return CODA_OK;
+}

@@ -200,6 +200,17 @@ int coda_b200_decode_attend_prepared(const coda_layer_cfg* cfg, const coda_state
                                      const void* norm_w, void* out, int64_t out_bs, int32_t* status,
                                      coda_stream_t stream);
 
+/* y[M][N] = x[M][K] . w[N][K]^T (+ residual[M][N]), bf16 with fp32 accumulation, for the decode step's few rows
+ * (M <= 32): the output projection of src/coda_gqa_l/attention.py:514 (`self.o_proj`, an nn.Linear without bias,
+ * weight [N][K]) with the decoder's residual added in the same pass (the product is rounded to bf16 before the
+ * add, as a GEMM followed by an add would).  x and w are dense row-major; y and residual have row strides in
+ * elements.  coda_b200_skinny_gemm_supported tells whether the shape is covered (K a multiple of 128 up to 4096,
+ * N a multiple of 64); status: optional device int, set non-zero if a bounded wait expired. */
+int coda_b200_skinny_gemm_supported(int32_t M, int32_t K, int32_t N);
+int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, int32_t N,
+                          const void* residual, int64_t res_rs, void* y, int64_t y_rs,
+                          int32_t* status, coda_stream_t stream);
+
 /* Differential attention of Lq query rows per state over [all Lbuf slots | optional block].
  * out = head_norm( softmax(q K^T) V - lam * softmax(q_noise K^T) V ), GQA by head index.
  * Slots are masked by `allowed` (when mask_unused); block key j is visible to row i iff j <= i.

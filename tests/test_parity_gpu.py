@@ -460,3 +460,57 @@ def test_attend_step_tuned_matches_generic():
         assert rel_err(ya, yb) < 5e-3, f"query_pos={qpos}"
     mod.use_tuned_kernels = True
     assert mod.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N,res", [(32, 4096, 4096, True), (32, 4096, 4096, False), (5, 512, 256, True), (1, 128, 64, False),
+                                       (17, 2048, 6208, True)])
+def test_skinny_gemm_matches_library_gemm(M, K, N, res):
+    """The decode step's output projection kernel (weight rows streamed through a TMA ring, K split over a CTA pair,
+    residual in the epilogue) against torch's GEMM: fp32 accumulation on both sides, so the results agree to
+    bf16 rounding of the outputs."""
+    import ctypes as C
+    from coda_gqa_l_b200._lib import lib, check
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    r = (torch.randn(M, N, device="cuda", generator=g)).to(torch.bfloat16) if res else None
+    y = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.coda_b200_skinny_gemm_supported(M, K, N)
+    check(lib.coda_b200_skinny_gemm(x.data_ptr(), M, K, w.data_ptr(), N, None if r is None else r.data_ptr(), N, y.data_ptr(), N,
+                                    status.data_ptr(), torch.cuda.current_stream().cuda_stream), "coda_b200_skinny_gemm")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = (x.float() @ w.float().t()).to(torch.bfloat16)
+    if res:
+        ref = (ref.float() + r.float()).to(torch.bfloat16)
+    assert torch.isfinite(y.float()).all()
+    err = rel_err(y, ref)
+    assert err < 4e-3, f"skinny gemm rel err {err:.3e}"
+    # element-wise: within one bf16 step of the fp32 reference
+    assert float((y.float() - ref.float()).abs().max()) <= 2.0 ** -7 * float(ref.float().abs().max())
+
+
+@pytest.mark.gpu
+def test_decode_step_with_own_output_gemm_matches_library_gemm():
+    """`use_skinny_gemm_kernel` swaps the decode step's output projection (+ residual) for this library's kernel."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, _deep_copy_state
+    torch.manual_seed(2)
+    mod = CoDAGQALandmarkPerf2(embed_dim=512, num_heads=4, num_kv_heads=2, window=48, num_landmarks_exact=16,
+                               num_landmarks_summary=16).eval().to(torch.bfloat16).cuda()
+    x = orc.mixture_inputs(4, 80, 512, centroids=12, sigma=0.3, seed=3, dtype=torch.bfloat16).cuda()
+    sa = mod.init_state(batch_size=4, device="cuda", dtype=torch.bfloat16)
+    _, sa = mod.prefill_chunked(x[:, :60], sa, block_size=20)
+    sb = _deep_copy_state(sa)
+    ya, yb = [], []
+    for t in range(60, 80):
+        mod.use_skinny_gemm_kernel = True
+        y, sa = mod.step(x[:, t:t + 1], sa)
+        ya.append(y)
+        mod.use_skinny_gemm_kernel = False
+        y, sb = mod.step(x[:, t:t + 1], sb)
+        yb.append(y)
+    assert mod.device_status() == 0
+    assert torch.equal(sa.k_buf, sb.k_buf) and torch.equal(sa.allowed, sb.allowed)
+    assert rel_err(torch.cat(ya, 1), torch.cat(yb, 1)) < 5e-3
