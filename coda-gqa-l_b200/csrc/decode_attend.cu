@@ -193,6 +193,8 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // everything above touched no global memory: from here on the previous kernel's results are needed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp >= DA_CWARPS + DA_AWARPS) {
     // ---------------- producer: records first, then the ring of K/V tiles, across plane boundaries ----------------
@@ -480,8 +482,20 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
     if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
   }
   const int nplanes = p.B * p.Hkv;
-  decode_attend_kernel<DH, NQ><<<nplanes < num_sms ? nplanes : num_sms, DA_THREADS, smem, s>>>(km, vm, p);
-  CODA_CHECK_LAUNCH("decode_attend");
+  // Programmatic dependent launch: the CTAs may start (shared-memory carve-up, barrier initialisation) while the
+  // kernel before this one on the stream is still finishing; they wait for it (griddepcontrol.wait) before the
+  // first global access.
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(nplanes < num_sms ? nplanes : num_sms, 1, 1);
+  lc.blockDim = dim3(DA_THREADS, 1, 1);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at; lc.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&lc, decode_attend_kernel<DH, NQ>, km, vm, p);
+  if (e != cudaSuccess) { coda_set_error("decode_attend: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
   return CODA_OK;
 }
 

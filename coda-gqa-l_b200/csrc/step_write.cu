@@ -783,6 +783,9 @@ __global__ void __launch_bounds__(288) step_append_kernel(StepParams p) {
   __shared__ unsigned char s_al[1024];                    // Lbuf <= 1024 (fused-mode limit)
   T* kb = (T*)p.st.k_buf + ((long long)b * Hkv + h) * Lbuf * DH;
   T* vb = (T*)p.st.v_buf + ((long long)b * Hkv + h) * Lbuf * DH;
+  // the kernel after this one (the decode attention) may start its prologue now; it waits for this grid to
+  // complete before it reads anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long long nsteps = ring_steps(p.rp);             // the ring position hangs on it: asked for first
   if (warp == NT / 32) {
     constexpr unsigned CH = 16384;
