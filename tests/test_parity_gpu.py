@@ -514,3 +514,39 @@ def test_decode_step_with_own_output_gemm_matches_library_gemm():
     assert mod.device_status() == 0
     assert torch.equal(sa.k_buf, sb.k_buf) and torch.equal(sa.allowed, sb.allowed)
     assert rel_err(torch.cat(ya, 1), torch.cat(yb, 1)) < 5e-3
+
+
+@pytest.mark.gpu
+def test_split_step_route_then_append_equals_single_launch_step():
+    """`coda_b200_step_route` + `coda_b200_step_append_fused` (the step in two launches, through
+    `route_launch` / `step_graphable(routed=True)`) leave the state exactly as the one-launch `step()` does,
+    across the fill -> evict boundary of the ring."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, _deep_copy_state
+    from coda_gqa_l_b200._lib import RingPos
+    from tests.scenarios import randomize_weights
+    torch.manual_seed(5)
+    mod = CoDAGQALandmarkPerf2(embed_dim=512, num_heads=8, num_kv_heads=2, window=40, num_landmarks_exact=16,
+                               num_landmarks_summary=16).eval()
+    randomize_weights(mod, 5)
+    mod = mod.to(torch.bfloat16).cuda()
+    B = 5
+    x = orc.mixture_inputs(B, 30 + 70, 512, centroids=16, sigma=0.3, seed=8, dtype=torch.bfloat16).cuda()
+    sa = mod.init_state(batch_size=B, device="cuda", dtype=torch.bfloat16)
+    _, sa = mod.prefill_chunked(x[:, :30], sa, block_size=16)         # ring not yet full
+    sb = _deep_copy_state(sa)
+    stream = torch.cuda.current_stream().cuda_stream
+    ya, yb = [], []
+    for t in range(30, 100):
+        xt = x[:, t:t + 1]
+        rp = RingPos(int(sa.pos), int(sa.recent_idx), int(sa.recent_filled), None)
+        assert mod.route_launch(xt.dtype, sa, rp, stream)
+        ya.append(mod.step_graphable(xt, sa, rp, routed=True))
+        mod.advance_host_scalars(sa)
+        y, sb = mod.step(xt, sb)
+        yb.append(y)
+    assert mod.device_status() == 0
+    assert (sa.pos, sa.recent_idx, sa.recent_filled) == (sb.pos, sb.recent_idx, sb.recent_filled)
+    assert torch.equal(sa.allowed, sb.allowed) and torch.equal(sa.mem_last_exact, sb.mem_last_exact)
+    assert torch.equal(sa.k_buf, sb.k_buf) and torch.equal(sa.v_buf, sb.v_buf) and torch.equal(sa.g_recent, sb.g_recent)
+    assert torch.equal(sa._exact_v_norm, sb._exact_v_norm) and torch.equal(sa._sum_lf_k_norm, sb._sum_lf_k_norm)
+    assert rel_err(torch.cat(ya, 1), torch.cat(yb, 1)) < 5e-3
