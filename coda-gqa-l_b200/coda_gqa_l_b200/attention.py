@@ -180,6 +180,9 @@ class CoDAGQALandmarkPerf2(nn.Module):
         # Output projection of a decode step through this library's own skinny GEMM (coda_b200_skinny_gemm) instead
         # of the vendor GEMM + add.  Off by default: at 32 x 4096 -> 4096 it measures 9.8 us against 9.5 us.
         self.use_skinny_gemm_kernel = False
+        # Second half of a split decode step (after route_launch / the stack's batched routing) as one launch:
+        # the attention kernel writes the new token itself (coda_b200_decode_attend_append).
+        self.fuse_append_into_attention = True
         self._status = None
 
     # ------------------------------------------------------------------ state
@@ -650,6 +653,21 @@ class CoDAGQALandmarkPerf2(nn.Module):
         if routed:
             if not fused_ok:
                 raise RuntimeError("routed=True needs the fused cache-write kernel")
+            one = getattr(cfg, "_attend_append", None)
+            if one is None:
+                one = bool(lib.coda_b200_decode_attend_append_supported(C.byref(cfg)))
+                cfg._attend_append = one
+            if one and self.fuse_append_into_attention:
+                # the attention kernel writes the new token itself: one launch between the two GEMMs
+                check(lib.coda_b200_decode_attend_append(
+                    C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                    _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(),
+                    q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0), cos_t.data_ptr(), sin_t.data_ptr(),
+                    _p(nw), out.data_ptr(), out.stride(0), self._status_word(dev).data_ptr(), s),
+                    "coda_b200_decode_attend_append")
+                if host_update:
+                    self.advance_host_scalars(state)
+                return self._out(out, residual)
             qrec = self._decode_records(cfg, dev)
             check(lib.coda_b200_step_append_fused(
                 C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),

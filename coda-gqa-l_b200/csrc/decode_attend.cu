@@ -42,6 +42,13 @@ struct DecodeParams {
   const bf16* norm_w;
   bf16* out; long long out_bs;
   int* status;
+  // APPEND variant only: the new token (raw projections of this step) and the state buffers it is written to
+  const bf16* k_raw; long long k_bs; const bf16* v_new; long long v_bs;
+  const bf16* gate_logit; long long gate_bs; int gated;
+  const float* inv_freq;
+  const bf16* q_raw; long long q_bs; const bf16* lam_logit; long long lam_bs;
+  const bf16* cos_t; const bf16* sin_t;
+  bf16* k_buf; bf16* v_buf; uint8_t* allowed_w; float* g_recent;
 };
 
 using tma::smem_u32; using tma::mbar_init; using tma::mbar_expect_tx; using tma::mbar_arrive; using tma::mbar_try;
@@ -84,13 +91,15 @@ __device__ __forceinline__ uint32_t tile_off(int s, int c) {
 template <int DH>
 struct DecodeSmem {
   static constexpr int TILE_BYTES = DA_TILE * DH * 2;
-  int comb, rec, rec_stride, sml, bars, total;
+  int comb, rec, rec_stride, sml, nkv, cs, bars, total;
   __host__ __device__ DecodeSmem(int stages, int G, int Lbuf) {
     int o = stages * 2 * TILE_BYTES;
     comb = o; o += DA_CWARPS * 2 * G * DH * 4;      // [DA_CWARPS][2G][DH] partial outputs
     rec_stride = (DecodeRecord::bytes(G, DH, Lbuf) + 127) / 128 * 128;
     rec = o;  o += 2 * rec_stride;                  // [2] decode records (double-buffered)
     sml = o;  o += 2 * DA_CWARPS * 16 * 4;          // [2][DA_CWARPS][16]  (m, l)
+    nkv = o;  o += 2 * 4 * DH;                      // [2][K row | V row] of the new token (APPEND variant)
+    cs = o;   o += 4 * DH + 16;                     // cos | sin of the position (floats), then the ring slot (int)
     bars = o; o += (2 * DA_MAX_STAGES + 6) * 8;     // full[], empty[], q_ready[2], q_free[2], comb_full, comb_free
     total = o;
   }
@@ -156,7 +165,12 @@ __global__ void __launch_bounds__(128) decode_prep_kernel(DecodeParams p, const 
   for (int i = tid; i < DecodeRecord::mask_bytes(p.Lbuf); i += blockDim.x) mk[i] = i < p.Lbuf ? alb[i] : 0;
 }
 
-template <int DH, int NQ>
+// APPEND: the kernel also writes the step's new token (what step_append_kernel does): the auxiliary warps build
+// each plane's decode record in shared memory themselves instead of receiving it by bulk copy, write the token's
+// RoPE'd key / value row to the ring slot in global memory, and leave a copy in shared memory with which the
+// consumer warp that owns the slot overwrites that row of the staged tile (the tile was requested from HBM
+// before the row was written).
+template <int DH, int NQ, bool APPEND>
 __global__ void __launch_bounds__(DA_THREADS, 1)
 decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, DecodeParams p) {
   constexpr int KSTEPS = DH / 16;            // k-steps of Q.K^T
@@ -187,7 +201,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
 
   if (tid == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
-    mbar_init(&q_ready[0], 1); mbar_init(&q_ready[1], 1);
+    mbar_init(&q_ready[0], APPEND ? DA_AWARPS : 1); mbar_init(&q_ready[1], APPEND ? DA_AWARPS : 1);
     mbar_init(&q_free[0], DA_CWARPS + DA_AWARPS); mbar_init(&q_free[1], DA_CWARPS + DA_AWARPS);
     mbar_init(comb_full, DA_CWARPS); mbar_init(comb_free, DA_AWARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -195,6 +209,61 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   __syncthreads();
   // everything above touched no global memory: from here on the previous kernel's results are needed
   asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- APPEND: the new token's inputs of one plane, as the auxiliary threads hold them between request and use ----
+  constexpr int HALF = DH / 2;
+  constexpr int QI = (8 * HALF + DA_AWARPS * 32 - 1) / (DA_AWARPS * 32);   // (head, RoPE pair) items per auxiliary thread, G <= 8
+  constexpr int MB = 8;                                                     // mask bytes per auxiliary thread (Lbuf <= 1024)
+  struct AppIn { uint32_t fq0[QI], fq1[QI]; bf16 fct[QI], fst[QI]; bf16 ka, kb, vv, lam, gate; uint8_t am[MB]; };
+  AppIn in;
+  long long nsteps = 0;
+  float inv_f = 0.f;
+  const int at = tid - DA_CWARPS * 32;                   // index among the 128 auxiliary threads
+  auto load_inputs = [&](int plane, AppIn& a) {
+    const int b = plane / p.Hkv, hk = plane % p.Hkv;
+    const bf16* qrow = p.q_raw + (long long)b * p.q_bs + (long long)hk * G * DH;
+#pragma unroll
+    for (int it = 0; it < QI; ++it) {
+      const int w = at + it * (DA_AWARPS * 32);
+      a.fq0[it] = a.fq1[it] = 0u; a.fct[it] = a.fst[it] = __float2bfloat16_rn(0.f);
+      if (w < G * HALF) {
+        const int g = w / HALF, i = w % HALF;
+        const bf16* qh = qrow + g * DH;
+        if (p.interleaved) {
+          a.fq0[it] = *reinterpret_cast<const uint32_t*>(qh + 2 * i);
+        } else {
+          const int pi = 2 * i < HALF ? 2 * i : 2 * i - HALF;
+          a.fq0[it] = *reinterpret_cast<const uint32_t*>(qh + pi);
+          a.fq1[it] = *reinterpret_cast<const uint32_t*>(qh + pi + HALF);
+        }
+        a.fct[it] = p.cos_t[(hk * G + g) * HALF + i];
+        a.fst[it] = p.sin_t[(hk * G + g) * HALF + i];
+      }
+    }
+    a.ka = a.kb = a.vv = a.lam = a.gate = __float2bfloat16_rn(0.f);
+    if (at < DH) {
+      const bf16* kn = p.k_raw + (long long)b * p.k_bs + hk * DH;
+      int ia, ib;
+      if (p.interleaved) { ia = 2 * (at >> 1); ib = ia + 1; }
+      else { ia = at < HALF ? at : at - HALF; ib = ia + HALF; }
+      a.ka = kn[ia]; a.kb = kn[ib];
+      a.vv = p.v_new[(long long)b * p.v_bs + hk * DH + at];
+    }
+    if (at < G) a.lam = p.lam_logit[(long long)b * p.lam_bs + hk * G + at];
+    if (at == 0 && p.gated) a.gate = p.gate_logit[(long long)b * p.gate_bs];
+#pragma unroll
+    for (int k = 0; k < MB; ++k) { const int m = at + k * (DA_AWARPS * 32); a.am[k] = m < p.Lbuf ? p.allowed[(long long)b * p.Lbuf + m] : (uint8_t)0; }
+  };
+  if (APPEND) {
+    // requested before the block barrier below, i.e. before the producer's first tile: a small load issued behind
+    // a ring's worth of tile traffic would wait for all of it
+    if (warp >= DA_CWARPS && warp < DA_CWARPS + DA_AWARPS) {
+      nsteps = ring_steps(p.rp);
+      if (at < HALF) inv_f = p.inv_freq[at];
+      if ((int)blockIdx.x < nplanes) load_inputs(blockIdx.x, in);
+    }
+    __syncthreads();
+  }
 
   if (warp >= DA_CWARPS + DA_AWARPS) {
     // ---------------- producer: records first, then the ring of K/V tiles, across plane boundaries ----------------
@@ -207,11 +276,12 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         mbar_expect_tx(&q_ready[buf], rec_bytes);
         tma::bulk_load(rec0 + buf * L.rec_stride, p.qrec + (long long)plane * rec_bytes, rec_bytes, &q_ready[buf]);
       };
-      if ((int)blockIdx.x < nplanes) load_record(blockIdx.x, 0);
+      if (!APPEND && (int)blockIdx.x < nplanes) load_record(blockIdx.x, 0);
       for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
         // The next plane's record is requested as soon as its buffer is free -- normally before this plane's
         // first tile, so that it never stands behind a ring's worth of tile traffic -- without holding up the tiles.
-        bool pending = plane + (int)gridDim.x < nplanes;
+        // (APPEND: the auxiliary warps build the records, nothing to request.)
+        bool pending = !APPEND && plane + (int)gridDim.x < nplanes;
         for (int s = 0; s < nst; ++s) {
           if (pending && record_free(i + 1)) { load_record(plane + gridDim.x, i + 1); pending = false; }
           if (round > 0) mbar_wait(&empty[bi], (round - 1) & 1, p.status, 1);
@@ -242,8 +312,102 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     float nw[DV];
 #pragma unroll
     for (int k = 0; k < DV; ++k) nw[k] = (p.norm_full && dact) ? __bfloat162float(p.norm_w[4 * lane + k]) : 1.f;
+    // ---- APPEND: record + new token row of a plane, from the inputs requested earlier ----
+    float* sCS = reinterpret_cast<float*>(smem + L.cs);    // cos [HALF] | sin [HALF] of the token's position
+    int* s_ev = reinterpret_cast<int*>(smem + L.cs + 4 * DH);
+    int ev = 0; bool ring_full = false;
+    auto build_record = [&](int plane, int buf, const AppIn& a) {
+      using T = bf16;
+      const int b = plane / p.Hkv, hk = plane % p.Hkv;
+      unsigned char* rec = rec0 + buf * L.rec_stride;
+      bf16* q_s = reinterpret_cast<bf16*>(rec);
+#pragma unroll
+      for (int it = 0; it < QI; ++it) {
+        const int w = at + it * (DA_AWARPS * 32);
+        if (w < G * HALF) {
+          const int g = w / HALF, i = w % HALF;
+          const float a0 = __uint_as_float(a.fq0[it] << 16), a1 = __uint_as_float(a.fq0[it] & 0xffff0000u);
+          const float b0 = __uint_as_float(a.fq1[it] << 16), b1 = __uint_as_float(a.fq1[it] & 0xffff0000u);
+          float e0, e1;                                    // RoPE'd elements 2i, 2i+1 (primitives.py:99-113)
+          if (p.interleaved) {
+            e0 = t_sub<T>(t_mul<T>(a0, sCS[i]), t_mul<T>(a1, sCS[HALF + i]));
+            e1 = t_add<T>(t_mul<T>(a0, sCS[HALF + i]), t_mul<T>(a1, sCS[i]));
+          } else {
+            const bool lo = 2 * i < HALF;
+            const int pi = lo ? 2 * i : 2 * i - HALF;
+            e0 = lo ? t_add<T>(t_mul<T>(a0, sCS[pi]), t_mul<T>(-b0, sCS[HALF + pi])) : t_add<T>(t_mul<T>(b0, sCS[pi]), t_mul<T>(a0, sCS[HALF + pi]));
+            e1 = lo ? t_add<T>(t_mul<T>(a1, sCS[pi + 1]), t_mul<T>(-b1, sCS[HALF + pi + 1])) : t_add<T>(t_mul<T>(b1, sCS[pi + 1]), t_mul<T>(a1, sCS[HALF + pi + 1]));
+          }
+          const float ct = __bfloat162float(a.fct[it]), st = __bfloat162float(a.fst[it]);
+          const float n0 = t_sub<T>(t_mul<T>(e0, ct), t_mul<T>(e1, st));
+          const float n1 = t_add<T>(t_mul<T>(e0, st), t_mul<T>(e1, ct));
+          *reinterpret_cast<__nv_bfloat162*>(q_s + g * QSTR + 2 * i) = __floats2bfloat162_rn(e0, e1);
+          *reinterpret_cast<__nv_bfloat162*>(q_s + (G + g) * QSTR + 2 * i) = __floats2bfloat162_rn(n0, n1);
+        }
+      }
+      const int rows = DecodeRecord::qrows(G);
+      #pragma unroll 1
+      for (int w = at; w < (rows - 2 * G) * HALF; w += DA_AWARPS * 32)   // unused rows of the query tile: zero
+        *reinterpret_cast<uint32_t*>(q_s + (2 * G + w / HALF) * QSTR + 2 * (w % HALF)) = 0u;
+      float* lam = reinterpret_cast<float*>(rec + lam_off);
+      if (at < 8) lam[at] = at < G ? t_sigmoid<T>(__bfloat162float(a.lam)) : 0.f;
+      uint8_t* mk = rec + mask_off;
+#pragma unroll
+      for (int k = 0; k < MB; ++k) {
+        const int m = at + k * (DA_AWARPS * 32);
+        if (m < DecodeRecord::mask_bytes(p.Lbuf)) mk[m] = m < p.Lbuf ? (m == ev ? (uint8_t)1 : a.am[k]) : (uint8_t)0;
+      }
+      // the token's own row: ring slot in global memory, and a copy for the consumer warp that patches the tile
+      if (at < DH) {
+        const int d = at;
+        const float ka = __bfloat162float(a.ka), kb = __bfloat162float(a.kb);
+        const int ri = p.interleaved ? (d >> 1) : (d < HALF ? d : d - HALF);
+        const float cc = sCS[ri], ss = sCS[HALF + ri];
+        float nk;
+        if (p.interleaved) nk = (d & 1) ? t_add<T>(t_mul<T>(ka, ss), t_mul<T>(kb, cc)) : t_sub<T>(t_mul<T>(ka, cc), t_mul<T>(kb, ss));
+        else nk = d < HALF ? t_add<T>(t_mul<T>(ka, cc), t_mul<T>(-kb, ss)) : t_add<T>(t_mul<T>(kb, cc), t_mul<T>(ka, ss));
+        const bf16 nkb = __float2bfloat16_rn(nk);
+        bf16* nkv = reinterpret_cast<bf16*>(smem + L.nkv + buf * 4 * DH);
+        nkv[d] = nkb; nkv[DH + d] = a.vv;
+        const long long row = ((long long)plane * p.Lbuf + ev) * DH + d;
+        p.k_buf[row] = nkb; p.v_buf[row] = a.vv;
+      }
+      if (hk == 0 && at == 0) {
+        p.g_recent[(long long)b * p.W + ev] = p.gated ? t_sigmoid<T>(__bfloat162float(a.gate)) : 1.0f;
+        if (!ring_full) p.allowed_w[(long long)b * p.Lbuf + ev] = 1;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_ready[buf]);
+    };
+    if (APPEND && (int)blockIdx.x < nplanes) {
+      const RingNow r = ring_after(p.rp, p.W, nsteps);
+      ring_full = r.filled >= p.W;
+      ev = ring_full ? r.idx : r.filled;
+      if (at == 0) *s_ev = ev;
+      if (at < HALF) {
+        float ta = (float)r.pos, inv = inv_f;
+        if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
+        float ang = __fmul_rn(ta, inv);
+        if (p.angle_bf16) ang = bf16_round(ang);
+        float cc, ss; sincos_call(ang, &ss, &cc);
+        if (p.angle_bf16) { cc = bf16_round(cc); ss = bf16_round(ss); }
+        sCS[at] = bf16_round(cc); sCS[HALF + at] = bf16_round(ss);
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");       // the four auxiliary warps
+      build_record(blockIdx.x, 0, in);
+      if ((int)(blockIdx.x + gridDim.x) < nplanes) load_inputs(blockIdx.x + gridDim.x, in);
+    }
     int i = 0;
     for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
+      if (APPEND) {
+        // the NEXT plane's record, while the consumers are on this plane's tiles (its inputs were requested a plane ago)
+        const int next = plane + gridDim.x;
+        if (next < nplanes) {
+          if (i + 1 >= 2) mbar_wait(&q_free[(i + 1) & 1], (((i + 1) >> 1) - 1) & 1, p.status, 6);
+          build_record(next, (i + 1) & 1, in);
+          if (next + (int)gridDim.x < nplanes) load_inputs(next + gridDim.x, in);
+        }
+      }
       mbar_wait(&q_ready[i & 1], (i >> 1) & 1, p.status, 7);   // lambda comes from the plane's record (a bulk copy: observed through its own barrier)
       mbar_wait(comb_full, i & 1, p.status, 5);
       const int b = plane / p.Hkv, hk = plane % p.Hkv;
@@ -349,6 +513,20 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       mbar_wait(&full[bi], round & 1, p.status, 2);
       const uint32_t kb = smem_u32(stage0 + bi * 2 * TILE_BYTES);
       const uint32_t vb = kb + TILE_BYTES;
+      if (APPEND) {
+        // the tile may have left HBM before the new token's row was written: the warp that owns the ring slot
+        // puts the row (left in shared memory by the auxiliary warps) over it -- only this warp reads these rows
+        const int ev = *reinterpret_cast<const int*>(smem + L.cs + 4 * DH);
+        if (s == ev / DA_TILE && gw == (ev % DA_TILE) / 16) {
+          constexpr int CPR = DH / 8;                      // 16-byte chunks per row
+          if (lane < 2 * CPR) {
+            const int which = lane / CPR, c = lane % CPR;
+            const uint4 v = *reinterpret_cast<const uint4*>(smem + L.nkv + buf * 4 * DH + which * 2 * DH + c * 16);
+            *reinterpret_cast<uint4*>(stage0 + bi * 2 * TILE_BYTES + which * TILE_BYTES + tile_off<DH>(ev % DA_TILE, c)) = v;
+          }
+          __syncwarp();
+        }
+      }
       // ---- S^T = K Q^T over this warp's 16 slots (two accumulation chains per n-tile) ----
       float sc[NQ][4], sd[NQ][4];
 #pragma unroll
@@ -459,7 +637,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   }  // plane loop
 }
 
-template <int DH, int NQ>
+template <int DH, int NQ, bool APPEND>
 int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, cudaStream_t s) {
   constexpr int BUDGET = 226 * 1024;
   // as many ring stages as fit beside the fixed buffers (at least 2, at most DA_MAX_STAGES)
@@ -472,7 +650,7 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
   const size_t smem = (size_t)DecodeSmem<DH>(stages, p.G, p.Lbuf).total + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(decode_attend_kernel<DH, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, BUDGET);
+    cudaFuncSetAttribute(decode_attend_kernel<DH, NQ, APPEND>, cudaFuncAttributeMaxDynamicSharedMemorySize, BUDGET);
     configured = true;
   }
   static int num_sms = 0;
@@ -494,7 +672,7 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at; lc.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&lc, decode_attend_kernel<DH, NQ>, km, vm, p);
+  cudaError_t e = cudaLaunchKernelEx(&lc, decode_attend_kernel<DH, NQ, APPEND>, km, vm, p);
   if (e != cudaSuccess) { coda_set_error("decode_attend: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
   return CODA_OK;
 }
@@ -520,16 +698,23 @@ DecodeParams make_params(const coda_layer_cfg* cfg, const coda_state_ptrs* st, v
   p.rp = coda_ring_pos{0, 0, 0, nullptr}; p.W = cfg->W;
   p.qrec = (unsigned char*)qrec; p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w;
   p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
+  p.k_raw = nullptr; p.k_bs = 0; p.v_new = nullptr; p.v_bs = 0; p.gate_logit = nullptr; p.gate_bs = 0; p.gated = 0;
+  p.inv_freq = nullptr; p.q_raw = nullptr; p.q_bs = 0; p.lam_logit = nullptr; p.lam_bs = 0; p.cos_t = nullptr; p.sin_t = nullptr;
+  p.k_buf = nullptr; p.v_buf = nullptr; p.allowed_w = nullptr; p.g_recent = nullptr;
   return p;
 }
 
-int launch_main(const coda_layer_cfg* cfg, const coda_state_ptrs* st, const DecodeParams& p, cudaStream_t s) {
+int launch_main(const coda_layer_cfg* cfg, const coda_state_ptrs* st, const DecodeParams& p, cudaStream_t s, bool append = false) {
   CUtensorMap km, vm;
   CODA_REQUIRE(tmaps::plane_map(&km, st->k_buf, cfg->B * cfg->Hkv, p.Lbuf, cfg->Dh) &&
                tmaps::plane_map(&vm, st->v_buf, cfg->B * cfg->Hkv, p.Lbuf, cfg->Dh), CODA_ERR_LAUNCH,
                "decode_attend: cuTensorMapEncodeTiled failed");
-  if (p.G <= 4) return cfg->Dh == 128 ? launch_decode<128, 1>(km, vm, p, s) : launch_decode<64, 1>(km, vm, p, s);
-  return cfg->Dh == 128 ? launch_decode<128, 2>(km, vm, p, s) : launch_decode<64, 2>(km, vm, p, s);
+  if (append) {
+    if (p.G <= 4) return cfg->Dh == 128 ? launch_decode<128, 1, true>(km, vm, p, s) : launch_decode<64, 1, true>(km, vm, p, s);
+    return cfg->Dh == 128 ? launch_decode<128, 2, true>(km, vm, p, s) : launch_decode<64, 2, true>(km, vm, p, s);
+  }
+  if (p.G <= 4) return cfg->Dh == 128 ? launch_decode<128, 1, false>(km, vm, p, s) : launch_decode<64, 1, false>(km, vm, p, s);
+  return cfg->Dh == 128 ? launch_decode<128, 2, false>(km, vm, p, s) : launch_decode<64, 2, false>(km, vm, p, s);
 }
 
 }  // namespace
@@ -578,4 +763,38 @@ extern "C" int coda_b200_decode_attend_prepared(const coda_layer_cfg* cfg, const
   if (rc != CODA_OK) return rc;
   const DecodeParams p = make_params(cfg, st, const_cast<void*>(qrec), norm_w, out, out_bs, status);
   return launch_main(cfg, st, p, (cudaStream_t)stream);
+}
+
+// The decode attention that also writes the step's new token (the second half of a split step, in place of
+// coda_b200_step_append_fused + coda_b200_decode_attend_prepared): ring slot, gate, slot flag, and the queries,
+// lambda and mask the attention itself needs, built in shared memory.  Same arguments as the two calls together;
+// the routing of the token the ring evicts (coda_b200_step_route / _batched with the same rp) must have run.
+extern "C" int coda_b200_decode_attend_append_supported(const coda_layer_cfg* cfg) {
+  return coda_b200_decode_attend_supported(cfg) && cfg->W + cfg->Me + cfg->Ms <= 1024;
+}
+
+extern "C" int coda_b200_decode_attend_append(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                              const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                              const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                              const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                              const void* cos_theta, const void* sin_theta, const void* norm_w,
+                                              void* out, int64_t out_bs, int32_t* status, coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "decode_attend_append: invalid layer configuration");
+  CODA_REQUIRE(coda_b200_decode_attend_append_supported(cfg), CODA_ERR_ARG,
+               "decode_attend_append: needs bf16, head_dim 64 or 128, at most 8 query heads per KV head and 1024 slots");
+  CODA_REQUIRE(out && st->k_buf && st->v_buf && st->allowed && st->g_recent && k_raw && v_new && inv_freq && q_raw && lam_logit &&
+               cos_theta && sin_theta && (!cfg->gated || gate_logit), CODA_ERR_ARG, "decode_attend_append: null pointer");
+  CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "decode_attend_append: head-norm weight missing");
+  CODA_REQUIRE(((uintptr_t)st->k_buf % 16 == 0) && ((uintptr_t)st->v_buf % 16 == 0) && ((uintptr_t)q_raw % 4 == 0) && (q_bs % 2 == 0),
+               CODA_ERR_ARG, "decode_attend_append: k_buf / v_buf must be 16-byte aligned, q_raw 4-byte aligned with an even stride");
+  CODA_REQUIRE(rp.recent_idx >= 0 && rp.recent_idx < cfg->W && rp.recent_filled >= 0 && rp.recent_filled <= cfg->W,
+               CODA_ERR_ARG, "decode_attend_append: ring scalars out of range");
+  DecodeParams p = make_params(cfg, st, nullptr, norm_w, out, out_bs, status);
+  p.rp = rp;
+  p.k_raw = (const bf16*)k_raw; p.k_bs = k_bs; p.v_new = (const bf16*)v_new; p.v_bs = v_bs;
+  p.gate_logit = (const bf16*)gate_logit; p.gate_bs = gate_bs; p.gated = cfg->gated;
+  p.inv_freq = inv_freq; p.q_raw = (const bf16*)q_raw; p.q_bs = q_bs; p.lam_logit = (const bf16*)lam_logit; p.lam_bs = lam_bs;
+  p.cos_t = (const bf16*)cos_theta; p.sin_t = (const bf16*)sin_theta;
+  p.k_buf = (bf16*)st->k_buf; p.v_buf = (bf16*)st->v_buf; p.allowed_w = st->allowed; p.g_recent = st->g_recent;
+  return launch_main(cfg, st, p, (cudaStream_t)stream, true);
 }

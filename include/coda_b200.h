@@ -211,6 +211,19 @@ int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, in
                           const void* residual, int64_t res_rs, void* y, int64_t y_rs,
                           int32_t* status, coda_stream_t stream);
 
+/* coda_b200_step_append_fused and coda_b200_decode_attend_prepared as ONE launch: the attention kernel's
+ * auxiliary warps write the new token (ring slot, gate, slot flag) and build each plane's queries / lambda / mask
+ * in shared memory; the consumer warp owning the ring slot overwrites that row of the staged tile.  Saves a
+ * launch and the record's round trip through global memory.  The token the ring evicts must have been routed
+ * before (coda_b200_step_route or coda_b200_step_route_batched, same rp).  <= 1024 slots. */
+int coda_b200_decode_attend_append_supported(const coda_layer_cfg* cfg);
+int coda_b200_decode_attend_append(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                   const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                   const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                   const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                   const void* cos_theta, const void* sin_theta, const void* norm_w,
+                                   void* out, int64_t out_bs, int32_t* status, coda_stream_t stream);
+
 /* Differential attention of Lq query rows per state over [all Lbuf slots | optional block].
  * out = head_norm( softmax(q K^T) V - lam * softmax(q_noise K^T) V ), GQA by head index.
  * Slots are masked by `allowed` (when mask_unused); block key j is visible to row i iff j <= i.

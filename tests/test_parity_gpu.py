@@ -517,7 +517,14 @@ def test_decode_step_with_own_output_gemm_matches_library_gemm():
 
 
 @pytest.mark.gpu
-def test_split_step_route_then_append_equals_single_launch_step():
+@pytest.mark.parametrize("B,kw", [
+    (5, dict(embed_dim=512, num_heads=8, num_kv_heads=2, window=40, num_landmarks_exact=16, num_landmarks_summary=16)),
+    # 480 planes on 148 SMs: three or four planes per CTA of the attention kernel that also writes the new token
+    (120, dict(embed_dim=256, num_heads=4, num_kv_heads=4, window=40, num_landmarks_exact=16, num_landmarks_summary=16)),
+    (40, dict(embed_dim=1024, num_heads=8, num_kv_heads=8, window=150, num_landmarks_exact=24, num_landmarks_summary=24,
+              rope_interleaved=False, head_norm_mode="identity")),
+])
+def test_split_step_route_then_append_equals_single_launch_step(B, kw):
     """`coda_b200_step_route` + `coda_b200_step_append_fused` (the step in two launches, through
     `route_launch` / `step_graphable(routed=True)`) leave the state exactly as the one-launch `step()` does,
     across the fill -> evict boundary of the ring."""
@@ -525,12 +532,10 @@ def test_split_step_route_then_append_equals_single_launch_step():
     from coda_gqa_l_b200._lib import RingPos
     from tests.scenarios import randomize_weights
     torch.manual_seed(5)
-    mod = CoDAGQALandmarkPerf2(embed_dim=512, num_heads=8, num_kv_heads=2, window=40, num_landmarks_exact=16,
-                               num_landmarks_summary=16).eval()
+    mod = CoDAGQALandmarkPerf2(**kw).eval()
     randomize_weights(mod, 5)
     mod = mod.to(torch.bfloat16).cuda()
-    B = 5
-    x = orc.mixture_inputs(B, 30 + 70, 512, centroids=16, sigma=0.3, seed=8, dtype=torch.bfloat16).cuda()
+    x = orc.mixture_inputs(B, 30 + 70, kw["embed_dim"], centroids=16, sigma=0.3, seed=8, dtype=torch.bfloat16).cuda()
     sa = mod.init_state(batch_size=B, device="cuda", dtype=torch.bfloat16)
     _, sa = mod.prefill_chunked(x[:, :30], sa, block_size=16)         # ring not yet full
     sb = _deep_copy_state(sa)
@@ -540,6 +545,7 @@ def test_split_step_route_then_append_equals_single_launch_step():
         xt = x[:, t:t + 1]
         rp = RingPos(int(sa.pos), int(sa.recent_idx), int(sa.recent_filled), None)
         assert mod.route_launch(xt.dtype, sa, rp, stream)
+        mod.fuse_append_into_attention = t % 3 != 0        # mostly the one-launch second half, sometimes the two-launch one
         ya.append(mod.step_graphable(xt, sa, rp, routed=True))
         mod.advance_host_scalars(sa)
         y, sb = mod.step(xt, sb)
