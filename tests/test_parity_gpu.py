@@ -244,22 +244,26 @@ def test_tuned_decode_kernel_matches_generic_kernels(shape):
     assert e < 5e-3, f"tuned vs generic decode attention: rel err {e:.3e}"
 
 
-def test_graph_replay_equals_eager_steps():
+@pytest.mark.parametrize("B,nl,steps,kw", [
+    (2, 3, 40, dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=8, num_landmarks_summary=8)),
+    # config-4 head geometry, 192 planes (two per CTA of the attention kernel), many replays
+    (24, 2, 150, dict(embed_dim=1024, num_heads=8, num_kv_heads=8, window=24, num_landmarks_exact=16, num_landmarks_summary=16)),
+])
+def test_graph_replay_equals_eager_steps(B, nl, steps, kw):
     """A captured stack step replayed N times gives the same states and outputs as N eager steps."""
     from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack, _deep_copy_state
-    kw = dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=8, num_landmarks_summary=8)
     layers = []
-    for i in range(3):
+    for i in range(nl):
         torch.manual_seed(i)
         layers.append(CoDAGQALandmarkPerf2(**kw).eval().to(torch.bfloat16).cuda())
     stack = CoDAStack(layers)
     torch.manual_seed(9)
-    sa = stack.init_states(batch_size=2, device="cuda", dtype=torch.bfloat16)
-    x = orc.mixture_inputs(2, 16 + 40, 256, centroids=8, sigma=0.3, seed=2, dtype=torch.bfloat16).cuda()
+    sa = stack.init_states(batch_size=B, device="cuda", dtype=torch.bfloat16)
+    x = orc.mixture_inputs(B, 16 + steps, kw["embed_dim"], centroids=8, sigma=0.3, seed=2, dtype=torch.bfloat16).cuda()
     stack.prefill(x[:, :16], sa, block_size=8)          # ring not yet full: replay crosses the fill -> evict boundary
     sb = [_deep_copy_state(s) for s in sa]
     outs_a, outs_b = [], []
-    for t in range(16, 56):
+    for t in range(16, 16 + steps):
         outs_a.append(stack.step_graph(x[:, t:t + 1], sa).clone())
         outs_b.append(stack.step(x[:, t:t + 1], sb))
     # Library GEMMs may pick another algorithm under capture, so floats are compared with the bf16 tolerance
