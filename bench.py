@@ -333,7 +333,7 @@ def main():
                 "ms_per_step": ms_e2e / K},
         # this repository's kernels inside the timed region: per layer the fused cache write and the decode
         # attention, plus the step-counter kernel of the captured graph (the two GEMMs per layer are library calls)
-        "gpu_launches": K * ((2 if args.eager or args.no_split_routing else 1) * w["layers"] + (0 if args.eager else (1 if args.no_split_routing else 2))),
+        "gpu_launches": K * ((2 if args.eager or args.no_split_routing else 1) * w["layers"] + (0 if args.eager else (1 if args.no_split_routing else 3))),
         "clocks": clocks.summary(),
         "roofline": {"kernel": "decode_attend_kernel (coda_b200_decode_attend_prepared)", "timing": "graph of back-to-back launches over all layers' states, CUDA events", "bound": "hbm", "achieved": achieved,
                      "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "of": peak_src,

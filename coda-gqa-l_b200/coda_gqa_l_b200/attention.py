@@ -635,7 +635,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
         return torch.addmm(residual.reshape(B * L, -1), heads.reshape(B * L, HD), self.o_proj.weight.t()).view(B, L, -1)
 
     def _step_fused(self, cfg, x, state, rp: RingPos, host_update: bool, routed: bool = False,
-                    residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    residual: Optional[torch.Tensor] = None, rope_cs: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Write-then-attend decode step on the tuned kernels: two launches between the two GEMMs.  The cache
         write applies RoPE / the gate sigmoid and, where it can, also prepares the attention's queries
         (decode records); the fused attention then only streams the state.  ``routed``: the evicted token
@@ -663,7 +663,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
                     C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
                     _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(),
                     q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0), cos_t.data_ptr(), sin_t.data_ptr(),
-                    _p(nw), out.data_ptr(), out.stride(0), self._status_word(dev).data_ptr(), s),
+                    _p(rope_cs), _p(nw), out.data_ptr(), out.stride(0), self._status_word(dev).data_ptr(), s),
                     "coda_b200_decode_attend_append")
                 if host_update:
                     self.advance_host_scalars(state)
@@ -719,18 +719,21 @@ class CoDAGQALandmarkPerf2(nn.Module):
             out.stride(0), self._status_word(out.device).data_ptr(), _stream()), "coda_b200_decode_attend_prepared")
 
     def step_graphable(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos,
-                       routed: bool = False, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       routed: bool = False, residual: Optional[torch.Tensor] = None,
+                       rope_cs: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The default ``step`` (write, then attend) with no host-side branching on the state, so that it
         can be captured in a CUDA graph: ring scalars come from ``rp`` (values at capture time plus the device
         step counter ``rp.step_dev``).  Does not touch the Python-side scalars.  With ``residual`` the result
-        is ``residual + y`` (added in the output GEMM)."""
+        is ``residual + y``; ``rope_cs``: float [head_dim] cos | sin table of this step's position from
+        ``coda_b200_rope_table`` (a stack computes it once per step for all its layers)."""
         if self._tracked(state):
             raise RuntimeError("a state with metrics or expandable banks needs a host read after every cache write "
                                "and cannot be replayed from a CUDA graph: use step()")
         B = x.shape[0]
         cfg = self._cfg(B, x.dtype, state)
         if self._tuned_decode(cfg):
-            return self._step_fused(cfg, x, state, rp, host_update=False, routed=routed, residual=residual)
+            return self._step_fused(cfg, x, state, rp, host_update=False, routed=routed, residual=residual,
+                                    rope_cs=rope_cs)
         if routed:
             raise RuntimeError("routed=True needs the tuned decode kernels")
         q, k, v, lam_logit, gate_logit = self._project(x, need_kv=True)

@@ -73,6 +73,9 @@ class CoDAStack(nn.Module):
         x_static = example_x.clone()
         rps = [RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), ctr.data_ptr()) for st in states]
         plan = self._route_plan(states, rps, x_static.dtype) if self.split_routing else None
+        rope_cs = None
+        if plan is not None and self._shared_rope(states, x_static.dtype):      # (compares tensors: outside the capture)
+            rope_cs = torch.empty(self.layers[0].head_dim, dtype=torch.float32, device=dev)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             # Routing of the tokens this step evicts needs the states only: all layers' in one launch up front
@@ -82,13 +85,31 @@ class CoDAStack(nn.Module):
                 check(lib.coda_b200_step_route_batched(C.byref(plan[0]), plan[1].data_ptr(), len(self.layers),
                                                        torch.cuda.current_stream(dev).cuda_stream),
                       "coda_b200_step_route_batched")
+            # cos / sin of this step's position: once for all layers instead of once per CTA of every layer
+            if rope_cs is not None:
+                l0 = self.layers[0]
+                check(lib.coda_b200_rope_table(C.byref(plan[0]), rps[0], l0._consts(dev, x_static.dtype)[0].data_ptr(),
+                                               rope_cs.data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
+                      "coda_b200_rope_table")
             h = x_static
             for layer, st, rp in zip(self.layers, states, rps):
-                h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h)
+                h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h, rope_cs=rope_cs)
             check(lib.coda_b200_advance_steps(ctr.data_ptr(), 1, torch.cuda.current_stream(dev).cuda_stream),
                   "coda_b200_advance_steps")
             out_static = h
-        self._graph = (g, x_static, out_static, ctr, [id(s) for s in states], plan)   # the plan lives as long as the graph
+        self._graph = (g, x_static, out_static, ctr, [id(s) for s in states], plan, rope_cs)   # plan / table live as long as the graph
+
+    def _shared_rope(self, states, dtype) -> bool:
+        """Do all layers rotate by the same angles at the same position (same head_dim, frequencies, angle dtype
+        and position)?  Then one cos / sin table per step serves them all."""
+        l0, s0 = self.layers[0], states[0]
+        f0 = l0._consts(s0.k_buf.device, dtype)[0]
+        for layer, st in zip(self.layers, states):
+            f = layer._consts(st.k_buf.device, dtype)[0]
+            if (layer.head_dim != l0.head_dim or st.pos != s0.pos or layer.rope.inv_freq.dtype != l0.rope.inv_freq.dtype
+                    or f.shape != f0.shape or not torch.equal(f, f0)):
+                return False
+        return True
 
     def _route_plan(self, states, rps, dtype):
         """Device plan for the batched routing launch, or None where the layers do not share one configuration

@@ -48,6 +48,7 @@ struct DecodeParams {
   const float* inv_freq;
   const bf16* q_raw; long long q_bs; const bf16* lam_logit; long long lam_bs;
   const bf16* cos_t; const bf16* sin_t;
+  const float* rope_cs;                           // optional: cos [Dh/2] | sin [Dh/2] of the token's position, precomputed
   bf16* k_buf; bf16* v_buf; uint8_t* allowed_w; float* g_recent;
 };
 
@@ -259,7 +260,8 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     // a ring's worth of tile traffic would wait for all of it
     if (warp >= DA_CWARPS && warp < DA_CWARPS + DA_AWARPS) {
       nsteps = ring_steps(p.rp);
-      if (at < HALF) inv_f = p.inv_freq[at];
+      if (p.rope_cs != nullptr) { if (at < DH) inv_f = p.rope_cs[at]; }      // the table entry itself
+      else if (at < HALF) inv_f = p.inv_freq[at];
       if ((int)blockIdx.x < nplanes) load_inputs(blockIdx.x, in);
     }
     __syncthreads();
@@ -384,7 +386,9 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       ring_full = r.filled >= p.W;
       ev = ring_full ? r.idx : r.filled;
       if (at == 0) *s_ev = ev;
-      if (at < HALF) {
+      if (p.rope_cs != nullptr) {
+        if (at < DH) sCS[at] = inv_f;                      // computed once per step for all layers (coda_b200_rope_table)
+      } else if (at < HALF) {
         float ta = (float)r.pos, inv = inv_f;
         if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
         float ang = __fmul_rn(ta, inv);
@@ -700,6 +704,7 @@ DecodeParams make_params(const coda_layer_cfg* cfg, const coda_state_ptrs* st, v
   p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
   p.k_raw = nullptr; p.k_bs = 0; p.v_new = nullptr; p.v_bs = 0; p.gate_logit = nullptr; p.gate_bs = 0; p.gated = 0;
   p.inv_freq = nullptr; p.q_raw = nullptr; p.q_bs = 0; p.lam_logit = nullptr; p.lam_bs = 0; p.cos_t = nullptr; p.sin_t = nullptr;
+  p.rope_cs = nullptr;
   p.k_buf = nullptr; p.v_buf = nullptr; p.allowed_w = nullptr; p.g_recent = nullptr;
   return p;
 }
@@ -777,7 +782,8 @@ extern "C" int coda_b200_decode_attend_append(const coda_layer_cfg* cfg, const c
                                               const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
                                               const void* gate_logit, int64_t gate_bs, const float* inv_freq,
                                               const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
-                                              const void* cos_theta, const void* sin_theta, const void* norm_w,
+                                              const void* cos_theta, const void* sin_theta, const float* rope_cs,
+                                              const void* norm_w,
                                               void* out, int64_t out_bs, int32_t* status, coda_stream_t stream) {
   CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "decode_attend_append: invalid layer configuration");
   CODA_REQUIRE(coda_b200_decode_attend_append_supported(cfg), CODA_ERR_ARG,
@@ -794,7 +800,32 @@ extern "C" int coda_b200_decode_attend_append(const coda_layer_cfg* cfg, const c
   p.k_raw = (const bf16*)k_raw; p.k_bs = k_bs; p.v_new = (const bf16*)v_new; p.v_bs = v_bs;
   p.gate_logit = (const bf16*)gate_logit; p.gate_bs = gate_bs; p.gated = cfg->gated;
   p.inv_freq = inv_freq; p.q_raw = (const bf16*)q_raw; p.q_bs = q_bs; p.lam_logit = (const bf16*)lam_logit; p.lam_bs = lam_bs;
-  p.cos_t = (const bf16*)cos_theta; p.sin_t = (const bf16*)sin_theta;
+  p.cos_t = (const bf16*)cos_theta; p.sin_t = (const bf16*)sin_theta; p.rope_cs = rope_cs;
   p.k_buf = (bf16*)st->k_buf; p.v_buf = (bf16*)st->v_buf; p.allowed_w = st->allowed; p.g_recent = st->g_recent;
   return launch_main(cfg, st, p, (cudaStream_t)stream, true);
+}
+
+// cos [Dh/2] | sin [Dh/2] of the position the ring scalars `rp` (+ device step counter) name, rounded as the decode
+// kernels round them (primitives.py:30-64 in bf16: angle dtype, then the K/V dtype): layers that share head_dim,
+// RoPE base and dtype can compute it once per step and hand it to coda_b200_decode_attend_append.
+__global__ void rope_table_kernel(coda_ring_pos rp, int W, const float* inv_freq, int half, int angle_bf16, float* out) {
+  const int i = threadIdx.x;
+  if (i >= half) return;
+  const RingNow r = ring_now(rp, W);
+  float ta = (float)r.pos, inv = inv_freq[i];
+  if (angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
+  float ang = __fmul_rn(ta, inv);
+  if (angle_bf16) ang = bf16_round(ang);
+  float cc, ss; sincos_call(ang, &ss, &cc);
+  if (angle_bf16) { cc = bf16_round(cc); ss = bf16_round(ss); }
+  out[i] = bf16_round(cc); out[half + i] = bf16_round(ss);
+}
+
+extern "C" int coda_b200_rope_table(const coda_layer_cfg* cfg, coda_ring_pos rp, const float* inv_freq, float* out,
+                                    coda_stream_t stream) {
+  CODA_REQUIRE(coda_cfg_ok(cfg) && inv_freq && out && cfg->Dh / 2 <= 1024, CODA_ERR_ARG, "rope_table: invalid arguments");
+  rope_table_kernel<<<1, (cfg->Dh / 2 + 31) / 32 * 32, 0, (cudaStream_t)stream>>>(rp, cfg->W, inv_freq, cfg->Dh / 2,
+                                                                                cfg->angle_dtype == CODA_BF16, out);
+  CODA_CHECK_LAUNCH("rope_table");
+  return CODA_OK;
 }

@@ -221,8 +221,13 @@ int coda_b200_decode_attend_append(const coda_layer_cfg* cfg, const coda_state_p
                                    const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
                                    const void* gate_logit, int64_t gate_bs, const float* inv_freq,
                                    const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
-                                   const void* cos_theta, const void* sin_theta, const void* norm_w,
+                                   const void* cos_theta, const void* sin_theta, const float* rope_cs,
+                                   const void* norm_w,
                                    void* out, int64_t out_bs, int32_t* status, coda_stream_t stream);
+/* rope_cs (optional, may be NULL): cos [Dh/2] | sin [Dh/2] of the token's position from coda_b200_rope_table --
+ * layers of a stack that share head_dim, RoPE base and dtype compute it once per step instead of once per CTA. */
+int coda_b200_rope_table(const coda_layer_cfg* cfg, coda_ring_pos rp, const float* inv_freq, float* out,
+                         coda_stream_t stream);
 
 /* Differential attention of Lq query rows per state over [all Lbuf slots | optional block].
  * out = head_norm( softmax(q K^T) V - lam * softmax(q_noise K^T) V ), GQA by head index.
