@@ -527,6 +527,10 @@ def test_decode_step_with_own_output_gemm_matches_library_gemm():
     (120, dict(embed_dim=256, num_heads=4, num_kv_heads=4, window=40, num_landmarks_exact=16, num_landmarks_summary=16)),
     (40, dict(embed_dim=1024, num_heads=8, num_kv_heads=8, window=150, num_landmarks_exact=24, num_landmarks_summary=24,
               rope_interleaved=False, head_norm_mode="identity")),
+    # eight query heads per KV head (two query n-tiles, two heads per auxiliary warp), head_dim 64 and 128
+    (6, dict(embed_dim=512, num_heads=8, num_kv_heads=1, window=40, num_landmarks_exact=16, num_landmarks_summary=8)),
+    (3, dict(embed_dim=1024, num_heads=8, num_kv_heads=1, window=70, num_landmarks_exact=8, num_landmarks_summary=16,
+             write_policy="none")),
 ])
 def test_split_step_route_then_append_equals_single_launch_step(B, kw):
     """`coda_b200_step_route` + `coda_b200_step_append_fused` (the step in two launches, through
