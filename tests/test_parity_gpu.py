@@ -564,3 +564,59 @@ def test_split_step_route_then_append_equals_single_launch_step(B, kw):
     assert torch.equal(sa.k_buf, sb.k_buf) and torch.equal(sa.v_buf, sb.v_buf) and torch.equal(sa.g_recent, sb.g_recent)
     assert torch.equal(sa._exact_v_norm, sb._exact_v_norm) and torch.equal(sa._sum_lf_k_norm, sb._sum_lf_k_norm)
     assert rel_err(torch.cat(ya, 1), torch.cat(yb, 1)) < 5e-3
+
+
+@pytest.mark.gpu
+def test_token_writing_attention_back_to_back_replays_are_stable():
+    """The attention kernel that also writes the step's new token, launched back to back on the same inputs and
+    ring position (a CUDA graph of four launches, replayed 1000 times; two planes per CTA): rewriting the same
+    token is idempotent, so every launch must return the same bits and leave the state as the first one did."""
+    import ctypes as C
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    from coda_gqa_l_b200._lib import RingPos, lib, check
+    torch.manual_seed(0)
+    B, H, Hkv, Dh = 32, 8, 8, 128
+    mod = CoDAGQALandmarkPerf2(embed_dim=H * Dh, num_heads=H, num_kv_heads=Hkv, window=256, num_landmarks_exact=64,
+                               num_landmarks_summary=64)
+    mod = mod.eval().to(torch.bfloat16).cuda()
+    st = mod.init_state(batch_size=B, device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(B, 385, H * Dh, device="cuda") * 0.5).to(torch.bfloat16)
+    mod.prefill_chunked(x[:, :384], st, block_size=128, return_outputs=False)
+    cfg = mod._cfg(B, torch.bfloat16, st)
+    assert lib.coda_b200_decode_attend_append_supported(C.byref(cfg))
+    rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
+    assert mod.route_launch(torch.bfloat16, st, rp, torch.cuda.current_stream().cuda_stream)
+    q, k, v, lam_logit, gate_logit = mod._project(x[:, 384:385], need_kv=True)
+    inv_freq, cos_t, sin_t, _, nw = mod._consts(x.device, torch.bfloat16)
+    ptrs = mod._ptrs(st)
+    outs = [torch.empty(B, 1, H * Dh, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+
+    def launch(o):
+        check(lib.coda_b200_decode_attend_append(
+            C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+            gate_logit.data_ptr(), gate_logit.stride(0), inv_freq.data_ptr(), q.data_ptr(), q.stride(0),
+            lam_logit.data_ptr(), lam_logit.stride(0), cos_t.data_ptr(), sin_t.data_ptr(), None,
+            None if nw is None else nw.data_ptr(), o.data_ptr(), o.stride(0), mod._status_word(x.device).data_ptr(),
+            torch.cuda.current_stream().cuda_stream), "coda_b200_decode_attend_append")
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launch(outs[0])
+        torch.cuda.synchronize()
+        ref = outs[0].clone()
+        k_ref, v_ref, al_ref, g_ref = st.k_buf.clone(), st.v_buf.clone(), st.allowed.clone(), st.g_recent.clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for o in outs:
+                launch(o)
+        for rep in range(1000):
+            g.replay()
+            if rep % 250 == 249:
+                torch.cuda.synchronize()
+                for o in outs:
+                    assert torch.equal(o, ref), f"replay {rep}: output changed"
+    torch.cuda.synchronize()
+    assert mod.device_status() == 0
+    assert torch.equal(st.k_buf, k_ref) and torch.equal(st.v_buf, v_ref)
+    assert torch.equal(st.allowed, al_ref) and torch.equal(st.g_recent, g_ref)
