@@ -657,7 +657,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
             if one is None:
                 one = bool(lib.coda_b200_decode_attend_append_supported(C.byref(cfg)))
                 cfg._attend_append = one
-            if one and self.fuse_append_into_attention:
+            if one and self.fuse_append_into_attention and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0:
                 # the attention kernel writes the new token itself: one launch between the two GEMMs
                 check(lib.coda_b200_decode_attend_append(
                     C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),

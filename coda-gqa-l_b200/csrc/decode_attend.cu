@@ -215,7 +215,15 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   constexpr int HALF = DH / 2;
   constexpr int QI = (8 * HALF + DA_AWARPS * 32 - 1) / (DA_AWARPS * 32);   // (head, RoPE pair) items per auxiliary thread, G <= 8
   constexpr int MB = 8;                                                     // mask bytes per auxiliary thread (Lbuf <= 1024)
-  struct AppIn { uint32_t fq0[QI], fq1[QI]; bf16 fct[QI], fst[QI]; bf16 ka, kb, vv, lam, gate; uint8_t am[MB]; };
+  // fq0 / fq1: raw query pairs of this thread's QI CONSECUTIVE (head, RoPE pair) items (one 16- or 8-byte request
+  // each); fct / fst: the matching cos / sin of the learned rotation, two bf16 per word
+  struct AppIn { uint32_t fq0[QI], fq1[QI], fct[QI / 2], fst[QI / 2]; bf16 ka, kb, vv, lam, gate; uint8_t am[MB]; };
+  static_assert(QI == 2 || QI == 4, "vector widths below assume 2 or 4 items per auxiliary thread");
+  auto ld_words = [](uint32_t* dst, const void* src, int n) {       // n = 1, 2 or 4 words, naturally aligned
+    if (n == 4) { const uint4 t = *reinterpret_cast<const uint4*>(src); dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w; }
+    else if (n == 2) { const uint2 t = *reinterpret_cast<const uint2*>(src); dst[0] = t.x; dst[1] = t.y; }
+    else dst[0] = *reinterpret_cast<const uint32_t*>(src);
+  };
   AppIn in;
   long long nsteps = 0;
   float inv_f = 0.f;
@@ -224,22 +232,22 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     const int b = plane / p.Hkv, hk = plane % p.Hkv;
     const bf16* qrow = p.q_raw + (long long)b * p.q_bs + (long long)hk * G * DH;
 #pragma unroll
-    for (int it = 0; it < QI; ++it) {
-      const int w = at + it * (DA_AWARPS * 32);
-      a.fq0[it] = a.fq1[it] = 0u; a.fct[it] = a.fst[it] = __float2bfloat16_rn(0.f);
-      if (w < G * HALF) {
-        const int g = w / HALF, i = w % HALF;
-        const bf16* qh = qrow + g * DH;
-        if (p.interleaved) {
-          a.fq0[it] = *reinterpret_cast<const uint32_t*>(qh + 2 * i);
-        } else {
-          const int pi = 2 * i < HALF ? 2 * i : 2 * i - HALF;
-          a.fq0[it] = *reinterpret_cast<const uint32_t*>(qh + pi);
-          a.fq1[it] = *reinterpret_cast<const uint32_t*>(qh + pi + HALF);
-        }
-        a.fct[it] = p.cos_t[(hk * G + g) * HALF + i];
-        a.fst[it] = p.sin_t[(hk * G + g) * HALF + i];
+    for (int it = 0; it < QI; ++it) a.fq0[it] = a.fq1[it] = 0u;
+#pragma unroll
+    for (int it = 0; it < QI / 2; ++it) a.fct[it] = a.fst[it] = 0u;
+    const int w0 = at * QI;                                // items w0 .. w0 + QI - 1: one head, consecutive pairs
+    if (w0 < G * HALF) {
+      const int g = w0 / HALF, i0 = w0 % HALF;
+      const bf16* qh = qrow + g * DH;
+      if (p.interleaved) {
+        ld_words(a.fq0, qh + 2 * i0, QI);
+      } else {
+        const int pi0 = 2 * i0 < HALF ? 2 * i0 : 2 * i0 - HALF;
+        ld_words(a.fq0, qh + pi0, QI);
+        ld_words(a.fq1, qh + pi0 + HALF, QI);
       }
+      ld_words(a.fct, p.cos_t + (hk * G + g) * HALF + i0, QI / 2);
+      ld_words(a.fst, p.sin_t + (hk * G + g) * HALF + i0, QI / 2);
     }
     a.ka = a.kb = a.vv = a.lam = a.gate = __float2bfloat16_rn(0.f);
     if (at < DH) {
@@ -323,11 +331,13 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       const int b = plane / p.Hkv, hk = plane % p.Hkv;
       unsigned char* rec = rec0 + buf * L.rec_stride;
       bf16* q_s = reinterpret_cast<bf16*>(rec);
+      const int w0 = at * QI;
+      if (w0 < G * HALF) {
+        const int g = w0 / HALF, i0 = w0 % HALF;
+        uint32_t sv[QI], nv[QI];
 #pragma unroll
-      for (int it = 0; it < QI; ++it) {
-        const int w = at + it * (DA_AWARPS * 32);
-        if (w < G * HALF) {
-          const int g = w / HALF, i = w % HALF;
+        for (int it = 0; it < QI; ++it) {
+          const int i = i0 + it;
           const float a0 = __uint_as_float(a.fq0[it] << 16), a1 = __uint_as_float(a.fq0[it] & 0xffff0000u);
           const float b0 = __uint_as_float(a.fq1[it] << 16), b1 = __uint_as_float(a.fq1[it] & 0xffff0000u);
           float e0, e1;                                    // RoPE'd elements 2i, 2i+1 (primitives.py:99-113)
@@ -340,11 +350,21 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
             e0 = lo ? t_add<T>(t_mul<T>(a0, sCS[pi]), t_mul<T>(-b0, sCS[HALF + pi])) : t_add<T>(t_mul<T>(b0, sCS[pi]), t_mul<T>(a0, sCS[HALF + pi]));
             e1 = lo ? t_add<T>(t_mul<T>(a1, sCS[pi + 1]), t_mul<T>(-b1, sCS[HALF + pi + 1])) : t_add<T>(t_mul<T>(b1, sCS[pi + 1]), t_mul<T>(a1, sCS[HALF + pi + 1]));
           }
-          const float ct = __bfloat162float(a.fct[it]), st = __bfloat162float(a.fst[it]);
+          const uint32_t cw = a.fct[it >> 1], sw = a.fst[it >> 1];
+          const float ct = __uint_as_float((it & 1) ? (cw & 0xffff0000u) : (cw << 16));
+          const float st = __uint_as_float((it & 1) ? (sw & 0xffff0000u) : (sw << 16));
           const float n0 = t_sub<T>(t_mul<T>(e0, ct), t_mul<T>(e1, st));
           const float n1 = t_add<T>(t_mul<T>(e0, st), t_mul<T>(e1, ct));
-          *reinterpret_cast<__nv_bfloat162*>(q_s + g * QSTR + 2 * i) = __floats2bfloat162_rn(e0, e1);
-          *reinterpret_cast<__nv_bfloat162*>(q_s + (G + g) * QSTR + 2 * i) = __floats2bfloat162_rn(n0, n1);
+          sv[it] = pack_bf16(e0, e1); nv[it] = pack_bf16(n0, n1);
+        }
+        bf16* srow = q_s + g * QSTR + 2 * i0;              // 4 * i0 bytes into a 272-byte row: aligned to QI words
+        bf16* nrow = q_s + (G + g) * QSTR + 2 * i0;
+        if (QI == 4) {
+          *reinterpret_cast<uint4*>(srow) = make_uint4(sv[0], sv[1], sv[2], sv[3]);
+          *reinterpret_cast<uint4*>(nrow) = make_uint4(nv[0], nv[1], nv[2], nv[3]);
+        } else {
+          *reinterpret_cast<uint2*>(srow) = make_uint2(sv[0], sv[1]);
+          *reinterpret_cast<uint2*>(nrow) = make_uint2(nv[0], nv[1]);
         }
       }
       const int rows = DecodeRecord::qrows(G);
@@ -791,8 +811,9 @@ extern "C" int coda_b200_decode_attend_append(const coda_layer_cfg* cfg, const c
   CODA_REQUIRE(out && st->k_buf && st->v_buf && st->allowed && st->g_recent && k_raw && v_new && inv_freq && q_raw && lam_logit &&
                cos_theta && sin_theta && (!cfg->gated || gate_logit), CODA_ERR_ARG, "decode_attend_append: null pointer");
   CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "decode_attend_append: head-norm weight missing");
-  CODA_REQUIRE(((uintptr_t)st->k_buf % 16 == 0) && ((uintptr_t)st->v_buf % 16 == 0) && ((uintptr_t)q_raw % 4 == 0) && (q_bs % 2 == 0),
-               CODA_ERR_ARG, "decode_attend_append: k_buf / v_buf must be 16-byte aligned, q_raw 4-byte aligned with an even stride");
+  CODA_REQUIRE(((uintptr_t)st->k_buf % 16 == 0) && ((uintptr_t)st->v_buf % 16 == 0) && ((uintptr_t)q_raw % 16 == 0) && (q_bs % 8 == 0) &&
+               ((uintptr_t)cos_theta % 8 == 0) && ((uintptr_t)sin_theta % 8 == 0), CODA_ERR_ARG,
+               "decode_attend_append: k_buf / v_buf / q_raw must be 16-byte aligned (q stride a multiple of 8 elements), the theta tables 8-byte aligned");
   CODA_REQUIRE(rp.recent_idx >= 0 && rp.recent_idx < cfg->W && rp.recent_filled >= 0 && rp.recent_filled <= cfg->W,
                CODA_ERR_ARG, "decode_attend_append: ring scalars out of range");
   DecodeParams p = make_params(cfg, st, nullptr, norm_w, out, out_bs, status);
