@@ -531,6 +531,9 @@ def test_decode_step_with_own_output_gemm_matches_library_gemm():
     (6, dict(embed_dim=512, num_heads=8, num_kv_heads=1, window=40, num_landmarks_exact=16, num_landmarks_summary=8)),
     (3, dict(embed_dim=1024, num_heads=8, num_kv_heads=1, window=70, num_landmarks_exact=8, num_landmarks_summary=16,
              write_policy="none")),
+    # half-split RoPE at head_dim 64 (two items per auxiliary thread), slot count not a multiple of 64
+    (4, dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=37, num_landmarks_exact=9, num_landmarks_summary=7,
+             rope_interleaved=False, rope_base=1e6)),
 ])
 def test_split_step_route_then_append_equals_single_launch_step(B, kw):
     """`coda_b200_step_route` + `coda_b200_step_append_fused` (the step in two launches, through
