@@ -171,6 +171,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
         self._const_cache: Dict[tuple, tuple] = {}
         self._scratch: Dict[tuple, torch.Tensor] = {}
         self._fused = None
+        self._fused_ptrs = []
         self._wt = None
         # When set to a list, every attention launch appends (Lq, start_event, end_event) to it.
         self.kernel_timers = None
@@ -398,15 +399,12 @@ class CoDAGQALandmarkPerf2(nn.Module):
         f = self._fused
         w0 = self.q_proj.weight
         if f is not None and f[0].device == w0.device and f[0].dtype == w0.dtype:
-            off, ok = 0, True
-            for l in lins:
-                if l.weight.data_ptr() != f[0][off:off + l.out_features].data_ptr():
+            # (addresses of the row ranges were noted when the matrix was built: no slicing on the decode path)
+            ok = True
+            for l, (wp, bp) in zip(lins, self._fused_ptrs):
+                if l.weight.data_ptr() != wp or (l.bias is not None and l.bias.data_ptr() != bp):
                     ok = False
                     break
-                if l.bias is not None and l.bias.data_ptr() != f[1][off:off + l.out_features].data_ptr():
-                    ok = False
-                    break
-                off += l.out_features
             if ok:
                 return f
         n = sum(l.out_features for l in lins)
@@ -422,6 +420,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
                 l.bias.data = b[off:off + l.out_features]
             off += l.out_features
         self._fused = (W, b)
+        self._fused_ptrs = [(l.weight.data_ptr(), None if l.bias is None else l.bias.data_ptr()) for l in lins]
         return self._fused
 
     # GEMMs with at most this many rows (decode) read transposed copies of the weights
