@@ -580,7 +580,10 @@ class CoDAGQALandmarkPerf2(nn.Module):
 
     def _decode_records(self, cfg, device) -> torch.Tensor:
         """Device buffer for the per-plane decode records (prepared queries, lambda, visibility mask)."""
-        n = int(lib.coda_b200_decode_record_bytes(C.byref(cfg)))
+        n = getattr(cfg, "_rec_bytes", None)
+        if n is None:
+            n = int(lib.coda_b200_decode_record_bytes(C.byref(cfg)))
+            cfg._rec_bytes = n
         buf = self._qrec
         if buf is None or buf.numel() < n or buf.device != device:
             buf = torch.empty(n, dtype=torch.uint8, device=device)
