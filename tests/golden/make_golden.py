@@ -1,8 +1,8 @@
 """Generate the golden fixtures under tests/golden/ from the upstream implementation.
 
-Run in a container where the upstream project is mounted (default /root/reference):
+Run where a checkout of the upstream project is available:
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <upstream checkout>      # or set CODA_GQA_L_REF
 
 For every scenario in ``SCENARIOS`` the script
   1. builds the upstream ``CoDAGQALandmarkPerf2`` (imported unmodified, with its optional
@@ -160,9 +160,11 @@ def run_scenario(name, sc, RefCls, out_dir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("CODA_GQA_L_REF"), help="root of the upstream checkout")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
+    if not args.ref:
+        ap.error("--ref (or CODA_GQA_L_REF) must point at the upstream checkout")
     RefCls = _load_reference(args.ref)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for name, sc in SCENARIOS.items():
