@@ -184,6 +184,10 @@ class CoDAGQALandmarkPerf2(nn.Module):
         # Second half of a split decode step (after route_launch / the stack's batched routing) as one launch:
         # the attention kernel writes the new token itself (coda_b200_decode_attend_append).
         self.fuse_append_into_attention = True
+        # Route the attention / cache-write / routing launches through the torch custom ops (torch.ops.coda_b200.*,
+        # see torch_ops.py) instead of the ctypes binding.  Same entry points underneath, so the same bits; states
+        # that report routing events (metrics, growing banks) and the fused decode-step launches stay on ctypes.
+        self.use_torch_ops = False
         self._status = None
 
     # ------------------------------------------------------------------ state
@@ -233,17 +237,26 @@ class CoDAGQALandmarkPerf2(nn.Module):
             raise RuntimeError("state and input must share device and dtype")
         if st.k_buf.shape != (x.shape[0], self.num_kv_heads, self.Lbuf, self.head_dim):
             raise RuntimeError(f"state k_buf shape {tuple(st.k_buf.shape)} does not match this layer / batch")
+        # A field that has to be replaced (non-contiguous view, a routing cache widened to fp32 by a serialisation
+        # helper) no longer lives in the state's arena: the arena is dropped so that nothing snapshots or ships stale
+        # bytes (capture_step then asks for an arena-backed state, state_to_bytes re-packs).
+        detached = False
         for name in ("k_buf", "v_buf", "allowed", "g_recent", "mem_last_exact"):
             t = getattr(st, name)
             if not t.is_contiguous():
                 setattr(st, name, t.contiguous())
-        # routing caches may have been widened to fp32 by a serialisation helper: bring them back
+                detached = True
         if st._exact_v_norm is not None and (st._exact_v_norm.dtype != x.dtype or not st._exact_v_norm.is_contiguous()):
             st._exact_v_norm = st._exact_v_norm.to(x.dtype).contiguous()
+            detached = True
         if st._sum_lf_k_norm is not None and (st._sum_lf_k_norm.dtype != x.dtype or not st._sum_lf_k_norm.is_contiguous()):
             st._sum_lf_k_norm = st._sum_lf_k_norm.to(x.dtype).contiguous()
+            detached = True
         if st.g_recent.dtype != torch.float32:
             st.g_recent = st.g_recent.float()
+            detached = True
+        if detached and getattr(st, "_arena", None) is not None:
+            st._arena = None
 
     # ------------------------------------------------------------------ metrics / bank expansion
     @property
@@ -479,6 +492,12 @@ class CoDAGQALandmarkPerf2(nn.Module):
         qn = torch.empty((B, L, self.num_heads * self.head_dim), device=dev, dtype=dt)
         lam = torch.empty((B, L, self.num_heads), device=dev, dtype=torch.float32)
         g = torch.empty((B, L), device=dev, dtype=torch.float32) if want_gate else None
+        if self.use_torch_ops and step_dev is None:
+            from . import torch_ops
+            ci, cf = torch_ops.cfg_lists(cfg)
+            torch_ops.load().prep(q, k, qn, lam_logit, lam, gate_logit if want_gate else None, g, inv_freq, cos_t, sin_t,
+                                  int(pos), ci, cf)
+            return qn, lam, g
         rp = RingPos(int(pos), 0, 0, step_dev)
         check(lib.coda_b200_prep(
             C.byref(cfg), L, rp,
@@ -498,6 +517,17 @@ class CoDAGQALandmarkPerf2(nn.Module):
         if timers is not None:                  # benchmark hook: CUDA events around the attention launch
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
+        if self.use_torch_ops:
+            from . import torch_ops
+            ci, cf = torch_ops.cfg_lists(cfg)
+            torch_ops.load().attend(out, st.k_buf, st.v_buf, st.allowed, q, qn, lam, k_blk, v_blk, nw, ci, cf)
+        else:
+            self._attend_ctypes(cfg, ptrs, Lq, q, qn, lam, k_blk, v_blk, nw, out)
+        if timers is not None:
+            ev1.record()
+            timers.append((Lq, ev0, ev1))
+
+    def _attend_ctypes(self, cfg, ptrs, Lq, q, qn, lam, k_blk, v_blk, nw, out):
         check(lib.coda_b200_attend(
             C.byref(cfg), C.byref(ptrs), Lq,
             q.data_ptr(), q.stride(0), q.stride(1), qn.data_ptr(), qn.stride(0), qn.stride(1),
@@ -505,9 +535,6 @@ class CoDAGQALandmarkPerf2(nn.Module):
             _p(k_blk), 0 if k_blk is None else k_blk.stride(0), 0 if k_blk is None else k_blk.stride(1),
             _p(v_blk), 0 if v_blk is None else v_blk.stride(0), 0 if v_blk is None else v_blk.stride(1),
             _p(nw), out.data_ptr(), out.stride(0), out.stride(1), _stream()), "coda_b200_attend")
-        if timers is not None:
-            ev1.record()
-            timers.append((Lq, ev0, ev1))
 
     def _write_one(self, cfg, st, k, v, g, rp: Optional[RingPos] = None):
         """Ring write of one token per state plus routing of the evicted one (upstream memory_banks.py:183-224).
@@ -520,9 +547,16 @@ class CoDAGQALandmarkPerf2(nn.Module):
             self._arm_events(st)
             rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
         ptrs = self._ptrs(st)
-        check(lib.coda_b200_step_write(C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0),
-                                       v.data_ptr(), v.stride(0), g.data_ptr(), eta.data_ptr(), _stream()),
-              "coda_b200_step_write")
+        if self.use_torch_ops and host and st._events is None:
+            from . import torch_ops
+            ci, cf = torch_ops.cfg_lists(cfg)
+            torch_ops.load().step_write(st.k_buf, st.v_buf, st.allowed, st.g_recent, st.mem_last_exact, st._exact_v_norm,
+                                        st._sum_lf_k_norm, k, v, g.view(-1), eta, int(st.pos), int(st.recent_idx),
+                                        int(st.recent_filled), ci, cf)
+        else:
+            check(lib.coda_b200_step_write(C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0),
+                                           v.data_ptr(), v.stride(0), g.data_ptr(), eta.data_ptr(), _stream()),
+                  "coda_b200_step_write")
         if host:
             self._account(st, int(st.recent_filled >= self.window), block=False)
             self.advance_host_scalars(st)
@@ -550,13 +584,19 @@ class CoDAGQALandmarkPerf2(nn.Module):
         if timers is not None:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
-        check(lib.coda_b200_prefill_attend(
-            C.byref(cfg), C.byref(ptrs), L, t0, blk,
-            q.data_ptr(), q.stride(0), q.stride(1), qn.data_ptr(), qn.stride(0), qn.stride(1),
-            lam.data_ptr(), lam.stride(0), lam.stride(1),
-            k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0), v.stride(1),
-            _p(nw), out.data_ptr(), out.stride(0), out.stride(1),
-            self._status_word(q.device).data_ptr(), _stream()), "coda_b200_prefill_attend")
+        if self.use_torch_ops:
+            from . import torch_ops
+            ci, cf = torch_ops.cfg_lists(cfg)
+            torch_ops.load().prefill_attend(out, st.k_buf, st.v_buf, st.allowed, q, qn, lam, k, v, nw,
+                                            self._status_word(q.device), int(t0), int(blk), ci, cf)
+        else:
+            check(lib.coda_b200_prefill_attend(
+                C.byref(cfg), C.byref(ptrs), L, t0, blk,
+                q.data_ptr(), q.stride(0), q.stride(1), qn.data_ptr(), qn.stride(0), qn.stride(1),
+                lam.data_ptr(), lam.stride(0), lam.stride(1),
+                k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0), v.stride(1),
+                _p(nw), out.data_ptr(), out.stride(0), out.stride(1),
+                self._status_word(q.device).data_ptr(), _stream()), "coda_b200_prefill_attend")
         if timers is not None:
             ev1.record()
             timers.append((blk, ev0, ev1))
@@ -706,6 +746,13 @@ class CoDAGQALandmarkPerf2(nn.Module):
         inv_freq, cos_t, sin_t, _, nw = self._consts(q.device, q.dtype)
         ptrs = self._ptrs(state)
         qrec = self._decode_records(cfg, q.device)
+        if self.use_torch_ops and rp.step_dev is None and q.dim() == 3:
+            from . import torch_ops
+            ci, cf = torch_ops.cfg_lists(cfg)
+            torch_ops.load().decode_attend(out, state.k_buf, state.v_buf, state.allowed, q, lam_logit, inv_freq, cos_t,
+                                           sin_t, nw, qrec, self._status_word(q.device), int(rp.pos), int(rp.recent_idx),
+                                           int(rp.recent_filled), int(token_already_written), ci, cf)
+            return
         check(lib.coda_b200_decode_attend(
             C.byref(cfg), C.byref(ptrs), rp, token_already_written, q.data_ptr(), q.stride(0),
             lam_logit.data_ptr(), lam_logit.stride(0), inv_freq.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
@@ -853,9 +900,16 @@ class CoDAGQALandmarkPerf2(nn.Module):
             ts = self.summary_candidates_per_block if self.Ms > 0 else 0
             tmax = max(1, min(max(te, ts), block))
             cand = torch.empty((B, nblk, tmax), device=dev, dtype=torch.int32)
+            ops = None
+            if self.use_torch_ops and not self._tracked(state):
+                from . import torch_ops
+                ops = torch_ops.load()
             if max(te, ts) > 0:
-                check(lib.coda_b200_select_candidates(C.byref(cfg), gates.data_ptr(), gates.stride(0), fill0, L, block,
-                                                      cand.data_ptr(), tmax, _stream()), "coda_b200_select_candidates")
+                if ops is not None:
+                    ops.select_candidates(cand, gates, fill0, L, block, *torch_ops.cfg_lists(cfg))
+                else:
+                    check(lib.coda_b200_select_candidates(C.byref(cfg), gates.data_ptr(), gates.stride(0), fill0, L, block,
+                                                          cand.data_ptr(), tmax, _stream()), "coda_b200_select_candidates")
             scratch = self._route_scratch(cfg, dev)
             _, _, _, eta, _ = self._consts(dev, dt)
             self._arm_events(state)
@@ -876,12 +930,17 @@ class CoDAGQALandmarkPerf2(nn.Module):
             if write_cache:
                 fill = int(state.recent_filled)
                 seen = fill0 + t0
-                check(lib.coda_b200_route_block(
-                    C.byref(cfg), C.byref(ptrs), fill, blk, pos0 + t0,
-                    kb.data_ptr(), k.stride(0), k.stride(1), vb.data_ptr(), v.stride(0), v.stride(1),
-                    gates.data_ptr(), gates.stride(0), seen - fill,
-                    cand[:, j].data_ptr(), cand.stride(0), eta.data_ptr(), scratch.data_ptr(), _stream()),
-                    "coda_b200_route_block")
+                if ops is not None:
+                    ops.route_block(state.k_buf, state.v_buf, state.allowed, state.g_recent, state.mem_last_exact,
+                                    state._exact_v_norm, state._sum_lf_k_norm, kb, vb, gates, cand[:, j], eta, scratch,
+                                    fill, pos0 + t0, seen - fill, *torch_ops.cfg_lists(cfg))
+                else:
+                    check(lib.coda_b200_route_block(
+                        C.byref(cfg), C.byref(ptrs), fill, blk, pos0 + t0,
+                        kb.data_ptr(), k.stride(0), k.stride(1), vb.data_ptr(), v.stride(0), v.stride(1),
+                        gates.data_ptr(), gates.stride(0), seen - fill,
+                        cand[:, j].data_ptr(), cand.stride(0), eta.data_ptr(), scratch.data_ptr(), _stream()),
+                        "coda_b200_route_block")
                 if state._events is not None:
                     self._account(state, fill + blk - min(W, fill + blk), block=True)
                     cfg = self._cfg(B, dt, state)          # the banks may have grown

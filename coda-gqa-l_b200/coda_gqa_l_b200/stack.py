@@ -20,9 +20,13 @@ from .state import CoDAGQALandmarkStatePerf2
 
 
 class CoDAStack(nn.Module):
-    def __init__(self, layers: List[CoDAGQALandmarkPerf2]):
+    """``residual=True`` chains the layers as ``h <- h + layer(h)``; ``residual=False`` as ``h <- layer(h)`` (a single
+    layer then returns exactly what ``layer.step`` / ``layer.prefill_chunked`` return)."""
+
+    def __init__(self, layers: List[CoDAGQALandmarkPerf2], residual: bool = True):
         super().__init__()
         self.layers = nn.ModuleList(layers)
+        self.residual = bool(residual)
         self._graph = None
         # Captured decode step: route every layer's evicted token in one launch at the start of the step instead of
         # inside each layer's own chain (set before the first step_graph).
@@ -37,7 +41,7 @@ class CoDAStack(nn.Module):
         h = x
         for layer, st in zip(self.layers, states):
             y, _ = layer.prefill_chunked(h, st, block_size=block_size)
-            h = h + y
+            h = h + y if self.residual else y
         self._graph = None                       # scalars baked into a captured step are stale now
         return h if return_outputs else None
 
@@ -47,7 +51,8 @@ class CoDAStack(nn.Module):
         h = x
         for layer, st in zip(self.layers, states):
             y, _ = layer.step(h, st)
-            h = h + y
+            h = h + y if self.residual else y
+        self._graph = None                       # the captured step's device counter did not see this write
         return h
 
     # ------------------------------------------------------------------ CUDA-graph decode
@@ -64,7 +69,10 @@ class CoDAStack(nn.Module):
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for _ in range(warmup):
-                self.step(example_x, states)
+                h = example_x
+                for layer, st in zip(self.layers, states):
+                    y, _ = layer.step(h, st)
+                    h = h + y if self.residual else y
         torch.cuda.current_stream(dev).wait_stream(side)
         for st, (arena, sc) in zip(states, snaps):
             st._arena.copy_(arena)
@@ -93,11 +101,34 @@ class CoDAStack(nn.Module):
                       "coda_b200_rope_table")
             h = x_static
             for layer, st, rp in zip(self.layers, states, rps):
-                h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h, rope_cs=rope_cs)
+                h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h if self.residual else None,
+                                         rope_cs=rope_cs)
             check(lib.coda_b200_advance_steps(ctr.data_ptr(), 1, torch.cuda.current_stream(dev).cuda_stream),
                   "coda_b200_advance_steps")
             out_static = h
-        self._graph = (g, x_static, out_static, ctr, [id(s) for s in states], plan, rope_cs)   # plan / table live as long as the graph
+        # Everything the graph's launches point at is kept alive with it (plan, table, the layers' derived weight and
+        # constant tensors), and what they were is noted so that a replay after any of them changed re-captures.
+        self._graph = dict(graph=g, x=x_static, out=out_static, ctr=ctr, plan=plan, rope_cs=rope_cs,
+                           states=list(states), key=self._graph_key(states, x_static.dtype),
+                           expect=[(st.pos, st.recent_idx, st.recent_filled) for st in states],
+                           keep=[(l._fused, l._wt, l._const_cache.get("k"), l._qrec, l._status) for l in self.layers])
+
+    def _graph_key(self, states, dtype):
+        """What a captured step depends on besides the ring scalars, cheap enough to evaluate before every replay:
+        the state objects and their active bank sizes, the layers' switches, and address + version counter of the
+        parameters the derived weight copies and constants are built from (``load_state_dict``, in-place updates and
+        ``.to()`` all move one of the two).  After writing a parameter through ``.data`` call :meth:`invalidate`."""
+        key = [self.split_routing, self.residual, dtype]
+        for layer, st in zip(self.layers, states):
+            qw, ow = layer.q_proj.weight, layer.o_proj.weight
+            key.append((id(st), st.active_exact, st.active_summary, qw.data_ptr(), qw._version, ow.data_ptr(),
+                        ow._version, layer.theta._version, layer.summary_eta_logit._version,
+                        layer.use_tuned_kernels, layer.fuse_append_into_attention, layer.use_skinny_gemm_kernel))
+        return key
+
+    def invalidate(self) -> None:
+        """Drop the captured step (the next :meth:`step_graph` captures again)."""
+        self._graph = None
 
     def _shared_rope(self, states, dtype) -> bool:
         """Do all layers rotate by the same angles at the same position (same head_dim, frequencies, angle dtype
@@ -139,11 +170,22 @@ class CoDAStack(nn.Module):
     def step_graph(self, x: torch.Tensor, states) -> torch.Tensor:
         """Replay the captured step on ``x`` (captures on first use).  Returns the stack's static output
         buffer, which the next replay overwrites."""
-        if self._graph is None or self._graph[4] != [id(s) for s in states]:
+        G = self._graph
+        if G is not None:
+            # Ring scalars are baked at capture time and advanced by the graph's own device counter, so a write that
+            # did not go through a replay (an eager step or prefill on one of the layers, a restored state) makes
+            # the graph stale; so does any rebuilt weight copy or constant.  Either way: capture again.
+            if (len(G["states"]) != len(states) or any(a is not b for a, b in zip(G["states"], states))
+                    or G["expect"] != [(st.pos, st.recent_idx, st.recent_filled) for st in states]
+                    or G["key"] != self._graph_key(states, x.dtype)
+                    or x.shape != G["x"].shape or x.dtype != G["x"].dtype):
+                G = None
+        if G is None:
             self.capture_step(states, x)
-        g, x_static, out_static = self._graph[:3]
-        x_static.copy_(x, non_blocking=True)
-        g.replay()
+            G = self._graph
+        G["x"].copy_(x, non_blocking=True)
+        G["graph"].replay()
         for layer, st in zip(self.layers, states):
             layer.advance_host_scalars(st)
-        return out_static
+        G["expect"] = [(st.pos, st.recent_idx, st.recent_filled) for st in states]
+        return G["out"]

@@ -1,0 +1,225 @@
+"""GPU: state invariants, edge configurations and determinism of the CUDA module, restating what upstream's own
+suite asserts of its PyTorch module (tests/test_invariants.py, tests/test_edge_configs.py:111-240,
+tests/test_correctness.py:332-424, tests/test_determinism.py:150-275 of the upstream project), on small fp32 shapes."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+D, H, HKV, W, ME, MS = 128, 4, 2, 32, 16, 16
+
+
+def _module(**over):
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    kw = dict(embed_dim=D, num_heads=H, num_kv_heads=HKV, window=W, num_landmarks_exact=ME, num_landmarks_summary=MS)
+    kw.update(over)
+    return CoDAGQALandmarkPerf2(**kw).eval().cuda()
+
+
+def _fresh(batch=1, seed=0, **over):
+    torch.manual_seed(seed)
+    m = _module(**over)
+    return m, m.init_state(batch_size=batch, device="cuda", dtype=torch.float32)
+
+
+def _x(b, n, d=D):
+    return torch.randn(b, n, d, device="cuda")
+
+
+def _feed(m, st, pattern, batch=1):
+    """pattern: list of ("p", tokens, block) prefill calls and ("d", steps) decode runs; yields the state after each
+    single call so that per-call properties can be asserted."""
+    for op in pattern:
+        if op[0] == "p":
+            _, st = m.prefill_chunked(_x(batch, op[1], m.embed_dim), st, block_size=op[2], return_outputs=False)
+            yield st
+        else:
+            for _ in range(op[1]):
+                _, st = m.step(_x(batch, 1, m.embed_dim), st)
+                yield st
+
+
+@pytest.mark.parametrize("pattern", [
+    [("p", 100, 64), ("d", 50)],
+    [("d", 70), ("p", 45, 16), ("d", 40), ("p", 3, 8), ("d", 5)],
+    [("p", 1, 64), ("p", 31, 7), ("p", 1, 1), ("d", 3), ("p", 200, 64)],
+])
+def test_ring_scalars_follow_the_token_count(pattern):
+    """pos counts every written token; recent_filled == min(pos, W); recent_idx stays inside the ring, is 0 after a
+    prefill call and walks one slot per decode step once the ring is full; the ring part of `allowed` covers exactly
+    the filled slots."""
+    m, st = _fresh(batch=2)
+    seen, prev_idx = 0, 0
+    ops = [o for op in pattern for o in ([op] if op[0] == "p" else [("d", 1)] * op[1])]
+    for op, st in zip(ops, _feed(m, st, pattern, batch=2)):
+        was_full = seen >= W
+        seen += op[1]
+        assert st.pos == seen and st.recent_filled == min(seen, W) and 0 <= st.recent_idx < W
+        if op[0] == "p":
+            assert st.recent_idx == 0
+        else:
+            assert st.recent_idx == ((prev_idx + 1) % W if was_full else prev_idx)
+        prev_idx = st.recent_idx
+        ring = st.allowed[:, :W]
+        assert int(ring.sum()) == 2 * min(seen, W)
+        if seen < W:
+            assert bool(ring[:, :seen].all()) and not bool(ring[:, seen:].any())
+
+
+def test_bank_occupancy_only_grows_and_is_bounded():
+    """Bank slots are never released: the allowed counts of both banks are non-decreasing over prefill chunks and
+    decode steps; the total never exceeds the buffer, nor the number of tokens seen."""
+    m, st = _fresh(write_policy="none")
+    pe = ps = 0
+    for st in _feed(m, st, [("p", W, W)] * 5 + [("d", 2 * W)]):
+        e, s = int(st.allowed[:, W:W + ME].sum()), int(st.allowed[:, W + ME:].sum())
+        assert e >= pe and s >= ps
+        pe, ps = e, s
+        assert int(st.allowed.sum()) <= min(m.Lbuf, st.pos)
+    assert pe > 0 and ps > 0
+
+
+def test_lru_stamps_and_norm_caches_track_the_banks():
+    """Used exact slots carry the (non-negative) position of the token that last touched them, unused ones keep 0;
+    the two routing caches equal F.normalize of the bank rows they mirror, after block and single-token updates."""
+    m, st = _fresh(batch=2, write_policy="none")
+    for st in _feed(m, st, [("p", 3 * W, 16), ("d", W + 5)], batch=2):
+        pass
+    used = st.allowed[:, W:W + ME]
+    assert bool((st.mem_last_exact[used] >= 0).all()) and bool((st.mem_last_exact[~used] == 0).all())
+    assert bool((st.mem_last_exact < st.pos).all())
+    want_v = F.normalize(st.v_buf[:, :, W:W + ME], dim=-1, eps=1e-6)
+    want_k = F.normalize(st.k_buf[:, :, W + ME:, m.lf_start:], dim=-1, eps=1e-6)
+    assert torch.allclose(st._exact_v_norm, want_v, atol=1e-5)
+    assert torch.allclose(st._sum_lf_k_norm, want_k, atol=1e-5)
+
+
+def test_summary_keys_keep_a_zero_high_frequency_band():
+    """Only the low-frequency half of a summary key is ever blended; the other half stays exactly zero."""
+    m, st = _fresh(seed=1)
+    lo = W + ME
+    assert float(st.k_buf[:, :, lo:, :m.lf_start].abs().max()) == 0.0
+    for st in _feed(m, st, [("p", 512, 128), ("d", 40)]):
+        pass
+    assert bool(st.allowed[:, lo:].any())
+    assert float(st.k_buf[:, :, lo:, :m.lf_start].abs().max()) == 0.0
+
+
+def test_block_queries_see_the_whole_prefix():
+    """Prefill attention is prefix-visible + causal inside the block (not upper-left triangular): the first query
+    of a block reacts to a change of the LAST valid prefix slot."""
+    from coda_gqa_l_b200 import _deep_copy_state
+    m, st = _fresh(seed=2)
+    _, st = m.prefill_chunked(_x(1, W), st, block_size=W, return_outputs=False)
+    xb = _x(1, 32)
+    y0, _ = m.prefill_chunked(xb, st, block_size=32, write_cache=False)
+    bad = _deep_copy_state(st)
+    last = int(bad.allowed[0].nonzero()[-1])
+    bad.k_buf[:, :, last, :] += 100.0
+    y1, _ = m.prefill_chunked(xb, bad, block_size=32, write_cache=False)
+    assert float((y0[:, 0] - y1[:, 0]).abs().max()) > 0.01
+    # ... and no query reacts to a later token of its own block
+    xc = xb.clone()
+    xc[:, 20:] += 3.0
+    y2, _ = m.prefill_chunked(xc, st, block_size=32, write_cache=False)
+    assert torch.equal(y0[:, :20], y2[:, :20]) and not torch.equal(y0[:, 20:], y2[:, 20:])
+
+
+@pytest.mark.parametrize("over,prefill,steps,block", [
+    (dict(num_landmarks_exact=0), 100, 20, 32),
+    (dict(num_landmarks_summary=0), 100, 20, 32),
+    (dict(num_landmarks_exact=0, num_landmarks_summary=0), 100, 20, 32),
+    (dict(window=4), 40, 20, 16),
+    (dict(window=1), 20, 10, 8),
+    (dict(write_policy="none"), 100, 20, 32),
+    (dict(exact_refresh_on_hit=True), 100, 20, 32),
+    (dict(summary_overwrite_on_insert=False), 100, 20, 32),
+    (dict(mem_init="zeros"), 100, 20, 32),
+    (dict(mask_unused_memory=False), 100, 20, 32),
+    (dict(window=64), 1, 3, 256),                 # a single prefill token
+    (dict(), W, 5, 256),                          # exactly one window: nothing evicted yet
+    (dict(), W + 1, 5, 256),                      # exactly one token evicted
+    (dict(window=64), 64, 0, 1024),               # block larger than the sequence
+])
+def test_edge_configurations_run_clean(over, prefill, steps, block):
+    """Zero-sized banks, tiny windows, policy switches and eviction-boundary lengths: right shapes, finite values,
+    position advanced by exactly the tokens fed; zero-sized banks carry no routing cache."""
+    m, st = _fresh(batch=2, seed=3, **over)
+    assert st.k_buf.shape == (2, HKV, m.Lbuf, D // H) and st.allowed.shape == (2, m.Lbuf)
+    assert st.g_recent.shape == (2, m.window) and st.mem_last_exact.shape == (2, m.Me)
+    assert (st._exact_v_norm is None) == (m.Me == 0) and (st._sum_lf_k_norm is None) == (m.Ms == 0)
+    y, st = m.prefill_chunked(_x(2, prefill), st, block_size=block)
+    assert y.shape == (2, prefill, D) and bool(torch.isfinite(y).all()) and st.pos == prefill
+    for i in range(steps):
+        y, st = m.step(_x(2, 1), st)
+        assert y.shape == (2, 1, D) and bool(torch.isfinite(y).all())
+    assert st.pos == prefill + steps and y.dtype == torch.float32
+    none, st2 = m.prefill_chunked(_x(2, 9), st, block_size=4, write_cache=False, return_outputs=False)
+    assert none is None and st2.pos == prefill + steps
+
+
+def test_same_seeds_same_bits_different_seeds_differ():
+    """Two runs from the same seeds agree bit for bit in outputs and state (prefill with evictions, then decode);
+    another input seed gives different outputs."""
+    def run(model_seed, input_seed):
+        torch.manual_seed(model_seed)
+        m = _module()
+        torch.manual_seed(99)
+        st = m.init_state(batch_size=2, device="cuda", dtype=torch.float32)
+        g = torch.Generator(device="cuda").manual_seed(input_seed)
+        x = torch.randn(2, 200 + 64, D, device="cuda", generator=g)
+        y, st = m.prefill_chunked(x[:, :200], st, block_size=64)
+        ys = [y] + [m.step(x[:, t:t + 1], st)[0] for t in range(200, 264)]
+        return torch.cat(ys, 1), st
+    ya, sa = run(42, 7)
+    yb, sb = run(42, 7)
+    assert torch.equal(ya, yb)
+    for f in ("k_buf", "v_buf", "allowed", "g_recent", "mem_last_exact", "_exact_v_norm", "_sum_lf_k_norm"):
+        assert torch.equal(getattr(sa, f), getattr(sb, f)), f
+    yc, _ = run(42, 8)
+    assert not torch.equal(ya, yc)
+
+
+def test_captured_step_notices_writes_made_outside_it():
+    """A captured stack step bakes the ring scalars in and advances them with its own device counter.  An eager
+    step (or prefill) between two replays moves the state without that counter: the next replay must capture
+    again instead of overwriting the wrong ring slot.  Checked against running everything eagerly."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack, _deep_copy_state
+    kw = dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=8, num_landmarks_summary=8)
+    layers = []
+    for i in range(2):
+        torch.manual_seed(i)
+        layers.append(CoDAGQALandmarkPerf2(**kw).eval().to(torch.bfloat16).cuda())
+    stack = CoDAStack(layers)
+    torch.manual_seed(5)
+    sa = stack.init_states(batch_size=3, device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(3, 120, 256, device="cuda") * 0.5).to(torch.bfloat16)
+    stack.prefill(x[:, :40], sa, block_size=16)
+    sb = [_deep_copy_state(s) for s in sa]
+    ya, yb = [], []
+    for t in range(40, 100):
+        kind = "eager" if t % 7 == 3 else ("layer" if t % 11 == 5 else "graph")
+        if kind == "graph":
+            ya.append(stack.step_graph(x[:, t:t + 1], sa).clone())
+        elif kind == "eager":
+            ya.append(stack.step(x[:, t:t + 1], sa))
+        else:                                   # a write through the layers themselves, behind the stack's back
+            h = x[:, t:t + 1]
+            for l, s in zip(stack.layers, sa):
+                h = h + l.step(h, s)[0]
+            ya.append(h)
+        yb.append(stack.step(x[:, t:t + 1], sb))
+    for a, b in zip(sa, sb):
+        assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
+        assert torch.equal(a.allowed, b.allowed) and torch.equal(a.mem_last_exact, b.mem_last_exact)
+    ea = (torch.cat(ya, 1).double() - torch.cat(yb, 1).double()).norm() / torch.cat(yb, 1).double().norm()
+    assert float(ea) < 2e-2
+    # a reloaded weight is noticed too
+    sd = {k: v.clone() for k, v in stack.layers[0].state_dict().items()}
+    sd["theta"] = sd["theta"] * 0.5
+    stack.step_graph(x[:, 100:101], sa)
+    g0 = stack._graph["graph"]
+    stack.layers[0].load_state_dict(sd)
+    stack.step_graph(x[:, 101:102], sa)
+    assert stack._graph["graph"] is not g0

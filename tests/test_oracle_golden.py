@@ -48,3 +48,38 @@ def test_known_answer_c1_slots():
     assert first[2][0].tolist() == [44, 41, 42, 43, 46, 47, 40, 45]
     assert ev[1][1][0].tolist()[:2] == [416, 447]
     assert sorted(ev[1][2][0].tolist()) == [30, 35, 36, 37, 38, 39, 48, 49]
+
+
+@pytest.mark.parametrize("name", ["c2_stack2", "c3_layer"])
+def test_oracle_matches_geometry_fixture(name):
+    """The benchmark-geometry fixtures (bf16, stacks chained as h <- h + layer(h)) re-derived by the oracle from
+    seeds: outputs within the bf16 tolerance of upstream's, ring scalars exact."""
+    from tests.scenarios import GEOMETRY_SCENARIOS
+    from tests.test_geometry_gpu import _build
+    sc = GEOMETRY_SCENARIOS[name]
+    dtype = getattr(torch, sc["dtype"])
+    gold = load_golden(name)
+    mods, sts = _build(sc, dtype)
+    nl = len(mods)
+    wts = [weights_of(m) for m in mods]
+    cfgs = [orc.OracleConfig.from_module(m) for m in mods]
+    for w, want in zip(wts, gold["weights_abs_sum"]):
+        assert abs(weights_checksum(w) - want) <= 1e-9 * want
+    osts = [oracle_state_from(s) for s in sts]
+    x_pre, x_dec = build_inputs(sc, dtype)
+    ts, fs = gold["y_stride"], gold.get("y_fstride", 1)
+
+    def through(fn, h):
+        for c, w, o in zip(cfgs, wts, osts):
+            y = fn(c, w, h, o)
+            h = h + y if nl > 1 else y
+        return h
+
+    for i, phase in enumerate(sc["phases"]):
+        if phase[0] == "prefill":
+            y = through(lambda c, w, h, o: orc.prefill_chunked(c, w, h, o, block_size=phase[3]), x_pre[:, phase[1]:phase[2]])
+        else:
+            y = torch.cat([through(orc.step, x_dec[:, t:t + 1]) for t in range(phase[1], phase[2])], 1)
+        assert rel_err(y[:, ::ts, ::fs], gold["y"][i]) < 3e-2
+        for o, snap in zip(osts, gold["snapshots"][i]):
+            assert (o.recent_idx, o.recent_filled, o.pos) == (snap["recent_idx"], snap["recent_filled"], snap["pos"])
