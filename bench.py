@@ -1,39 +1,47 @@
 """Benchmark of the bounded-cache differential-attention path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference-gpu] [--workload NAME]
 
-Workload (BASELINE config 4, the one the headline metric is quoted on): Mistral-7B attention shape, 32
+Default workload (BASELINE config 4, the one the headline metric is quoted on): Mistral-7B attention shape, 32
 stacked layers, embed 4096, 32 query heads / 8 KV heads, head_dim 128, RoPE base 1e6, W=256 / Me=64 / Ms=64,
 bf16, random-init weights, 32 independent sequence states per GPU (256 over 8 GPUs, weak scaling), seeded
 4096-centroid Gaussian-mixture hidden states (sigma 0.5).  A "step" is one decode token for every state
 through all layers.  Prints ONE JSON line (rank 0).
+
+``--impl reference`` times the reference's own PyTorch implementation of the same step on the host cores (the
+unmodified upstream package from oracle/_ref when present, else this repository's CPU restatement of it);
+``--impl reference-gpu`` runs that same upstream eager code on cuda:0 as a second reference line.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for _p in (ROOT, os.path.join(ROOT, "coda-gqa-l_b200")):
-    if _p not in sys.path:
-        sys.path.insert(0, _p)
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
 WORKLOADS = {
-    # name: (layers, D, H, Hkv, W, Me, Ms, states per GPU, prefill block, mixture centroids, sigma, rope base)
+    # layers, embed, heads, KV heads, window / exact / summary slots, states per GPU, prefill block, mixture centroids, sigma
     "c4_mistral7b": dict(layers=32, D=4096, H=32, Hkv=8, W=256, Me=64, Ms=64, B=32, block=128, K=4096, sigma=0.5,
                          rope_base=1e6, head_norm_mode="identity", rope_interleaved=False),
     "c2_smollm135m": dict(layers=30, D=576, H=9, Hkv=3, W=128, Me=32, Ms=32, B=512, block=128, K=1024, sigma=0.3,
                           rope_base=1e4, head_norm_mode="identity", rope_interleaved=False),
     "c3_medium": dict(layers=1, D=512, H=8, Hkv=2, W=256, Me=64, Ms=64, B=8, block=256, K=512, sigma=0.3,
                       rope_base=1e4, head_norm_mode="full", rope_interleaved=True),
+    "c5_70b": dict(layers=80, D=8192, H=64, Hkv=8, W=512, Me=128, Ms=128, B=64, block=256, K=8192, sigma=0.5,
+                   rope_base=1e6, head_norm_mode="identity", rope_interleaved=False),
 }
+METRIC = "decode tokens/s, bounded attention stack"
 
 
 def decode_bytes_per_state_layer(w) -> int:
@@ -42,6 +50,12 @@ def decode_bytes_per_state_layer(w) -> int:
     Dh = w["D"] // w["H"]
     Lbuf, e = w["W"] + w["Me"] + w["Ms"], 2
     return 2 * w["Hkv"] * Lbuf * Dh * e + 2 * w["H"] * Dh * e + 6 * w["Hkv"] * Dh * e + 4 * w["H"] + Lbuf
+
+
+def weight_bytes_per_layer(w) -> int:
+    """bf16 bytes of the projection weights one decode step streams per layer: [q|k|v|lambda|gate] and o_proj."""
+    Dh = w["D"] // w["H"]
+    return 2 * (w["D"] * (w["H"] * Dh + 2 * w["Hkv"] * Dh + w["H"] + 1) + w["H"] * Dh * w["D"])
 
 
 def prefill_flops_per_state_layer_block(w) -> float:
@@ -57,11 +71,27 @@ def layer_kwargs(w):
                 head_norm_mode=w["head_norm_mode"], rope_interleaved=w["rope_interleaved"])
 
 
-def mixture_on_device(B, L, D, centroids, sigma, seed, device, dtype):
+def mixture(B, L, D, centroids, sigma, seed, device, dtype):
     g = torch.Generator(device=device).manual_seed(seed)
     cent = torch.randn(centroids, D, generator=g, device=device)
     ids = torch.randint(0, centroids, (B, L), generator=g, device=device)
     return (cent[ids] + sigma * torch.randn(B, L, D, generator=g, device=device)).to(dtype)
+
+
+def profiled_traffic(workload: str, variant: str):
+    """(DRAM bytes per launch, states of that capture) of the decode attention kernel from the ncu summaries kept
+    beside this file: a line ``bench-traffic: <workload> <variant> dram_bytes_per_launch=<N> states=<B>``."""
+    folder = os.path.join(ROOT, "profiles")
+    pat = re.compile(r"bench-traffic:\s*(\S+)\s+(\S+)\s+dram_bytes_per_launch=(\d+)\s+states=(\d+)")
+    try:
+        for name in sorted(os.listdir(folder)):
+            if name.endswith((".md", ".txt")):
+                for m in pat.finditer(open(os.path.join(folder, name)).read()):
+                    if m.group(1) == workload and m.group(2) == variant:
+                        return int(m.group(3)), int(m.group(4))
+    except OSError:
+        pass
+    return None
 
 
 class ClockSampler:
@@ -103,38 +133,106 @@ class ClockSampler:
                 "samples": len(self.rows)}
 
 
-def cpu_decode_baseline(w, budget_s: float, threads: int, seed: int = 0):
-    """The CPU oracle (restatement of the reference's PyTorch path) timed on the host: a bounded sample of the
-    same workload -- `B` states, a couple of layers, a few decode steps after a short prefill -- scaled to
-    tokens/s of the full stack (tokens/s = B*steps / (t * layers_full / layers_sampled))."""
-    from oracle import coda_oracle as orc
-    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+# ------------------------------------------------------------------------------------------------ reference arm
+def reference_decode(w, steps: int, warmup: int, device: str, threads: int, sample_layers: int, budget_s: float = None):
+    """The reference's PyTorch implementation of the decode step, timed on ``device``.
+
+    Runs ``sample_layers`` independent layers (chained h <- h + layer(h), default seeded weights) of the workload's
+    shape at the workload's states-per-GPU, warmed by a prefill that fills every ring, for ``steps`` decode tokens
+    after ``warmup`` untimed ones.  Tokens/s of the full stack = states / (seconds per sampled step x layers /
+    sample_layers): every layer of the stack has the same shape and cost.  With ``budget_s`` the step count is cut so
+    that the timed region stays near that many seconds.  Nothing of this repository's package is imported."""
+    from oracle import build_ref
     torch.set_num_threads(threads)
     dtype = torch.bfloat16
-    B = min(w["B"], 8)
-    n_layers = 1
-    torch.manual_seed(seed)
-    mod = CoDAGQALandmarkPerf2(**layer_kwargs(w)).eval().to(dtype)
-    wts = {k: v.detach() for k, v in mod.state_dict().items()}
-    cfg = orc.OracleConfig.from_module(mod)
-    torch.manual_seed(seed + 1)
-    st = orc.init_state(cfg, B, dtype)
-    x = orc.mixture_inputs(B, w["W"] + w["block"] + 64, w["D"], centroids=min(w["K"], 256), sigma=w["sigma"],
-                           seed=seed + 2, dtype=dtype)
+    dev = torch.device(device)
+    B, D, nl = w["B"], w["D"], sample_layers
+    kind = "reference" if build_ref.available() else "port"
+    layers, states = [], []
+    if kind == "reference":
+        Ref = build_ref.load()
+        for i in range(nl):
+            torch.manual_seed(1000 + i)
+            m = Ref(**layer_kwargs(w)).eval().to(dtype).to(dev)
+            torch.manual_seed(7 + i)
+            layers.append(m)
+            states.append(m.init_state(batch_size=B, device=dev, dtype=dtype))
+
+        def prefill(x):
+            for i, m in enumerate(layers):
+                y, states[i] = m.prefill_chunked(x, states[i], block_size=w["block"])
+                x = x + y
+
+        def step(x):
+            for i, m in enumerate(layers):
+                y, states[i] = m.step(x, states[i])
+                x = x + y
+            return x
+    else:
+        from oracle import coda_oracle as orc
+        from oracle.coda_oracle import OracleConfig
+        import math
+        cfgs, wts = [], []
+        for i in range(nl):
+            # the module's default initialisation (upstream attention.py:189-234) restated with plain tensors
+            torch.manual_seed(1000 + i)
+            H, Hkv, Dh = w["H"], w["Hkv"], D // w["H"]
+            lin = lambda o, n: (torch.rand(o, n) * 2 - 1) / math.sqrt(n)          # noqa: E731
+            sd = {"q_proj.weight": lin(H * Dh, D), "k_proj.weight": lin(Hkv * Dh, D), "v_proj.weight": lin(Hkv * Dh, D),
+                  "theta": torch.full((H, Dh // 2), math.pi / 2), "lambda_proj.weight": lin(H, D),
+                  "lambda_proj.bias": torch.full((H,), -6.0), "write_proj.weight": torch.zeros(1, D),
+                  "write_proj.bias": torch.full((1,), -2.0), "summary_eta_logit": torch.full((Hkv,), -3.0),
+                  "o_proj.weight": lin(D, H * Dh)}
+            if w["head_norm_mode"] == "full":
+                sd["head_norm.weight"] = torch.ones(Dh)
+            wts.append({k: v.to(dtype) for k, v in sd.items()})
+            cfg = OracleConfig(embed_dim=D, num_heads=H, num_kv_heads=Hkv, window=w["W"], num_landmarks_exact=w["Me"],
+                               num_landmarks_summary=w["Ms"], rope_base=w["rope_base"], head_norm_mode=w["head_norm_mode"],
+                               rope_interleaved=w["rope_interleaved"], angle_dtype=dtype)
+            cfgs.append(cfg)
+            torch.manual_seed(7 + i)
+            states.append(orc.init_state(cfg, B, dtype))
+
+        def prefill(x):
+            for c, wt, st in zip(cfgs, wts, states):
+                x = x + orc.prefill_chunked(c, wt, x, st, block_size=w["block"])
+
+        def step(x):
+            for c, wt, st in zip(cfgs, wts, states):
+                x = x + orc.step(c, wt, x, st)
+            return x
+
+    sync = (lambda: torch.cuda.synchronize(dev)) if dev.type == "cuda" else (lambda: None)
+    P = (w["W"] + w["block"] + w["block"] - 1) // w["block"] * w["block"]
+    x_pre = mixture(B, P, D, min(w["K"], 512), w["sigma"], 11, "cpu", dtype).to(dev)
+    x_dec = mixture(B, steps + warmup + 1, D, min(w["K"], 512), w["sigma"], 13, "cpu", dtype).to(dev)
     with torch.no_grad():
-        orc.prefill_chunked(cfg, wts, x[:, :w["W"] + w["block"]], st, block_size=w["block"])   # ring full, banks live
+        prefill(x_pre)                                                        # every ring full, banks live
+        sync()
         t0 = time.perf_counter()
-        orc.step(cfg, wts, x[:, -64:-63], st)                                                 # warm-up + probe
+        step(x_dec[:, :1])
+        sync()
         probe = time.perf_counter() - t0
-        steps = int(max(2, min(62, budget_s / max(probe, 1e-3))))
+        if budget_s is not None:
+            steps = int(max(2, min(steps, budget_s / max(probe, 1e-4))))
+            warmup = min(warmup, 1)
+        t = 1
+        for _ in range(warmup):
+            step(x_dec[:, t:t + 1]); t += 1
+        sync()
         t0 = time.perf_counter()
-        for t in range(steps):
-            orc.step(cfg, wts, x[:, -63 + t:-62 + t], st)
+        for _ in range(steps):
+            step(x_dec[:, t:t + 1]); t += 1
+        sync()
         dt = time.perf_counter() - t0
-    tok_s = B * steps / (dt * w["layers"] / n_layers)
-    return {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"CPU oracle, bf16, {B} states x {n_layers} of {w['layers']} layers x {steps} decode steps after a "
-                      f"{w['W'] + w['block']}-token prefill; scaled by layers"}
+    s_per_step = dt / steps
+    tok_s = B / (s_per_step * w["layers"] / nl)
+    where = f"{threads} host threads" if dev.type == "cpu" else torch.cuda.get_device_name(dev)
+    what = "upstream CoDAGQALandmarkPerf2, PyTorch path, unmodified" if kind == "reference" else "CPU restatement of upstream (oracle)"
+    return {"value": tok_s, "unit": "tokens/s", "cores": threads if dev.type == "cpu" else 0, "kind": kind,
+            "sample": f"{what}, bf16, on {where}: {B} states x {nl} of {w['layers']} layers x {steps} decode steps after a "
+                      f"{P}-token prefill; tokens/s scaled to the full stack by layers ({w['layers']}/{nl})",
+            "steps": steps, "sample_layers": nl, "seconds_per_sampled_step": s_per_step, "seconds_timed": dt}
 
 
 def workload_config(args, w, world):
@@ -150,20 +248,40 @@ def workload_config(args, w, world):
             "warm_state": f"{2 * P}-token prefill in blocks of {w['block']}"}
 
 
+def reference_main(args, w, K, Wm, rank):
+    """`--impl reference` (host cores) / `--impl reference-gpu` (upstream eager on cuda:0).  Rank 0 alone runs."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    if args.impl == "reference":
+        r = reference_decode(w, K, Wm, "cpu", cores, sample_layers=1)
+    else:
+        r = reference_decode(w, K, Wm, "cuda:0", cores, sample_layers=w["layers"])
+    # ms_per_step is the MEASURED time of one sampled step (steps x ms_per_step = the timed region); `value` scales
+    # it to the full stack as stated in cpu_baseline.sample
+    print(json.dumps({
+        "impl": args.impl, "metric": METRIC, "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": r["steps"],
+        "warmup": Wm, "ms_per_step": 1e3 * r["seconds_per_sampled_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, w, max(1, args.gpus)),
+        "cpu_baseline": r, "ms_per_full_stack_step": 1e3 * r["seconds_per_sampled_step"] * w["layers"] / r["sample_layers"],
+        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ------------------------------------------------------------------------------------------------------ our arm
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--workload", default="c4_mistral7b", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (profiling small cases)")
-    ap.add_argument("--states", type=int, default=None, help="override states per GPU (profiling small cases)")
+    ap.add_argument("--states", type=int, default=None, help="override states per GPU")
     ap.add_argument("--prefill-tokens", type=int, default=512)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replay")
     ap.add_argument("--no-split-routing", action="store_true",
-                    help="route the evicted tokens inside each layer's chain instead of on a second graph branch")
+                    help="route the evicted tokens inside each layer's chain instead of in one launch per step")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.layers:
@@ -177,22 +295,16 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     cores = os.cpu_count() or 1
 
-    if args.impl == "reference":
-        # The reference's own (CPU, PyTorch) implementation of the path; rank 0 alone runs it.
-        if rank != 0:
-            return
-        cb = cpu_decode_baseline(w, budget_s=20.0 * K / 64, threads=cores)
-        print(json.dumps({
-            "impl": "reference", "metric": "decode tokens/s, 7B-shape bounded attention stack", "value": cb["value"],
-            "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": Wm, "ms_per_step": 1e3 * w["B"] / cb["value"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(args, w, max(1, args.gpus)),
-            "cpu_baseline": cb,
-            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+    if args.impl != "ours":
+        reference_main(args, w, K, Wm, rank)
         return
 
+    pkg = os.path.join(ROOT, "coda-gqa-l_b200")
+    if pkg not in sys.path:
+        sys.path.insert(0, pkg)
     import torch.distributed as dist
     from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack
+    from coda_gqa_l_b200._lib import RingPos, check, lib
     from coda_gqa_l_b200.sharding import max_over_ranks
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -218,8 +330,8 @@ def main():
     states = stack.init_states(batch_size=B, device=dev, dtype=dtype)
     P = max(args.prefill_tokens, w["W"] + w["block"])
     P = (P + w["block"] - 1) // w["block"] * w["block"]
-    x_pre = mixture_on_device(B, 2 * P, D, w["K"], w["sigma"], 11 + rank, dev, dtype)
-    x_dec = mixture_on_device(B, 2 * (K + Wm) + 8, D, w["K"], w["sigma"], 13 + rank, dev, dtype)
+    x_pre = mixture(B, 2 * P, D, w["K"], w["sigma"], 11 + rank, dev, dtype)
+    x_dec = mixture(B, 2 * (K + Wm) + 8, D, w["K"], w["sigma"], 13 + rank, dev, dtype)
     x_dec_host = x_dec.cpu().pin_memory()
 
     # ---- prefill (brings every ring to steady state); timed as a secondary figure ----
@@ -238,6 +350,7 @@ def main():
     pre_kernel_ms = sum(att_ms) / max(1, len(att_ms))
     for l in stack.layers:
         l.kernel_timers = None
+    del x_pre
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -280,74 +393,120 @@ def main():
     ms_e2e = max_over_ranks(e0.elapsed_time(e1), dev)
     e2e_tok_s = world * B * K / (ms_e2e * 1e-3)
 
-    # ---- roofline of the dominant kernel (decode attention) ----
-    # One CUDA graph holding one attention launch per layer (each on its own layer's state, so consecutive
-    # launches never find their planes in L2 once layers * bytes_per_launch exceeds it), replayed and timed
-    # with events on the launching stream; per-launch time = elapsed / launches.
-    from coda_gqa_l_b200._lib import RingPos
+    # ---- roofline of the dominant kernel: the decode attention AS THE TIMED STEP RUNS IT ----
+    # The captured step launches decode_attend_kernel<Dh, NQ, true> (coda_b200_decode_attend_append: the attention that
+    # also writes the step's new token).  Timed here as one CUDA graph holding one such launch per layer, each on its
+    # own layer's state (so no launch finds its planes in L2 once layers x bytes-per-launch exceeds it), replayed and
+    # timed with events on the launching stream; re-writing the same token at the same ring position is idempotent.
+    # The variant without the token write (records prepared beforehand) and the step's batched routing launch are
+    # timed the same way for the secondary figures.  This section runs last: it leaves the states as they are.
     roof_stream = torch.cuda.Stream(dev)
-    dt = dtype
     H_, Dh_ = w["H"], D // w["H"]
-    q_fix = torch.randn(B, H_ * Dh_, device=dev, dtype=dt)
-    lam_fix = torch.randn(B, H_, device=dev, dtype=dt)
-    outs = [torch.empty(B, 1, H_ * Dh_, device=dev, dtype=dt) for _ in stack.layers]
+    x_fix = mixture(B, 1, D, w["K"], w["sigma"], 17, dev, dtype)
+    q_fix = torch.randn(B, H_ * Dh_, device=dev, dtype=dtype)
+    lam_fix = torch.randn(B, H_, device=dev, dtype=dtype)
+    outs = [torch.empty(B, 1, H_ * Dh_, device=dev, dtype=dtype) for _ in stack.layers]
     reps = max(1, -(-8 // len(stack.layers)))            # layer sweeps per replay (>= 8 launches per graph)
-    def launch_all(prepare=False):
-        for _ in range(1 if prepare else reps):
-            for l, st, o in zip(stack.layers, states, outs):
-                cfg = l._cfg(B, dt, st)
-                if prepare:          # decode records (prepared queries + mask) of this layer's state, once
-                    rp = RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None)
-                    l.decode_attend_launch(cfg, st, rp, 1, q_fix, lam_fix, o)
-                else:                # the attention kernel alone
-                    l.decode_attend_prepared_launch(cfg, st, o)
+    cfgs = [l._cfg(B, dtype, st) for l, st in zip(stack.layers, states)]
+    rps = [RingPos(int(st.pos), int(st.recent_idx), int(st.recent_filled), None) for st in states]
+    append_ok = all(bool(lib.coda_b200_decode_attend_append_supported(C.byref(c))) and l._fused_write_ok(c)
+                    for l, c in zip(stack.layers, cfgs))
+
+    def timed_graph(body, nrep=10):
+        """Mean ms per call of `body` from `nrep` replays of a graph holding `reps` calls."""
+        with torch.cuda.stream(roof_stream):
+            body()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=roof_stream):
+                for _ in range(reps):
+                    body()
+            for _ in range(3):
+                g.replay()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record(roof_stream)
+            for _ in range(nrep):
+                g.replay()
+            r1.record(roof_stream)
+        roof_stream.synchronize()
+        return r0.elapsed_time(r1) / (nrep * reps)
+
     roof_stream.wait_stream(torch.cuda.current_stream(dev))
     with torch.cuda.stream(roof_stream):
-        launch_all(prepare=True)
-        launch_all()
-        roof_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(roof_graph, stream=roof_stream):
-            launch_all()
-        for _ in range(3):
-            roof_graph.replay()
-        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        nrep = 10
-        r0.record(roof_stream)
-        for _ in range(nrep):
-            roof_graph.replay()
-        r1.record(roof_stream)
+        projs = [l._project(x_fix, need_kv=True) for l in stack.layers]          # raw projections of one token per layer
+        for l, st, c, rp, o in zip(stack.layers, states, cfgs, rps, outs):      # decode records for the prepared variant
+            l.decode_attend_launch(c, st, rp, 1, q_fix, lam_fix, o)
     roof_stream.synchronize()
-    kern_ms = r0.elapsed_time(r1) / (nrep * reps * len(stack.layers))
+
+    def sweep_prepared():
+        for l, st, c, o in zip(stack.layers, states, cfgs, outs):
+            l.decode_attend_prepared_launch(c, st, o)
+
+    def sweep_append():
+        for l, st, c, rp, pr, o in zip(stack.layers, states, cfgs, rps, projs, outs):
+            l.decode_attend_append_launch(c, st, rp, pr, o)
+
+    nl = len(stack.layers)
+    prepared_ms = timed_graph(sweep_prepared) / nl
+    append_ms = timed_graph(sweep_append) / nl if append_ok else None
+    route_ms = None
+    plan = stack._route_plan(states, rps, dtype) if append_ok else None
+    if plan is not None:
+        def route_all():
+            check(lib.coda_b200_step_route_batched(C.byref(plan[0]), plan[1].data_ptr(), nl, roof_stream.cuda_stream),
+                  "coda_b200_step_route_batched")
+        route_ms = timed_graph(route_all)
     for l in stack.layers:
         if l.device_status() != 0:
-            raise RuntimeError("decode attention reported an expired device-side wait")
+            raise RuntimeError("a tuned kernel reported an expired device-side wait")
     bytes_launch = decode_bytes_per_state_layer(w) * B
+    kern_ms = append_ms if append_ms is not None else prepared_ms
+    variant = "append" if append_ms is not None else "prepared"
     achieved = bytes_launch / (kern_ms * 1e-3) / 1e9
+    prof = profiled_traffic(args.workload, variant)
+    step_bytes = w["layers"] * (bytes_launch + weight_bytes_per_layer(w))
+    roofline = {
+        "kernel": (f"decode_attend_kernel<{Dh_},*,true> (coda_b200_decode_attend_append: attention + the new token's write, "
+                   "the launch the timed step makes)" if variant == "append" else
+                   f"decode_attend_kernel<{Dh_},*,false> (coda_b200_decode_attend_prepared)"),
+        "timing": "graph of back-to-back launches over all layers' states, CUDA events on the launching stream",
+        "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "of": peak_src,
+        "frac_of_nominal_8000": achieved / 8000.0, "kernel_ms": kern_ms, "bytes_per_launch": bytes_launch,
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch of this variant from the ncu capture kept beside this
+        # file, scaled by the states processed (traffic grows with the planes streamed)
+        "traffic": None if prof is None else int(round(prof[0] * B / prof[1])),
+        "prepared_variant": {"kernel_ms": prepared_ms, "achieved": bytes_launch / (prepared_ms * 1e-3) / 1e9,
+                             "frac": bytes_launch / (prepared_ms * 1e-3) / 1e9 / hbm_peak},
+        # attention + new-token write + this layer's share of the step's routing launch, same algorithmic bytes
+        "with_routing": None if route_ms is None else {
+            "routing_launch_ms": route_ms, "ms_per_layer": kern_ms + route_ms / nl,
+            "achieved": bytes_launch / ((kern_ms + route_ms / nl) * 1e-3) / 1e9,
+            "frac": bytes_launch / ((kern_ms + route_ms / nl) * 1e-3) / 1e9 / hbm_peak},
+        # the whole timed step against HBM: every layer's state traffic plus its projection weights, once per step
+        "whole_step": {"bytes_per_step": step_bytes, "achieved": step_bytes / (ms / K * 1e-3) / 1e9,
+                       "frac": step_bytes / (ms / K * 1e-3) / 1e9 / hbm_peak},
+    }
 
+    per_step_launches = ((2 if args.eager or args.no_split_routing else 1) * w["layers"]
+                         + (0 if args.eager else (1 if args.no_split_routing else 3)))
     line = {
-        "metric": "decode tokens/s, 7B-shape bounded attention stack", "value": tok_s, "unit": "tokens/s",
+        "metric": METRIC, "value": tok_s, "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, w, world),
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": B * D * 2, "d2h_bytes_per_step": B * D * 2,
                 "ms_per_step": ms_e2e / K},
-        # this repository's kernels inside the timed region: per layer the fused cache write and the decode
-        # attention, plus the step-counter kernel of the captured graph (the two GEMMs per layer are library calls)
-        "gpu_launches": K * ((2 if args.eager or args.no_split_routing else 1) * w["layers"] + (0 if args.eager else (1 if args.no_split_routing else 3))),
+        # this repository's kernels inside the timed region: per layer the decode attention (which writes the new
+        # token), per step the batched routing, the cos/sin table and the step counter (the two GEMMs per layer are
+        # library calls)
+        "gpu_launches": K * per_step_launches,
         "clocks": clocks.summary(),
-        "roofline": {"kernel": "decode_attend_kernel (coda_b200_decode_attend_prepared)", "timing": "graph of back-to-back launches over all layers' states, CUDA events", "bound": "hbm", "achieved": achieved,
-                     "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "of": peak_src,
-                     "frac_of_nominal_8000": achieved / 8000.0,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this workload
-                     # (ncu capture summarised under profiles/), scaled by the states processed
-                     "traffic": int(round(51044000 * B / 32)) if args.workload == "c4_mistral7b" else None, "kernel_ms": kern_ms,
-                     "bytes_per_launch": bytes_launch},
+        "roofline": roofline,
         "prefill": {"tokens_per_s": world * pre_tokens / (prefill_ms * 1e-3), "tokens": pre_tokens, "ms": prefill_ms,
                     "attention_kernel_ms_per_block": pre_kernel_ms, "attention_tflops": pre_tf,
                     "tensor_frac": pre_tf / tc_peak, "tensor_peak": tc_peak, "of": peak_src},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_decode_baseline(w, budget_s=15.0, threads=cores)
+        line["cpu_baseline"] = reference_decode(w, 64, 1, "cpu", cores, sample_layers=1, budget_s=15.0)
     # Every rank finishes its own (unsynchronised) roofline section before any rank tears the process group down:
     # a communicator destroyed while a peer still runs kernels took that peer's kernels down with it.
     barrier()

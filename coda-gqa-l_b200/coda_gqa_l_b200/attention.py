@@ -326,9 +326,15 @@ class CoDAGQALandmarkPerf2(nn.Module):
         zero = evf.new_zeros(1)
         fill_e = st.allowed[:, W:W + Me].any(dim=0).float().mean().double().view(1) if do_e else zero
         fill_s = st.allowed[:, W + Me:].any(dim=0).float().mean().double().view(1) if do_s else zero
-        host = torch.cat([evf.sum(dim=0), evf[:, 7].min().view(1), fill_e, fill_s]).tolist()
+        # (the kernels' status word rides along: this read synchronises anyway, so an expired device-side wait
+        # surfaces here instead of going unnoticed)
+        stat = self._status.to(torch.float64) if self._status is not None and self._status.device == evf.device else zero
+        host = torch.cat([evf.sum(dim=0), evf[:, 7].min().view(1), fill_e, fill_s, stat]).tolist()
+        if int(host[-1]) != 0:
+            raise RuntimeError(f"a bounded device-side wait expired in one of the tuned kernels (code {int(host[-1])}): "
+                               "results since the last check are not valid")
         ev = [int(t) for t in host[:_lib.CODA_EVENT_WORDS]]
-        every, fill_e, fill_s = int(host[-3]) == 1, host[-2], host[-1]
+        every, fill_e, fill_s = int(host[-4]) == 1, host[-3], host[-2]
         if do_e:
             if m is not None:
                 if block:
@@ -701,12 +707,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
                 cfg._attend_append = one
             if one and self.fuse_append_into_attention and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0:
                 # the attention kernel writes the new token itself: one launch between the two GEMMs
-                check(lib.coda_b200_decode_attend_append(
-                    C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
-                    _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(),
-                    q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0), cos_t.data_ptr(), sin_t.data_ptr(),
-                    _p(rope_cs), _p(nw), out.data_ptr(), out.stride(0), self._status_word(dev).data_ptr(), s),
-                    "coda_b200_decode_attend_append")
+                self.decode_attend_append_launch(cfg, state, rp, (q, k, v, lam_logit, gate_logit), out, rope_cs)
                 if host_update:
                     self.advance_host_scalars(state)
                 return self._out(out, residual)
@@ -758,6 +759,20 @@ class CoDAGQALandmarkPerf2(nn.Module):
             lam_logit.data_ptr(), lam_logit.stride(0), inv_freq.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
             _p(nw), qrec.data_ptr(), out.data_ptr(), out.stride(0), self._status_word(q.device).data_ptr(), _stream()),
             "coda_b200_decode_attend")
+
+    def decode_attend_append_launch(self, cfg, state, rp: RingPos, proj, out, rope_cs=None) -> None:
+        """One launch of the decode attention kernel that also writes the step's new token (ring slot, gate, slot
+        flag) from the raw projections ``proj = (q, k, v, lambda logits, gate logits)`` of :meth:`_project`; the
+        token the ring evicts must have been routed before (``route_launch`` / the stack's batched routing)."""
+        q, k, v, lam_logit, gate_logit = proj
+        inv_freq, cos_t, sin_t, _, nw = self._consts(out.device, out.dtype)
+        ptrs = self._ptrs(state)
+        check(lib.coda_b200_decode_attend_append(
+            C.byref(cfg), C.byref(ptrs), rp, k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+            _p(gate_logit), 0 if gate_logit is None else gate_logit.stride(0), inv_freq.data_ptr(),
+            q.data_ptr(), q.stride(0), lam_logit.data_ptr(), lam_logit.stride(0), cos_t.data_ptr(), sin_t.data_ptr(),
+            _p(rope_cs), _p(nw), out.data_ptr(), out.stride(0), self._status_word(out.device).data_ptr(), _stream()),
+            "coda_b200_decode_attend_append")
 
     def decode_attend_prepared_launch(self, cfg, state, out) -> None:
         """One launch of the decode attention kernel on the records the last fused cache write left behind."""

@@ -2,6 +2,7 @@
 // selection-order helpers.
 #include "coda_common.cuh"
 #include "topk_order.h"
+#include "tma_utils.cuh"
 #include <stdarg.h>
 #include <vector>
 
@@ -50,6 +51,41 @@ extern "C" int coda_b200_advance_steps(int64_t* step_dev, int64_t n, coda_stream
   CODA_REQUIRE(step_dev, CODA_ERR_ARG, "advance_steps: null counter");
   advance_steps_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((long long*)step_dev, (long long)n);
   CODA_CHECK_LAUNCH("advance_steps");
+  return CODA_OK;
+}
+
+// Self-test of the bounded waits every pipelined kernel here is built on (tma::mbar_wait).  One CTA, two barriers
+// that nobody ever arrives at.  Thread 0 waits on the first with `poll_limit` polls: the wait must give up, record
+// its code in the status word and set the CTA's abort word.  Thread 32 waits on the second with the kernels' full
+// limit: it must leave as soon as it sees the abort word, long before its own limit.  Nothing traps, nothing spins
+// without a bound, and the context stays usable.
+__global__ void selftest_wait_kernel(int poll_limit, int* status, int* report) {
+  __shared__ uint64_t bars[2];
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    tma::mbar_init(&bars[0], 1);
+    tma::mbar_init(&bars[1], 1);
+    tma::fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 || threadIdx.x == 32) {
+    const int who = threadIdx.x / 32;
+    const long long t0 = clock64();
+    const bool ok = tma::mbar_wait(&bars[who], 0, status, 77 + who, &s_abort, who == 0 ? poll_limit : tma::WAIT_LIMIT);
+    const long long dt = clock64() - t0;
+    report[2 * who] = ok ? 1 : 0;
+    report[2 * who + 1] = dt > 0x7fffffffLL ? 0x7fffffff : (int)dt;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) report[4] = s_abort;
+}
+
+extern "C" int coda_b200_selftest_bounded_wait(int32_t poll_limit, int32_t* status, int32_t* report, coda_stream_t stream) {
+  CODA_REQUIRE(status && report, CODA_ERR_ARG, "selftest_bounded_wait: null pointer");
+  CODA_REQUIRE(poll_limit > 0 && poll_limit <= (1 << 16), CODA_ERR_ARG, "selftest_bounded_wait: poll_limit must be in 1..65536");
+  selftest_wait_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(poll_limit, status, report);
+  CODA_CHECK_LAUNCH("selftest_bounded_wait");
   return CODA_OK;
 }
 

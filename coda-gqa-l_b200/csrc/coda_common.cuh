@@ -124,6 +124,39 @@ void coda_set_error(const char* fmt, ...);
 #define CODA_CHECK_LAUNCH(what) do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) { \
   coda_set_error("%s: %s", what, cudaGetErrorString(e__)); return CODA_ERR_LAUNCH; } } while (0)
 
+// ---- per-device launch set-up ------------------------------------------------------------------
+// cudaFuncSetAttribute and the SM count belong to a device, not to the process: a process that drives several
+// GPUs (a model spread over devices, one thread per GPU) repeats them for every device it launches on.
+// `once` is a launcher's own table; returns true exactly once per device for it, holding off concurrent callers
+// on the same table until the first one has finished its set-up (the caller does the set-up while `lock` lives).
+#include <mutex>
+constexpr int CODA_MAX_DEVICES = 64;
+struct coda_device_once {
+  std::mutex mu;
+  bool done[CODA_MAX_DEVICES] = {};
+  int sms[CODA_MAX_DEVICES] = {};
+};
+static inline int coda_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= CODA_MAX_DEVICES) return -1;
+  return dev;
+}
+// Runs `setup` the first time this table sees the current device; returns that device's SM count.
+template <typename F>
+static inline int coda_on_first_use(coda_device_once& once, F&& setup) {
+  const int dev = coda_current_device();
+  std::lock_guard<std::mutex> lock(once.mu);
+  if (dev < 0) { setup(); return 148; }               // unknown ordinal: configure every time
+  if (!once.done[dev]) {
+    setup();
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    once.sms[dev] = n;
+    once.done[dev] = true;
+  }
+  return once.sms[dev];
+}
+
 static inline bool coda_cfg_ok(const coda_layer_cfg* c) {
   return c && c->B > 0 && c->H > 0 && c->Hkv > 0 && c->H % c->Hkv == 0 && c->Dh > 0 && (c->Dh % 2) == 0 &&
          c->W > 0 && c->Me >= 0 && c->Ms >= 0 && (c->dtype == CODA_F32 || c->dtype == CODA_BF16);

@@ -53,7 +53,7 @@ struct DecodeParams {
 };
 
 using tma::smem_u32; using tma::mbar_init; using tma::mbar_expect_tx; using tma::mbar_arrive; using tma::mbar_try;
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) { tma::mbar_wait(bar, parity, status, code); }
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, int* abort) { tma::mbar_wait(bar, parity, status, code, abort); }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
@@ -200,7 +200,10 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   uint64_t* comb_full = q_free + 2;
   uint64_t* comb_free = comb_full + 1;
 
+  __shared__ int s_abort;                          // set by the first bounded wait of this CTA that expires
+  int* const abortw = &s_abort;
   if (tid == 0) {
+    s_abort = 0;
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
     mbar_init(&q_ready[0], APPEND ? DA_AWARPS : 1); mbar_init(&q_ready[1], APPEND ? DA_AWARPS : 1);
     mbar_init(&q_free[0], DA_CWARPS + DA_AWARPS); mbar_init(&q_free[1], DA_CWARPS + DA_AWARPS);
@@ -294,7 +297,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         bool pending = !APPEND && plane + (int)gridDim.x < nplanes;
         for (int s = 0; s < nst; ++s) {
           if (pending && record_free(i + 1)) { load_record(plane + gridDim.x, i + 1); pending = false; }
-          if (round > 0) mbar_wait(&empty[bi], (round - 1) & 1, p.status, 1);
+          if (round > 0) mbar_wait(&empty[bi], (round - 1) & 1, p.status, 1, abortw);
           mbar_expect_tx(&full[bi], 2 * TILE_BYTES);
           unsigned char* kd = stage0 + bi * 2 * TILE_BYTES;
           unsigned char* vd = kd + TILE_BYTES;
@@ -306,7 +309,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
           if (++bi == S) { bi = 0; ++round; }
         }
         if (pending) {
-          mbar_wait(&q_free[(i + 1) & 1], (((i + 1) >> 1) - 1) & 1, p.status, 6);
+          mbar_wait(&q_free[(i + 1) & 1], (((i + 1) >> 1) - 1) & 1, p.status, 6, abortw);
           load_record(plane + gridDim.x, i + 1);
         }
       }
@@ -427,13 +430,13 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         // the NEXT plane's record, while the consumers are on this plane's tiles (its inputs were requested a plane ago)
         const int next = plane + gridDim.x;
         if (next < nplanes) {
-          if (i + 1 >= 2) mbar_wait(&q_free[(i + 1) & 1], (((i + 1) >> 1) - 1) & 1, p.status, 6);
+          if (i + 1 >= 2) mbar_wait(&q_free[(i + 1) & 1], (((i + 1) >> 1) - 1) & 1, p.status, 6, abortw);
           build_record(next, (i + 1) & 1, in);
           if (next + (int)gridDim.x < nplanes) load_inputs(next + gridDim.x, in);
         }
       }
-      mbar_wait(&q_ready[i & 1], (i >> 1) & 1, p.status, 7);   // lambda comes from the plane's record (a bulk copy: observed through its own barrier)
-      mbar_wait(comb_full, i & 1, p.status, 5);
+      mbar_wait(&q_ready[i & 1], (i >> 1) & 1, p.status, 7, abortw);   // lambda comes from the plane's record (a bulk copy: observed through its own barrier)
+      mbar_wait(comb_full, i & 1, p.status, 5, abortw);
       const int b = plane / p.Hkv, hk = plane % p.Hkv;
       const float* sLam = reinterpret_cast<const float*>(rec0 + (i & 1) * L.rec_stride + lam_off);
       const float lam_a = sLam[aw], lam_b = sLam[(aw + DA_AWARPS) & 7];   // heads aw and aw + 4 of the group (G <= 8)
@@ -506,7 +509,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   int i = 0;
   for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
     const int buf = i & 1;
-    mbar_wait(&q_ready[buf], (i >> 1) & 1, p.status, 3);
+    mbar_wait(&q_ready[buf], (i >> 1) & 1, p.status, 3, abortw);
     const unsigned char* rec = rec0 + buf * L.rec_stride;
     const uint8_t* al_s = rec + mask_off;
     // B fragments of Q^T: one ldmatrix.x4 covers two k-steps of one n-tile (matrices: dh chunks 4j .. 4j+3)
@@ -534,7 +537,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     int bi = (i * nst + s0) % S, round = (i * nst + s0) / S;
 
     for (int s = s0; s < nst; s += 2) {
-      mbar_wait(&full[bi], round & 1, p.status, 2);
+      mbar_wait(&full[bi], round & 1, p.status, 2, abortw);
       const uint32_t kb = smem_u32(stage0 + bi * 2 * TILE_BYTES);
       const uint32_t vb = kb + TILE_BYTES;
       if (APPEND) {
@@ -625,7 +628,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         lrun[nq][0] += __shfl_xor_sync(0xffffffffu, lrun[nq][0], o);
         lrun[nq][1] += __shfl_xor_sync(0xffffffffu, lrun[nq][1], o);
       }
-    if (i >= 1) mbar_wait(comb_free, (i - 1) & 1, p.status, 4);
+    if (i >= 1) mbar_wait(comb_free, (i - 1) & 1, p.status, 4, abortw);
     if (lane < 4) {
 #pragma unroll
       for (int nq = 0; nq < NQ; ++nq)
@@ -672,17 +675,10 @@ int launch_decode(const CUtensorMap& km, const CUtensorMap& vm, DecodeParams p, 
   CODA_REQUIRE(stages >= 2, CODA_ERR_LIMIT, "decode_attend: %d slots leave no room for the tile ring in shared memory", p.Lbuf);
   p.stages = stages;
   const size_t smem = (size_t)DecodeSmem<DH>(stages, p.G, p.Lbuf).total + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static coda_device_once once;
+  const int num_sms = coda_on_first_use(once, [] {
     cudaFuncSetAttribute(decode_attend_kernel<DH, NQ, APPEND>, cudaFuncAttributeMaxDynamicSharedMemorySize, BUDGET);
-    configured = true;
-  }
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
-  }
+  });
   const int nplanes = p.B * p.Hkv;
   // Programmatic dependent launch: the CTAs may start (shared-memory carve-up, barrier initialisation) while the
   // kernel before this one on the stream is still finishing; they wait for it (griddepcontrol.wait) before the

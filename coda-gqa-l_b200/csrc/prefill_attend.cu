@@ -216,7 +216,10 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
   const int NB = last_row / PF_BN + 1;                                            // block tiles (causal limit)
   const int NT = NP + NB;
 
+  __shared__ int s_abort;                          // set by the first bounded wait of this CTA that expires
+  int* const abortw = &s_abort;
   if (tid == 0) {
+    s_abort = 0;
     tma::mbar_init(q_full, 1);
     for (int i = 0; i < PF_STAGES; ++i) { tma::mbar_init(&kv_full[i], 1); tma::mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { tma::mbar_init(&s_full[i], 1); tma::mbar_init(&p_full[i], 4); tma::mbar_init(&pv_done[i], 1); }
@@ -245,7 +248,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       }
       for (int j = 0; j < NT; ++j) {
         const int st = j % PF_STAGES;
-        if (j >= PF_STAGES) tma::mbar_wait(&kv_empty[st], ((j / PF_STAGES) - 1) & 1, p.status, 11);
+        if (j >= PF_STAGES) tma::mbar_wait(&kv_empty[st], ((j / PF_STAGES) - 1) & 1, p.status, 11, abortw);
         tma::mbar_expect_tx(&kv_full[st], 2 * KV_BYTES);
         unsigned char* kd = sK + st * KV_BYTES;
         unsigned char* vd = sV + st * KV_BYTES;
@@ -280,18 +283,18 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
         }
         tc_commit(&s_full[s]);
       };
-      tma::mbar_wait(q_full, 0, p.status, 13);
-      tma::mbar_wait(&kv_full[0], 0, p.status, 14);
+      tma::mbar_wait(q_full, 0, p.status, 13, abortw);
+      tma::mbar_wait(&kv_full[0], 0, p.status, 14, abortw);
       tc_fence_after();
       issue_qk(0, 0);
       issue_qk(0, 1);
       for (int j = 0; j < NT; ++j) {
         const int st = j % PF_STAGES;
         const uint32_t vbase = smem_u32(sV + st * KV_BYTES);
-        if (j + 1 < NT) tma::mbar_wait(&kv_full[(j + 1) % PF_STAGES], ((j + 1) / PF_STAGES) & 1, p.status, 14);
+        if (j + 1 < NT) tma::mbar_wait(&kv_full[(j + 1) % PF_STAGES], ((j + 1) / PF_STAGES) & 1, p.status, 14, abortw);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-          tma::mbar_wait(&p_full[s], j & 1, p.status, 12);
+          tma::mbar_wait(&p_full[s], j & 1, p.status, 12, abortw);
           tc_fence_after();
           const uint32_t pcol = tmem + (s ? TM_SN : 0u);          // P (bf16 pairs) sits in the first 64 S columns
           const uint32_t dcol = tmem + (s ? TM_ON : TM_OS);
@@ -338,7 +341,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     float mb = -INFINITY;                                 // exponent base (lags the true max by < GAP)
     float l = 0.f;
     for (int j = 0; j < NT; ++j) {
-      tma::mbar_wait(&s_full[s], j & 1, p.status, 16);
+      tma::mbar_wait(&s_full[s], j & 1, p.status, 16, abortw);
       tc_fence_after();
       // Visibility per group of 32 keys.  cls: 2 = all visible, 0 = none, 1 = mixed; the class is the same for
       // every lane of a warp: prefix slots carry one mask per state, and in a block tile the 32 rows of a warp
@@ -396,7 +399,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
       // rescale O when some row of this warp moved its exponent base (not for the first tile: the first
       // P.V overwrites O instead of accumulating); O must be quiescent: wait for the previous P.V
       if (__any_sync(0xffffffffu, (alpha != 1.f) && j > 0)) {
-        tma::mbar_wait(&pv_done[s], (j - 1) & 1, p.status, 19);
+        tma::mbar_wait(&pv_done[s], (j - 1) & 1, p.status, 19, abortw);
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < DH / 16; ++c) {
@@ -466,7 +469,7 @@ prefill_attend_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_con
     // Each group waits for ITS stream's last P.V only -- a barrier whose phases it has followed in order; a
     // parity wait on the other stream's barrier could pass on a phase two tiles back.  The block barrier below
     // then carries "both streams are complete" across the groups.
-    tma::mbar_wait(&pv_done[s], (NT - 1) & 1, p.status, 18);
+    tma::mbar_wait(&pv_done[s], (NT - 1) & 1, p.status, 18, abortw);
     tc_fence_after();
     float* xch = reinterpret_cast<float*>(sQs);            // [2][128] 1/l, then [2][128] partial sums of squares
     xch[s * PF_BM + row] = l > 0.f ? 1.f / l : 0.f;
@@ -524,11 +527,10 @@ template <int DH>
 int launch_prefill(const CUtensorMap* maps, const PrefillParams& p, cudaStream_t s) {
   const size_t smem = prefill_smem<DH>(p.Lbuf);
   CODA_REQUIRE(smem <= 226 * 1024, CODA_ERR_LIMIT, "prefill_attend: %d slots need %zu bytes of shared memory", p.Lbuf, smem);
-  static bool configured = false;
-  if (!configured) {
+  static coda_device_once once;
+  coda_on_first_use(once, [] {
     cudaFuncSetAttribute(prefill_attend_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    configured = true;
-  }
+  });
   dim3 grid((p.blk + PF_BM - 1) / PF_BM, p.H, p.B);
   {
     static int pool = 0;

@@ -343,18 +343,22 @@ __global__ void __launch_bounds__(64) route_decide_kernel(RouteParams p) {
 // candidate rows in batches.
 template <typename T>
 __global__ void __launch_bounds__(128) route_apply_kernel(RouteParams p) {
-  extern __shared__ float stash[];                                   // [Hkv*Dh] new row for re-normalising
+  extern __shared__ float stash[];                                   // [Hkv*Dh] new row for re-normalising, then the slot's candidate list
   const coda_layer_cfg& c = p.c;
   const int b = blockIdx.y, tid = threadIdx.x, NT = blockDim.x, lane = tid & 31, warp = tid >> 5, NW = NT >> 5;
   const int Hkv = c.Hkv, Dh = c.Dh, HD = Hkv * Dh, lf = Dh / 2, lfd = Dh - lf;
+  // Every candidate of the block may land on one slot (a one-slot summary bank, clustered keys), so the list
+  // staged per slot holds max(te, ts) entries: nothing is ever dropped from a slot's sum.
+  const int TMAX = max(max(p.te, p.ts), 1);
+  int* s_cand = reinterpret_cast<int*>(stash + HD);
+  float* s_wt = reinterpret_cast<float*>(s_cand + TMAX);
   const int Me = c.Me, Ms = c.Ms, W = c.W, Lbuf = W + Me + Ms;
   const int te = (Me > 0) ? p.te : 0;
   uint8_t* al = p.st.allowed + (long long)b * Lbuf;
   T* kb = (T*)p.st.k_buf + (long long)b * Hkv * Lbuf * Dh;
   T* vb = (T*)p.st.v_buf + (long long)b * Hkv * Lbuf * Dh;
   const Plan pl = plan_of(p, b);
-  __shared__ int s_n, s_cand[128];
-  __shared__ float s_wt[128];
+  __shared__ int s_n;
   const bool exact = (int)blockIdx.x < te;
   int slot;                                                          // slot index inside its bank
   float cden = 1.f; bool fresh = false;
@@ -365,7 +369,7 @@ __global__ void __launch_bounds__(128) route_apply_kernel(RouteParams p) {
     slot = pl.e_tgt[t];
     if (tid == 0) {
       int nn = 0;
-      for (int u = t; u < te && nn < 128; ++u)
+      for (int u = t; u < te; ++u)
         if ((pl.e_flag[u] & 1) && pl.e_tgt[u] == slot) { s_cand[nn] = p.cand[(long long)b * p.cand_bs + u]; s_wt[nn] = 1.f; ++nn; }
       s_n = nn;
     }
@@ -380,7 +384,7 @@ __global__ void __launch_bounds__(128) route_apply_kernel(RouteParams p) {
     if (tid == 0) {
       const int a0 = pl.s_start[slot], a1 = pl.s_start[slot + 1];
       int nn = 0;
-      for (int a = a0; a < a1 && nn < 128; ++a) {
+      for (int a = a0; a < a1; ++a) {
         const int t = pl.s_ord[a];
         s_cand[nn] = p.cand[(long long)b * p.cand_bs + t]; s_wt[nn] = pl.s_w[t]; ++nn;
       }
@@ -548,8 +552,8 @@ static int launch_route(RouteParams& p, cudaStream_t s) {
     if (smem2 > 48 * 1024) cudaFuncSetAttribute(route_decide_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     route_decide_kernel<T><<<c.B, 64, smem2, s>>>(p);
     CODA_CHECK_LAUNCH("route_block (decide)");
-    const size_t smem3 = sizeof(float) * (size_t)HD;
-    CODA_REQUIRE(smem3 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: Hkv*Dh = %d too large", HD);
+    const size_t smem3 = sizeof(float) * (size_t)HD + 8 * (size_t)(tmax > 0 ? tmax : 1);   // new row + the slot's candidate list
+    CODA_REQUIRE(smem3 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: Hkv*Dh = %d with %d candidates per block needs %zu bytes of shared memory", HD, tmax, smem3);
     if (smem3 > 48 * 1024) cudaFuncSetAttribute(route_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
     const int nslots = (c.Me > 0 ? p.te : 0) + (p.ts > 0 ? c.Ms : 0);
     if (nslots > 0) {

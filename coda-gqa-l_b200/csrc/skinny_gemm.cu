@@ -86,7 +86,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 
   // The other CTA's shared memory may be written only once that CTA runs: announce here, wait before the exchange.
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  __shared__ int s_abort;                          // set by the first bounded wait of this CTA that expires
+  int* const abortw = &s_abort;
   if (tid == 0) {
+    s_abort = 0;
     for (int i = 0; i < SG_STAGES; ++i) { tma::mbar_init(&full[i], 1); tma::mbar_init(&empty[i], SG_CWARPS); }
     for (int i = 0; i < SG_MAXXG; ++i) tma::mbar_init(&xbar[i], 1);
     tma::fence_barrier_init();
@@ -111,7 +114,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
           for (int j = 0; j < nb; ++j) sg_tma_load(xs + (i + j) * SG_XBOX, &xmap, &xbar[g], kbase + (i + j) * SG_BK, 0);
         }
         const int s = i % SG_STAGES, round = i / SG_STAGES;
-        if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, p.status, 21);
+        if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, p.status, 21, abortw);
         tma::mbar_expect_tx(&full[s], SG_WBOX);
         sg_tma_load(ring + s * SG_WBOX, &wmap, &full[s], kbase + i * SG_BK, n0);
       }
@@ -121,9 +124,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     // ---------------- consumers ----------------
     const uint32_t xs_u = smem_u32(xs), ring_u = smem_u32(ring);
     for (int i = 0; i < nbox; ++i) {
-      if (i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 22);   // each X barrier completes once
+      if (i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 22, abortw);   // each X barrier completes once
       const int s = i % SG_STAGES, round = i / SG_STAGES;
-      tma::mbar_wait(&full[s], round & 1, p.status, 23);
+      tma::mbar_wait(&full[s], round & 1, p.status, 23, abortw);
       const uint32_t wb = ring_u + s * SG_WBOX, xb = xs_u + i * SG_XBOX;
       uint32_t a0[4], a1[4];                               // weight fragments of the two k-steps
       const int wrow = rb * 16 + (li & 1) * 8 + lr;
@@ -212,11 +215,10 @@ extern "C" int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const 
   SkinnyParams p;
   p.M = M; p.N = N; p.K = K; p.res = (const bf16*)residual; p.res_rs = res_rs; p.y = (bf16*)y; p.y_rs = y_rs; p.status = status;
   const size_t smem = (size_t)SkinnySmem(K / 2).total + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static coda_device_once once;
+  coda_on_first_use(once, [] {
     cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    configured = true;
-  }
+  });
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(2, N / SG_BN, 1);
   lc.blockDim = dim3(SG_THREADS, 1, 1);

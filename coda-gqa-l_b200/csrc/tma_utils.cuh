@@ -1,6 +1,10 @@
 // mbarrier / TMA (cp.async.bulk) primitives shared by the kernels, as inline PTX.
 // Every wait is bounded: after WAIT_LIMIT polls it records a code in a status word (when one is
 // given) and returns, so that a lost completion shows up as an error flag, never as a hang.
+// A kernel also gives its waits one word of shared memory (`abort`, zero at start): the first wait of the CTA
+// that expires sets it, and every other wait of that CTA returns false within a few polls of seeing it, so that
+// after one lost completion all roles run out of their loops promptly (on meaningless data -- the status word
+// says so) and the normal exit path still frees what the CTA holds (tensor memory, cluster barriers).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -27,9 +31,14 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (int it = 0; it < WAIT_LIMIT; ++it) if (mbar_try(bar, parity)) return true;
-  if (status) atomicExch(status, code);
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, int* abort = nullptr,
+                                          int limit = WAIT_LIMIT) {
+  for (int it = 0; it < limit; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if (abort != nullptr && (it & 15) == 15 && *reinterpret_cast<volatile int*>(abort) != 0) return false;
+  }
+  if (abort != nullptr) *reinterpret_cast<volatile int*>(abort) = code;
+  if (status) atomicCAS(status, 0, code);            // the first code stays: it names the wait that gave up
   return false;
 }
 // Contiguous global -> shared copy; both addresses 16-byte aligned, bytes a multiple of 16.

@@ -18,7 +18,10 @@
 #include <torch/library.h>
 #include <torch/types.h>
 
+#include <cstdarg>
+#include <cstdio>
 #include <optional>
+#include <string>
 
 #include "coda_b200.h"
 
@@ -27,11 +30,22 @@ namespace {
 using torch::Tensor;
 using OptTensor = std::optional<Tensor>;
 
+// Error texts are composed with snprintf and handed to TORCH_CHECK as one string: numbers never go through the
+// C++ stream formatting of whichever libstdc++ copy happens to be first in the process's symbol scope.
+std::string text(const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  return std::string(buf);
+}
+
 static_assert(sizeof(coda_layer_cfg) == 25 * 4, "coda_layer_cfg is 19 int32 fields followed by 6 floats");
 
 coda_layer_cfg make_cfg(c10::IntArrayRef ci, c10::ArrayRef<double> cf) {
-  TORCH_CHECK(ci.size() == 19, "cfg_i must hold the 19 integer fields of coda_layer_cfg, got ", ci.size());
-  TORCH_CHECK(cf.size() == 6, "cfg_f must hold the 6 float fields of coda_layer_cfg, got ", cf.size());
+  TORCH_CHECK(ci.size() == 19, text("cfg_i must hold the 19 integer fields of coda_layer_cfg, got %zu", ci.size()));
+  TORCH_CHECK(cf.size() == 6, text("cfg_f must hold the 6 float fields of coda_layer_cfg, got %zu", cf.size()));
   coda_layer_cfg c;
   int32_t* ip = &c.B;
   for (int i = 0; i < 19; ++i) ip[i] = static_cast<int32_t>(ci[i]);
@@ -44,7 +58,7 @@ at::ScalarType model_dtype(const coda_layer_cfg& c) { return c.dtype == CODA_BF1
 
 void on_device(const Tensor& t, const Tensor& like, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (this library has no CPU path)");
-  TORCH_CHECK(t.device() == like.device(), name, " is on ", t.device(), " but the state is on ", like.device());
+  TORCH_CHECK(t.device() == like.device(), text("%s is on cuda:%d but the state is on cuda:%d", name, int(t.device().index()), int(like.device().index())));
 }
 
 void dense_rows(const Tensor& t, const char* name) {
@@ -52,67 +66,70 @@ void dense_rows(const Tensor& t, const char* name) {
 }
 
 void failed(int rc, const char* what) {
-  TORCH_CHECK(rc == 0, what, " rejected the call (", rc, "): ", coda_b200_last_error());
+  TORCH_CHECK(rc == 0, text("%s rejected the call (%d): %s", what, rc, coda_b200_last_error()));
 }
 
-// The state planes of one layer, validated against the configuration.
-struct State {
+// The state planes of one layer, validated against the configuration (absent tensors: nullptr).
+coda_state_ptrs bind_state(const coda_layer_cfg& c, const Tensor& k_buf, const Tensor& v_buf, const Tensor& allowed,
+                           const Tensor* g_recent, const Tensor* mem_last_exact, const Tensor* exact_v_norm,
+                           const Tensor* sum_lf_k_norm) {
+  const int64_t Lbuf = int64_t(c.W) + c.Me + c.Ms;
+  const auto dt = model_dtype(c);
+  TORCH_CHECK(k_buf.is_cuda(), "k_buf must be a CUDA tensor (this library has no CPU path)");
+  on_device(v_buf, k_buf, "v_buf");
+  on_device(allowed, k_buf, "allowed");
+  TORCH_CHECK(k_buf.scalar_type() == dt && v_buf.scalar_type() == dt, "k_buf / v_buf must have the configuration's dtype");
+  const bool shape_ok = k_buf.dim() == 4 && k_buf.size(0) == c.B && k_buf.size(1) == c.Hkv && k_buf.size(2) == Lbuf &&
+                        k_buf.size(3) == c.Dh && v_buf.dim() == 4 && v_buf.size(0) == c.B && v_buf.size(1) == c.Hkv &&
+                        v_buf.size(2) == Lbuf && v_buf.size(3) == c.Dh;
+  TORCH_CHECK(shape_ok, text("k_buf / v_buf must be [B, Hkv, W+Me+Ms, Dh] = [%d, %d, %lld, %d]", c.B, c.Hkv, (long long)Lbuf, c.Dh));
+  TORCH_CHECK(k_buf.is_contiguous() && v_buf.is_contiguous() && allowed.is_contiguous(), "state tensors must be contiguous");
+  TORCH_CHECK(allowed.element_size() == 1 && allowed.numel() == c.B * Lbuf, "allowed must be [B, W+Me+Ms] of 1-byte elements");
   coda_state_ptrs p;
-  State(const coda_layer_cfg& c, const Tensor& k_buf, const Tensor& v_buf, const Tensor& allowed,
-        const OptTensor& g_recent, const OptTensor& mem_last_exact, const OptTensor& exact_v_norm,
-        const OptTensor& sum_lf_k_norm) {
-    const int64_t Lbuf = c.W + c.Me + c.Ms;
-    const auto dt = model_dtype(c);
-    TORCH_CHECK(k_buf.is_cuda(), "k_buf must be a CUDA tensor (this library has no CPU path)");
-    on_device(v_buf, k_buf, "v_buf");
-    on_device(allowed, k_buf, "allowed");
-    TORCH_CHECK(k_buf.scalar_type() == dt && v_buf.scalar_type() == dt, "k_buf / v_buf must have the configuration's dtype");
-    TORCH_CHECK(k_buf.sizes() == c10::IntArrayRef({c.B, c.Hkv, Lbuf, c.Dh}) && v_buf.sizes() == k_buf.sizes(),
-                "k_buf / v_buf must be [B, Hkv, W+Me+Ms, Dh] = [", c.B, ", ", c.Hkv, ", ", Lbuf, ", ", c.Dh, "]");
-    TORCH_CHECK(k_buf.is_contiguous() && v_buf.is_contiguous() && allowed.is_contiguous(), "state tensors must be contiguous");
-    TORCH_CHECK(allowed.element_size() == 1 && allowed.numel() == c.B * Lbuf, "allowed must be [B, W+Me+Ms] of 1-byte elements");
-    p.k_buf = k_buf.data_ptr();
-    p.v_buf = v_buf.data_ptr();
-    p.allowed = static_cast<uint8_t*>(allowed.data_ptr());
-    p.g_recent = nullptr;
-    p.mem_last_exact = nullptr;
-    p.exact_v_norm = nullptr;
-    p.sum_lf_k_norm = nullptr;
-    p.events = nullptr;
-    if (g_recent) {
-      on_device(*g_recent, k_buf, "g_recent");
-      TORCH_CHECK(g_recent->scalar_type() == at::kFloat && g_recent->is_contiguous() && g_recent->numel() == int64_t(c.B) * c.W,
-                  "g_recent must be a contiguous float32 [B, W]");
-      p.g_recent = g_recent->data_ptr<float>();
-    }
-    if (mem_last_exact && mem_last_exact->numel() > 0) {
-      on_device(*mem_last_exact, k_buf, "mem_last_exact");
-      TORCH_CHECK(mem_last_exact->scalar_type() == at::kLong && mem_last_exact->is_contiguous() &&
-                      mem_last_exact->numel() == int64_t(c.B) * c.Me, "mem_last_exact must be a contiguous int64 [B, Me]");
-      p.mem_last_exact = mem_last_exact->data_ptr<int64_t>();
-    }
-    if (exact_v_norm) {
-      on_device(*exact_v_norm, k_buf, "exact_v_norm");
-      TORCH_CHECK(exact_v_norm->scalar_type() == dt && exact_v_norm->is_contiguous() &&
-                      exact_v_norm->numel() == int64_t(c.B) * c.Hkv * c.Me * c.Dh, "exact_v_norm must be [B, Hkv, Me, Dh] in the model dtype");
-      p.exact_v_norm = exact_v_norm->data_ptr();
-    }
-    if (sum_lf_k_norm) {
-      on_device(*sum_lf_k_norm, k_buf, "sum_lf_k_norm");
-      TORCH_CHECK(sum_lf_k_norm->scalar_type() == dt && sum_lf_k_norm->is_contiguous() &&
-                      sum_lf_k_norm->numel() == int64_t(c.B) * c.Hkv * c.Ms * (c.Dh - c.Dh / 2),
-                  "sum_lf_k_norm must be [B, Hkv, Ms, Dh/2] in the model dtype");
-      p.sum_lf_k_norm = sum_lf_k_norm->data_ptr();
-    }
+  p.k_buf = k_buf.data_ptr();
+  p.v_buf = v_buf.data_ptr();
+  p.allowed = static_cast<uint8_t*>(allowed.data_ptr());
+  p.g_recent = nullptr;
+  p.mem_last_exact = nullptr;
+  p.exact_v_norm = nullptr;
+  p.sum_lf_k_norm = nullptr;
+  p.events = nullptr;
+  if (g_recent != nullptr) {
+    on_device(*g_recent, k_buf, "g_recent");
+    TORCH_CHECK(g_recent->scalar_type() == at::kFloat && g_recent->is_contiguous() && g_recent->numel() == int64_t(c.B) * c.W,
+                "g_recent must be a contiguous float32 [B, W]");
+    p.g_recent = g_recent->data_ptr<float>();
   }
-};
+  if (mem_last_exact != nullptr && mem_last_exact->numel() > 0) {
+    on_device(*mem_last_exact, k_buf, "mem_last_exact");
+    TORCH_CHECK(mem_last_exact->scalar_type() == at::kLong && mem_last_exact->is_contiguous() &&
+                    mem_last_exact->numel() == int64_t(c.B) * c.Me, "mem_last_exact must be a contiguous int64 [B, Me]");
+    p.mem_last_exact = mem_last_exact->data_ptr<int64_t>();
+  }
+  if (exact_v_norm != nullptr) {
+    on_device(*exact_v_norm, k_buf, "exact_v_norm");
+    TORCH_CHECK(exact_v_norm->scalar_type() == dt && exact_v_norm->is_contiguous() &&
+                    exact_v_norm->numel() == int64_t(c.B) * c.Hkv * c.Me * c.Dh, "exact_v_norm must be [B, Hkv, Me, Dh] in the model dtype");
+    p.exact_v_norm = exact_v_norm->data_ptr();
+  }
+  if (sum_lf_k_norm != nullptr) {
+    on_device(*sum_lf_k_norm, k_buf, "sum_lf_k_norm");
+    TORCH_CHECK(sum_lf_k_norm->scalar_type() == dt && sum_lf_k_norm->is_contiguous() &&
+                    sum_lf_k_norm->numel() == int64_t(c.B) * c.Hkv * c.Ms * (c.Dh - c.Dh / 2),
+                "sum_lf_k_norm must be [B, Hkv, Ms, Dh/2] in the model dtype");
+    p.sum_lf_k_norm = sum_lf_k_norm->data_ptr();
+  }
+  return p;
+}
+
+const Tensor* opt_ref(const OptTensor& t) { return t.has_value() ? &t.value() : nullptr; }
 
 void check_act(const Tensor& t, const Tensor& like, const coda_layer_cfg& c, int64_t rows, int64_t feat, const char* name) {
   on_device(t, like, name);
   dense_rows(t, name);
   TORCH_CHECK(t.scalar_type() == model_dtype(c), name, " must have the configuration's dtype");
-  TORCH_CHECK(t.dim() == 3 && t.size(0) == c.B && t.size(1) == rows && t.size(2) == feat, name, " must be [", c.B, ", ", rows,
-              ", ", feat, "], got ", t.sizes());
+  TORCH_CHECK(t.dim() == 3 && t.size(0) == c.B && t.size(1) == rows && t.size(2) == feat,
+              text("%s must be [%d, %lld, %lld] (got %lld dimensions)", name, c.B, (long long)rows, (long long)feat, (long long)t.dim()));
 }
 
 const void* opt_ptr(const OptTensor& t) { return t ? t->data_ptr() : nullptr; }
@@ -162,7 +179,7 @@ void attend(Tensor& out, const Tensor& k_buf, const Tensor& v_buf, const Tensor&
             const Tensor& q_noise, const Tensor& lam, const OptTensor& k_blk, const OptTensor& v_blk,
             const OptTensor& norm_w, c10::IntArrayRef ci, c10::ArrayRef<double> cf) {
   auto c = make_cfg(ci, cf);
-  State st(c, k_buf, v_buf, allowed, std::nullopt, std::nullopt, std::nullopt, std::nullopt);
+  const coda_state_ptrs st = bind_state(c, k_buf, v_buf, allowed, nullptr, nullptr, nullptr, nullptr);
   TORCH_CHECK(q.dim() == 3, "q must be [B, Lq, H*Dh]");
   const int64_t Lq = q.size(1);
   check_act(q, k_buf, c, Lq, int64_t(c.H) * c.Dh, "q");
@@ -177,7 +194,7 @@ void attend(Tensor& out, const Tensor& k_buf, const Tensor& v_buf, const Tensor&
   }
   if (norm_w) TORCH_CHECK(norm_w->is_cuda() && norm_w->numel() == c.Dh && norm_w->scalar_type() == model_dtype(c), "norm_w must be [Dh] in the model dtype");
   const at::cuda::CUDAGuard guard(k_buf.device());
-  failed(coda_b200_attend(&c, &st.p, int32_t(Lq), q.data_ptr(), q.stride(0), q.stride(1), q_noise.data_ptr(),
+  failed(coda_b200_attend(&c, &st, int32_t(Lq), q.data_ptr(), q.stride(0), q.stride(1), q_noise.data_ptr(),
                           q_noise.stride(0), q_noise.stride(1), lam.data_ptr<float>(), lam.stride(0), lam.stride(1),
                           opt_ptr(k_blk), k_blk ? k_blk->stride(0) : 0, k_blk ? k_blk->stride(1) : 0, opt_ptr(v_blk),
                           v_blk ? v_blk->stride(0) : 0, v_blk ? v_blk->stride(1) : 0, opt_ptr(norm_w), out.data_ptr(),
@@ -192,7 +209,7 @@ void decode_attend(Tensor& out, const Tensor& k_buf, const Tensor& v_buf, const 
   auto c = make_cfg(ci, cf);
   TORCH_CHECK(coda_b200_decode_attend_supported(&c), "decode_attend: this configuration is not covered by the fused decode kernel "
               "(needs bfloat16, head_dim 64 or 128, at most 8 query heads per KV head); use attend");
-  State st(c, k_buf, v_buf, allowed, std::nullopt, std::nullopt, std::nullopt, std::nullopt);
+  const coda_state_ptrs st = bind_state(c, k_buf, v_buf, allowed, nullptr, nullptr, nullptr, nullptr);
   check_act(q_raw, k_buf, c, 1, int64_t(c.H) * c.Dh, "q_raw");
   check_act(lam_logit, k_buf, c, 1, c.H, "lam_logit");
   check_act(out, k_buf, c, 1, int64_t(c.H) * c.Dh, "out");
@@ -200,13 +217,13 @@ void decode_attend(Tensor& out, const Tensor& k_buf, const Tensor& v_buf, const 
   on_device(status, k_buf, "status");
   TORCH_CHECK(qrec.is_contiguous() && int64_t(qrec.numel() * qrec.element_size()) >= coda_b200_decode_record_bytes(&c) &&
                   reinterpret_cast<uintptr_t>(qrec.data_ptr()) % 16 == 0,
-              "qrec must be a contiguous, 16-byte aligned buffer of at least ", coda_b200_decode_record_bytes(&c), " bytes");
+              text("qrec must be a contiguous, 16-byte aligned buffer of at least %lld bytes", (long long)coda_b200_decode_record_bytes(&c)));
   TORCH_CHECK(status.scalar_type() == at::kInt && status.numel() >= 1, "status must be an int32 tensor");
   TORCH_CHECK(inv_freq.is_cuda() && inv_freq.scalar_type() == at::kFloat && inv_freq.numel() == c.Dh / 2, "inv_freq must be float32 [Dh/2]");
   TORCH_CHECK(cos_theta.numel() == int64_t(c.H) * (c.Dh / 2) && sin_theta.numel() == cos_theta.numel(), "cos/sin theta must be [H, Dh/2]");
   const at::cuda::CUDAGuard guard(k_buf.device());
   coda_ring_pos rp{pos, int32_t(recent_idx), int32_t(recent_filled), nullptr};
-  failed(coda_b200_decode_attend(&c, &st.p, rp, int32_t(token_already_written), q_raw.data_ptr(), q_raw.stride(0),
+  failed(coda_b200_decode_attend(&c, &st, rp, int32_t(token_already_written), q_raw.data_ptr(), q_raw.stride(0),
                                  lam_logit.data_ptr(), lam_logit.stride(0), inv_freq.data_ptr<float>(), cos_theta.data_ptr(),
                                  sin_theta.data_ptr(), opt_ptr(norm_w), qrec.data_ptr(), out.data_ptr(), out.stride(0),
                                  status.data_ptr<int32_t>(), at::cuda::getCurrentCUDAStream()),
@@ -220,7 +237,7 @@ void prefill_attend(Tensor& out, const Tensor& k_buf, const Tensor& v_buf, const
   auto c = make_cfg(ci, cf);
   TORCH_CHECK(coda_b200_prefill_attend_supported(&c), "prefill_attend: this configuration is not covered by the tensor-core "
               "prefill kernel (needs bfloat16 and head_dim 64 or 128); use attend");
-  State st(c, k_buf, v_buf, allowed, std::nullopt, std::nullopt, std::nullopt, std::nullopt);
+  const coda_state_ptrs st = bind_state(c, k_buf, v_buf, allowed, nullptr, nullptr, nullptr, nullptr);
   TORCH_CHECK(q.dim() == 3, "q must be [B, L, H*Dh]");
   const int64_t L = q.size(1);
   TORCH_CHECK(t0 >= 0 && blk > 0 && t0 + blk <= L, "rows t0 .. t0+blk must lie inside the chunk");
@@ -236,7 +253,7 @@ void prefill_attend(Tensor& out, const Tensor& k_buf, const Tensor& v_buf, const
   on_device(status, k_buf, "status");
   TORCH_CHECK(status.scalar_type() == at::kInt && status.numel() >= 1, "status must be an int32 tensor");
   const at::cuda::CUDAGuard guard(k_buf.device());
-  failed(coda_b200_prefill_attend(&c, &st.p, int32_t(L), int32_t(t0), int32_t(blk), q.data_ptr(), q.stride(0), q.stride(1),
+  failed(coda_b200_prefill_attend(&c, &st, int32_t(L), int32_t(t0), int32_t(blk), q.data_ptr(), q.stride(0), q.stride(1),
                                   q_noise.data_ptr(), q_noise.stride(0), q_noise.stride(1), lam.data_ptr<float>(),
                                   lam.stride(0), lam.stride(1), k_seq.data_ptr(), k_seq.stride(0), k_seq.stride(1),
                                   v_seq.data_ptr(), v_seq.stride(0), v_seq.stride(1), opt_ptr(norm_w), out.data_ptr(),
@@ -249,7 +266,7 @@ void step_write(Tensor& k_buf, Tensor& v_buf, Tensor& allowed, Tensor& g_recent,
                 const Tensor& gate, const Tensor& eta_logit, int64_t pos, int64_t recent_idx, int64_t recent_filled,
                 c10::IntArrayRef ci, c10::ArrayRef<double> cf) {
   auto c = make_cfg(ci, cf);
-  State st(c, k_buf, v_buf, allowed, g_recent, mem_last_exact, exact_v_norm, sum_lf_k_norm);
+  const coda_state_ptrs st = bind_state(c, k_buf, v_buf, allowed, &g_recent, &mem_last_exact, opt_ref(exact_v_norm), opt_ref(sum_lf_k_norm));
   check_act(k_new, k_buf, c, 1, int64_t(c.Hkv) * c.Dh, "k_new");
   check_act(v_new, k_buf, c, 1, int64_t(c.Hkv) * c.Dh, "v_new");
   on_device(gate, k_buf, "gate");
@@ -259,7 +276,7 @@ void step_write(Tensor& k_buf, Tensor& v_buf, Tensor& allowed, Tensor& g_recent,
   TORCH_CHECK(recent_filled >= 0 && recent_filled <= c.W && recent_idx >= 0 && recent_idx < c.W, "ring scalars out of range");
   const at::cuda::CUDAGuard guard(k_buf.device());
   coda_ring_pos rp{pos, int32_t(recent_idx), int32_t(recent_filled), nullptr};
-  failed(coda_b200_step_write(&c, &st.p, rp, k_new.data_ptr(), k_new.stride(0), v_new.data_ptr(), v_new.stride(0),
+  failed(coda_b200_step_write(&c, &st, rp, k_new.data_ptr(), k_new.stride(0), v_new.data_ptr(), v_new.stride(0),
                               gate.data_ptr<float>(), eta_logit.data_ptr<float>(), at::cuda::getCurrentCUDAStream()),
          "coda_b200_step_write");
 }
@@ -286,7 +303,7 @@ void route_block(Tensor& k_buf, Tensor& v_buf, Tensor& allowed, Tensor& g_recent
                  const Tensor& gates, const Tensor& cand, const Tensor& eta_logit, Tensor& scratch, int64_t ring_fill,
                  int64_t pos0, int64_t gate_ev0, c10::IntArrayRef ci, c10::ArrayRef<double> cf) {
   auto c = make_cfg(ci, cf);
-  State st(c, k_buf, v_buf, allowed, g_recent, mem_last_exact, exact_v_norm, sum_lf_k_norm);
+  const coda_state_ptrs st = bind_state(c, k_buf, v_buf, allowed, &g_recent, &mem_last_exact, opt_ref(exact_v_norm), opt_ref(sum_lf_k_norm));
   TORCH_CHECK(k_blk.dim() == 3, "k_blk must be [B, blk, Hkv*Dh]");
   const int64_t blk = k_blk.size(1);
   check_act(k_blk, k_buf, c, blk, int64_t(c.Hkv) * c.Dh, "k_blk");
@@ -300,9 +317,9 @@ void route_block(Tensor& k_buf, Tensor& v_buf, Tensor& allowed, Tensor& g_recent
   TORCH_CHECK(eta_logit.scalar_type() == at::kFloat && eta_logit.numel() == c.Hkv, "eta_logit must be float32 [Hkv]");
   TORCH_CHECK(ring_fill >= 0 && ring_fill <= c.W, "ring_fill out of range");
   TORCH_CHECK(scratch.is_contiguous() && int64_t(scratch.numel() * scratch.element_size()) >= coda_b200_route_scratch_bytes(&c),
-              "scratch must hold at least ", coda_b200_route_scratch_bytes(&c), " bytes");
+              text("scratch must hold at least %lld bytes", (long long)coda_b200_route_scratch_bytes(&c)));
   const at::cuda::CUDAGuard guard(k_buf.device());
-  failed(coda_b200_route_block(&c, &st.p, int32_t(ring_fill), int32_t(blk), pos0, k_blk.data_ptr(), k_blk.stride(0),
+  failed(coda_b200_route_block(&c, &st, int32_t(ring_fill), int32_t(blk), pos0, k_blk.data_ptr(), k_blk.stride(0),
                                k_blk.stride(1), v_blk.data_ptr(), v_blk.stride(0), v_blk.stride(1), gates.data_ptr<float>(),
                                gates.stride(0), gate_ev0, cand.data_ptr<int32_t>(), cand.stride(0),
                                eta_logit.data_ptr<float>(), scratch.data_ptr(), at::cuda::getCurrentCUDAStream()),

@@ -319,6 +319,17 @@ int coda_b200_route_block_noalloc(const coda_layer_cfg* cfg, const coda_state_pt
 /* Adds `n` to the int64 step counter that coda_ring_pos.step_dev points to (one thread). */
 int coda_b200_advance_steps(int64_t* step_dev, int64_t n, coda_stream_t stream);
 
+/* Self-test of the bounded device-side waits (no reference counterpart: the reference has no device-side waits).
+ * Every pipelined kernel here waits on shared-memory barriers through one helper that gives up after a fixed
+ * number of polls, records a code in the kernel's status word and sets a CTA-wide abort word that makes every other
+ * wait of the CTA return at once; the kernel then runs out on meaningless data and exits normally (tensor memory
+ * freed), and the host finds the code in the status word.  This entry point runs that helper on two barriers that
+ * nobody arrives at: thread 0 with `poll_limit` polls (1..65536), thread 32 with the kernels' full limit.
+ * status: device int32, zero before the call, 77 afterwards (the code of the wait that gave up first).
+ * report: device int32[5] = {thread 0 saw its barrier complete (0), its cycles, thread 32 saw its barrier complete (0),
+ * its cycles, the abort word (77)}.  Returns after the launch like every other entry point. */
+int coda_b200_selftest_bounded_wait(int32_t poll_limit, int32_t* status, int32_t* report, coda_stream_t stream);
+
 /* Host-only helpers (no GPU needed): the selection order used by select_candidates and by
  * the LRU victim ranking, exposed so that CPU tests can compare it with torch.topk. */
 int coda_b200_host_topk_f32(const float* v, int32_t n, int32_t k, int32_t largest, int32_t sorted, int32_t* out);

@@ -95,6 +95,15 @@ SCENARIOS = {
         inputs=dict(kind="mixture", centroids=64, sigma=0.3, seed=17, L=320, Ldec=64, repeat_prob=0.10),
         phases=[("prefill", 0, 320, 64), ("decode", 0, 64)],
     ),
+    # more candidates per block than any fixed staging size: one summary slot takes all 160 summary candidates of a
+    # block, the exact bank takes up to 150 with refresh-on-hit and many exact repeats (several overwrites per slot)
+    "many_candidates": dict(
+        model=dict(_SMALL, num_landmarks_summary=1, summary_candidates_per_block=160, exact_candidates_per_block=150,
+                   exact_refresh_on_hit=True),
+        model_seed=42, state_seed=99, B=2, random_gate=True,
+        inputs=dict(kind="mixture", centroids=12, sigma=0.3, seed=19, L=720, Ldec=40, repeat_prob=0.5),
+        phases=[("prefill", 0, 720, 240), ("decode", 0, 40)],
+    ),
     "policy_none": dict(
         model=dict(_SMALL, write_policy="none", summary_overwrite_on_insert=False),
         model_seed=42, state_seed=99, B=2,

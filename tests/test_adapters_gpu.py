@@ -16,13 +16,17 @@ from tests.scenarios import ADAPTER_SCENARIOS, fake_eve_attention, fake_llama_at
 pytestmark = pytest.mark.gpu
 
 
-def _make(sc):
+def _make_pair(sc):
+    """Two adapters built one after the other from ONE stand-in attention module, as the fixture generator does:
+    the lambda projection keeps its random initialisation, so the second adapter's differs from the first's."""
     from coda_gqa_l_b200 import EveCoDAAdapter, LlamaCoDAAdapter
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         if sc["kind"] == "llama":
-            return LlamaCoDAAdapter.from_llama_attention(fake_llama_attention(sc), bounded=True, **sc["kwargs"])
-        return EveCoDAAdapter.from_eve_attention(fake_eve_attention(sc), bounded=True, **sc["kwargs"])
+            src = fake_llama_attention(sc)
+            return [LlamaCoDAAdapter.from_llama_attention(src, bounded=True, **sc["kwargs"]) for _ in range(2)]
+        src = fake_eve_attention(sc)
+        return [EveCoDAAdapter.from_eve_attention(src, bounded=True, **sc["kwargs"]) for _ in range(2)]
 
 
 @pytest.mark.parametrize("name", list(ADAPTER_SCENARIOS))
@@ -33,7 +37,7 @@ def test_adapter_forward_matches_upstream_adapter(name):
     f32 = dtype == torch.float32
     tol = TOL_F32 if f32 else TOL_BF16
     gold = load_golden(name)
-    ad, ad2 = _make(sc).eval().to(dtype), _make(sc).eval().to(dtype)
+    ad, ad2 = (a.eval().to(dtype) for a in _make_pair(sc))
     got = float(sum(v.double().abs().sum() for v in ad.coda.state_dict().values()))
     assert abs(got - gold["weights_abs_sum"]) <= 1e-6 * gold["weights_abs_sum"], "adapter weights differ from upstream's"
     assert ad.cache_bytes(batch_size=sc["B"], dtype=dtype) == gold["cache_bytes"]

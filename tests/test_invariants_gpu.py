@@ -223,3 +223,23 @@ def test_captured_step_notices_writes_made_outside_it():
     stack.layers[0].load_state_dict(sd)
     stack.step_graph(x[:, 101:102], sa)
     assert stack._graph["graph"] is not g0
+
+
+def test_a_wait_that_runs_out_reports_and_releases_the_cta():
+    """The bounded wait all pipelined kernels use, on barriers nobody arrives at: the short wait gives up and
+    leaves its code in the status word and the CTA's abort word; the long wait of the same CTA sees the abort
+    word and leaves at once instead of polling to its own limit; the context stays usable afterwards."""
+    from coda_gqa_l_b200._lib import check, lib
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    report = torch.full((5,), -1, dtype=torch.int32, device="cuda")
+    check(lib.coda_b200_selftest_bounded_wait(2048, status.data_ptr(), report.data_ptr(),
+                                              torch.cuda.current_stream().cuda_stream), "coda_b200_selftest_bounded_wait")
+    torch.cuda.synchronize()
+    r = report.tolist()
+    assert int(status.item()) == 77, "the first wait to give up names itself in the status word"
+    assert r[0] == 0 and r[2] == 0 and r[4] == 77
+    # the second waiter was released by the abort word: it took about as long as the first, not 2048x longer
+    assert r[3] <= 4 * r[1] + 100_000, r
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0          # the context still works
+    with pytest.raises(RuntimeError):
+        check(lib.coda_b200_selftest_bounded_wait(0, status.data_ptr(), report.data_ptr(), None), "selftest")
