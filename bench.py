@@ -134,34 +134,36 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ reference arm
-def reference_decode(w, steps: int, warmup: int, device: str, threads: int, sample_layers: int, budget_s: float = None):
+def reference_decode(w, steps: int, warmup: int, device: str, threads: int, sample_layers: int = None,
+                     budget_s: float = None, region_s: float = 90.0):
     """The reference's PyTorch implementation of the decode step, timed on ``device``.
 
     Runs ``sample_layers`` independent layers (chained h <- h + layer(h), default seeded weights) of the workload's
-    shape at the workload's states-per-GPU, warmed by a prefill that fills every ring, for ``steps`` decode tokens
-    after ``warmup`` untimed ones.  Tokens/s of the full stack = states / (seconds per sampled step x layers /
-    sample_layers): every layer of the stack has the same shape and cost.  With ``budget_s`` the step count is cut so
-    that the timed region stays near that many seconds.  Nothing of this repository's package is imported."""
+    shape at the workload's states-per-GPU, each warmed by a prefill that fills its ring, for ``steps`` decode tokens
+    after ``warmup`` untimed ones.  ``sample_layers=None``: as many layers of the stack as keep warm-up + timed steps
+    within ``region_s`` seconds (all of them when they fit), judged from one layer's probed step time.  Tokens/s of
+    the full stack = states / (seconds per sampled step x layers / sample_layers): every layer of the stack has the
+    same shape and cost.  With ``budget_s`` the step count is cut instead so that the timed region stays near that
+    many seconds.  Nothing of this repository's package is imported."""
     from oracle import build_ref
     torch.set_num_threads(threads)
     dtype = torch.bfloat16
     dev = torch.device(device)
-    B, D, nl = w["B"], w["D"], sample_layers
+    B, D = w["B"], w["D"]
     kind = "reference" if build_ref.available() else "port"
     layers, states = [], []
     if kind == "reference":
         Ref = build_ref.load()
-        for i in range(nl):
+
+        def add_layer(i):
             torch.manual_seed(1000 + i)
             m = Ref(**layer_kwargs(w)).eval().to(dtype).to(dev)
             torch.manual_seed(7 + i)
             layers.append(m)
             states.append(m.init_state(batch_size=B, device=dev, dtype=dtype))
 
-        def prefill(x):
-            for i, m in enumerate(layers):
-                y, states[i] = m.prefill_chunked(x, states[i], block_size=w["block"])
-                x = x + y
+        def prefill_layer(i, x):
+            _, states[i] = layers[i].prefill_chunked(x, states[i], block_size=w["block"], return_outputs=False)
 
         def step(x):
             for i, m in enumerate(layers):
@@ -169,11 +171,11 @@ def reference_decode(w, steps: int, warmup: int, device: str, threads: int, samp
                 x = x + y
             return x
     else:
+        import math
         from oracle import coda_oracle as orc
         from oracle.coda_oracle import OracleConfig
-        import math
-        cfgs, wts = [], []
-        for i in range(nl):
+
+        def add_layer(i):
             # the module's default initialisation (upstream attention.py:189-234) restated with plain tensors
             torch.manual_seed(1000 + i)
             H, Hkv, Dh = w["H"], w["Hkv"], D // w["H"]
@@ -185,38 +187,45 @@ def reference_decode(w, steps: int, warmup: int, device: str, threads: int, samp
                   "o_proj.weight": lin(D, H * Dh)}
             if w["head_norm_mode"] == "full":
                 sd["head_norm.weight"] = torch.ones(Dh)
-            wts.append({k: v.to(dtype) for k, v in sd.items()})
             cfg = OracleConfig(embed_dim=D, num_heads=H, num_kv_heads=Hkv, window=w["W"], num_landmarks_exact=w["Me"],
                                num_landmarks_summary=w["Ms"], rope_base=w["rope_base"], head_norm_mode=w["head_norm_mode"],
                                rope_interleaved=w["rope_interleaved"], angle_dtype=dtype)
-            cfgs.append(cfg)
+            layers.append((cfg, {k: v.to(dtype) for k, v in sd.items()}))
             torch.manual_seed(7 + i)
             states.append(orc.init_state(cfg, B, dtype))
 
-        def prefill(x):
-            for c, wt, st in zip(cfgs, wts, states):
-                x = x + orc.prefill_chunked(c, wt, x, st, block_size=w["block"])
+        def prefill_layer(i, x):
+            orc.prefill_chunked(layers[i][0], layers[i][1], x, states[i], block_size=w["block"])
 
         def step(x):
-            for c, wt, st in zip(cfgs, wts, states):
+            for (c, wt), st in zip(layers, states):
                 x = x + orc.step(c, wt, x, st)
             return x
 
     sync = (lambda: torch.cuda.synchronize(dev)) if dev.type == "cuda" else (lambda: None)
     P = (w["W"] + w["block"] + w["block"] - 1) // w["block"] * w["block"]
     x_pre = mixture(B, P, D, min(w["K"], 512), w["sigma"], 11, "cpu", dtype).to(dev)
-    x_dec = mixture(B, steps + warmup + 1, D, min(w["K"], 512), w["sigma"], 13, "cpu", dtype).to(dev)
+    x_dec = mixture(B, steps + warmup + 2, D, min(w["K"], 512), w["sigma"], 13, "cpu", dtype).to(dev)
     with torch.no_grad():
-        prefill(x_pre)                                                        # every ring full, banks live
+        add_layer(0)
+        prefill_layer(0, x_pre)                                               # ring full, banks live
         sync()
-        t0 = time.perf_counter()
         step(x_dec[:, :1])
         sync()
-        probe = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        step(x_dec[:, 1:2])
+        sync()
+        probe = time.perf_counter() - t0                                      # one layer, one step
         if budget_s is not None:
             steps = int(max(2, min(steps, budget_s / max(probe, 1e-4))))
             warmup = min(warmup, 1)
-        t = 1
+        nl = sample_layers
+        if nl is None:
+            nl = int(max(1, min(w["layers"], region_s / ((steps + warmup) * max(probe, 1e-5)))))
+        for i in range(1, nl):
+            add_layer(i)
+            prefill_layer(i, x_pre)
+        t = 2
         for _ in range(warmup):
             step(x_dec[:, t:t + 1]); t += 1
         sync()
@@ -254,7 +263,7 @@ def reference_main(args, w, K, Wm, rank):
         return
     cores = os.cpu_count() or 1
     if args.impl == "reference":
-        r = reference_decode(w, K, Wm, "cpu", cores, sample_layers=1)
+        r = reference_decode(w, K, Wm, "cpu", cores)
     else:
         r = reference_decode(w, K, Wm, "cuda:0", cores, sample_layers=w["layers"])
     # ms_per_step is the MEASURED time of one sampled step (steps x ms_per_step = the timed region); `value` scales

@@ -181,6 +181,11 @@ class CoDAGQALandmarkPerf2(nn.Module):
         # Output projection of a decode step through this library's own skinny GEMM (coda_b200_skinny_gemm) instead
         # of the vendor GEMM + add.  Off by default: at 32 x 4096 -> 4096 it measures 9.8 us against 9.5 us.
         self.use_skinny_gemm_kernel = False
+        # The decode step's two projections (at most 64 rows, bfloat16) on this library's tcgen05 GEMM
+        # (coda_b200_proj_gemm: weight rows as the MMA's M, split-K over a cluster, bias / residual in the epilogue,
+        # programmatic dependent launch) instead of the vendor GEMM (+ add).  Other shapes and float32 use torch.
+        self.use_own_gemm = True
+        self._gemm_ok: Dict[tuple, bool] = {}
         # Second half of a split decode step (after route_launch / the stack's batched routing) as one launch:
         # the attention kernel writes the new token itself (coda_b200_decode_attend_append).
         self.fuse_append_into_attention = True
@@ -469,14 +474,48 @@ class CoDAGQALandmarkPerf2(nn.Module):
         do not see, e.g. through ``.data``)."""
         self._wt = None
 
+    def _own_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], residual: Optional[torch.Tensor]
+                  ) -> Optional[torch.Tensor]:
+        """``x @ w.T (+ bias) (+ residual)`` for the few rows of a decode step on coda_b200_proj_gemm, or None where
+        that kernel does not apply (more than 64 rows, not bfloat16, K not a multiple of 64, unaligned views)."""
+        B, L, K = x.shape
+        rows, N = B * L, w.shape[0]
+        if not (self.use_own_gemm and rows <= 64 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda):
+            return None
+        ok = self._gemm_ok.get((rows, K, N))
+        if ok is None:
+            ok = bool(lib.coda_b200_proj_gemm_supported(rows, K, N))
+            self._gemm_ok[(rows, K, N)] = ok
+        if not ok or not w.is_contiguous() or w.data_ptr() % 16:
+            return None
+
+        def rows_of(t):                      # (tensor, row stride) of t seen as [rows, features]
+            if L == 1 and t.stride(2) == 1:
+                return t, t.stride(0)
+            t = t if t.is_contiguous() else t.contiguous()
+            return t, t.shape[-1]
+        x, x_rs = rows_of(x)
+        if x.data_ptr() % 16 or x_rs % 8:
+            x, x_rs = x.contiguous(), K
+        res_rs = 0
+        if residual is not None:
+            residual, res_rs = rows_of(residual)
+        y = torch.empty((B, L, N), device=x.device, dtype=x.dtype)
+        check(lib.coda_b200_proj_gemm(x.data_ptr(), x_rs, rows, K, w.data_ptr(), N, _p(bias), _p(residual), res_rs,
+                                      y.data_ptr(), N, self._status_word(x.device).data_ptr(), _stream()), "coda_b200_proj_gemm")
+        return y
+
     def _project(self, x: torch.Tensor, need_kv: bool):
         """q, k, v, lambda logits, gate logits as (B, L, features) tensors (upstream attention.py:396-410,508)."""
         f = self._fused_weight() if need_kv else None
         if f is not None:
             H, Hkv, Dh = self.num_heads, self.num_kv_heads, self.head_dim
             rows = x.shape[0] * x.shape[1]
-            wt = self._skinny_weights() if rows <= self.SKINNY_ROWS else None
-            if wt is not None:
+            y = self._own_gemm(x, f[0], f[1], None)
+            wt = self._skinny_weights() if y is None and rows <= self.SKINNY_ROWS else None
+            if y is not None:
+                pass
+            elif wt is not None:
                 y = torch.addmm(f[1], x.reshape(rows, -1), wt[1]).view(x.shape[0], x.shape[1], -1)
             else:
                 y = F.linear(x, f[0], f[1])
@@ -670,6 +709,10 @@ class CoDAGQALandmarkPerf2(nn.Module):
             check(lib.coda_b200_skinny_gemm(heads.data_ptr(), B * L, HD, w.data_ptr(), N, _p(residual), N, y.data_ptr(), N,
                                             self._status_word(heads.device).data_ptr(), _stream()), "coda_b200_skinny_gemm")
             return y
+        if type(self.o_proj) is nn.Linear:
+            y = self._own_gemm(heads, self.o_proj.weight, self.o_proj.bias, residual)
+            if y is not None:
+                return y
         wt = self._skinny_weights() if B * L <= self.SKINNY_ROWS else None
         if wt is not None:
             h2 = heads.reshape(B * L, HD)

@@ -54,6 +54,13 @@ bool plane_map(CUtensorMap* out, const void* base, int planes, int rows, int Dh,
   return encode(out, Key(base, planes, rows, Dh, 0, 0, box_rows, 3), 3, base, dims, strides, box);
 }
 
+bool matrix_map(CUtensorMap* out, const void* base, int rows, int cols, long long row_stride, int box_rows) {
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)rows * (cuuint64_t)row_stride * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  return encode(out, Key(base, -1, rows, cols, row_stride, 0, box_rows, 3), 3, base, dims, strides, box);
+}
+
 bool token_map(CUtensorMap* out, const void* base, int B, int L, int heads, int Dh, long long bs, long long rs,
                int box_rows) {
   cuuint64_t dims[4] = {(cuuint64_t)Dh, (cuuint64_t)heads, (cuuint64_t)L, (cuuint64_t)B};

@@ -14,6 +14,10 @@ bool available();
 // 128-byte swizzle.  Rows past `rows` inside a box read as zeros and never bleed into the next plane.
 bool plane_map(CUtensorMap* out, const void* base, int planes, int rows, int Dh, int box_rows = 64);
 
+// [rows][cols] bf16 matrix whose rows are row_stride elements apart (a multiple of 8): box = 64 elements x box_rows
+// rows, 128-byte swizzle, addressed with coordinates (column, row, 0).  Rows past `rows` read as zeros.
+bool matrix_map(CUtensorMap* out, const void* base, int rows, int cols, long long row_stride, int box_rows);
+
 // [B][L][heads][Dh] bf16 activations with element strides (batch, token): box = 64 elements x 1 head x
 // box_rows tokens x 1 batch row, 128-byte swizzle.
 bool token_map(CUtensorMap* out, const void* base, int B, int L, int heads, int Dh, long long bs, long long rs,

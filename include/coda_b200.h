@@ -211,6 +211,21 @@ int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, in
                           const void* residual, int64_t res_rs, void* y, int64_t y_rs,
                           int32_t* status, coda_stream_t stream);
 
+/* The decode step's two projections on the tcgen05 tensor cores: y[M][N] = x[M][K] . w[N][K]^T (+ bias[N]) (+ residual[M][N]),
+ * bf16 with fp32 accumulation, M <= 64 rows.  Replaces the nn.Linear calls of src/coda_gqa_l/attention.py:396-410,508 (the
+ * q / k / v / lambda / write-gate projections, given here as ONE weight matrix whose rows are the five weights stacked,
+ * bias likewise) and :467-470,514 (o_proj; `residual` adds the decoder's skip connection in the same pass: the product
+ * (+ bias) is rounded to bf16 before the add, as a GEMM followed by an add would).  w is the nn.Linear weight as it is
+ * ([out][in], dense); x, y and residual have row strides in elements (x's a multiple of 8, x 16-byte aligned); bias may be
+ * NULL.  K must be a multiple of 64.  The weight rows are the MMA's M (tiles of 128), the tokens its N, K is split over the CTAs of a cluster and reduced
+ * through distributed shared memory.  Launched as a programmatic dependent launch: the weight stream starts before the
+ * kernel ahead of it on the stream has finished, x / residual / y are touched only after it has.  status: optional device
+ * int, set non-zero if a bounded wait expired. */
+int coda_b200_proj_gemm_supported(int32_t M, int32_t K, int32_t N);
+int coda_b200_proj_gemm(const void* x, int64_t x_rs, int32_t M, int32_t K, const void* w, int32_t N, const void* bias,
+                        const void* residual, int64_t res_rs, void* y, int64_t y_rs, int32_t* status,
+                        coda_stream_t stream);
+
 /* coda_b200_step_append_fused and coda_b200_decode_attend_prepared as ONE launch: the attention kernel's
  * auxiliary warps write the new token (ring slot, gate, slot flag) and build each plane's queries / lambda / mask
  * in shared memory; the consumer warp owning the ring slot overwrites that row of the staged tile.  Saves a

@@ -623,3 +623,85 @@ def test_token_writing_attention_back_to_back_replays_are_stable():
     assert mod.device_status() == 0
     assert torch.equal(st.k_buf, k_ref) and torch.equal(st.v_buf, v_ref)
     assert torch.equal(st.allowed, al_ref) and torch.equal(st.g_recent, g_ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N,bias,res", [
+    (32, 4096, 6208, True, False),      # the 7B shape's fused input projection: 48.5 weight tiles, K split three ways
+    (32, 4096, 4096, False, True),      # its output projection with the residual
+    (64, 8192, 8192, False, True),      # 70B shape, 64 tokens (the wider token tile)
+    (33, 1024, 1280, True, True),
+    (5, 512, 256, True, True),
+    (1, 128, 64, False, False),         # half a weight tile, two k-blocks
+    (17, 576, 1000, True, False),       # K = 9 k-blocks, N not a multiple of the tile
+    (8, 64, 130, True, True),           # a single k-block: no split
+])
+def test_projection_gemm_matches_library_gemm(M, K, N, bias, res):
+    """The decode step's projection kernel (tcgen05, weight rows as the MMA's M, split-K over a cluster, bias and
+    residual in the epilogue) against torch: fp32 accumulation on both sides, one bf16 rounding of the product (+ bias),
+    a second one after the residual.  x is a row-strided view, as a slice of a longer sequence is."""
+    from coda_gqa_l_b200._lib import check, lib
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    xs = (torch.randn(M, 3, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    x = xs[:, 1]                                                    # rows 3*K elements apart
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    b = (torch.randn(N, device="cuda", generator=g)).to(torch.bfloat16) if bias else None
+    r = (torch.randn(M, N, device="cuda", generator=g)).to(torch.bfloat16) if res else None
+    y = torch.full((M, N + 8), float("nan"), device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.coda_b200_proj_gemm_supported(M, K, N)
+    for _ in range(2):                                              # twice: the second launch overlaps the first's tail
+        check(lib.coda_b200_proj_gemm(x.data_ptr(), x.stride(0), M, K, w.data_ptr(), N, None if b is None else b.data_ptr(),
+                                      None if r is None else r.data_ptr(), N, y.data_ptr(), N + 8, status.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream), "coda_b200_proj_gemm")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = x.float() @ w.float().t()
+    if bias:
+        ref = ref + b.float()
+    ref = ref.to(torch.bfloat16)
+    if res:
+        ref = (ref.float() + r.float()).to(torch.bfloat16)
+    got = y[:, :N]
+    assert torch.isnan(y[:, N:].float()).all(), "wrote past the row"
+    assert torch.isfinite(got.float()).all()
+    err = rel_err(got, ref)
+    assert err < 4e-3, f"projection gemm rel err {err:.3e}"
+    # element-wise: within one bf16 step of the fp32 reference
+    assert float((got.float() - ref.float()).abs().max()) <= 2.0 ** -7 * float(ref.float().abs().max())
+
+
+@pytest.mark.gpu
+def test_decode_step_on_own_gemms_matches_library_gemms():
+    """`use_own_gemm` (default) swaps both projections of a decode step for coda_b200_proj_gemm; the step must agree
+    with the library-GEMM step to bf16 rounding, eagerly and through a captured stack step (where the kernels chain
+    as programmatic dependent launches)."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack, _deep_copy_state
+    layers = []
+    for i in range(3):
+        torch.manual_seed(20 + i)
+        layers.append(CoDAGQALandmarkPerf2(embed_dim=1024, num_heads=8, num_kv_heads=2, window=48, num_landmarks_exact=16,
+                                           num_landmarks_summary=16).eval().to(torch.bfloat16).cuda())
+    stack = CoDAStack(layers)
+    x = orc.mixture_inputs(6, 60 + 80, 1024, centroids=12, sigma=0.3, seed=3, dtype=torch.bfloat16).cuda()
+    torch.manual_seed(4)
+    sa = stack.init_states(batch_size=6, device="cuda", dtype=torch.bfloat16)
+    stack.prefill(x[:, :60], sa, block_size=20)
+    sb = [_deep_copy_state(s) for s in sa]
+    sc_ = [_deep_copy_state(s) for s in sa]
+    ya, yb, yc = [], [], []
+    for t in range(60, 140):
+        for l in layers:
+            l.use_own_gemm = True
+        ya.append(stack.step_graph(x[:, t:t + 1], sa).clone())
+        yc.append(stack.step(x[:, t:t + 1], sc_))
+        for l in layers:
+            l.use_own_gemm = False
+        yb.append(stack.step(x[:, t:t + 1], sb))
+    for l in layers:
+        assert l.device_status() == 0
+    for a, b, c in zip(sa, sb, sc_):
+        assert torch.equal(a.allowed, b.allowed) and torch.equal(c.allowed, b.allowed)
+        assert rel_err(a.k_buf, b.k_buf) < 5e-3 and rel_err(c.k_buf, b.k_buf) < 5e-3
+    assert rel_err(torch.cat(ya, 1), torch.cat(yb, 1)) < 1e-2
+    assert rel_err(torch.cat(yc, 1), torch.cat(yb, 1)) < 1e-2
