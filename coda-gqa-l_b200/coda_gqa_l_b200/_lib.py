@@ -69,7 +69,9 @@ def _load() -> C.CDLL:
                                                    vp, i64, vp, i64, vp, vp, fp, vp, vp, i64, vp, vp]
     lib.coda_b200_rope_table.argtypes = [cfgp, RingPos, fp, fp, vp]
     lib.coda_b200_proj_gemm_supported.argtypes = [i32, i32, i32]
-    lib.coda_b200_proj_gemm.argtypes = [vp, i64, i32, i32, vp, i32, vp, vp, i64, vp, i64, vp, vp]
+    lib.coda_b200_proj_gemm.argtypes = [vp, i64, i32, i32, vp, i32, vp, vp, i64, vp, i64, vp, vp, vp]
+    lib.coda_b200_proj_gemm_workspace_bytes.argtypes = [i32, i32, i32]
+    lib.coda_b200_proj_gemm_workspace_bytes.restype = C.c_int64
     lib.coda_b200_skinny_gemm_supported.argtypes = [i32, i32, i32]
     lib.coda_b200_skinny_gemm.argtypes = [vp, i32, i32, vp, i32, vp, i64, vp, i64, vp, vp]
     lib.coda_b200_step_append_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp,
@@ -95,7 +97,7 @@ def _load() -> C.CDLL:
     for name in EXPORTS:
         fn = getattr(lib, name)
         if name not in ("coda_b200_last_error", "coda_b200_route_scratch_bytes", "coda_b200_route_static_scratch_bytes",
-                        "coda_b200_decode_record_bytes"):
+                        "coda_b200_decode_record_bytes", "coda_b200_proj_gemm_workspace_bytes"):
             fn.restype = C.c_int
     return lib
 
@@ -105,7 +107,7 @@ EXPORTS = (
     "coda_b200_step_write_raw", "coda_b200_step_write_fused", "coda_b200_step_write_fused_supported",
     "coda_b200_step_route", "coda_b200_step_append_fused", "coda_b200_step_route_plan_bytes",
     "coda_b200_step_route_plan", "coda_b200_step_route_batched",
-    "coda_b200_skinny_gemm_supported", "coda_b200_skinny_gemm", "coda_b200_proj_gemm_supported", "coda_b200_proj_gemm",
+    "coda_b200_skinny_gemm_supported", "coda_b200_skinny_gemm", "coda_b200_proj_gemm_supported", "coda_b200_proj_gemm", "coda_b200_proj_gemm_workspace_bytes",
     "coda_b200_decode_attend_append_supported", "coda_b200_decode_attend_append", "coda_b200_rope_table",
     "coda_b200_decode_attend_supported", "coda_b200_decode_attend", "coda_b200_decode_attend_prepared",
     "coda_b200_decode_record_bytes",

@@ -27,6 +27,7 @@ from .state import CoDAGQALandmarkStatePerf2, allocate_state
 __all__ = ["CoDAGQALandmarkPerf2", "CoDAGQALandmarkStatePerf2"]
 
 _DT = {torch.float32: _lib.CODA_F32, torch.bfloat16: _lib.CODA_BF16}
+_GEMM_WS: Dict[torch.device, torch.Tensor] = {}      # split-K workspace of the projection GEMM, one per device
 
 
 METRIC_KEYS = ("exact_hits", "exact_inserts", "exact_overwrites", "exact_fill_ratio", "summary_updates",
@@ -182,9 +183,11 @@ class CoDAGQALandmarkPerf2(nn.Module):
         # of the vendor GEMM + add.  Off by default: at 32 x 4096 -> 4096 it measures 9.8 us against 9.5 us.
         self.use_skinny_gemm_kernel = False
         # The decode step's two projections (at most 64 rows, bfloat16) on this library's tcgen05 GEMM
-        # (coda_b200_proj_gemm: weight rows as the MMA's M, split-K over a cluster, bias / residual in the epilogue,
-        # programmatic dependent launch) instead of the vendor GEMM (+ add).  Other shapes and float32 use torch.
-        self.use_own_gemm = True
+        # (coda_b200_proj_gemm: weight rows as the MMA's M, K split over the SMs with a counter-based fix-up, bias /
+        # residual in the epilogue, programmatic dependent launch) instead of the vendor GEMM (+ add).  Off by default:
+        # its weight stream runs at HBM speed, but the split-K fix-up is a chain of global round trips, and at the 7B
+        # shape it measures 14.8 / 13.4 us (input / output projection) against 11.8 / 10.3 us for the vendor kernels.
+        self.use_own_gemm = False
         self._gemm_ok: Dict[tuple, bool] = {}
         # Second half of a split decode step (after route_launch / the stack's batched routing) as one launch:
         # the attention kernel writes the new token itself (coda_b200_decode_attend_append).
@@ -474,8 +477,18 @@ class CoDAGQALandmarkPerf2(nn.Module):
         do not see, e.g. through ``.data``)."""
         self._wt = None
 
-    def _own_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], residual: Optional[torch.Tensor]
-                  ) -> Optional[torch.Tensor]:
+    def _gemm_workspace(self, device, nbytes: int) -> torch.Tensor:
+        """Split-K workspace of coda_b200_proj_gemm: one per device for every layer of the process (the calls of a
+        decode step follow one another on one stream); its head (the tile counters) starts out zero and the kernel
+        leaves it zero."""
+        ws = _GEMM_WS.get(device)
+        if ws is None or ws.numel() < nbytes:
+            ws = torch.zeros(max(nbytes, 1 << 22), dtype=torch.uint8, device=device)
+            _GEMM_WS[device] = ws
+        return ws
+
+    def _own_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                  residual: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """``x @ w.T (+ bias) (+ residual)`` for the few rows of a decode step on coda_b200_proj_gemm, or None where
         that kernel does not apply (more than 64 rows, not bfloat16, K not a multiple of 64, unaligned views)."""
         B, L, K = x.shape
@@ -488,6 +501,11 @@ class CoDAGQALandmarkPerf2(nn.Module):
             self._gemm_ok[(rows, K, N)] = ok
         if not ok or not w.is_contiguous() or w.data_ptr() % 16:
             return None
+        ws = self._gemm_ok.get(("ws", rows, K, N))
+        if ws is None:
+            ws = int(lib.coda_b200_proj_gemm_workspace_bytes(rows, K, N))
+            self._gemm_ok[("ws", rows, K, N)] = ws
+        ws = self._gemm_workspace(x.device, ws)
 
         def rows_of(t):                      # (tensor, row stride) of t seen as [rows, features]
             if L == 1 and t.stride(2) == 1:
@@ -502,7 +520,8 @@ class CoDAGQALandmarkPerf2(nn.Module):
             residual, res_rs = rows_of(residual)
         y = torch.empty((B, L, N), device=x.device, dtype=x.dtype)
         check(lib.coda_b200_proj_gemm(x.data_ptr(), x_rs, rows, K, w.data_ptr(), N, _p(bias), _p(residual), res_rs,
-                                      y.data_ptr(), N, self._status_word(x.device).data_ptr(), _stream()), "coda_b200_proj_gemm")
+                                      y.data_ptr(), N, ws.data_ptr(), self._status_word(x.device).data_ptr(), _stream()),
+              "coda_b200_proj_gemm")
         return y
 
     def _project(self, x: torch.Tensor, need_kv: bool):

@@ -216,14 +216,21 @@ int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, in
  * q / k / v / lambda / write-gate projections, given here as ONE weight matrix whose rows are the five weights stacked,
  * bias likewise) and :467-470,514 (o_proj; `residual` adds the decoder's skip connection in the same pass: the product
  * (+ bias) is rounded to bf16 before the add, as a GEMM followed by an add would).  w is the nn.Linear weight as it is
- * ([out][in], dense); x, y and residual have row strides in elements (x's a multiple of 8, x 16-byte aligned); bias may be
- * NULL.  K must be a multiple of 64.  The weight rows are the MMA's M (tiles of 128), the tokens its N, K is split over the CTAs of a cluster and reduced
- * through distributed shared memory.  Launched as a programmatic dependent launch: the weight stream starts before the
- * kernel ahead of it on the stream has finished, x / residual / y are touched only after it has.  status: optional device
- * int, set non-zero if a bounded wait expired. */
+ * ([out][in], dense, 16-byte aligned); x, y and residual have row strides in elements (x's a multiple of 8, x 16-byte
+ * aligned); bias may be NULL.  K must be a multiple of 64.
+ * The weight rows are the MMA's M (tiles of 128), the tokens its N.  All tiles' k-blocks, laid end to end, are cut into one
+ * equal run per SM; a tile shared by several CTAs is summed through `workspace`: every contributor stores its fp32 partial
+ * tile there, and the one that arrives last (a counter per tile, nobody waits) adds them in a fixed order and writes the
+ * rows, so results are bit-reproducible.  workspace: coda_b200_proj_gemm_workspace_bytes(M, K, N) bytes on the device,
+ * 16-byte aligned, its first 4096 bytes ZERO before the first use (the kernel leaves them zero); one workspace may serve
+ * every call made on one stream (of the largest size asked for), calls that overlap on the GPU need their own.
+ * Launched as a programmatic dependent launch: the weight stream starts before the kernel ahead of it on the stream has
+ * finished; x, residual, workspace and y are touched only after it has.  status: optional device int, set non-zero if a
+ * bounded wait expired. */
 int coda_b200_proj_gemm_supported(int32_t M, int32_t K, int32_t N);
+int64_t coda_b200_proj_gemm_workspace_bytes(int32_t M, int32_t K, int32_t N);
 int coda_b200_proj_gemm(const void* x, int64_t x_rs, int32_t M, int32_t K, const void* w, int32_t N, const void* bias,
-                        const void* residual, int64_t res_rs, void* y, int64_t y_rs, int32_t* status,
+                        const void* residual, int64_t res_rs, void* y, int64_t y_rs, void* workspace, int32_t* status,
                         coda_stream_t stream);
 
 /* coda_b200_step_append_fused and coda_b200_decode_attend_prepared as ONE launch: the attention kernel's

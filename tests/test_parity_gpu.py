@@ -634,7 +634,9 @@ def test_token_writing_attention_back_to_back_replays_are_stable():
     (5, 512, 256, True, True),
     (1, 128, 64, False, False),         # half a weight tile, two k-blocks
     (17, 576, 1000, True, False),       # K = 9 k-blocks, N not a multiple of the tile
-    (8, 64, 130, True, True),           # a single k-block: no split
+    (8, 64, 130, True, True),           # a single k-block per tile: no tile is shared
+    (32, 8192, 10368, True, False),     # 70B shape's input projection: 81 tiles, runs of ~70 k-blocks crossing tile boundaries
+    (3, 4096, 128, False, True),        # one tile cut into 64 single-k-block runs
 ])
 def test_projection_gemm_matches_library_gemm(M, K, N, bias, res):
     """The decode step's projection kernel (tcgen05, weight rows as the MMA's M, split-K over a cluster, bias and
@@ -650,12 +652,18 @@ def test_projection_gemm_matches_library_gemm(M, K, N, bias, res):
     y = torch.full((M, N + 8), float("nan"), device="cuda", dtype=torch.bfloat16)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     assert lib.coda_b200_proj_gemm_supported(M, K, N)
-    for _ in range(2):                                              # twice: the second launch overlaps the first's tail
+    ws = torch.zeros(int(lib.coda_b200_proj_gemm_workspace_bytes(M, K, N)), dtype=torch.uint8, device="cuda")
+    outs = []
+    for _ in range(3):                      # again and again: the tile counters return to zero, the bits repeat
+        y.fill_(float("nan"))
         check(lib.coda_b200_proj_gemm(x.data_ptr(), x.stride(0), M, K, w.data_ptr(), N, None if b is None else b.data_ptr(),
-                                      None if r is None else r.data_ptr(), N, y.data_ptr(), N + 8, status.data_ptr(),
+                                      None if r is None else r.data_ptr(), N, y.data_ptr(), N + 8, ws.data_ptr(), status.data_ptr(),
                                       torch.cuda.current_stream().cuda_stream), "coda_b200_proj_gemm")
+        outs.append(y.clone())
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+    assert int(ws[:4096].view(torch.int32).abs().sum()) == 0, "tile counters must be back at zero"
+    assert torch.equal(outs[0][:, :N], outs[1][:, :N]) and torch.equal(outs[1][:, :N], outs[2][:, :N])
     ref = x.float() @ w.float().t()
     if bias:
         ref = ref + b.float()
@@ -673,7 +681,7 @@ def test_projection_gemm_matches_library_gemm(M, K, N, bias, res):
 
 @pytest.mark.gpu
 def test_decode_step_on_own_gemms_matches_library_gemms():
-    """`use_own_gemm` (default) swaps both projections of a decode step for coda_b200_proj_gemm; the step must agree
+    """`use_own_gemm` swaps both projections of a decode step for coda_b200_proj_gemm; the step must agree
     with the library-GEMM step to bf16 rounding, eagerly and through a captured stack step (where the kernels chain
     as programmatic dependent launches)."""
     from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack, _deep_copy_state
