@@ -44,8 +44,15 @@ def new_metrics(active_exact: int, active_summary: int) -> Dict[str, object]:
     return m
 
 
-def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream(device: Optional[torch.device] = None) -> int:
+    """Handle of the current CUDA stream (of ``device``, default the current device)."""
+    if _raw_stream is not None:
+        idx = device.index if device is not None and device.index is not None else torch.cuda.current_device()
+        return _raw_stream(idx)
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -524,6 +531,98 @@ class CoDAGQALandmarkPerf2(nn.Module):
               "coda_b200_proj_gemm")
         return y
 
+    def _decode_bundle(self, device, dtype):
+        """Everything an eager decode step needs besides the state, gathered once and re-validated cheaply: the fused
+        and transposed weights, the constant tables and their raw addresses.  ``step()`` is called once per layer per
+        token by adapter-driven loops, where the host time of walking ``nn.Module`` attributes and rebuilding cache
+        keys (~60 us per call) outweighs the kernels; the bundle is checked by module identity plus address and
+        version counter of every parameter it was built from.  None where the fused layout does not apply."""
+        c = self.__dict__.get("_bundle")
+        mods = self._modules
+        if c is not None and c["dev"] == device and c["dt"] == dtype:
+            ok = all(mods[n] is m for n, m in c["mods"])
+            if ok:
+                for prm, ver, ptr in c["stamps"]:
+                    if prm._version != ver or prm.data_ptr() != ptr:
+                        ok = False
+                        break
+            if ok:
+                return c
+        f = self._fused_weight()
+        wt = self._skinny_weights()
+        if f is None or wt is None or f[0].device != device or f[0].dtype != dtype:
+            self.__dict__["_bundle"] = None
+            return None
+        inv_freq, cos_t, sin_t, eta, nw = self._consts(device, dtype)
+        names = ("q_proj", "k_proj", "v_proj", "lambda_proj", "write_proj", "o_proj", "head_norm", "rope")
+        prms = [p for n in names[:6] for p in mods[n].parameters()] + [self.theta, self.summary_eta_logit, self.rope.inv_freq]
+        if nw is not None:
+            prms.append(self.head_norm.weight)
+        H, Hkv, Dh = self.num_heads, self.num_kv_heads, self.head_dim
+        es = f[0].element_size()
+        c = dict(dev=device, dt=dtype, mods=[(n, mods[n]) for n in names], stamps=[(p, p._version, p.data_ptr()) for p in prms],
+                 bias=f[1], w_in_t=wt[1], w_out_t=wt[2], npad=f[0].shape[0], nq=H * Dh, nkv=Hkv * Dh,
+                 off_k=H * Dh * es, off_v=(H * Dh + Hkv * Dh) * es, off_lam=(H * Dh + 2 * Hkv * Dh) * es,
+                 off_gate=(H * Dh + 2 * Hkv * Dh + H) * es, gated=self.write_policy != "none",
+                 inv_freq=inv_freq.data_ptr(), cos=cos_t.data_ptr(), sin=sin_t.data_ptr(), eta=eta.data_ptr(), nw=_p(nw),
+                 keep=(inv_freq, cos_t, sin_t, eta, nw, f, wt))
+        self.__dict__["_bundle"] = c
+        return c
+
+    def _step_eager_fast(self, x: torch.Tensor, st: CoDAGQALandmarkStatePerf2) -> Optional[torch.Tensor]:
+        """The default decode step (write, then attend) with as little host work as the launches allow; same kernels
+        and the same bits as the general path.  Returns None where it does not apply (the caller then takes the
+        general path)."""
+        if self.use_torch_ops or self.use_own_gemm or self.use_skinny_gemm_kernel or self.kernel_timers is not None:
+            return None
+        if st.metrics is not None or self.Me_min != self.Me_max or self.Ms_min != self.Ms_max or not self.detach_evicted:
+            return None
+        B = x.shape[0]
+        if B > self.SKINNY_ROWS or x.dtype != torch.bfloat16:
+            return None
+        dev = x.device
+        bd = self._decode_bundle(dev, x.dtype)
+        if bd is None:
+            return None
+        cfg = self._cfg(B, x.dtype, st)
+        if not (self._tuned_decode(cfg) and self._fused_write_ok(cfg)):
+            return None
+        pc = st.__dict__.get("_pc")
+        kptr = st.k_buf.data_ptr()
+        if pc is None or pc[0] != kptr or pc[2] is not st._exact_v_norm or pc[3] is not st._sum_lf_k_norm:
+            if not (st.k_buf.shape == (B, self.num_kv_heads, self.Lbuf, self.head_dim) and st.v_buf.shape == st.k_buf.shape
+                    and st.k_buf.is_contiguous() and st.v_buf.is_contiguous() and st.allowed.is_contiguous()
+                    and st.g_recent.dtype == torch.float32 and st.g_recent.is_contiguous() and st.mem_last_exact.is_contiguous()
+                    and st.k_buf.dtype == x.dtype and st.k_buf.device == dev
+                    and (st._exact_v_norm is None or (st._exact_v_norm.dtype == x.dtype and st._exact_v_norm.is_contiguous()))
+                    and (st._sum_lf_k_norm is None or (st._sum_lf_k_norm.dtype == x.dtype and st._sum_lf_k_norm.is_contiguous()))):
+                return None
+            st._events = None
+            pc = (kptr, self._ptrs(st), st._exact_v_norm, st._sum_lf_k_norm)
+            st.__dict__["_pc"] = pc
+        ptrs = pc[1]
+        y = torch.addmm(bd["bias"], x.reshape(B, -1), bd["w_in_t"])
+        base, npad = y.data_ptr(), bd["npad"]
+        if base % 16:
+            return None
+        s = _stream(dev)
+        rp = RingPos(st.pos, st.recent_idx, st.recent_filled, None)
+        qrec = self._decode_records(cfg, dev)
+        out = torch.empty((B, self.num_heads * self.head_dim), device=dev, dtype=x.dtype)
+        status = self._status_word(dev).data_ptr()
+        gate = base + bd["off_gate"] if bd["gated"] else None
+        rc = lib.coda_b200_step_write_fused(
+            C.byref(cfg), C.byref(ptrs), rp, base + bd["off_k"], npad, base + bd["off_v"], npad, gate, npad if gate else 0,
+            bd["inv_freq"], bd["eta"], base, npad, base + bd["off_lam"], npad, bd["cos"], bd["sin"], qrec.data_ptr(), s)
+        if rc:
+            check(rc, "coda_b200_step_write_fused")
+        rc = lib.coda_b200_decode_attend_prepared(C.byref(cfg), C.byref(ptrs), qrec.data_ptr(), bd["nw"], out.data_ptr(),
+                                                  out.shape[1], status, s)
+        if rc:
+            check(rc, "coda_b200_decode_attend_prepared")
+        self.advance_host_scalars(st)
+        return torch.mm(out, bd["w_out_t"]).view(B, 1, -1)
+
     def _project(self, x: torch.Tensor, need_kv: bool):
         """q, k, v, lambda logits, gate logits as (B, L, features) tensors (upstream attention.py:396-410,508)."""
         f = self._fused_weight() if need_kv else None
@@ -906,6 +1005,11 @@ class CoDAGQALandmarkPerf2(nn.Module):
         to the cache first and then attends over all slots, itself included."""
         B, L, _ = x.shape
         assert L == 1
+        if (attend and write_cache and include_current_in_attention and not self.training and x.is_cuda
+                and state.k_buf.shape[0] == B):
+            y = self._step_eager_fast(x, state)
+            if y is not None:
+                return y, state
         self._require_ready(x, state)
         cfg = self._cfg(B, x.dtype, state)
         qp = int(state.pos)

@@ -1,5 +1,8 @@
 // Projection post-processing: RoPE on q/k, the theta-rotated noise query, lambda / gate sigmoids.
 // One CTA per token; HBM-bound elementwise work (reads q,k once, writes q,k,q_noise once).
+// Two kernels with the same arithmetic: prep_vec_kernel moves 16-byte vectors (a thread owns whole RoPE pairs AND
+// whole noise-rotation pairs, so nothing crosses threads) and is used whenever rows are 16-byte aligned and the head
+// dimension allows; prep_kernel is the element-wise fallback for any layout.
 #include "coda_common.cuh"
 
 struct PrepParams {
@@ -86,6 +89,129 @@ __global__ void __launch_bounds__(256) prep_kernel(PrepParams p) {
   }
 }
 
+// 16-byte vectors of T <-> fp32
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void ld(const float* p, float (&o)[4]) { const float4 v = *reinterpret_cast<const float4*>(p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+  static __device__ __forceinline__ void st(float* p, const float (&o)[4]) { *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]); }
+};
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void ld(const bf16* p, float (&o)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { o[2 * j] = __uint_as_float(w[j] << 16); o[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+  }
+  static __device__ __forceinline__ void st(bf16* p, const float (&o)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { __nv_bfloat162 t = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]); w[j] = *reinterpret_cast<uint32_t*>(&t); }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// Vectorised variant.  Work item = one 16-byte chunk of a head row (interleaved pairs) or the two chunks c and
+// c + Dh/2 that hold each other's RoPE partners (half-split pairs).  The noise query always rotates (even, odd)
+// neighbours of the ROTATED row (primitives.py:58-80), which lie inside one chunk, so an item is self-contained.
+template <typename T, typename A>
+__global__ void __launch_bounds__(320) prep_vec_kernel(PrepParams p) {
+  constexpr int N = Vec16<T>::N;
+  extern __shared__ float sm[];
+  const int half = p.Dh >> 1;
+  float* cs = sm;                 // [half] cos, rounded to T
+  float* sn = sm + half;          // [half] sin
+  const int tid = threadIdx.x, NT = blockDim.x;
+  const long long ntok = (long long)p.B * p.L;
+  const long long pos_base = ring_now(p.rp, p.W).pos;
+  const int per_head = p.interleaved ? p.Dh / N : half / N;       // items per head row
+  const int nq = p.H * per_head, nk = p.k ? p.Hkv * per_head : 0;
+  for (long long tok = blockIdx.x; tok < ntok; tok += gridDim.x) {
+    const int b = (int)(tok / p.L), t = (int)(tok % p.L);
+    const long long pos = pos_base + t;
+    __syncthreads();                                               // the previous token's table is no longer read
+    for (int i = tid; i < half; i += NT) {
+      float ta = El<A>::rnd((float)pos);
+      float inv = El<A>::rnd(p.inv_freq[i]);
+      float ang = El<A>::rnd(__fmul_rn(ta, inv));
+      cs[i] = El<T>::rnd(El<A>::rnd(cosf(ang)));
+      sn[i] = El<T>::rnd(El<A>::rnd(sinf(ang)));
+    }
+    __syncthreads();
+    T* qt = (T*)p.q + (long long)b * p.q_bs + (long long)t * p.q_rs;
+    T* kt = p.k ? (T*)p.k + (long long)b * p.k_bs + (long long)t * p.k_rs : nullptr;
+    T* qnt = (T*)p.qn + tok * (long long)(p.H * p.Dh);
+    for (int w = tid; w < nq + nk; w += NT) {
+      const bool isq = w < nq;
+      const int ww = isq ? w : w - nq;
+      const int h = ww / per_head, c = ww % per_head;
+      T* row = (isq ? qt : kt) + h * p.Dh;
+      const T* cth = (const T*)p.cos_t + h * half;
+      const T* sth = (const T*)p.sin_t + h * half;
+      if (p.interleaved) {                  // primitives.py:99-106: pairs (2i, 2i+1) share cos/sin i
+        float x[N], o[N];
+        Vec16<T>::ld(row + c * N, x);
+#pragma unroll
+        for (int e = 0; e < N; e += 2) {
+          const int i = (c * N + e) >> 1;
+          const float cc = cs[i], ss = sn[i];
+          o[e] = t_sub<T>(t_mul<T>(x[e], cc), t_mul<T>(x[e + 1], ss));
+          o[e + 1] = t_add<T>(t_mul<T>(x[e], ss), t_mul<T>(x[e + 1], cc));
+        }
+        Vec16<T>::st(row + c * N, o);
+        if (isq) {
+          float n[N];
+#pragma unroll
+          for (int e = 0; e < N; e += 2) {
+            const int i = (c * N + e) >> 1;
+            const float ct = El<T>::ld(cth + i), st = El<T>::ld(sth + i);
+            n[e] = t_sub<T>(t_mul<T>(o[e], ct), t_mul<T>(o[e + 1], st));
+            n[e + 1] = t_add<T>(t_mul<T>(o[e], st), t_mul<T>(o[e + 1], ct));
+          }
+          Vec16<T>::st(qnt + h * p.Dh + c * N, n);
+        }
+      } else {                              // primitives.py:108-113: x*cos_full + rotate_half(x)*sin_full
+        float x1[N], x2[N], oa[N], ob[N];
+        Vec16<T>::ld(row + c * N, x1);
+        Vec16<T>::ld(row + half + c * N, x2);
+#pragma unroll
+        for (int e = 0; e < N; ++e) {
+          const float cc = cs[c * N + e], ss = sn[c * N + e];
+          oa[e] = t_add<T>(t_mul<T>(x1[e], cc), t_mul<T>(-x2[e], ss));
+          ob[e] = t_add<T>(t_mul<T>(x2[e], cc), t_mul<T>(x1[e], ss));
+        }
+        Vec16<T>::st(row + c * N, oa);
+        Vec16<T>::st(row + half + c * N, ob);
+        if (isq) {
+          float na[N], nb[N];
+#pragma unroll
+          for (int e = 0; e < N; e += 2) {
+            const int ia = (c * N + e) >> 1, ib = (half + c * N + e) >> 1;
+            const float cta = El<T>::ld(cth + ia), sta = El<T>::ld(sth + ia);
+            const float ctb = El<T>::ld(cth + ib), stb = El<T>::ld(sth + ib);
+            na[e] = t_sub<T>(t_mul<T>(oa[e], cta), t_mul<T>(oa[e + 1], sta));
+            na[e + 1] = t_add<T>(t_mul<T>(oa[e], sta), t_mul<T>(oa[e + 1], cta));
+            nb[e] = t_sub<T>(t_mul<T>(ob[e], ctb), t_mul<T>(ob[e + 1], stb));
+            nb[e + 1] = t_add<T>(t_mul<T>(ob[e], stb), t_mul<T>(ob[e + 1], ctb));
+          }
+          Vec16<T>::st(qnt + h * p.Dh + c * N, na);
+          Vec16<T>::st(qnt + h * p.Dh + half + c * N, nb);
+        }
+      }
+    }
+    for (int h = tid; h < p.H; h += NT) {
+      const float z = El<T>::ld((const T*)p.lam_logit + (long long)b * p.lam_bs + (long long)t * p.lam_rs + h);
+      p.lam[tok * p.H + h] = t_sigmoid<T>(z);
+    }
+    if (tid == 0 && p.gate != nullptr) {
+      float g = 1.0f;                       // write_policy "none": attention.py:407-408
+      if (p.gated) g = t_sigmoid<T>(El<T>::ld((const T*)p.gate_logit + (long long)b * p.gate_bs + (long long)t * p.gate_rs));
+      p.gate[tok] = g;
+    }
+  }
+}
+
 extern "C" int coda_b200_prep(const coda_layer_cfg* cfg, int32_t L, coda_ring_pos rp,
                               void* q, int64_t q_bs, int64_t q_rs,
                               void* k, int64_t k_bs, int64_t k_rs,
@@ -111,7 +237,12 @@ extern "C" int coda_b200_prep(const coda_layer_cfg* cfg, int32_t L, coda_ring_po
   const size_t smem = sizeof(float) * (size_t)(cfg->Dh + cfg->H * cfg->Dh);
   CODA_REQUIRE(smem <= 200 * 1024, CODA_ERR_LIMIT, "prep: H*Dh = %d exceeds the shared-memory row limit", cfg->H * cfg->Dh);
   cudaStream_t s = (cudaStream_t)stream;
+  // 16-byte vectors need aligned rows and chunks that do not straddle a RoPE half / head row
+  const int vn = cfg->dtype == CODA_F32 ? 4 : 8;
+  const bool vec = ((cfg->rope_interleaved ? cfg->Dh : cfg->Dh / 2) % vn) == 0 && ((uintptr_t)q | (uintptr_t)q_noise) % 16 == 0 &&
+                   (q_bs | q_rs) % vn == 0 && (k == nullptr || ((uintptr_t)k % 16 == 0 && (k_bs | k_rs) % vn == 0));
 #define LAUNCH(T, A) do { \
+    if (vec) { prep_vec_kernel<T, A><<<grid, 320, sizeof(float) * (size_t)cfg->Dh, s>>>(p); break; } \
     if (smem > 48 * 1024) cudaFuncSetAttribute(prep_kernel<T, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     prep_kernel<T, A><<<grid, 256, smem, s>>>(p); } while (0)
   if (cfg->dtype == CODA_F32) {

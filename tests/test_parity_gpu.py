@@ -713,3 +713,40 @@ def test_decode_step_on_own_gemms_matches_library_gemms():
         assert rel_err(a.k_buf, b.k_buf) < 5e-3 and rel_err(c.k_buf, b.k_buf) < 5e-3
     assert rel_err(torch.cat(ya, 1), torch.cat(yb, 1)) < 1e-2
     assert rel_err(torch.cat(yc, 1), torch.cat(yb, 1)) < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("Dh,H,Hkv", [(128, 8, 2), (64, 9, 3), (32, 4, 2)])
+def test_vectorised_projection_postprocessing_equals_elementwise_kernel(dtype, interleaved, Dh, H, Hkv):
+    """RoPE of q and k, the theta-rotated noise query and the two sigmoids: the 16-byte-vector kernel (aligned rows)
+    and the element-wise kernel (here forced by rows that start 2 or 4 bytes off a 16-byte boundary) do the same
+    arithmetic, so their results are bit-equal."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    from tests.scenarios import randomize_weights
+    torch.manual_seed(1)
+    mod = CoDAGQALandmarkPerf2(embed_dim=H * Dh, num_heads=H, num_kv_heads=Hkv, window=16, num_landmarks_exact=4,
+                               num_landmarks_summary=4, rope_interleaved=interleaved, rope_base=1e6).eval()
+    randomize_weights(mod, 2)
+    mod = mod.to(dtype).cuda()
+    B, L = 3, 37
+    st = mod.init_state(batch_size=B, device="cuda", dtype=dtype)
+    cfg = mod._cfg(B, dtype, st)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    nq, nk = H * Dh, Hkv * Dh
+    pad = 8 if dtype == torch.bfloat16 else 4                    # keeps every row start 16-byte aligned in the base layout
+    width = (nq + nk + H + 1 + pad + 7) // 8 * 8
+    outs = []
+    for shift in (0, 1):                                         # shift 1: every row starts one element off alignment
+        y = torch.zeros(B, L, width + 8, device="cuda", dtype=dtype)
+        src = torch.randn(B, L, nq + nk + H + 1, device="cuda", generator=torch.Generator(device="cuda").manual_seed(4)).to(dtype)
+        y[..., shift:shift + nq + nk + H + 1] = src
+        q, k = y[..., shift:shift + nq], y[..., shift + nq:shift + nq + nk]
+        lam_logit, gate_logit = y[..., shift + nq + nk:shift + nq + nk + H], y[..., shift + nq + nk + H:shift + nq + nk + H + 1]
+        qn, lam, gate = mod._prep(cfg, L, 1000, q, k, lam_logit, gate_logit, True)
+        outs.append((q.clone(), k.clone(), qn.clone(), lam.clone(), gate.clone()))
+    torch.cuda.synchronize()
+    for a, b, name in zip(outs[0], outs[1], ("q", "k", "q_noise", "lambda", "gate")):
+        assert torch.equal(a, b), f"{name} differs between the vector and the element-wise kernel"
+    assert not torch.equal(outs[0][0], outs[0][2])               # the noise rotation did something
