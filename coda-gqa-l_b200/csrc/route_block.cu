@@ -426,6 +426,8 @@ __global__ void __launch_bounds__(128) route_apply_kernel(RouteParams p) {
         else { ak[i] = t_add<T>(ak[i], t_mul<T>(xk[i], w)); av[i] = t_add<T>(av[i], t_mul<T>(xv[i], w)); }
       }
     }
+    // the slot's EMA rate depends on the head only: one sigmoid per run, not one per element
+    const float eta_run = (exact || fresh) ? 1.f : t_sigmoid<T>(p.eta_logit[h]);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const int e = e0 + i;
@@ -439,7 +441,7 @@ __global__ void __launch_bounds__(128) route_apply_kernel(RouteParams p) {
         El<T>::st(qv, nv);
         stash[e] = nv;
       } else {                                                         // phase-safe EMA
-        const float eta = fresh ? 1.f : t_sigmoid<T>(p.eta_logit[hh]);
+        const float eta = fresh ? 1.f : (runs ? eta_run : t_sigmoid<T>(p.eta_logit[hh]));
         El<T>::st(qv, t_add<T>(ov[i], t_mul<T>(eta, t_sub<T>(t_div<T>(av[i], cden), ov[i]))));
         if (dd >= lf) {
           const float inc = El<T>::rnd(__fmul_rn(t_div<T>(ak[i], cden), c.energy_scale));
