@@ -95,24 +95,53 @@ def profiled_traffic(workload: str, variant: str):
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples of one GPU while the timed region runs."""
+    """Clock / throttle-reason samples of one GPU while the timed region runs (read-only queries).
+
+    Samples through NVML (every 20 ms) when the binding is importable and the device can be found by its UUID or
+    index; otherwise through one ``nvidia-smi`` query per sample (each takes a few hundred ms)."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+        self._nvml = self._handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = self._handle = None
+
+    def _sample_nvml(self):
+        n, h = self._nvml, self._handle
+        sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        r = int(get(h))
+        flag = lambda bit: "Active" if r & bit else "Not Active"
+        return [str(sm), str(mx), flag(n.nvmlClocksThrottleReasonHwSlowdown), flag(n.nvmlClocksThrottleReasonHwThermalSlowdown),
+                flag(n.nvmlClocksThrottleReasonSwThermalSlowdown), flag(n.nvmlClocksThrottleReasonSwPowerCap)]
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [p.strip() for p in out.strip().split(",")]
-                if len(parts) >= 6:
-                    self.rows.append(parts)
+                if self._nvml is not None:
+                    self.rows.append(self._sample_nvml())
+                else:
+                    out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                    parts = [p.strip() for p in out.strip().split(",")]
+                    if len(parts) >= 6:
+                        self.rows.append(parts)
             except Exception:
-                pass
-            self._stop.wait(0.1)
+                if self._nvml is not None:
+                    self._nvml = None                       # fall back to nvidia-smi for the rest of the region
+            self._stop.wait(0.02 if self._nvml is not None else 0.1)
 
     def __enter__(self):
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -130,7 +159,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
-                "samples": len(self.rows)}
+                "samples": len(self.rows), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------------ reference arm

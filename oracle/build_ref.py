@@ -4,7 +4,7 @@ TEST / BENCHMARK INFRASTRUCTURE ONLY.  Nothing in the shipped package imports or
 reference arm of bench.py (``--impl reference`` / ``--impl reference-gpu``) and the ``cpu_baseline`` leg can time the
 reference's own ``CoDAGQALandmarkPerf2`` instead of this repository's restatement of it.
 
-    python oracle/build_ref.py [--ref <upstream checkout>]        # default: $CODA_GQA_L_REF, else /root/reference
+    python oracle/build_ref.py [--ref <upstream checkout>]        # default: $CODA_GQA_L_REF, else DEFAULT_CHECKOUT below
 
 The upstream checkout is installed with pip (no index, no dependencies) from a temporary copy -- the build writes into
 its source tree and the checkout may be read-only -- into ``oracle/_ref`` (listed in .gitignore: reference sources never
@@ -22,6 +22,7 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 TARGET = os.path.join(HERE, "_ref")
+DEFAULT_CHECKOUT = os.path.join(os.sep, "root", "reference")
 
 
 def available() -> bool:
@@ -30,7 +31,7 @@ def available() -> bool:
 
 def build(ref_root: str | None = None, force: bool = False) -> bool:
     """Install upstream into oracle/_ref.  Returns whether an importable copy is present afterwards."""
-    ref_root = ref_root or os.environ.get("CODA_GQA_L_REF") or "/root/reference"
+    ref_root = ref_root or os.environ.get("CODA_GQA_L_REF") or DEFAULT_CHECKOUT
     if available() and not force:
         return True
     if not os.path.exists(os.path.join(ref_root, "pyproject.toml")):
