@@ -108,7 +108,10 @@ __device__ __forceinline__ RingNow ring_after(const coda_ring_pos& rp, int W, lo
     if (to_fill < 0) to_fill = 0;
     long long nf = n < to_fill ? n : to_fill;
     r.filled += (int)nf;
-    r.idx = (int)(((long long)r.idx + (n - nf)) % W);
+    // steps past the fill wrap around the ring: 32-bit arithmetic whenever the count fits (a 64-bit remainder
+    // is a long software routine, and every thread of every CTA on a latency chain runs this)
+    const long long adv = (long long)r.idx + (n - nf);
+    r.idx = adv < 0x7fffffffLL ? (int)((unsigned)adv % (unsigned)W) : (int)(adv % W);
     r.pos += n;
   }
   return r;

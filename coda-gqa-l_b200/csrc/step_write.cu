@@ -580,12 +580,14 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
     }
     return acc0 + acc1;
   };
-  // the rounded per-head dot of bank slot m goes to every CTA of the cluster
-  auto send = [&](int m, float acc) {
+  // The rounded per-head dot of bank slot m goes to every CTA of the cluster.  After the butterfly reduction all
+  // `per` lanes of the row hold the sum, so lane `first` of the row serves ranks first, first + per, ...: one
+  // remote store per lane at the sizes in use (Hkv <= lanes per row) instead of a loop over the ranks in one lane.
+  auto send = [&](int m, float acc, int first, int per) {
     const float v = El<T>::rnd(acc);
     const uint32_t local = tma::smem_u32(xdots + h * MM + m);
     #pragma unroll 1
-    for (int rk = 0; rk < Hkv; ++rk) {
+    for (int rk = first; rk < Hkv; rk += per) {
       uint32_t remote;
       asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rk));
       asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
@@ -601,14 +603,14 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
       float acc = ch < nce ? chunk_dot(v, ae) : 0.f;
 #pragma unroll
       for (int o = CE / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ch < nce && ce == 0) send(ch / CE, acc);
+      if (ch < nce) send(ch / CE, acc, ce, CE);
     };
     auto summary_pass = [&](const uint4& v, int j) {
       const int ch = tid + j * NT;
       float acc = ch < ncs ? chunk_dot(v, as) : 0.f;
 #pragma unroll
       for (int o = CS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ch < ncs && cs_ == 0) send(Me + ch / CS, acc);
+      if (ch < ncs) send(Me + ch / CS, acc, cs_, CS);
     };
 #pragma unroll
     for (int j = 0; j < PE; ++j) if (j * NT < nce) exact_pass(pe[j], j);
