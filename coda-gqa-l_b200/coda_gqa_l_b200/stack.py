@@ -60,7 +60,8 @@ class CoDAStack(nn.Module):
     def capture_step(self, states, example_x: torch.Tensor, warmup: int = 2) -> None:
         """Capture one decode step of the whole stack.  The states' contents are preserved: the warm-up
         steps run on the live buffers and are undone by restoring a snapshot of every arena."""
-        dev = example_x.device
+        dev = states[0].k_buf.device
+        example_x = example_x.to(dev)
         snaps = [(st._arena.clone() if st._arena is not None else None,
                   (st.pos, st.recent_idx, st.recent_filled)) for st in states]
         if any(s[0] is None for s in snaps):
@@ -84,8 +85,7 @@ class CoDAStack(nn.Module):
         rope_cs = None
         if plan is not None and self._shared_rope(states, x_static.dtype):      # (compares tensors: outside the capture)
             rope_cs = torch.empty(self.layers[0].head_dim, dtype=torch.float32, device=dev)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        def body(h):
             # Routing of the tokens this step evicts needs the states only: all layers' in one launch up front
             # (one layer's routing is a chain of memory round trips; side by side they are bandwidth-bound), so
             # that a layer's own chain is projection -> new token's write -> attention -> output projection.
@@ -99,16 +99,31 @@ class CoDAStack(nn.Module):
                 check(lib.coda_b200_rope_table(C.byref(plan[0]), rps[0], l0._consts(dev, x_static.dtype)[0].data_ptr(),
                                                rope_cs.data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
                       "coda_b200_rope_table")
-            h = x_static
             for layer, st, rp in zip(self.layers, states, rps):
                 h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h if self.residual else None,
                                          rope_cs=rope_cs)
             check(lib.coda_b200_advance_steps(ctr.data_ptr(), 1, torch.cuda.current_stream(dev).cuda_stream),
                   "coda_b200_advance_steps")
-            out_static = h
+            return h
+
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out_static = body(x_static)
+        # The same step with its host traffic inside the graph: pinned input -> device, the step, result -> pinned
+        # output.  One launch per token for a caller that feeds tokens from the host (step_graph_host); both graphs
+        # advance the same device counter, so replays of either may be mixed.
+        x_pin = torch.empty(x_static.shape, dtype=x_static.dtype).pin_memory()
+        x_pin.copy_(x_static)
+        out_pin = torch.empty(out_static.shape, dtype=out_static.dtype).pin_memory()
+        gh = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gh):
+            x_static.copy_(x_pin, non_blocking=True)
+            out_h = body(x_static)
+            out_pin.copy_(out_h, non_blocking=True)
         # Everything the graph's launches point at is kept alive with it (plan, table, the layers' derived weight and
         # constant tensors), and what they were is noted so that a replay after any of them changed re-captures.
         self._graph = dict(graph=g, x=x_static, out=out_static, ctr=ctr, plan=plan, rope_cs=rope_cs,
+                           host_graph=gh, x_pin=x_pin, out_pin=out_pin, out_host_dev=out_h,
                            states=list(states), key=self._graph_key(states, x_static.dtype),
                            expect=[(st.pos, st.recent_idx, st.recent_filled) for st in states],
                            keep=[(l._fused, l._wt, l._const_cache.get("k"), l._qrec, l._status) for l in self.layers])
@@ -168,9 +183,8 @@ class CoDAStack(nn.Module):
         return cfg, buf
 
     @torch.no_grad()
-    def step_graph(self, x: torch.Tensor, states) -> torch.Tensor:
-        """Replay the captured step on ``x`` (captures on first use).  Returns the stack's static output
-        buffer, which the next replay overwrites."""
+    def _live_graph(self, x: torch.Tensor, states):
+        """The captured step for these states, re-captured when it no longer describes them."""
         G = self._graph
         if G is not None:
             # Ring scalars are baked at capture time and advanced by the graph's own device counter, so a write that
@@ -184,9 +198,30 @@ class CoDAStack(nn.Module):
         if G is None:
             self.capture_step(states, x)
             G = self._graph
-        G["x"].copy_(x, non_blocking=True)
-        G["graph"].replay()
+        return G
+
+    def _replayed(self, G, states) -> None:
         for layer, st in zip(self.layers, states):
             layer.advance_host_scalars(st)
         G["expect"] = [(st.pos, st.recent_idx, st.recent_filled) for st in states]
+
+    def step_graph(self, x: torch.Tensor, states) -> torch.Tensor:
+        """Replay the captured step on ``x`` (captures on first use).  Returns the stack's static output
+        buffer, which the next replay overwrites."""
+        G = self._live_graph(x, states)
+        G["x"].copy_(x, non_blocking=True)
+        G["graph"].replay()
+        self._replayed(G, states)
         return G["out"]
+
+    def step_graph_host(self, x_host: torch.Tensor, states) -> torch.Tensor:
+        """One decode step fed from and answered to the host in ONE launch: ``x_host`` (a CPU tensor) is copied into
+        the stack's pinned input buffer, and the replayed graph carries the host-to-device copy, the step and the
+        device-to-host copy of the result.  Returns the pinned CPU output buffer; it is valid once the current stream
+        has been synchronised and is overwritten by the next call (so synchronise before calling again: the input
+        buffer is rewritten by the host at once)."""
+        G = self._live_graph(x_host, states)
+        G["x_pin"].copy_(x_host)
+        G["host_graph"].replay()
+        self._replayed(G, states)
+        return G["out_pin"]

@@ -243,3 +243,36 @@ def test_a_wait_that_runs_out_reports_and_releases_the_cta():
     assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0          # the context still works
     with pytest.raises(RuntimeError):
         check(lib.coda_b200_selftest_bounded_wait(0, status.data_ptr(), report.data_ptr(), None), "selftest")
+
+
+@pytest.mark.gpu
+def test_host_fed_captured_step_equals_device_fed_one():
+    """`step_graph_host` carries the host-to-device copy, the step and the device-to-host copy in one graph; its
+    results and the states it leaves equal those of `step_graph` on a device tensor bit for bit, and replays of
+    the two graphs may be mixed (they advance one device counter)."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack, _deep_copy_state
+    kw = dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=8, num_landmarks_summary=8)
+    layers = []
+    for i in range(2):
+        torch.manual_seed(i)
+        layers.append(CoDAGQALandmarkPerf2(**kw).eval().to(torch.bfloat16).cuda())
+    sa_stack, sb_stack = CoDAStack(layers), CoDAStack(layers)
+    torch.manual_seed(6)
+    sa = sa_stack.init_states(batch_size=3, device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(3, 90, 256, device="cuda") * 0.5).to(torch.bfloat16)
+    sa_stack.prefill(x[:, :40], sa, block_size=16)
+    sb = [_deep_copy_state(s) for s in sa]
+    xh = x.cpu().pin_memory()
+    for t in range(40, 90):
+        if t % 5 == 2:                                   # a device-fed replay in between
+            ya = sa_stack.step_graph(x[:, t:t + 1], sa).clone()
+        else:
+            out = sa_stack.step_graph_host(xh[:, t:t + 1], sa)
+            torch.cuda.current_stream().synchronize()
+            assert out.device.type == "cpu" and out.is_pinned()
+            ya = out.cuda()
+        yb = sb_stack.step_graph(x[:, t:t + 1], sb)
+        assert torch.equal(ya, yb), f"token {t}"
+    for a, b in zip(sa, sb):
+        assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
+        assert torch.equal(a._arena, b._arena)
