@@ -300,9 +300,15 @@ __global__ void __launch_bounds__(512) step_write_kernel(StepParams p) {
 //   0: everything (route the evicted token, then the new token takes its ring slot; fused mode: + record)
 //   1: routing only: banks, routing caches, LRU stamps, slot flags, event record; the ring is left alone
 //   2: the new token only, after a MODE 1 launch on the same ring position: ring slot, gate, record
-template <typename T, int DH, int MODE>
+//
+// STAGE: both routing caches of the head (contiguous, 16-byte aligned) are brought into shared memory by two
+// bulk copies issued by the first thread at entry instead of into registers by every thread: the scoring loop
+// reads them from there, no thread holds cache chunks across the entry phase, and more CTAs fit an SM.  The
+// launcher adds their bytes (rounded up to 16) to the dynamic shared memory and picks STAGE only when they fit.
+template <typename T, int DH, int MODE, bool STAGE = false>
 __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   constexpr bool ROUTE = MODE != 2, APPEND = MODE != 1;
+  static_assert(!STAGE || MODE == 1, "staged caches are for the routing-only launch");
   constexpr int NT = 256, LF = DH / 2, LFD = DH - LF;
   constexpr int EPV = 16 / (int)sizeof(T);                // elements per 16-byte chunk
   constexpr int CE = DH / EPV, CS = LFD / EPV;            // chunks per exact / summary routing-cache row (powers of two <= 32)
@@ -324,6 +330,9 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   long long* s_last = reinterpret_cast<long long*>((reinterpret_cast<uintptr_t>(sc + MM) + 7) & ~(uintptr_t)7);  // [Me]
   unsigned char* s_al = reinterpret_cast<unsigned char*>(s_last + Me);                                           // [Lbuf] slot flags before the write
   unsigned char* s_used = s_al + W;                                                                              // [MM] the banks' part
+  unsigned char* stage_e = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(s_al + Lbuf) + 15) & ~(uintptr_t)15);   // STAGE: [Me][DH] T
+  unsigned char* stage_s = stage_e + (size_t)Me * DH * sizeof(T);                                                // STAGE: [Ms][LFD] T
+  __shared__ __align__(8) uint64_t s_stage_bar;
 
   T* kb = (T*)p.st.k_buf + ((long long)b * Hkv + h) * Lbuf * DH;       // this head's planes
   T* vb = (T*)p.st.v_buf + ((long long)b * Hkv + h) * Lbuf * DH;
@@ -354,10 +363,21 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   const uint4* kn4 = reinterpret_cast<const uint4*>(knorm);
   const int nce = Me * CE, ncs = Ms * CS;
   uint4 pe[PE], ps[PS];
+  if constexpr (STAGE) {
+    if (tid == 0) {
+      tma::mbar_init(&s_stage_bar, 1);
+      tma::fence_barrier_init();
+      const uint32_t be = (uint32_t)((size_t)Me * DH * sizeof(T)), bs = (uint32_t)((size_t)Ms * LFD * sizeof(T));
+      tma::mbar_expect_tx(&s_stage_bar, be + bs);
+      if (be > 0) tma::bulk_load(stage_e, vnorm, be, &s_stage_bar);
+      if (bs > 0) tma::bulk_load(stage_s, knorm, bs, &s_stage_bar);
+    }
+  } else {
 #pragma unroll
-  for (int j = 0; j < PE; ++j) pe[j] = (ROUTE && tid + j * NT < nce) ? vn4[tid + j * NT] : make_uint4(0u, 0u, 0u, 0u);
+    for (int j = 0; j < PE; ++j) pe[j] = (ROUTE && tid + j * NT < nce) ? vn4[tid + j * NT] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-  for (int j = 0; j < PS; ++j) ps[j] = (ROUTE && tid + j * NT < ncs) ? kn4[tid + j * NT] : make_uint4(0u, 0u, 0u, 0u);
+    for (int j = 0; j < PS; ++j) ps[j] = (ROUTE && tid + j * NT < ncs) ? kn4[tid + j * NT] : make_uint4(0u, 0u, 0u, 0u);
+  }
   // slot flags and LRU stamps: requested into registers now, parked in shared memory once every other request
   // is out (a load -> shared-store loop would cost one memory round trip per loop); Lbuf <= 4 * NT, Me <= NT
   uint8_t alr[4];
@@ -535,6 +555,7 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
   if (!full || !ROUTE) {                                  // ring still filling (memory_banks.py:195-201; uniform over the grid), or routing done by an earlier launch
     if (fused) write_record(-1, -1);
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    if constexpr (STAGE) tma::mbar_wait(&s_stage_bar, 0, p.status, 31);    // no copy may be in flight into a CTA that leaves
     if (APPEND) {
       if (is_k) El<T>::st(kb + (long long)ev * DH + d, new_k);
       if (is_v) vb[(long long)ev * DH + d] = nv_raw;
@@ -612,6 +633,21 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
       for (int o = CS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (ch < ncs) send(Me + ch / CS, acc, cs_, CS);
     };
+    if constexpr (STAGE) {
+      tma::mbar_wait(&s_stage_bar, 0, p.status, 31);
+      const uint4* se4 = reinterpret_cast<const uint4*>(stage_e);
+      const uint4* ss4 = reinterpret_cast<const uint4*>(stage_s);
+      #pragma unroll 2
+      for (int j = 0; j * NT < nce; ++j) {
+        const int ch = tid + j * NT;
+        exact_pass(ch < nce ? se4[ch] : make_uint4(0u, 0u, 0u, 0u), j);
+      }
+      #pragma unroll 2
+      for (int j = 0; j * NT < ncs; ++j) {
+        const int ch = tid + j * NT;
+        summary_pass(ch < ncs ? ss4[ch] : make_uint4(0u, 0u, 0u, 0u), j);
+      }
+    } else {
 #pragma unroll
     for (int j = 0; j < PE; ++j) if (j * NT < nce) exact_pass(pe[j], j);
     #pragma unroll 1
@@ -625,6 +661,7 @@ __device__ __forceinline__ void step_cluster_body(const StepParams& p) {
     for (int j = PS; j * NT < ncs; ++j) {
       const int ch = tid + j * NT;
       summary_pass(ch < ncs ? kn4[ch] : make_uint4(0u, 0u, 0u, 0u), j);
+    }
     }
   }
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -920,14 +957,14 @@ __global__ void __launch_bounds__(256) step_write_cluster_kernel(StepParams p) {
 // Routing (MODE 1) of MANY layers' states in one launch: blockIdx.z picks the layer's parameter block from a
 // device array.  The routing of one layer is a latency chain that keeps an SM's resources while it waits; all
 // layers' chains side by side fill the machine and are bounded by memory bandwidth instead.
-template <typename T, int DH>
-__global__ void __launch_bounds__(256, 4) step_route_batched_kernel(const StepParams* __restrict__ layers) {
+template <typename T, int DH, bool STAGE, int NCTA>
+__global__ void __launch_bounds__(256, NCTA) step_route_batched_kernel(const StepParams* __restrict__ layers) {
   __shared__ StepParams sp;
   static_assert(sizeof(StepParams) % 4 == 0, "StepParams is copied word by word");
   const uint32_t* src = reinterpret_cast<const uint32_t*>(layers + blockIdx.z);
   for (int i = threadIdx.x; i < (int)(sizeof(StepParams) / 4); i += 256) reinterpret_cast<uint32_t*>(&sp)[i] = src[i];
   __syncthreads();
-  step_cluster_body<T, DH, 1>(sp);
+  step_cluster_body<T, DH, 1, STAGE>(sp);
 }
 
 template <typename T, int DH, int MODE>
@@ -1146,8 +1183,20 @@ extern "C" int coda_b200_step_route_batched(const coda_layer_cfg* cfg, const voi
   at[0].val.clusterDim.x = cfg->Hkv; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   lc.attrs = at; lc.numAttrs = 1;
   const StepParams* plan = (const StepParams*)plan_dev;
-  cudaError_t e = cfg->Dh == 128 ? cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 128>, plan)
-                                 : cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 64>, plan);
+  // both routing caches of a head in shared memory when they fit beside the rest (six CTAs per SM at the 7B shape)
+  const size_t stage_bytes = ((size_t)cfg->Me * cfg->Dh + (size_t)cfg->Ms * (cfg->Dh - cfg->Dh / 2)) * 2;
+  const bool stage = stage_bytes > 0 && stage_bytes % 16 == 0 && ((size_t)cfg->Me * cfg->Dh * 2) % 16 == 0 &&
+                     lc.dynamicSmemBytes + 16 + stage_bytes <= 30 * 1024;
+  cudaError_t e;
+  if (stage) {
+    lc.dynamicSmemBytes += 16 + stage_bytes;
+    // five CTAs per SM measured best at the 7B shape (4: 122 us, 5: 111 us, 6: 114 us for 32 layers x 32 states)
+    e = cfg->Dh == 128 ? cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 128, true, 5>, plan)
+                       : cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 64, true, 5>, plan);
+  } else {
+    e = cfg->Dh == 128 ? cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 128, false, 4>, plan)
+                       : cudaLaunchKernelEx(&lc, step_route_batched_kernel<bf16, 64, false, 4>, plan);
+  }
   if (e != cudaSuccess) { coda_set_error("step_route_batched: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
   return CODA_OK;
 }
