@@ -50,6 +50,7 @@ struct DecodeParams {
   const bf16* cos_t; const bf16* sin_t;
   const float* rope_cs;                           // optional: cos [Dh/2] | sin [Dh/2] of the token's position, precomputed
   bf16* k_buf; bf16* v_buf; uint8_t* allowed_w; float* g_recent;
+  long long* trace;
 };
 
 using tma::smem_u32; using tma::mbar_init; using tma::mbar_expect_tx; using tma::mbar_arrive; using tma::mbar_try;
@@ -202,6 +203,9 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
 
   __shared__ int s_abort;                          // set by the first bounded wait of this CTA that expires
   int* const abortw = &s_abort;
+  long long* const tr = (p.trace != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
+                            ? p.trace + (APPEND ? 0 : 64) + (blockIdx.x == 0 ? 0 : 32) : nullptr;
+  if (tr && tid == 0) tr[0] = clock64();
   if (tid == 0) {
     s_abort = 0;
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
@@ -213,6 +217,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   __syncthreads();
   // everything above touched no global memory: from here on the previous kernel's results are needed
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tr && tid == 0) tr[1] = clock64();
 
   // ---- APPEND: the new token's inputs of one plane, as the auxiliary threads hold them between request and use ----
   constexpr int HALF = DH / 2;
@@ -274,6 +279,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       if (p.rope_cs != nullptr) { if (at < DH) inv_f = p.rope_cs[at]; }      // the table entry itself
       else if (at < HALF) inv_f = p.inv_freq[at];
       if ((int)blockIdx.x < nplanes) load_inputs(blockIdx.x, in);
+      if (tr && at == 0) tr[2] = clock64();
     }
     __syncthreads();
   }
@@ -298,6 +304,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         for (int s = 0; s < nst; ++s) {
           if (pending && record_free(i + 1)) { load_record(plane + gridDim.x, i + 1); pending = false; }
           if (round > 0) mbar_wait(&empty[bi], (round - 1) & 1, p.status, 1, abortw);
+          if (tr && i == 0 && s == 0) tr[3] = clock64();
           mbar_expect_tx(&full[bi], 2 * TILE_BYTES);
           unsigned char* kd = stage0 + bi * 2 * TILE_BYTES;
           unsigned char* vd = kd + TILE_BYTES;
@@ -421,7 +428,9 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         sCS[at] = bf16_round(cc); sCS[HALF + at] = bf16_round(ss);
       }
       asm volatile("bar.sync 2, 128;" ::: "memory");       // the four auxiliary warps
+      if (tr && at == 0) tr[4] = clock64();
       build_record(blockIdx.x, 0, in);
+      if (tr && at == 0) tr[5] = clock64();
       if ((int)(blockIdx.x + gridDim.x) < nplanes) load_inputs(blockIdx.x + gridDim.x, in);
     }
     int i = 0;
@@ -494,6 +503,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(comb_free);
+      if (tr && aw == 0 && lane == 0 && i < 2) tr[16 + i] = clock64();
     }
     return;
   }
@@ -510,6 +520,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
     const int buf = i & 1;
     mbar_wait(&q_ready[buf], (i >> 1) & 1, p.status, 3, abortw);
+    if (tr && tid == 0 && i < 2) tr[6 + 4 * i] = clock64();
     const unsigned char* rec = rec0 + buf * L.rec_stride;
     const uint8_t* al_s = rec + mask_off;
     // B fragments of Q^T: one ldmatrix.x4 covers two k-steps of one n-tile (matrices: dh chunks 4j .. 4j+3)
@@ -538,6 +549,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
 
     for (int s = s0; s < nst; s += 2) {
       mbar_wait(&full[bi], round & 1, p.status, 2, abortw);
+      if (tr && tid == 0 && i < 2 && s == s0) tr[7 + 4 * i] = clock64();
       const uint32_t kb = smem_u32(stage0 + bi * 2 * TILE_BYTES);
       const uint32_t vb = kb + TILE_BYTES;
       if (APPEND) {
@@ -619,6 +631,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     }
 
     __syncwarp();
+    if (tr && tid == 0 && i < 2) tr[8 + 4 * i] = clock64();
     if (lane == 0) mbar_arrive(&q_free[buf]);              // queries are in registers, the mask is no longer read
     // ---- hand the partial softmax of this warp to the auxiliary warps ----
 #pragma unroll
@@ -661,6 +674,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(comb_full);
+    if (tr && tid == 0 && i < 2) tr[9 + 4 * i] = clock64();
   }  // plane loop
 }
 
@@ -718,6 +732,7 @@ DecodeParams make_params(const coda_layer_cfg* cfg, const coda_state_ptrs* st, v
   p.rp = coda_ring_pos{0, 0, 0, nullptr}; p.W = cfg->W;
   p.qrec = (unsigned char*)qrec; p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w;
   p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
+  { const char* t = getenv("CODA_DA_TRACE"); p.trace = t ? (long long*)strtoull(t, nullptr, 0) : nullptr; }
   p.k_raw = nullptr; p.k_bs = 0; p.v_new = nullptr; p.v_bs = 0; p.gate_logit = nullptr; p.gate_bs = 0; p.gated = 0;
   p.inv_freq = nullptr; p.q_raw = nullptr; p.q_bs = 0; p.lam_logit = nullptr; p.lam_bs = 0; p.cos_t = nullptr; p.sin_t = nullptr;
   p.rope_cs = nullptr;
