@@ -50,7 +50,6 @@ struct DecodeParams {
   const bf16* cos_t; const bf16* sin_t;
   const float* rope_cs;                           // optional: cos [Dh/2] | sin [Dh/2] of the token's position, precomputed
   bf16* k_buf; bf16* v_buf; uint8_t* allowed_w; float* g_recent;
-  long long* trace;
 };
 
 using tma::smem_u32; using tma::mbar_init; using tma::mbar_expect_tx; using tma::mbar_arrive; using tma::mbar_try;
@@ -102,7 +101,7 @@ struct DecodeSmem {
     sml = o;  o += 2 * DA_CWARPS * 16 * 4;          // [2][DA_CWARPS][16]  (m, l)
     nkv = o;  o += 2 * 4 * DH;                      // [2][K row | V row] of the new token (APPEND variant)
     cs = o;   o += 4 * DH + 16;                     // cos | sin of the position (floats), then the ring slot (int)
-    bars = o; o += (2 * DA_MAX_STAGES + 6) * 8;     // full[], empty[], q_ready[2], q_free[2], comb_full, comb_free
+    bars = o; o += (2 * DA_MAX_STAGES + 8) * 8;     // full[], empty[], q_ready[2], q_free[2], comb_full, comb_free, row_ready[2]
     total = o;
   }
 };
@@ -200,24 +199,31 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   uint64_t* q_free = q_ready + 2;                  // [2] record buffer may be overwritten
   uint64_t* comb_full = q_free + 2;
   uint64_t* comb_free = comb_full + 1;
+  uint64_t* row_ready = comb_free + 1;             // [2] APPEND: the new token's row of the plane is in shared memory
 
   __shared__ int s_abort;                          // set by the first bounded wait of this CTA that expires
   int* const abortw = &s_abort;
-  long long* const tr = (p.trace != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
-                            ? p.trace + (APPEND ? 0 : 64) + (blockIdx.x == 0 ? 0 : 32) : nullptr;
-  if (tr && tid == 0) tr[0] = clock64();
   if (tid == 0) {
     s_abort = 0;
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
     mbar_init(&q_ready[0], APPEND ? DA_AWARPS : 1); mbar_init(&q_ready[1], APPEND ? DA_AWARPS : 1);
     mbar_init(&q_free[0], DA_CWARPS + DA_AWARPS); mbar_init(&q_free[1], DA_CWARPS + DA_AWARPS);
     mbar_init(comb_full, DA_CWARPS); mbar_init(comb_free, DA_AWARPS);
+    mbar_init(&row_ready[0], DA_AWARPS); mbar_init(&row_ready[1], DA_AWARPS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (APPEND && warp >= DA_CWARPS && warp < DA_CWARPS + DA_AWARPS) {
+    // rows of the two query tiles that no head uses stay zero for the whole launch (the records are built in place)
+    const int rows = DecodeRecord::qrows(G), at0 = tid - DA_CWARPS * 32;
+    for (int buf = 0; buf < 2; ++buf) {
+      bf16* q_s = reinterpret_cast<bf16*>(rec0 + buf * L.rec_stride);
+      for (int w = at0; w < (rows - 2 * G) * (DH / 2); w += DA_AWARPS * 32)
+        *reinterpret_cast<uint32_t*>(q_s + (2 * G + w / (DH / 2)) * QSTR + 2 * (w % (DH / 2))) = 0u;
+    }
+  }
   // everything above touched no global memory: from here on the previous kernel's results are needed
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (tr && tid == 0) tr[1] = clock64();
 
   // ---- APPEND: the new token's inputs of one plane, as the auxiliary threads hold them between request and use ----
   constexpr int HALF = DH / 2;
@@ -225,7 +231,8 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   constexpr int MB = 8;                                                     // mask bytes per auxiliary thread (Lbuf <= 1024)
   // fq0 / fq1: raw query pairs of this thread's QI CONSECUTIVE (head, RoPE pair) items (one 16- or 8-byte request
   // each); fct / fst: the matching cos / sin of the learned rotation, two bf16 per word
-  struct AppIn { uint32_t fq0[QI], fq1[QI], fct[QI / 2], fst[QI / 2]; bf16 ka, kb, vv, lam, gate; uint8_t am[MB]; };
+  // lam0 / lam1: lambda logits of the two query heads this thread's warp finishes in the epilogue (aw, aw + 4)
+  struct AppIn { uint32_t fq0[QI], fq1[QI], fct[QI / 2], fst[QI / 2]; bf16 ka, kb, vv, lam0, lam1, gate; uint8_t am[MB]; };
   static_assert(QI == 2 || QI == 4, "vector widths below assume 2 or 4 items per auxiliary thread");
   auto ld_words = [](uint32_t* dst, const void* src, int n) {       // n = 1, 2 or 4 words, naturally aligned
     if (n == 4) { const uint4 t = *reinterpret_cast<const uint4*>(src); dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w; }
@@ -257,7 +264,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       ld_words(a.fct, p.cos_t + (hk * G + g) * HALF + i0, QI / 2);
       ld_words(a.fst, p.sin_t + (hk * G + g) * HALF + i0, QI / 2);
     }
-    a.ka = a.kb = a.vv = a.lam = a.gate = __float2bfloat16_rn(0.f);
+    a.ka = a.kb = a.vv = a.lam0 = a.lam1 = a.gate = __float2bfloat16_rn(0.f);
     if (at < DH) {
       const bf16* kn = p.k_raw + (long long)b * p.k_bs + hk * DH;
       int ia, ib;
@@ -266,7 +273,11 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       a.ka = kn[ia]; a.kb = kn[ib];
       a.vv = p.v_new[(long long)b * p.v_bs + hk * DH + at];
     }
-    if (at < G) a.lam = p.lam_logit[(long long)b * p.lam_bs + hk * G + at];
+    {
+      const int aw_ = at >> 5;
+      if (aw_ < G) a.lam0 = p.lam_logit[(long long)b * p.lam_bs + hk * G + aw_];
+      if (aw_ + DA_AWARPS < G) a.lam1 = p.lam_logit[(long long)b * p.lam_bs + hk * G + aw_ + DA_AWARPS];
+    }
     if (at == 0 && p.gated) a.gate = p.gate_logit[(long long)b * p.gate_bs];
 #pragma unroll
     for (int k = 0; k < MB; ++k) { const int m = at + k * (DA_AWARPS * 32); a.am[k] = m < p.Lbuf ? p.allowed[(long long)b * p.Lbuf + m] : (uint8_t)0; }
@@ -279,7 +290,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       if (p.rope_cs != nullptr) { if (at < DH) inv_f = p.rope_cs[at]; }      // the table entry itself
       else if (at < HALF) inv_f = p.inv_freq[at];
       if ((int)blockIdx.x < nplanes) load_inputs(blockIdx.x, in);
-      if (tr && at == 0) tr[2] = clock64();
     }
     __syncthreads();
   }
@@ -304,7 +314,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         for (int s = 0; s < nst; ++s) {
           if (pending && record_free(i + 1)) { load_record(plane + gridDim.x, i + 1); pending = false; }
           if (round > 0) mbar_wait(&empty[bi], (round - 1) & 1, p.status, 1, abortw);
-          if (tr && i == 0 && s == 0) tr[3] = clock64();
           mbar_expect_tx(&full[bi], 2 * TILE_BYTES);
           unsigned char* kd = stage0 + bi * 2 * TILE_BYTES;
           unsigned char* vd = kd + TILE_BYTES;
@@ -336,6 +345,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     float* sCS = reinterpret_cast<float*>(smem + L.cs);    // cos [HALF] | sin [HALF] of the token's position
     int* s_ev = reinterpret_cast<int*>(smem + L.cs + 4 * DH);
     int ev = 0; bool ring_full = false;
+    float lam_next[2] = {0.f, 0.f}, lam_cur[2] = {0.f, 0.f};     // APPEND: sigma(lambda) of heads aw, aw + 4: plane being built / plane in its epilogue
     auto build_record = [&](int plane, int buf, const AppIn& a) {
       using T = bf16;
       const int b = plane / p.Hkv, hk = plane % p.Hkv;
@@ -377,18 +387,15 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
           *reinterpret_cast<uint2*>(nrow) = make_uint2(nv[0], nv[1]);
         }
       }
-      const int rows = DecodeRecord::qrows(G);
-      #pragma unroll 1
-      for (int w = at; w < (rows - 2 * G) * HALF; w += DA_AWARPS * 32)   // unused rows of the query tile: zero
-        *reinterpret_cast<uint32_t*>(q_s + (2 * G + w / HALF) * QSTR + 2 * (w % HALF)) = 0u;
-      float* lam = reinterpret_cast<float*>(rec + lam_off);
-      if (at < 8) lam[at] = at < G ? t_sigmoid<T>(__bfloat162float(a.lam)) : 0.f;
       uint8_t* mk = rec + mask_off;
 #pragma unroll
       for (int k = 0; k < MB; ++k) {
         const int m = at + k * (DA_AWARPS * 32);
         if (m < DecodeRecord::mask_bytes(p.Lbuf)) mk[m] = m < p.Lbuf ? (m == ev ? (uint8_t)1 : a.am[k]) : (uint8_t)0;
       }
+      // queries and mask are what the consumers wait for: everything else of the plane follows behind the barrier
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_ready[buf]);
       // the token's own row: ring slot in global memory, and a copy for the consumer warp that patches the tile
       if (at < DH) {
         const int d = at;
@@ -404,12 +411,15 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         const long long row = ((long long)plane * p.Lbuf + ev) * DH + d;
         p.k_buf[row] = nkb; p.v_buf[row] = a.vv;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&row_ready[buf]);
       if (hk == 0 && at == 0) {
         p.g_recent[(long long)b * p.W + ev] = p.gated ? t_sigmoid<T>(__bfloat162float(a.gate)) : 1.0f;
         if (!ring_full) p.allowed_w[(long long)b * p.Lbuf + ev] = 1;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&q_ready[buf]);
+      // sigma(lambda) of this warp's two heads, kept in registers for the plane's epilogue
+      lam_next[0] = t_sigmoid<T>(__bfloat162float(a.lam0));
+      lam_next[1] = t_sigmoid<T>(__bfloat162float(a.lam1));
     };
     if (APPEND && (int)blockIdx.x < nplanes) {
       const RingNow r = ring_after(p.rp, p.W, nsteps);
@@ -428,14 +438,13 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         sCS[at] = bf16_round(cc); sCS[HALF + at] = bf16_round(ss);
       }
       asm volatile("bar.sync 2, 128;" ::: "memory");       // the four auxiliary warps
-      if (tr && at == 0) tr[4] = clock64();
       build_record(blockIdx.x, 0, in);
-      if (tr && at == 0) tr[5] = clock64();
       if ((int)(blockIdx.x + gridDim.x) < nplanes) load_inputs(blockIdx.x + gridDim.x, in);
     }
     int i = 0;
     for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
       if (APPEND) {
+        lam_cur[0] = lam_next[0]; lam_cur[1] = lam_next[1];
         // the NEXT plane's record, while the consumers are on this plane's tiles (its inputs were requested a plane ago)
         const int next = plane + gridDim.x;
         if (next < nplanes) {
@@ -448,7 +457,8 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       mbar_wait(comb_full, i & 1, p.status, 5, abortw);
       const int b = plane / p.Hkv, hk = plane % p.Hkv;
       const float* sLam = reinterpret_cast<const float*>(rec0 + (i & 1) * L.rec_stride + lam_off);
-      const float lam_a = sLam[aw], lam_b = sLam[(aw + DA_AWARPS) & 7];   // heads aw and aw + 4 of the group (G <= 8)
+      const float lam_a = APPEND ? lam_cur[0] : sLam[aw];                 // heads aw and aw + 4 of the group (G <= 8)
+      const float lam_b = APPEND ? lam_cur[1] : sLam[(aw + DA_AWARPS) & 7];
       __syncwarp();
       if (lane == 0) mbar_arrive(&q_free[i & 1]);          // the record buffer is no longer needed by this warp
       for (int g = aw; g < G; g += DA_AWARPS) {
@@ -503,7 +513,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(comb_free);
-      if (tr && aw == 0 && lane == 0 && i < 2) tr[16 + i] = clock64();
     }
     return;
   }
@@ -520,7 +529,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   for (int plane = blockIdx.x; plane < nplanes; plane += gridDim.x, ++i) {
     const int buf = i & 1;
     mbar_wait(&q_ready[buf], (i >> 1) & 1, p.status, 3, abortw);
-    if (tr && tid == 0 && i < 2) tr[6 + 4 * i] = clock64();
     const unsigned char* rec = rec0 + buf * L.rec_stride;
     const uint8_t* al_s = rec + mask_off;
     // B fragments of Q^T: one ldmatrix.x4 covers two k-steps of one n-tile (matrices: dh chunks 4j .. 4j+3)
@@ -549,7 +557,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
 
     for (int s = s0; s < nst; s += 2) {
       mbar_wait(&full[bi], round & 1, p.status, 2, abortw);
-      if (tr && tid == 0 && i < 2 && s == s0) tr[7 + 4 * i] = clock64();
       const uint32_t kb = smem_u32(stage0 + bi * 2 * TILE_BYTES);
       const uint32_t vb = kb + TILE_BYTES;
       if (APPEND) {
@@ -557,6 +564,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         // puts the row (left in shared memory by the auxiliary warps) over it -- only this warp reads these rows
         const int ev = *reinterpret_cast<const int*>(smem + L.cs + 4 * DH);
         if (s == ev / DA_TILE && gw == (ev % DA_TILE) / 16) {
+          mbar_wait(&row_ready[buf], (i >> 1) & 1, p.status, 8, abortw);
           constexpr int CPR = DH / 8;                      // 16-byte chunks per row
           if (lane < 2 * CPR) {
             const int which = lane / CPR, c = lane % CPR;
@@ -631,7 +639,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     }
 
     __syncwarp();
-    if (tr && tid == 0 && i < 2) tr[8 + 4 * i] = clock64();
     if (lane == 0) mbar_arrive(&q_free[buf]);              // queries are in registers, the mask is no longer read
     // ---- hand the partial softmax of this warp to the auxiliary warps ----
 #pragma unroll
@@ -674,7 +681,6 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(comb_full);
-    if (tr && tid == 0 && i < 2) tr[9 + 4 * i] = clock64();
   }  // plane loop
 }
 
@@ -732,7 +738,6 @@ DecodeParams make_params(const coda_layer_cfg* cfg, const coda_state_ptrs* st, v
   p.rp = coda_ring_pos{0, 0, 0, nullptr}; p.W = cfg->W;
   p.qrec = (unsigned char*)qrec; p.allowed = st->allowed; p.norm_w = (const bf16*)norm_w;
   p.out = (bf16*)out; p.out_bs = out_bs; p.status = status;
-  { const char* t = getenv("CODA_DA_TRACE"); p.trace = t ? (long long*)strtoull(t, nullptr, 0) : nullptr; }
   p.k_raw = nullptr; p.k_bs = 0; p.v_new = nullptr; p.v_bs = 0; p.gate_logit = nullptr; p.gate_bs = 0; p.gated = 0;
   p.inv_freq = nullptr; p.q_raw = nullptr; p.q_bs = 0; p.lam_logit = nullptr; p.lam_bs = 0; p.cos_t = nullptr; p.sin_t = nullptr;
   p.rope_cs = nullptr;
