@@ -485,9 +485,18 @@ def main():
         for l, st, c, o in zip(stack.layers, states, cfgs, outs):
             l.decode_attend_prepared_launch(c, st, o)
 
+    # cos / sin of the token's position, computed once for all layers as the captured step does
+    rope_cs = None
+    if append_ok and stack._shared_rope(states, dtype):
+        rope_cs = torch.empty(stack.layers[0].head_dim, dtype=torch.float32, device=dev)
+        with torch.cuda.stream(roof_stream):
+            check(lib.coda_b200_rope_table(C.byref(cfgs[0]), rps[0], stack.layers[0]._consts(dev, dtype)[0].data_ptr(),
+                                           rope_cs.data_ptr(), roof_stream.cuda_stream), "coda_b200_rope_table")
+        roof_stream.synchronize()
+
     def sweep_append():
         for l, st, c, rp, pr, o in zip(stack.layers, states, cfgs, rps, projs, outs):
-            l.decode_attend_append_launch(c, st, rp, pr, o)
+            l.decode_attend_append_launch(c, st, rp, pr, o, rope_cs)
 
     nl = len(stack.layers)
     prepared_ms = timed_graph(sweep_prepared) / nl
