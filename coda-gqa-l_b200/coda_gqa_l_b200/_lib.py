@@ -58,6 +58,8 @@ def _load() -> C.CDLL:
     lib.coda_b200_step_write_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp, fp,
                                                vp, i64, vp, i64, vp, vp, vp, vp]
     lib.coda_b200_step_write_fused_supported.argtypes = [cfgp]
+    lib.coda_b200_step_write_attend.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp, fp,
+                                                vp, i64, vp, i64, vp, vp, vp, vp, vp, i64, vp, vp]
     lib.coda_b200_step_route.argtypes = [cfgp, stp, RingPos, fp, vp]
     lib.coda_b200_step_route_plan_bytes.argtypes = [i32]
     lib.coda_b200_step_route_plan_bytes.restype = C.c_int64
@@ -104,7 +106,7 @@ def _load() -> C.CDLL:
 
 EXPORTS = (
     "coda_b200_last_error", "coda_b200_version", "coda_b200_prep", "coda_b200_step_write",
-    "coda_b200_step_write_raw", "coda_b200_step_write_fused", "coda_b200_step_write_fused_supported",
+    "coda_b200_step_write_raw", "coda_b200_step_write_fused", "coda_b200_step_write_fused_supported", "coda_b200_step_write_attend",
     "coda_b200_step_route", "coda_b200_step_append_fused", "coda_b200_step_route_plan_bytes",
     "coda_b200_step_route_plan", "coda_b200_step_route_batched",
     "coda_b200_skinny_gemm_supported", "coda_b200_skinny_gemm", "coda_b200_proj_gemm_supported", "coda_b200_proj_gemm", "coda_b200_proj_gemm_workspace_bytes",

@@ -569,10 +569,11 @@ class CoDAGQALandmarkPerf2(nn.Module):
         self.__dict__["_bundle"] = c
         return c
 
-    def _step_eager_fast(self, x: torch.Tensor, st: CoDAGQALandmarkStatePerf2) -> Optional[torch.Tensor]:
+    def _step_eager_fast(self, x: torch.Tensor, st: CoDAGQALandmarkStatePerf2,
+                         residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """The default decode step (write, then attend) with as little host work as the launches allow; same kernels
         and the same bits as the general path.  Returns None where it does not apply (the caller then takes the
-        general path)."""
+        general path).  ``residual``: added to the result inside the output projection's GEMM call."""
         if self.use_torch_ops or self.use_own_gemm or self.use_skinny_gemm_kernel or self.kernel_timers is not None:
             return None
         if st.metrics is not None or self.Me_min != self.Me_max or self.Ms_min != self.Ms_max or not self.detach_evicted:
@@ -611,16 +612,16 @@ class CoDAGQALandmarkPerf2(nn.Module):
         out = torch.empty((B, self.num_heads * self.head_dim), device=dev, dtype=x.dtype)
         status = self._status_word(dev).data_ptr()
         gate = base + bd["off_gate"] if bd["gated"] else None
-        rc = lib.coda_b200_step_write_fused(
+        rc = lib.coda_b200_step_write_attend(
             C.byref(cfg), C.byref(ptrs), rp, base + bd["off_k"], npad, base + bd["off_v"], npad, gate, npad if gate else 0,
-            bd["inv_freq"], bd["eta"], base, npad, base + bd["off_lam"], npad, bd["cos"], bd["sin"], qrec.data_ptr(), s)
+            bd["inv_freq"], bd["eta"], base, npad, base + bd["off_lam"], npad, bd["cos"], bd["sin"], qrec.data_ptr(),
+            bd["nw"], out.data_ptr(), out.shape[1], status, s)
         if rc:
-            check(rc, "coda_b200_step_write_fused")
-        rc = lib.coda_b200_decode_attend_prepared(C.byref(cfg), C.byref(ptrs), qrec.data_ptr(), bd["nw"], out.data_ptr(),
-                                                  out.shape[1], status, s)
-        if rc:
-            check(rc, "coda_b200_decode_attend_prepared")
+            check(rc, "coda_b200_step_write_attend")
         self.advance_host_scalars(st)
+        if residual is not None:
+            # an eager step is bound by the host: one call for GEMM + residual beats the faster GEMM plus a separate add
+            return torch.addmm(residual.reshape(B, -1), out, bd["w_out_t"]).view(B, 1, -1)
         return torch.mm(out, bd["w_out_t"]).view(B, 1, -1)
 
     def _project(self, x: torch.Tensor, need_kv: bool):
@@ -996,6 +997,19 @@ class CoDAGQALandmarkPerf2(nn.Module):
         out = torch.empty_like(q)
         self._attend(cfg, state, 1, q, qn, lam, None, None, out)
         return self._out(out, None)
+
+    @torch.no_grad()
+    def step_residual(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2) -> torch.Tensor:
+        """``x + step(x)``: the residual connection of a decoder layer around the default decode step.  On the eager
+        fast path the sum is taken inside the output projection's GEMM call (one rounding of the fp32 sum instead
+        of two), which saves a launch and a host call per layer; elsewhere it is the plain sum."""
+        B, L, _ = x.shape
+        if L == 1 and not self.training and x.is_cuda and state.k_buf.shape[0] == B:
+            y = self._step_eager_fast(x, state, residual=x)
+            if y is not None:
+                return y
+        y, _ = self.step(x, state)
+        return x + y
 
     @torch.no_grad()
     def step(self, x: torch.Tensor, state: CoDAGQALandmarkStatePerf2, *, attend: bool = True,

@@ -50,8 +50,7 @@ class CoDAStack(nn.Module):
         """One decode token per state through every layer (eager launches)."""
         h = x
         for layer, st in zip(self.layers, states):
-            y, _ = layer.step(h, st)
-            h = h + y if self.residual else y
+            h = layer.step_residual(h, st) if self.residual else layer.step(h, st)[0]
         self._graph = None                       # the captured step's device counter did not see this write
         return h
 

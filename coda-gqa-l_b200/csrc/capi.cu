@@ -106,3 +106,20 @@ extern "C" int coda_b200_host_topk_f32(const float* v, int32_t n, int32_t k, int
 extern "C" int coda_b200_host_topk_i64(const int64_t* v, int32_t n, int32_t k, int32_t largest, int32_t sorted, int32_t* out) {
   return host_topk<long long>((const long long*)v, n, k, largest, sorted, out);
 }
+
+// The default decode step between its two GEMMs as ONE library call: coda_b200_step_write_fused, then
+// coda_b200_decode_attend_prepared on the records it left.  Two launches as before; a caller that drives the step
+// eagerly from an interpreter pays one foreign call per layer instead of two.
+extern "C" int coda_b200_step_write_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                           const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                           const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                           const float* eta_logit,
+                                           const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                           const void* cos_theta, const void* sin_theta, void* qrec,
+                                           const void* norm_w, void* out, int64_t out_bs, int32_t* status,
+                                           coda_stream_t stream) {
+  const int rc = coda_b200_step_write_fused(cfg, st, rp, k_raw, k_bs, v_new, v_bs, gate_logit, gate_bs, inv_freq, eta_logit,
+                                            q_raw, q_bs, lam_logit, lam_bs, cos_theta, sin_theta, qrec, stream);
+  if (rc != CODA_OK) return rc;
+  return coda_b200_decode_attend_prepared(cfg, st, qrec, norm_w, out, out_bs, status, stream);
+}

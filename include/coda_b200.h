@@ -200,6 +200,18 @@ int coda_b200_decode_attend_prepared(const coda_layer_cfg* cfg, const coda_state
                                      const void* norm_w, void* out, int64_t out_bs, int32_t* status,
                                      coda_stream_t stream);
 
+/* coda_b200_step_write_fused followed by coda_b200_decode_attend_prepared on the records it wrote, as one call
+ * (the default `step` of src/coda_gqa_l/attention.py:516-547 between its projections): same arguments, same two
+ * launches, same results; for hosts where a foreign call costs more than the launch it makes. */
+int coda_b200_step_write_attend(const coda_layer_cfg* cfg, const coda_state_ptrs* st, coda_ring_pos rp,
+                                const void* k_raw, int64_t k_bs, const void* v_new, int64_t v_bs,
+                                const void* gate_logit, int64_t gate_bs, const float* inv_freq,
+                                const float* eta_logit,
+                                const void* q_raw, int64_t q_bs, const void* lam_logit, int64_t lam_bs,
+                                const void* cos_theta, const void* sin_theta, void* qrec,
+                                const void* norm_w, void* out, int64_t out_bs, int32_t* status,
+                                coda_stream_t stream);
+
 /* y[M][N] = x[M][K] . w[N][K]^T (+ residual[M][N]), bf16 with fp32 accumulation, for the decode step's few rows
  * (M <= 32): the output projection of src/coda_gqa_l/attention.py:514 (`self.o_proj`, an nn.Linear without bias,
  * weight [N][K]) with the decoder's residual added in the same pass (the product is rounded to bf16 before the
