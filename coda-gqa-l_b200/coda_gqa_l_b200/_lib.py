@@ -88,6 +88,8 @@ def _load() -> C.CDLL:
     lib.coda_b200_route_scratch_bytes.restype = i64
     lib.coda_b200_route_block.argtypes = [cfgp, stp, i32, i32, i64, vp, i64, i64, vp, i64, i64,
                                           fp, i64, i64, vp, i64, fp, vp, vp]
+    lib.coda_b200_route_block_phase.argtypes = [cfgp, stp, i32, i32, i64, vp, i64, i64, vp, i64, i64,
+                                                fp, i64, i64, vp, i64, fp, vp, i32, vp]
     lib.coda_b200_route_static_scratch_bytes.argtypes = []
     lib.coda_b200_route_static_scratch_bytes.restype = i64
     lib.coda_b200_route_block_noalloc.argtypes = [cfgp, stp, i32, i32, i64, vp, i64, i64, vp, i64, i64,
@@ -115,7 +117,7 @@ EXPORTS = (
     "coda_b200_decode_record_bytes",
     "coda_b200_prefill_attend_supported", "coda_b200_prefill_attend",
     "coda_b200_attend", "coda_b200_select_candidates", "coda_b200_route_scratch_bytes",
-    "coda_b200_route_block", "coda_b200_route_static_scratch_bytes", "coda_b200_route_block_noalloc",
+    "coda_b200_route_block", "coda_b200_route_block_phase", "coda_b200_route_static_scratch_bytes", "coda_b200_route_block_noalloc",
     "coda_b200_advance_steps", "coda_b200_selftest_bounded_wait", "coda_b200_host_topk_f32",
     "coda_b200_host_topk_i64",
 )

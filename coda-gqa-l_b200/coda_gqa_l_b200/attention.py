@@ -55,6 +55,18 @@ def _stream(device: Optional[torch.device] = None) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream_for(device: torch.device) -> "torch.cuda.Stream":
+    """One extra stream per device for work that runs beside the current stream (kept for the process)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _SIDE_STREAMS.get(idx)
+    if st is None:
+        st = _SIDE_STREAMS[idx] = torch.cuda.Stream(device=idx)
+    return st
+
+
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
@@ -199,6 +211,11 @@ class CoDAGQALandmarkPerf2(nn.Module):
         # Second half of a split decode step (after route_launch / the stack's batched routing) as one launch:
         # the attention kernel writes the new token itself (coda_b200_decode_attend_append).
         self.fuse_append_into_attention = True
+        # chunked prefill: scores and decisions of a block's routing on a second stream beside the block's attention.
+        # Same results; measured slower at the 7B shape (2.27 against 2.15 ms per layer and 512-token chunk: a scoring
+        # CTA and an attention CTA do not fit one SM together, so the scoring kernel takes whole SMs from the attention
+        # for as long as its latency chains last), hence off.
+        self.overlap_block_routing = False
         # Route the attention / cache-write / routing launches through the torch custom ops (torch.ops.coda_b200.*,
         # see torch_ops.py) instead of the ctypes binding.  Same entry points underneath, so the same bits; states
         # that report routing events (metrics, growing banks) and the fused decode-step launches stay on ctypes.
@@ -1113,10 +1130,37 @@ class CoDAGQALandmarkPerf2(nn.Module):
         tc_ok = (return_outputs and self._tuned_prefill(cfg) and q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0
                  and v.data_ptr() % 16 == 0 and all(t.stride(i) % 8 == 0 for t in (q, k, v) for i in (0, 1)))
 
+        # Scores and decisions of a block's routing read the state the block's attention reads and write nothing
+        # it reads, so they run beside it on a second stream; slot updates and the ring rewrite follow both.
+        overlap = (self.overlap_block_routing and return_outputs and tc_ok and write_cache and ops is None
+                   and state._events is None and not torch.cuda.is_current_stream_capturing())
+        if overlap:
+            main = torch.cuda.current_stream(dev)
+            side = _side_stream_for(dev)
+            ev_state, ev_plan = torch.cuda.Event(), torch.cuda.Event()
+
         for j in range(nblk):
             t0 = j * block
             blk = min(block, L - t0)
             kb, vb = k[:, t0:t0 + blk], v[:, t0:t0 + blk]
+            if overlap:
+                fill = int(state.recent_filled)
+                seen = fill0 + t0
+                route_args = (C.byref(cfg), C.byref(ptrs), fill, blk, pos0 + t0,
+                              kb.data_ptr(), k.stride(0), k.stride(1), vb.data_ptr(), v.stride(0), v.stride(1),
+                              gates.data_ptr(), gates.stride(0), seen - fill,
+                              cand[:, j].data_ptr(), cand.stride(0), eta.data_ptr(), scratch.data_ptr())
+                ev_state.record(main)
+                side.wait_event(ev_state)
+                check(lib.coda_b200_route_block_phase(*route_args, 1, side.cuda_stream), "coda_b200_route_block_phase")
+                ev_plan.record(side)
+                self._attend_block_tc(cfg, state, L, t0, blk, q, qn, lam, k, v, y_heads)
+                main.wait_event(ev_plan)
+                check(lib.coda_b200_route_block_phase(*route_args, 2, main.cuda_stream), "coda_b200_route_block_phase")
+                state.recent_filled = min(W, fill + blk)
+                state.recent_idx = 0
+                state.pos = pos0 + t0 + blk
+                continue
             if return_outputs and tc_ok:
                 self._attend_block_tc(cfg, state, L, t0, blk, q, qn, lam, k, v, y_heads)
             elif return_outputs:

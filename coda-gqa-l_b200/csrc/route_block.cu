@@ -538,10 +538,12 @@ extern "C" int64_t coda_b200_route_scratch_bytes(const coda_layer_cfg* cfg) {
 }
 
 template <typename T>
-static int launch_route(RouteParams& p, cudaStream_t s) {
+// phase 0: everything; 1: scores and decisions only (they read the state and write the scratch and the LRU
+// stamps: nothing the attention of the same block reads is touched); 2: slot updates and the ring rewrite only.
+static int launch_route(RouteParams& p, cudaStream_t s, int phase = 0) {
   const coda_layer_cfg& c = p.c;
   const int HD = c.Hkv * c.Dh;
-  if (p.te > 0 || p.ts > 0) {
+  if ((p.te > 0 || p.ts > 0) && phase != 2) {
     const size_t smem1 = sizeof(float) * (size_t)(RS_KC * 64 + RS_KC * RS_COLS + 64 * (RS_COLS + 1) + 64 * c.Hkv + 64);
     CODA_REQUIRE(smem1 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: %d KV heads too many for the scoring tile", c.Hkv);
     if (smem1 > 48 * 1024) cudaFuncSetAttribute(route_score_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
@@ -554,6 +556,10 @@ static int launch_route(RouteParams& p, cudaStream_t s) {
     if (smem2 > 48 * 1024) cudaFuncSetAttribute(route_decide_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     route_decide_kernel<T><<<c.B, 64, smem2, s>>>(p);
     CODA_CHECK_LAUNCH("route_block (decide)");
+  }
+  if (phase == 1) return CODA_OK;
+  if (p.te > 0 || p.ts > 0) {
+    const int tmax = p.te > p.ts ? p.te : p.ts;
     const size_t smem3 = sizeof(float) * (size_t)HD + 8 * (size_t)(tmax > 0 ? tmax : 1);   // new row + the slot's candidate list
     CODA_REQUIRE(smem3 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: Hkv*Dh = %d with %d candidates per block needs %zu bytes of shared memory", HD, tmax, smem3);
     if (smem3 > 48 * 1024) cudaFuncSetAttribute(route_apply_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
@@ -630,7 +636,19 @@ extern "C" int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state
                                      const float* gates, int64_t gates_bs, int64_t gate_ev0,
                                      const int32_t* cand, int64_t cand_bs,
                                      const float* eta_logit, void* scratch, coda_stream_t stream) {
+  return coda_b200_route_block_phase(cfg, st, ring_fill, blk, pos0, k_blk, kb_bs, kb_rs, v_blk, vb_bs, vb_rs, gates, gates_bs,
+                                     gate_ev0, cand, cand_bs, eta_logit, scratch, 0, stream);
+}
+
+extern "C" int coda_b200_route_block_phase(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                                           int32_t ring_fill, int32_t blk, int64_t pos0,
+                                           const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                                           const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                                           const float* gates, int64_t gates_bs, int64_t gate_ev0,
+                                           const int32_t* cand, int64_t cand_bs,
+                                           const float* eta_logit, void* scratch, int32_t phase, coda_stream_t stream) {
   CODA_REQUIRE(coda_cfg_ok(cfg) && st, CODA_ERR_ARG, "route_block: invalid layer configuration");
+  CODA_REQUIRE(phase >= 0 && phase <= 2, CODA_ERR_ARG, "route_block: phase %d is not 0, 1 or 2", phase);
   CODA_REQUIRE(blk > 0 && ring_fill >= 0 && ring_fill <= cfg->W, CODA_ERR_ARG, "route_block: bad block / ring sizes");
   CODA_REQUIRE(st->k_buf && st->v_buf && st->allowed && st->g_recent && k_blk && v_blk && gates, CODA_ERR_ARG,
                "route_block: null pointer");
@@ -660,5 +678,5 @@ extern "C" int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state
     p.ex_best = nullptr; p.ex_bi = nullptr; p.su_idx = nullptr; p.plan = nullptr;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  return cfg->dtype == CODA_F32 ? launch_route<float>(p, s) : launch_route<bf16>(p, s);
+  return cfg->dtype == CODA_F32 ? launch_route<float>(p, s, phase) : launch_route<bf16>(p, s, phase);
 }

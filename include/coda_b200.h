@@ -329,6 +329,18 @@ int coda_b200_route_block(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
                           const int32_t* cand, int64_t cand_bs,
                           const float* eta_logit, void* scratch, coda_stream_t stream);
 
+/* The same block update in two halves, for callers that overlap the first with the block's attention:
+ * phase 1 = scores and decisions (reads the state; writes only the scratch and the exact bank's LRU stamps, which
+ * no attention kernel reads), phase 2 = slot updates and the ring rewrite (after phase 1 AND after the block's
+ * attention have finished, same arguments, same scratch); phase 0 = both, i.e. coda_b200_route_block. */
+int coda_b200_route_block_phase(const coda_layer_cfg* cfg, const coda_state_ptrs* st,
+                                int32_t ring_fill, int32_t blk, int64_t pos0,
+                                const void* k_blk, int64_t kb_bs, int64_t kb_rs,
+                                const void* v_blk, int64_t vb_bs, int64_t vb_rs,
+                                const float* gates, int64_t gates_bs, int64_t gate_ev0,
+                                const int32_t* cand, int64_t cand_bs,
+                                const float* eta_logit, void* scratch, int32_t phase, coda_stream_t stream);
+
 /* coda_b200_route_block for callers that may not allocate device memory -- code running where cudaMalloc is
  * forbidden or unavailable: inside a serving engine whose memory pool is frozen after start-up, under a
  * framework that owns all allocations, or in a latency-critical loop where an allocation could stall.  It has no

@@ -276,3 +276,32 @@ def test_host_fed_captured_step_equals_device_fed_one():
     for a, b in zip(sa, sb):
         assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
         assert torch.equal(a._arena, b._arena)
+
+
+@pytest.mark.gpu
+def test_block_routing_beside_attention_equals_routing_after_it():
+    """Chunked prefill can run the scores and decisions of a block's routing on a second stream beside the block's
+    attention (`overlap_block_routing`; they read what it reads and write nothing it reads).  Outputs and states
+    equal the serial order's bit for bit, over several chunks and with decode steps in between."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
+    kw = dict(embed_dim=512, num_heads=8, num_kv_heads=2, window=48, num_landmarks_exact=16, num_landmarks_summary=16)
+    torch.manual_seed(3)
+    mod = CoDAGQALandmarkPerf2(**kw).eval().to(torch.bfloat16).cuda()
+    x = (torch.randn(3, 400, 512, device="cuda") * 0.5).to(torch.bfloat16)
+    outs, states = [], []
+    for overlap in (True, False):
+        mod.overlap_block_routing = overlap
+        torch.manual_seed(9)
+        st = mod.init_state(batch_size=3, device="cuda", dtype=torch.bfloat16)
+        ys = []
+        y, st = mod.prefill_chunked(x[:, :160], st, block_size=32); ys.append(y)
+        for t in range(160, 170):
+            y, st = mod.step(x[:, t:t + 1], st); ys.append(y)
+        y, st = mod.prefill_chunked(x[:, 170:400], st, block_size=64); ys.append(y)      # ragged last block
+        torch.cuda.synchronize()
+        outs.append(torch.cat(ys, 1)); states.append(st)
+    mod.overlap_block_routing = False
+    assert torch.equal(outs[0], outs[1])
+    a, b = states
+    assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
+    assert torch.equal(a._arena, b._arena)
