@@ -186,6 +186,177 @@ __global__ void __launch_bounds__(256) route_score_kernel(RouteParams p) {
   else if (p.ts > 0 && p.c.Ms > 0) route_score_bank<T, 4>(p, blockIdx.y, false, sm);
 }
 
+// ---- the same scores with the KV heads side by side: one CTA per (bank, state, head), the heads of a state in one cluster ----
+// route_score_bank walks the heads one after the other (2 x Hkv tile loads per output tile, each a memory round
+// trip); here CTA h computes head h's rounded dot products only, leaves them in its shared memory, and after one
+// cluster barrier every CTA finishes the output rows r with r % Hkv == h: it adds the Hkv partials in head order
+// (the order route_score_bank adds them in, so the results are the same bits), takes the mean, applies the slot
+// masks and keeps the running first-index argmax of its rows.
+template <typename T, int TM>
+__device__ __forceinline__ void route_score_bank_heads(const RouteParams& p, int b, bool exact, float* sm) {
+  constexpr int ROWS = 16 * TM;
+  const coda_layer_cfg& c = p.c;
+  const int tid = threadIdx.x, h = blockIdx.z;
+  const int Hkv = c.Hkv, Dh = c.Dh, lf = Dh / 2, W = c.W, Me = c.Me, Ms = c.Ms;
+  const int n = exact ? Dh : Dh - lf, M = exact ? Me : Ms, Tn = exact ? p.te : p.ts;
+  const int active = exact ? c.active_exact : c.active_summary;
+  const T* cache = exact ? (const T*)p.st.exact_v_norm + (long long)b * Hkv * Me * Dh
+                         : (const T*)p.st.sum_lf_k_norm + (long long)b * Hkv * Ms * n;
+  const uint8_t* al = p.st.allowed + (long long)b * (W + Me + Ms);
+  float* As = sm;                                  // [RS_KC][ROWS]
+  float* Bs = As + RS_KC * ROWS;                   // [RS_KC][RS_COLS]
+  float* Ps = Bs + RS_KC * RS_COLS;                // [ROWS][RS_COLS]   this head's rounded dots (read by the whole cluster)
+  float* Fs = Ps + ROWS * RS_COLS;                 // [ROWS / Hkv + 1][RS_COLS + 1]  final scores of the rows this CTA owns
+  float* den = Fs + (ROWS / Hkv + 1) * (RS_COLS + 1);   // [ROWS]
+  int* cidx = reinterpret_cast<int*>(den + ROWS);  // [ROWS]
+  const int ty = tid >> 4, tx = tid & 15;          // 16 x 16 thread grid
+  const int nown_max = ROWS / Hkv + 1;
+
+  for (int r0 = 0; r0 < Tn; r0 += ROWS) {
+    const int nrows = min(ROWS, Tn - r0);
+    __syncthreads();
+    for (int r = tid; r < ROWS; r += 256) cidx[r] = r < nrows ? p.cand[(long long)b * p.cand_bs + r0 + r] : -1;
+    __syncthreads();
+    // ||x|| of every candidate of the tile for this head, batched loads  (memory_banks.py:498-500).  One thread per
+    // row (every fourth): the fp32 sum of squares runs over the elements in order, as route_score_bank's does.
+    {
+      const int r = tid >> 2, part = tid & 3;
+      float ss = 0.f;
+      if (r < ROWS && cidx[r] >= 0) {
+        const T* row = exact ? src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, cidx[r], h)
+                             : src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, cidx[r], h) + lf;
+        if (part == 0) {
+          int d = 0;
+          for (; d + 16 <= n; d += 16) {
+            float x[16];
+            load_run<T, 16>(row + d, x);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ss = fmaf(x[i], x[i], ss);
+          }
+          for (; d < n; ++d) { const float v = El<T>::ld(row + d); ss = fmaf(v, v, ss); }
+        }
+      }
+      if (r < ROWS && part == 0) den[r] = fmaxf(El<T>::rnd(sqrtf(ss)), 1e-6f);
+    }
+    float best = 0.f; int bi = 0;                  // running first-index argmax of owned row `tid` (tid < rows owned)
+    for (int c0 = 0; c0 < M; c0 += RS_COLS) {
+      float acc[TM][4];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+      for (int k0 = 0; k0 < n; k0 += RS_KC) {
+        __syncthreads();
+        {
+          constexpr int KRUN_A = RS_KC * ROWS / 256;          // 16 (64-row tile) or 4 (16-row tile)
+          const int r = tid % ROWS, kq0 = (tid / ROWS) * KRUN_A;
+          float x[KRUN_A];
+#pragma unroll
+          for (int i = 0; i < KRUN_A; ++i) x[i] = 0.f;
+          if (cidx[r] >= 0) {
+            const T* row = exact ? src_row<T>(p, p.st.v_buf, p.vblk, p.vb_bs, p.vb_rs, b, cidx[r], h)
+                                 : src_row<T>(p, p.st.k_buf, p.kblk, p.kb_bs, p.kb_rs, b, cidx[r], h) + lf;
+            if (k0 + kq0 + KRUN_A <= n) load_run<T, KRUN_A>(row + k0 + kq0, x);
+            else
+              for (int i = 0; i < KRUN_A; ++i) if (k0 + kq0 + i < n) x[i] = El<T>::ld(row + k0 + kq0 + i);
+            const float dn = den[r];
+#pragma unroll
+            for (int i = 0; i < KRUN_A; ++i) x[i] = t_div<T>(x[i], dn);
+          }
+#pragma unroll
+          for (int i = 0; i < KRUN_A; ++i) As[(kq0 + i) * ROWS + r] = x[i];
+        }
+        {
+          constexpr int KRUN_B = RS_KC * RS_COLS / 256;       // 16
+          const int col = tid % RS_COLS, kq0 = (tid / RS_COLS) * KRUN_B, m = c0 + col;
+          float x[KRUN_B];
+#pragma unroll
+          for (int i = 0; i < KRUN_B; ++i) x[i] = 0.f;
+          if (m < M) {
+            const T* row = cache + ((long long)h * M + m) * n;
+            if (k0 + kq0 + KRUN_B <= n) load_run<T, KRUN_B>(row + k0 + kq0, x);
+            else
+              for (int i = 0; i < KRUN_B; ++i) if (k0 + kq0 + i < n) x[i] = El<T>::ld(row + k0 + kq0 + i);
+          }
+#pragma unroll
+          for (int i = 0; i < KRUN_B; ++i) Bs[(kq0 + i) * RS_COLS + col] = x[i];
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kq = 0; kq < RS_KC; ++kq) {
+          float a[TM];
+#pragma unroll
+          for (int i = 0; i < TM; ++i) a[i] = As[kq * ROWS + ty * TM + i];
+          const float4 bv = *reinterpret_cast<const float4*>(Bs + kq * RS_COLS + tx * 4);
+#pragma unroll
+          for (int i = 0; i < TM; ++i) {
+            acc[i][0] = fmaf(a[i], bv.x, acc[i][0]); acc[i][1] = fmaf(a[i], bv.y, acc[i][1]);
+            acc[i][2] = fmaf(a[i], bv.z, acc[i][2]); acc[i][3] = fmaf(a[i], bv.w, acc[i][3]);
+          }
+        }
+      }
+      // every CTA of the cluster has read the previous tile's partials before they are overwritten
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) Ps[(ty * TM + i) * RS_COLS + tx * 4 + jj] = El<T>::rnd(acc[i][jj]);
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      // rows r = h, h + Hkv, ... of the tile are finished here: partials of all heads, in head order
+      for (int o = tid; o < nown_max * RS_COLS; o += 256) {
+        const int lr = o / RS_COLS, col = o % RS_COLS, r = h + lr * Hkv;
+        if (r < ROWS) {
+          const uint32_t local = tma::smem_u32(Ps + r * RS_COLS + col);
+          float pv[8];                                 // all requests first, then the sum in head order
+#pragma unroll
+          for (int hh = 0; hh < 8; ++hh) {
+            pv[hh] = 0.f;
+            if (hh < Hkv) {
+              uint32_t remote;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(hh));
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv[hh]) : "r"(remote) : "memory");
+            }
+          }
+          float tot = 0.f;
+#pragma unroll
+          for (int hh = 0; hh < 8; ++hh) if (hh < Hkv) tot += pv[hh];
+          const int m = c0 + col;
+          float sc = El<T>::rnd(tot / (float)Hkv);
+          if (m >= M) sc = -INFINITY;                                   // padding column: never wins
+          else if (m >= active || (exact && !al[W + m])) sc = -1e9f;    // (:646-650, :875-877)
+          Fs[lr * (RS_COLS + 1) + col] = sc;
+        }
+      }
+      __syncthreads();
+      {
+        const int r = h + tid * Hkv;                 // owned row `tid`
+        if (tid < nown_max && r < nrows) {
+          for (int col = 0; col < RS_COLS && c0 + col < M; ++col) {
+            const float sc = Fs[tid * (RS_COLS + 1) + col];
+            if ((c0 == 0 && col == 0) || sc > best) { best = sc; bi = c0 + col; }
+          }
+        }
+      }
+    }
+    {
+      const int r = h + tid * Hkv;
+      if (tid < nown_max && r < nrows) {
+        if (exact) { p.ex_best[(long long)b * c.Te + r0 + r] = best; p.ex_bi[(long long)b * c.Te + r0 + r] = bi; }
+        else p.su_idx[(long long)b * c.Ts + r0 + r] = bi;
+      }
+    }
+  }
+  // no CTA may leave while another still reads its partials
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) route_score_heads_kernel(RouteParams p) {
+  extern __shared__ float sm[];
+  const bool exact = blockIdx.x == 0;
+  // (both branches are uniform over a cluster: its CTAs differ in blockIdx.z only)
+  if (exact) { if (p.te > 0 && p.c.Me > 0) route_score_bank_heads<T, 1>(p, blockIdx.y, true, sm); }
+  else if (p.ts > 0 && p.c.Ms > 0) route_score_bank_heads<T, 4>(p, blockIdx.y, false, sm);
+}
+
 // Per-state plan written by route_decide and consumed by route_apply (all int32 / fp32, in global scratch).
 struct Plan {
   int* e_tgt; int* e_flag;            // [Te]  target slot; bit0 overwrite, bit1 touch, bit2 first overwriter of its slot
@@ -547,8 +718,25 @@ static int launch_route(RouteParams& p, cudaStream_t s, int phase = 0) {
     const size_t smem1 = sizeof(float) * (size_t)(RS_KC * 64 + RS_KC * RS_COLS + 64 * (RS_COLS + 1) + 64 * c.Hkv + 64);
     CODA_REQUIRE(smem1 <= 200 * 1024, CODA_ERR_LIMIT, "route_block: %d KV heads too many for the scoring tile", c.Hkv);
     if (smem1 > 48 * 1024) cudaFuncSetAttribute(route_score_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
-    route_score_kernel<T><<<dim3(2, c.B), 256, smem1, s>>>(p);
-    CODA_CHECK_LAUNCH("route_block (score)");
+    if (c.Hkv >= 2 && c.Hkv <= 8 && c.B <= 65535) {
+      // the heads of a state side by side: clusters of Hkv CTAs along z
+      const size_t smemh = sizeof(float) * (size_t)(RS_KC * 64 + RS_KC * RS_COLS + 64 * RS_COLS + (64 / c.Hkv + 1) * (RS_COLS + 1) + 64 + 64);
+      if (smemh > 48 * 1024) cudaFuncSetAttribute(route_score_heads_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smemh);
+      cudaLaunchConfig_t lc = {};
+      lc.gridDim = dim3(2, c.B, c.Hkv);
+      lc.blockDim = dim3(256, 1, 1);
+      lc.dynamicSmemBytes = smemh;
+      lc.stream = s;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = c.Hkv;
+      lc.attrs = at; lc.numAttrs = 1;
+      cudaError_t e = cudaLaunchKernelEx(&lc, route_score_heads_kernel<T>, p);
+      if (e != cudaSuccess) { coda_set_error("route_block (score): %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
+    } else {
+      route_score_kernel<T><<<dim3(2, c.B), 256, smem1, s>>>(p);
+      CODA_CHECK_LAUNCH("route_block (score)");
+    }
     const int tmax = p.te > p.ts ? p.te : p.ts;
     const size_t smem2 = 32 * (size_t)(c.Me > 0 ? c.Me : 1) + 4 * ((size_t)2 * (tmax + 1) + 4 * (size_t)(p.te + 1) + 4 * (size_t)(p.ts + 1) +
                          3 * (size_t)(c.Ms + 1) + 2) + c.Me + c.Ms + 64;
