@@ -542,7 +542,10 @@ def main():
                        "frac": step_bytes / (ms / K * 1e-3) / 1e9 / hbm_peak},
     }
 
-    per_step_launches = ((2 if args.eager or args.no_split_routing else 1) * w["layers"]
+    # own output-projection GEMM: one more launch of this repository's per layer where the layers use it
+    Dh_ = D // w["H"]
+    own_out = all(l.use_skinny_gemm_kernel and bool(lib.coda_b200_skinny_gemm_supported(B, w["H"] * Dh_, D)) for l in stack.layers)
+    per_step_launches = ((2 if args.eager or args.no_split_routing else 1) * w["layers"] + (w["layers"] if own_out else 0)
                          + (0 if args.eager else (1 if args.no_split_routing else 3)))
     line = {
         "metric": METRIC, "value": tok_s, "unit": "tokens/s",
@@ -552,8 +555,8 @@ def main():
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": B * D * 2, "d2h_bytes_per_step": B * D * 2,
                 "ms_per_step": ms_e2e / K},
         # this repository's kernels inside the timed region: per layer the decode attention (which writes the new
-        # token), per step the batched routing, the cos/sin table and the step counter (the two GEMMs per layer are
-        # library calls)
+        # token) and the output-projection GEMM, per step the batched routing, the cos/sin table and the step counter
+        # (the input projection is a library call)
         "gpu_launches": K * per_step_launches,
         "clocks": clocks.summary(),
         "roofline": roofline,
