@@ -502,6 +502,10 @@ def main():
             l.decode_attend_append_launch(c, st, rp, pr, o, rope_cs)
 
     nl = len(stack.layers)
+    # In the step the attention lets the kernel after it (the output projection) onto SMs as they free up.  In a
+    # train of attention launches that would let consecutive launches overlap, so the trains below are captured
+    # with the implicit trigger at grid completion: the figure stays the duration of one launch.
+    lib.coda_b200_decode_set_early_trigger(0)
     prepared_ms = timed_graph(sweep_prepared) / nl
     append_ms = timed_graph(sweep_append) / nl if append_ok else None
     route_ms = None
@@ -511,6 +515,7 @@ def main():
             check(lib.coda_b200_step_route_batched(C.byref(plan[0]), plan[1].data_ptr(), nl, roof_stream.cuda_stream),
                   "coda_b200_step_route_batched")
         route_ms = timed_graph(route_all)
+    lib.coda_b200_decode_set_early_trigger(1)
     for l in stack.layers:
         if l.device_status() != 0:
             raise RuntimeError("a tuned kernel reported an expired device-side wait")

@@ -53,6 +53,8 @@ def _load() -> C.CDLL:
     lib.coda_b200_decode_attend_supported.argtypes = [cfgp]
     lib.coda_b200_decode_attend.argtypes = [cfgp, stp, RingPos, i32, vp, i64, vp, i64, fp, vp, vp, vp, vp, vp, i64, vp, vp]
     lib.coda_b200_decode_attend_prepared.argtypes = [cfgp, stp, vp, vp, vp, i64, vp, vp]
+    lib.coda_b200_decode_set_early_trigger.argtypes = [i32]
+    lib.coda_b200_decode_set_early_trigger.restype = None
     lib.coda_b200_decode_record_bytes.argtypes = [cfgp]
     lib.coda_b200_decode_record_bytes.restype = C.c_int64
     lib.coda_b200_step_write_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp, fp,
@@ -101,7 +103,7 @@ def _load() -> C.CDLL:
     for name in EXPORTS:
         fn = getattr(lib, name)
         if name not in ("coda_b200_last_error", "coda_b200_route_scratch_bytes", "coda_b200_route_static_scratch_bytes",
-                        "coda_b200_decode_record_bytes", "coda_b200_proj_gemm_workspace_bytes"):
+                        "coda_b200_decode_record_bytes", "coda_b200_decode_set_early_trigger", "coda_b200_proj_gemm_workspace_bytes"):
             fn.restype = C.c_int
     return lib
 
@@ -114,7 +116,7 @@ EXPORTS = (
     "coda_b200_skinny_gemm_supported", "coda_b200_skinny_gemm", "coda_b200_proj_gemm_supported", "coda_b200_proj_gemm", "coda_b200_proj_gemm_workspace_bytes",
     "coda_b200_decode_attend_append_supported", "coda_b200_decode_attend_append", "coda_b200_rope_table",
     "coda_b200_decode_attend_supported", "coda_b200_decode_attend", "coda_b200_decode_attend_prepared",
-    "coda_b200_decode_record_bytes",
+    "coda_b200_decode_record_bytes", "coda_b200_decode_set_early_trigger",
     "coda_b200_prefill_attend_supported", "coda_b200_prefill_attend",
     "coda_b200_attend", "coda_b200_select_candidates", "coda_b200_route_scratch_bytes",
     "coda_b200_route_block", "coda_b200_route_block_phase", "coda_b200_route_static_scratch_bytes", "coda_b200_route_block_noalloc",

@@ -25,6 +25,12 @@
 
 extern "C" int coda_b200_decode_attend_supported(const coda_layer_cfg* cfg);
 
+// Whether the decode attention kernels let the kernel after them be brought onto the SMs as these become free
+// (griddepcontrol.launch_dependents right after their own dependency wait).  On by default; a benchmark that times a
+// train of these launches switches it off so that consecutive launches do not overlap.
+static int g_early_trigger = 1;
+extern "C" void coda_b200_decode_set_early_trigger(int32_t on) { g_early_trigger = on ? 1 : 0; }
+
 namespace {
 
 constexpr int DA_TILE = 64;          // slots per stage
@@ -50,6 +56,7 @@ struct DecodeParams {
   const bf16* cos_t; const bf16* sin_t;
   const float* rope_cs;                           // optional: cos [Dh/2] | sin [Dh/2] of the token's position, precomputed
   bf16* k_buf; bf16* v_buf; uint8_t* allowed_w; float* g_recent;
+  int early_trigger;
 };
 
 using tma::smem_u32; using tma::mbar_init; using tma::mbar_expect_tx; using tma::mbar_arrive; using tma::mbar_try;
@@ -224,6 +231,9 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   }
   // everything above touched no global memory: from here on the previous kernel's results are needed
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The kernel after this one may be brought onto the SMs as they become free (its own griddepcontrol.wait holds
+  // it back from this kernel's results until the whole grid has finished): the CTAs with one plane fewer leave early.
+  if (p.early_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- APPEND: the new token's inputs of one plane, as the auxiliary threads hold them between request and use ----
   constexpr int HALF = DH / 2;
@@ -742,6 +752,7 @@ DecodeParams make_params(const coda_layer_cfg* cfg, const coda_state_ptrs* st, v
   p.inv_freq = nullptr; p.q_raw = nullptr; p.q_bs = 0; p.lam_logit = nullptr; p.lam_bs = 0; p.cos_t = nullptr; p.sin_t = nullptr;
   p.rope_cs = nullptr;
   p.k_buf = nullptr; p.v_buf = nullptr; p.allowed_w = nullptr; p.g_recent = nullptr;
+  p.early_trigger = g_early_trigger;
   return p;
 }
 

@@ -191,6 +191,163 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
   }
 }
 
+
+// ---- the same product with K split four ways -------------------------------------------------------------------
+// A CTA takes in its weight rows AND its share of X, and what bounds the kernel is the bytes one SM can take in
+// (about 45 GB/s).  With a pair per 64 rows every CTA reads half of X: a third of its traffic.  Here a cluster of
+// FOUR CTAs shares a tile of `bn` (112 or 128) weight rows, each CTA reads a quarter of K -- a quarter of X -- and,
+// with 112-row tiles at N = 4096, 37 clusters put a CTA on every one of the 148 SMs.  Consumer warp w owns weight
+// rows 16 w .. 16 w + 15 of the tile and all four k-steps of a box.  At the end the 16-row groups of the tile are
+// dealt out to the four CTAs (group g to CTA g % 4): every CTA sends its partial sums of a group to the group's
+// owner through distributed shared memory, and the owner adds the four partials (in rank order), the residual,
+// and writes.
+constexpr int S4_CL = 4;
+constexpr int S4_STAGES = 8;
+constexpr int S4_MAXBN = 128;
+constexpr int S4_WBOX = S4_MAXBN * 128;      // ring slot (a box of bn <= 128 rows)
+
+struct Skinny4Smem {
+  int x, ring, bars, total;
+  __host__ __device__ explicit Skinny4Smem(int kq) {
+    x = 0;
+    ring = x + (kq / SG_BK) * SG_XBOX;
+    bars = ring + S4_STAGES * S4_WBOX;
+    total = bars + (2 * S4_STAGES + SG_MAXXG) * 8;
+  }
+};
+
+__global__ void __launch_bounds__(SG_THREADS, 1)
+skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, SkinnyParams p, int bn) {
+  extern __shared__ unsigned char sg_raw[];
+  unsigned char* smem = sg_raw + ((1024u - (smem_u32(sg_raw) & 1023u)) & 1023u);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rank = blockIdx.x;                           // cluster rank (cluster dims (4,1,1))
+  const int n0 = blockIdx.y * bn;
+  const int kq = p.K / S4_CL, kbase = rank * kq, nbox = kq / SG_BK;
+  const int ngrp = bn / 16;                              // 16-row groups of the tile = working consumer warps
+  const Skinny4Smem L(kq);
+  unsigned char* xs = smem + L.x;
+  unsigned char* ring = smem + L.ring;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* empty = full + S4_STAGES;
+  uint64_t* xbar = empty + S4_STAGES;
+  const uint32_t wbox_bytes = (uint32_t)bn * 128;
+
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  __shared__ int s_abort;
+  int* const abortw = &s_abort;
+  if (tid == 0) {
+    s_abort = 0;
+    for (int i = 0; i < S4_STAGES; ++i) { tma::mbar_init(&full[i], 1); tma::mbar_init(&empty[i], ngrp); }
+    for (int i = 0; i < SG_MAXXG; ++i) tma::mbar_init(&xbar[i], 1);
+    tma::fence_barrier_init();
+  }
+  __syncthreads();
+
+  float acc[4][4];
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+  const int li = lane >> 3, lr = lane & 7;
+
+  if (warp == SG_CWARPS) {
+    if (lane == 0) {
+      // The weights do not depend on the kernel before this one: the first pass of the ring is requested BEFORE
+      // waiting for it (programmatic dependent launch), X -- that kernel's output -- after.
+      const int pre = min(nbox, S4_STAGES);
+      for (int i = 0; i < pre; ++i) {
+        tma::mbar_expect_tx(&full[i], wbox_bytes);
+        sg_tma_load(ring + i * S4_WBOX, &wmap, &full[i], kbase + i * SG_BK, n0);
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (int i = 0; i < nbox; ++i) {
+        if (i % SG_XGROUP == 0) {
+          const int g = i / SG_XGROUP, nb = min(SG_XGROUP, nbox - i);
+          tma::mbar_expect_tx(&xbar[g], (uint32_t)nb * SG_XBOX);
+          for (int j = 0; j < nb; ++j) sg_tma_load(xs + (i + j) * SG_XBOX, &xmap, &xbar[g], kbase + (i + j) * SG_BK, 0);
+        }
+        if (i < pre) continue;
+        const int s = i % S4_STAGES, round = i / S4_STAGES;
+        if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, p.status, 24, abortw);
+        tma::mbar_expect_tx(&full[s], wbox_bytes);
+        sg_tma_load(ring + s * S4_WBOX, &wmap, &full[s], kbase + i * SG_BK, n0);
+      }
+    }
+    __syncwarp();
+  } else if (warp < ngrp) {
+    const uint32_t xs_u = smem_u32(xs), ring_u = smem_u32(ring);
+    const int wrow = warp * 16 + (li & 1) * 8 + lr;
+    for (int i = 0; i < nbox; ++i) {
+      if (i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 25, abortw);
+      const int s = i % S4_STAGES, round = i / S4_STAGES;
+      tma::mbar_wait(&full[s], round & 1, p.status, 26, abortw);
+      const uint32_t wb = ring_u + s * S4_WBOX, xb = xs_u + i * SG_XBOX;
+      uint32_t a[4][4];                                  // weight fragments of the box's four k-steps
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) sg_ldsm_x4(a[ks], wb + sg_off(wrow, ks * 2 + (li >> 1)));
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t b0[4], b1[4];                           // X^T fragments: k 0-31 and k 32-63 of the box
+        sg_ldsm_x4(b0, xb + sg_off(mt * 8 + lr, li));
+        sg_ldsm_x4(b1, xb + sg_off(mt * 8 + lr, 4 + li));
+        sg_mma(acc[mt], a[0], b0[0], b0[1]);
+        sg_mma(acc[mt], a[1], b0[2], b0[3]);
+        sg_mma(acc[mt], a[2], b1[0], b1[1]);
+        sg_mma(acc[mt], a[3], b1[2], b1[3]);
+      }
+      __syncwarp();
+      if (lane == 0) tma::mbar_arrive(&empty[s]);
+    }
+  }
+
+  // ---- exchange: every CTA has consumed its ring (cluster barrier), whose space then takes the partial sums ----
+  asm volatile("griddepcontrol.wait;" ::: "memory");                   // (residual and output belong to this kernel's place in the stream)
+  asm volatile("barrier.cluster.wait.aligned;" ::: "memory");          // (pairs with the arrive at entry: all CTAs run)
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  // xch[src rank][owner's group slot gs][token 32][row 16] fp32, in the OWNER's shared memory (its ring space)
+  float* xch = reinterpret_cast<float*>(ring);
+  if (warp < ngrp) {
+    const int g = warp, owner = g & 3, gs = g >> 2;
+    const uint32_t base_local = smem_u32(xch + ((rank * 2 + gs) * SG_MAXM) * 16);
+    uint32_t base_remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base_remote) : "r"(base_local), "r"(owner));
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      const int tok = mt * 8 + 2 * (lane & 3), nl = lane >> 2;         // C fragment: rows nl, nl + 8 of the group; tokens tok, tok + 1
+      const uint32_t a0 = base_remote + (uint32_t)((tok * 16 + nl) * 4);
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0), "f"(acc[mt][0]) : "memory");
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 16 * 4), "f"(acc[mt][1]) : "memory");
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 8 * 4), "f"(acc[mt][2]) : "memory");
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + (16 + 8) * 4), "f"(acc[mt][3]) : "memory");
+    }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  // ---- the owner of a group adds the four partials, the residual, and writes 4 consecutive outputs per thread ----
+  if (warp < SG_CWARPS) {
+    const int gs = tid >> 7, g = rank + 4 * gs;                        // group slot, group of the tile
+    const int m = (tid & 127) >> 2, nq = (tid & 3) * 4;                // token, first of 4 rows inside the group
+    const int n = n0 + g * 16 + nq;
+    if (g < ngrp && m < p.M && n < p.N) {
+      float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int src = 0; src < S4_CL; ++src) {
+        const float4 v = *reinterpret_cast<const float4*>(xch + ((src * 2 + gs) * SG_MAXM + m) * 16 + nq);
+        t[0] += v.x; t[1] += v.y; t[2] += v.z; t[3] += v.w;
+      }
+      if (p.res != nullptr) {
+        const uint2 rv = *reinterpret_cast<const uint2*>(p.res + (long long)m * p.res_rs + n);
+        // the product is rounded to bf16 first, as a GEMM followed by a separate add would
+        t[0] = bf16_round(t[0]) + __uint_as_float(rv.x << 16);
+        t[1] = bf16_round(t[1]) + __uint_as_float(rv.x & 0xffff0000u);
+        t[2] = bf16_round(t[2]) + __uint_as_float(rv.y << 16);
+        t[3] = bf16_round(t[3]) + __uint_as_float(rv.y & 0xffff0000u);
+      }
+      uint2 ov;
+      ov.x = bf16_pack(t[0], t[1]); ov.y = bf16_pack(t[2], t[3]);
+      *reinterpret_cast<uint2*>(p.y + (long long)m * p.y_rs + n) = ov;
+    }
+  }
+}
+
 }  // namespace
 
 // Shapes the kernel covers: up to 32 rows, K a multiple of 128 and at most 4096 (each CTA of a pair keeps K/2
@@ -214,6 +371,48 @@ extern "C" int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const 
                "skinny_gemm: cuTensorMapEncodeTiled failed");
   SkinnyParams p;
   p.M = M; p.N = N; p.K = K; p.res = (const bf16*)residual; p.res_rs = res_rs; p.y = (bf16*)y; p.y_rs = y_rs; p.status = status;
+  // The four-way split when its clusters fit the device in one wave: 112-row tiles if that many clusters of four can
+  // be resident at once (37 at N = 4096: a CTA on every SM), else 128-row tiles, else the pair kernel below.
+  if (K % 256 == 0 && K / 4 / SG_BK <= SG_XGROUP * SG_MAXXG && N % 16 == 0 && getenv("CODA_SKINNY_PAIR") == nullptr) {
+    const size_t smem4 = (size_t)Skinny4Smem(K / 4).total + 1024;
+    static coda_device_once once4;
+    static int max_clusters[64];
+    const int dev = coda_current_device();
+    coda_on_first_use(once4, [smem4, dev] {
+      cudaFuncSetAttribute(skinny_gemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+      cudaFuncSetAttribute(skinny_gemm4_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(S4_CL, 64, 1); q.blockDim = dim3(SG_THREADS, 1, 1); q.dynamicSmemBytes = smem4;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = S4_CL; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, skinny_gemm4_kernel, &q) != cudaSuccess) { n = 0; cudaGetLastError(); }
+      if (dev >= 0 && dev < 64) max_clusters[dev] = n;
+    });
+    const int mc = (dev >= 0 && dev < 64) ? max_clusters[dev] : 0;
+    int bn = 0;
+    if ((N + 111) / 112 <= mc) bn = 112; else if ((N + 127) / 128 <= mc) bn = 128;
+    if (bn != 0) {
+      CUtensorMap wm4;
+      CODA_REQUIRE(tmaps::plane_map(&wm4, w, 1, N, K, bn), CODA_ERR_LAUNCH, "skinny_gemm: cuTensorMapEncodeTiled failed");
+      cudaLaunchConfig_t lc4 = {};
+      lc4.gridDim = dim3(S4_CL, (N + bn - 1) / bn, 1);
+      lc4.blockDim = dim3(SG_THREADS, 1, 1);
+      lc4.dynamicSmemBytes = smem4;
+      lc4.stream = (cudaStream_t)stream;
+      cudaLaunchAttribute at4[2];
+      at4[0].id = cudaLaunchAttributeClusterDimension;
+      at4[0].val.clusterDim.x = S4_CL; at4[0].val.clusterDim.y = 1; at4[0].val.clusterDim.z = 1;
+      at4[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at4[1].val.programmaticStreamSerializationAllowed = 1;
+      lc4.attrs = at4; lc4.numAttrs = 2;
+      cudaError_t e4 = cudaLaunchKernelEx(&lc4, skinny_gemm4_kernel, xm, wm4, p, bn);
+      if (e4 != cudaSuccess) { coda_set_error("skinny_gemm (four-way): %s", cudaGetErrorString(e4)); return CODA_ERR_LAUNCH; }
+      return CODA_OK;
+    }
+  }
   const size_t smem = (size_t)SkinnySmem(K / 2).total + 1024;
   static coda_device_once once;
   coda_on_first_use(once, [] {

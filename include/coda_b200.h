@@ -200,6 +200,14 @@ int coda_b200_decode_attend_prepared(const coda_layer_cfg* cfg, const coda_state
                                      const void* norm_w, void* out, int64_t out_bs, int32_t* status,
                                      coda_stream_t stream);
 
+/* Process-wide switch (default 1): the decode attention kernels signal `griddepcontrol.launch_dependents` right
+ * after their own dependency wait, so that a following kernel launched as a programmatic dependent (the output
+ * projection coda_b200_skinny_gemm is) is brought onto SMs as they become free and can stream its weights while the
+ * attention's last planes finish; such a kernel still waits for the whole attention grid before it reads its
+ * result.  0 restores the implicit trigger at grid completion (used to time a train of attention launches without
+ * overlap between them).  Applies to launches made after the call. */
+void coda_b200_decode_set_early_trigger(int32_t on);
+
 /* coda_b200_step_write_fused followed by coda_b200_decode_attend_prepared on the records it wrote, as one call
  * (the default `step` of src/coda_gqa_l/attention.py:516-547 between its projections): same arguments, same two
  * launches, same results; for hosts where a foreign call costs more than the launch it makes. */

@@ -468,11 +468,14 @@ def test_attend_step_tuned_matches_generic():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,K,N,res", [(32, 4096, 4096, True), (32, 4096, 4096, False), (5, 512, 256, True), (1, 128, 64, False),
-                                       (17, 2048, 6208, True)])
+                                       (17, 2048, 6208, True),
+                                       # four-way split: 128-row tiles (112-row ones would need more clusters than fit),
+                                       # a ragged last tile, few rows of X
+                                       (32, 4096, 4608, True), (9, 1024, 4160, True), (3, 256, 64, False)])
 def test_skinny_gemm_matches_library_gemm(M, K, N, res):
-    """The decode step's output projection kernel (weight rows streamed through a TMA ring, K split over a CTA pair,
-    residual in the epilogue) against torch's GEMM: fp32 accumulation on both sides, so the results agree to
-    bf16 rounding of the outputs."""
+    """The decode step's output projection kernels (weight rows streamed through a TMA ring, K split over a cluster of
+    four CTAs or over a CTA pair, residual in the epilogue) against torch's GEMM: fp32 accumulation on both sides, so
+    the results agree to bf16 rounding of the outputs."""
     import ctypes as C
     from coda_gqa_l_b200._lib import lib, check
     g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
