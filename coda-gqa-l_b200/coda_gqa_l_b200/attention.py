@@ -203,6 +203,11 @@ class CoDAGQALandmarkPerf2(nn.Module):
         # + add.  On by default where the shape is supported: in the captured step of the 7B shape the two are at
         # parity (1.290 against 1.287 ms per step, three runs each), and on the eager path it is one host call fewer.
         self.use_skinny_gemm_kernel = True
+        # The fused INPUT projection on the same kernel family (coda_b200_skinny_gemm_bias).  The eager fast path uses
+        # it whenever use_skinny_gemm_kernel is on (one host call instead of a tensor-library call: 1.47 against
+        # 1.67 ms per 32-layer step); inside the captured step the vendor GEMM is 0.9 % faster at the 7B shape (1.205
+        # against 1.216 ms per step, three runs each), so the general path takes the own kernel only when this is set.
+        self.use_skinny_in_proj = False
         # The decode step's two projections (at most 64 rows, bfloat16) on this library's tcgen05 GEMM
         # (coda_b200_proj_gemm: weight rows as the MMA's M, K split over the SMs with a counter-based fix-up, bias /
         # residual in the epilogue, programmatic dependent launch) instead of the vendor GEMM (+ add).  Off by default:
@@ -550,6 +555,27 @@ class CoDAGQALandmarkPerf2(nn.Module):
               "coda_b200_proj_gemm")
         return y
 
+    def _skinny_in(self, x: torch.Tensor, f, rows: int) -> Optional[torch.Tensor]:
+        """The fused input projection of a decode step on this library's own skinny GEMM (bias in its epilogue), where
+        the switch is on and the kernel covers the shape; None otherwise."""
+        if not (self.use_skinny_gemm_kernel and self.use_skinny_in_proj and x.is_cuda and x.dtype == torch.bfloat16 and rows <= 32):
+            return None
+        W, bias = f
+        K, N = W.shape[1], W.shape[0]
+        ok = self._gemm_ok.get(("skinny_in", rows, K, N))
+        if ok is None:
+            ok = self._gemm_ok[("skinny_in", rows, K, N)] = bool(
+                W.dtype == torch.bfloat16 and W.is_contiguous() and W.data_ptr() % 16 == 0 and bias.data_ptr() % 16 == 0
+                and lib.coda_b200_skinny_gemm_bias_supported(rows, K, N))
+        x2 = x.reshape(rows, K)
+        if not ok or not x2.is_contiguous() or x2.data_ptr() % 16:
+            return None
+        y = torch.empty((x.shape[0], x.shape[1], N), device=x.device, dtype=x.dtype)
+        check(lib.coda_b200_skinny_gemm_bias(x2.data_ptr(), rows, K, W.data_ptr(), N, bias.data_ptr(), None, 0, y.data_ptr(), N,
+                                             self._status_word(x.device).data_ptr(), _stream(x.device)),
+              "coda_b200_skinny_gemm_bias")
+        return y
+
     def _decode_bundle(self, device, dtype):
         """Everything an eager decode step needs besides the state, gathered once and re-validated cheaply: the fused
         and transposed weights, the constant tables and their raw addresses.  ``step()`` is called once per layer per
@@ -585,6 +611,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
                  off_gate=(H * Dh + 2 * Hkv * Dh + H) * es, gated=self.write_policy != "none",
                  inv_freq=inv_freq.data_ptr(), cos=cos_t.data_ptr(), sin=sin_t.data_ptr(), eta=eta.data_ptr(), nw=_p(nw),
                  w_out=self.o_proj.weight.data_ptr(), n_out=self.o_proj.weight.shape[0], skinny_ok={},
+                 w_in=f[0].data_ptr(), bias_ptr=f[1].data_ptr(), skinny_in_ok={},
                  keep=(inv_freq, cos_t, sin_t, eta, nw, f, wt))
         self.__dict__["_bundle"] = c
         return c
@@ -622,7 +649,22 @@ class CoDAGQALandmarkPerf2(nn.Module):
             pc = (kptr, self._ptrs(st), st._exact_v_norm, st._sum_lf_k_norm)
             st.__dict__["_pc"] = pc
         ptrs = pc[1]
-        y = torch.addmm(bd["bias"], x.reshape(B, -1), bd["w_in_t"])
+        y = None
+        if self.use_skinny_gemm_kernel:
+            ok = bd["skinny_in_ok"].get(B)
+            if ok is None:
+                f = bd["keep"][5]
+                ok = bd["skinny_in_ok"][B] = bool(f[0].is_contiguous() and f[0].data_ptr() % 16 == 0 and f[1].data_ptr() % 16 == 0
+                                                  and lib.coda_b200_skinny_gemm_bias_supported(B, f[0].shape[1], f[0].shape[0]))
+            x2 = x.reshape(B, -1)
+            if ok and x2.is_contiguous() and x2.data_ptr() % 16 == 0:
+                y = torch.empty((B, bd["npad"]), device=dev, dtype=x.dtype)
+                rc = lib.coda_b200_skinny_gemm_bias(x2.data_ptr(), B, x2.shape[1], bd["w_in"], bd["npad"], bd["bias_ptr"], None, 0,
+                                                    y.data_ptr(), bd["npad"], self._status_word(dev).data_ptr(), _stream(dev))
+                if rc:
+                    check(rc, "coda_b200_skinny_gemm_bias")
+        if y is None:
+            y = torch.addmm(bd["bias"], x.reshape(B, -1), bd["w_in_t"])
         base, npad = y.data_ptr(), bd["npad"]
         if base % 16:
             return None
@@ -666,6 +708,8 @@ class CoDAGQALandmarkPerf2(nn.Module):
             H, Hkv, Dh = self.num_heads, self.num_kv_heads, self.head_dim
             rows = x.shape[0] * x.shape[1]
             y = self._own_gemm(x, f[0], f[1], None)
+            if y is None:
+                y = self._skinny_in(x, f, rows)
             wt = self._skinny_weights() if y is None and rows <= self.SKINNY_ROWS else None
             if y is not None:
                 pass

@@ -137,7 +137,7 @@ class CoDAStack(nn.Module):
             qw, ow = layer.q_proj.weight, layer.o_proj.weight
             key.append((id(st), st.active_exact, st.active_summary, qw.data_ptr(), qw._version, ow.data_ptr(),
                         ow._version, layer.theta._version, layer.summary_eta_logit._version,
-                        layer.use_tuned_kernels, layer.fuse_append_into_attention, layer.use_skinny_gemm_kernel,
+                        layer.use_tuned_kernels, layer.fuse_append_into_attention, layer.use_skinny_gemm_kernel, layer.use_skinny_in_proj,
                         layer.use_own_gemm))
         return key
 

@@ -30,6 +30,7 @@ constexpr int SG_XBOX = SG_MAXM * 128;
 struct SkinnyParams {
   int M, N, K;
   const bf16* res; long long res_rs;   // optional residual [M][N]
+  const bf16* bias;                    // optional bias [N] (four-way kernel)
   bf16* y; long long y_rs;
   int* status;
 };
@@ -195,29 +196,32 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 // ---- the same product with K split four ways -------------------------------------------------------------------
 // A CTA takes in its weight rows AND its share of X, and what bounds the kernel is the bytes one SM can take in
 // (about 45 GB/s).  With a pair per 64 rows every CTA reads half of X: a third of its traffic.  Here a cluster of
-// FOUR CTAs shares a tile of `bn` (112 or 128) weight rows, each CTA reads a quarter of K -- a quarter of X -- and,
-// with 112-row tiles at N = 4096, 37 clusters put a CTA on every one of the 148 SMs.  Consumer warp w owns weight
-// rows 16 w .. 16 w + 15 of the tile and all four k-steps of a box.  At the end the 16-row groups of the tile are
-// dealt out to the four CTAs (group g to CTA g % 4): every CTA sends its partial sums of a group to the group's
-// owner through distributed shared memory, and the owner adds the four partials (in rank order), the residual,
-// and writes.
+// FOUR CTAs shares a tile of `bn` weight rows (a multiple of 16, chosen so that the clusters fill the device in one
+// wave: 112 at N = 4096, 176 at N = 6208), each CTA reads a quarter of K -- a quarter of X.  Consumer warp w owns
+// weight rows 16 w .. 16 w + 15 of the tile and all four k-steps of a box.  At the end the 16-row groups of the tile
+// are dealt out to the four CTAs (group g to CTA g % 4): every CTA sends its partial sums of a group to the group's
+// owner through distributed shared memory, and the owner adds the four partials (in rank order), bias or residual,
+// and writes.  Launched as a programmatic dependent: the first ring pass of WEIGHT boxes goes out before the wait
+// for the kernel that produces X, and the kernel after this one is let onto the SMs from the start.
+// CW: consumer warps (tiles of up to 16 CW rows); STAGES ring slots of 16 CW x 128 bytes.
 constexpr int S4_CL = 4;
-constexpr int S4_STAGES = 8;
-constexpr int S4_MAXBN = 128;
-constexpr int S4_WBOX = S4_MAXBN * 128;      // ring slot (a box of bn <= 128 rows)
 
+template <int CW, int STAGES>
 struct Skinny4Smem {
+  static constexpr int SLOT = CW * 16 * 128;
   int x, ring, bars, total;
   __host__ __device__ explicit Skinny4Smem(int kq) {
     x = 0;
     ring = x + (kq / SG_BK) * SG_XBOX;
-    bars = ring + S4_STAGES * S4_WBOX;
-    total = bars + (2 * S4_STAGES + SG_MAXXG) * 8;
+    bars = ring + STAGES * SLOT;
+    total = bars + (2 * STAGES + SG_MAXXG) * 8;
   }
 };
 
-__global__ void __launch_bounds__(SG_THREADS, 1)
+template <int CW, int STAGES>
+__global__ void __launch_bounds__((CW + 1) * 32, 1)
 skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, SkinnyParams p, int bn) {
+  constexpr int SLOT = Skinny4Smem<CW, STAGES>::SLOT;
   extern __shared__ unsigned char sg_raw[];
   unsigned char* smem = sg_raw + ((1024u - (smem_u32(sg_raw) & 1023u)) & 1023u);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -225,20 +229,21 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   const int n0 = blockIdx.y * bn;
   const int kq = p.K / S4_CL, kbase = rank * kq, nbox = kq / SG_BK;
   const int ngrp = bn / 16;                              // 16-row groups of the tile = working consumer warps
-  const Skinny4Smem L(kq);
+  const Skinny4Smem<CW, STAGES> L(kq);
   unsigned char* xs = smem + L.x;
   unsigned char* ring = smem + L.ring;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
-  uint64_t* empty = full + S4_STAGES;
-  uint64_t* xbar = empty + S4_STAGES;
+  uint64_t* empty = full + STAGES;
+  uint64_t* xbar = empty + STAGES;
   const uint32_t wbox_bytes = (uint32_t)bn * 128;
 
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ int s_abort;
   int* const abortw = &s_abort;
   if (tid == 0) {
     s_abort = 0;
-    for (int i = 0; i < S4_STAGES; ++i) { tma::mbar_init(&full[i], 1); tma::mbar_init(&empty[i], ngrp); }
+    for (int i = 0; i < STAGES; ++i) { tma::mbar_init(&full[i], 1); tma::mbar_init(&empty[i], ngrp); }
     for (int i = 0; i < SG_MAXXG; ++i) tma::mbar_init(&xbar[i], 1);
     tma::fence_barrier_init();
   }
@@ -249,14 +254,14 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   for (int mt = 0; mt < 4; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
   const int li = lane >> 3, lr = lane & 7;
 
-  if (warp == SG_CWARPS) {
+  if (warp == CW) {
     if (lane == 0) {
       // The weights do not depend on the kernel before this one: the first pass of the ring is requested BEFORE
-      // waiting for it (programmatic dependent launch), X -- that kernel's output -- after.
-      const int pre = min(nbox, S4_STAGES);
+      // waiting for it, X -- that kernel's output -- after.
+      const int pre = min(nbox, STAGES);
       for (int i = 0; i < pre; ++i) {
         tma::mbar_expect_tx(&full[i], wbox_bytes);
-        sg_tma_load(ring + i * S4_WBOX, &wmap, &full[i], kbase + i * SG_BK, n0);
+        sg_tma_load(ring + i * SLOT, &wmap, &full[i], kbase + i * SG_BK, n0);
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int i = 0; i < nbox; ++i) {
@@ -266,10 +271,10 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           for (int j = 0; j < nb; ++j) sg_tma_load(xs + (i + j) * SG_XBOX, &xmap, &xbar[g], kbase + (i + j) * SG_BK, 0);
         }
         if (i < pre) continue;
-        const int s = i % S4_STAGES, round = i / S4_STAGES;
+        const int s = i % STAGES, round = i / STAGES;
         if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, p.status, 24, abortw);
         tma::mbar_expect_tx(&full[s], wbox_bytes);
-        sg_tma_load(ring + s * S4_WBOX, &wmap, &full[s], kbase + i * SG_BK, n0);
+        sg_tma_load(ring + s * SLOT, &wmap, &full[s], kbase + i * SG_BK, n0);
       }
     }
     __syncwarp();
@@ -278,9 +283,9 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     const int wrow = warp * 16 + (li & 1) * 8 + lr;
     for (int i = 0; i < nbox; ++i) {
       if (i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 25, abortw);
-      const int s = i % S4_STAGES, round = i / S4_STAGES;
+      const int s = i % STAGES, round = i / STAGES;
       tma::mbar_wait(&full[s], round & 1, p.status, 26, abortw);
-      const uint32_t wb = ring_u + s * S4_WBOX, xb = xs_u + i * SG_XBOX;
+      const uint32_t wb = ring_u + s * SLOT, xb = xs_u + i * SG_XBOX;
       uint32_t a[4][4];                                  // weight fragments of the box's four k-steps
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) sg_ldsm_x4(a[ks], wb + sg_off(wrow, ks * 2 + (li >> 1)));
@@ -300,14 +305,15 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   }
 
   // ---- exchange: every CTA has consumed its ring (cluster barrier), whose space then takes the partial sums ----
-  asm volatile("griddepcontrol.wait;" ::: "memory");                   // (residual and output belong to this kernel's place in the stream)
+  asm volatile("griddepcontrol.wait;" ::: "memory");                   // (bias, residual and output belong to this kernel's place in the stream)
   asm volatile("barrier.cluster.wait.aligned;" ::: "memory");          // (pairs with the arrive at entry: all CTAs run)
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   // xch[src rank][owner's group slot gs][token 32][row 16] fp32, in the OWNER's shared memory (its ring space)
+  constexpr int GS = (CW + 3) / 4;                                     // group slots per owner
   float* xch = reinterpret_cast<float*>(ring);
   if (warp < ngrp) {
     const int g = warp, owner = g & 3, gs = g >> 2;
-    const uint32_t base_local = smem_u32(xch + ((rank * 2 + gs) * SG_MAXM) * 16);
+    const uint32_t base_local = smem_u32(xch + ((rank * GS + gs) * SG_MAXM) * 16);
     uint32_t base_remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base_remote) : "r"(base_local), "r"(owner));
 #pragma unroll
@@ -321,17 +327,22 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     }
   }
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-  // ---- the owner of a group adds the four partials, the residual, and writes 4 consecutive outputs per thread ----
-  if (warp < SG_CWARPS) {
+  // ---- the owner of a group adds the four partials, bias / residual, and writes 4 consecutive outputs per thread ----
+  if (warp < CW) {
     const int gs = tid >> 7, g = rank + 4 * gs;                        // group slot, group of the tile
     const int m = (tid & 127) >> 2, nq = (tid & 3) * 4;                // token, first of 4 rows inside the group
     const int n = n0 + g * 16 + nq;
-    if (g < ngrp && m < p.M && n < p.N) {
+    if (gs < GS && g < ngrp && m < p.M && n < p.N) {
       float t[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int src = 0; src < S4_CL; ++src) {
-        const float4 v = *reinterpret_cast<const float4*>(xch + ((src * 2 + gs) * SG_MAXM + m) * 16 + nq);
+        const float4 v = *reinterpret_cast<const float4*>(xch + ((src * GS + gs) * SG_MAXM + m) * 16 + nq);
         t[0] += v.x; t[1] += v.y; t[2] += v.z; t[3] += v.w;
+      }
+      if (p.bias != nullptr) {                                         // fp32 sum + bias, one rounding (a linear layer's epilogue)
+        const uint2 bv = *reinterpret_cast<const uint2*>(p.bias + n);
+        t[0] += __uint_as_float(bv.x << 16); t[1] += __uint_as_float(bv.x & 0xffff0000u);
+        t[2] += __uint_as_float(bv.y << 16); t[3] += __uint_as_float(bv.y & 0xffff0000u);
       }
       if (p.res != nullptr) {
         const uint2 rv = *reinterpret_cast<const uint2*>(p.res + (long long)m * p.res_rs + n);
@@ -348,6 +359,65 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   }
 }
 
+// One instance of the four-way kernel: set-up once per device, clusters that fit at once, launch.
+template <int CW, int STAGES>
+struct Skinny4 {
+  static int max_clusters(size_t smem) {
+    static coda_device_once once;
+    static int mc[64];
+    const int dev = coda_current_device();
+    coda_on_first_use(once, [smem, dev] {
+      cudaFuncSetAttribute(skinny_gemm4_kernel<CW, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(S4_CL, 64, 1); q.blockDim = dim3((CW + 1) * 32, 1, 1); q.dynamicSmemBytes = smem;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = S4_CL; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, skinny_gemm4_kernel<CW, STAGES>, &q) != cudaSuccess) { n = 0; cudaGetLastError(); }
+      if (dev >= 0 && dev < 64) mc[dev] = n;
+    });
+    return (dev >= 0 && dev < 64) ? mc[dev] : 0;
+  }
+  static int launch(const CUtensorMap& xm, const void* w, const SkinnyParams& p, int bn, size_t smem, cudaStream_t stream) {
+    CUtensorMap wm;
+    CODA_REQUIRE(tmaps::plane_map(&wm, w, 1, p.N, p.K, bn), CODA_ERR_LAUNCH, "skinny_gemm: cuTensorMapEncodeTiled failed");
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(S4_CL, (p.N + bn - 1) / bn, 1);
+    lc.blockDim = dim3((CW + 1) * 32, 1, 1);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = S4_CL; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&lc, skinny_gemm4_kernel<CW, STAGES>, xm, wm, p, bn);
+    if (e != cudaSuccess) { coda_set_error("skinny_gemm (four-way): %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
+    return CODA_OK;
+  }
+};
+
+// Tile height for the four-way kernel: the smallest multiple of 16 rows with which the clusters fit the device at
+// once; 0 when no instance covers it.  `cw` receives the instance (8 or 12 consumer warps).
+static int skinny4_plan(int K, int N, int* cw) {
+  if (K % 256 != 0 || K / 4 / SG_BK > SG_XGROUP * SG_MAXXG || N % 16 != 0) return 0;
+  const int kq = K / 4;
+  const int mc8 = Skinny4<8, 8>::max_clusters((size_t)Skinny4Smem<8, 8>(kq).total + 1024);
+  if (mc8 > 0) {
+    const int bn = ((N + mc8 - 1) / mc8 + 15) / 16 * 16;
+    if (bn <= 128) { *cw = 8; return bn < 16 ? 16 : bn; }
+  }
+  const int mc12 = Skinny4<12, 6>::max_clusters((size_t)Skinny4Smem<12, 6>(kq).total + 1024);
+  if (mc12 > 0) {
+    const int bn = ((N + mc12 - 1) / mc12 + 15) / 16 * 16;
+    if (bn <= 192) { *cw = 12; return bn; }
+  }
+  return 0;
+}
+
 }  // namespace
 
 // Shapes the kernel covers: up to 32 rows, K a multiple of 128 and at most 4096 (each CTA of a pair keeps K/2
@@ -360,59 +430,33 @@ extern "C" int coda_b200_skinny_gemm_supported(int32_t M, int32_t K, int32_t N) 
 extern "C" int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, int32_t N,
                                      const void* residual, int64_t res_rs, void* y, int64_t y_rs,
                                      int32_t* status, coda_stream_t stream) {
+  return coda_b200_skinny_gemm_bias(x, M, K, w, N, nullptr, residual, res_rs, y, y_rs, status, stream);
+}
+
+extern "C" int coda_b200_skinny_gemm_bias(const void* x, int32_t M, int32_t K, const void* w, int32_t N, const void* bias,
+                                          const void* residual, int64_t res_rs, void* y, int64_t y_rs,
+                                          int32_t* status, coda_stream_t stream) {
   CODA_REQUIRE(coda_b200_skinny_gemm_supported(M, K, N), CODA_ERR_ARG,
                "skinny_gemm: needs 1..32 rows, K a multiple of 128 up to 4096, N a multiple of 64 (got %d x %d -> %d)", M, K, N);
   CODA_REQUIRE(x && w && y && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)y % 16 == 0 && y_rs % 8 == 0 && y_rs >= N,
                CODA_ERR_ARG, "skinny_gemm: null or misaligned pointer / output stride");
   CODA_REQUIRE(!residual || ((uintptr_t)residual % 16 == 0 && res_rs % 8 == 0 && res_rs >= N), CODA_ERR_ARG,
                "skinny_gemm: misaligned residual");
+  CODA_REQUIRE(!bias || (uintptr_t)bias % 16 == 0, CODA_ERR_ARG, "skinny_gemm: misaligned bias");
   CUtensorMap xm, wm;
-  CODA_REQUIRE(tmaps::plane_map(&xm, x, 1, M, K, SG_MAXM) && tmaps::plane_map(&wm, w, 1, N, K, SG_BN), CODA_ERR_LAUNCH,
-               "skinny_gemm: cuTensorMapEncodeTiled failed");
+  CODA_REQUIRE(tmaps::plane_map(&xm, x, 1, M, K, SG_MAXM), CODA_ERR_LAUNCH, "skinny_gemm: cuTensorMapEncodeTiled failed");
   SkinnyParams p;
-  p.M = M; p.N = N; p.K = K; p.res = (const bf16*)residual; p.res_rs = res_rs; p.y = (bf16*)y; p.y_rs = y_rs; p.status = status;
-  // The four-way split when its clusters fit the device in one wave: 112-row tiles if that many clusters of four can
-  // be resident at once (37 at N = 4096: a CTA on every SM), else 128-row tiles, else the pair kernel below.
-  if (K % 256 == 0 && K / 4 / SG_BK <= SG_XGROUP * SG_MAXXG && N % 16 == 0 && getenv("CODA_SKINNY_PAIR") == nullptr) {
-    const size_t smem4 = (size_t)Skinny4Smem(K / 4).total + 1024;
-    static coda_device_once once4;
-    static int max_clusters[64];
-    const int dev = coda_current_device();
-    coda_on_first_use(once4, [smem4, dev] {
-      cudaFuncSetAttribute(skinny_gemm4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-      cudaFuncSetAttribute(skinny_gemm4_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
-      cudaLaunchConfig_t q = {};
-      q.gridDim = dim3(S4_CL, 64, 1); q.blockDim = dim3(SG_THREADS, 1, 1); q.dynamicSmemBytes = smem4;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = S4_CL; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
-      q.attrs = qa; q.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, skinny_gemm4_kernel, &q) != cudaSuccess) { n = 0; cudaGetLastError(); }
-      if (dev >= 0 && dev < 64) max_clusters[dev] = n;
-    });
-    const int mc = (dev >= 0 && dev < 64) ? max_clusters[dev] : 0;
-    int bn = 0;
-    if ((N + 111) / 112 <= mc) bn = 112; else if ((N + 127) / 128 <= mc) bn = 128;
-    if (bn != 0) {
-      CUtensorMap wm4;
-      CODA_REQUIRE(tmaps::plane_map(&wm4, w, 1, N, K, bn), CODA_ERR_LAUNCH, "skinny_gemm: cuTensorMapEncodeTiled failed");
-      cudaLaunchConfig_t lc4 = {};
-      lc4.gridDim = dim3(S4_CL, (N + bn - 1) / bn, 1);
-      lc4.blockDim = dim3(SG_THREADS, 1, 1);
-      lc4.dynamicSmemBytes = smem4;
-      lc4.stream = (cudaStream_t)stream;
-      cudaLaunchAttribute at4[2];
-      at4[0].id = cudaLaunchAttributeClusterDimension;
-      at4[0].val.clusterDim.x = S4_CL; at4[0].val.clusterDim.y = 1; at4[0].val.clusterDim.z = 1;
-      at4[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      at4[1].val.programmaticStreamSerializationAllowed = 1;
-      lc4.attrs = at4; lc4.numAttrs = 2;
-      cudaError_t e4 = cudaLaunchKernelEx(&lc4, skinny_gemm4_kernel, xm, wm4, p, bn);
-      if (e4 != cudaSuccess) { coda_set_error("skinny_gemm (four-way): %s", cudaGetErrorString(e4)); return CODA_ERR_LAUNCH; }
-      return CODA_OK;
-    }
+  p.M = M; p.N = N; p.K = K; p.res = (const bf16*)residual; p.res_rs = res_rs; p.bias = (const bf16*)bias;
+  p.y = (bf16*)y; p.y_rs = y_rs; p.status = status;
+  // The four-way split whenever an instance covers the shape with its clusters resident at once
+  int cw = 0;
+  const int bn = skinny4_plan(K, N, &cw);
+  if (bn != 0) {
+    if (cw == 8) return Skinny4<8, 8>::launch(xm, w, p, bn, (size_t)Skinny4Smem<8, 8>(K / 4).total + 1024, (cudaStream_t)stream);
+    return Skinny4<12, 6>::launch(xm, w, p, bn, (size_t)Skinny4Smem<12, 6>(K / 4).total + 1024, (cudaStream_t)stream);
   }
+  CODA_REQUIRE(!bias, CODA_ERR_LIMIT, "skinny_gemm: the bias epilogue needs the four-way kernel, which does not cover %d x %d -> %d here", M, K, N);
+  CODA_REQUIRE(tmaps::plane_map(&wm, w, 1, N, K, SG_BN), CODA_ERR_LAUNCH, "skinny_gemm: cuTensorMapEncodeTiled failed");
   const size_t smem = (size_t)SkinnySmem(K / 2).total + 1024;
   static coda_device_once once;
   coda_on_first_use(once, [] {
@@ -430,4 +474,11 @@ extern "C" int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const 
   cudaError_t e = cudaLaunchKernelEx(&lc, skinny_gemm_kernel, xm, wm, p);
   if (e != cudaSuccess) { coda_set_error("skinny_gemm: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
   return CODA_OK;
+}
+
+// Whether coda_b200_skinny_gemm_bias can take a bias for this shape on the current device (the four-way kernel covers it).
+extern "C" int coda_b200_skinny_gemm_bias_supported(int32_t M, int32_t K, int32_t N) {
+  if (!coda_b200_skinny_gemm_supported(M, K, N)) return 0;
+  int cw = 0;
+  return skinny4_plan(K, N, &cw) != 0;
 }

@@ -231,6 +231,16 @@ int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, in
                           const void* residual, int64_t res_rs, void* y, int64_t y_rs,
                           int32_t* status, coda_stream_t stream);
 
+/* The same product with a bias[N] added to the fp32 sum before its one rounding: the decode step's fused input
+ * projection (the nn.Linear calls of src/coda_gqa_l/attention.py:396-410,508 as one [q|k|v|lambda|gate] matrix).
+ * Runs on the variant of the kernel that splits K over clusters of four CTAs; coda_b200_skinny_gemm_bias_supported
+ * tells whether that variant covers the shape on the current device (its clusters must be resident at once).
+ * bias may be NULL (then this is coda_b200_skinny_gemm). */
+int coda_b200_skinny_gemm_bias_supported(int32_t M, int32_t K, int32_t N);
+int coda_b200_skinny_gemm_bias(const void* x, int32_t M, int32_t K, const void* w, int32_t N, const void* bias,
+                               const void* residual, int64_t res_rs, void* y, int64_t y_rs,
+                               int32_t* status, coda_stream_t stream);
+
 /* The decode step's two projections on the tcgen05 tensor cores: y[M][N] = x[M][K] . w[N][K]^T (+ bias[N]) (+ residual[M][N]),
  * bf16 with fp32 accumulation, M <= 64 rows.  Replaces the nn.Linear calls of src/coda_gqa_l/attention.py:396-410,508 (the
  * q / k / v / lambda / write-gate projections, given here as ONE weight matrix whose rows are the five weights stacked,

@@ -500,6 +500,33 @@ def test_skinny_gemm_matches_library_gemm(M, K, N, res):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N", [(32, 4096, 6208), (7, 1024, 1088), (32, 2048, 4096), (1, 256, 64)])
+def test_skinny_gemm_with_bias_matches_linear(M, K, N):
+    """The fused input projection's kernel (`coda_b200_skinny_gemm_bias`: K split over clusters of four CTAs, tile
+    height chosen so that the clusters fill the device, bias added to the fp32 sum) against `F.linear`."""
+    from coda_gqa_l_b200._lib import lib, check
+    if not lib.coda_b200_skinny_gemm_bias_supported(M, K, N):
+        pytest.skip("the four-way kernel does not cover this shape on this device")
+    g = torch.Generator(device="cuda").manual_seed(M + K + N)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
+    y = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(3):                                                    # repeated launches: same bits
+        check(lib.coda_b200_skinny_gemm_bias(x.data_ptr(), M, K, w.data_ptr(), N, b.data_ptr(), None, 0, y.data_ptr(), N,
+                                             status.data_ptr(), torch.cuda.current_stream().cuda_stream), "coda_b200_skinny_gemm_bias")
+        torch.cuda.synchronize()
+        y_prev = y.clone() if _ == 0 else y_prev
+        assert torch.equal(y, y_prev)
+    assert int(status.item()) == 0
+    ref = (x.float() @ w.float().t() + b.float()).to(torch.bfloat16)
+    assert torch.isfinite(y.float()).all()
+    assert rel_err(y, ref) < 4e-3
+    assert float((y.float() - ref.float()).abs().max()) <= 2.0 ** -7 * float(ref.float().abs().max())
+
+
+@pytest.mark.gpu
 def test_decode_step_with_own_output_gemm_matches_library_gemm():
     """`use_skinny_gemm_kernel` swaps the decode step's output projection (+ residual) for this library's kernel."""
     from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, _deep_copy_state
