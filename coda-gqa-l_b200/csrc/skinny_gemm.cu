@@ -196,8 +196,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 // ---- the same product with K split four ways -------------------------------------------------------------------
 // A CTA takes in its weight rows AND its share of X, and what bounds the kernel is the bytes one SM can take in
 // (about 45 GB/s).  With a pair per 64 rows every CTA reads half of X: a third of its traffic.  Here a cluster of
-// FOUR CTAs shares a tile of `bn` weight rows (a multiple of 16, chosen so that the clusters fill the device in one
-// wave: 112 at N = 4096, 176 at N = 6208), each CTA reads a quarter of K -- a quarter of X.  Consumer warp w owns
+// FOUR CTAs shares a tile of `bn` weight rows (the smallest multiple of 16 with which all clusters are resident at
+// once, as the occupancy query of the device says: 128 at N = 4096 where 32 clusters of four fit), each CTA reads
+// a quarter of K -- a quarter of X.  Consumer warp w owns
 // weight rows 16 w .. 16 w + 15 of the tile and all four k-steps of a box.  At the end the 16-row groups of the tile
 // are dealt out to the four CTAs (group g to CTA g % 4): every CTA sends its partial sums of a group to the group's
 // owner through distributed shared memory, and the owner adds the four partials (in rank order), bias or residual,
