@@ -477,6 +477,16 @@ extern "C" int coda_b200_skinny_gemm_bias(const void* x, int32_t M, int32_t K, c
   return CODA_OK;
 }
 
+// How the four-way kernel would cover a shape on the current device: tile height in weight rows (0: not covered) and
+// the number of clusters of four CTAs it launches.
+extern "C" int coda_b200_skinny_gemm_plan(int32_t K, int32_t N, int32_t* tile_rows, int32_t* clusters) {
+  int cw = 0;
+  const int bn = skinny4_plan(K, N, &cw);
+  if (tile_rows) *tile_rows = bn;
+  if (clusters) *clusters = bn ? (N + bn - 1) / bn : 0;
+  return bn != 0;
+}
+
 // Whether coda_b200_skinny_gemm_bias can take a bias for this shape on the current device (the four-way kernel covers it).
 extern "C" int coda_b200_skinny_gemm_bias_supported(int32_t M, int32_t K, int32_t N) {
   if (!coda_b200_skinny_gemm_supported(M, K, N)) return 0;

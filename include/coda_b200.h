@@ -237,6 +237,9 @@ int coda_b200_skinny_gemm(const void* x, int32_t M, int32_t K, const void* w, in
  * tells whether that variant covers the shape on the current device (its clusters must be resident at once).
  * bias may be NULL (then this is coda_b200_skinny_gemm). */
 int coda_b200_skinny_gemm_bias_supported(int32_t M, int32_t K, int32_t N);
+/* How the four-way variant covers K x N on the current device: tile height in weight rows (0 when it does not)
+ * and the number of clusters of four CTAs launched; returns whether it is covered. */
+int coda_b200_skinny_gemm_plan(int32_t K, int32_t N, int32_t* tile_rows, int32_t* clusters);
 int coda_b200_skinny_gemm_bias(const void* x, int32_t M, int32_t K, const void* w, int32_t N, const void* bias,
                                const void* residual, int64_t res_rs, void* y, int64_t y_rs,
                                int32_t* status, coda_stream_t stream);

@@ -780,3 +780,19 @@ def test_vectorised_projection_postprocessing_equals_elementwise_kernel(dtype, i
     for a, b, name in zip(outs[0], outs[1], ("q", "k", "q_noise", "lambda", "gate")):
         assert torch.equal(a, b), f"{name} differs between the vector and the element-wise kernel"
     assert not torch.equal(outs[0][0], outs[0][2])               # the noise rotation did something
+
+
+@pytest.mark.gpu
+def test_four_way_gemm_plan_keeps_its_clusters_resident():
+    """The launcher of the four-way GEMM sizes its tiles from the device's own answer to "how many clusters of four
+    fit at once": every planned launch is one wave, and its tiles cover all weight rows."""
+    import ctypes as C
+    from coda_gqa_l_b200._lib import lib
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for K, N in ((4096, 4096), (4096, 6208), (2048, 4096), (1024, 1088), (256, 64)):
+        t, c = C.c_int32(), C.c_int32()
+        if not lib.coda_b200_skinny_gemm_plan(K, N, C.byref(t), C.byref(c)):
+            continue
+        assert t.value % 16 == 0 and 16 <= t.value <= 192
+        assert c.value * t.value >= N and (c.value - 1) * t.value < N
+        assert 4 * c.value <= sms
