@@ -9,14 +9,37 @@ independent states across ranks and needs no collective on this path.
 from __future__ import annotations
 
 import ctypes as C
+import operator
 from typing import List, Optional
 
 import torch
 import torch.nn as nn
+from torch.nn.modules import module as _nn_module
 
 from ._lib import RingPos, StatePtrs, check, lib
 from .attention import CoDAGQALandmarkPerf2
 from .state import CoDAGQALandmarkStatePerf2
+
+
+# A captured step is keyed on the parameters its weight copies come from.  Reading 32 layers' parameters through
+# ``nn.Module`` attribute look-ups before every replay costs more host time than the launch itself, so the stack
+# keeps the Parameter objects in a flat tuple and lets ``map`` read their version counters and addresses; the
+# tuple is rebuilt whenever any module of the process registers a parameter or a sub-module (an epoch that torch's
+# registration hooks advance), which is what replacing a Parameter object instead of writing into it does.
+_REGISTRATION_EPOCH = [0]
+
+
+def _bump_epoch(*_args):
+    _REGISTRATION_EPOCH[0] += 1
+    return None
+
+
+_nn_module.register_module_parameter_registration_hook(_bump_epoch)
+_nn_module.register_module_module_registration_hook(_bump_epoch)
+_version_of = operator.attrgetter("_version")
+_switches_of = operator.attrgetter("use_tuned_kernels", "fuse_append_into_attention", "use_skinny_gemm_kernel",
+                                   "use_skinny_in_proj", "use_own_gemm")
+_banks_of = operator.attrgetter("active_exact", "active_summary")
 
 
 class CoDAStack(nn.Module):
@@ -28,6 +51,7 @@ class CoDAStack(nn.Module):
         self.layers = nn.ModuleList(layers)
         self.residual = bool(residual)
         self._graph = None
+        self._watch = None                       # (epoch, layers, versioned tensors, addressed tensors)
         # Captured decode step: route every layer's evicted token in one launch at the start of the step instead of
         # inside each layer's own chain (set before the first step_graph).
         self.split_routing = True
@@ -132,14 +156,15 @@ class CoDAStack(nn.Module):
         the state objects and their active bank sizes, the layers' switches, and address + version counter of the
         parameters the derived weight copies and constants are built from (``load_state_dict``, in-place updates and
         ``.to()`` all move one of the two).  After writing a parameter through ``.data`` call :meth:`invalidate`."""
-        key = [self.split_routing, self.residual, dtype]
-        for layer, st in zip(self.layers, states):
-            qw, ow = layer.q_proj.weight, layer.o_proj.weight
-            key.append((id(st), st.active_exact, st.active_summary, qw.data_ptr(), qw._version, ow.data_ptr(),
-                        ow._version, layer.theta._version, layer.summary_eta_logit._version,
-                        layer.use_tuned_kernels, layer.fuse_append_into_attention, layer.use_skinny_gemm_kernel, layer.use_skinny_in_proj,
-                        layer.use_own_gemm))
-        return key
+        w = self._watch
+        if w is None or w[0] != _REGISTRATION_EPOCH[0]:
+            layers = tuple(self.layers)
+            weights = tuple(t for l in layers for t in (l.q_proj.weight, l.o_proj.weight))
+            w = self._watch = (_REGISTRATION_EPOCH[0], layers,
+                               weights + tuple(t for l in layers for t in (l.theta, l.summary_eta_logit)), weights)
+        return (self.split_routing, self.residual, dtype, w[0], tuple(map(_version_of, w[2])),
+                tuple(map(torch.Tensor.data_ptr, w[3])), tuple(map(_switches_of, w[1])),
+                tuple(map(id, states)), tuple(map(_banks_of, states)))
 
     def invalidate(self) -> None:
         """Drop the captured step (the next :meth:`step_graph` captures again)."""
@@ -189,7 +214,7 @@ class CoDAStack(nn.Module):
             # Ring scalars are baked at capture time and advanced by the graph's own device counter, so a write that
             # did not go through a replay (an eager step or prefill on one of the layers, a restored state) makes
             # the graph stale; so does any rebuilt weight copy or constant.  Either way: capture again.
-            if (len(G["states"]) != len(states) or any(a is not b for a, b in zip(G["states"], states))
+            if (len(G["states"]) != len(states) or any(map(operator.is_not, G["states"], states))
                     or G["expect"] != [(st.pos, st.recent_idx, st.recent_filled) for st in states]
                     or G["key"] != self._graph_key(states, x.dtype)
                     or x.shape != G["x"].shape or x.dtype != G["x"].dtype):

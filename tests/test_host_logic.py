@@ -187,3 +187,37 @@ def test_state_wire_format_round_trip_and_validation():
             state_from_bytes(blob[:-1], "cpu")
         with pytest.raises(ValueError):
             state_from_bytes(blob[:8] + (99).to_bytes(4, "little") + blob[12:], "cpu")
+
+
+def test_captured_step_key_sees_every_way_a_parameter_can_change():
+    """The key a captured decode step is checked against before every replay is read through a flat tuple of the
+    Parameter objects; it must still change on an in-place write, on a replaced Parameter object (directly on the
+    layer and inside a sub-module), on a flipped switch, on a dtype conversion and on other states."""
+    from types import SimpleNamespace
+    from coda_gqa_l_b200.stack import CoDAStack
+    kw = dict(embed_dim=64, num_heads=4, num_kv_heads=2, window=8, num_landmarks_exact=4, num_landmarks_summary=4)
+    layers = [CoDAGQALandmarkPerf2(**kw) for _ in range(3)]
+    stack = CoDAStack(layers)
+    states = [SimpleNamespace(active_exact=4, active_summary=4) for _ in layers]
+    key = lambda: stack._graph_key(states, torch.bfloat16)
+    k = key()
+    assert key() == k
+    with torch.no_grad():
+        layers[1].q_proj.weight.mul_(1.0)
+    assert key() != k; k = key()
+    with torch.no_grad():
+        layers[2].summary_eta_logit.add_(0.0)
+    assert key() != k; k = key()
+    layers[0].theta = torch.nn.Parameter(layers[0].theta.detach().clone())
+    assert key() != k; k = key()
+    layers[2].o_proj.weight = torch.nn.Parameter(layers[2].o_proj.weight.detach().clone())
+    assert key() != k; k = key()
+    layers[1].use_skinny_in_proj = not layers[1].use_skinny_in_proj
+    assert key() != k; k = key()
+    stack.to(torch.float64)
+    assert key() != k; k = key()
+    states[1].active_exact = 2
+    assert key() != k; k = key()
+    assert stack._graph_key(list(states[:2]) + [SimpleNamespace(active_exact=4, active_summary=4)], torch.bfloat16) != k
+    assert stack._graph_key(states, torch.float32) != k
+    assert key() == k
