@@ -1151,9 +1151,33 @@ class CoDAGQALandmarkPerf2(nn.Module):
         """Blockwise prefill (upstream attention.py:567-728): block j attends over
         [state after block j-1 | block j, causal], then the block is pushed through the ring and the
         tokens it evicts are routed into the banks."""
-        B, L, _ = x_seq.shape
-        if L == 0:
+        if x_seq.shape[1] == 0:
             return (x_seq[:, :0, :].clone() if return_outputs else None), state
+        y_heads = self._prefill_heads(x_seq, state, block_size, write_cache, return_outputs)
+        if not return_outputs:
+            return None, state
+        return self.o_proj(y_heads), state
+
+    @torch.no_grad()
+    def prefill_chunked_residual(self, h: torch.Tensor, state: CoDAGQALandmarkStatePerf2, *, block_size: int = 256,
+                                 inplace: bool = False) -> torch.Tensor:
+        """``h + layer(h)`` over a chunk, the sum taken by the output projection itself (fp32 accumulator plus
+        residual, one rounding) instead of by an add behind it.  ``inplace=True`` accumulates into ``h``'s own
+        memory (a GEMM with beta = 1: no copy of the residual, no extra pass over the chunk) and returns ``h``."""
+        B, L, D = h.shape
+        if L == 0:
+            return h
+        y_heads = self._prefill_heads(h, state, block_size, True, True)
+        if (inplace and h.is_contiguous() and type(self.o_proj) is nn.Linear and self.o_proj.bias is None
+                and self.o_proj.weight.dtype == h.dtype):
+            h.view(B * L, D).addmm_(y_heads.view(B * L, -1), self.o_proj.weight.t())
+            return h
+        return self._out(y_heads, h)
+
+    def _prefill_heads(self, x_seq: torch.Tensor, state: CoDAGQALandmarkStatePerf2, block_size: int,
+                       write_cache: bool, return_outputs: bool) -> Optional[torch.Tensor]:
+        """The blockwise prefill up to the output projection: (B, L, H*Dh) head outputs, or None."""
+        B, L, _ = x_seq.shape
         if block_size <= 0:
             raise ValueError("block_size must be positive")
         self._require_ready(x_seq, state)
@@ -1248,9 +1272,7 @@ class CoDAGQALandmarkPerf2(nn.Module):
                 state.recent_filled = min(W, fill + blk)
                 state.recent_idx = 0
                 state.pos = pos0 + t0 + blk
-        if not return_outputs:
-            return None, state
-        return self.o_proj(y_heads), state
+        return y_heads
 
     # ------------------------------------------------------------------ utility
     def cache_bytes(self, *, batch_size: int, dtype: torch.dtype) -> int:

@@ -63,9 +63,13 @@ class CoDAStack(nn.Module):
     def prefill(self, x: torch.Tensor, states, *, block_size: int = 256, return_outputs: bool = True):
         """Layer by layer over the whole chunk ``x`` (B, L, D)."""
         h = x
-        for layer, st in zip(self.layers, states):
-            y, _ = layer.prefill_chunked(h, st, block_size=block_size)
-            h = h + y if self.residual else y
+        for i, (layer, st) in enumerate(zip(self.layers, states)):
+            if self.residual:
+                # the residual rides in the output projection; from the second layer on into h's own memory
+                # (the first layer's h is the caller's tensor)
+                h = layer.prefill_chunked_residual(h, st, block_size=block_size, inplace=i > 0)
+            else:
+                h, _ = layer.prefill_chunked(h, st, block_size=block_size)
         self._graph = None                       # scalars baked into a captured step are stale now
         return h if return_outputs else None
 

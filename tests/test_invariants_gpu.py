@@ -305,3 +305,38 @@ def test_block_routing_beside_attention_equals_routing_after_it():
     a, b = states
     assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
     assert torch.equal(a._arena, b._arena)
+
+
+def test_stack_prefill_with_the_residual_in_the_output_projection():
+    """`CoDAStack.prefill` lets the output projection take the residual (one rounding of accumulator + residual;
+    from the second layer on into the chain's own buffer).  Against the chain written out with a separate add:
+    the caller's chunk is left untouched, the first layer's state is identical (its input is the same tensor),
+    the outputs agree to bf16 rounding, and in fp32 the two chains are equal to accumulation order."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack
+    kw = dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=8, num_landmarks_summary=8)
+    for dtype, tol in ((torch.bfloat16, 3e-2), (torch.float32, 2e-5)):
+        layers = []
+        for i in range(3):
+            torch.manual_seed(i)
+            layers.append(CoDAGQALandmarkPerf2(**kw).eval().to(dtype).cuda())
+        stack = CoDAStack(layers)
+        torch.manual_seed(9)
+        x = (torch.randn(2, 70, 256, device="cuda") * 0.5).to(dtype)
+        x_before = x.clone()
+        torch.manual_seed(10)                            # the banks start from N(0, 0.02^2) draws: same draws for both
+        sa = stack.init_states(batch_size=2, device="cuda", dtype=dtype)
+        torch.manual_seed(10)
+        sb = stack.init_states(batch_size=2, device="cuda", dtype=dtype)
+        ya = stack.prefill(x, sa, block_size=16)
+        assert torch.equal(x, x_before)
+        h = x
+        for layer, st in zip(layers, sb):
+            y, _ = layer.prefill_chunked(h, st, block_size=16)
+            h = h + y
+        for name in ("k_buf", "v_buf", "allowed", "g_recent", "mem_last_exact"):
+            assert torch.equal(getattr(sa[0], name), getattr(sb[0], name)), name
+        assert ya.shape == h.shape and ya.data_ptr() != x.data_ptr()
+        err = (ya.float() - h.float()).abs().max().item() / h.float().abs().max().item()
+        assert err < tol, (dtype, err)
+        for a, b in zip(sa, sb):
+            assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
