@@ -112,6 +112,21 @@ template <> struct Vec16<bf16> {
   }
 };
 
+// Packed bf16 arithmetic: one instruction for two elements, each result the correctly rounded bf16 of the exact
+// product / sum -- the same value as the fp32 operation followed by a rounding to bf16 that the scalar code spells
+// out (a product of two bf16 is exact in fp32; a sum of two bf16 is exact in fp32 unless their exponents are more
+// than 16 apart, and then it is more than a bf16 rounding step away from any tie).
+__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) { uint32_t d; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) { uint32_t d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
+__device__ __forceinline__ uint32_t bneg2(uint32_t a) { return a ^ 0x80008000u; }
+__device__ __forceinline__ uint32_t bdup_lo(uint32_t a) { return __byte_perm(a, a, 0x1010); }     // (x, y) -> (x, x)
+__device__ __forceinline__ uint32_t bdup_hi(uint32_t a) { return __byte_perm(a, a, 0x3232); }     // (x, y) -> (y, y)
+// (x, y) -> (-y, x): the second addend of a plane rotation (a, b) -> (a c - b s, b c + a s) written as
+// (a, b) * (c, c) + (-(b s), a s)
+__device__ __forceinline__ uint32_t bswap_neg(uint32_t a) { return __byte_perm(a, a, 0x1032) ^ 0x00008000u; }
+// rotation of the pair held in one word by the angle (c, s) given as duplicated words
+__device__ __forceinline__ uint32_t brot(uint32_t xy, uint32_t cc, uint32_t ss) { return badd2(bmul2(xy, cc), bswap_neg(bmul2(xy, ss))); }
+
 // Vectorised variant.  Work item = one 16-byte chunk of a head row (interleaved pairs) or the two chunks c and
 // c + Dh/2 that hold each other's RoPE partners (half-split pairs).  The noise query always rotates (even, odd)
 // neighbours of the ROTATED row (primitives.py:58-80), which lie inside one chunk, so an item is self-contained.
@@ -122,6 +137,9 @@ __global__ void __launch_bounds__(320) prep_vec_kernel(PrepParams p) {
   const int half = p.Dh >> 1;
   float* cs = sm;                 // [half] cos, rounded to T
   float* sn = sm + half;          // [half] sin
+  bf16* csb = reinterpret_cast<bf16*>(sm + 2 * half);   // bf16 activations: the same tables as bf16, [half] cos | [half] sin
+  bf16* snb = csb + half;
+  constexpr bool PACKED = sizeof(T) == 2;
   const int tid = threadIdx.x, NT = blockDim.x;
   const long long ntok = (long long)p.B * p.L;
   const long long pos_base = ring_now(p.rp, p.W).pos;
@@ -137,6 +155,7 @@ __global__ void __launch_bounds__(320) prep_vec_kernel(PrepParams p) {
       float ang = El<A>::rnd(__fmul_rn(ta, inv));
       cs[i] = El<T>::rnd(El<A>::rnd(cosf(ang)));
       sn[i] = El<T>::rnd(El<A>::rnd(sinf(ang)));
+      if (PACKED) { csb[i] = __float2bfloat16_rn(cs[i]); snb[i] = __float2bfloat16_rn(sn[i]); }
     }
     __syncthreads();
     T* qt = (T*)p.q + (long long)b * p.q_bs + (long long)t * p.q_rs;
@@ -149,7 +168,45 @@ __global__ void __launch_bounds__(320) prep_vec_kernel(PrepParams p) {
       T* row = (isq ? qt : kt) + h * p.Dh;
       const T* cth = (const T*)p.cos_t + h * half;
       const T* sth = (const T*)p.sin_t + h * half;
-      if (p.interleaved) {                  // primitives.py:99-106: pairs (2i, 2i+1) share cos/sin i
+      if (PACKED) {
+        // eight elements per 16-byte vector, four words of two; the tables' entries come four at a time (8 bytes)
+        if (p.interleaved) {                // word j = pair i = 4c + j, rotated by the position's angle i
+          uint4 xv = *reinterpret_cast<const uint4*>(row + c * N);
+          const uint2 cw = *reinterpret_cast<const uint2*>(csb + 4 * c), sw = *reinterpret_cast<const uint2*>(snb + 4 * c);
+          uint4 ov;
+          ov.x = brot(xv.x, bdup_lo(cw.x), bdup_lo(sw.x)); ov.y = brot(xv.y, bdup_hi(cw.x), bdup_hi(sw.x));
+          ov.z = brot(xv.z, bdup_lo(cw.y), bdup_lo(sw.y)); ov.w = brot(xv.w, bdup_hi(cw.y), bdup_hi(sw.y));
+          *reinterpret_cast<uint4*>(row + c * N) = ov;
+          if (isq) {
+            const uint2 ct = *reinterpret_cast<const uint2*>(cth + 4 * c), st = *reinterpret_cast<const uint2*>(sth + 4 * c);
+            uint4 nv;
+            nv.x = brot(ov.x, bdup_lo(ct.x), bdup_lo(st.x)); nv.y = brot(ov.y, bdup_hi(ct.x), bdup_hi(st.x));
+            nv.z = brot(ov.z, bdup_lo(ct.y), bdup_lo(st.y)); nv.w = brot(ov.w, bdup_hi(ct.y), bdup_hi(st.y));
+            *reinterpret_cast<uint4*>(qnt + h * p.Dh + c * N) = nv;
+          }
+        } else {                            // x1 = elements 8c.., x2 = their partners half + 8c..; angles 8c..8c+7
+          const uint4 x1 = *reinterpret_cast<const uint4*>(row + c * N), x2 = *reinterpret_cast<const uint4*>(row + half + c * N);
+          const uint4 cv = *reinterpret_cast<const uint4*>(csb + c * N), sv = *reinterpret_cast<const uint4*>(snb + c * N);
+          uint4 oa, ob;                       // x1 c + (-x2) s ; x2 c + x1 s
+          oa.x = badd2(bmul2(x1.x, cv.x), bmul2(bneg2(x2.x), sv.x)); ob.x = badd2(bmul2(x2.x, cv.x), bmul2(x1.x, sv.x));
+          oa.y = badd2(bmul2(x1.y, cv.y), bmul2(bneg2(x2.y), sv.y)); ob.y = badd2(bmul2(x2.y, cv.y), bmul2(x1.y, sv.y));
+          oa.z = badd2(bmul2(x1.z, cv.z), bmul2(bneg2(x2.z), sv.z)); ob.z = badd2(bmul2(x2.z, cv.z), bmul2(x1.z, sv.z));
+          oa.w = badd2(bmul2(x1.w, cv.w), bmul2(bneg2(x2.w), sv.w)); ob.w = badd2(bmul2(x2.w, cv.w), bmul2(x1.w, sv.w));
+          *reinterpret_cast<uint4*>(row + c * N) = oa;
+          *reinterpret_cast<uint4*>(row + half + c * N) = ob;
+          if (isq) {                        // (even, odd) neighbours of the rotated row: pairs 4c.. and half/2 + 4c..
+            const uint2 cta = *reinterpret_cast<const uint2*>(cth + 4 * c), sta = *reinterpret_cast<const uint2*>(sth + 4 * c);
+            const uint2 ctb = *reinterpret_cast<const uint2*>(cth + (half >> 1) + 4 * c), stb = *reinterpret_cast<const uint2*>(sth + (half >> 1) + 4 * c);
+            uint4 na, nb;
+            na.x = brot(oa.x, bdup_lo(cta.x), bdup_lo(sta.x)); na.y = brot(oa.y, bdup_hi(cta.x), bdup_hi(sta.x));
+            na.z = brot(oa.z, bdup_lo(cta.y), bdup_lo(sta.y)); na.w = brot(oa.w, bdup_hi(cta.y), bdup_hi(sta.y));
+            nb.x = brot(ob.x, bdup_lo(ctb.x), bdup_lo(stb.x)); nb.y = brot(ob.y, bdup_hi(ctb.x), bdup_hi(stb.x));
+            nb.z = brot(ob.z, bdup_lo(ctb.y), bdup_lo(stb.y)); nb.w = brot(ob.w, bdup_hi(ctb.y), bdup_hi(stb.y));
+            *reinterpret_cast<uint4*>(qnt + h * p.Dh + c * N) = na;
+            *reinterpret_cast<uint4*>(qnt + h * p.Dh + half + c * N) = nb;
+          }
+        }
+      } else if (p.interleaved) {                  // primitives.py:99-106: pairs (2i, 2i+1) share cos/sin i
         float x[N], o[N];
         Vec16<T>::ld(row + c * N, x);
 #pragma unroll
@@ -242,7 +299,7 @@ extern "C" int coda_b200_prep(const coda_layer_cfg* cfg, int32_t L, coda_ring_po
   const bool vec = ((cfg->rope_interleaved ? cfg->Dh : cfg->Dh / 2) % vn) == 0 && ((uintptr_t)q | (uintptr_t)q_noise) % 16 == 0 &&
                    (q_bs | q_rs) % vn == 0 && (k == nullptr || ((uintptr_t)k % 16 == 0 && (k_bs | k_rs) % vn == 0));
 #define LAUNCH(T, A) do { \
-    if (vec) { prep_vec_kernel<T, A><<<grid, 320, sizeof(float) * (size_t)cfg->Dh, s>>>(p); break; } \
+    if (vec) { prep_vec_kernel<T, A><<<grid, 320, sizeof(float) * (size_t)cfg->Dh + 2 * sizeof(bf16) * (size_t)(cfg->Dh / 2), s>>>(p); break; } \
     if (smem > 48 * 1024) cudaFuncSetAttribute(prep_kernel<T, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     prep_kernel<T, A><<<grid, 256, smem, s>>>(p); } while (0)
   if (cfg->dtype == CODA_F32) {

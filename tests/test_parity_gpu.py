@@ -749,10 +749,14 @@ def test_decode_step_on_own_gemms_matches_library_gemms():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("interleaved", [True, False])
 @pytest.mark.parametrize("Dh,H,Hkv", [(128, 8, 2), (64, 9, 3), (32, 4, 2)])
-def test_vectorised_projection_postprocessing_equals_elementwise_kernel(dtype, interleaved, Dh, H, Hkv):
+@pytest.mark.parametrize("spread", [False, True])
+def test_vectorised_projection_postprocessing_equals_elementwise_kernel(dtype, interleaved, Dh, H, Hkv, spread):
     """RoPE of q and k, the theta-rotated noise query and the two sigmoids: the 16-byte-vector kernel (aligned rows)
     and the element-wise kernel (here forced by rows that start 2 or 4 bytes off a 16-byte boundary) do the same
-    arithmetic, so their results are bit-equal."""
+    arithmetic, so their results are bit-equal -- in bf16 the vector kernel computes on packed pairs with native
+    bf16 instructions, the element-wise one in fp32 with a rounding after every operation.  ``spread`` scales every
+    input element by its own power of two (2^-120 .. 2^30), so that partners of a rotation lie many binades apart and
+    results fall into the subnormal range."""
     from coda_gqa_l_b200 import CoDAGQALandmarkPerf2
     from tests.scenarios import randomize_weights
     torch.manual_seed(1)
@@ -770,7 +774,11 @@ def test_vectorised_projection_postprocessing_equals_elementwise_kernel(dtype, i
     outs = []
     for shift in (0, 1):                                         # shift 1: every row starts one element off alignment
         y = torch.zeros(B, L, width + 8, device="cuda", dtype=dtype)
-        src = torch.randn(B, L, nq + nk + H + 1, device="cuda", generator=torch.Generator(device="cuda").manual_seed(4)).to(dtype)
+        src = torch.randn(B, L, nq + nk + H + 1, device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
+        if spread:
+            e = torch.randint(-120, 31, src.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+            src = torch.ldexp(src, e)
+        src = src.to(dtype)
         y[..., shift:shift + nq + nk + H + 1] = src
         q, k = y[..., shift:shift + nq], y[..., shift + nq:shift + nq + nk]
         lam_logit, gate_logit = y[..., shift + nq + nk:shift + nq + nk + H], y[..., shift + nq + nk + H:shift + nq + nk + H + 1]
