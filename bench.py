@@ -368,16 +368,17 @@ def main():
     states = stack.init_states(batch_size=B, device=dev, dtype=dtype)
     P = max(args.prefill_tokens, w["W"] + w["block"])
     P = (P + w["block"] - 1) // w["block"] * w["block"]
-    x_pre = mixture(B, 3 * P, D, w["K"], w["sigma"], 11 + rank, dev, dtype)
+    # three chunks of one token stream, each a tensor of its own (a chunk arrives as a contiguous batch)
+    x_pre = [c.contiguous() for c in mixture(B, 3 * P, D, w["K"], w["sigma"], 11 + rank, dev, dtype).split(P, dim=1)]
     x_dec = mixture(B, 2 * (K + Wm) + 8, D, w["K"], w["sigma"], 13 + rank, dev, dtype)
     x_dec_host = x_dec.cpu().pin_memory()
 
     # ---- prefill (brings every ring to steady state); timed as a secondary figure ----
-    stack.prefill(x_pre[:, :P], states, block_size=w["block"])                  # warm-up chunk: fills every ring
+    stack.prefill(x_pre[0], states, block_size=w["block"])                      # warm-up chunk: fills every ring
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    stack.prefill(x_pre[:, P:2 * P], states, block_size=w["block"])             # timed chunk: same shapes, steady state
+    stack.prefill(x_pre[1], states, block_size=w["block"])                      # timed chunk: same shapes, steady state
     e1.record()
     barrier()
     prefill_ms = max_over_ranks(e0.elapsed_time(e1), dev)
@@ -385,7 +386,7 @@ def main():
     # the attention kernel by itself: a third chunk with events around every attention launch
     for l in stack.layers:
         l.kernel_timers = []
-    stack.prefill(x_pre[:, 2 * P:], states, block_size=w["block"])
+    stack.prefill(x_pre[2], states, block_size=w["block"])
     barrier()
     att_ms = [a.elapsed_time(b) for l in stack.layers for (_, a, b) in l.kernel_timers]
     pre_kernel_ms = sum(att_ms) / max(1, len(att_ms))
