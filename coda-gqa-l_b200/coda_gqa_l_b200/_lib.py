@@ -81,6 +81,8 @@ def _load() -> C.CDLL:
     lib.coda_b200_skinny_gemm_bias.argtypes = [vp, i32, i32, vp, i32, vp, vp, i64, vp, i64, vp, vp]
     lib.coda_b200_skinny_gemm_bias_supported.argtypes = [i32, i32, i32]
     lib.coda_b200_skinny_gemm_plan.argtypes = [i32, i32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.coda_b200_skinny_gemm_chain_supported.argtypes = [i32, i32, i32, i32]
+    lib.coda_b200_skinny_gemm_chain.argtypes = [vp, i32, i32, vp, i32, vp, i64, vp, vp, i32, vp, vp, i64, vp, vp, vp]
     lib.coda_b200_step_append_fused.argtypes = [cfgp, stp, RingPos, vp, i64, vp, i64, vp, i64, fp,
                                                 vp, i64, vp, i64, vp, vp, vp, vp]
     lib.coda_b200_prefill_attend_supported.argtypes = [cfgp]
@@ -116,7 +118,7 @@ EXPORTS = (
     "coda_b200_step_write_raw", "coda_b200_step_write_fused", "coda_b200_step_write_fused_supported", "coda_b200_step_write_attend",
     "coda_b200_step_route", "coda_b200_step_append_fused", "coda_b200_step_route_plan_bytes",
     "coda_b200_step_route_plan", "coda_b200_step_route_batched",
-    "coda_b200_skinny_gemm_supported", "coda_b200_skinny_gemm", "coda_b200_skinny_gemm_bias", "coda_b200_skinny_gemm_bias_supported", "coda_b200_skinny_gemm_plan", "coda_b200_proj_gemm_supported", "coda_b200_proj_gemm", "coda_b200_proj_gemm_workspace_bytes",
+    "coda_b200_skinny_gemm_supported", "coda_b200_skinny_gemm", "coda_b200_skinny_gemm_bias", "coda_b200_skinny_gemm_bias_supported", "coda_b200_skinny_gemm_plan", "coda_b200_skinny_gemm_chain_supported", "coda_b200_skinny_gemm_chain", "coda_b200_proj_gemm_supported", "coda_b200_proj_gemm", "coda_b200_proj_gemm_workspace_bytes",
     "coda_b200_decode_attend_append_supported", "coda_b200_decode_attend_append", "coda_b200_rope_table",
     "coda_b200_decode_attend_supported", "coda_b200_decode_attend", "coda_b200_decode_attend_prepared",
     "coda_b200_decode_record_bytes", "coda_b200_decode_set_early_trigger",

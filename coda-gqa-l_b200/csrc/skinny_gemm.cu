@@ -401,6 +401,205 @@ struct Skinny4 {
   }
 };
 
+// ---- two dependent products behind one launch -------------------------------------------------------------------
+// A decode step's output projection (with the residual) is followed by the next layer's input projection, whose X is
+// the first product's Y.  As two launches the second pays its own ramp: launch, barrier set-up, first boxes.  Here
+// the same CTAs run both products (phase A, then phase B) with a barrier across the whole grid in between:
+//   * the grid is one wave (the launcher sizes the tiles so that all clusters are resident at once), so every CTA
+//     reaches the barrier; the wait is bounded all the same and reports through the status word;
+//   * phase B's first ring pass of WEIGHT boxes goes out before the barrier -- the weights depend on nothing --
+//     and streams while the slower CTAs finish phase A;
+//   * phase A's outputs are written with generic stores, fenced, and read in phase B by TMA behind a proxy fence.
+// `gsync`: two words of device memory, zero before the first launch: arrival count and generation.  Launches that
+// share them must be ordered on one stream.
+__device__ __forceinline__ void sg_grid_barrier(unsigned int* gsync, unsigned int nctas, int* status) {
+  unsigned int gen, now;
+  asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(gen) : "l"(gsync + 1) : "memory");
+  __threadfence();
+  const unsigned int old = atomicAdd(gsync, 1u);
+  if (old == nctas - 1) {
+    gsync[0] = 0u;
+    __threadfence();
+    atomicAdd(gsync + 1, 1u);
+    return;
+  }
+  for (int it = 0; it < (1 << 22); ++it) {
+    asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(now) : "l"(gsync + 1) : "memory");
+    if (now != gen) return;
+    __nanosleep(32);
+  }
+  if (status) atomicCAS(status, 0, 27);                                // gave up: the results of phase B are not valid
+}
+
+template <int CW, int STAGES>
+__global__ void __launch_bounds__((CW + 1) * 32, 1)
+skinny_gemm4_chain_kernel(const __grid_constant__ CUtensorMap xmapA, const __grid_constant__ CUtensorMap wmapA, SkinnyParams pA, int bnA,
+                          const __grid_constant__ CUtensorMap xmapB, const __grid_constant__ CUtensorMap wmapB, SkinnyParams pB, int bnB,
+                          unsigned int* gsync, int kq_max) {
+  constexpr int SLOT = Skinny4Smem<CW, STAGES>::SLOT;
+  constexpr int NBAR = 2 * STAGES + SG_MAXXG;                          // barriers of one phase
+  extern __shared__ unsigned char sg_raw[];
+  unsigned char* smem = sg_raw + ((1024u - (smem_u32(sg_raw) & 1023u)) & 1023u);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rank = blockIdx.x;                           // cluster rank (cluster dims (4,1,1))
+  const Skinny4Smem<CW, STAGES> L(kq_max);
+  unsigned char* xs = smem + L.x;
+  unsigned char* ring = smem + L.ring;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);         // [2 phases][NBAR]
+
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ int s_abort;
+  int* const abortw = &s_abort;
+  if (tid == 0) {
+    s_abort = 0;
+    for (int ph = 0; ph < 2; ++ph) {
+      uint64_t* b = bars + ph * NBAR;
+      const int ngrp = (ph ? bnB : bnA) / 16;
+      for (int i = 0; i < STAGES; ++i) { tma::mbar_init(&b[i], 1); tma::mbar_init(&b[STAGES + i], ngrp); }
+      for (int i = 0; i < SG_MAXXG; ++i) tma::mbar_init(&b[2 * STAGES + i], 1);
+    }
+    tma::fence_barrier_init();
+  }
+  __syncthreads();
+  const int li = lane >> 3, lr = lane & 7;
+  const unsigned int nctas = gridDim.x * gridDim.y;
+
+#pragma unroll 1
+  for (int ph = 0; ph < 2; ++ph) {
+    const CUtensorMap* xmap = ph ? &xmapB : &xmapA;
+    const CUtensorMap* wmap = ph ? &wmapB : &wmapA;
+    const SkinnyParams& p = ph ? pB : pA;
+    const int bn = ph ? bnB : bnA;
+    const int n0 = blockIdx.y * bn;
+    const bool active = n0 < p.N;                        // (a phase with fewer tiles leaves the last clusters idle)
+    const int kq = p.K / S4_CL, kbase = rank * kq, nbox = kq / SG_BK;
+    const int ngrp = bn / 16;                            // 16-row groups of the tile = working consumer warps
+    uint64_t* full = bars + ph * NBAR;
+    uint64_t* empty = full + STAGES;
+    uint64_t* xbar = empty + STAGES;
+    const uint32_t wbox_bytes = (uint32_t)bn * 128;
+    float acc[4][4];
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+
+    if (ph == 1) {
+      // everything this CTA wrote in phase A is out and fenced, and its exchange space (the ring) has been read
+      __threadfence();
+      __syncthreads();
+    }
+    if (warp == CW) {
+      if (lane == 0) {
+        // The weights depend on nothing that runs before: the first pass of the ring is requested BEFORE waiting
+        // (phase A: for the kernel that produces X; phase B: for the other CTAs' phase A).
+        const int pre = active ? min(nbox, STAGES) : 0;
+        for (int i = 0; i < pre; ++i) {
+          tma::mbar_expect_tx(&full[i], wbox_bytes);
+          sg_tma_load(ring + i * SLOT, wmap, &full[i], kbase + i * SG_BK, n0);
+        }
+        if (ph == 0) {
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+        } else {
+          sg_grid_barrier(gsync, nctas, p.status);
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int i = 0; active && i < nbox; ++i) {
+          if (i % SG_XGROUP == 0) {
+            const int g = i / SG_XGROUP, nb = min(SG_XGROUP, nbox - i);
+            tma::mbar_expect_tx(&xbar[g], (uint32_t)nb * SG_XBOX);
+            for (int j = 0; j < nb; ++j) sg_tma_load(xs + (i + j) * SG_XBOX, xmap, &xbar[g], kbase + (i + j) * SG_BK, 0);
+          }
+          if (i < pre) continue;
+          const int s = i % STAGES, round = i / STAGES;
+          if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, p.status, 24, abortw);
+          tma::mbar_expect_tx(&full[s], wbox_bytes);
+          sg_tma_load(ring + s * SLOT, wmap, &full[s], kbase + i * SG_BK, n0);
+        }
+      }
+      __syncwarp();
+    } else if (active && warp < ngrp) {
+      const uint32_t xs_u = smem_u32(xs), ring_u = smem_u32(ring);
+      const int wrow = warp * 16 + (li & 1) * 8 + lr;
+      for (int i = 0; i < nbox; ++i) {
+        if (i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 25, abortw);
+        const int s = i % STAGES, round = i / STAGES;
+        tma::mbar_wait(&full[s], round & 1, p.status, 26, abortw);
+        const uint32_t wb = ring_u + s * SLOT, xb = xs_u + i * SG_XBOX;
+        uint32_t a[4][4];                                  // weight fragments of the box's four k-steps
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) sg_ldsm_x4(a[ks], wb + sg_off(wrow, ks * 2 + (li >> 1)));
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          uint32_t b0[4], b1[4];                           // X^T fragments: k 0-31 and k 32-63 of the box
+          sg_ldsm_x4(b0, xb + sg_off(mt * 8 + lr, li));
+          sg_ldsm_x4(b1, xb + sg_off(mt * 8 + lr, 4 + li));
+          sg_mma(acc[mt], a[0], b0[0], b0[1]);
+          sg_mma(acc[mt], a[1], b0[2], b0[3]);
+          sg_mma(acc[mt], a[2], b1[0], b1[1]);
+          sg_mma(acc[mt], a[3], b1[2], b1[3]);
+        }
+        __syncwarp();
+        if (lane == 0) tma::mbar_arrive(&empty[s]);
+      }
+    }
+
+    // ---- exchange: every CTA has consumed its ring (cluster barrier), whose space then takes the partial sums ----
+    if (ph == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");               // (residual and output belong to this kernel's place in the stream)
+      asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // (pairs with the arrive at entry: all CTAs run)
+    }
+    if (!active) continue;                                             // (the whole cluster: same tile index)
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    constexpr int GS = (CW + 3) / 4;                                   // group slots per owner
+    float* xch = reinterpret_cast<float*>(ring);
+    if (warp < ngrp) {
+      const int g = warp, owner = g & 3, gs = g >> 2;
+      const uint32_t base_local = smem_u32(xch + ((rank * GS + gs) * SG_MAXM) * 16);
+      uint32_t base_remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base_remote) : "r"(base_local), "r"(owner));
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        const int tok = mt * 8 + 2 * (lane & 3), nl = lane >> 2;       // C fragment: rows nl, nl + 8 of the group; tokens tok, tok + 1
+        const uint32_t a0 = base_remote + (uint32_t)((tok * 16 + nl) * 4);
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0), "f"(acc[mt][0]) : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 16 * 4), "f"(acc[mt][1]) : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 8 * 4), "f"(acc[mt][2]) : "memory");
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + (16 + 8) * 4), "f"(acc[mt][3]) : "memory");
+      }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp < CW) {
+      const int gs = tid >> 7, g = rank + 4 * gs;                      // group slot, group of the tile
+      const int m = (tid & 127) >> 2, nq = (tid & 3) * 4;              // token, first of 4 rows inside the group
+      const int n = n0 + g * 16 + nq;
+      if (gs < GS && g < ngrp && m < p.M && n < p.N) {
+        float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int src = 0; src < S4_CL; ++src) {
+          const float4 v = *reinterpret_cast<const float4*>(xch + ((src * GS + gs) * SG_MAXM + m) * 16 + nq);
+          t[0] += v.x; t[1] += v.y; t[2] += v.z; t[3] += v.w;
+        }
+        if (p.bias != nullptr) {                                       // fp32 sum + bias, one rounding (a linear layer's epilogue)
+          const uint2 bv = *reinterpret_cast<const uint2*>(p.bias + n);
+          t[0] += __uint_as_float(bv.x << 16); t[1] += __uint_as_float(bv.x & 0xffff0000u);
+          t[2] += __uint_as_float(bv.y << 16); t[3] += __uint_as_float(bv.y & 0xffff0000u);
+        }
+        if (p.res != nullptr) {
+          const uint2 rv = *reinterpret_cast<const uint2*>(p.res + (long long)m * p.res_rs + n);
+          // the product is rounded to bf16 first, as a GEMM followed by a separate add would
+          t[0] = bf16_round(t[0]) + __uint_as_float(rv.x << 16);
+          t[1] = bf16_round(t[1]) + __uint_as_float(rv.x & 0xffff0000u);
+          t[2] = bf16_round(t[2]) + __uint_as_float(rv.y << 16);
+          t[3] = bf16_round(t[3]) + __uint_as_float(rv.y & 0xffff0000u);
+        }
+        uint2 ov;
+        ov.x = bf16_pack(t[0], t[1]); ov.y = bf16_pack(t[2], t[3]);
+        *reinterpret_cast<uint2*>(p.y + (long long)m * p.y_rs + n) = ov;
+      }
+    }
+  }
+}
+
 // Tile height for the four-way kernel: the smallest multiple of 16 rows with which the clusters fit the device at
 // once; 0 when no instance covers it.  `cw` receives the instance (8 or 12 consumer warps).
 static int skinny4_plan(int K, int N, int* cw) {
@@ -474,6 +673,95 @@ extern "C" int coda_b200_skinny_gemm_bias(const void* x, int32_t M, int32_t K, c
   lc.attrs = at; lc.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&lc, skinny_gemm_kernel, xm, wm, p);
   if (e != cudaSuccess) { coda_set_error("skinny_gemm: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
+  return CODA_OK;
+}
+
+// ---- the chain: Y_A = X_A . W_A^T + R (phase A), Y_B = Y_A . W_B^T + bias (phase B), one launch ----------------------
+namespace {
+constexpr int CH_CW = 12, CH_STAGES = 6;
+constexpr int CH_NBAR = 2 * CH_STAGES + SG_MAXXG;
+size_t chain_smem(int kq_max) { return (size_t)Skinny4Smem<CH_CW, CH_STAGES>(kq_max).total + CH_NBAR * 8 + 1024; }
+// clusters of four CTAs of the chain kernel that are resident at once on the current device (0: unknown)
+int chain_max_clusters(int kq_max) {
+  static coda_device_once once;
+  static int mc[64][3];                                  // by kq_max / 512 - 1 (K = 2048, 4096 in use)
+  const int dev = coda_current_device();
+  coda_on_first_use(once, [dev] {
+    cudaFuncSetAttribute(skinny_gemm4_chain_kernel<CH_CW, CH_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    for (int k = 0; k < 3; ++k) {
+      const int kq = 512 * (k + 1) <= 1024 ? 512 * (k + 1) : 1024;
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(S4_CL, 64, 1); q.blockDim = dim3((CH_CW + 1) * 32, 1, 1); q.dynamicSmemBytes = chain_smem(kq);
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = S4_CL; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, skinny_gemm4_chain_kernel<CH_CW, CH_STAGES>, &q) != cudaSuccess) { n = 0; cudaGetLastError(); }
+      if (dev >= 0 && dev < 64) mc[dev][k] = n;
+    }
+  });
+  if (dev < 0 || dev >= 64) return 0;
+  return mc[dev][kq_max <= 512 ? 0 : 1];
+}
+// tile heights of the two phases such that the larger tile count still is one wave; false when a phase does not fit
+bool chain_plan(int KA, int NA, int NB, int* bnA, int* bnB, int* clusters) {
+  if (KA % 256 != 0 || NA % 256 != 0 || NA % 16 != 0 || NB % 16 != 0 || KA > 4096 || NA > 4096) return false;
+  const int kq_max = (KA > NA ? KA : NA) / 4;
+  if (kq_max / SG_BK > SG_XGROUP * SG_MAXXG) return false;
+  const int mc = chain_max_clusters(kq_max);
+  if (mc <= 0) return false;
+  int a = ((NA + mc - 1) / mc + 15) / 16 * 16, b = ((NB + mc - 1) / mc + 15) / 16 * 16;
+  if (a < 16) a = 16;
+  if (b < 16) b = 16;
+  if (a > 16 * CH_CW || b > 16 * CH_CW) return false;
+  const int ca = (NA + a - 1) / a, cb = (NB + b - 1) / b;
+  *bnA = a; *bnB = b; *clusters = ca > cb ? ca : cb;
+  return *clusters <= mc;
+}
+}  // namespace
+
+extern "C" int coda_b200_skinny_gemm_chain_supported(int32_t M, int32_t KA, int32_t NA, int32_t NB) {
+  if (!(M >= 1 && M <= SG_MAXM && tmaps::available())) return 0;
+  int a, b, c;
+  return chain_plan(KA, NA, NB, &a, &b, &c) ? 1 : 0;
+}
+
+extern "C" int coda_b200_skinny_gemm_chain(const void* xA, int32_t M, int32_t KA, const void* wA, int32_t NA,
+                                           const void* residualA, int64_t res_rs, void* yA,
+                                           const void* wB, int32_t NB, const void* biasB, void* yB, int64_t yB_rs,
+                                           uint32_t* gsync, int32_t* status, coda_stream_t stream) {
+  int bnA = 0, bnB = 0, clusters = 0;
+  CODA_REQUIRE(M >= 1 && M <= SG_MAXM && tmaps::available() && chain_plan(KA, NA, NB, &bnA, &bnB, &clusters), CODA_ERR_ARG,
+               "skinny_gemm_chain: %d x %d -> %d -> %d is not covered on this device", M, KA, NA, NB);
+  CODA_REQUIRE(xA && wA && yA && wB && yB && gsync, CODA_ERR_ARG, "skinny_gemm_chain: null pointer");
+  const uintptr_t al = (uintptr_t)xA | (uintptr_t)wA | (uintptr_t)yA | (uintptr_t)wB | (uintptr_t)yB | (uintptr_t)residualA | (uintptr_t)biasB;
+  CODA_REQUIRE(al % 16 == 0 && (uintptr_t)gsync % 8 == 0 && yB_rs % 8 == 0 && yB_rs >= NB && (!residualA || (res_rs % 8 == 0 && res_rs >= NA)),
+               CODA_ERR_ARG, "skinny_gemm_chain: misaligned pointer or stride");
+  CUtensorMap xmA, wmA, xmB, wmB;
+  const bool ok = tmaps::plane_map(&xmA, xA, 1, M, KA, SG_MAXM) && tmaps::plane_map(&wmA, wA, 1, NA, KA, bnA) &&
+                  tmaps::plane_map(&xmB, yA, 1, M, NA, SG_MAXM) && tmaps::plane_map(&wmB, wB, 1, NB, NA, bnB);
+  CODA_REQUIRE(ok, CODA_ERR_LAUNCH, "skinny_gemm_chain: cuTensorMapEncodeTiled failed");
+  SkinnyParams pA, pB;
+  pA.M = M; pA.N = NA; pA.K = KA; pA.res = (const bf16*)residualA; pA.res_rs = res_rs; pA.bias = nullptr;
+  pA.y = (bf16*)yA; pA.y_rs = NA; pA.status = status;
+  pB.M = M; pB.N = NB; pB.K = NA; pB.res = nullptr; pB.res_rs = 0; pB.bias = (const bf16*)biasB;
+  pB.y = (bf16*)yB; pB.y_rs = yB_rs; pB.status = status;
+  const int kq_max = (KA > NA ? KA : NA) / 4;
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(S4_CL, clusters, 1);
+  lc.blockDim = dim3((CH_CW + 1) * 32, 1, 1);
+  lc.dynamicSmemBytes = chain_smem(kq_max);
+  lc.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute at[2];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = S4_CL; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at; lc.numAttrs = 2;
+  cudaError_t e = cudaLaunchKernelEx(&lc, skinny_gemm4_chain_kernel<CH_CW, CH_STAGES>, xmA, wmA, pA, bnA, xmB, wmB, pB, bnB,
+                                     (unsigned int*)gsync, kq_max);
+  if (e != cudaSuccess) { coda_set_error("skinny_gemm_chain: %s", cudaGetErrorString(e)); return CODA_ERR_LAUNCH; }
   return CODA_OK;
 }
 

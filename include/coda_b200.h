@@ -244,6 +244,21 @@ int coda_b200_skinny_gemm_bias(const void* x, int32_t M, int32_t K, const void* 
                                const void* residual, int64_t res_rs, void* y, int64_t y_rs,
                                int32_t* status, coda_stream_t stream);
 
+/* A layer's output projection and the NEXT layer's fused input projection behind one launch:
+ *   y_a[M][Na] = x_a[M][Ka] . w_a[Na][Ka]^T (+ residual_a, as coda_b200_skinny_gemm adds it), then
+ *   y_b[M][Nb] = y_a . w_b[Nb][Na]^T + bias_b (as coda_b200_skinny_gemm_bias).
+ * (src/coda_gqa_l/attention.py:514 of one layer followed by :396-410,508 of the next in a decoder that chains layers
+ * as h <- h + layer(h).)  The same CTAs run both products with a barrier across the grid in between; the second
+ * product's first weight boxes stream while the slower CTAs finish the first.  y_a is written densely (row stride Na).
+ * gsync: two 32-bit words of device memory, zero before the first call and owned by the calls that share them, which
+ * must be ordered on one stream.  coda_b200_skinny_gemm_chain_supported: whether both products fit the device as one
+ * wave of clusters (needed for the barrier).  A barrier wait that runs out stores code 27 in the status word. */
+int coda_b200_skinny_gemm_chain_supported(int32_t M, int32_t Ka, int32_t Na, int32_t Nb);
+int coda_b200_skinny_gemm_chain(const void* x_a, int32_t M, int32_t Ka, const void* w_a, int32_t Na,
+                                const void* residual_a, int64_t res_rs, void* y_a,
+                                const void* w_b, int32_t Nb, const void* bias_b, void* y_b, int64_t y_b_rs,
+                                uint32_t* gsync, int32_t* status, coda_stream_t stream);
+
 /* The decode step's two projections on the tcgen05 tensor cores: y[M][N] = x[M][K] . w[N][K]^T (+ bias[N]) (+ residual[M][N]),
  * bf16 with fp32 accumulation, M <= 64 rows.  Replaces the nn.Linear calls of src/coda_gqa_l/attention.py:396-410,508 (the
  * q / k / v / lambda / write-gate projections, given here as ONE weight matrix whose rows are the five weights stacked,

@@ -527,6 +527,44 @@ def test_skinny_gemm_with_bias_matches_linear(M, K, N):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M,KA,NA,NB", [(32, 4096, 4096, 6208), (7, 1024, 1024, 1088), (32, 2048, 4096, 6208), (1, 256, 256, 64),
+                                        (32, 512, 4096, 1024)])
+def test_chained_projections_equal_the_two_separate_launches(M, KA, NA, NB):
+    """`coda_b200_skinny_gemm_chain` (a layer's output projection with the residual, a barrier across the grid, the
+    next layer's input projection with its bias, one launch) against the two launches it replaces: the same bits
+    in both outputs, over many launches that share the barrier words, and a clean status word."""
+    from coda_gqa_l_b200._lib import lib, check
+    if not (lib.coda_b200_skinny_gemm_chain_supported(M, KA, NA, NB) and lib.coda_b200_skinny_gemm_bias_supported(M, NA, NB)
+            and lib.coda_b200_skinny_gemm_supported(M, KA, NA)):
+        pytest.skip("not covered on this device")
+    g = torch.Generator(device="cuda").manual_seed(M + KA + NA + NB)
+    wa = (torch.randn(NA, KA, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    wb = (torch.randn(NB, NA, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(NB, device="cuda", generator=g).to(torch.bfloat16)
+    gsync = torch.zeros(2, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    for it in range(12):
+        x = (torch.randn(M, KA, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+        res = torch.randn(M, NA, device="cuda", generator=g).to(torch.bfloat16)
+        ya = torch.full((M, NA), float("nan"), device="cuda", dtype=torch.bfloat16)
+        yb = torch.full((M, NB), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ra, rb = torch.empty_like(ya), torch.empty_like(yb)
+        check(lib.coda_b200_skinny_gemm_chain(x.data_ptr(), M, KA, wa.data_ptr(), NA, res.data_ptr(), NA, ya.data_ptr(),
+                                              wb.data_ptr(), NB, bias.data_ptr(), yb.data_ptr(), NB,
+                                              gsync.data_ptr(), status.data_ptr(), s), "coda_b200_skinny_gemm_chain")
+        check(lib.coda_b200_skinny_gemm(x.data_ptr(), M, KA, wa.data_ptr(), NA, res.data_ptr(), NA, ra.data_ptr(), NA,
+                                        status.data_ptr(), s), "coda_b200_skinny_gemm")
+        check(lib.coda_b200_skinny_gemm_bias(ra.data_ptr(), M, NA, wb.data_ptr(), NB, bias.data_ptr(), None, 0, rb.data_ptr(), NB,
+                                             status.data_ptr(), s), "coda_b200_skinny_gemm_bias")
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, f"launch {it}"
+        assert torch.equal(ya, ra), f"launch {it}: first product"
+        assert torch.equal(yb, rb), f"launch {it}: second product"
+    assert gsync.tolist() == [0, 12]                       # every launch passed the barrier once and left the count at zero
+
+
+@pytest.mark.gpu
 def test_decode_step_with_own_output_gemm_matches_library_gemm():
     """`use_skinny_gemm_kernel` swaps the decode step's output projection (+ residual) for this library's kernel."""
     from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, _deep_copy_state
