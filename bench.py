@@ -558,11 +558,13 @@ def main():
         "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, w, world),
+        "chained_projections": bool(not args.eager and stack._graph is not None and stack._graph.get("chained")),
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": B * D * 2, "d2h_bytes_per_step": B * D * 2,
                 "ms_per_step": ms_e2e / K},
         # this repository's kernels inside the timed region: per layer the decode attention (which writes the new
         # token) and the output-projection GEMM, per step the batched routing, the cos/sin table and the step counter
-        # (the input projection is a library call)
+        # (the first layer's input projection is a library call; where the stack chains its projections, the other
+        # layers' input projections are the second phase of the launch that holds the output projection before them)
         "gpu_launches": K * per_step_launches,
         "clocks": clocks.summary(),
         "roofline": roofline,

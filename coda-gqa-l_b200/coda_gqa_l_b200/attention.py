@@ -717,16 +717,21 @@ class CoDAGQALandmarkPerf2(nn.Module):
                 y = torch.addmm(f[1], x.reshape(rows, -1), wt[1]).view(x.shape[0], x.shape[1], -1)
             else:
                 y = F.linear(x, f[0], f[1])
-            nq, nkv = H * Dh, Hkv * Dh
-            gate = y[..., nq + 2 * nkv + H:nq + 2 * nkv + H + 1] if self.write_policy != "none" else None
-            return (y[..., :nq], y[..., nq:nq + nkv], y[..., nq + nkv:nq + 2 * nkv],
-                    y[..., nq + 2 * nkv:nq + 2 * nkv + H], gate)
+            return self._split_fused(y)
         q = self.q_proj(x)
         k = self.k_proj(x) if need_kv else None
         v = self.v_proj(x) if need_kv else None
         lam = self.lambda_proj(x)
         gate = self.write_proj(x) if (need_kv and self.write_policy != "none") else None
         return q, k, v, lam, gate
+
+    def _split_fused(self, y: torch.Tensor):
+        """The five views (q, k, v, lambda logits, gate logits) of a fused projection output (B, L, [q|k|v|lambda|gate|pad])."""
+        H, Hkv, Dh = self.num_heads, self.num_kv_heads, self.head_dim
+        nq, nkv = H * Dh, Hkv * Dh
+        gate = y[..., nq + 2 * nkv + H:nq + 2 * nkv + H + 1] if self.write_policy != "none" else None
+        return (y[..., :nq], y[..., nq:nq + nkv], y[..., nq + nkv:nq + 2 * nkv],
+                y[..., nq + 2 * nkv:nq + 2 * nkv + H], gate)
 
     def _prep(self, cfg, L, pos, q, k, lam_logit, gate_logit, want_gate: bool, step_dev=None):
         B = q.shape[0]
@@ -1047,6 +1052,55 @@ class CoDAGQALandmarkPerf2(nn.Module):
         out = torch.empty((B, 1, self.num_heads * self.head_dim), device=x.device, dtype=x.dtype)
         self._attend(cfg, state, 1, q, qn, lam, None, None, out)
         return self._out(out, residual)
+
+    # -- a captured step whose layer boundary is one launch: output projection + next layer's input projection --
+    def chain_ready(self, B: int, dtype: torch.dtype, state: CoDAGQALandmarkStatePerf2,
+                    next_layer: Optional["CoDAGQALandmarkPerf2"]) -> bool:
+        """Can this layer's captured decode step take its projections from the previous layer's chained launch and
+        hand its own output projection, with ``next_layer``'s input projection, to one
+        ``coda_b200_skinny_gemm_chain`` launch?  (bf16, the attention kernel that writes the new token itself, a plain
+        bias-free output projection, a fused input weight on the next layer, shapes the kernel covers as one wave.)"""
+        if dtype != torch.bfloat16 or not (self.use_tuned_kernels and self.use_skinny_gemm_kernel and self.fuse_append_into_attention):
+            return False
+        if self._tracked(state) or type(self.o_proj) is not nn.Linear or self.o_proj.bias is not None:
+            return False
+        cfg = self._cfg(B, dtype, state)
+        if not (self._tuned_decode(cfg) and self._fused_write_ok(cfg) and lib.coda_b200_decode_attend_append_supported(C.byref(cfg))):
+            return False
+        if self._fused_weight() is None:
+            return False
+        if next_layer is None:
+            return True
+        f = next_layer._fused_weight()
+        w = self.o_proj.weight
+        if f is None or f[0].dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not (f[0].is_contiguous() and w.is_contiguous()):
+            return False
+        if f[0].shape[1] != w.shape[0] or (f[0].data_ptr() | f[1].data_ptr() | w.data_ptr()) % 16:
+            return False
+        return bool(lib.coda_b200_skinny_gemm_chain_supported(B, w.shape[1], w.shape[0], f[0].shape[0]))
+
+    def step_chained(self, h: torch.Tensor, state: CoDAGQALandmarkStatePerf2, rp: RingPos, *, rope_cs, proj_y,
+                     next_layer: Optional["CoDAGQALandmarkPerf2"], gsync: torch.Tensor):
+        """One layer of a captured decode step (the evicted token routed beforehand) between chained launches:
+        ``proj_y`` is this layer's fused projection output as the previous layer's launch left it (None: computed
+        here); the layer's output projection with the residual ``h`` and ``next_layer``'s fused input projection
+        leave in one launch.  Returns ``(h + layer(h), next layer's fused projection output or None)``."""
+        B = h.shape[0]
+        cfg = self._cfg(B, h.dtype, state)
+        proj = self._project(h, need_kv=True) if proj_y is None else self._split_fused(proj_y)
+        out = torch.empty((B, 1, self.num_heads * self.head_dim), device=h.device, dtype=h.dtype)
+        self.decode_attend_append_launch(cfg, state, rp, proj, out, rope_cs)
+        if next_layer is None:
+            return self._out(out, h), None
+        W_in, bias = next_layer._fused_weight()
+        w = self.o_proj.weight
+        D, N = w.shape[0], W_in.shape[0]
+        h_next = torch.empty((B, 1, D), device=h.device, dtype=h.dtype)
+        y_next = torch.empty((B, 1, N), device=h.device, dtype=h.dtype)
+        check(lib.coda_b200_skinny_gemm_chain(out.data_ptr(), B, w.shape[1], w.data_ptr(), D, h.data_ptr(), D, h_next.data_ptr(),
+                                              W_in.data_ptr(), N, bias.data_ptr(), y_next.data_ptr(), N, gsync.data_ptr(),
+                                              self._status_word(h.device).data_ptr(), _stream()), "coda_b200_skinny_gemm_chain")
+        return h_next, y_next
 
     def _nothing_visible(self, st) -> bool:
         # Only an empty ring can leave every slot masked; the check costs a sync, so it is made

@@ -55,6 +55,10 @@ class CoDAStack(nn.Module):
         # Captured decode step: route every layer's evicted token in one launch at the start of the step instead of
         # inside each layer's own chain (set before the first step_graph).
         self.split_routing = True
+        # Captured decode step: a layer's output projection and the next layer's input projection as ONE launch
+        # (coda_b200_skinny_gemm_chain) wherever every layer can (set before the first step_graph).  Off: two
+        # launches chained by programmatic dependent launch measure faster (1.21 against 1.32 ms per C4 step).
+        self.chain_projections = False
 
     def init_states(self, *, batch_size: int, device, dtype) -> List[CoDAGQALandmarkStatePerf2]:
         return [l.init_state(batch_size=batch_size, device=device, dtype=dtype) for l in self.layers]
@@ -112,6 +116,12 @@ class CoDAStack(nn.Module):
         rope_cs = None
         if plan is not None and self._shared_rope(states, x_static.dtype):      # (compares tensors: outside the capture)
             rope_cs = torch.empty(self.layers[0].head_dim, dtype=torch.float32, device=dev)
+        n_layers = len(self.layers)
+        chain = (self.chain_projections and self.residual and plan is not None and n_layers > 1
+                 and x_static.dim() == 3 and x_static.shape[1] == 1 and x_static.is_contiguous()
+                 and all(layer.chain_ready(x_static.shape[0], x_static.dtype, st, self.layers[i + 1] if i + 1 < n_layers else None)
+                         for i, (layer, st) in enumerate(zip(self.layers, states))))
+        gsync = torch.zeros(2, dtype=torch.int32, device=dev) if chain else None      # the chained launches' grid barrier
         def body(h):
             # Routing of the tokens this step evicts needs the states only: all layers' in one launch up front
             # (one layer's routing is a chain of memory round trips; side by side they are bandwidth-bound), so
@@ -126,9 +136,17 @@ class CoDAStack(nn.Module):
                 check(lib.coda_b200_rope_table(C.byref(plan[0]), rps[0], l0._consts(dev, x_static.dtype)[0].data_ptr(),
                                                rope_cs.data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
                       "coda_b200_rope_table")
-            for layer, st, rp in zip(self.layers, states, rps):
-                h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h if self.residual else None,
-                                         rope_cs=rope_cs)
+            if chain:
+                # per layer: attention (writes the new token) -> [output projection + residual | next layer's input
+                # projection] in one launch; the first layer's input projection is a launch of its own
+                proj_y = None
+                for i, (layer, st, rp) in enumerate(zip(self.layers, states, rps)):
+                    h, proj_y = layer.step_chained(h, st, rp, rope_cs=rope_cs, proj_y=proj_y,
+                                                   next_layer=self.layers[i + 1] if i + 1 < n_layers else None, gsync=gsync)
+            else:
+                for layer, st, rp in zip(self.layers, states, rps):
+                    h = layer.step_graphable(h, st, rp, routed=plan is not None, residual=h if self.residual else None,
+                                             rope_cs=rope_cs)
             check(lib.coda_b200_advance_steps(ctr.data_ptr(), 1, torch.cuda.current_stream(dev).cuda_stream),
                   "coda_b200_advance_steps")
             return h
@@ -149,7 +167,7 @@ class CoDAStack(nn.Module):
             out_pin.copy_(out_h, non_blocking=True)
         # Everything the graph's launches point at is kept alive with it (plan, table, the layers' derived weight and
         # constant tensors), and what they were is noted so that a replay after any of them changed re-captures.
-        self._graph = dict(graph=g, x=x_static, out=out_static, ctr=ctr, plan=plan, rope_cs=rope_cs,
+        self._graph = dict(graph=g, x=x_static, out=out_static, ctr=ctr, plan=plan, rope_cs=rope_cs, gsync=gsync, chained=chain,
                            host_graph=gh, x_pin=x_pin, out_pin=out_pin, out_host_dev=out_h,
                            states=list(states), key=self._graph_key(states, x_static.dtype),
                            expect=[(st.pos, st.recent_idx, st.recent_filled) for st in states],
@@ -166,7 +184,7 @@ class CoDAStack(nn.Module):
             weights = tuple(t for l in layers for t in (l.q_proj.weight, l.o_proj.weight))
             w = self._watch = (_REGISTRATION_EPOCH[0], layers,
                                weights + tuple(t for l in layers for t in (l.theta, l.summary_eta_logit)), weights)
-        return (self.split_routing, self.residual, dtype, w[0], tuple(map(_version_of, w[2])),
+        return (self.split_routing, self.chain_projections, self.residual, dtype, w[0], tuple(map(_version_of, w[2])),
                 tuple(map(torch.Tensor.data_ptr, w[3])), tuple(map(_switches_of, w[1])),
                 tuple(map(id, states)), tuple(map(_banks_of, states)))
 

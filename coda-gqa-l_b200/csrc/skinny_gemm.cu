@@ -423,29 +423,46 @@ __device__ __forceinline__ void sg_grid_barrier(unsigned int* gsync, unsigned in
     atomicAdd(gsync + 1, 1u);
     return;
   }
-  for (int it = 0; it < (1 << 22); ++it) {
+  for (int it = 0; it < (1 << 24); ++it) {
     asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(now) : "l"(gsync + 1) : "memory");
     if (now != gen) return;
-    __nanosleep(32);
   }
   if (status) atomicCAS(status, 0, 27);                                // gave up: the results of phase B are not valid
 }
+
+template <int CW, int STAGES>
+struct ChainSmem {
+  static constexpr int SLOT = CW * 16 * 128;
+  static constexpr int GS = (CW + 3) / 4;                // group slots per owner
+  static constexpr int NBAR = 2 * STAGES + 2 * SG_MAXXG; // full, empty, X arrivals of phase A and of phase B
+  int x, ring, xch, bars, total;
+  __host__ __device__ explicit ChainSmem(int kq_max) {
+    x = 0;
+    ring = x + (kq_max / SG_BK) * SG_XBOX;
+    xch = ring + STAGES * SLOT;                          // partial sums [src rank][group slot][token 32][row 16] fp32
+    bars = xch + S4_CL * GS * SG_MAXM * 16 * 4;
+    total = bars + NBAR * 8;
+  }
+};
 
 template <int CW, int STAGES>
 __global__ void __launch_bounds__((CW + 1) * 32, 1)
 skinny_gemm4_chain_kernel(const __grid_constant__ CUtensorMap xmapA, const __grid_constant__ CUtensorMap wmapA, SkinnyParams pA, int bnA,
                           const __grid_constant__ CUtensorMap xmapB, const __grid_constant__ CUtensorMap wmapB, SkinnyParams pB, int bnB,
                           unsigned int* gsync, int kq_max) {
-  constexpr int SLOT = Skinny4Smem<CW, STAGES>::SLOT;
-  constexpr int NBAR = 2 * STAGES + SG_MAXXG;                          // barriers of one phase
+  using SM = ChainSmem<CW, STAGES>;
+  constexpr int SLOT = SM::SLOT, GS = SM::GS;
   extern __shared__ unsigned char sg_raw[];
   unsigned char* smem = sg_raw + ((1024u - (smem_u32(sg_raw) & 1023u)) & 1023u);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rank = blockIdx.x;                           // cluster rank (cluster dims (4,1,1))
-  const Skinny4Smem<CW, STAGES> L(kq_max);
+  const SM L(kq_max);
   unsigned char* xs = smem + L.x;
   unsigned char* ring = smem + L.ring;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars);         // [2 phases][NBAR]
+  float* xch = reinterpret_cast<float*>(smem + L.xch);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
+  uint64_t* empty = full + STAGES;
+  uint64_t* xbars = empty + STAGES;                      // [2 phases][SG_MAXXG]
 
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -453,17 +470,28 @@ skinny_gemm4_chain_kernel(const __grid_constant__ CUtensorMap xmapA, const __gri
   int* const abortw = &s_abort;
   if (tid == 0) {
     s_abort = 0;
-    for (int ph = 0; ph < 2; ++ph) {
-      uint64_t* b = bars + ph * NBAR;
-      const int ngrp = (ph ? bnB : bnA) / 16;
-      for (int i = 0; i < STAGES; ++i) { tma::mbar_init(&b[i], 1); tma::mbar_init(&b[STAGES + i], ngrp); }
-      for (int i = 0; i < SG_MAXXG; ++i) tma::mbar_init(&b[2 * STAGES + i], 1);
-    }
+    // one ring for both phases: every consumer warp takes part in its hand-shake, also where a phase's tile leaves
+    // it without rows, so that the arrival count of a slot does not depend on the phase
+    for (int i = 0; i < STAGES; ++i) { tma::mbar_init(&full[i], 1); tma::mbar_init(&empty[i], CW); }
+    for (int i = 0; i < 2 * SG_MAXXG; ++i) tma::mbar_init(&xbars[i], 1);
     tma::fence_barrier_init();
   }
   __syncthreads();
   const int li = lane >> 3, lr = lane & 7;
   const unsigned int nctas = gridDim.x * gridDim.y;
+  const int n0A = blockIdx.y * bnA, n0B = blockIdx.y * bnB;
+  const bool activeA = n0A < pA.N, activeB = n0B < pB.N; // (a phase with fewer tiles leaves the last clusters idle)
+  const int nboxA = pA.K / S4_CL / SG_BK, nboxB = pB.K / S4_CL / SG_BK;
+  int gi = 0;                                            // boxes through the ring so far (producer and consumers count alike)
+
+  // producer: box i of a phase into the next ring slot, behind the consumers' release of that slot
+  auto issue_w = [&](const CUtensorMap* wmap, int kcoord, int n0, uint32_t bytes, int* status) {
+    const int s = gi % STAGES, round = gi / STAGES;
+    if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, status, 24, abortw);
+    tma::mbar_expect_tx(&full[s], bytes);
+    sg_tma_load(ring + s * SLOT, wmap, &full[s], kcoord, n0);
+    ++gi;
+  };
 
 #pragma unroll 1
   for (int ph = 0; ph < 2; ++ph) {
@@ -471,33 +499,24 @@ skinny_gemm4_chain_kernel(const __grid_constant__ CUtensorMap xmapA, const __gri
     const CUtensorMap* wmap = ph ? &wmapB : &wmapA;
     const SkinnyParams& p = ph ? pB : pA;
     const int bn = ph ? bnB : bnA;
-    const int n0 = blockIdx.y * bn;
-    const bool active = n0 < p.N;                        // (a phase with fewer tiles leaves the last clusters idle)
-    const int kq = p.K / S4_CL, kbase = rank * kq, nbox = kq / SG_BK;
-    const int ngrp = bn / 16;                            // 16-row groups of the tile = working consumer warps
-    uint64_t* full = bars + ph * NBAR;
-    uint64_t* empty = full + STAGES;
-    uint64_t* xbar = empty + STAGES;
+    const int n0 = ph ? n0B : n0A;
+    const bool active = ph ? activeB : activeA;
+    const int kq = p.K / S4_CL, kbase = rank * kq, nbox = ph ? nboxB : nboxA;
+    const int ngrp = bn / 16;                            // 16-row groups of the tile = consumer warps with rows
+    uint64_t* xbar = xbars + ph * SG_MAXXG;
     const uint32_t wbox_bytes = (uint32_t)bn * 128;
     float acc[4][4];
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
 
-    if (ph == 1) {
-      // everything this CTA wrote in phase A is out and fenced, and its exchange space (the ring) has been read
-      __threadfence();
-      __syncthreads();
-    }
     if (warp == CW) {
       if (lane == 0) {
-        // The weights depend on nothing that runs before: the first pass of the ring is requested BEFORE waiting
-        // (phase A: for the kernel that produces X; phase B: for the other CTAs' phase A).
+        // Weights depend on nothing that runs before.  Phase A: the first ring pass goes out BEFORE the wait for
+        // the kernel that produces X.  Phase B: its first ring pass was requested at the end of phase A (below), so
+        // the ring refills while this CTA's last boxes, its exchange and the barrier across the grid go by.
         const int pre = active ? min(nbox, STAGES) : 0;
-        for (int i = 0; i < pre; ++i) {
-          tma::mbar_expect_tx(&full[i], wbox_bytes);
-          sg_tma_load(ring + i * SLOT, wmap, &full[i], kbase + i * SG_BK, n0);
-        }
         if (ph == 0) {
+          for (int i = 0; i < pre; ++i) issue_w(wmap, kbase + i * SG_BK, n0, wbox_bytes, p.status);
           asm volatile("griddepcontrol.wait;" ::: "memory");
         } else {
           sg_grid_barrier(gsync, nctas, p.status);
@@ -509,93 +528,102 @@ skinny_gemm4_chain_kernel(const __grid_constant__ CUtensorMap xmapA, const __gri
             tma::mbar_expect_tx(&xbar[g], (uint32_t)nb * SG_XBOX);
             for (int j = 0; j < nb; ++j) sg_tma_load(xs + (i + j) * SG_XBOX, xmap, &xbar[g], kbase + (i + j) * SG_BK, 0);
           }
-          if (i < pre) continue;
-          const int s = i % STAGES, round = i / STAGES;
-          if (round > 0) tma::mbar_wait(&empty[s], (round - 1) & 1, p.status, 24, abortw);
-          tma::mbar_expect_tx(&full[s], wbox_bytes);
-          sg_tma_load(ring + s * SLOT, wmap, &full[s], kbase + i * SG_BK, n0);
+          if (i >= pre) issue_w(wmap, kbase + i * SG_BK, n0, wbox_bytes, p.status);
+        }
+        if (ph == 0 && activeB) {                        // phase B's first ring pass, into the slots phase A's consumers free
+          const int preB = min(nboxB, STAGES), kqB = pB.K / S4_CL;
+          for (int i = 0; i < preB; ++i) issue_w(&wmapB, rank * kqB + i * SG_BK, n0B, (uint32_t)bnB * 128, pB.status);
         }
       }
       __syncwarp();
-    } else if (active && warp < ngrp) {
+    } else if (active) {
       const uint32_t xs_u = smem_u32(xs), ring_u = smem_u32(ring);
       const int wrow = warp * 16 + (li & 1) * 8 + lr;
-      for (int i = 0; i < nbox; ++i) {
-        if (i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 25, abortw);
-        const int s = i % STAGES, round = i / STAGES;
+      const bool rows = warp < ngrp;
+      for (int i = 0; i < nbox; ++i, ++gi) {
+        if (rows && i % SG_XGROUP == 0) tma::mbar_wait(&xbar[i / SG_XGROUP], 0, p.status, 25, abortw);
+        const int s = gi % STAGES, round = gi / STAGES;
         tma::mbar_wait(&full[s], round & 1, p.status, 26, abortw);
-        const uint32_t wb = ring_u + s * SLOT, xb = xs_u + i * SG_XBOX;
-        uint32_t a[4][4];                                  // weight fragments of the box's four k-steps
+        if (rows) {
+          const uint32_t wb = ring_u + s * SLOT, xb = xs_u + i * SG_XBOX;
+          uint32_t a[4][4];                                // weight fragments of the box's four k-steps
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) sg_ldsm_x4(a[ks], wb + sg_off(wrow, ks * 2 + (li >> 1)));
+          for (int ks = 0; ks < 4; ++ks) sg_ldsm_x4(a[ks], wb + sg_off(wrow, ks * 2 + (li >> 1)));
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-          uint32_t b0[4], b1[4];                           // X^T fragments: k 0-31 and k 32-63 of the box
-          sg_ldsm_x4(b0, xb + sg_off(mt * 8 + lr, li));
-          sg_ldsm_x4(b1, xb + sg_off(mt * 8 + lr, 4 + li));
-          sg_mma(acc[mt], a[0], b0[0], b0[1]);
-          sg_mma(acc[mt], a[1], b0[2], b0[3]);
-          sg_mma(acc[mt], a[2], b1[0], b1[1]);
-          sg_mma(acc[mt], a[3], b1[2], b1[3]);
+          for (int mt = 0; mt < 4; ++mt) {
+            uint32_t b0[4], b1[4];                         // X^T fragments: k 0-31 and k 32-63 of the box
+            sg_ldsm_x4(b0, xb + sg_off(mt * 8 + lr, li));
+            sg_ldsm_x4(b1, xb + sg_off(mt * 8 + lr, 4 + li));
+            sg_mma(acc[mt], a[0], b0[0], b0[1]);
+            sg_mma(acc[mt], a[1], b0[2], b0[3]);
+            sg_mma(acc[mt], a[2], b1[0], b1[1]);
+            sg_mma(acc[mt], a[3], b1[2], b1[3]);
+          }
         }
         __syncwarp();
         if (lane == 0) tma::mbar_arrive(&empty[s]);
       }
     }
 
-    // ---- exchange: every CTA has consumed its ring (cluster barrier), whose space then takes the partial sums ----
+    // ---- exchange through the owners' shared memory (its own space: the ring already holds the next phase) ----
     if (ph == 0) {
       asm volatile("griddepcontrol.wait;" ::: "memory");               // (residual and output belong to this kernel's place in the stream)
       asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // (pairs with the arrive at entry: all CTAs run)
     }
-    if (!active) continue;                                             // (the whole cluster: same tile index)
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    constexpr int GS = (CW + 3) / 4;                                   // group slots per owner
-    float* xch = reinterpret_cast<float*>(ring);
-    if (warp < ngrp) {
-      const int g = warp, owner = g & 3, gs = g >> 2;
-      const uint32_t base_local = smem_u32(xch + ((rank * GS + gs) * SG_MAXM) * 16);
-      uint32_t base_remote;
-      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base_remote) : "r"(base_local), "r"(owner));
+    if (active) {                                                      // (the whole cluster: same tile index)
+      // every owner has read the previous phase's partial sums
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      if (warp < ngrp) {
+        const int g = warp, owner = g & 3, gs = g >> 2;
+        const uint32_t base_local = smem_u32(xch + ((rank * GS + gs) * SG_MAXM) * 16);
+        uint32_t base_remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(base_remote) : "r"(base_local), "r"(owner));
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        const int tok = mt * 8 + 2 * (lane & 3), nl = lane >> 2;       // C fragment: rows nl, nl + 8 of the group; tokens tok, tok + 1
-        const uint32_t a0 = base_remote + (uint32_t)((tok * 16 + nl) * 4);
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0), "f"(acc[mt][0]) : "memory");
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 16 * 4), "f"(acc[mt][1]) : "memory");
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 8 * 4), "f"(acc[mt][2]) : "memory");
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + (16 + 8) * 4), "f"(acc[mt][3]) : "memory");
+        for (int mt = 0; mt < 4; ++mt) {
+          const int tok = mt * 8 + 2 * (lane & 3), nl = lane >> 2;     // C fragment: rows nl, nl + 8 of the group; tokens tok, tok + 1
+          const uint32_t a0 = base_remote + (uint32_t)((tok * 16 + nl) * 4);
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0), "f"(acc[mt][0]) : "memory");
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 16 * 4), "f"(acc[mt][1]) : "memory");
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + 8 * 4), "f"(acc[mt][2]) : "memory");
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a0 + (16 + 8) * 4), "f"(acc[mt][3]) : "memory");
+        }
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+      if (warp < CW) {
+        const int gs = tid >> 7, g = rank + 4 * gs;                    // group slot, group of the tile
+        const int m = (tid & 127) >> 2, nq = (tid & 3) * 4;            // token, first of 4 rows inside the group
+        const int n = n0 + g * 16 + nq;
+        if (gs < GS && g < ngrp && m < p.M && n < p.N) {
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int src = 0; src < S4_CL; ++src) {
+            const float4 v = *reinterpret_cast<const float4*>(xch + ((src * GS + gs) * SG_MAXM + m) * 16 + nq);
+            t[0] += v.x; t[1] += v.y; t[2] += v.z; t[3] += v.w;
+          }
+          if (p.bias != nullptr) {                                     // fp32 sum + bias, one rounding (a linear layer's epilogue)
+            const uint2 bv = *reinterpret_cast<const uint2*>(p.bias + n);
+            t[0] += __uint_as_float(bv.x << 16); t[1] += __uint_as_float(bv.x & 0xffff0000u);
+            t[2] += __uint_as_float(bv.y << 16); t[3] += __uint_as_float(bv.y & 0xffff0000u);
+          }
+          if (p.res != nullptr) {
+            const uint2 rv = *reinterpret_cast<const uint2*>(p.res + (long long)m * p.res_rs + n);
+            // the product is rounded to bf16 first, as a GEMM followed by a separate add would
+            t[0] = bf16_round(t[0]) + __uint_as_float(rv.x << 16);
+            t[1] = bf16_round(t[1]) + __uint_as_float(rv.x & 0xffff0000u);
+            t[2] = bf16_round(t[2]) + __uint_as_float(rv.y << 16);
+            t[3] = bf16_round(t[3]) + __uint_as_float(rv.y & 0xffff0000u);
+          }
+          uint2 ov;
+          ov.x = bf16_pack(t[0], t[1]); ov.y = bf16_pack(t[2], t[3]);
+          *reinterpret_cast<uint2*>(p.y + (long long)m * p.y_rs + n) = ov;
+        }
       }
     }
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (warp < CW) {
-      const int gs = tid >> 7, g = rank + 4 * gs;                      // group slot, group of the tile
-      const int m = (tid & 127) >> 2, nq = (tid & 3) * 4;              // token, first of 4 rows inside the group
-      const int n = n0 + g * 16 + nq;
-      if (gs < GS && g < ngrp && m < p.M && n < p.N) {
-        float t[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int src = 0; src < S4_CL; ++src) {
-          const float4 v = *reinterpret_cast<const float4*>(xch + ((src * GS + gs) * SG_MAXM + m) * 16 + nq);
-          t[0] += v.x; t[1] += v.y; t[2] += v.z; t[3] += v.w;
-        }
-        if (p.bias != nullptr) {                                       // fp32 sum + bias, one rounding (a linear layer's epilogue)
-          const uint2 bv = *reinterpret_cast<const uint2*>(p.bias + n);
-          t[0] += __uint_as_float(bv.x << 16); t[1] += __uint_as_float(bv.x & 0xffff0000u);
-          t[2] += __uint_as_float(bv.y << 16); t[3] += __uint_as_float(bv.y & 0xffff0000u);
-        }
-        if (p.res != nullptr) {
-          const uint2 rv = *reinterpret_cast<const uint2*>(p.res + (long long)m * p.res_rs + n);
-          // the product is rounded to bf16 first, as a GEMM followed by a separate add would
-          t[0] = bf16_round(t[0]) + __uint_as_float(rv.x << 16);
-          t[1] = bf16_round(t[1]) + __uint_as_float(rv.x & 0xffff0000u);
-          t[2] = bf16_round(t[2]) + __uint_as_float(rv.y << 16);
-          t[3] = bf16_round(t[3]) + __uint_as_float(rv.y & 0xffff0000u);
-        }
-        uint2 ov;
-        ov.x = bf16_pack(t[0], t[1]); ov.y = bf16_pack(t[2], t[3]);
-        *reinterpret_cast<uint2*>(p.y + (long long)m * p.y_rs + n) = ov;
-      }
+    if (ph == 0) {
+      // everything this CTA wrote in phase A is out and fenced before its producer joins the barrier across the grid;
+      // phase A's X is no longer read
+      __threadfence();
+      __syncthreads();
     }
   }
 }
@@ -678,9 +706,8 @@ extern "C" int coda_b200_skinny_gemm_bias(const void* x, int32_t M, int32_t K, c
 
 // ---- the chain: Y_A = X_A . W_A^T + R (phase A), Y_B = Y_A . W_B^T + bias (phase B), one launch ----------------------
 namespace {
-constexpr int CH_CW = 12, CH_STAGES = 6;
-constexpr int CH_NBAR = 2 * CH_STAGES + SG_MAXXG;
-size_t chain_smem(int kq_max) { return (size_t)Skinny4Smem<CH_CW, CH_STAGES>(kq_max).total + CH_NBAR * 8 + 1024; }
+constexpr int CH_CW = 12, CH_STAGES = 5;
+size_t chain_smem(int kq_max) { return (size_t)ChainSmem<CH_CW, CH_STAGES>(kq_max).total + 1024; }
 // clusters of four CTAs of the chain kernel that are resident at once on the current device (0: unknown)
 int chain_max_clusters(int kq_max) {
   static coda_device_once once;

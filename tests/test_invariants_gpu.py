@@ -340,3 +340,35 @@ def test_stack_prefill_with_the_residual_in_the_output_projection():
         assert err < tol, (dtype, err)
         for a, b in zip(sa, sb):
             assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
+
+
+def test_captured_step_with_chained_projections_equals_the_unchained_one():
+    """With `chain_projections` a layer's output projection and the next layer's input projection leave in one launch
+    (two phases, a barrier across the grid between them).  Against the same stack with the two products as launches of
+    their own (`use_skinny_in_proj`, so that both run this library's GEMM): the same bits in every output and state."""
+    from coda_gqa_l_b200 import CoDAGQALandmarkPerf2, CoDAStack, _deep_copy_state
+    kw = dict(embed_dim=256, num_heads=4, num_kv_heads=2, window=24, num_landmarks_exact=8, num_landmarks_summary=8)
+    layers = []
+    for i in range(4):
+        torch.manual_seed(i)
+        l = CoDAGQALandmarkPerf2(**kw).eval().to(torch.bfloat16).cuda()
+        l.use_skinny_in_proj = True
+        layers.append(l)
+    sa_stack, sb_stack = CoDAStack(layers), CoDAStack(layers)
+    sa_stack.chain_projections, sb_stack.chain_projections = True, False
+    torch.manual_seed(6)
+    sa = sa_stack.init_states(batch_size=3, device="cuda", dtype=torch.bfloat16)
+    x = (torch.randn(3, 90, 256, device="cuda") * 0.5).to(torch.bfloat16)
+    sa_stack.prefill(x[:, :40], sa, block_size=16)
+    sb = [_deep_copy_state(s) for s in sa]
+    for t in range(40, 90):
+        ya = sa_stack.step_graph(x[:, t:t + 1], sa).clone()
+        yb = sb_stack.step_graph(x[:, t:t + 1], sb)
+        assert torch.equal(ya, yb), f"token {t}"
+    assert sa_stack._graph["chained"] and not sb_stack._graph["chained"]
+    assert sa_stack._graph["gsync"].tolist() == [0, 50 * 3]            # three chained launches per step, each passed its barrier
+    for l in layers:
+        assert l.device_status() == 0
+    for a, b in zip(sa, sb):
+        assert (a.pos, a.recent_idx, a.recent_filled) == (b.pos, b.recent_idx, b.recent_filled)
+        assert torch.equal(a._arena, b._arena)
