@@ -107,7 +107,7 @@ struct DecodeSmem {
     rec = o;  o += 2 * rec_stride;                  // [2] decode records (double-buffered)
     sml = o;  o += 2 * DA_CWARPS * 16 * 4;          // [2][DA_CWARPS][16]  (m, l)
     nkv = o;  o += 2 * 4 * DH;                      // [2][K row | V row] of the new token (APPEND variant)
-    cs = o;   o += 4 * DH + 16;                     // cos | sin of the position (floats), then the ring slot (int)
+    cs = o;   o += 4 * DH + 16 + 2 * DH;            // cos | sin of the position (floats), the ring slot (int), cos | sin again as bf16
     bars = o; o += (2 * DA_MAX_STAGES + 8) * 8;     // full[], empty[], q_ready[2], q_free[2], comb_full, comb_free, row_ready[2]
     total = o;
   }
@@ -354,6 +354,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     // ---- APPEND: record + new token row of a plane, from the inputs requested earlier ----
     float* sCS = reinterpret_cast<float*>(smem + L.cs);    // cos [HALF] | sin [HALF] of the token's position
     int* s_ev = reinterpret_cast<int*>(smem + L.cs + 4 * DH);
+    bf16* sCSb = reinterpret_cast<bf16*>(smem + L.cs + 4 * DH + 16);       // the same table as bf16 (its entries are bf16 values)
     int ev = 0; bool ring_full = false;
     float lam_next[2] = {0.f, 0.f}, lam_cur[2] = {0.f, 0.f};     // APPEND: sigma(lambda) of heads aw, aw + 4: plane being built / plane in its epilogue
     auto build_record = [&](int plane, int buf, const AppIn& a) {
@@ -364,28 +365,28 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       const int w0 = at * QI;
       if (w0 < G * HALF) {
         const int g = w0 / HALF, i0 = w0 % HALF;
+        // Packed bf16 arithmetic (one instruction per element pair, each result the bf16 rounding of the exact
+        // product or sum, as the reference's op-by-op bf16 arithmetic gives it): this chain stands between the
+        // token's inputs and the consumers' first tile.
+        const uint32_t* cw32 = reinterpret_cast<const uint32_t*>(sCSb);         // (cos[2j], cos[2j+1])
+        const uint32_t* sw32 = cw32 + HALF / 2;
         uint32_t sv[QI], nv[QI];
 #pragma unroll
         for (int it = 0; it < QI; ++it) {
           const int i = i0 + it;
-          const float a0 = __uint_as_float(a.fq0[it] << 16), a1 = __uint_as_float(a.fq0[it] & 0xffff0000u);
-          const float b0 = __uint_as_float(a.fq1[it] << 16), b1 = __uint_as_float(a.fq1[it] & 0xffff0000u);
-          float e0, e1;                                    // RoPE'd elements 2i, 2i+1 (primitives.py:99-113)
-          if (p.interleaved) {
-            e0 = t_sub<T>(t_mul<T>(a0, sCS[i]), t_mul<T>(a1, sCS[HALF + i]));
-            e1 = t_add<T>(t_mul<T>(a0, sCS[HALF + i]), t_mul<T>(a1, sCS[i]));
-          } else {
+          uint32_t e;                                      // RoPE'd elements 2i, 2i+1 (primitives.py:99-113)
+          if (p.interleaved) {                             // the pair (2i, 2i+1) turns by the position's angle i
+            const uint32_t cp = cw32[i >> 1], sp = sw32[i >> 1];
+            e = brot(a.fq0[it], (i & 1) ? bdup_hi(cp) : bdup_lo(cp), (i & 1) ? bdup_hi(sp) : bdup_lo(sp));
+          } else {                                         // x cos + rotate_half(x) sin, two neighbouring elements at once
             const bool lo = 2 * i < HALF;
             const int pi = lo ? 2 * i : 2 * i - HALF;
-            e0 = lo ? t_add<T>(t_mul<T>(a0, sCS[pi]), t_mul<T>(-b0, sCS[HALF + pi])) : t_add<T>(t_mul<T>(b0, sCS[pi]), t_mul<T>(a0, sCS[HALF + pi]));
-            e1 = lo ? t_add<T>(t_mul<T>(a1, sCS[pi + 1]), t_mul<T>(-b1, sCS[HALF + pi + 1])) : t_add<T>(t_mul<T>(b1, sCS[pi + 1]), t_mul<T>(a1, sCS[HALF + pi + 1]));
+            const uint32_t c2 = cw32[pi >> 1], s2 = sw32[pi >> 1];
+            e = lo ? badd2(bmul2(a.fq0[it], c2), bmul2(bneg2(a.fq1[it]), s2)) : badd2(bmul2(a.fq1[it], c2), bmul2(a.fq0[it], s2));
           }
           const uint32_t cw = a.fct[it >> 1], sw = a.fst[it >> 1];
-          const float ct = __uint_as_float((it & 1) ? (cw & 0xffff0000u) : (cw << 16));
-          const float st = __uint_as_float((it & 1) ? (sw & 0xffff0000u) : (sw << 16));
-          const float n0 = t_sub<T>(t_mul<T>(e0, ct), t_mul<T>(e1, st));
-          const float n1 = t_add<T>(t_mul<T>(e0, st), t_mul<T>(e1, ct));
-          sv[it] = pack_bf16(e0, e1); nv[it] = pack_bf16(n0, n1);
+          sv[it] = e;
+          nv[it] = brot(e, (it & 1) ? bdup_hi(cw) : bdup_lo(cw), (it & 1) ? bdup_hi(sw) : bdup_lo(sw));   // the learned rotation of the pair
         }
         bf16* srow = q_s + g * QSTR + 2 * i0;              // 4 * i0 bytes into a 272-byte row: aligned to QI words
         bf16* nrow = q_s + (G + g) * QSTR + 2 * i0;
@@ -437,7 +438,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       ev = ring_full ? r.idx : r.filled;
       if (at == 0) *s_ev = ev;
       if (p.rope_cs != nullptr) {
-        if (at < DH) sCS[at] = inv_f;                      // computed once per step for all layers (coda_b200_rope_table)
+        if (at < DH) { sCS[at] = inv_f; sCSb[at] = __float2bfloat16_rn(inv_f); }   // computed once per step for all layers (coda_b200_rope_table)
       } else if (at < HALF) {
         float ta = (float)r.pos, inv = inv_f;
         if (p.angle_bf16) { ta = bf16_round(ta); inv = bf16_round(inv); }
@@ -446,6 +447,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         float cc, ss; sincos_call(ang, &ss, &cc);
         if (p.angle_bf16) { cc = bf16_round(cc); ss = bf16_round(ss); }
         sCS[at] = bf16_round(cc); sCS[HALF + at] = bf16_round(ss);
+        sCSb[at] = __float2bfloat16_rn(cc); sCSb[HALF + at] = __float2bfloat16_rn(ss);
       }
       asm volatile("bar.sync 2, 128;" ::: "memory");       // the four auxiliary warps
       build_record(blockIdx.x, 0, in);

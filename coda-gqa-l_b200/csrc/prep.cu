@@ -112,21 +112,6 @@ template <> struct Vec16<bf16> {
   }
 };
 
-// Packed bf16 arithmetic: one instruction for two elements, each result the correctly rounded bf16 of the exact
-// product / sum -- the same value as the fp32 operation followed by a rounding to bf16 that the scalar code spells
-// out (a product of two bf16 is exact in fp32; a sum of two bf16 is exact in fp32 unless their exponents are more
-// than 16 apart, and then it is more than a bf16 rounding step away from any tie).
-__device__ __forceinline__ uint32_t bmul2(uint32_t a, uint32_t b) { uint32_t d; asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
-__device__ __forceinline__ uint32_t badd2(uint32_t a, uint32_t b) { uint32_t d; asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d; }
-__device__ __forceinline__ uint32_t bneg2(uint32_t a) { return a ^ 0x80008000u; }
-__device__ __forceinline__ uint32_t bdup_lo(uint32_t a) { return __byte_perm(a, a, 0x1010); }     // (x, y) -> (x, x)
-__device__ __forceinline__ uint32_t bdup_hi(uint32_t a) { return __byte_perm(a, a, 0x3232); }     // (x, y) -> (y, y)
-// (x, y) -> (-y, x): the second addend of a plane rotation (a, b) -> (a c - b s, b c + a s) written as
-// (a, b) * (c, c) + (-(b s), a s)
-__device__ __forceinline__ uint32_t bswap_neg(uint32_t a) { return __byte_perm(a, a, 0x1032) ^ 0x00008000u; }
-// rotation of the pair held in one word by the angle (c, s) given as duplicated words
-__device__ __forceinline__ uint32_t brot(uint32_t xy, uint32_t cc, uint32_t ss) { return badd2(bmul2(xy, cc), bswap_neg(bmul2(xy, ss))); }
-
 // Vectorised variant.  Work item = one 16-byte chunk of a head row (interleaved pairs) or the two chunks c and
 // c + Dh/2 that hold each other's RoPE partners (half-split pairs).  The noise query always rotates (even, odd)
 // neighbours of the ROTATED row (primitives.py:58-80), which lie inside one chunk, so an item is self-contained.
