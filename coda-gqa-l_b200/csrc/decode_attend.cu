@@ -429,8 +429,8 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
         if (!ring_full) p.allowed_w[(long long)b * p.Lbuf + ev] = 1;
       }
       // sigma(lambda) of this warp's two heads, kept in registers for the plane's epilogue
-      lam_next[0] = t_sigmoid<T>(__bfloat162float(a.lam0));
-      lam_next[1] = t_sigmoid<T>(__bfloat162float(a.lam1));
+      if (aw < G) lam_next[0] = t_sigmoid<T>(__bfloat162float(a.lam0));
+      if (aw + DA_AWARPS < G) lam_next[1] = t_sigmoid<T>(__bfloat162float(a.lam1));
     };
     if (APPEND && (int)blockIdx.x < nplanes) {
       const RingNow r = ring_after(p.rp, p.W, nsteps);
