@@ -210,11 +210,16 @@ constexpr int S4_CL = 4;
 template <int CW, int STAGES>
 struct Skinny4Smem {
   static constexpr int SLOT = CW * 16 * 128;
-  int x, ring, bars, total;
+  static constexpr int XCH_BYTES = S4_CL * ((CW + 3) / 4) * SG_MAXM * 16 * 4;   // partial sums [src rank][group slot][token][row] fp32
+  // The exchange space is the instance's own where X at its largest, the ring and it fit one CTA; otherwise it
+  // lies over the ring, which must then be drained in every CTA of the cluster before the first partial sum lands.
+  static constexpr bool OWN_XCH = SG_XGROUP * SG_MAXXG / 2 * SG_XBOX + STAGES * SLOT + XCH_BYTES + 2048 <= 226 * 1024;
+  int x, ring, xch, bars, total;
   __host__ __device__ explicit Skinny4Smem(int kq) {
     x = 0;
     ring = x + (kq / SG_BK) * SG_XBOX;
-    bars = ring + STAGES * SLOT;
+    xch = OWN_XCH ? ring + STAGES * SLOT : ring;
+    bars = ring + STAGES * SLOT + (OWN_XCH ? XCH_BYTES : 0);
     total = bars + (2 * STAGES + SG_MAXXG) * 8;
   }
 };
@@ -305,13 +310,16 @@ skinny_gemm4_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     }
   }
 
-  // ---- exchange: every CTA has consumed its ring (cluster barrier), whose space then takes the partial sums ----
+  // ---- exchange: partial sums go to the owners' shared memory.  Where that space lies over the ring, every CTA of the
+  // cluster must have consumed its ring first (cluster barrier); where it is the instance's own, a warp sends its sums
+  // as soon as it has them, under the other CTAs' last boxes ----
   asm volatile("griddepcontrol.wait;" ::: "memory");                   // (bias, residual and output belong to this kernel's place in the stream)
   asm volatile("barrier.cluster.wait.aligned;" ::: "memory");          // (pairs with the arrive at entry: all CTAs run)
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-  // xch[src rank][owner's group slot gs][token 32][row 16] fp32, in the OWNER's shared memory (its ring space)
+  if (!Skinny4Smem<CW, STAGES>::OWN_XCH)
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  // xch[src rank][owner's group slot gs][token 32][row 16] fp32, in the OWNER's shared memory
   constexpr int GS = (CW + 3) / 4;                                     // group slots per owner
-  float* xch = reinterpret_cast<float*>(ring);
+  float* xch = reinterpret_cast<float*>(smem + L.xch);
   if (warp < ngrp) {
     const int g = warp, owner = g & 3, gs = g >> 2;
     const uint32_t base_local = smem_u32(xch + ((rank * GS + gs) * SG_MAXM) * 16);
