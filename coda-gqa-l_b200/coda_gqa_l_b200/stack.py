@@ -122,7 +122,7 @@ class CoDAStack(nn.Module):
                  and all(layer.chain_ready(x_static.shape[0], x_static.dtype, st, self.layers[i + 1] if i + 1 < n_layers else None)
                          for i, (layer, st) in enumerate(zip(self.layers, states))))
         gsync = torch.zeros(2, dtype=torch.int32, device=dev) if chain else None      # the chained launches' grid barrier
-        def body(h):
+        def body(h, before_layers=None):
             # Routing of the tokens this step evicts needs the states only: all layers' in one launch up front
             # (one layer's routing is a chain of memory round trips; side by side they are bandwidth-bound), so
             # that a layer's own chain is projection -> new token's write -> attention -> output projection.
@@ -136,6 +136,8 @@ class CoDAStack(nn.Module):
                 check(lib.coda_b200_rope_table(C.byref(plan[0]), rps[0], l0._consts(dev, x_static.dtype)[0].data_ptr(),
                                                rope_cs.data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
                       "coda_b200_rope_table")
+            if before_layers is not None:
+                before_layers()                      # (the host-fed graph joins its input copy here)
             if chain:
                 # per layer: attention (writes the new token) -> [output projection + residual | next layer's input
                 # projection] in one launch; the first layer's input projection is a launch of its own
@@ -161,9 +163,15 @@ class CoDAStack(nn.Module):
         x_pin.copy_(x_static)
         out_pin = torch.empty(out_static.shape, dtype=out_static.dtype).pin_memory()
         gh = torch.cuda.CUDAGraph()
+        copy_stream = torch.cuda.Stream(device=dev)
         with torch.cuda.graph(gh):
-            x_static.copy_(x_pin, non_blocking=True)
-            out_h = body(x_static)
+            # the routing launch and the cos / sin table need the states only: the input's copy from the host is a
+            # branch of its own beside them and joins ahead of the first layer
+            cur = torch.cuda.current_stream(dev)
+            copy_stream.wait_stream(cur)
+            with torch.cuda.stream(copy_stream):
+                x_static.copy_(x_pin, non_blocking=True)
+            out_h = body(x_static, before_layers=lambda: cur.wait_stream(copy_stream))
             out_pin.copy_(out_h, non_blocking=True)
         # Everything the graph's launches point at is kept alive with it (plan, table, the layers' derived weight and
         # constant tensors), and what they were is noted so that a replay after any of them changed re-captures.
