@@ -57,7 +57,14 @@ struct DecodeParams {
   const float* rope_cs;                           // optional: cos [Dh/2] | sin [Dh/2] of the token's position, precomputed
   bf16* k_buf; bf16* v_buf; uint8_t* allowed_w; float* g_recent;
   int early_trigger;
+  unsigned int hkv_magic;                         // ceil(2^32 / Hkv): plane -> (state, KV head) without a division
 };
+
+// plane = b * Hkv + hk for plane < 2^20 and Hkv < 2^8 (then the rounded-up reciprocal is exact)
+__device__ __forceinline__ void plane_split(const DecodeParams& p, int plane, int& b, int& hk) {
+  b = p.Hkv == 1 ? plane : (int)__umulhi((unsigned int)plane, p.hkv_magic);
+  hk = plane - b * p.Hkv;
+}
 
 using tma::smem_u32; using tma::mbar_init; using tma::mbar_expect_tx; using tma::mbar_arrive; using tma::mbar_try;
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, int* abort) { tma::mbar_wait(bar, parity, status, code, abort); }
@@ -254,7 +261,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
   float inv_f = 0.f;
   const int at = tid - DA_CWARPS * 32;                   // index among the 128 auxiliary threads
   auto load_inputs = [&](int plane, AppIn& a) {
-    const int b = plane / p.Hkv, hk = plane % p.Hkv;
+    int b, hk; plane_split(p, plane, b, hk);
     const bf16* qrow = p.q_raw + (long long)b * p.q_bs + (long long)hk * G * DH;
 #pragma unroll
     for (int it = 0; it < QI; ++it) a.fq0[it] = a.fq1[it] = 0u;
@@ -290,7 +297,10 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     }
     if (at == 0 && p.gated) a.gate = p.gate_logit[(long long)b * p.gate_bs];
 #pragma unroll
-    for (int k = 0; k < MB; ++k) { const int m = at + k * (DA_AWARPS * 32); a.am[k] = m < p.Lbuf ? p.allowed[(long long)b * p.Lbuf + m] : (uint8_t)0; }
+    for (int k = 0; k < MB; ++k) {
+      if (k * (DA_AWARPS * 32) >= p.Lbuf) break;           // (the same for every thread)
+      const int m = at + k * (DA_AWARPS * 32); a.am[k] = m < p.Lbuf ? p.allowed[(long long)b * p.Lbuf + m] : (uint8_t)0;
+    }
   };
   if (APPEND) {
     // requested before the block barrier below, i.e. before the producer's first tile: a small load issued behind
@@ -359,7 +369,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
     float lam_next[2] = {0.f, 0.f}, lam_cur[2] = {0.f, 0.f};     // APPEND: sigma(lambda) of heads aw, aw + 4: plane being built / plane in its epilogue
     auto build_record = [&](int plane, int buf, const AppIn& a) {
       using T = bf16;
-      const int b = plane / p.Hkv, hk = plane % p.Hkv;
+      int b, hk; plane_split(p, plane, b, hk);
       unsigned char* rec = rec0 + buf * L.rec_stride;
       bf16* q_s = reinterpret_cast<bf16*>(rec);
       const int w0 = at * QI;
@@ -401,6 +411,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       uint8_t* mk = rec + mask_off;
 #pragma unroll
       for (int k = 0; k < MB; ++k) {
+        if (k * (DA_AWARPS * 32) >= DecodeRecord::mask_bytes(p.Lbuf)) break;   // (the same for every thread)
         const int m = at + k * (DA_AWARPS * 32);
         if (m < DecodeRecord::mask_bytes(p.Lbuf)) mk[m] = m < p.Lbuf ? (m == ev ? (uint8_t)1 : a.am[k]) : (uint8_t)0;
       }
@@ -467,7 +478,7 @@ decode_attend_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_cons
       }
       mbar_wait(&q_ready[i & 1], (i >> 1) & 1, p.status, 7, abortw);   // lambda comes from the plane's record (a bulk copy: observed through its own barrier)
       mbar_wait(comb_full, i & 1, p.status, 5, abortw);
-      const int b = plane / p.Hkv, hk = plane % p.Hkv;
+      int b, hk; plane_split(p, plane, b, hk);
       const float* sLam = reinterpret_cast<const float*>(rec0 + (i & 1) * L.rec_stride + lam_off);
       const float lam_a = APPEND ? lam_cur[0] : sLam[aw];                 // heads aw and aw + 4 of the group (G <= 8)
       const float lam_b = APPEND ? lam_cur[1] : sLam[(aw + DA_AWARPS) & 7];
@@ -737,6 +748,8 @@ int check_common(const coda_layer_cfg* cfg, const coda_state_ptrs* st, const voi
   CODA_REQUIRE(!cfg->head_norm_full || norm_w, CODA_ERR_ARG, "decode_attend: head-norm weight missing");
   CODA_REQUIRE(((uintptr_t)st->k_buf % 16 == 0) && ((uintptr_t)st->v_buf % 16 == 0) && ((uintptr_t)qrec % 16 == 0), CODA_ERR_ARG,
                "decode_attend: k_buf / v_buf / record buffer must be 16-byte aligned");
+  // (the kernel splits a plane index into state and KV head by a reciprocal multiply, exact below this bound)
+  CODA_REQUIRE((long long)cfg->B * cfg->Hkv * cfg->Hkv < (1ll << 32), CODA_ERR_LIMIT, "decode_attend: %d states x %d KV heads exceed the plane index range", cfg->B, cfg->Hkv);
   return CODA_OK;
 }
 
@@ -744,6 +757,7 @@ DecodeParams make_params(const coda_layer_cfg* cfg, const coda_state_ptrs* st, v
                          int64_t out_bs, int32_t* status) {
   DecodeParams p;
   p.B = cfg->B; p.H = cfg->H; p.Hkv = cfg->Hkv; p.G = cfg->H / cfg->Hkv; p.Lbuf = cfg->W + cfg->Me + cfg->Ms;
+  p.hkv_magic = (unsigned int)((0x100000000ull + (unsigned long long)cfg->Hkv - 1) / (unsigned long long)cfg->Hkv);
   p.mask_unused = cfg->mask_unused; p.norm_full = cfg->head_norm_full; p.interleaved = cfg->rope_interleaved;
   p.angle_bf16 = cfg->angle_dtype == CODA_BF16; p.stages = 0; p.eps = cfg->eps;
   p.scale_log2 = 1.4426950408889634f / sqrtf((float)cfg->Dh);
